@@ -1,0 +1,354 @@
+"""Benchmark of the quantized linear-layer hot path on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference]
+
+Workload (BASELINE.json configs[1]): NVFP4 batched decode, 8 lanes, one 27B-style dense layer with
+hidden 5120 -- q 5120->6144, k and v 5120->1024, o 6144->5120, gate and up 5120->17408,
+down 17408->5120 -- repeated over 64 layers of distinct synthetic weights (12.27 GB, far larger than
+L2, so no timed iteration finds its weights cached). A step is one pass over all layers. The
+metric is the weight-stream rate: algorithmic bytes (codes + scales + divisors + activations in
+and out) per second, whole job.
+
+At N > 1 (launched under torch.distributed.run) every matrix is sharded column-wise over N and each
+rank streams its own rows: strong scaling, no collective in the timed region (outputs stay
+sharded). Rank 0 prints one JSON line.
+
+`--impl reference` times the reference's CPU implementation of the same path (its host
+dequantizer compiled in place when available, else the oracle port, plus the fp64 product) on
+the host cores, each step a bounded sample of the workload.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+# (name, n, k, input): the seven matrices of one layer and which activation buffer each reads
+LAYER = [("q", 6144, 5120, "h"), ("k", 1024, 5120, "h"), ("v", 1024, 5120, "h"), ("o", 5120, 6144, "a"),
+         ("gate", 17408, 5120, "h"), ("up", 17408, 5120, "h"), ("down", 5120, 17408, "m")]
+INPUT_WIDTH = {"h": 5120, "a": 6144, "m": 17408}
+GROUPS = [["q", "k", "v"], ["o"], ["gate", "up"], ["down"]]  # calls that share one activation read
+METRIC = "nvfp4_gemv_hbm_gbs"
+UNIT = "GB/s"
+
+
+def weight_bytes(n: int, k: int) -> int:
+    return n * k // 2 + n * k // 16 + 4
+
+
+def layer_algorithmic_bytes(tokens: int, world: int = 1) -> int:
+    """Bytes one rank must move for one layer: its shard of every payload, each activation read
+    once per call that uses it, each output written once."""
+    total = 0
+    for _, n, k, _ in LAYER:
+        total += weight_bytes(n // world, k) + tokens * k * 2 + tokens * (n // world) * 2
+    return total
+
+
+def measured_peak() -> tuple[float, str]:
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            return float(json.load(f)["hbm_gbs"]), "measured"
+    return 6650.0, "fallback"
+
+
+class ClockSampler:
+    """Samples SM clock and throttle reasons through NVML (read-only) while the timed region runs."""
+
+    REASONS = {0x4: "sw_power_cap", 0x8: "hw_slowdown", 0x20: "sw_thermal_slowdown", 0x40: "hw_thermal_slowdown",
+               0x80: "hw_power_brake_slowdown"}
+
+    def __init__(self, index: int) -> None:
+        self.samples: list[int] = []
+        self.reasons: set[str] = set()
+        self.max_mhz = None
+        self._stop = threading.Event()
+        self._thread = None
+        try:
+            import pynvml
+
+            pynvml.nvmlInit()
+            self._nvml = pynvml
+            self._handle = pynvml.nvmlDeviceGetHandleByIndex(index)
+            self.max_mhz = pynvml.nvmlDeviceGetMaxClockInfo(self._handle, pynvml.NVML_CLOCK_SM)
+        except Exception:  # NVML missing: the bench still runs, clocks are reported as unknown
+            self._nvml = None
+
+    def _run(self) -> None:
+        while not self._stop.is_set():
+            try:
+                self.samples.append(self._nvml.nvmlDeviceGetClockInfo(self._handle, self._nvml.NVML_CLOCK_SM))
+                mask = self._nvml.nvmlDeviceGetCurrentClocksEventReasons(self._handle)
+                for bit, name in self.REASONS.items():
+                    if mask & bit:
+                        self.reasons.add(name)
+            except Exception:
+                pass
+            self._stop.wait(0.02)
+
+    def __enter__(self):
+        if self._nvml is not None:
+            self._thread = threading.Thread(target=self._run, daemon=True)
+            self._thread.start()
+        return self
+
+    def __exit__(self, *exc):
+        self._stop.set()
+        if self._thread is not None:
+            self._thread.join()
+
+    def summary(self) -> dict:
+        s = sorted(self.samples)
+        return {"sm_mhz": s[len(s) // 2] if s else None, "sm_max_mhz": self.max_mhz, "reasons": sorted(self.reasons),
+                "samples": len(s)}
+
+
+# ---- the CPU arm --------------------------------------------------------------------------------
+
+def cpu_sample(seconds_target: float = 12.0):
+    """Times the reference's CPU path on a bounded sample: rows of the q matrix (K = 5120) at
+    8 tokens -- dequantize to the logical FP32 weight, then the threaded fp64 product -- and
+    returns (GB/s of algorithmic bytes, description dict)."""
+    import numpy as np
+    import torch
+
+    from ignis_b200 import nvfp4
+    from oracle.oracle import Oracle, default_threads
+
+    orc = Oracle()
+    kind, dequant = "port", orc.nvfp4_dequant
+    try:
+        from oracle.oracle import Reference
+
+        dequant = Reference().nvfp4_dequant
+        kind = "reference"
+    except (FileNotFoundError, OSError):
+        pass
+    threads = default_threads()
+    k, tokens = 5120, 8
+    rng = np.random.default_rng(20261126)
+    x = torch.randn(tokens, k, generator=torch.Generator().manual_seed(20261126)).to(torch.bfloat16).float().numpy()
+
+    def run(rows: int) -> float:
+        codes = rng.integers(0, 256, (rows, k // 2)).astype(np.uint8)
+        natural = torch.from_numpy((np.abs(rng.standard_normal((rows, k // 16))) + 0.1).astype(np.float32))
+        scales = nvfp4.swizzle_scales(natural.to(torch.float8_e4m3fn).view(torch.uint8).numpy())
+        t0 = time.perf_counter()
+        w = dequant(codes, scales, rows, k, 448.0)
+        orc.gemm_f64(w, x, threads)
+        return time.perf_counter() - t0
+
+    probe_rows = 256
+    t = run(probe_rows)
+    rows = int(min(6144, max(256, seconds_target / max(t, 1e-6) * probe_rows))) // 128 * 128
+    elapsed = run(rows)
+    nbytes = weight_bytes(rows, k) + tokens * k * 2 + tokens * rows * 2
+    desc = {"kind": kind, "cores": threads,
+            "sample": f"{rows} rows of q (K=5120) at 8 tokens: host dequantize ({kind}, 1 thread) + fp64 product "
+                      f"({threads} threads), {elapsed:.2f} s"}
+    return nbytes / elapsed / 1e9, desc
+
+
+def run_reference_arm(args) -> None:
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    values = []
+    desc = {}
+    for _ in range(args.warmup):
+        cpu_sample(2.0)
+    t0 = time.perf_counter()
+    for _ in range(max(1, args.steps)):
+        v, desc = cpu_sample(6.0)
+        values.append(v)
+    total = time.perf_counter() - t0
+    value = sum(values) / len(values)
+    line = {"impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus, "steps": args.steps,
+            "warmup": args.warmup, "ms_per_step": total / max(1, args.steps) * 1e3, "higher_is_better": True,
+            "scaling": "strong", "vs_baseline": None, "dtype": "f64", "data": "synthetic",
+            "config": {"workload": "configs[1]: NVFP4 decode, 8 lanes, 27B-style dense layer (CPU: a bounded row sample per step)"},
+            "cpu_baseline": {"value": value, "unit": UNIT, **desc},
+            "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
+    print(json.dumps(line))
+
+
+# ---- the CUDA arm -------------------------------------------------------------------------------
+
+def build_workload(layers: int, rank: int, world: int, tokens: int, device):
+    import torch
+
+    from ignis_b200 import nvfp4
+
+    gen = torch.Generator(device=device)
+    weights = []
+    for layer in range(layers):
+        entry = {}
+        for idx, (name, n, k, _) in enumerate(LAYER):
+            rows = n // world
+            gen.manual_seed(20261126 + (layer * 16 + idx) * 64 + rank)
+            codes = torch.randint(0, 256, (rows, k // 2), dtype=torch.uint8, device=device, generator=gen)
+            natural = (torch.randn((rows, k // 16), device=device, generator=gen).abs() + 0.1).to(torch.float8_e4m3fn)
+            natural = natural.view(torch.uint8)
+            stored = natural.reshape(rows // 128, 4, 32, k // 64, 4).permute(0, 3, 2, 1, 4).contiguous().reshape(-1)
+            entry[name] = nvfp4.Weight(codes, stored, rows, k, 448.0, 448.0)
+        weights.append(entry)
+    cpu_gen = torch.Generator().manual_seed(20261126)
+    host_inputs = {key: torch.randn(tokens, width, generator=cpu_gen).to(torch.bfloat16).pin_memory()
+                   for key, width in INPUT_WIDTH.items()}
+    inputs = {key: t.to(device) for key, t in host_inputs.items()}
+    outputs = {name: torch.empty(tokens, n // world, dtype=torch.bfloat16, device=device) for name, n, _, _ in LAYER}
+    return weights, host_inputs, inputs, outputs
+
+
+def run_cuda_arm(args) -> None:
+    import torch
+    import torch.distributed as dist
+
+    from ignis_b200 import nvfp4
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: the product has no CPU path (use --impl reference for the CPU arm)")
+    torch.cuda.set_device(local_rank)
+    device = torch.device("cuda", local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=device)
+    nvfp4.prepare()
+    tokens = args.tokens
+    weights, host_inputs, inputs, outputs = build_workload(args.layers, rank, world, tokens, device)
+    by_name = {name: (n, k, src) for name, n, k, src in LAYER}
+    calls = GROUPS if args.group else [[name] for name, *_ in LAYER]
+
+    def one_step() -> None:
+        for layer in weights:
+            for names in calls:
+                src = inputs[by_name[names[0]][2]]
+                if len(names) == 1:
+                    nvfp4.linear(src, layer[names[0]], out=outputs[names[0]])
+                else:
+                    nvfp4.linear_group(src, [layer[nm] for nm in names], outs=[outputs[nm] for nm in names])
+
+    launches_per_step = len(calls) * args.layers
+    stream = torch.cuda.Stream()
+    graph = None
+    with torch.cuda.stream(stream):
+        one_step()  # untimed: first-launch costs
+        stream.synchronize()
+        if args.graph:
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph, stream=stream):
+                one_step()
+        step = graph.replay if graph is not None else one_step
+
+        def barrier() -> None:
+            if world > 1:
+                dist.barrier()
+            torch.cuda.synchronize()
+
+        for _ in range(args.warmup):
+            step()
+        barrier()
+        start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        with ClockSampler(local_rank) as clocks:
+            start.record(stream)
+            for _ in range(args.steps):
+                step()
+            stop.record(stream)
+            barrier()
+        device_ms = start.elapsed_time(stop)
+
+        # end to end: host activations in, last output back, every step
+        result_host = torch.empty_like(outputs["down"], device="cpu").pin_memory()
+        for _ in range(2):
+            for key in inputs:
+                inputs[key].copy_(host_inputs[key], non_blocking=True)
+            step()
+            result_host.copy_(outputs["down"], non_blocking=True)
+        barrier()
+        e2e_start, e2e_stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e2e_start.record(stream)
+        for _ in range(args.steps):
+            for key in inputs:
+                inputs[key].copy_(host_inputs[key], non_blocking=True)
+            step()
+            result_host.copy_(outputs["down"], non_blocking=True)
+        e2e_stop.record(stream)
+        barrier()
+        e2e_ms = e2e_start.elapsed_time(e2e_stop)
+
+    times = torch.tensor([device_ms, e2e_ms], dtype=torch.float64, device=device)
+    if world > 1:
+        dist.all_reduce(times, op=dist.ReduceOp.MAX)
+    device_ms, e2e_ms = times.tolist()
+    if world > 1:
+        dist.destroy_process_group()
+    if rank != 0:
+        return
+
+    per_rank_bytes = layer_algorithmic_bytes(tokens, world) * args.layers
+    job_bytes = per_rank_bytes * world
+    ms_per_step = device_ms / args.steps
+    value = job_bytes / (ms_per_step * 1e-3) / 1e9
+    e2e_value = job_bytes / (e2e_ms / args.steps * 1e-3) / 1e9
+    peak, peak_kind = measured_peak()
+    per_gpu = value / world
+    line = {
+        "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f16xf16->f32",
+        "data": "synthetic",
+        "config": {"workload": "configs[1]: NVFP4 decode, 8 lanes (M=8), 27B-style dense layer (q,k,v,o,gate,up,down), hidden 5120",
+                   "layers": args.layers, "tokens": tokens, "policy": "A16", "sharding": f"column-wise over N, {world} rank(s)",
+                   "calls_per_layer": len(calls), "cuda_graph": bool(args.graph),
+                   "l2": "inputs larger than L2: %.2f GB of distinct weights per rank per step" % (per_rank_bytes / 1e9),
+                   "collective": "none (outputs stay sharded)"},
+        "e2e": {"value": e2e_value, "unit": UNIT,
+                "h2d_bytes_per_step": sum(t.numel() * 2 for t in host_inputs.values()),
+                "d2h_bytes_per_step": outputs["down"].numel() * 2},
+        "gpu_launches": launches_per_step * args.steps,
+        "clocks": clocks.summary(),
+        "roofline": {"bound": "hbm", "achieved": per_gpu, "peak": peak, "unit": "GB/s", "frac": per_gpu / peak,
+                     "peak_source": f"{peak_kind} copy bandwidth", "frac_of_nominal_8000": per_gpu / 8000.0,
+                     "kernel": "nvfp4_gemv_kernel<1>", "bytes_per_launch": per_rank_bytes / launches_per_step,
+                     "us_per_launch": ms_per_step * 1e3 / launches_per_step, "traffic": TRAFFIC_PER_LAUNCH},
+    }
+    if world == 1 and not args.no_cpu_baseline:
+        v, desc = cpu_sample()
+        line["cpu_baseline"] = {"value": v, "unit": UNIT, **desc}
+    print(json.dumps(line))
+
+
+# dram__bytes_read.sum + dram__bytes_write.sum per launch of the dominant kernel from the ncu
+# capture summarised under profiles/; None until a capture exists.
+TRAFFIC_PER_LAUNCH = None
+
+
+def main() -> None:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="b200q", choices=["b200q", "reference"])
+    ap.add_argument("--layers", type=int, default=64)
+    ap.add_argument("--tokens", type=int, default=8)
+    ap.add_argument("--group", type=int, default=1, help="1: q|k|v and gate|up share one launch each; 0: seven launches per layer")
+    ap.add_argument("--graph", type=int, default=1, help="replay the step as one CUDA graph")
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        run_reference_arm(args)
+    else:
+        run_cuda_arm(args)
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,64 @@
+"""Loads ``libignis_b200.so`` and declares the C ABI of ``include/*.h`` for ctypes."""
+from __future__ import annotations
+
+import ctypes as C
+import os
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(HERE, "libignis_b200.so")
+
+_lib = None
+
+
+class LibraryMissing(RuntimeError):
+    pass
+
+
+class Nvfp4Weight(C.Structure):
+    """``b200q_nvfp4_weight`` (include/b200q_nvfp4.h)."""
+
+    _fields_ = [("codes", C.c_void_p), ("scales", C.c_void_p), ("n", C.c_uint32), ("k", C.c_uint32),
+                ("weight_scale_divisor", C.c_float), ("input_scale_divisor", C.c_float)]
+
+
+class Workspace(C.Structure):
+    """``b200q_nvfp4_workspace`` / ``ignis_trellis_workspace``: base pointer and byte count."""
+
+    _fields_ = [("base", C.c_void_p), ("bytes", C.c_uint64)]
+
+
+# name -> (restype, argtypes); every symbol the headers declare appears here.
+NVFP4_SYMBOLS = {
+    "b200q_nvfp4_prepare": (C.c_int32, []),
+    "b200q_nvfp4_workspace_bytes": (C.c_uint64, [C.c_uint32, C.c_uint32, C.c_uint32, C.c_uint32]),
+    "b200q_nvfp4_linear": (C.c_int32, [C.POINTER(Nvfp4Weight), C.c_void_p, C.c_uint32, C.c_void_p, C.c_uint32,
+                                       C.c_uint32, C.c_uint32, C.POINTER(Workspace), C.c_void_p]),
+    "b200q_nvfp4_linear_group": (C.c_int32, [C.POINTER(C.POINTER(Nvfp4Weight)), C.c_uint32, C.c_void_p, C.c_uint32,
+                                             C.POINTER(C.c_void_p), C.POINTER(C.c_uint32), C.c_uint32, C.c_uint32,
+                                             C.POINTER(Workspace), C.c_void_p]),
+    "b200q_nvfp4_linear_swiglu": (C.c_int32, [C.POINTER(Nvfp4Weight), C.c_void_p, C.c_uint32, C.c_void_p, C.c_uint32,
+                                              C.c_uint32, C.POINTER(Workspace), C.c_void_p]),
+    "b200q_nvfp4_dequantize": (C.c_int32, [C.POINTER(Nvfp4Weight), C.c_void_p, C.c_void_p]),
+    "b200q_nvfp4_quantize_activations": (C.c_int32, [C.c_void_p, C.c_uint32, C.c_uint32, C.c_float, C.c_void_p,
+                                                     C.c_void_p, C.c_void_p]),
+    "b200q_nvfp4_last_error": (C.c_char_p, []),
+}
+
+ALL_SYMBOLS = dict(NVFP4_SYMBOLS)
+
+
+def load() -> C.CDLL:
+    """The library handle; raises LibraryMissing when it was never built (no fallback exists)."""
+    global _lib
+    if _lib is not None:
+        return _lib
+    if not os.path.exists(LIB_PATH):
+        raise LibraryMissing(f"{LIB_PATH} is missing: build it with `python -m ignis_b200.build` "
+                             "(there is no CPU or PyTorch fallback)")
+    lib = C.CDLL(LIB_PATH)
+    for name, (restype, argtypes) in ALL_SYMBOLS.items():
+        fn = getattr(lib, name)
+        fn.restype = restype
+        fn.argtypes = argtypes
+    _lib = lib
+    return lib

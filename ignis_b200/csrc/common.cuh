@@ -1,0 +1,135 @@
+// Shared host/device helpers of the library: the error channel, per-device state, launch helper
+// with programmatic dependent launch, and the PTX wrappers the kernels use. sm_100a only.
+#ifndef B200Q_COMMON_CUH
+#define B200Q_COMMON_CUH
+
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+
+#include <cstdarg>
+#include <cstdint>
+#include <cstdio>
+
+namespace b200q {
+
+// ---- error channel ---------------------------------------------------------------------------
+// One thread-local message per op family, as the reference keeps (trellis_linear.cu:29-44).
+struct ErrorSlot {
+  char text[512];
+};
+ErrorSlot &nvfp4_error();
+ErrorSlot &trellis_error();
+ErrorSlot &moe_error();
+
+inline int32_t fail(ErrorSlot &slot, const char *fmt, ...) {
+  va_list args;
+  va_start(args, fmt);
+  vsnprintf(slot.text, sizeof(slot.text), fmt, args);
+  va_end(args);
+  return -1;
+}
+
+// ---- per-device state --------------------------------------------------------------------------
+struct DeviceState {
+  bool prepared = false;
+  int sm_count = 0;
+  int pdl = 1;           // programmatic dependent launch between the kernels of a call chain
+  int gemv_rb = 0;       // B200Q_GEMV_RM: 32-row groups per CTA of the NVFP4 decode kernel (0: auto)
+  int gemv_kc = 0;       // B200Q_GEMV_KC: its cluster size (0: auto)
+  int gemv_ctas_per_sm = 2;
+  int sm_cap = 0;        // IGNIS_TRELLIS_SM_CAP
+};
+// State of the current device, nullptr (and `slot` filled) when the device query fails.
+DeviceState *device_state(ErrorSlot &slot);
+// Prepares the current device once (thread-safe). 0 on success.
+int32_t prepare_device(ErrorSlot &slot);
+
+// ---- launch helper -----------------------------------------------------------------------------
+// Launches with the programmatic-stream-serialization attribute when `pdl` is set: the kernel may
+// start while its predecessor in the stream drains, and orders itself with griddep_wait().
+template <typename... KernelArgs, typename... Args>
+inline cudaError_t launch(void (*kernel)(KernelArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                          bool pdl, Args... args) {
+  cudaLaunchConfig_t config = {};
+  config.gridDim = grid;
+  config.blockDim = block;
+  config.dynamicSmemBytes = smem;
+  config.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  config.attrs = attr;
+  config.numAttrs = pdl ? 1 : 0;
+  return cudaLaunchKernelEx(&config, kernel, static_cast<KernelArgs>(args)...);
+}
+
+#ifdef __CUDACC__
+// ---- PTX wrappers ------------------------------------------------------------------------------
+
+// Blocks until every grid this one depends on has completed and its writes are visible. A no-op
+// when the grid was launched without a programmatic dependency.
+__device__ __forceinline__ void griddep_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+// Lets the next grid in the stream start its independent prologue.
+__device__ __forceinline__ void griddep_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
+// 32 bytes of a read-only stream that is touched once: no L1 allocation.
+__device__ __forceinline__ void ldg256_stream(const void *p, uint32_t (&r)[8]) {
+  asm volatile("ld.global.nc.L1::no_allocate.v8.b32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7])
+               : "l"(p));
+}
+__device__ __forceinline__ uint4 ldg128_stream(const void *p) {
+  uint4 v;
+  asm volatile("ld.global.nc.L1::no_allocate.v4.b32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p));
+  return v;
+}
+// 16 bytes of data an earlier kernel in the stream may have written while this grid was already
+// resident (programmatic dependent launch): an ordinary coherent load, never the read-only path.
+__device__ __forceinline__ uint4 ldg128_coherent(const void *p) {
+  uint4 v;
+  asm volatile("ld.global.v4.b32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p) : "memory");
+  return v;
+}
+
+// Four packed E2M1 pairs (one 32-bit word, eight codes) to four half2: word byte i -> h[i], the
+// low nibble in the low half.
+__device__ __forceinline__ void e2m1x8_to_half2x4(uint32_t word, uint32_t (&h)[4]) {
+  asm("{\n"
+      ".reg .b8 b0, b1, b2, b3;\n"
+      "mov.b32 {b0, b1, b2, b3}, %4;\n"
+      "cvt.rn.f16x2.e2m1x2 %0, b0;\n"
+      "cvt.rn.f16x2.e2m1x2 %1, b1;\n"
+      "cvt.rn.f16x2.e2m1x2 %2, b2;\n"
+      "cvt.rn.f16x2.e2m1x2 %3, b3;\n"
+      "}\n"
+      : "=r"(h[0]), "=r"(h[1]), "=r"(h[2]), "=r"(h[3])
+      : "r"(word));
+}
+
+// Two E4M3 bytes (low 16 bits of `pair`) to half2, byte 0 in the low half.
+__device__ __forceinline__ uint32_t e4m3x2_to_half2(uint32_t pair) {
+  uint32_t h;
+  asm("cvt.rn.f16x2.e4m3x2 %0, %1;" : "=r"(h) : "h"(static_cast<uint16_t>(pair)));
+  return h;
+}
+
+__device__ __forceinline__ uint32_t hmul2_u32(uint32_t a, uint32_t b) {
+  const __half2 r = __hmul2(*reinterpret_cast<const __half2 *>(&a), *reinterpret_cast<const __half2 *>(&b));
+  return *reinterpret_cast<const uint32_t *>(&r);
+}
+
+// D += A(16x16, row) * B(16x8, col), fp16 operands, fp32 accumulate.
+__device__ __forceinline__ void mma_f16_f32(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
+                                            uint32_t b0, uint32_t b1) {
+  asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+               : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+               : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+__device__ __forceinline__ float bf16_bits_to_f32(uint32_t bits16) { return __uint_as_float(bits16 << 16); }
+#endif  // __CUDACC__
+
+}  // namespace b200q
+
+#endif  // B200Q_COMMON_CUH

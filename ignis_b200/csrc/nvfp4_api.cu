@@ -1,0 +1,177 @@
+// Entry points of include/b200q_nvfp4.h: argument checks, route choice and launches.
+#include "../../include/b200q_nvfp4.h"
+
+#include "nvfp4_internal.cuh"
+
+#include <cmath>
+
+namespace b200q {
+namespace {
+
+bool aligned(const void *p, uintptr_t a) { return (reinterpret_cast<uintptr_t>(p) & (a - 1)) == 0; }
+
+int32_t check_weight(ErrorSlot &slot, const b200q_nvfp4_weight *w, const char *what) {
+  if (w == nullptr) return fail(slot, "%s: weight is NULL", what);
+  if (w->codes == nullptr || w->scales == nullptr) return fail(slot, "%s: weight planes are NULL", what);
+  if (w->n == 0 || (w->n % 128u) != 0) return fail(slot, "%s: n = %u is not a positive multiple of 128", what, w->n);
+  if (w->k == 0 || (w->k % 64u) != 0) return fail(slot, "%s: k = %u is not a positive multiple of 64", what, w->k);
+  if (!aligned(w->codes, 32)) return fail(slot, "%s: the code plane is not 32-byte aligned", what);
+  if (!aligned(w->scales, 16)) return fail(slot, "%s: the scale plane is not 16-byte aligned", what);
+  if (!std::isfinite(w->weight_scale_divisor) || !(w->weight_scale_divisor > 0.0f)) {
+    return fail(slot, "%s: weight_scale_divisor must be finite and positive", what);
+  }
+  return 0;
+}
+
+const DeviceState *prepared_state(ErrorSlot &slot, const char *what) {
+  const DeviceState *dev = device_state(slot);
+  if (dev == nullptr) return nullptr;
+  if (!dev->prepared) {
+    fail(slot, "%s: the device was not prepared (call b200q_nvfp4_prepare at load)", what);
+    return nullptr;
+  }
+  return dev;
+}
+
+// The decode route over `count` weights that share x, in passes of at most 32 tokens.
+int32_t decode_route(ErrorSlot &slot, const DeviceState &dev, const b200q_nvfp4_weight *const *w, uint32_t count,
+                     const void *x, uint32_t tokens, void *const *y, const uint32_t *ldy, uint32_t epilogue,
+                     cudaStream_t stream) {
+  const uint32_t k = w[0]->k;
+  const bool swiglu = (epilogue & kEpilogueSwiglu) != 0u;
+  const size_t out_elem = (epilogue & kEpilogueF32) ? 4u : 2u;
+  uint32_t groups = 0;
+  for (uint32_t i = 0; i < count; ++i) groups += w[i]->n / 32u;
+  for (uint32_t t0 = 0; t0 < tokens; t0 += B200Q_NVFP4_DECODE_MAX_TOKENS) {
+    const uint32_t pass = tokens - t0 < B200Q_NVFP4_DECODE_MAX_TOKENS ? tokens - t0 : B200Q_NVFP4_DECODE_MAX_TOKENS;
+    const int nt = pass <= 8 ? 1 : (pass <= 16 ? 2 : 4);
+    GemvParams p = {};
+    p.x = static_cast<const uint16_t *>(x) + static_cast<size_t>(t0) * k;
+    p.count = count;
+    p.k = k;
+    p.ksteps = (k + 255u) / 256u;
+    p.tokens = pass;
+    p.epilogue = epilogue;
+    const GemvPlan plan = gemv_plan(dev, groups, p.ksteps, nt, swiglu);
+    const uint32_t rows_per_cta = static_cast<uint32_t>(swiglu ? plan.rm / 2 : plan.rm);
+    uint32_t ctas = 0;
+    for (uint32_t i = 0; i < count; ++i) {
+      GemvWeight &g = p.w[i];
+      g.codes = static_cast<const uint8_t *>(w[i]->codes);
+      g.scales = static_cast<const uint8_t *>(w[i]->scales);
+      g.y = static_cast<uint8_t *>(y[i]) + static_cast<size_t>(t0) * ldy[i] * out_elem;
+      g.n = w[i]->n;
+      g.ldy = ldy[i];
+      g.inv_dw = 1.0f / w[i]->weight_scale_divisor;
+      g.block_begin = ctas;
+      const uint32_t out_groups = swiglu ? w[i]->n / 64u : w[i]->n / 32u;
+      ctas += (out_groups + rows_per_cta - 1) / rows_per_cta * static_cast<uint32_t>(plan.kc);
+    }
+    if (gemv_launch(slot, dev, p, nt, plan, ctas, stream) != 0) return -1;
+  }
+  return 0;
+}
+
+int32_t linear_group_impl(const b200q_nvfp4_weight *const *w, uint32_t count, const void *x, uint32_t tokens,
+                          void *const *y, const uint32_t *ldy, uint32_t epilogue, uint32_t policy,
+                          const b200q_nvfp4_workspace *workspace, void *stream, const char *what) {
+  ErrorSlot &slot = nvfp4_error();
+  (void)workspace;
+  if (w == nullptr || y == nullptr || ldy == nullptr) return fail(slot, "%s: NULL argument array", what);
+  if (count == 0 || count > B200Q_NVFP4_MAX_GROUP) return fail(slot, "%s: count = %u is outside 1..%d", what, count, B200Q_NVFP4_MAX_GROUP);
+  if (tokens == 0) return fail(slot, "%s: tokens must be positive", what);
+  if (policy != B200Q_NVFP4_A16_ONLY && policy != B200Q_NVFP4_ALLOW_A4) return fail(slot, "%s: unknown policy %u", what, policy);
+  if ((epilogue & ~(kEpilogueAdd | kEpilogueF32 | kEpilogueSwiglu)) != 0u) return fail(slot, "%s: unknown epilogue 0x%x", what, epilogue);
+  if (x == nullptr || !aligned(x, 16)) return fail(slot, "%s: x is NULL or not 16-byte aligned", what);
+  const bool swiglu = (epilogue & kEpilogueSwiglu) != 0u;
+  for (uint32_t i = 0; i < count; ++i) {
+    if (check_weight(slot, w[i], what) != 0) return -1;
+    if (w[i]->k != w[0]->k) return fail(slot, "%s: the weights of a group must share k", what);
+    if (y[i] == nullptr) return fail(slot, "%s: output %u is NULL", what, i);
+    const uint32_t width = swiglu ? w[i]->n / 2u : w[i]->n;
+    if (ldy[i] < width) return fail(slot, "%s: ldy[%u] = %u is narrower than the output (%u)", what, i, ldy[i], width);
+    if (swiglu && (w[i]->n % 256u) != 0) return fail(slot, "%s: a fused gate_up parent needs n a multiple of 256", what);
+  }
+  const DeviceState *dev = prepared_state(slot, what);
+  if (dev == nullptr) return -1;
+  // Every token count takes the decode route (the weights are re-read once per 32 tokens); the
+  // tensor-core prefill route replaces it for wide calls under B200Q_NVFP4_ALLOW_A4.
+  return decode_route(slot, *dev, w, count, x, tokens, y, ldy, epilogue, static_cast<cudaStream_t>(stream));
+}
+
+}  // namespace
+}  // namespace b200q
+
+using namespace b200q;
+
+extern "C" {
+
+int32_t b200q_nvfp4_prepare(void) {
+  ErrorSlot &slot = nvfp4_error();
+  if (prepare_device(slot) != 0) return -1;
+  return gemv_prepare(slot);
+}
+
+uint64_t b200q_nvfp4_workspace_bytes(uint32_t n, uint32_t k, uint32_t policy, uint32_t tokens) {
+  if (n == 0 || (n % 128u) != 0 || k == 0 || (k % 64u) != 0 || tokens == 0) return 0;
+  if (policy != B200Q_NVFP4_A16_ONLY && policy != B200Q_NVFP4_ALLOW_A4) return 0;
+  // The decode route keeps its partial sums in distributed shared memory and needs no global
+  // scratch; a caller still reserves one aligned line so a workspace pointer is never NULL.
+  return 256;
+}
+
+int32_t b200q_nvfp4_linear(const b200q_nvfp4_weight *w, const void *x, uint32_t tokens, void *y, uint32_t ldy,
+                           uint32_t epilogue, uint32_t policy, const b200q_nvfp4_workspace *workspace, void *stream) {
+  if ((epilogue & ~(B200Q_NVFP4_ADD | B200Q_NVFP4_OUT_F32)) != 0u) {
+    return fail(nvfp4_error(), "b200q_nvfp4_linear: unknown epilogue 0x%x", epilogue);
+  }
+  const b200q_nvfp4_weight *ws[1] = {w};
+  void *ys[1] = {y};
+  const uint32_t lds[1] = {ldy};
+  return linear_group_impl(ws, 1, x, tokens, ys, lds, epilogue, policy, workspace, stream, "b200q_nvfp4_linear");
+}
+
+int32_t b200q_nvfp4_linear_group(const b200q_nvfp4_weight *const *w, uint32_t count, const void *x, uint32_t tokens,
+                                 void *const *y, const uint32_t *ldy, uint32_t epilogue, uint32_t policy,
+                                 const b200q_nvfp4_workspace *workspace, void *stream) {
+  if ((epilogue & ~(B200Q_NVFP4_ADD | B200Q_NVFP4_OUT_F32)) != 0u) {
+    return fail(nvfp4_error(), "b200q_nvfp4_linear_group: unknown epilogue 0x%x", epilogue);
+  }
+  return linear_group_impl(w, count, x, tokens, y, ldy, epilogue, policy, workspace, stream, "b200q_nvfp4_linear_group");
+}
+
+int32_t b200q_nvfp4_linear_swiglu(const b200q_nvfp4_weight *gate_up, const void *x, uint32_t tokens, void *h, uint32_t ldh,
+                                  uint32_t policy, const b200q_nvfp4_workspace *workspace, void *stream) {
+  const b200q_nvfp4_weight *ws[1] = {gate_up};
+  void *ys[1] = {h};
+  const uint32_t lds[1] = {ldh};
+  return linear_group_impl(ws, 1, x, tokens, ys, lds, kEpilogueSwiglu, policy, workspace, stream, "b200q_nvfp4_linear_swiglu");
+}
+
+int32_t b200q_nvfp4_dequantize(const b200q_nvfp4_weight *w, float *out, void *stream) {
+  ErrorSlot &slot = nvfp4_error();
+  if (check_weight(slot, w, "b200q_nvfp4_dequantize") != 0) return -1;
+  if (out == nullptr || !aligned(out, 16)) return fail(slot, "b200q_nvfp4_dequantize: out is NULL or not 16-byte aligned");
+  if (prepared_state(slot, "b200q_nvfp4_dequantize") == nullptr) return -1;
+  return dequantize_launch(slot, static_cast<const uint8_t *>(w->codes), static_cast<const uint8_t *>(w->scales), w->n, w->k,
+                           w->weight_scale_divisor, out, static_cast<cudaStream_t>(stream));
+}
+
+int32_t b200q_nvfp4_quantize_activations(const void *x, uint32_t tokens, uint32_t k, float input_scale_divisor, void *codes,
+                                         void *scales, void *stream) {
+  ErrorSlot &slot = nvfp4_error();
+  if (x == nullptr || codes == nullptr || scales == nullptr) return fail(slot, "b200q_nvfp4_quantize_activations: NULL argument");
+  if (tokens == 0 || k == 0 || (k % 16u) != 0) return fail(slot, "b200q_nvfp4_quantize_activations: tokens must be positive and k a positive multiple of 16");
+  if (!aligned(x, 16) || !aligned(codes, 8)) return fail(slot, "b200q_nvfp4_quantize_activations: x must be 16-byte and codes 8-byte aligned");
+  if (!std::isfinite(input_scale_divisor) || !(input_scale_divisor > 0.0f)) {
+    return fail(slot, "b200q_nvfp4_quantize_activations: input_scale_divisor must be finite and positive");
+  }
+  if (prepared_state(slot, "b200q_nvfp4_quantize_activations") == nullptr) return -1;
+  return quantize_activations_launch(slot, static_cast<const uint16_t *>(x), tokens, k, input_scale_divisor,
+                                     static_cast<uint8_t *>(codes), static_cast<uint8_t *>(scales),
+                                     static_cast<cudaStream_t>(stream));
+}
+
+const char *b200q_nvfp4_last_error(void) { return nvfp4_error().text; }
+
+}  // extern "C"

@@ -1,0 +1,58 @@
+// Types shared by the NVFP4 kernels and their entry points.
+#ifndef B200Q_NVFP4_INTERNAL_CUH
+#define B200Q_NVFP4_INTERNAL_CUH
+
+#include "common.cuh"
+
+namespace b200q {
+
+constexpr uint32_t kMaxGroup = 8;  // B200Q_NVFP4_MAX_GROUP
+
+// Epilogue bits as the kernels see them (the public STORE/ADD/OUT_F32 plus the fused SwiGLU).
+constexpr uint32_t kEpilogueAdd = 1u;
+constexpr uint32_t kEpilogueF32 = 0x100u;
+constexpr uint32_t kEpilogueSwiglu = 0x200u;
+
+struct GemvWeight {
+  const uint8_t *codes;
+  const uint8_t *scales;
+  void *y;               // [tokens][ldy], BF16 or float32
+  uint32_t n;
+  uint32_t ldy;
+  float inv_dw;          // 1 / weight_scale_divisor
+  uint32_t block_begin;  // first CTA of this weight in the launch
+};
+
+struct GemvParams {
+  GemvWeight w[kMaxGroup];
+  const uint16_t *x;  // BF16 [tokens][k]
+  uint32_t count;
+  uint32_t k;
+  uint32_t ksteps;    // ceil(k / 256)
+  uint32_t tokens;    // of this pass, at most 8 NT
+  uint32_t epilogue;
+  uint32_t rm;        // 32-row groups per CTA: 1, 2, 4 or 8
+  uint32_t kc;        // cluster size: K slices across CTAs
+  uint32_t xs_steps;  // steps of activation fragments shared memory holds at a time
+};
+
+struct GemvPlan {
+  int rm;
+  int kc;
+  uint32_t row_blocks;
+  uint32_t xs_steps;
+};
+
+int32_t gemv_prepare(ErrorSlot &slot);
+GemvPlan gemv_plan(const DeviceState &dev, uint32_t groups, uint32_t ksteps, int nt, bool swiglu);
+int32_t gemv_launch(ErrorSlot &slot, const DeviceState &dev, GemvParams &p, int nt, const GemvPlan &plan, uint32_t ctas,
+                    cudaStream_t stream);
+
+int32_t dequantize_launch(ErrorSlot &slot, const uint8_t *codes, const uint8_t *scales, uint32_t n, uint32_t k, float d_w,
+                          float *out, cudaStream_t stream);
+int32_t quantize_activations_launch(ErrorSlot &slot, const uint16_t *x, uint32_t tokens, uint32_t k, float d_in,
+                                    uint8_t *codes, uint8_t *scales, cudaStream_t stream);
+
+}  // namespace b200q
+
+#endif

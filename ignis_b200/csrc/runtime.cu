@@ -1,0 +1,80 @@
+// Error slots and per-device state shared by every op family.
+#include "common.cuh"
+
+#include <cstdlib>
+#include <cstring>
+#include <mutex>
+
+namespace b200q {
+
+ErrorSlot &nvfp4_error() {
+  static thread_local ErrorSlot slot = {""};
+  return slot;
+}
+ErrorSlot &trellis_error() {
+  static thread_local ErrorSlot slot = {""};
+  return slot;
+}
+ErrorSlot &moe_error() {
+  static thread_local ErrorSlot slot = {""};
+  return slot;
+}
+
+namespace {
+constexpr int kMaxDevices = 64;
+DeviceState g_state[kMaxDevices];
+std::mutex g_mutex;
+
+// A measurement switch read once per prepare, as the reference reads its own
+// (kernel/src/process_environment.h:17-34): unset or unparsable gives `fallback`.
+int env_int(const char *name, int fallback) {
+  const char *v = std::getenv(name);
+  if (v == nullptr || *v == '\0') return fallback;
+  char *end = nullptr;
+  const long parsed = std::strtol(v, &end, 10);
+  return (end == v) ? fallback : static_cast<int>(parsed);
+}
+}  // namespace
+
+DeviceState *device_state(ErrorSlot &slot) {
+  int device = -1;
+  const cudaError_t err = cudaGetDevice(&device);
+  if (err != cudaSuccess) {
+    fail(slot, "no CUDA device: %s", cudaGetErrorString(err));
+    return nullptr;
+  }
+  if (device < 0 || device >= kMaxDevices) {
+    fail(slot, "device ordinal %d is outside the supported range", device);
+    return nullptr;
+  }
+  return &g_state[device];
+}
+
+int32_t prepare_device(ErrorSlot &slot) {
+  std::lock_guard<std::mutex> lock(g_mutex);
+  DeviceState *state = device_state(slot);
+  if (state == nullptr) return -1;
+  // A repeated call re-reads the environment switches (tests and sweeps flip them between
+  // calls); everything else it computes is a function of the device alone.
+  int device = 0;
+  cudaGetDevice(&device);
+  cudaDeviceProp prop;
+  cudaError_t err = cudaGetDeviceProperties(&prop, device);
+  if (err != cudaSuccess) return fail(slot, "cudaGetDeviceProperties: %s", cudaGetErrorString(err));
+  if (prop.major != 10) {
+    return fail(slot, "this library is built for sm_100a only; device %d is sm_%d%d", device, prop.major, prop.minor);
+  }
+  DeviceState fresh;
+  fresh.sm_count = prop.multiProcessorCount;
+  fresh.pdl = env_int("B200Q_PDL", 1) != 0;
+  fresh.gemv_rb = env_int("B200Q_GEMV_RM", 0);
+  fresh.gemv_kc = env_int("B200Q_GEMV_KC", 0);
+  fresh.gemv_ctas_per_sm = env_int("B200Q_GEMV_CTAS_PER_SM", 2);
+  fresh.sm_cap = env_int("IGNIS_TRELLIS_SM_CAP", 0);
+  if (fresh.sm_cap < 0 || fresh.sm_cap > fresh.sm_count) fresh.sm_cap = 0;
+  fresh.prepared = true;
+  *state = fresh;
+  return 0;
+}
+
+}  // namespace b200q

@@ -1,0 +1,126 @@
+/* NVFP4 linear layers for B200 (sm_100a): flat C ABI.
+ *
+ * The reference engine has no flat C entry for its NVFP4 linear: the op is the C++ family
+ * ninfer::ops::linear (kernel/vendor/include/ninfer/ops/linear.h:20-119), called inside its kernel
+ * leaf, and the weight crosses the real step ABI as an `ignis_bound_tensor`
+ * (kernel/include/ignis_model.h:79-100: qdata, scales, shape, weight_scale_divisor,
+ * input_scale_divisor). This header gives that op the same flat conventions the reference uses
+ * for its trellis and MoE ops (kernel/include/ignis_trellis_linear.h): plain pointers and sizes,
+ * caller-owned buffers, 0 / -1 return codes with a thread-local message.
+ *
+ * Weight format (unchanged from the reference's artifact, `blockscale-k16-m128x4-v1`,
+ * kernel/vendor/src/ops/linear/nvfp4/nvfp4_format.cpp:38-71, nvfp4_codec.cuh:32-42):
+ *   codes   E2M1, [n][k/2] row-major, the even k in the low nibble;
+ *   scales  E4M3FN (non-negative, finite), one per 16 along k, swizzled: the scale of
+ *           (row r, group g) is byte ((r/128)*(k/64) + g/4)*512 + (r%32)*16 + ((r%128)/32)*4 + g%4;
+ *   w[r][c] = E2M1(code) * E4M3(scale) / weight_scale_divisor.
+ * n is a positive multiple of 128, k a positive multiple of 64.
+ *
+ * Conventions of every entry point:
+ * - Activations are device-resident, token-major BF16: x [tokens][k] contiguous, 16-byte aligned
+ *   (the reference's `[K,T]` tensor with dimension zero fastest). Outputs are [tokens][ldy].
+ * - A call enqueues on `stream` (a cudaStream_t, NULL for the legacy stream), allocates nothing
+ *   and never synchronizes the host. Scratch lives in the caller's workspace, sized by
+ *   b200q_nvfp4_workspace_bytes from the load's maxima; one workspace serves the calls of one
+ *   stream in sequence.
+ * - Results are deterministic: no floating-point atomics, fixed reduction order.
+ * - Return 0 on success, -1 on an argument the op does not accept or a launch error; the reason
+ *   is in b200q_nvfp4_last_error(). There is no CPU fallback: without a prepared CUDA device the
+ *   calls fail.
+ */
+#ifndef B200Q_NVFP4_H
+#define B200Q_NVFP4_H
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* The fields of the reference's bound NVFP4 tensor that the linear reads
+ * (kernel/include/ignis_model.h:79-100; kernel/vendor/src/core/tensor.h:49-75). */
+typedef struct b200q_nvfp4_weight {
+  const void *codes;  /* device, 32-byte aligned */
+  const void *scales; /* device, 16-byte aligned */
+  uint32_t n;
+  uint32_t k;
+  float weight_scale_divisor; /* finite, positive */
+  float input_scale_divisor;  /* finite, positive; read by the W4A4 policy only */
+} b200q_nvfp4_weight;
+
+typedef struct b200q_nvfp4_workspace {
+  void *base;     /* device, 256-byte aligned */
+  uint64_t bytes; /* at least what b200q_nvfp4_workspace_bytes asked for */
+} b200q_nvfp4_workspace;
+
+/* Activation-compute policy, the reference's LinearPolicy (ninfer/ops/linear.h:20-24):
+ * A16 multiplies the exactly decoded weights with the BF16 activations; ALLOW_A4 lets wide calls
+ * quantize the activations to NVFP4 (nvfp4_codec.cuh:81-110) and multiply in FP4. */
+#define B200Q_NVFP4_A16_ONLY 0
+#define B200Q_NVFP4_ALLOW_A4 1
+
+/* Epilogues. STORE and ADD write BF16; OR-ing B200Q_NVFP4_OUT_F32 makes `y` float32 (the FP32
+ * accumulators before the final rounding, for numerical checks). ADD is the residual add of the
+ * reference's linear_add (linear_add/nvfp4/nvfp4_linear_add_epilogue.cuh:9-17): one rounding of
+ * acc + float(y). */
+#define B200Q_NVFP4_STORE 0
+#define B200Q_NVFP4_ADD 1
+#define B200Q_NVFP4_OUT_F32 0x100
+
+/* The most weights one b200q_nvfp4_linear_group call takes. */
+#define B200Q_NVFP4_MAX_GROUP 8
+/* The most tokens the decode route (weights streamed once for all tokens) serves per pass. */
+#define B200Q_NVFP4_DECODE_MAX_TOKENS 32
+
+/* Prepares the current device: kernel attributes, SM count, environment switches. Once per
+ * device at load, outside any stream capture; the ops refuse to run on an unprepared device.
+ * Stands where the reference configures its ops at ignis_model_load
+ * (kernel/include/ignis_model.h:820). */
+int32_t b200q_nvfp4_prepare(void);
+
+/* Workspace bytes of a call at (n, k) with `tokens` tokens under `policy`; 0 for a shape the ops
+ * refuse. Mirrors linear_workspace_capacity_bytes (ninfer/ops/linear.h:31-35). */
+uint64_t b200q_nvfp4_workspace_bytes(uint32_t n, uint32_t k, uint32_t policy, uint32_t tokens);
+
+/* y[t][r] = sum_c w[r][c] x[t][c] through `epilogue`: ninfer::ops::linear
+ * (ninfer/ops/linear.h:99-119) and, with B200Q_NVFP4_ADD, ninfer::ops::linear_add. */
+int32_t b200q_nvfp4_linear(const b200q_nvfp4_weight *w, const void *x, uint32_t tokens, void *y,
+                           uint32_t ldy, uint32_t epilogue, uint32_t policy,
+                           const b200q_nvfp4_workspace *workspace, void *stream);
+
+/* `count` weights of the same k applied to the same x in one pass, weight i writing
+ * y[i][t][..ldy[i]]: the split-output projections the reference fuses into one parent
+ * (attn_input_proj's q|k|gate|v rows, kernel/vendor/src/ops/linear/nvfp4/nvfp4_w4a4_tma.cu:23-30;
+ * gdn_input_proj's qkv|z), kept here as separate matrices sharing the activation read. */
+int32_t b200q_nvfp4_linear_group(const b200q_nvfp4_weight *const *w, uint32_t count, const void *x,
+                                 uint32_t tokens, void *const *y, const uint32_t *ldy,
+                                 uint32_t epilogue, uint32_t policy,
+                                 const b200q_nvfp4_workspace *workspace, void *stream);
+
+/* h[t][c] = BF16(silu(g) * u), g and u the products with rows [0, n/2) and [n/2, n) of the fused
+ * gate_up parent: ninfer::ops::linear_swiglu at decode widths
+ * (linear_swiglu/nvfp4/nvfp4_linear_swiglu_decode.cu:57-69), one rounding from FP32. */
+int32_t b200q_nvfp4_linear_swiglu(const b200q_nvfp4_weight *gate_up, const void *x, uint32_t tokens,
+                                  void *h, uint32_t ldh, uint32_t policy,
+                                  const b200q_nvfp4_workspace *workspace, void *stream);
+
+/* The logical weight as float32 [n][k], bit for bit the reference's host dequantizer
+ * (kernel/vendor/tests/ops/quantized_weight.h:642-690). Not on the serving path: the seam the
+ * decode is held to, as ignis_trellis_reconstruct is for the trellis. */
+int32_t b200q_nvfp4_dequantize(const b200q_nvfp4_weight *w, float *out, void *stream);
+
+/* The activation block quantizer of the W4A4 route as a seam: x BF16 [tokens][k] to E2M1 codes
+ * [tokens][k/2] and E4M3 scales [tokens][k/16], token-major, bit for bit
+ * kernel/vendor/src/ops/linear/nvfp4/nvfp4_codec.cuh:81-110 (nvfp4_w4a4_mma.cuh:388-409). */
+int32_t b200q_nvfp4_quantize_activations(const void *x, uint32_t tokens, uint32_t k,
+                                         float input_scale_divisor, void *codes, void *scales,
+                                         void *stream);
+
+/* Thread-local message from the most recent failed call. Never NULL. */
+const char *b200q_nvfp4_last_error(void);
+
+#ifdef __cplusplus
+}
+#endif
+
+#endif /* B200Q_NVFP4_H */
