@@ -44,7 +44,27 @@ NVFP4_SYMBOLS = {
     "b200q_nvfp4_last_error": (C.c_char_p, []),
 }
 
-ALL_SYMBOLS = dict(NVFP4_SYMBOLS)
+class TrellisWeight(C.Structure):
+    """``ignis_trellis_weight`` (include/ignis_trellis_linear.h), 40 bytes."""
+
+    _fields_ = [("trellis", C.c_void_p), ("suh", C.c_void_p), ("svh", C.c_void_p), ("k2", C.c_uint32),
+                ("in_", C.c_uint32), ("out", C.c_uint32), ("tile_stride", C.c_uint32)]
+
+
+TRELLIS_SYMBOLS = {
+    "ignis_trellis_prepare": (C.c_int32, []),
+    "ignis_trellis_sm_cap": (C.c_uint32, []),
+    "ignis_trellis_workspace_bytes": (C.c_uint64, [C.c_uint32, C.c_uint32, C.c_uint32, C.c_uint32]),
+    "ignis_trellis_workspace_init": (C.c_int32, [C.POINTER(Workspace), C.c_void_p]),
+    "ignis_trellis_linear": (C.c_int32, [C.POINTER(TrellisWeight), C.c_void_p, C.c_uint32, C.c_void_p, C.c_uint32,
+                                         C.c_uint32, C.POINTER(Workspace), C.c_void_p]),
+    "ignis_trellis_linear_swiglu": (C.c_int32, [C.POINTER(TrellisWeight), C.POINTER(TrellisWeight), C.c_void_p,
+                                                C.c_uint32, C.c_void_p, C.c_uint32, C.POINTER(Workspace), C.c_void_p]),
+    "ignis_trellis_reconstruct": (C.c_int32, [C.POINTER(TrellisWeight), C.c_void_p, C.c_void_p]),
+    "ignis_trellis_last_error": (C.c_char_p, []),
+}
+
+ALL_SYMBOLS = {**NVFP4_SYMBOLS, **TRELLIS_SYMBOLS}
 
 
 def load() -> C.CDLL:

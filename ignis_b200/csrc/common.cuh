@@ -38,6 +38,7 @@ struct DeviceState {
   int gemv_rb = 0;       // B200Q_GEMV_RM: 32-row groups per CTA of the NVFP4 decode kernel (0: auto)
   int gemv_kc = 0;       // B200Q_GEMV_KC: its cluster size (0: auto)
   int gemv_ctas_per_sm = 2;
+  int gemv_xu = 8;       // B200Q_GEMV_XU: words per row of 8 decoded by the hardware E2M1 conversion
   int sm_cap = 0;        // IGNIS_TRELLIS_SM_CAP
 };
 // State of the current device, nullptr (and `slot` filled) when the device query fails.
@@ -89,6 +90,12 @@ __device__ __forceinline__ uint4 ldg128_stream(const void *p) {
 __device__ __forceinline__ uint4 ldg128_coherent(const void *p) {
   uint4 v;
   asm volatile("ld.global.v4.b32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p) : "memory");
+  return v;
+}
+
+__device__ __forceinline__ uint2 ldg64_coherent(const void *p) {
+  uint2 v;
+  asm volatile("ld.global.v2.b32 {%0,%1}, [%2];" : "=r"(v.x), "=r"(v.y) : "l"(p) : "memory");
   return v;
 }
 

@@ -9,12 +9,11 @@
 //    scales share one 16-byte word of the swizzled scale plane, and walks K in steps of 256. Per
 //    step a lane loads 32 contiguous bytes of codes per row (one 256-bit load each: the 64
 //    weights of one scale tile) and the 16 scale bytes of those 4 rows x 4 groups.
-//  * Codes go to fp16 with the hardware E2M1 conversion and are multiplied by their E4M3 scale in
-//    fp16 (exact: at most 6 significant bits, magnitude within [2^-10, 2688]). The products are
-//    the A fragments of mma.sync m16n8k16 (fp16 in, fp32 accumulate); the tokens are the MMA's N,
-//    so 1 and 8 tokens cost the same weight traffic and the same decode. The order of k inside an
-//    MMA is permuted (lane t supplies the k of its own 64-weight chunk): a sum does not care, and
-//    both operands use the same permutation.
+//  * Codes become fp16 and are multiplied by their E4M3 scale in fp16 (exact: at most 6
+//    significant bits). The products are the A fragments of mma.sync m16n8k16 (fp16 in, fp32
+//    accumulate); the tokens are the MMA's N, so 1 and 8 tokens cost the same weight traffic and
+//    the same decode. The order of k inside an MMA is permuted (lane t supplies the k of its own
+//    64-weight chunk): a sum does not care, and both operands use the same permutation.
 //  * The CTA first rewrites its K slice of the BF16 activations as fp16 B fragments in shared
 //    memory, scaled per (token, slice) by a power of two so the largest magnitude sits in
 //    [2^13, 2^14): every BF16 value within 2^-27 of the slice's maximum converts exactly. The
@@ -67,17 +66,42 @@ __device__ __forceinline__ void load_stage(Stage &st, const WarpRows &rows, int 
   }
 }
 
+// Eight E2M1 codes (one word) to four half2 on the integer pipe alone. A code's three magnitude
+// bits and its sign are placed in a byte as [s 0 0 0 e1 e0 m 0]: read as the high byte of an fp16
+// (low byte zero) that is the code's value times 2^-14 exactly, the subnormal code 0.5 included.
+// The registers pair the codes (0,2) (4,6) (1,3) (5,7); the activation fragments of such a word
+// are stored in the same order.
+__device__ __forceinline__ void e2m1x8_to_half2x4_alu(uint32_t w, uint32_t (&h)[4]) {
+  const uint32_t even = ((w << 1) & 0x0E0E0E0Eu) | ((w << 4) & 0x80808080u);  // codes 0,2,4,6
+  const uint32_t odd = ((w >> 3) & 0x0E0E0E0Eu) | (w & 0x80808080u);          // codes 1,3,5,7
+  h[0] = __byte_perm(even, 0u, 0x1404);
+  h[1] = __byte_perm(even, 0u, 0x3424);
+  h[2] = __byte_perm(odd, 0u, 0x1404);
+  h[3] = __byte_perm(odd, 0u, 0x3424);
+}
+
 // One K step of a warp: 4 rows x 64 weights per lane against the prepared activations of the
-// step (`xs_step`: [8 chunks][NT tiles][32 lanes] uint4).
-template <int NT>
+// step (`xs_step`: [8 words][NT tiles][32 slots] uint4, slot = lane ^ (word << 2)).
+//
+// The hardware E2M1 conversion runs on the quarter-rate special-function pipe, which alone would
+// cap the kernel below the HBM rate, so only the first XU of a row's 8 words take it; the others
+// are decoded with integer operations. Both kinds end as (code * scale * 2^-7) in fp16: the
+// converted words are multiplied by scale * 2^-7, the integer-decoded ones (already times 2^-14)
+// by scale * 2^7, all exact; the epilogue multiplies by 2^7.
+template <int NT, int XU>
 __device__ __forceinline__ void compute_stage(const Stage &st, const uint4 *xs_step, int lane, float (&acc)[2][NT][4]) {
-  uint32_t sp[4][2];
+  uint32_t sp_lo[4][2], sp_hi[4][2];
   {
     const uint32_t w[4] = {st.sc.x, st.sc.y, st.sc.z, st.sc.w};
+    const uint32_t down = 0x20002000u;  // half2(2^-7, 2^-7)
+    const uint32_t up = 0x58005800u;    // half2(2^7, 2^7)
 #pragma unroll
     for (int q = 0; q < 4; ++q) {
-      sp[q][0] = e4m3x2_to_half2(w[q] & 0xFFFFu);
-      sp[q][1] = e4m3x2_to_half2(w[q] >> 16);
+      const uint32_t a = e4m3x2_to_half2(w[q] & 0xFFFFu), b = e4m3x2_to_half2(w[q] >> 16);
+      sp_lo[q][0] = hmul2_u32(a, down);
+      sp_lo[q][1] = hmul2_u32(b, down);
+      sp_hi[q][0] = hmul2_u32(a, up);
+      sp_hi[q][1] = hmul2_u32(b, up);
     }
   }
 #pragma unroll
@@ -85,8 +109,14 @@ __device__ __forceinline__ void compute_stage(const Stage &st, const uint4 *xs_s
     uint32_t h[4][4];
 #pragma unroll
     for (int q = 0; q < 4; ++q) {
-      e2m1x8_to_half2x4(st.c[q][i], h[q]);
-      const uint32_t pair = sp[q][i >> 2];
+      uint32_t pair;
+      if (i < XU) {
+        e2m1x8_to_half2x4(st.c[q][i], h[q]);
+        pair = sp_lo[q][i >> 2];
+      } else {
+        e2m1x8_to_half2x4_alu(st.c[q][i], h[q]);
+        pair = sp_hi[q][i >> 2];
+      }
       const __half2 p2 = *reinterpret_cast<const __half2 *>(&pair);
       const __half2 sb = ((i >> 1) & 1) ? __high2half2(p2) : __low2half2(p2);
       const uint32_t sbu = *reinterpret_cast<const uint32_t *>(&sb);
@@ -95,7 +125,7 @@ __device__ __forceinline__ void compute_stage(const Stage &st, const uint4 *xs_s
     }
 #pragma unroll
     for (int tt = 0; tt < NT; ++tt) {
-      const uint4 v = xs_step[(i * NT + tt) * 32 + lane];
+      const uint4 v = xs_step[(i * NT + tt) * 32 + (lane ^ (i << 2))];
       mma_f16_f32(acc[0][tt], h[0][0], h[1][0], h[0][1], h[1][1], v.x, v.y);
       mma_f16_f32(acc[1][tt], h[2][0], h[3][0], h[2][1], h[3][1], v.x, v.y);
       mma_f16_f32(acc[0][tt], h[0][2], h[1][2], h[0][3], h[1][3], v.z, v.w);
@@ -125,27 +155,80 @@ __device__ __forceinline__ float4 ld_cluster_f4(const void *local_smem, uint32_t
 
 __device__ __forceinline__ float silu_f32(float v) { return v / (1.0f + __expf(-v)); }
 
+// Eight BF16 values (one 16-byte chunk) times a power of two, as fp16, in the order the MMA
+// fragments of word `i` want: natural pairs for a hardware-converted word, the pairs (0,2) (4,6)
+// (1,3) (5,7) for an integer-decoded one.
+template <int XU>
+__device__ __forceinline__ uint4 convert_chunk(const uint4 v, float scale, int i) {
+  const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+  float f[8];
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    f[2 * j] = bf16_bits_to_f32(w[j] & 0xFFFFu) * scale;
+    f[2 * j + 1] = __uint_as_float(w[j] & 0xFFFF0000u) * scale;
+  }
+  __half2 r[4];
+  if (i < XU) {
+    r[0] = __floats2half2_rn(f[0], f[1]);
+    r[1] = __floats2half2_rn(f[2], f[3]);
+    r[2] = __floats2half2_rn(f[4], f[5]);
+    r[3] = __floats2half2_rn(f[6], f[7]);
+  } else {
+    r[0] = __floats2half2_rn(f[0], f[2]);
+    r[1] = __floats2half2_rn(f[4], f[6]);
+    r[2] = __floats2half2_rn(f[1], f[3]);
+    r[3] = __floats2half2_rn(f[5], f[7]);
+  }
+  return make_uint4(*reinterpret_cast<uint32_t *>(&r[0]), *reinterpret_cast<uint32_t *>(&r[1]),
+                    *reinterpret_cast<uint32_t *>(&r[2]), *reinterpret_cast<uint32_t *>(&r[3]));
+}
+
+__device__ __forceinline__ float chunk_amax(const uint4 v) {
+  const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+  float amax = 0.0f;
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    amax = fmaxf(amax, fabsf(bf16_bits_to_f32(w[j] & 0xFFFFu)));
+    amax = fmaxf(amax, fabsf(__uint_as_float(w[j] & 0xFFFF0000u)));
+  }
+  return amax;
+}
+
+constexpr int kPrepRegs = 5;  // chunks a lane keeps in registers between the amax and the store
+
 // Rewrites steps [cb, ce) of the activations as scaled fp16 B fragments. Warp w prepares token
-// slots w, w + 8, ...; the slot's inverse scale goes to inv_s.
-template <int NT>
+// slots w, w + 8, ...; lane l owns the 16-byte chunk l of every step (t = l / 8 is the lane
+// quarter that will read it, i = l % 8 the word it multiplies). The slot's inverse scale goes to
+// inv_s, its scale to scale_s.
+template <int NT, int XU>
 __device__ __forceinline__ void prepare_activations(const GemvParams &p, int cb, int ce, uint4 *xs, float *inv_s,
                                                     float *scale_s, int warp, int lane) {
-  const int chunks = (ce - cb) * 32;  // 16-byte chunks of 8 values per token
+  const int nsteps = ce - cb;
+  const int t = lane >> 3, i = lane & 7;
+  const int slot = ((warp ^ i) << 2) | t;  // fragment slot of lane (g = warp, t), swizzled by the word
 #pragma unroll
   for (int tt = 0; tt < NT; ++tt) {
     const uint32_t tok = static_cast<uint32_t>(tt * 8 + warp);
     const bool live = tok < p.tokens;
-    const uint4 *src = reinterpret_cast<const uint4 *>(p.x + static_cast<size_t>(tok) * p.k + static_cast<size_t>(cb) * 256u);
-    const int valid_chunks = live ? min(chunks, static_cast<int>((p.k - static_cast<uint32_t>(cb) * 256u) / 8u)) : 0;
+    const uint4 *src =
+        reinterpret_cast<const uint4 *>(p.x + static_cast<size_t>(tok) * p.k + static_cast<size_t>(cb) * 256u) + lane;
+    // steps whose chunk for this lane lies inside K
+    const int inside = (static_cast<int>(p.k / 8u) - cb * 32 - lane + 31) / 32;
+    const int valid = live ? min(nsteps, max(inside, 0)) : 0;
+    uint4 *dst = xs + tt * 32 + slot + static_cast<size_t>(i) * NT * 32;
     float amax = 0.0f;
-    for (int c = lane; c < valid_chunks; c += 32) {
-      const uint4 v = ldg128_coherent(src + c);
-      const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+    uint4 held[kPrepRegs];
+    const bool hold = nsteps <= kPrepRegs;
+    if (hold) {
 #pragma unroll
-      for (int j = 0; j < 4; ++j) {
-        amax = fmaxf(amax, fabsf(bf16_bits_to_f32(w[j] & 0xFFFFu)));
-        amax = fmaxf(amax, fabsf(__uint_as_float(w[j] & 0xFFFF0000u)));
+      for (int m = 0; m < kPrepRegs; ++m) {
+        held[m] = make_uint4(0u, 0u, 0u, 0u);
+        if (m < valid) held[m] = ldg128_coherent(src + m * 32);
       }
+#pragma unroll
+      for (int m = 0; m < kPrepRegs; ++m) amax = fmaxf(amax, chunk_amax(held[m]));
+    } else {
+      for (int m = 0; m < valid; ++m) amax = fmaxf(amax, chunk_amax(ldg128_coherent(src + m * 32)));
     }
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xFFFFFFFFu, amax, o));
@@ -160,29 +243,22 @@ __device__ __forceinline__ void prepare_activations(const GemvParams &p, int cb,
       inv_s[tt * 8 + warp] = live ? ldexpf(1.0f, -shift) : 0.0f;
       scale_s[tt * 8 + warp] = scale;
     }
-    for (int c = lane; c < chunks; c += 32) {
-      uint4 out = make_uint4(0u, 0u, 0u, 0u);
-      if (c < valid_chunks) {
-        const uint4 v = ldg128_coherent(src + c);
-        const uint32_t w[4] = {v.x, v.y, v.z, v.w};
-        uint32_t r[4];
+    if (hold) {
 #pragma unroll
-        for (int j = 0; j < 4; ++j) {
-          const float lo = bf16_bits_to_f32(w[j] & 0xFFFFu) * scale;
-          const float hi = __uint_as_float(w[j] & 0xFFFF0000u) * scale;
-          const __half2 hh = __floats2half2_rn(lo, hi);
-          r[j] = *reinterpret_cast<const uint32_t *>(&hh);
-        }
-        out = make_uint4(r[0], r[1], r[2], r[3]);
+      for (int m = 0; m < kPrepRegs; ++m) {
+        if (m < nsteps) dst[static_cast<size_t>(m) * 8 * NT * 32] = convert_chunk<XU>(held[m], scale, i);
       }
-      // chunk c = step 32 s + 8 t + i  ->  fragment slot [s][i][tt][g = warp][t]
-      const int s = c >> 5, t = (c >> 3) & 3, i = c & 7;
-      xs[((s * 8 + i) * NT + tt) * 32 + warp * 4 + t] = out;
+    } else {
+      for (int m = 0; m < nsteps; ++m) {
+        uint4 v = make_uint4(0u, 0u, 0u, 0u);
+        if (m < valid) v = ldg128_coherent(src + m * 32);
+        dst[static_cast<size_t>(m) * 8 * NT * 32] = convert_chunk<XU>(v, scale, i);
+      }
     }
   }
 }
 
-template <int NT>
+template <int NT, int XU>
 __global__ void __launch_bounds__(kThreads, NT <= 2 ? 2 : 1) nvfp4_gemv_kernel(const __grid_constant__ GemvParams p) {
   extern __shared__ __align__(16) uint8_t smem_raw[];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -265,7 +341,7 @@ __global__ void __launch_bounds__(kThreads, NT <= 2 ? 2 : 1) nvfp4_gemv_kernel(c
       }
       __syncthreads();  // the previous chunk's fragments and scales are no longer read
     }
-    prepare_activations<NT>(p, cb, ce, xs, inv_s, scale_s, warp, lane);
+    prepare_activations<NT, XU>(p, cb, ce, xs, inv_s, scale_s, warp, lane);
     __syncthreads();
     if (cb != c0) {
 #pragma unroll
@@ -281,10 +357,10 @@ __global__ void __launch_bounds__(kThreads, NT <= 2 ? 2 : 1) nvfp4_gemv_kernel(c
       }
     }
     while (s < ce) {
-      compute_stage<NT>(st0, xs + static_cast<size_t>(s - cb) * 8 * NT * 32, lane, tot);
+      compute_stage<NT, XU>(st0, xs + static_cast<size_t>(s - cb) * 8 * NT * 32, lane, tot);
       if (s + kw_count < ce) {
         load_stage(st0, rows, s + 2 * kw_count, c1, t, scale_tiles);
-        compute_stage<NT>(st1, xs + static_cast<size_t>(s + kw_count - cb) * 8 * NT * 32, lane, tot);
+        compute_stage<NT, XU>(st1, xs + static_cast<size_t>(s + kw_count - cb) * 8 * NT * 32, lane, tot);
         load_stage(st1, rows, s + 3 * kw_count, c1, t, scale_tiles);
         s += 2 * kw_count;
       } else {
@@ -341,6 +417,7 @@ __global__ void __launch_bounds__(kThreads, NT <= 2 ? 2 : 1) nvfp4_gemv_kernel(c
   cluster_sync_all();
   const int out_groups = swiglu ? rm / 2 : rm;
   const int items = out_groups * 2 * NT;
+  const float coef = W.inv_dw * 128.0f;  // the operands carried 2^-7
   for (int f = static_cast<int>(rank) + static_cast<int>(kc) * warp; f < items; f += static_cast<int>(kc) * kWarps) {
     const int og = f / (2 * NT), a = (f / NT) & 1, tt = f % NT;
     float4 sum = make_float4(0.f, 0.f, 0.f, 0.f), sum_up = make_float4(0.f, 0.f, 0.f, 0.f);
@@ -357,9 +434,9 @@ __global__ void __launch_bounds__(kThreads, NT <= 2 ? 2 : 1) nvfp4_gemv_kernel(c
     if (og_group >= og_limit) continue;
     const uint32_t out_row = (og_group >> 2) * 128u + (og_group & 3u) * 8u + g + 64u * a;  // q = 2a, 2a + 1
     const uint32_t tok0 = tt * 8 + 2 * t;
-    float v[4] = {sum.x * W.inv_dw, sum.y * W.inv_dw, sum.z * W.inv_dw, sum.w * W.inv_dw};
+    float v[4] = {sum.x * coef, sum.y * coef, sum.z * coef, sum.w * coef};
     if (swiglu) {
-      const float u[4] = {sum_up.x * W.inv_dw, sum_up.y * W.inv_dw, sum_up.z * W.inv_dw, sum_up.w * W.inv_dw};
+      const float u[4] = {sum_up.x * coef, sum_up.y * coef, sum_up.z * coef, sum_up.w * coef};
 #pragma unroll
       for (int e = 0; e < 4; ++e) v[e] = silu_f32(v[e]) * u[e];
     }
@@ -382,13 +459,15 @@ __global__ void __launch_bounds__(kThreads, NT <= 2 ? 2 : 1) nvfp4_gemv_kernel(c
   cluster_sync_all();  // no CTA leaves while a peer may still read its partial sums
 }
 
+constexpr size_t kGemvMaxSmem = 160 * 1024;
+
 size_t gemv_smem_bytes(int nt, int rm, int xs_steps) {
   const int kw_count = kWarps / rm;
   return static_cast<size_t>(xs_steps) * 4096u * nt + static_cast<size_t>(kw_count - 1) * rm * 2 * nt * 32 * 16 +
          static_cast<size_t>(rm) * 2 * nt * 32 * 16 + static_cast<size_t>(16 * nt) * 4;
 }
 
-template <int NT>
+template <int NT, int XU>
 cudaError_t launch_gemv(const GemvParams &p, uint32_t ctas, size_t smem, cudaStream_t stream, bool pdl) {
   cudaLaunchConfig_t config = {};
   config.gridDim = dim3(ctas, 1, 1);
@@ -404,17 +483,38 @@ cudaError_t launch_gemv(const GemvParams &p, uint32_t ctas, size_t smem, cudaStr
   attr[1].val.programmaticStreamSerializationAllowed = 1;
   config.attrs = attr;
   config.numAttrs = pdl ? 2 : 1;
-  return cudaLaunchKernelEx(&config, nvfp4_gemv_kernel<NT>, p);
+  return cudaLaunchKernelEx(&config, nvfp4_gemv_kernel<NT, XU>, p);
+}
+
+template <int NT, int XU>
+cudaError_t set_smem_attr() {
+  return cudaFuncSetAttribute(nvfp4_gemv_kernel<NT, XU>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                              static_cast<int>(kGemvMaxSmem));
+}
+
+template <int XU>
+cudaError_t set_smem_attrs() {
+  cudaError_t err = set_smem_attr<1, XU>();
+  if (err == cudaSuccess) err = set_smem_attr<2, XU>();
+  if (err == cudaSuccess) err = set_smem_attr<4, XU>();
+  return err;
+}
+
+template <int XU>
+cudaError_t launch_for_nt(int nt, const GemvParams &p, uint32_t ctas, size_t smem, cudaStream_t stream, bool pdl) {
+  if (nt == 1) return launch_gemv<1, XU>(p, ctas, smem, stream, pdl);
+  if (nt == 2) return launch_gemv<2, XU>(p, ctas, smem, stream, pdl);
+  return launch_gemv<4, XU>(p, ctas, smem, stream, pdl);
 }
 
 }  // namespace
 
-constexpr size_t kGemvMaxSmem = 160 * 1024;
-
 int32_t gemv_prepare(ErrorSlot &slot) {
-  cudaError_t err = cudaFuncSetAttribute(nvfp4_gemv_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(kGemvMaxSmem));
-  if (err == cudaSuccess) err = cudaFuncSetAttribute(nvfp4_gemv_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(kGemvMaxSmem));
-  if (err == cudaSuccess) err = cudaFuncSetAttribute(nvfp4_gemv_kernel<4>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(kGemvMaxSmem));
+  cudaError_t err = set_smem_attrs<0>();
+  if (err == cudaSuccess) err = set_smem_attrs<2>();
+  if (err == cudaSuccess) err = set_smem_attrs<3>();
+  if (err == cudaSuccess) err = set_smem_attrs<4>();
+  if (err == cudaSuccess) err = set_smem_attrs<8>();
   if (err != cudaSuccess) return fail(slot, "nvfp4 decode kernel attributes: %s", cudaGetErrorString(err));
   return 0;
 }
@@ -468,12 +568,13 @@ int32_t gemv_launch(ErrorSlot &slot, const DeviceState &dev, GemvParams &p, int 
   const size_t smem = gemv_smem_bytes(nt, plan.rm, plan.xs_steps);
   if (smem > kGemvMaxSmem) return fail(slot, "nvfp4 decode: %zu bytes of shared memory exceed the kernel's limit", smem);
   cudaError_t err;
-  if (nt == 1) {
-    err = launch_gemv<1>(p, ctas, smem, stream, dev.pdl != 0);
-  } else if (nt == 2) {
-    err = launch_gemv<2>(p, ctas, smem, stream, dev.pdl != 0);
-  } else {
-    err = launch_gemv<4>(p, ctas, smem, stream, dev.pdl != 0);
+  const bool pdl = dev.pdl != 0;
+  switch (dev.gemv_xu) {  // words per row of 8 that take the hardware E2M1 conversion
+    case 0: err = launch_for_nt<0>(nt, p, ctas, smem, stream, pdl); break;
+    case 2: err = launch_for_nt<2>(nt, p, ctas, smem, stream, pdl); break;
+    case 4: err = launch_for_nt<4>(nt, p, ctas, smem, stream, pdl); break;
+    case 8: err = launch_for_nt<8>(nt, p, ctas, smem, stream, pdl); break;
+    default: err = launch_for_nt<3>(nt, p, ctas, smem, stream, pdl); break;
   }
   if (err != cudaSuccess) return fail(slot, "nvfp4 decode launch: %s", cudaGetErrorString(err));
   return 0;

@@ -70,6 +70,7 @@ int32_t prepare_device(ErrorSlot &slot) {
   fresh.gemv_rb = env_int("B200Q_GEMV_RM", 0);
   fresh.gemv_kc = env_int("B200Q_GEMV_KC", 0);
   fresh.gemv_ctas_per_sm = env_int("B200Q_GEMV_CTAS_PER_SM", 2);
+  fresh.gemv_xu = env_int("B200Q_GEMV_XU", 8);
   fresh.sm_cap = env_int("IGNIS_TRELLIS_SM_CAP", 0);
   if (fresh.sm_cap < 0 || fresh.sm_cap > fresh.sm_count) fresh.sm_cap = 0;
   fresh.prepared = true;

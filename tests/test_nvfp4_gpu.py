@@ -55,10 +55,13 @@ def check_f32(y: torch.Tensor, ref: np.ndarray):
 def check_bf16(y: torch.Tensor, ref: np.ndarray):
     got = y.float().cpu().numpy().astype(np.float64)
     want = torch.from_numpy(ref).to(torch.bfloat16)
-    # one unit in the last place of the rounded oracle value
-    ulp = np.maximum(np.abs(want.float().numpy()), 2.0 ** -126) * 2.0 ** -7
+    # one unit in the last place of the rounded oracle value, plus the fp32 accumulation's own
+    # error (relative to the size of the sums, not of a nearly cancelled output)
+    ulp = np.abs(want.float().numpy()) * 2.0 ** -7 + 1e-5 * np.abs(ref).max()
     assert np.all(np.abs(got - want.float().numpy()) <= ulp)
     assert np.mean(bf16_bits(y) != bf16_bits(want)) < 0.02      # rounding flips are rare
+    # BF16 storage alone costs up to 2^-8 of a value, so the 2e-3 bar is held on the float32 outputs
+    assert np.all(np.abs(got - ref) <= 2.0 ** -8 * np.abs(ref) + REL_TOL * np.abs(ref).max())
     assert np.linalg.norm(got - ref) <= 2.0 ** -8 * np.linalg.norm(ref)
 
 

@@ -1,0 +1,237 @@
+"""Dense trellis parity on a B200 through the C ABI.
+
+Bars: `reconstruct` bit-exact against the recorded exllamav3 output, the oracle and the recorded
+real-shape checksums; linear outputs inside the reference's own tolerance
+|y - Y| <= 2^-8 |Y| + 2^-9 s against the fp64 product (kernel/include/ignis_trellis_linear.h:32-44,
+kernel/tests/trellis_test_common.h:165-189) and, apart from the BF16 storage rounding (2^-8 of a
+value), within 2e-3 of the largest output.
+"""
+from __future__ import annotations
+
+import numpy as np
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+K_NAMES = {"k2": 4, "k2p5": 5, "k3": 6, "k4": 8, "k5": 10, "k6": 12}
+
+
+@pytest.fixture(scope="module")
+def tr():
+    from ignis_b200 import trellis
+
+    trellis.prepare()
+    return trellis
+
+
+def f16_bits(t: torch.Tensor) -> np.ndarray:
+    return t.contiguous().view(torch.int16).cpu().numpy().view(np.uint16)
+
+
+def make_scales(rng, n, amplitude):
+    """+-(0.5..2) x amplitude, as the reference's tests draw suh and svh (test_trellis_linear.cu:50-58)."""
+    v = rng.uniform(0.5, 2.0, n) * amplitude * rng.choice([-1.0, 1.0], n)
+    return v.astype(np.float16).view(np.uint16)
+
+
+def tolerance(oracle, inner, suh, svh, x64):
+    """2^-9 s per output: |svh| times the block RMS of sqrt(sum_k (x'_k inner_kj)^2)."""
+    in_, out = inner.shape
+    lut = np.arange(65536, dtype=np.uint16).view(np.float16).astype(np.float64)
+    xs = x64 * lut[suh][None, :]
+    for t in range(xs.shape[0]):
+        oracle.lib.orc_hadamard128(xs[t], in_)
+    w = lut[inner]
+    sq = np.sqrt((xs ** 2) @ (w ** 2))                      # [tokens][out]
+    block_rms = np.sqrt((sq.reshape(sq.shape[0], out // 128, 128) ** 2).mean(axis=2))
+    return np.abs(lut[svh])[None, :] * np.repeat(block_rms, 128, axis=1)
+
+
+def check_linear(y: torch.Tensor, ref: np.ndarray, s: np.ndarray):
+    got = y.float().cpu().numpy().astype(np.float64)
+    bound = 2.0 ** -8 * np.abs(ref) + 2.0 ** -9 * s
+    worst = (np.abs(got - ref) / bound).max()
+    assert worst <= 1.0, f"worst output used {worst:.2f} of the reference bound"
+    # BF16 storage costs up to 2^-8 of a value; beyond it the error stays within 2e-3 of the largest output
+    assert np.all(np.abs(got - ref) <= 2.0 ** -8 * np.abs(ref) + 2e-3 * np.abs(ref).max())
+    assert np.linalg.norm(got - ref) <= 2.0 ** -8 * np.linalg.norm(ref)
+
+
+@pytest.mark.parametrize("family,kn", [("dense", k) for k in K_NAMES] + [("moe", k) for k in ("k2", "k2p5", "k3", "k4")])
+def test_reconstruct_equals_the_recorded_exllamav3_output(tr, golden, family, kn):
+    g = golden(f"trellis_{family}_{kn}.npz")
+    k2 = int(g["K_times_2"][0])
+    in_, out = g["reconstruct"].shape
+    w = tr.Weight.from_numpy(g["trellis"], g["suh"], g["svh"], k2, in_, out)
+    assert np.array_equal(f16_bits(tr.reconstruct(w)), g["reconstruct"])
+
+
+@pytest.mark.parametrize("key", ["z_k3", "kv_k3", "gdn_out_k3", "gate_k3", "down_k3", "kv_k2", "kv_k2p5", "kv_k4",
+                                 "q_k5", "kv_k6", "qkv_k4"])
+def test_reconstruct_real_shape_checksums(tr, oracle, golden, key):
+    """Counter-hash words at the 27B's real shapes against the 64-bit checksums of exllamav3's
+    `reconstruct` (kernel/tests/fixtures/trellis_dense/provenance.json)."""
+    entry = golden("trellis_checksums.json")["dense"][key]
+    in_, out = entry["in_out"]
+    k2 = K_NAMES[key.split("_")[-1]]
+    n_words = (in_ // 16) * (out // 16) * 8 * k2
+    # the recorder's words: lowbias32(i * 0x9E3779B9 + stream * 0x85EBCA6B) & 0xFFFF, on the device
+    i = torch.arange(n_words, dtype=torch.int64, device="cuda")
+    x = (i * 0x9E3779B9 + entry["stream"] * 0x85EBCA6B) & 0xFFFFFFFF
+    x = x ^ (x >> 16)
+    x = (x * 0x7FEB352D) & 0xFFFFFFFF
+    x = x ^ (x >> 15)
+    x = (x * 0x846CA68B) & 0xFFFFFFFF
+    x = x ^ (x >> 16)
+    words = (x & 0xFFFF).to(torch.int32)
+    words = torch.where(words >= 32768, words - 65536, words).to(torch.int16)
+    del i, x
+    dummy = torch.zeros(max(in_, out), dtype=torch.float16, device="cuda")
+    w = tr.Weight(words, dummy, dummy, k2, in_, out)
+    recon = tr.reconstruct(w)
+    # the checksum sum_i u16[i] * (lowbias32(i) | 1) mod 2^64, on the device in int64 (wraps mod 2^64)
+    v = recon.view(torch.int16).reshape(-1).to(torch.int64) & 0xFFFF
+    j = torch.arange(v.numel(), dtype=torch.int64, device="cuda")
+    m = j & 0xFFFFFFFF
+    m = m ^ (m >> 16)
+    m = (m * 0x7FEB352D) & 0xFFFFFFFF
+    m = m ^ (m >> 15)
+    m = (m * 0x846CA68B) & 0xFFFFFFFF
+    m = (m ^ (m >> 16)) | 1
+    total = int((v * m).sum().item()) & 0xFFFFFFFFFFFFFFFF
+    assert "%016x" % total == entry["checksum"]
+    if in_ * out <= 5120 * 1024:   # and against the oracle bit for bit where that is quick
+        host_words = oracle.hash_trellis_words(entry["stream"], in_, out, k2)
+        assert np.array_equal(f16_bits(recon), oracle.trellis_decode(host_words, k2, in_, out))
+
+
+@pytest.mark.parametrize("kn", list(K_NAMES))
+def test_linear_on_the_recorded_fixtures(tr, oracle, golden, kn):
+    """The recorded three tokens and their fp64 outputs through the full weight."""
+    g = golden(f"trellis_dense_{kn}.npz")
+    k2 = int(g["K_times_2"][0])
+    in_, out = g["reconstruct"].shape
+    w = tr.Weight.from_numpy(g["trellis"], g["suh"], g["svh"], k2, in_, out)
+    x = torch.from_numpy(g["x"]).to(torch.bfloat16)
+    x64 = x.double().numpy()
+    ref = oracle.trellis_project(g["reconstruct"], g["suh"], g["svh"], x64)
+    s = tolerance(oracle, g["reconstruct"], g["suh"], g["svh"], x64)
+    check_linear(tr.linear(w, x.cuda()), ref, s)
+    # the recorded activations are fp32; where BF16 rounding of x is small the recorded y64 agrees
+    assert np.abs(ref - g["y64"]).max() <= 2.0 ** -7 * np.abs(g["y64"]).max()
+
+
+@pytest.mark.parametrize("in_,out,k2", [(128, 128, 6), (256, 384, 4), (1024, 256, 5), (512, 1024, 8), (640, 128, 10),
+                                        (384, 256, 12), (5120, 1024, 6), (6144, 5120, 6)])
+@pytest.mark.parametrize("tokens", [1, 2, 8, 11])
+def test_linear_shapes_and_token_counts(tr, oracle, in_, out, k2, tokens):
+    rng = np.random.default_rng(in_ + out + k2 + tokens)
+    words = oracle.hash_trellis_words(4000 + in_ + out + k2, in_, out, k2)
+    suh, svh = make_scales(rng, in_, 0.05), make_scales(rng, out, 0.03)
+    inner = oracle.trellis_decode(words, k2, in_, out)
+    x = torch.randn(tokens, in_, generator=torch.Generator().manual_seed(tokens + out)).to(torch.bfloat16)
+    x64 = x.double().numpy()
+    ref = oracle.trellis_project(inner, suh, svh, x64)
+    w = tr.Weight.from_numpy(words, suh, svh, k2, in_, out)
+    y = tr.linear(w, x.cuda())
+    check_linear(y, ref, tolerance(oracle, inner, suh, svh, x64))
+    assert torch.equal(y, tr.linear(w, x.cuda()))   # deterministic run to run
+
+
+def test_loud_channels_and_tiny_tokens(tr, oracle):
+    """A few inputs 1000x louder than the rest, and tokens of very different scale: the per-block
+    power-of-two scaling keeps every block in fp16 range (test_trellis_linear.cu:80-89)."""
+    in_, out, k2 = 1024, 256, 6
+    rng = np.random.default_rng(31)
+    words = oracle.hash_trellis_words(777, in_, out, k2)
+    suh, svh = make_scales(rng, in_, 0.05), make_scales(rng, out, 0.03)
+    inner = oracle.trellis_decode(words, k2, in_, out)
+    x = torch.randn(8, in_, generator=torch.Generator().manual_seed(31))
+    x[:, 5] *= 1000.0
+    x[:, 700] *= 3000.0
+    x[3] *= 1e-20
+    x[4] *= 1e15
+    x[5] = 0.0
+    x = x.to(torch.bfloat16)
+    x64 = x.double().numpy()
+    ref = oracle.trellis_project(inner, suh, svh, x64)
+    s = tolerance(oracle, inner, suh, svh, x64)
+    w = tr.Weight.from_numpy(words, suh, svh, k2, in_, out)
+    got = tr.linear(w, x.cuda()).float().cpu().numpy().astype(np.float64)
+    bound = 2.0 ** -8 * np.abs(ref) + 2.0 ** -9 * s
+    assert (np.abs(got - ref) <= bound).all()
+    assert np.all(got[5] == 0.0)
+
+
+def test_epilogues_views_and_swiglu(tr, oracle):
+    in_, out, k2 = 512, 512, 6
+    rng = np.random.default_rng(32)
+    words = oracle.hash_trellis_words(888, in_, out, k2)
+    suh, svh = make_scales(rng, in_, 0.05), make_scales(rng, out, 0.03)
+    inner = oracle.trellis_decode(words, k2, in_, out)
+    w = tr.Weight.from_numpy(words, suh, svh, k2, in_, out)
+    x = torch.randn(5, in_, generator=torch.Generator().manual_seed(32)).to(torch.bfloat16)
+    x64 = x.double().numpy()
+    ref = oracle.trellis_project(inner, suh, svh, x64)
+    s = tolerance(oracle, inner, suh, svh, x64)
+    # residual add into a wider buffer
+    base = torch.randn(5, out + 128, generator=torch.Generator().manual_seed(33)).to(torch.bfloat16)
+    y = base.clone().cuda()
+    tr.linear(w, x.cuda(), out=y, epilogue=tr.ADD)
+    check_linear(y[:, :out], ref + base[:, :out].double().numpy(), s + 2.0 * np.abs(base[:, :out].double().numpy()))
+    assert torch.equal(y[:, out:].cpu(), base[:, out:])
+    # a column view of the plane gives the same columns
+    view = w.columns(128, 384)
+    yv = tr.linear(view, x.cuda())
+    full = tr.linear(w, x.cuda())
+    assert torch.equal(yv, full[:, 128:384])
+    assert np.array_equal(f16_bits(tr.reconstruct(view)), inner[:, 128:384])
+    # SwiGLU: gate and up with their own scales and K
+    words_u = oracle.hash_trellis_words(889, in_, out, 8)
+    suh_u, svh_u = make_scales(rng, in_, 0.05), make_scales(rng, out, 0.03)
+    inner_u = oracle.trellis_decode(words_u, 8, in_, out)
+    up = tr.Weight.from_numpy(words_u, suh_u, svh_u, 8, in_, out)
+    g64 = ref
+    u64 = oracle.trellis_project(inner_u, suh_u, svh_u, x64)
+    want = g64 / (1.0 + np.exp(-g64)) * u64
+    got = tr.linear_swiglu(w, up, x.cuda()).float().cpu().numpy().astype(np.float64)
+    assert np.linalg.norm(got - want) <= 2.0 ** -7 * np.linalg.norm(want)
+    assert np.abs(got - want).max() <= 2.0 ** -6 * np.abs(want).max()
+
+
+def test_full_size_gate_projection(tr, oracle):
+    """configs[3]: 5120 -> 17408 at 3 bits per weight, 8 tokens."""
+    in_, out, k2 = 5120, 17408, 6
+    rng = np.random.default_rng(34)
+    words = oracle.hash_trellis_words(34301, in_, out, k2)
+    suh, svh = make_scales(rng, in_, 0.05), make_scales(rng, out, 0.03)
+    inner = oracle.trellis_decode(words, k2, in_, out)
+    x = torch.randn(8, in_, generator=torch.Generator().manual_seed(34)).to(torch.bfloat16)
+    x64 = x.double().numpy()
+    ref = oracle.trellis_project(inner, suh, svh, x64)
+    w = tr.Weight.from_numpy(words, suh, svh, k2, in_, out)
+    got = tr.linear(w, x.cuda()).float().cpu().numpy().astype(np.float64)
+    assert np.linalg.norm(got - ref) <= 2.0 ** -8 * np.linalg.norm(ref)
+    assert np.abs(got - ref).max() <= 4e-3 * np.abs(ref).max()
+
+
+def test_workspace_and_rejects(tr):
+    assert tr.workspace_bytes(5120, 17408, 1, 8) > 0
+    assert tr.workspace_bytes(5120, 17408, 2, 64) > 0
+    assert tr.workspace_bytes(100, 128, 1, 1) == 0
+    ws = tr.WorkspaceBuffer(tr.workspace_bytes(5120, 17408, 2, 8))
+    dummy = torch.zeros(256, dtype=torch.float16, device="cuda")
+    words = torch.zeros(16 * 16 * 48, dtype=torch.int16, device="cuda")
+    w = tr.Weight(words, dummy, dummy, 6, 256, 256)
+    x = torch.zeros(1, 256, dtype=torch.bfloat16, device="cuda")
+    tr.linear(w, x, workspace=ws)
+    for bad in (tr.Weight(words, dummy, dummy, 7, 256, 256), tr.Weight(words, dummy, dummy, 6, 200, 256),
+                tr.Weight(words, dummy, dummy, 6, 256, 64)):
+        with pytest.raises(tr.TrellisError):
+            tr.linear(bad, x)
+    with pytest.raises(tr.TrellisError):
+        tr.linear(w, torch.zeros(0, 256, dtype=torch.bfloat16, device="cuda"))
+    with pytest.raises(tr.TrellisError):
+        tr.linear(w, x, epilogue=5)
+    assert tr.sm_cap() == 0
