@@ -31,6 +31,8 @@ class Workspace(C.Structure):
 NVFP4_SYMBOLS = {
     "b200q_nvfp4_prepare": (C.c_int32, []),
     "b200q_nvfp4_workspace_bytes": (C.c_uint64, [C.c_uint32, C.c_uint32, C.c_uint32, C.c_uint32]),
+    "b200q_nvfp4_workspace_init": (C.c_int32, [C.POINTER(Workspace), C.c_void_p]),
+    "b200q_nvfp4_workspace_status": (C.c_int32, [C.POINTER(Workspace), C.c_void_p, C.POINTER(C.c_uint32)]),
     "b200q_nvfp4_linear": (C.c_int32, [C.POINTER(Nvfp4Weight), C.c_void_p, C.c_uint32, C.c_void_p, C.c_uint32,
                                        C.c_uint32, C.c_uint32, C.POINTER(Workspace), C.c_void_p]),
     "b200q_nvfp4_linear_group": (C.c_int32, [C.POINTER(C.POINTER(Nvfp4Weight)), C.c_uint32, C.c_void_p, C.c_uint32,

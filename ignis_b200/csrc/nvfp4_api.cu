@@ -76,7 +76,6 @@ int32_t linear_group_impl(const b200q_nvfp4_weight *const *w, uint32_t count, co
                           void *const *y, const uint32_t *ldy, uint32_t epilogue, uint32_t policy,
                           const b200q_nvfp4_workspace *workspace, void *stream, const char *what) {
   ErrorSlot &slot = nvfp4_error();
-  (void)workspace;
   if (w == nullptr || y == nullptr || ldy == nullptr) return fail(slot, "%s: NULL argument array", what);
   if (count == 0 || count > B200Q_NVFP4_MAX_GROUP) return fail(slot, "%s: count = %u is outside 1..%d", what, count, B200Q_NVFP4_MAX_GROUP);
   if (tokens == 0) return fail(slot, "%s: tokens must be positive", what);
@@ -94,8 +93,25 @@ int32_t linear_group_impl(const b200q_nvfp4_weight *const *w, uint32_t count, co
   }
   const DeviceState *dev = prepared_state(slot, what);
   if (dev == nullptr) return -1;
-  // Every token count takes the decode route (the weights are re-read once per 32 tokens); the
-  // tensor-core prefill route replaces it for wide calls under B200Q_NVFP4_ALLOW_A4.
+  // Wide calls under B200Q_NVFP4_ALLOW_A4 quantize the activations and take the tensor-core route
+  // (the reference's AllowA4 resolution, nvfp4_dispatch.cpp:31-39, with one threshold); everything
+  // else takes the decode route, which re-reads the weights once per 32 tokens.
+  if (policy == B200Q_NVFP4_ALLOW_A4 && tokens > B200Q_NVFP4_DECODE_MAX_TOKENS && count == 1 && !swiglu &&
+      (epilogue & kEpilogueAdd) == 0u && w4a4_shape_ok(w[0]->n, w[0]->k)) {
+    const b200q_nvfp4_weight *w0 = w[0];
+    if (!std::isfinite(w0->input_scale_divisor) || !(w0->input_scale_divisor > 0.0f)) {
+      return fail(slot, "%s: input_scale_divisor must be finite and positive for the A4 route", what);
+    }
+    const uint64_t need = w4a4_workspace_bytes(w0->k, tokens);
+    if (workspace == nullptr || workspace->base == nullptr || workspace->bytes < need || !aligned(workspace->base, 256)) {
+      return fail(slot, "%s: the A4 route needs a 256-byte aligned workspace of %llu bytes", what,
+                  static_cast<unsigned long long>(need));
+    }
+    if (!aligned(y[0], 16) || (ldy[0] % 8u) != 0) return fail(slot, "%s: the A4 route needs y 16-byte aligned and ldy a multiple of 8", what);
+    return w4a4_launch(slot, *dev, static_cast<const uint8_t *>(w0->codes), static_cast<const uint8_t *>(w0->scales), w0->n,
+                       w0->k, w0->weight_scale_divisor, w0->input_scale_divisor, static_cast<const uint16_t *>(x), tokens,
+                       y[0], ldy[0], epilogue, static_cast<uint8_t *>(workspace->base), static_cast<cudaStream_t>(stream));
+  }
   return decode_route(slot, *dev, w, count, x, tokens, y, ldy, epilogue, static_cast<cudaStream_t>(stream));
 }
 
@@ -109,15 +125,42 @@ extern "C" {
 int32_t b200q_nvfp4_prepare(void) {
   ErrorSlot &slot = nvfp4_error();
   if (prepare_device(slot) != 0) return -1;
-  return gemv_prepare(slot);
+  if (gemv_prepare(slot) != 0) return -1;
+  return w4a4_prepare(slot);
 }
 
 uint64_t b200q_nvfp4_workspace_bytes(uint32_t n, uint32_t k, uint32_t policy, uint32_t tokens) {
   if (n == 0 || (n % 128u) != 0 || k == 0 || (k % 64u) != 0 || tokens == 0) return 0;
   if (policy != B200Q_NVFP4_A16_ONLY && policy != B200Q_NVFP4_ALLOW_A4) return 0;
   // The decode route keeps its partial sums in distributed shared memory and needs no global
-  // scratch; a caller still reserves one aligned line so a workspace pointer is never NULL.
+  // scratch (one aligned line, so a workspace pointer is never NULL); the A4 route keeps the
+  // quantized activations there.
+  if (policy == B200Q_NVFP4_ALLOW_A4 && tokens > B200Q_NVFP4_DECODE_MAX_TOKENS && w4a4_shape_ok(n, k)) {
+    return w4a4_workspace_bytes(k, tokens);
+  }
   return 256;
+}
+
+int32_t b200q_nvfp4_workspace_init(const b200q_nvfp4_workspace *workspace, void *stream) {
+  ErrorSlot &slot = nvfp4_error();
+  if (workspace == nullptr || workspace->base == nullptr || workspace->bytes < 256) {
+    return fail(slot, "b200q_nvfp4_workspace_init: workspace is NULL or shorter than 256 bytes");
+  }
+  if (!aligned(workspace->base, 256)) return fail(slot, "b200q_nvfp4_workspace_init: base is not 256-byte aligned");
+  const cudaError_t err = cudaMemsetAsync(workspace->base, 0, 256, static_cast<cudaStream_t>(stream));
+  if (err != cudaSuccess) return fail(slot, "b200q_nvfp4_workspace_init: %s", cudaGetErrorString(err));
+  return 0;
+}
+
+int32_t b200q_nvfp4_workspace_status(const b200q_nvfp4_workspace *workspace, void *stream, uint32_t *status) {
+  ErrorSlot &slot = nvfp4_error();
+  if (workspace == nullptr || workspace->base == nullptr || status == nullptr) {
+    return fail(slot, "b200q_nvfp4_workspace_status: NULL argument");
+  }
+  cudaError_t err = cudaMemcpyAsync(status, workspace->base, sizeof(uint32_t), cudaMemcpyDeviceToHost, static_cast<cudaStream_t>(stream));
+  if (err == cudaSuccess) err = cudaStreamSynchronize(static_cast<cudaStream_t>(stream));
+  if (err != cudaSuccess) return fail(slot, "b200q_nvfp4_workspace_status: %s", cudaGetErrorString(err));
+  return 0;
 }
 
 int32_t b200q_nvfp4_linear(const b200q_nvfp4_weight *w, const void *x, uint32_t tokens, void *y, uint32_t ldy,

@@ -53,6 +53,14 @@ int32_t dequantize_launch(ErrorSlot &slot, const uint8_t *codes, const uint8_t *
 int32_t quantize_activations_launch(ErrorSlot &slot, const uint16_t *x, uint32_t tokens, uint32_t k, float d_in,
                                     uint8_t *codes, uint8_t *scales, cudaStream_t stream);
 
+// The tensor-core prefill route (nvfp4_w4a4.cu).
+int32_t w4a4_prepare(ErrorSlot &slot);
+bool w4a4_shape_ok(uint32_t n, uint32_t k);
+uint64_t w4a4_workspace_bytes(uint32_t k, uint32_t tokens);
+int32_t w4a4_launch(ErrorSlot &slot, const DeviceState &dev, const uint8_t *w_codes, const uint8_t *w_scales, uint32_t n,
+                    uint32_t k, float d_w, float d_in, const uint16_t *x, uint32_t tokens, void *y, uint32_t ldy,
+                    uint32_t epilogue, uint8_t *workspace, cudaStream_t stream);
+
 }  // namespace b200q
 
 #endif

@@ -1,0 +1,393 @@
+// NVFP4 prefill route (W4A4): out[t][r] = bf16(alpha * sum_k E2M1(a) E4M3(sa) E2M1(w) E4M3(sw)),
+// alpha = 1 / (d_in d_w), on the 5th-generation tensor cores.
+//
+// Stands where the reference quantizes activations and runs its FP4 GEMMs
+// (kernel/vendor/src/ops/linear/nvfp4/nvfp4_w4a4_mma.cuh:203-436, nvfp4_w4a4_tma.cuh:264-508,
+// launch_problem nvfp4_w4a4.cu:74-110) - warp-level mma.sync on its RTX target. Here:
+//
+//  1. `quantize_swizzled_kernel` turns the BF16 activations into E2M1 codes [T_pad][K/2] and E4M3
+//     scales, bit for bit the reference's rule (nvfp4_codec.cuh:81-110), the scales written in the
+//     same 512-byte (128 rows x 4 groups) tiles the weight plane uses - which is the scale-factor
+//     atom the block-scaled MMA reads, so neither operand's scales are ever reshuffled.
+//  2. `w4a4_gemm_kernel`: one CTA per 128-token x 256-row output tile. A producer thread streams
+//     K in stages of 256 (TMA 2-D tiles of codes with the 128-byte swizzle, plain bulk copies of
+//     the scale tiles) into a 4-deep mbarrier ring; one thread copies each stage's scale atoms to
+//     tensor memory (tcgen05.cp) and issues tcgen05.mma kind::mxf4nvf4 block_scale scale_vec::4X
+//     (M 128, N 256, K 64) with the fp32 accumulator in tensor memory; four warps read the
+//     accumulator back (tcgen05.ld), apply alpha and store BF16.
+//
+// Every wait on an mbarrier is bounded: after the limit the thread records a status bit in the
+// workspace, stops issuing and the CTA tears down (tensor memory freed) instead of hanging.
+#include "nvfp4_internal.cuh"
+
+#include <cuda.h>
+
+namespace b200q {
+namespace {
+
+constexpr int kBM = 128;          // tokens per tile (MMA M)
+constexpr int kBN = 256;          // weight rows per tile (MMA N)
+constexpr int kBKBytes = 128;     // bytes of codes per row per stage: 256 values along K
+constexpr int kStages = 4;
+constexpr uint32_t kABytes = kBM * kBKBytes;        // 16 KB
+constexpr uint32_t kBBytes = kBN * kBKBytes;        // 32 KB
+constexpr uint32_t kSfaBytes = 4 * 512;             // 4 K-atoms of one 128-row tile
+constexpr uint32_t kSfbBytes = 2 * 4 * 512;         // two 128-row tiles
+constexpr uint32_t kStageBytes = kABytes + kBBytes + kSfaBytes + kSfbBytes;  // 54 KB
+constexpr uint32_t kSmemBytes = kStages * kStageBytes + 256 + 1024;          // + barriers + alignment slack
+constexpr uint32_t kTmemCols = 512;
+constexpr uint32_t kSfColsPerStage = 48;  // 16 for the activations, 32 for the weights
+constexpr uint32_t kSpinLimit = 1u << 22;
+
+constexpr uint32_t kStatusProducerTimeout = 1u, kStatusMmaTimeout = 2u, kStatusEpilogueTimeout = 4u;
+
+// ---- activation quantizer, scales in tile order -------------------------------------------------
+__device__ __forceinline__ void quantize_block16(const uint4 lo, const uint4 hi, float d_in, uint2 &codes, uint8_t &scale) {
+  const uint32_t w[8] = {lo.x, lo.y, lo.z, lo.w, hi.x, hi.y, hi.z, hi.w};
+  float v[16];
+  float amax = 0.0f;
+#pragma unroll
+  for (int j = 0; j < 8; ++j) {
+    v[2 * j] = bf16_bits_to_f32(w[j] & 0xFFFFu);
+    v[2 * j + 1] = __uint_as_float(w[j] & 0xFFFF0000u);
+    amax = fmaxf(amax, fabsf(v[2 * j]));
+    amax = fmaxf(amax, fabsf(v[2 * j + 1]));
+  }
+  const float unencoded = __fdiv_rn(__fmul_rn(d_in, amax), 6.0f);
+  uint16_t s2;
+  asm("cvt.rn.satfinite.e4m3x2.f32 %0, %1, %2;" : "=h"(s2) : "f"(0.0f), "f"(unencoded));
+  scale = static_cast<uint8_t>(s2 & 0xFFu);
+  codes = make_uint2(0u, 0u);
+  if (scale == 0) return;
+  const uint32_t sh = e4m3x2_to_half2(scale);
+  const float dec = __half2float(__ushort_as_half(static_cast<unsigned short>(sh & 0xFFFFu)));
+  uint32_t packed[2] = {0u, 0u};
+#pragma unroll
+  for (int j = 0; j < 8; ++j) {
+    const float q0 = __fdiv_rn(__fmul_rn(v[2 * j], d_in), dec);
+    const float q1 = __fdiv_rn(__fmul_rn(v[2 * j + 1], d_in), dec);
+    uint32_t byte;
+    asm("{ .reg .b8 b; cvt.rn.satfinite.e2m1x2.f32 b, %1, %2; cvt.u32.u8 %0, b; }" : "=r"(byte) : "f"(q1), "f"(q0));
+    packed[j >> 2] |= byte << (8 * (j & 3));
+  }
+  codes = make_uint2(packed[0], packed[1]);
+}
+
+// One thread per (token row of the padded range, 16-value group). Rows at and beyond `tokens`
+// get zero codes and zero scales.
+__global__ void __launch_bounds__(256) quantize_swizzled_kernel(const uint16_t *x, uint32_t tokens, uint32_t tokens_pad,
+                                                                uint32_t k, float d_in, uint8_t *codes, uint8_t *scales) {
+  griddep_launch_dependents();
+  griddep_wait();
+  const uint32_t groups = k / 16u;
+  const uint64_t total = static_cast<uint64_t>(tokens_pad) * groups;
+  for (uint64_t bi = blockIdx.x * static_cast<uint64_t>(blockDim.x) + threadIdx.x; bi < total;
+       bi += static_cast<uint64_t>(gridDim.x) * blockDim.x) {
+    const uint32_t t = static_cast<uint32_t>(bi / groups), g = static_cast<uint32_t>(bi % groups);
+    uint2 c = make_uint2(0u, 0u);
+    uint8_t s = 0;
+    if (t < tokens) {
+      const uint16_t *src = x + static_cast<uint64_t>(t) * k + g * 16u;
+      quantize_block16(ldg128_coherent(src), ldg128_coherent(src + 8), d_in, c, s);
+    }
+    *reinterpret_cast<uint2 *>(codes + bi * 8u) = c;
+    const uint64_t so = (static_cast<uint64_t>(t >> 7) * (k / 64u) + (g >> 2)) * 512u + (t & 31u) * 16u + ((t & 127u) >> 5) * 4u + (g & 3u);
+    scales[so] = s;
+  }
+}
+
+// ---- mbarrier / TMA / tcgen05 wrappers ------------------------------------------------------------
+__device__ __forceinline__ uint32_t smem_u32(const void *p) { return static_cast<uint32_t>(__cvta_generic_to_shared(p)); }
+
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+// Bounded wait for the phase with `parity` to complete; false when the limit ran out.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
+  for (uint32_t spin = 0; spin < kSpinLimit; ++spin) {
+    uint32_t done;
+    asm volatile("{ .reg .pred p; mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2; selp.u32 %0, 1, 0, p; }"
+                 : "=r"(done)
+                 : "r"(bar), "r"(parity)
+                 : "memory");
+    if (done) return true;
+  }
+  return false;
+}
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap *map, uint32_t bar, int32_t x, int32_t y) {
+  asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+               ::"r"(dst), "l"(map), "r"(bar), "r"(x), "r"(y)
+               : "memory");
+}
+__device__ __forceinline__ void bulk_load(uint32_t dst, const void *src, uint32_t bytes, uint32_t bar) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+               ::"r"(dst), "l"(src), "r"(bytes), "r"(bar)
+               : "memory");
+}
+
+// Shared-memory matrix descriptor: start address and byte offsets in 16-byte units, descriptor
+// version 1 (bits 46..47), layout type in bits 61..63 (0 none, 2 the 128-byte swizzle).
+__device__ __forceinline__ uint64_t smem_desc(uint32_t addr, uint32_t sbo_bytes, uint32_t layout) {
+  return static_cast<uint64_t>((addr & 0x3FFFFu) >> 4) | (static_cast<uint64_t>(sbo_bytes >> 4) << 32) | (1ull << 46) |
+         (static_cast<uint64_t>(layout) << 61);
+}
+
+__device__ __forceinline__ void tmem_cp_sf(uint32_t taddr, uint64_t desc) {
+  asm volatile("tcgen05.cp.cta_group::1.32x128b.warpx4 [%0], %1;" ::"r"(taddr), "l"(desc) : "memory");
+}
+__device__ __forceinline__ void mma_mxf4nvf4(uint32_t d, uint64_t a, uint64_t b, uint32_t idesc, uint32_t sfa, uint32_t sfb,
+                                             uint32_t accumulate) {
+  asm volatile("{ .reg .pred p; setp.ne.u32 p, %6, 0;\n"
+               "tcgen05.mma.cta_group::1.kind::mxf4nvf4.block_scale.scale_vec::4X [%0], %1, %2, %3, [%4], [%5], p; }"
+               ::"r"(d), "l"(a), "l"(b), "r"(idesc), "r"(sfa), "r"(sfb), "r"(accumulate)
+               : "memory");
+}
+__device__ __forceinline__ void mma_commit(uint32_t bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+
+struct W4A4Params {
+  const uint8_t *sfa;   // activation scales, tile order
+  const uint8_t *sfb;   // weight scales, tile order
+  void *y;
+  uint32_t *status;
+  uint32_t tokens, n, k, ldy;
+  float alpha;
+  uint32_t epilogue;
+};
+
+__global__ void __launch_bounds__(192, 1) w4a4_gemm_kernel(const __grid_constant__ CUtensorMap map_a,
+                                                          const __grid_constant__ CUtensorMap map_b,
+                                                          const __grid_constant__ W4A4Params p) {
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t raw = smem_u32(smem_raw);
+  const uint32_t base = (raw + 1023u) & ~1023u;  // the 128-byte swizzle wants 1024-byte aligned tiles
+  uint8_t *base_ptr = smem_raw + (base - raw);
+  const uint32_t bars = base + kStages * kStageBytes;  // full[4], empty[4], tmem_full, then the tmem slot
+  uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(base_ptr + kStages * kStageBytes + 128);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const uint32_t m_tile = blockIdx.x, n_tile = blockIdx.y;
+  const uint32_t k_iters = p.k / 256u;
+  const uint32_t k_atoms = p.k / 64u;
+  const bool second_half = (n_tile * 2u + 1u) * 128u < p.n;  // the tile's rows 128..255 exist
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < kStages; ++s) {
+      mbar_init(bars + 8 * s, 1);
+      mbar_init(bars + 8 * (kStages + s), 1);
+    }
+    mbar_init(bars + 8 * 2 * kStages, 1);
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 5) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(kTmemCols) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+  const uint32_t tmem = *tmem_slot;
+
+  // the quantized activations come from the previous kernel in the stream
+  griddep_launch_dependents();
+  griddep_wait();
+
+  if (warp == 4 && lane == 0) {
+    // ---- producer ----
+    for (uint32_t it = 0; it < k_iters; ++it) {
+      const uint32_t s = it % kStages;
+      if (!mbar_wait(bars + 8 * (kStages + s), ((it / kStages) & 1u) ^ 1u)) {
+        atomicOr(p.status, kStatusProducerTimeout);
+        break;
+      }
+      const uint32_t full = bars + 8 * s;
+      const uint32_t stage = base + s * kStageBytes;
+      mbar_expect_tx(full, kABytes + kBBytes + kSfaBytes + (second_half ? kSfbBytes : kSfbBytes / 2));
+      tma_load_2d(stage, &map_a, full, static_cast<int32_t>(it * kBKBytes), static_cast<int32_t>(m_tile * kBM));
+      tma_load_2d(stage + kABytes, &map_b, full, static_cast<int32_t>(it * kBKBytes), static_cast<int32_t>(n_tile * kBN));
+      bulk_load(stage + kABytes + kBBytes, p.sfa + (static_cast<uint64_t>(m_tile) * k_atoms + it * 4u) * 512u, kSfaBytes, full);
+      const uint8_t *sfb0 = p.sfb + (static_cast<uint64_t>(n_tile * 2u) * k_atoms + it * 4u) * 512u;
+      bulk_load(stage + kABytes + kBBytes + kSfaBytes, sfb0, kSfbBytes / 2, full);
+      if (second_half) {
+        bulk_load(stage + kABytes + kBBytes + kSfaBytes + kSfbBytes / 2, sfb0 + static_cast<uint64_t>(k_atoms) * 512u, kSfbBytes / 2, full);
+      }
+    }
+  } else if (warp == 5 && lane == 0) {
+    // ---- MMA issuer ----
+    // instruction descriptor: E2M1 x E2M1 (format 1 at bits 7 and 10), both K-major, N >> 3 at
+    // bit 17, UE4M3 scales (bit 23 clear), M >> 4 at bit 24, scale ids 0, K 64
+    const uint32_t idesc = (1u << 7) | (1u << 10) | ((kBN >> 3) << 17) | ((kBM >> 4) << 24);
+    bool ok = true;
+    for (uint32_t it = 0; it < k_iters && ok; ++it) {
+      const uint32_t s = it % kStages;
+      if (!mbar_wait(bars + 8 * s, (it / kStages) & 1u)) {
+        atomicOr(p.status, kStatusMmaTimeout);
+        ok = false;
+        break;
+      }
+      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+      const uint32_t stage = base + s * kStageBytes;
+      const uint32_t sf_cols = tmem + 256u + s * kSfColsPerStage;
+      const uint32_t sfa_smem = stage + kABytes + kBBytes, sfb_smem = sfa_smem + kSfaBytes;
+#pragma unroll
+      for (uint32_t kb = 0; kb < 4; ++kb) {
+        tmem_cp_sf(sf_cols + kb * 4u, smem_desc(sfa_smem + kb * 512u, 128u, 0u));
+        tmem_cp_sf(sf_cols + 16u + kb * 8u, smem_desc(sfb_smem + kb * 512u, 128u, 0u));
+        tmem_cp_sf(sf_cols + 16u + kb * 8u + 4u, smem_desc(sfb_smem + kSfbBytes / 2 + kb * 512u, 128u, 0u));
+      }
+      const uint64_t a_desc = smem_desc(stage, 1024u, 2u);
+      const uint64_t b_desc = smem_desc(stage + kABytes, 1024u, 2u);
+#pragma unroll
+      for (uint32_t kb = 0; kb < 4; ++kb) {
+        // 64 values along K are 32 bytes: two 16-byte units further inside the swizzled row
+        mma_mxf4nvf4(tmem, a_desc + 2u * kb, b_desc + 2u * kb, idesc, sf_cols + kb * 4u, sf_cols + 16u + kb * 8u,
+                     (it | kb) != 0u ? 1u : 0u);
+      }
+      mma_commit(bars + 8 * (kStages + s));  // the stage's shared memory is free once these MMAs retire
+    }
+    if (ok) mma_commit(bars + 8 * 2 * kStages);  // accumulator complete
+  } else if (warp < 4) {
+    // ---- epilogue: warp q owns accumulator lanes (tokens) 32 q .. 32 q + 31 ----
+    if (mbar_wait(bars + 8 * 2 * kStages, 0u)) {
+      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+      const uint32_t token = m_tile * kBM + warp * 32 + lane;
+      const uint32_t lane_base = tmem + (static_cast<uint32_t>(warp * 32) << 16);
+#pragma unroll 1
+      for (uint32_t c = 0; c < kBN; c += 32) {
+        uint32_t r[32];
+        asm volatile(
+            "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+            "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
+            : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+              "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
+              "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
+              "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+            : "r"(lane_base + c)
+            : "memory");
+        asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+        const uint32_t row0 = n_tile * kBN + c;
+        if (token < p.tokens && row0 < p.n) {  // n is a multiple of 128, so a 32-row chunk is whole
+          if (p.epilogue & kEpilogueF32) {
+            float4 *dst = reinterpret_cast<float4 *>(static_cast<float *>(p.y) + static_cast<size_t>(token) * p.ldy + row0);
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+              dst[j] = make_float4(__uint_as_float(r[4 * j]) * p.alpha, __uint_as_float(r[4 * j + 1]) * p.alpha,
+                                   __uint_as_float(r[4 * j + 2]) * p.alpha, __uint_as_float(r[4 * j + 3]) * p.alpha);
+            }
+          } else {
+            uint4 *dst = reinterpret_cast<uint4 *>(static_cast<__nv_bfloat16 *>(p.y) + static_cast<size_t>(token) * p.ldy + row0);
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              uint32_t o[4];
+#pragma unroll
+              for (int e = 0; e < 4; ++e) {
+                const __nv_bfloat162 h = __floats2bfloat162_rn(__uint_as_float(r[8 * j + 2 * e]) * p.alpha,
+                                                               __uint_as_float(r[8 * j + 2 * e + 1]) * p.alpha);
+                o[e] = *reinterpret_cast<const uint32_t *>(&h);
+              }
+              dst[j] = make_uint4(o[0], o[1], o[2], o[3]);
+            }
+          }
+        }
+      }
+    } else if (lane == 0) {
+      atomicOr(p.status, kStatusEpilogueTimeout);
+    }
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  if (warp == 5) {
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(kTmemCols) : "memory");
+  }
+}
+
+// ---- host side --------------------------------------------------------------------------------
+using EncodeTiledFn = CUresult (*)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
+                                   const cuuint64_t *, const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave,
+                                   CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_tiled_fn() {
+  static EncodeTiledFn fn = [] {
+    void *sym = nullptr;
+    cudaDriverEntryPointQueryResult result;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &result) != cudaSuccess ||
+        result != cudaDriverEntryPointSuccess) {
+      return static_cast<EncodeTiledFn>(nullptr);
+    }
+    return reinterpret_cast<EncodeTiledFn>(sym);
+  }();
+  return fn;
+}
+
+// A [rows][k/2]-byte plane as a 2-D byte tensor with (128 bytes x box_rows) boxes, 128-byte swizzle.
+bool make_code_map(CUtensorMap *map, const void *codes, uint64_t rows, uint64_t row_bytes, uint32_t box_rows) {
+  EncodeTiledFn fn = encode_tiled_fn();
+  if (fn == nullptr) return false;
+  const cuuint64_t dims[2] = {row_bytes, rows};
+  const cuuint64_t strides[1] = {row_bytes};
+  const cuuint32_t box[2] = {static_cast<cuuint32_t>(kBKBytes), box_rows};
+  const cuuint32_t elem[2] = {1, 1};
+  return fn(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void *>(codes), dims, strides, box, elem,
+            CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+}  // namespace
+
+uint32_t w4a4_tokens_pad(uint32_t tokens) { return (tokens + kBM - 1) / kBM * kBM; }
+
+// Workspace of a W4A4 call: one status line, then the codes, then the scale tiles.
+uint64_t w4a4_workspace_bytes(uint32_t k, uint32_t tokens) {
+  const uint64_t pad = w4a4_tokens_pad(tokens);
+  return 256u + pad * (k / 2u) + pad * (k / 16u);
+}
+
+bool w4a4_shape_ok(uint32_t n, uint32_t k) { return (k % 256u) == 0 && (n % 128u) == 0; }
+
+int32_t w4a4_prepare(ErrorSlot &slot) {
+  const cudaError_t err = cudaFuncSetAttribute(w4a4_gemm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                               static_cast<int>(kSmemBytes));
+  if (err != cudaSuccess) return fail(slot, "nvfp4 prefill kernel attributes: %s", cudaGetErrorString(err));
+  if (encode_tiled_fn() == nullptr) return fail(slot, "cuTensorMapEncodeTiled is not available from this driver");
+  return 0;
+}
+
+int32_t w4a4_launch(ErrorSlot &slot, const DeviceState &dev, const uint8_t *w_codes, const uint8_t *w_scales, uint32_t n,
+                    uint32_t k, float d_w, float d_in, const uint16_t *x, uint32_t tokens, void *y, uint32_t ldy,
+                    uint32_t epilogue, uint8_t *workspace, cudaStream_t stream) {
+  const uint32_t pad = w4a4_tokens_pad(tokens);
+  uint32_t *status = reinterpret_cast<uint32_t *>(workspace);
+  uint8_t *a_codes = workspace + 256;
+  uint8_t *a_scales = a_codes + static_cast<uint64_t>(pad) * (k / 2u);
+  {
+    const uint64_t total = static_cast<uint64_t>(pad) * (k / 16u);
+    const uint32_t grid = static_cast<uint32_t>(total / 256u < 148u * 16u ? (total + 255u) / 256u : 148u * 16u);
+    const cudaError_t err = launch(quantize_swizzled_kernel, dim3(grid), dim3(256), 0, stream, dev.pdl != 0, x, tokens, pad,
+                                   k, d_in, a_codes, a_scales);
+    if (err != cudaSuccess) return fail(slot, "nvfp4 activation quantizer launch: %s", cudaGetErrorString(err));
+  }
+  CUtensorMap map_a, map_b;
+  if (!make_code_map(&map_a, a_codes, pad, k / 2u, kBM) || !make_code_map(&map_b, w_codes, n, k / 2u, kBN)) {
+    return fail(slot, "nvfp4 prefill: tensor map encoding failed");
+  }
+  W4A4Params p = {};
+  p.sfa = a_scales;
+  p.sfb = w_scales;
+  p.y = y;
+  p.status = status;
+  p.tokens = tokens;
+  p.n = n;
+  p.k = k;
+  p.ldy = ldy;
+  p.alpha = 1.0f / (d_in * d_w);
+  p.epilogue = epilogue;
+  const dim3 grid(pad / kBM, (n + kBN - 1) / kBN, 1);
+  const cudaError_t err = launch(w4a4_gemm_kernel, grid, dim3(192), kSmemBytes, stream, dev.pdl != 0, map_a, map_b, p);
+  if (err != cudaSuccess) return fail(slot, "nvfp4 prefill launch: %s", cudaGetErrorString(err));
+  return 0;
+}
+
+}  // namespace b200q

@@ -138,6 +138,21 @@ def _stream() -> C.c_void_p:
     return C.c_void_p(torch.cuda.current_stream().cuda_stream)
 
 
+class Workspace:
+    """A reserved and initialised workspace (one per stream): ``b200q_nvfp4_workspace``."""
+
+    def __init__(self, nbytes: int, device: str | torch.device = "cuda") -> None:
+        self.buffer = torch.empty(max(256, int(nbytes)), dtype=torch.uint8, device=device)
+        self.c = _lib.Workspace(self.buffer.data_ptr(), self.buffer.numel())
+        _check(_lib.load().b200q_nvfp4_workspace_init(C.byref(self.c), _stream()))
+
+    def status(self) -> int:
+        """The device-side status word (blocks until the stream is idle); 0 when no kernel gave up a wait."""
+        word = C.c_uint32(0)
+        _check(_lib.load().b200q_nvfp4_workspace_status(C.byref(self.c), _stream(), C.byref(word)))
+        return int(word.value)
+
+
 def _check_x(x: torch.Tensor, k: int) -> None:
     if x.dtype != torch.bfloat16 or x.dim() != 2 or x.shape[1] != k or not x.is_contiguous() or not x.is_cuda:
         raise Nvfp4Error("x must be a contiguous CUDA BF16 [tokens, k] tensor")
@@ -155,14 +170,15 @@ def _out(tokens: int, width: int, epilogue: int, out: torch.Tensor | None, devic
 
 
 def linear(x: torch.Tensor, w: Weight, out: torch.Tensor | None = None, policy: int = A16_ONLY,
-           epilogue: int = STORE) -> torch.Tensor:
-    """``out[t, r] = sum_c w[r, c] x[t, c]``: ninfer::ops::linear; with ``ADD``, linear_add."""
+           epilogue: int = STORE, workspace: Workspace | None = None) -> torch.Tensor:
+    """``out[t, r] = sum_c w[r, c] x[t, c]``: ninfer::ops::linear; with ``ADD``, linear_add. Under
+    ``ALLOW_A4`` wide calls take the tensor-core W4A4 route and need `workspace`."""
     _check_x(x, w.k)
     tokens = x.shape[0]
     y = _out(tokens, w.n, epilogue, out, x.device)
     ws = w.c_struct()
     _check(_lib.load().b200q_nvfp4_linear(C.byref(ws), x.data_ptr(), tokens, y.data_ptr(), y.stride(0), epilogue, policy,
-                                           None, _stream()))
+                                           C.byref(workspace.c) if workspace is not None else None, _stream()))
     return y
 
 

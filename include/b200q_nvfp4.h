@@ -60,7 +60,11 @@ typedef struct b200q_nvfp4_workspace {
 #define B200Q_NVFP4_ALLOW_A4 1
 
 /* Epilogues. STORE and ADD write BF16; OR-ing B200Q_NVFP4_OUT_F32 makes `y` float32 (the FP32
- * accumulators before the final rounding, for numerical checks). ADD is the residual add of the
+ * accumulators before the final rounding, for numerical checks). Under B200Q_NVFP4_ALLOW_A4 a call
+ * of more than B200Q_NVFP4_DECODE_MAX_TOKENS tokens with k a multiple of 256 takes the tensor-core
+ * route (activations quantized to NVFP4 under input_scale_divisor, tcgen05 block-scaled MMA,
+ * out = BF16(acc / (d_in d_w)): nvfp4_w4a4.cu:37); it serves STORE only, needs the workspace, y
+ * 16-byte aligned and ldy a multiple of 8. ADD is the residual add of the
  * reference's linear_add (linear_add/nvfp4/nvfp4_linear_add_epilogue.cuh:9-17): one rounding of
  * acc + float(y). */
 #define B200Q_NVFP4_STORE 0
@@ -81,6 +85,17 @@ int32_t b200q_nvfp4_prepare(void);
 /* Workspace bytes of a call at (n, k) with `tokens` tokens under `policy`; 0 for a shape the ops
  * refuse. Mirrors linear_workspace_capacity_bytes (ninfer/ops/linear.h:31-35). */
 uint64_t b200q_nvfp4_workspace_bytes(uint32_t n, uint32_t k, uint32_t policy, uint32_t tokens);
+
+/* Zeroes the workspace's status line, once after it is reserved (the ops leave it zero unless a
+ * device-side wait ran out). Mirrors ignis_trellis_workspace_init
+ * (kernel/include/ignis_trellis_linear.h:124). */
+int32_t b200q_nvfp4_workspace_init(const b200q_nvfp4_workspace *workspace, void *stream);
+
+/* Copies the workspace's status word to `*status` and blocks until `stream` has finished: 0 when
+ * no kernel gave up a bounded wait (bit 0 producer, bit 1 MMA issuer, bit 2 epilogue of the
+ * tensor-core route). For tests and tools, like the reference's ignis_moe_stream_sync
+ * (kernel/include/ignis_moe.h:212); the reference's own kernels trap or spin instead. */
+int32_t b200q_nvfp4_workspace_status(const b200q_nvfp4_workspace *workspace, void *stream, uint32_t *status);
 
 /* y[t][r] = sum_c w[r][c] x[t][c] through `epilogue`: ninfer::ops::linear
  * (ninfer/ops/linear.h:99-119) and, with B200Q_NVFP4_ADD, ninfer::ops::linear_add. */

@@ -308,3 +308,36 @@ def test_rejects(nv):
         nv.linear(x, bad)
     with pytest.raises(nv.Nvfp4Error):
         nv.linear(x, w, policy=9)
+
+
+# ---- the tensor-core W4A4 route (policy ALLOW_A4, more than 32 tokens) --------------------------
+
+def w4a4_reference(oracle, codes, scales, n, k, d_w, d_in, x_bf16: torch.Tensor):
+    """The reference's W4A4 arithmetic on the host: its activation quantizer, then
+    alpha * sum of exactly representable products accumulated in fp64."""
+    a_codes, a_scales = oracle.nvfp4_quantize_act(bf16_bits(x_bf16), d_in)
+    return oracle.nvfp4_w4a4_gemm(codes, scales, n, k, d_w, a_codes, a_scales, d_in)
+
+
+@pytest.mark.parametrize("tokens,n,k", [(128, 256, 256), (200, 256, 512), (33, 128, 1024), (300, 384, 768), (256, 512, 2048)])
+def test_w4a4_tensor_core_route(nv, oracle, tokens, n, k):
+    rng = np.random.default_rng(tokens + n + k)
+    codes, scales, d_w = make_weight(rng, n, k)
+    d_in = 448.0
+    w = nv.Weight.from_planes(codes, scales, d_w, d_in)
+    x = torch.randn(tokens, k, generator=torch.Generator().manual_seed(k + tokens)).to(torch.bfloat16)
+    ref = w4a4_reference(oracle, codes, scales, n, k, d_w, d_in, x)
+    ws = nv.Workspace(nv.workspace_bytes(n, k, nv.ALLOW_A4, tokens))
+    y32 = nv.linear(x.cuda(), w, policy=nv.ALLOW_A4, epilogue=nv.OUT_F32, workspace=ws)
+    assert ws.status() == 0
+    check_f32(y32, ref)
+    y16 = nv.linear(x.cuda(), w, policy=nv.ALLOW_A4, workspace=ws)
+    assert ws.status() == 0
+    check_bf16(y16, ref)
+    # and inside the reference's own A4 allowance against the unquantized product
+    exact = ref_product(oracle, codes, scales, n, k, d_w, x)
+    got = y16.double().cpu().numpy()
+    assert np.linalg.norm(got - exact) <= 0.16 * np.linalg.norm(exact)
+    # the route needs its workspace
+    with pytest.raises(nv.Nvfp4Error):
+        nv.linear(x.cuda(), w, policy=nv.ALLOW_A4)
