@@ -40,6 +40,8 @@ NVFP4_SYMBOLS = {
                                              C.POINTER(Workspace), C.c_void_p]),
     "b200q_nvfp4_linear_swiglu": (C.c_int32, [C.POINTER(Nvfp4Weight), C.c_void_p, C.c_uint32, C.c_void_p, C.c_uint32,
                                               C.c_uint32, C.POINTER(Workspace), C.c_void_p]),
+    "b200q_nvfp4_linear_noalloc": (C.c_int32, [C.POINTER(Nvfp4Weight), C.c_void_p, C.c_uint32, C.c_void_p, C.c_uint32,
+                                               C.c_uint32, C.c_void_p]),
     "b200q_nvfp4_dequantize": (C.c_int32, [C.POINTER(Nvfp4Weight), C.c_void_p, C.c_void_p]),
     "b200q_nvfp4_quantize_activations": (C.c_int32, [C.c_void_p, C.c_uint32, C.c_uint32, C.c_float, C.c_void_p,
                                                      C.c_void_p, C.c_void_p]),

@@ -18,9 +18,14 @@
 //
 // Every wait on an mbarrier is bounded: after the limit the thread records a status bit in the
 // workspace, stops issuing and the CTA tears down (tensor memory freed) instead of hanging.
+#include "../../include/b200q_nvfp4.h"
+
 #include "nvfp4_internal.cuh"
 
 #include <cuda.h>
+
+#include <cmath>
+#include <mutex>
 
 namespace b200q {
 namespace {
@@ -391,3 +396,81 @@ int32_t w4a4_launch(ErrorSlot &slot, const DeviceState &dev, const uint8_t *w_co
 }
 
 }  // namespace b200q
+
+// ---- the entry that allocates nothing ------------------------------------------------------------
+//
+// The W4A4 route keeps the quantized activations and a status line in scratch memory. Here that
+// scratch is a fixed array inside the library's own device image instead of a caller-supplied
+// workspace, for callers that have no way to hand over device memory when they call.
+namespace b200q {
+namespace {
+
+static __device__ __align__(256) uint8_t g_static_scratch[B200Q_NVFP4_NOALLOC_SCRATCH_BYTES];
+
+constexpr int kMaxScratchDevices = 64;
+// The array's address on each device. In host code the symbol `g_static_scratch` itself is only a
+// handle for the runtime, never a device pointer: the address a kernel can use comes from
+// cudaGetSymbolAddress, asked once per device while that device is current.
+uint8_t *g_scratch_address[kMaxScratchDevices] = {};
+std::mutex g_scratch_mutex;
+
+int32_t static_scratch(ErrorSlot &slot, cudaStream_t stream, uint8_t **out) {
+  int device = -1;
+  cudaError_t err = cudaGetDevice(&device);
+  if (err != cudaSuccess) return fail(slot, "b200q_nvfp4_linear_noalloc: no CUDA device: %s", cudaGetErrorString(err));
+  if (device < 0 || device >= kMaxScratchDevices) return fail(slot, "b200q_nvfp4_linear_noalloc: device ordinal %d is out of range", device);
+  std::lock_guard<std::mutex> lock(g_scratch_mutex);
+  if (g_scratch_address[device] == nullptr) {
+    void *address = nullptr;
+    err = cudaGetSymbolAddress(&address, g_static_scratch);
+    if (err != cudaSuccess || address == nullptr) {
+      return fail(slot, "b200q_nvfp4_linear_noalloc: cudaGetSymbolAddress failed: %s", cudaGetErrorString(err));
+    }
+    // the status line must start at zero; everything else is rewritten by every call
+    err = cudaMemsetAsync(address, 0, 256, stream);
+    if (err != cudaSuccess) return fail(slot, "b200q_nvfp4_linear_noalloc: clearing the status line failed: %s", cudaGetErrorString(err));
+    g_scratch_address[device] = static_cast<uint8_t *>(address);
+  }
+  *out = g_scratch_address[device];
+  return 0;
+}
+
+bool is_aligned(const void *p, uintptr_t a) { return (reinterpret_cast<uintptr_t>(p) & (a - 1)) == 0; }
+
+}  // namespace
+}  // namespace b200q
+
+extern "C" int32_t b200q_nvfp4_linear_noalloc(const b200q_nvfp4_weight *w, const void *x, uint32_t tokens, void *y,
+                                              uint32_t ldy, uint32_t epilogue, void *stream) {
+  using namespace b200q;
+  ErrorSlot &slot = nvfp4_error();
+  const char *what = "b200q_nvfp4_linear_noalloc";
+  if (w == nullptr || w->codes == nullptr || w->scales == nullptr) return fail(slot, "%s: weight is NULL", what);
+  if (w->n == 0 || (w->n % 128u) != 0) return fail(slot, "%s: n = %u is not a positive multiple of 128", what, w->n);
+  if (w->k == 0 || (w->k % 256u) != 0) return fail(slot, "%s: k = %u is not a positive multiple of 256", what, w->k);
+  if (!is_aligned(w->codes, 32) || !is_aligned(w->scales, 16)) return fail(slot, "%s: weight planes are misaligned", what);
+  if (!std::isfinite(w->weight_scale_divisor) || !(w->weight_scale_divisor > 0.0f) ||
+      !std::isfinite(w->input_scale_divisor) || !(w->input_scale_divisor > 0.0f)) {
+    return fail(slot, "%s: both scale divisors must be finite and positive", what);
+  }
+  if (tokens == 0) return fail(slot, "%s: tokens must be positive", what);
+  if ((epilogue & ~static_cast<uint32_t>(B200Q_NVFP4_OUT_F32)) != 0u) return fail(slot, "%s: only STORE (optionally OUT_F32) is served", what);
+  if (x == nullptr || !is_aligned(x, 16)) return fail(slot, "%s: x is NULL or not 16-byte aligned", what);
+  if (y == nullptr || !is_aligned(y, 16) || (ldy % 8u) != 0 || ldy < w->n) {
+    return fail(slot, "%s: y must be 16-byte aligned, ldy a multiple of 8 and at least n", what);
+  }
+  const uint64_t need = w4a4_workspace_bytes(w->k, tokens);
+  if (need > B200Q_NVFP4_NOALLOC_SCRATCH_BYTES) {
+    return fail(slot, "%s: %u tokens at k = %u need %llu bytes of scratch, the built-in array holds %llu", what, tokens, w->k,
+                static_cast<unsigned long long>(need), static_cast<unsigned long long>(B200Q_NVFP4_NOALLOC_SCRATCH_BYTES));
+  }
+  const DeviceState *dev = device_state(slot);
+  if (dev == nullptr) return -1;
+  if (!dev->prepared) return fail(slot, "%s: the device was not prepared (call b200q_nvfp4_prepare at load)", what);
+  uint8_t *scratch = nullptr;
+  if (static_scratch(slot, static_cast<cudaStream_t>(stream), &scratch) != 0) return -1;
+  return w4a4_launch(slot, *dev, static_cast<const uint8_t *>(w->codes), static_cast<const uint8_t *>(w->scales), w->n, w->k,
+                     w->weight_scale_divisor, w->input_scale_divisor, static_cast<const uint16_t *>(x), tokens, y, ldy,
+                     epilogue, scratch, static_cast<cudaStream_t>(stream));
+}
+

@@ -182,6 +182,21 @@ def linear(x: torch.Tensor, w: Weight, out: torch.Tensor | None = None, policy: 
     return y
 
 
+NOALLOC_SCRATCH_BYTES = 6 << 20
+
+
+def linear_noalloc(x: torch.Tensor, w: Weight, out: torch.Tensor, epilogue: int = STORE) -> torch.Tensor:
+    """``b200q_nvfp4_linear_noalloc``: the W4A4 linear with its scratch inside the library. The
+    caller passes the output too, so nothing is allocated anywhere on this path."""
+    _check_x(x, w.k)
+    tokens = x.shape[0]
+    y = _out(tokens, w.n, epilogue, out, x.device)
+    ws = w.c_struct()
+    _check(_lib.load().b200q_nvfp4_linear_noalloc(C.byref(ws), x.data_ptr(), tokens, y.data_ptr(), y.stride(0), epilogue,
+                                                   _stream()))
+    return y
+
+
 def linear_group(x: torch.Tensor, weights: list[Weight], outs: list[torch.Tensor] | None = None,
                  policy: int = A16_ONLY, epilogue: int = STORE) -> list[torch.Tensor]:
     """Several weights of the same k over one x in one pass (the reference's split-output parents)."""

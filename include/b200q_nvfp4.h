@@ -131,6 +131,30 @@ int32_t b200q_nvfp4_quantize_activations(const void *x, uint32_t tokens, uint32_
                                          float input_scale_divisor, void *codes, void *scales,
                                          void *stream);
 
+/* The tensor-core W4A4 linear without any caller-supplied scratch. No counterpart in the
+ * reference: its ops always take a workspace the load reserved.
+ *
+ * Who it is for: a caller that cannot obtain device memory at the moment it calls - an engine
+ * whose device arena was sealed at load with no plan line for this op, a plugin running inside a
+ * host that owns all device memory, or a latency-critical loop where cudaMalloc's device-wide
+ * synchronisation is not acceptable. The quantized activations and the status line live in an
+ * array of B200Q_NVFP4_NOALLOC_SCRATCH_BYTES built into the library's device image; every GPU that
+ * loads the library holds that array until the process exits. The call itself allocates nothing,
+ * on the host or the device.
+ *
+ * Same result as b200q_nvfp4_linear under B200Q_NVFP4_ALLOW_A4 (any token count >= 1 takes the
+ * tensor-core route here): y = BF16 (or float32 with B200Q_NVFP4_OUT_F32) of acc / (d_in d_w),
+ * STORE only, k a multiple of 256, y 16-byte aligned, ldy a multiple of 8.
+ * Limit: 256 + ceil128(tokens) * k * 9 / 16 bytes must fit the array (for example 2048 tokens at
+ * k = 5120, 512 tokens at k = 17408); larger calls return -1 and say so.
+ * The first call on a device looks the array's address up and clears its status line; make that
+ * first call outside any stream capture. All calls on a device share the one array and it keeps
+ * the previous call's contents (each call rewrites all it reads), so two calls whose kernels
+ * overlap on the GPU - different streams, no ordering between them - race; order them. */
+#define B200Q_NVFP4_NOALLOC_SCRATCH_BYTES (6u << 20)
+int32_t b200q_nvfp4_linear_noalloc(const b200q_nvfp4_weight *w, const void *x, uint32_t tokens, void *y,
+                                   uint32_t ldy, uint32_t epilogue, void *stream);
+
 /* Thread-local message from the most recent failed call. Never NULL. */
 const char *b200q_nvfp4_last_error(void);
 
