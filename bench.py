@@ -208,6 +208,128 @@ def build_workload(layers: int, rank: int, world: int, tokens: int, device):
     return weights, host_inputs, inputs, outputs
 
 
+TRELLIS_LAYER = [("q", 5120, 6144), ("k", 5120, 1024), ("v", 5120, 1024), ("o", 6144, 5120), ("gate", 5120, 17408),
+                 ("up", 5120, 17408), ("down", 17408, 5120)]  # (name, in, out), configs[3]
+
+
+def build_trellis_workload(layers: int, rank: int, world: int, tokens: int, device):
+    """configs[3]: the layer's seven shapes at 3 bits per weight (k2 = 6), random words (every bit
+    pattern is a valid encoding), suh / svh = +-(0.5..2) x {0.05, 0.03}."""
+    import torch
+
+    from ignis_b200 import trellis
+
+    gen = torch.Generator(device=device)
+    weights = []
+    total = 0
+    for layer in range(layers):
+        entry = {}
+        for idx, (name, in_, out) in enumerate(TRELLIS_LAYER):
+            cols = out // world
+            gen.manual_seed(20261127 + (layer * 16 + idx) * 64 + rank)
+            words = torch.randint(-32768, 32767, ((in_ // 16) * (cols // 16) * 48,), dtype=torch.int16, device=device,
+                                  generator=gen)
+            suh = ((torch.rand(in_, device=device, generator=gen) * 1.5 + 0.5) * 0.05).to(torch.float16)
+            svh = ((torch.rand(cols, device=device, generator=gen) * 1.5 + 0.5) * 0.03).to(torch.float16)
+            entry[name] = trellis.Weight(words, suh, svh, 6, in_, cols)
+            if layer == 0:
+                total += trellis.weight_bytes(in_, cols, 6) + tokens * in_ * 2 + tokens * cols * 2
+        weights.append(entry)
+    cpu_gen = torch.Generator().manual_seed(20261127)
+    inputs = {w: torch.randn(tokens, w, generator=cpu_gen).to(torch.bfloat16).to(device) for w in (5120, 6144, 17408)}
+    outputs = {name: torch.empty(tokens, out // world, dtype=torch.bfloat16, device=device) for name, _, out in TRELLIS_LAYER}
+    return weights, inputs, outputs, total * layers
+
+
+def run_side_workload(args) -> None:
+    """The other measured configs, one JSON line each, same timing rules as the headline:
+    `--workload prefill` (configs[2], W4A4 tensor-core GEMM, TFLOP/s) and `--workload trellis`
+    (configs[3], 3-bit trellis decode, GB/s). One GPU."""
+    import torch
+
+    from ignis_b200 import nvfp4, trellis
+
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device")
+    device = torch.device("cuda", 0)
+    torch.cuda.set_device(device)
+    nvfp4.prepare()
+    trellis.prepare()
+    stream = torch.cuda.Stream()
+    peak_hbm, peak_kind = measured_peak()
+    with torch.cuda.stream(stream):
+        if args.workload == "prefill":
+            tokens = args.tokens if args.tokens > 8 else 8192
+            shapes = [("up", 17408, 5120), ("down", 5120, 17408)]
+            gen = torch.Generator(device=device)
+            ws_bytes = max(nvfp4.workspace_bytes(n, k, nvfp4.ALLOW_A4, tokens) for _, n, k in shapes)
+            ws = nvfp4.Workspace(ws_bytes, device)
+            items = []
+            for idx, (name, n, k) in enumerate(shapes):
+                gen.manual_seed(20261128 + idx)
+                codes = torch.randint(0, 256, (n, k // 2), dtype=torch.uint8, device=device, generator=gen)
+                natural = (torch.randn((n, k // 16), device=device, generator=gen).abs() + 0.1).to(torch.float8_e4m3fn).view(torch.uint8)
+                stored = natural.reshape(n // 128, 4, 32, k // 64, 4).permute(0, 3, 2, 1, 4).contiguous().reshape(-1)
+                w = nvfp4.Weight(codes, stored, n, k, 448.0, 448.0)
+                x = torch.randn(tokens, k, device=device, generator=gen).to(torch.bfloat16)
+                y = torch.empty(tokens, n, dtype=torch.bfloat16, device=device)
+                items.append((w, x, y))
+            flops = sum(2.0 * tokens * w.n * w.k for w, _, _ in items)
+
+            def one_step() -> None:
+                for w, x, y in items:
+                    nvfp4.linear(x, w, out=y, policy=nvfp4.ALLOW_A4, workspace=ws)
+
+            launches = 2 * len(items)
+            metric, unit, work = "nvfp4_prefill_gemm_tflops", "TFLOP/s", flops / 1e12
+            workload = f"configs[2]: NVFP4 W4A4 prefill GEMM, M={tokens}, up 5120->17408 and down 17408->5120, fused-layout activation quantizer + tcgen05 block-scaled MMA"
+        else:
+            weights, inputs, outputs, nbytes = build_trellis_workload(args.layers, 0, 1, args.tokens, device)
+            by = {name: (in_, out) for name, in_, out in TRELLIS_LAYER}
+
+            def one_step() -> None:
+                for layer in weights:
+                    for name, w in layer.items():
+                        trellis.linear(w, inputs[by[name][0]], out=outputs[name])
+
+            launches = 7 * args.layers
+            metric, unit, work = "trellis_gemv_gbs", "GB/s", nbytes / 1e9
+            workload = f"configs[3]: trellis 3 bpw decode, M={args.tokens}, 27B-style layer x {args.layers} layers of distinct weights"
+        one_step()
+        stream.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph, stream=stream):
+            one_step()
+        for _ in range(args.warmup):
+            graph.replay()
+        torch.cuda.synchronize()
+        start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        with ClockSampler(0) as clocks:
+            start.record(stream)
+            for _ in range(args.steps):
+                graph.replay()
+            stop.record(stream)
+            torch.cuda.synchronize()
+        ms = start.elapsed_time(stop) / args.steps
+    value = work / (ms * 1e-3)
+    if args.workload == "prefill":
+        status = ws.status()
+        peak = 4.0 * 1403.2
+        roof = {"bound": "tensor", "achieved": value, "peak": peak, "unit": "TFLOP/s", "frac": value / peak,
+                "peak_source": "4 x the measured sustained BF16 cuBLAS rate (FP4 dense is 4 x BF16 dense on this part)",
+                "frac_of_nominal_9000": value / 9000.0, "kernel": "w4a4_gemm_kernel", "traffic": None,
+                "device_status": status}
+    else:
+        roof = {"bound": "hbm", "achieved": value, "peak": peak_hbm, "unit": "GB/s", "frac": value / peak_hbm,
+                "peak_source": f"{peak_kind} copy bandwidth; the kernel is instruction-issue bound (about 5 integer operations per weight)",
+                "kernel": "trellis_linear_kernel", "traffic": None}
+    print(json.dumps({"metric": metric, "value": value, "unit": unit, "n_gpus": 1, "steps": args.steps, "warmup": args.warmup,
+                      "ms_per_step": ms, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+                      "dtype": "e2m1xe2m1->f32" if args.workload == "prefill" else "f16xf16->f32", "data": "synthetic",
+                      "config": {"workload": workload, "cuda_graph": True, "l2": "inputs larger than L2"},
+                      "gpu_launches": launches * args.steps, "clocks": clocks.summary(), "roofline": roof}))
+
+
 def run_cuda_arm(args) -> None:
     import torch
     import torch.distributed as dist
@@ -343,9 +465,13 @@ def main() -> None:
     ap.add_argument("--group", type=int, default=1, help="1: q|k|v and gate|up share one launch each; 0: seven launches per layer")
     ap.add_argument("--graph", type=int, default=1, help="replay the step as one CUDA graph")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--workload", default="decode", choices=["decode", "prefill", "trellis"],
+                    help="decode: configs[1] (the headline); prefill: configs[2]; trellis: configs[3]")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference_arm(args)
+    elif args.workload != "decode":
+        run_side_workload(args)
     else:
         run_cuda_arm(args)
 

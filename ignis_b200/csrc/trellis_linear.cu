@@ -185,6 +185,19 @@ struct TileWords {
   uint32_t w[8][3];
 };
 
+// The lane's three words of each of the 8 tiles of one 16-input step. `p0/p1/p2` point at the
+// lane's words w0/w1/w2 of the step's first tile; tiles are 4 K2 words apart (a compile-time
+// distance, so the loads carry immediate offsets).
+template <int K2>
+__device__ __forceinline__ void load_step(TileWords &tw, const uint32_t *p0, const uint32_t *p1, const uint32_t *p2) {
+#pragma unroll
+  for (int j = 0; j < 8; ++j) {
+    tw.w[j][0] = __ldg(p0 + j * 4 * K2);
+    tw.w[j][1] = __ldg(p1 + j * 4 * K2);
+    tw.w[j][2] = __ldg(p2 + j * 4 * K2);
+  }
+}
+
 // One step of 16 inputs: the 8 tiles of the column block, decoded and multiplied.
 template <int K2>
 __device__ __forceinline__ void step_tiles(const TileWords &tw, uint32_t off, const uint2 bfrag, float (&acc)[8][4]) {
@@ -196,26 +209,63 @@ __device__ __forceinline__ void step_tiles(const TileWords &tw, uint32_t off, co
   }
 }
 
-__device__ __forceinline__ void step_tiles_any(uint32_t k2, const TileWords &tw, uint32_t off, const uint2 bfrag,
-                                               float (&acc)[8][4]) {
-  switch (k2) {
-    case 4: step_tiles<4>(tw, off, bfrag, acc); break;
-    case 5: step_tiles<5>(tw, off, bfrag, acc); break;
-    case 6: step_tiles<6>(tw, off, bfrag, acc); break;
-    case 8: step_tiles<8>(tw, off, bfrag, acc); break;
-    case 10: step_tiles<10>(tw, off, bfrag, acc); break;
-    default: step_tiles<12>(tw, off, bfrag, acc); break;
+// A warp's walk over its 128-input blocks [blk, b1) in strides of `stride` blocks: 8 steps per
+// block, the words of the next step in flight while the current one is decoded (two register
+// buffers, alternating). Accumulators live in the units of the current block's per-token scale
+// and are carried into the next block's units by an exact power-of-two factor.
+template <int K2>
+__device__ __forceinline__ void walk_blocks(const uint32_t *col_base, uint64_t tk_stride, const LaneWindow &win, uint32_t blk,
+                                            uint32_t b0, uint32_t b1, uint32_t stride, const uint2 *xs_side,
+                                            const float *inv_side, const float *scale_side, int lane, float (&tot)[8][4]) {
+  if (blk >= b1) return;
+  const int t2 = (lane & 3) * 2;
+  // Three running pointers (the lane's words w0, w1, w2 of the step to load next); every load is
+  // pointer + compile-time offset. Inside a block the next step is one tile row further; after a
+  // block's last step the pointers jump to the warp's next block.
+  const uint32_t *q0 = col_base + win.w0 + static_cast<uint64_t>(blk) * 8u * tk_stride;
+  const uint32_t *q1 = q0 + (static_cast<int64_t>(win.w1) - static_cast<int64_t>(win.w0));
+  const uint32_t *q2 = q0 + (static_cast<int64_t>(win.w2) - static_cast<int64_t>(win.w0));
+  const int64_t step = static_cast<int64_t>(tk_stride);
+  const int64_t jump = static_cast<int64_t>(static_cast<uint64_t>(stride) * 8u - 7u) * step;
+  TileWords even, odd;
+  load_step<K2>(even, q0, q1, q2);
+  q0 += step, q1 += step, q2 += step;
+  float carry0 = 0.0f, carry1 = 0.0f;
+  for (; blk < b1; blk += stride) {
+    const uint32_t bl = blk - b0;
+    const float f0 = carry0 * scale_side[bl * 8 + t2], f1 = carry1 * scale_side[bl * 8 + t2 + 1];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      tot[j][0] *= f0;
+      tot[j][1] *= f1;
+      tot[j][2] *= f0;
+      tot[j][3] *= f1;
+    }
+    // after this block's last step: on to the next block, or (last block) back one step, so the
+    // final prefetch re-reads the last step instead of running past the tensor
+    const int64_t after = blk + stride < b1 ? jump : -step;
+    const uint2 *xb = xs_side + static_cast<size_t>(bl) * 8 * 32 + lane;
+#pragma unroll
+    for (int kt = 0; kt < 8; kt += 2) {
+      load_step<K2>(odd, q0, q1, q2);  // step kt + 1
+      {
+        const int64_t d = kt + 1 == 7 ? after : step;
+        q0 += d, q1 += d, q2 += d;
+      }
+      step_tiles<K2>(even, win.off, xb[kt * 32], tot);
+      load_step<K2>(even, q0, q1, q2);  // step kt + 2, or the first step of the next block
+      q0 += step, q1 += step, q2 += step;
+      step_tiles<K2>(odd, win.off, xb[(kt + 1) * 32], tot);
+    }
+    carry0 = inv_side[bl * 8 + t2];
+    carry1 = inv_side[bl * 8 + t2 + 1];
   }
-}
-
-__device__ __forceinline__ void load_tile_words(TileWords &tw, const uint32_t *row_base, uint32_t tile_words,
-                                                const LaneWindow &win, bool live) {
 #pragma unroll
   for (int j = 0; j < 8; ++j) {
-    const uint32_t *t = row_base + j * tile_words;
-    tw.w[j][0] = live ? __ldg(t + win.w0) : 0u;
-    tw.w[j][1] = live ? __ldg(t + win.w1) : 0u;
-    tw.w[j][2] = live ? __ldg(t + win.w2) : 0u;
+    tot[j][0] *= carry0;
+    tot[j][1] *= carry1;
+    tot[j][2] *= carry0;
+    tot[j][3] *= carry1;
   }
 }
 
@@ -247,14 +297,11 @@ __global__ void __launch_bounds__(kThreads, 2) trellis_linear_kernel(const __gri
   float *inv_s = reinterpret_cast<float *>(smem_raw + region + 2 * 8 * 32 * 16);  // [side][block][token 8]
   float *scale_s = inv_s + static_cast<size_t>(sides) * p.slice_cap * 8;
 
-  // ---- prefetch the first step's weight words: they never depend on the previous kernel ----
   const LaneWindow win = lane_window(S.k2, lane);
   const uint32_t tile_words = 4u * S.k2;
   const uint32_t *col_base = S.trellis + static_cast<uint64_t>(col_block) * 8u * tile_words;
   const uint64_t tk_stride = static_cast<uint64_t>(S.tile_stride) * tile_words;
-  uint32_t blk = b0 + static_cast<uint32_t>(wslot);  // this warp's current block
-  TileWords cur, nxt;
-  load_tile_words(cur, col_base + static_cast<uint64_t>(blk) * 8u * tk_stride, tile_words, win, blk < b1);
+  const uint32_t blk_first = b0 + static_cast<uint32_t>(wslot);  // this warp's first block
 
   griddep_launch_dependents();
   griddep_wait();
@@ -306,46 +353,23 @@ __global__ void __launch_bounds__(kThreads, 2) trellis_linear_kernel(const __gri
   __syncthreads();
 
   // ---- main loop: this warp's blocks, 8 steps of 16 inputs each ----
-  // The accumulators live in the units of the current block's per-token scale and are carried
-  // into the next block's units by an exact power-of-two factor.
   float tot[8][4];
 #pragma unroll
   for (int j = 0; j < 8; ++j)
 #pragma unroll
     for (int e = 0; e < 4; ++e) tot[j][e] = 0.0f;
-  const int t2 = (lane & 3) * 2;  // the tokens of this lane's accumulators
-  float carry0 = 0.0f, carry1 = 0.0f;  // inverse scales of the block just finished
-  for (; blk < b1; blk += lanes_per_side) {
-    const size_t blk_slot = static_cast<size_t>(side) * p.slice_cap + (blk - b0);
-    const float f0 = carry0 * scale_s[blk_slot * 8 + t2], f1 = carry1 * scale_s[blk_slot * 8 + t2 + 1];
-#pragma unroll
-    for (int j = 0; j < 8; ++j) {
-      tot[j][0] *= f0;
-      tot[j][1] *= f1;
-      tot[j][2] *= f0;
-      tot[j][3] *= f1;
+  {
+    const size_t side_slot = static_cast<size_t>(side) * p.slice_cap;
+    const uint2 *xs_side = xs + side_slot * 8 * 32;
+    const float *inv_side = inv_s + side_slot * 8, *scale_side = scale_s + side_slot * 8;
+    switch (S.k2) {
+      case 4: walk_blocks<4>(col_base, tk_stride, win, blk_first, b0, b1, lanes_per_side, xs_side, inv_side, scale_side, lane, tot); break;
+      case 5: walk_blocks<5>(col_base, tk_stride, win, blk_first, b0, b1, lanes_per_side, xs_side, inv_side, scale_side, lane, tot); break;
+      case 6: walk_blocks<6>(col_base, tk_stride, win, blk_first, b0, b1, lanes_per_side, xs_side, inv_side, scale_side, lane, tot); break;
+      case 8: walk_blocks<8>(col_base, tk_stride, win, blk_first, b0, b1, lanes_per_side, xs_side, inv_side, scale_side, lane, tot); break;
+      case 10: walk_blocks<10>(col_base, tk_stride, win, blk_first, b0, b1, lanes_per_side, xs_side, inv_side, scale_side, lane, tot); break;
+      default: walk_blocks<12>(col_base, tk_stride, win, blk_first, b0, b1, lanes_per_side, xs_side, inv_side, scale_side, lane, tot); break;
     }
-#pragma unroll 1
-    for (int kt = 0; kt < 8; ++kt) {
-      // prefetch the next step (of this block, or the first of the warp's next block)
-      const bool last = kt == 7;
-      const uint32_t blk_next = last ? blk + lanes_per_side : blk;
-      const uint32_t kt_next = last ? 0u : static_cast<uint32_t>(kt + 1);
-      load_tile_words(nxt, col_base + (static_cast<uint64_t>(blk_next) * 8u + kt_next) * tk_stride, tile_words, win,
-                      blk_next < b1);
-      const uint2 bfrag = xs[(blk_slot * 8 + kt) * 32 + lane];
-      step_tiles_any(S.k2, cur, win.off, bfrag, tot);
-      cur = nxt;
-    }
-    carry0 = inv_s[blk_slot * 8 + t2];
-    carry1 = inv_s[blk_slot * 8 + t2 + 1];
-  }
-#pragma unroll
-  for (int j = 0; j < 8; ++j) {
-    tot[j][0] *= carry0;
-    tot[j][1] *= carry1;
-    tot[j][2] *= carry0;
-    tot[j][3] *= carry1;
   }
 
   // ---- reduce the warps of each side (fixed order), then the cluster ----
