@@ -8,5 +8,6 @@ without a CUDA device raises.
 from . import _lib  # noqa: F401
 from . import nvfp4  # noqa: F401
 from . import trellis  # noqa: F401
+from . import moe  # noqa: F401
 
-__all__ = ["nvfp4", "trellis"]
+__all__ = ["nvfp4", "trellis", "moe"]

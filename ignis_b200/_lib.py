@@ -68,7 +68,49 @@ TRELLIS_SYMBOLS = {
     "ignis_trellis_last_error": (C.c_char_p, []),
 }
 
-ALL_SYMBOLS = {**NVFP4_SYMBOLS, **TRELLIS_SYMBOLS}
+class MoeSlot(C.Structure):
+    """``ignis_moe_slot`` (include/ignis_moe.h), 16 bytes."""
+
+    _fields_ = [("record", C.c_void_p), ("k2", C.c_uint32), ("reserved", C.c_uint32)]
+
+
+class MoeWorkspace(C.Structure):
+    """``ignis_moe_workspace``, 24 bytes."""
+
+    _fields_ = [("base", C.c_void_p), ("decode_tokens", C.c_uint32), ("prefill_tokens", C.c_uint32),
+                ("decode_route", C.c_uint32)]
+
+
+class MoePlan(C.Structure):
+    """``ignis_moe_plan``, five u64."""
+
+    _fields_ = [("workspace", C.c_uint64), ("acc", C.c_uint64), ("router", C.c_uint64), ("shared", C.c_uint64),
+                ("total", C.c_uint64)]
+
+
+_experts_args = [C.c_void_p, C.c_uint32, C.c_void_p, C.c_void_p, C.c_void_p, C.POINTER(MoeWorkspace), C.c_void_p, C.c_void_p]
+MOE_SYMBOLS = {
+    "b200q_moe_set_geometry": (C.c_int32, [C.c_uint32] * 4),
+    "ignis_moe_record_bytes": (C.c_int32, [C.c_uint32, C.c_uint32, C.POINTER(C.c_uint64)]),
+    "ignis_moe_trellis_reconstruct": (C.c_int32, [C.c_void_p, C.c_uint32, C.c_uint32, C.c_uint32, C.c_void_p, C.c_void_p]),
+    "ignis_moe_router": (C.c_int32, [C.c_void_p, C.c_uint32, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p]),
+    "ignis_moe_router_logits": (C.c_int32, [C.c_void_p, C.c_uint32, C.c_void_p, C.c_void_p, C.c_void_p]),
+    "ignis_moe_prepare": (C.c_int32, []),
+    "ignis_moe_workspace_bytes": (C.c_uint64, [C.c_uint32, C.c_uint32]),
+    "ignis_moe_workspace_init": (C.c_int32, [C.POINTER(MoeWorkspace), C.c_void_p, C.c_void_p]),
+    "ignis_moe_plan_bytes": (C.c_int32, [C.c_uint32, C.c_uint32, C.POINTER(MoePlan)]),
+    "ignis_moe_experts_decode": (C.c_int32, _experts_args),
+    "ignis_moe_experts_prefill": (C.c_int32, _experts_args),
+    "ignis_moe_decode_cluster_size": (C.c_int32, []),
+    "ignis_moe_shared_expert": (C.c_int32, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_uint32, C.c_void_p,
+                                            C.c_void_p, C.c_void_p]),
+    "ignis_moe_combine": (C.c_int32, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_uint32, C.c_void_p, C.c_void_p]),
+    "ignis_moe_stream_sync": (C.c_int32, [C.c_void_p]),
+    "ignis_moe_workspace_status": (C.c_int32, [C.POINTER(MoeWorkspace), C.c_void_p, C.POINTER(C.c_uint32)]),
+    "ignis_moe_last_error": (C.c_char_p, []),
+}
+
+ALL_SYMBOLS = {**NVFP4_SYMBOLS, **TRELLIS_SYMBOLS, **MOE_SYMBOLS}
 
 
 def load() -> C.CDLL:

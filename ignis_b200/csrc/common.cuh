@@ -46,6 +46,10 @@ DeviceState *device_state(ErrorSlot &slot);
 // Prepares the current device once (thread-safe). 0 on success.
 int32_t prepare_device(ErrorSlot &slot);
 
+// The trellis tile decoder as a launch (trellis_linear.cu), shared by the dense and MoE entry points.
+int32_t trellis_reconstruct_raw(ErrorSlot &slot, const char *what, const void *trellis, uint32_t k2, uint32_t in,
+                                uint32_t out, uint32_t tile_stride, void *w_f16, void *stream);
+
 // ---- launch helper -----------------------------------------------------------------------------
 // Launches with the programmatic-stream-serialization attribute when `pdl` is set: the kernel may
 // start while its predecessor in the stream drains, and orders itself with griddep_wait().

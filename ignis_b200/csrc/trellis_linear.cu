@@ -24,74 +24,16 @@
 // for its predecessor in the stream.
 #include "../../include/ignis_trellis_linear.h"
 
-#include "common.cuh"
+#include "trellis_device.cuh"
 
 namespace b200q {
 namespace {
 
-constexpr uint32_t kMul1 = 0x83DCD12Du;
+using namespace trellis_dev;
+
 constexpr int kThreads = 256;
 constexpr int kWarps = 8;
 constexpr uint32_t kMaxSliceBlocks = 40;  // 128-input blocks of rotated activations a CTA holds (80 KB)
-
-// Exclusive end bit of step p in a tile of class k2 = 2 K.
-__host__ __device__ constexpr int step_end(int k2, int p) {
-  return k2 == 5 ? 3 * ((p + 1) / 2) + 2 * (p / 2 + 1) : (k2 / 2) * (p + 1);
-}
-
-struct LaneWindow {
-  uint32_t w0, w1, w2;  // word indices inside the tile
-  uint32_t off;         // bit offset of the lane's first window bit inside word w0
-};
-
-__device__ __forceinline__ LaneWindow lane_window(uint32_t k2, int lane) {
-  const int words = 4 * static_cast<int>(k2), bits = 128 * static_cast<int>(k2);
-  int first = 4 * static_cast<int>(k2) * lane + static_cast<int>(k2 >> 1) - 16;  // end of step 8 lane, minus 16
-  if (first < 0) first += bits;
-  LaneWindow w;
-  w.w0 = static_cast<uint32_t>(first >> 5);
-  w.off = static_cast<uint32_t>(first & 31);
-  w.w1 = w.w0 + 1 == static_cast<uint32_t>(words) ? 0u : w.w0 + 1;
-  w.w2 = w.w1 + 1 == static_cast<uint32_t>(words) ? 0u : w.w1 + 1;
-  return w;
-}
-
-// The lane's eight weights from its three words: four half2 in step order (steps 0,1 | 2,3 | 4,5 |
-// 6,7), i.e. tile elements (r0, c0) (r0+1, c0) | (r0+8, c0) (r0+9, c0) | the same rows at c0 + 8,
-// r0 = 2 (lane % 4), c0 = lane / 4.
-template <int K2>
-__device__ __forceinline__ void decode8(uint32_t a, uint32_t b, uint32_t c, uint32_t off, uint32_t (&frag)[4]) {
-  const uint32_t hi = __funnelshift_l(b, a, off);
-  const uint32_t mid = __funnelshift_l(c, b, off);
-  uint32_t code[8];
-#pragma unroll
-  for (int j = 0; j < 8; ++j) {
-    constexpr int base = step_end(K2, 0);
-    const int d = step_end(K2, j) - base;  // constant after unrolling
-    const uint32_t x = d == 0 ? hi : (d < 32 ? __funnelshift_l(mid, hi, d) : mid << (d - 32));
-    code[j] = __dp4a((x >> 16) * kMul1, 0x01010101u, 0x6400u);
-  }
-  const __half2 k_inv = __halves2half2(__ushort_as_half(0x1EEE), __ushort_as_half(0x1EEE));
-  const __half2 k_bias = __halves2half2(__ushort_as_half(0xC931), __ushort_as_half(0xC931));
-#pragma unroll
-  for (int i = 0; i < 4; ++i) {
-    const uint32_t packed = __byte_perm(code[2 * i], code[2 * i + 1], 0x5410);
-    const __half2 v = __hfma2(*reinterpret_cast<const __half2 *>(&packed), k_inv, k_bias);
-    frag[i] = *reinterpret_cast<const uint32_t *>(&v);
-  }
-}
-
-__device__ __forceinline__ void decode8_any(uint32_t k2, uint32_t a, uint32_t b, uint32_t c, uint32_t off,
-                                            uint32_t (&frag)[4]) {
-  switch (k2) {
-    case 4: decode8<4>(a, b, c, off, frag); break;
-    case 5: decode8<5>(a, b, c, off, frag); break;
-    case 6: decode8<6>(a, b, c, off, frag); break;
-    case 8: decode8<8>(a, b, c, off, frag); break;
-    case 10: decode8<10>(a, b, c, off, frag); break;
-    default: decode8<12>(a, b, c, off, frag); break;
-  }
-}
 
 // ---- reconstruct: one warp per tile ---------------------------------------------------------
 __global__ void __launch_bounds__(kThreads) trellis_reconstruct_kernel(const uint32_t *__restrict__ trellis, uint32_t k2,
@@ -141,133 +83,6 @@ struct TrellisParams {
 };
 
 constexpr uint32_t kEpiAdd = 1, kEpiSwiglu = 2;  // 0 stores
-
-// v holds elements 4 lane .. 4 lane + 3 of a 128-vector; on return the vector times the natural
-// order Sylvester Hadamard / sqrt(128): two stages inside the lane, five across lanes.
-__device__ __forceinline__ void hadamard128(float (&v)[4], int lane) {
-  const float a = v[0] + v[1], b = v[0] - v[1], c = v[2] + v[3], d = v[2] - v[3];
-  v[0] = a + c;
-  v[1] = b + d;
-  v[2] = a - c;
-  v[3] = b - d;
-#pragma unroll
-  for (int m = 1; m < 32; m <<= 1) {
-    const bool upper = (lane & m) != 0;
-#pragma unroll
-    for (int i = 0; i < 4; ++i) {
-      const float o = __shfl_xor_sync(0xFFFFFFFFu, v[i], m);
-      v[i] = upper ? o - v[i] : v[i] + o;
-    }
-  }
-#pragma unroll
-  for (int i = 0; i < 4; ++i) v[i] *= 0.08838834764831845f;
-}
-
-__device__ __forceinline__ uint32_t cluster_rank() {
-  uint32_t r;
-  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
-  return r;
-}
-__device__ __forceinline__ void cluster_barrier() {
-  asm volatile("barrier.cluster.arrive.release.aligned;\n"
-               "barrier.cluster.wait.acquire.aligned;" ::: "memory");
-}
-__device__ __forceinline__ float ld_cluster_f32(const float *local_smem, uint32_t rank) {
-  const uint32_t local = static_cast<uint32_t>(__cvta_generic_to_shared(local_smem));
-  uint32_t remote;
-  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(local), "r"(rank));
-  float v;
-  asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(remote) : "memory");
-  return v;
-}
-
-struct TileWords {
-  uint32_t w[8][3];
-};
-
-// The lane's three words of each of the 8 tiles of one 16-input step. `p0/p1/p2` point at the
-// lane's words w0/w1/w2 of the step's first tile; tiles are 4 K2 words apart (a compile-time
-// distance, so the loads carry immediate offsets).
-template <int K2>
-__device__ __forceinline__ void load_step(TileWords &tw, const uint32_t *p0, const uint32_t *p1, const uint32_t *p2) {
-#pragma unroll
-  for (int j = 0; j < 8; ++j) {
-    tw.w[j][0] = __ldg(p0 + j * 4 * K2);
-    tw.w[j][1] = __ldg(p1 + j * 4 * K2);
-    tw.w[j][2] = __ldg(p2 + j * 4 * K2);
-  }
-}
-
-// One step of 16 inputs: the 8 tiles of the column block, decoded and multiplied.
-template <int K2>
-__device__ __forceinline__ void step_tiles(const TileWords &tw, uint32_t off, const uint2 bfrag, float (&acc)[8][4]) {
-#pragma unroll
-  for (int j = 0; j < 8; ++j) {
-    uint32_t frag[4];
-    decode8<K2>(tw.w[j][0], tw.w[j][1], tw.w[j][2], off, frag);
-    mma_f16_f32(acc[j], frag[0], frag[2], frag[1], frag[3], bfrag.x, bfrag.y);
-  }
-}
-
-// A warp's walk over its 128-input blocks [blk, b1) in strides of `stride` blocks: 8 steps per
-// block, the words of the next step in flight while the current one is decoded (two register
-// buffers, alternating). Accumulators live in the units of the current block's per-token scale
-// and are carried into the next block's units by an exact power-of-two factor.
-template <int K2>
-__device__ __forceinline__ void walk_blocks(const uint32_t *col_base, uint64_t tk_stride, const LaneWindow &win, uint32_t blk,
-                                            uint32_t b0, uint32_t b1, uint32_t stride, const uint2 *xs_side,
-                                            const float *inv_side, const float *scale_side, int lane, float (&tot)[8][4]) {
-  if (blk >= b1) return;
-  const int t2 = (lane & 3) * 2;
-  // Three running pointers (the lane's words w0, w1, w2 of the step to load next); every load is
-  // pointer + compile-time offset. Inside a block the next step is one tile row further; after a
-  // block's last step the pointers jump to the warp's next block.
-  const uint32_t *q0 = col_base + win.w0 + static_cast<uint64_t>(blk) * 8u * tk_stride;
-  const uint32_t *q1 = q0 + (static_cast<int64_t>(win.w1) - static_cast<int64_t>(win.w0));
-  const uint32_t *q2 = q0 + (static_cast<int64_t>(win.w2) - static_cast<int64_t>(win.w0));
-  const int64_t step = static_cast<int64_t>(tk_stride);
-  const int64_t jump = static_cast<int64_t>(static_cast<uint64_t>(stride) * 8u - 7u) * step;
-  TileWords even, odd;
-  load_step<K2>(even, q0, q1, q2);
-  q0 += step, q1 += step, q2 += step;
-  float carry0 = 0.0f, carry1 = 0.0f;
-  for (; blk < b1; blk += stride) {
-    const uint32_t bl = blk - b0;
-    const float f0 = carry0 * scale_side[bl * 8 + t2], f1 = carry1 * scale_side[bl * 8 + t2 + 1];
-#pragma unroll
-    for (int j = 0; j < 8; ++j) {
-      tot[j][0] *= f0;
-      tot[j][1] *= f1;
-      tot[j][2] *= f0;
-      tot[j][3] *= f1;
-    }
-    // after this block's last step: on to the next block, or (last block) back one step, so the
-    // final prefetch re-reads the last step instead of running past the tensor
-    const int64_t after = blk + stride < b1 ? jump : -step;
-    const uint2 *xb = xs_side + static_cast<size_t>(bl) * 8 * 32 + lane;
-#pragma unroll
-    for (int kt = 0; kt < 8; kt += 2) {
-      load_step<K2>(odd, q0, q1, q2);  // step kt + 1
-      {
-        const int64_t d = kt + 1 == 7 ? after : step;
-        q0 += d, q1 += d, q2 += d;
-      }
-      step_tiles<K2>(even, win.off, xb[kt * 32], tot);
-      load_step<K2>(even, q0, q1, q2);  // step kt + 2, or the first step of the next block
-      q0 += step, q1 += step, q2 += step;
-      step_tiles<K2>(odd, win.off, xb[(kt + 1) * 32], tot);
-    }
-    carry0 = inv_side[bl * 8 + t2];
-    carry1 = inv_side[bl * 8 + t2 + 1];
-  }
-#pragma unroll
-  for (int j = 0; j < 8; ++j) {
-    tot[j][0] *= carry0;
-    tot[j][1] *= carry1;
-    tot[j][2] *= carry0;
-    tot[j][3] *= carry1;
-  }
-}
 
 __global__ void __launch_bounds__(kThreads, 2) trellis_linear_kernel(const __grid_constant__ TrellisParams p) {
   extern __shared__ __align__(16) uint8_t smem_raw[];
@@ -570,6 +385,27 @@ int32_t run_linear(ErrorSlot &slot, const ignis_trellis_weight *a, const ignis_t
 }
 
 }  // namespace
+
+// The tile decoder as a launch over any [in][out] tensor with 16-aligned extents: shared by
+// ignis_trellis_reconstruct and ignis_moe_trellis_reconstruct.
+int32_t trellis_reconstruct_raw(ErrorSlot &slot, const char *what, const void *trellis, uint32_t k2, uint32_t in,
+                                uint32_t out, uint32_t tile_stride, void *w_f16, void *stream) {
+  if (trellis == nullptr || w_f16 == nullptr) return fail(slot, "%s: NULL argument", what);
+  if (!valid_k2(k2)) return fail(slot, "%s: k2 = %u is not one of 4, 5, 6, 8, 10, 12", what, k2);
+  if (in == 0 || (in % 16u) != 0 || out == 0 || (out % 16u) != 0) return fail(slot, "%s: in and out must be positive multiples of 16", what);
+  if (!aligned(trellis, 4)) return fail(slot, "%s: trellis is not 4-byte aligned", what);
+  if (prepared(slot, what) == nullptr) return -1;
+  const uint32_t tiles_k = in / 16u, tiles_n = out / 16u;
+  const uint32_t stride = tile_stride ? tile_stride : tiles_n;
+  const uint64_t tiles = static_cast<uint64_t>(tiles_k) * tiles_n;
+  const uint32_t grid = static_cast<uint32_t>(tiles / kWarps + 1 < 148u * 8u ? tiles / kWarps + 1 : 148u * 8u);
+  trellis_reconstruct_kernel<<<grid, kThreads, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const uint32_t *>(trellis), k2, tiles_k, tiles_n, stride, static_cast<uint16_t *>(w_f16));
+  const cudaError_t err = cudaGetLastError();
+  if (err != cudaSuccess) return fail(slot, "%s: launch failed: %s", what, cudaGetErrorString(err));
+  return 0;
+}
+
 }  // namespace b200q
 
 using namespace b200q;
@@ -627,23 +463,9 @@ int32_t ignis_trellis_linear_swiglu(const ignis_trellis_weight *gate, const igni
 
 int32_t ignis_trellis_reconstruct(const ignis_trellis_weight *w, void *w_f16, void *stream) {
   ErrorSlot &slot = trellis_error();
-  if (w == nullptr || w->trellis == nullptr) return fail(slot, "ignis_trellis_reconstruct: weight is NULL");
-  if (!valid_k2(w->k2)) return fail(slot, "ignis_trellis_reconstruct: k2 = %u is not one of 4, 5, 6, 8, 10, 12", w->k2);
-  if (w->in == 0 || (w->in % 16u) != 0 || w->out == 0 || (w->out % 16u) != 0) {
-    return fail(slot, "ignis_trellis_reconstruct: in and out must be positive multiples of 16");
-  }
-  if (w_f16 == nullptr) return fail(slot, "ignis_trellis_reconstruct: output is NULL");
-  if (!aligned(w->trellis, 4)) return fail(slot, "ignis_trellis_reconstruct: trellis is not 4-byte aligned");
-  if (prepared(slot, "ignis_trellis_reconstruct") == nullptr) return -1;
-  const uint32_t tiles_k = w->in / 16u, tiles_n = w->out / 16u;
-  const uint32_t stride = w->tile_stride ? w->tile_stride : tiles_n;
-  const uint64_t tiles = static_cast<uint64_t>(tiles_k) * tiles_n;
-  const uint32_t grid = static_cast<uint32_t>(tiles / kWarps + 1 < 148u * 8u ? tiles / kWarps + 1 : 148u * 8u);
-  trellis_reconstruct_kernel<<<grid, kThreads, 0, static_cast<cudaStream_t>(stream)>>>(
-      static_cast<const uint32_t *>(w->trellis), w->k2, tiles_k, tiles_n, stride, static_cast<uint16_t *>(w_f16));
-  const cudaError_t err = cudaGetLastError();
-  if (err != cudaSuccess) return fail(slot, "ignis_trellis_reconstruct: launch failed: %s", cudaGetErrorString(err));
-  return 0;
+  if (w == nullptr) return fail(slot, "ignis_trellis_reconstruct: weight is NULL");
+  return trellis_reconstruct_raw(slot, "ignis_trellis_reconstruct", w->trellis, w->k2, w->in, w->out, w->tile_stride, w_f16,
+                                 stream);
 }
 
 const char *ignis_trellis_last_error(void) { return trellis_error().text; }

@@ -1,0 +1,191 @@
+"""Flash-Next mixture-of-experts ops: the host-side mirror of ``include/ignis_moe.h``.
+
+Names follow the reference's Rust binding of the same ABI (crates/core/src/moe.rs:87-170):
+``record_bytes``, ``trellis_reconstruct``, ``router``, ``router_logits``, ``prepare``,
+``workspace_bytes``, ``plan_bytes``, ``experts_decode``, ``experts_prefill``, ``shared_expert``,
+``combine``; a failed call raises ``MoeError`` carrying ``ignis_moe_last_error()``.
+"""
+from __future__ import annotations
+
+import ctypes as C
+from dataclasses import dataclass
+
+import numpy as np
+import torch
+
+from . import _lib
+
+PROJ_GATE_UP = 0
+PROJ_DOWN = 1
+DECODE_MAX_TOKENS = 8
+
+
+class MoeError(RuntimeError):
+    pass
+
+
+def _check(rc: int) -> None:
+    if rc != 0:
+        raise MoeError(_lib.load().ignis_moe_last_error().decode())
+
+
+def _stream() -> C.c_void_p:
+    return C.c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+@dataclass
+class Geometry:
+    hidden: int = 2560
+    inter: int = 640
+    experts: int = 512
+    top_k: int = 10
+
+
+_geometry = Geometry()
+
+
+def set_geometry(hidden: int, inter: int, experts: int, top_k: int) -> None:
+    """``b200q_moe_set_geometry``: the reference's compile-time geometry made a setting."""
+    global _geometry
+    _check(_lib.load().b200q_moe_set_geometry(hidden, inter, experts, top_k))
+    _geometry = Geometry(hidden, inter, experts, top_k)
+
+
+def geometry() -> Geometry:
+    return _geometry
+
+
+def prepare() -> None:
+    _check(_lib.load().ignis_moe_prepare())
+
+
+def record_bytes(projection: int, k2: int) -> int:
+    out = C.c_uint64(0)
+    _check(_lib.load().ignis_moe_record_bytes(projection, k2, C.byref(out)))
+    return int(out.value)
+
+
+def pack_record(words: np.ndarray, suh: np.ndarray, svh: np.ndarray, projection: int, k2: int) -> np.ndarray:
+    """One expert-projection record as the artifact stores it: trellis words, suh, svh, zero
+    padding to 4096 bytes (docs/formats/flash-next-layout.md section 3)."""
+    body = np.concatenate([np.ascontiguousarray(words).view(np.uint8).reshape(-1),
+                           np.ascontiguousarray(suh).view(np.uint8).reshape(-1),
+                           np.ascontiguousarray(svh).view(np.uint8).reshape(-1)])
+    size = record_bytes(projection, k2)
+    if body.size > size:
+        raise ValueError("record contents exceed the record size of this geometry")
+    out = np.zeros(size, np.uint8)
+    out[: body.size] = body
+    return out
+
+
+class SlotTable:
+    """A layer's slot table on the device: `records` is a list of (bytes, k2) placed in one buffer,
+    `assign[expert][projection]` the index of the record each expert projection uses."""
+
+    def __init__(self, records: list[tuple[np.ndarray, int]], assign: list[tuple[int, int]], device="cuda") -> None:
+        offsets, at = [], 0
+        for blob, _ in records:
+            offsets.append(at)
+            at += (blob.size + 4095) // 4096 * 4096
+        self.buffer = torch.zeros(max(at, 4096), dtype=torch.uint8, device=device)
+        for (blob, _), off in zip(records, offsets):
+            self.buffer[off: off + blob.size] = torch.from_numpy(blob).to(device)
+        base = self.buffer.data_ptr()
+        table = np.zeros(len(assign) * 2, dtype=[("record", np.uint64), ("k2", np.uint32), ("reserved", np.uint32)])
+        for e, pair in enumerate(assign):
+            for proj, idx in enumerate(pair):
+                if idx is not None and idx >= 0:
+                    table[e * 2 + proj] = (base + offsets[idx], records[idx][1], 0)
+        self.slots = torch.from_numpy(table.view(np.uint8)).to(device)
+
+
+class Workspace:
+    """The workspace and the routed accumulator of one MoE block, initialised."""
+
+    def __init__(self, decode_tokens: int, prefill_tokens: int, device="cuda") -> None:
+        nbytes = int(_lib.load().ignis_moe_workspace_bytes(decode_tokens, prefill_tokens))
+        if nbytes == 0:
+            raise MoeError("ignis_moe_workspace_bytes refused the token counts")
+        self.buffer = torch.empty(nbytes, dtype=torch.uint8, device=device)
+        self.c = _lib.MoeWorkspace(self.buffer.data_ptr(), decode_tokens, prefill_tokens, 0)
+        self.acc = torch.empty((max(decode_tokens, prefill_tokens), _geometry.hidden), dtype=torch.int64, device=device)
+        _check(_lib.load().ignis_moe_workspace_init(C.byref(self.c), self.acc.data_ptr(), _stream()))
+
+    def status(self) -> int:
+        word = C.c_uint32(0)
+        _check(_lib.load().ignis_moe_workspace_status(C.byref(self.c), _stream(), C.byref(word)))
+        return int(word.value)
+
+
+def plan_bytes(decode_tokens: int, prefill_tokens: int) -> dict:
+    plan = _lib.MoePlan()
+    _check(_lib.load().ignis_moe_plan_bytes(decode_tokens, prefill_tokens, C.byref(plan)))
+    return {k: int(getattr(plan, k)) for k in ("workspace", "acc", "router", "shared", "total")}
+
+
+def trellis_reconstruct(words: torch.Tensor, k2: int, in_: int, out: int) -> torch.Tensor:
+    w = torch.empty((in_, out), dtype=torch.float16, device=words.device)
+    _check(_lib.load().ignis_moe_trellis_reconstruct(words.data_ptr(), k2, in_, out, w.data_ptr(), _stream()))
+    return w
+
+
+def router(x: torch.Tensor, w_router: torch.Tensor):
+    """(ids int32 [tokens, top_k], weights fp32 [tokens, top_k], logits fp32 [tokens, experts])."""
+    g = _geometry
+    tokens = x.shape[0]
+    ids = torch.empty((tokens, g.top_k), dtype=torch.int32, device=x.device)
+    weights = torch.empty((tokens, g.top_k), dtype=torch.float32, device=x.device)
+    logits = torch.empty((tokens, g.experts), dtype=torch.float32, device=x.device)
+    _check(_lib.load().ignis_moe_router(x.data_ptr(), tokens, w_router.data_ptr(), ids.data_ptr(), weights.data_ptr(),
+                                         logits.data_ptr(), _stream()))
+    return ids, weights, logits
+
+
+def _experts(fn, x, ids, weights, table: SlotTable, ws: Workspace) -> torch.Tensor:
+    tokens = x.shape[0]
+    _check(fn(x.data_ptr(), tokens, ids.data_ptr(), weights.data_ptr(), table.slots.data_ptr(), C.byref(ws.c),
+              ws.acc.data_ptr(), _stream()))
+    return ws.acc
+
+
+def experts_prefill(x, ids, weights, table: SlotTable, ws: Workspace) -> torch.Tensor:
+    """Adds the routed experts of every token into ``ws.acc`` (int64, value = acc * 2^-32)."""
+    return _experts(_lib.load().ignis_moe_experts_prefill, x, ids, weights, table, ws)
+
+
+def experts_decode(x, ids, weights, table: SlotTable, ws: Workspace) -> torch.Tensor:
+    return _experts(_lib.load().ignis_moe_experts_decode, x, ids, weights, table, ws)
+
+
+def fp8_row_scale_payload(w: torch.Tensor) -> np.ndarray:
+    """A [rows, cols] float weight as an FP8 row-scale payload: E4M3FN codes, zero padding to 256
+    bytes, BF16 scales (kernel/include/ignis_fp8_linear.h:4-10)."""
+    w = w.float()
+    amax = w.abs().amax(dim=1).clamp(min=1e-30)
+    scale = (amax / 448.0).to(torch.bfloat16)
+    codes = (w / scale.float().unsqueeze(1)).clamp(-448, 448).to(torch.float8_e4m3fn).view(torch.uint8).numpy()
+    rows, cols = w.shape
+    pad = (rows * cols + 255) // 256 * 256
+    out = np.zeros(pad + 2 * rows, np.uint8)
+    out[: rows * cols] = codes.reshape(-1)
+    out[pad:] = scale.view(torch.int16).numpy().view(np.uint8)
+    return out
+
+
+def shared_expert(gate: torch.Tensor, up: torch.Tensor, down: torch.Tensor, x: torch.Tensor):
+    g = _geometry
+    tokens = x.shape[0]
+    h = torch.empty((tokens, g.inter), dtype=torch.bfloat16, device=x.device)
+    shared = torch.empty((tokens, g.hidden), dtype=torch.float32, device=x.device)
+    _check(_lib.load().ignis_moe_shared_expert(gate.data_ptr(), up.data_ptr(), down.data_ptr(), x.data_ptr(), tokens,
+                                                h.data_ptr(), shared.data_ptr(), _stream()))
+    return shared, h
+
+
+def combine(ws: Workspace, shared: torch.Tensor, x: torch.Tensor, w_gate: torch.Tensor) -> torch.Tensor:
+    tokens = x.shape[0]
+    out = torch.empty((tokens, _geometry.hidden), dtype=torch.bfloat16, device=x.device)
+    _check(_lib.load().ignis_moe_combine(ws.acc.data_ptr(), shared.data_ptr(), x.data_ptr(), w_gate.data_ptr(), tokens,
+                                          out.data_ptr(), _stream()))
+    return out

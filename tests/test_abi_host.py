@@ -41,6 +41,7 @@ def test_struct_layouts():
 
     assert C.sizeof(_lib.Nvfp4Weight) == 32
     assert C.sizeof(_lib.Workspace) == 16
+    assert C.sizeof(_lib.MoeSlot) == 16 and C.sizeof(_lib.MoeWorkspace) == 24 and C.sizeof(_lib.MoePlan) == 40  # crates/core/src/moe.rs:355-388
     assert C.sizeof(_lib.TrellisWeight) == 40   # pinned by the reference's Rust mirror (crates/core/src/trellis.rs:229-234)
     assert _lib.Nvfp4Weight.n.offset == 16 and _lib.Nvfp4Weight.weight_scale_divisor.offset == 24
 
