@@ -38,6 +38,7 @@ struct DeviceState {
   int gemv_rb = 0;       // B200Q_GEMV_RM: 32-row groups per CTA of the NVFP4 decode kernel (0: auto)
   int gemv_kc = 0;       // B200Q_GEMV_KC: its cluster size (0: auto)
   int gemv_ctas_per_sm = 2;
+  int gemv_slots[9] = {};  // CTAs of the NVFP4 decode kernel resident at once, by cluster size (0: unknown)
   int gemv_xu = 8;       // B200Q_GEMV_XU: words per row of 8 decoded by the hardware E2M1 conversion
   int sm_cap = 0;        // IGNIS_TRELLIS_SM_CAP
 };

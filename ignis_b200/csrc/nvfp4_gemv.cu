@@ -516,6 +516,30 @@ int32_t gemv_prepare(ErrorSlot &slot) {
   if (err == cudaSuccess) err = set_smem_attrs<4>();
   if (err == cudaSuccess) err = set_smem_attrs<8>();
   if (err != cudaSuccess) return fail(slot, "nvfp4 decode kernel attributes: %s", cudaGetErrorString(err));
+  // How many CTAs the device keeps resident for each cluster size: clusters are placed inside one
+  // GPC, so the count is not simply slots / size. The plan uses it to tell one wave from two.
+  DeviceState *dev = device_state(slot);
+  if (dev == nullptr) return -1;
+  for (int kc = 1; kc <= 8; ++kc) {
+    cudaLaunchConfig_t config = {};
+    config.gridDim = dim3(static_cast<unsigned>(kc) * 1024u, 1, 1);
+    config.blockDim = dim3(kThreads, 1, 1);
+    config.dynamicSmemBytes = 56 * 1024;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = static_cast<unsigned>(kc);
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    config.attrs = attr;
+    config.numAttrs = 1;
+    int clusters = 0;
+    if (cudaOccupancyMaxActiveClusters(&clusters, nvfp4_gemv_kernel<1, 8>, &config) == cudaSuccess && clusters > 0) {
+      dev->gemv_slots[kc] = clusters * kc;
+    } else {
+      dev->gemv_slots[kc] = 0;
+      (void)cudaGetLastError();
+    }
+  }
   return 0;
 }
 
@@ -530,7 +554,7 @@ GemvPlan gemv_plan(const DeviceState &dev, uint32_t groups, uint32_t ksteps, int
   for (int pass = 0; pass < 2 && best.rm == 0; ++pass) {
     double best_cost = 1e30;
     for (int rm = 8; rm >= rm_min; rm >>= 1) {
-      for (int kc = 1; kc <= 8; kc <<= 1) {
+      for (int kc = 1; kc <= 8; ++kc) {
         if (pass == 0 && dev.gemv_rb > 0 && rm != dev.gemv_rb) continue;
         if (pass == 0 && dev.gemv_kc > 0 && kc != dev.gemv_kc) continue;
         if (static_cast<uint32_t>(kc) > ksteps) continue;
@@ -539,12 +563,13 @@ GemvPlan gemv_plan(const DeviceState &dev, uint32_t groups, uint32_t ksteps, int
         const uint32_t rows_per_cta = swiglu ? rm / 2 : rm;
         const uint32_t row_blocks = (out_groups + rows_per_cta - 1) / rows_per_cta;
         const double ctas = static_cast<double>(row_blocks) * kc;
-        const double waves = ceil(ctas / slots);
+        const double resident = nt <= 2 && dev.gemv_slots[kc] > 0 ? static_cast<double>(dev.gemv_slots[kc]) : slots;
+        const double waves = ceil(ctas / resident);
         const double slice = ceil(static_cast<double>(ksteps) / kc);
         const double steps = ceil(slice / kwc);
-        // a step costs 1; preparing one step of activations costs about 0.09 per token tile; a
-        // fixed 2 stands for the launch ramp and the reductions
-        const double cost = waves * (steps + 0.09 * nt * slice + 2.0) + 0.02 * kc;
+        // fitted on B200 (microseconds per launch): a warp's step costs about 1.6, a step of the
+        // CTA's activation slice 0.3 per token tile, a wave of CTAs 3, the launch itself 2.4
+        const double cost = waves * (1.57 * steps + 0.3 * nt * slice + 3.0) + 2.4 + 0.01 * kc;
         if (cost < best_cost) {
           best_cost = cost;
           best.rm = rm;

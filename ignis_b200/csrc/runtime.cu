@@ -73,6 +73,7 @@ int32_t prepare_device(ErrorSlot &slot) {
   fresh.gemv_xu = env_int("B200Q_GEMV_XU", 8);
   fresh.sm_cap = env_int("IGNIS_TRELLIS_SM_CAP", 0);
   if (fresh.sm_cap < 0 || fresh.sm_cap > fresh.sm_count) fresh.sm_cap = 0;
+  for (int i = 0; i < 9; ++i) fresh.gemv_slots[i] = state->gemv_slots[i];
   fresh.prepared = true;
   *state = fresh;
   return 0;
