@@ -79,15 +79,24 @@ __device__ __forceinline__ void griddep_wait() { asm volatile("griddepcontrol.wa
 // Lets the next grid in the stream start its independent prologue.
 __device__ __forceinline__ void griddep_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 
-// 32 bytes of a read-only stream that is touched once: no L1 allocation.
-__device__ __forceinline__ void ldg256_stream(const void *p, uint32_t (&r)[8]) {
-  asm volatile("ld.global.nc.L1::no_allocate.v8.b32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];"
-               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7])
-               : "l"(p));
+// An L2 policy for data that is read once: first in line for eviction, so a weight stream does not
+// push the (re-read) activations out of L2.
+__device__ __forceinline__ uint64_t l2_evict_first_policy() {
+  uint64_t policy;
+  asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(policy));
+  return policy;
 }
-__device__ __forceinline__ uint4 ldg128_stream(const void *p) {
+// 32 bytes of a read-only stream that is touched once: no L1 allocation, evict-first in L2.
+__device__ __forceinline__ void ldg256_stream(const void *p, uint32_t (&r)[8], uint64_t policy) {
+  asm volatile("ld.global.nc.L1::no_allocate.L2::cache_hint.v8.b32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8], %9;"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7])
+               : "l"(p), "l"(policy));
+}
+__device__ __forceinline__ uint4 ldg128_stream(const void *p, uint64_t policy) {
   uint4 v;
-  asm volatile("ld.global.nc.L1::no_allocate.v4.b32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p));
+  asm volatile("ld.global.nc.L1::no_allocate.L2::cache_hint.v4.b32 {%0,%1,%2,%3}, [%4], %5;"
+               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+               : "l"(p), "l"(policy));
   return v;
 }
 // 16 bytes of data an earlier kernel in the stream may have written while this grid was already

@@ -50,6 +50,7 @@ struct WarpRows {
   const uint8_t *codes;   // row (base + g), byte 32 t
   const uint8_t *scales;  // scale tile (m_tile, 0), byte 16 (J 8 + g)
   size_t row_stride32;    // bytes between rows 32 apart
+  uint64_t policy;        // L2 eviction policy of the weight stream
   bool active;
 };
 
@@ -59,8 +60,8 @@ __device__ __forceinline__ void load_stage(Stage &st, const WarpRows &rows, int 
   if (rows.active && step < c1 && tile < scale_tiles) {
     const uint8_t *c = rows.codes + static_cast<size_t>(step) * 128u;
 #pragma unroll
-    for (int q = 0; q < 4; ++q) ldg256_stream(c + q * rows.row_stride32, st.c[q]);
-    st.sc = ldg128_stream(rows.scales + static_cast<size_t>(tile) * 512u);
+    for (int q = 0; q < 4; ++q) ldg256_stream(c + q * rows.row_stride32, st.c[q], rows.policy);
+    st.sc = ldg128_stream(rows.scales + static_cast<size_t>(tile) * 512u, rows.policy);
   } else {
     zero_stage(st);
   }
@@ -151,6 +152,15 @@ __device__ __forceinline__ float4 ld_cluster_f4(const void *local_smem, uint32_t
   float4 v;
   asm volatile("ld.shared::cluster.v4.f32 {%0,%1,%2,%3}, [%4];" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "r"(remote) : "memory");
   return v;
+}
+
+// Measurement hook: warp 0 lane 0 of a CTA stamps the nanosecond timer at phase boundaries.
+__device__ __forceinline__ void stamp(unsigned long long *trace, int slot) {
+  if (trace != nullptr && threadIdx.x == 0) {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    trace[static_cast<size_t>(blockIdx.x) * 8 + slot] = t;
+  }
 }
 
 __device__ __forceinline__ float silu_f32(float v) { return v / (1.0f + __expf(-v)); }
@@ -301,6 +311,7 @@ __global__ void __launch_bounds__(kThreads, NT <= 2 ? 2 : 1) nvfp4_gemv_kernel(c
 
   WarpRows rows;
   rows.active = active;
+  rows.policy = l2_evict_first_policy();
   const uint32_t row0 = m_tile * 128u + jq * 8u + g;
   rows.codes = W.codes + static_cast<size_t>(row0) * (p.k / 2u) + t * 32;
   rows.scales = W.scales + static_cast<size_t>(m_tile) * scale_tiles * 512u + (jq * 8u + g) * 16u;
@@ -311,6 +322,7 @@ __global__ void __launch_bounds__(kThreads, NT <= 2 ? 2 : 1) nvfp4_gemv_kernel(c
   const int c1 = static_cast<int>(static_cast<uint64_t>(p.ksteps) * (rank + 1) / kc);
   const int ch = static_cast<int>(p.xs_steps);
 
+  stamp(p.trace, 0);
   Stage st0, st1;
   int s = c0 + kw;
   load_stage(st0, rows, s, c1, t, scale_tiles);
@@ -319,6 +331,7 @@ __global__ void __launch_bounds__(kThreads, NT <= 2 ? 2 : 1) nvfp4_gemv_kernel(c
   // The weights above never depend on the previous kernel; the activations may.
   griddep_launch_dependents();
   griddep_wait();
+  stamp(p.trace, 1);
 
   // Accumulators live in the units of the current chunk's per-token scale; at a chunk boundary
   // they are carried into the next chunk's units by an exact power-of-two factor.
@@ -343,6 +356,7 @@ __global__ void __launch_bounds__(kThreads, NT <= 2 ? 2 : 1) nvfp4_gemv_kernel(c
     }
     prepare_activations<NT, XU>(p, cb, ce, xs, inv_s, scale_s, warp, lane);
     __syncthreads();
+    stamp(p.trace, 2);
     if (cb != c0) {
 #pragma unroll
       for (int tt = 0; tt < NT; ++tt) {
@@ -383,6 +397,7 @@ __global__ void __launch_bounds__(kThreads, NT <= 2 ? 2 : 1) nvfp4_gemv_kernel(c
     }
   }
 
+  stamp(p.trace, 3);
   // ---- K reduction inside the CTA: columns kw = 1.. hand their sums to column 0, fixed order ----
   if (kw > 0) {
 #pragma unroll
@@ -414,7 +429,9 @@ __global__ void __launch_bounds__(kThreads, NT <= 2 ? 2 : 1) nvfp4_gemv_kernel(c
   }
 
   // ---- K reduction across the cluster, then the epilogue, the items dealt over ranks and warps ----
+  stamp(p.trace, 4);
   cluster_sync_all();
+  stamp(p.trace, 5);
   const int out_groups = swiglu ? rm / 2 : rm;
   const int items = out_groups * 2 * NT;
   const float coef = W.inv_dw * 128.0f;  // the operands carried 2^-7
@@ -456,7 +473,9 @@ __global__ void __launch_bounds__(kThreads, NT <= 2 ? 2 : 1) nvfp4_gemv_kernel(c
       }
     }
   }
+  stamp(p.trace, 6);
   cluster_sync_all();  // no CTA leaves while a peer may still read its partial sums
+  stamp(p.trace, 7);
 }
 
 constexpr size_t kGemvMaxSmem = 160 * 1024;
@@ -585,8 +604,12 @@ GemvPlan gemv_plan(const DeviceState &dev, uint32_t groups, uint32_t ksteps, int
   return best;
 }
 
+// Measurement only: where the next launches write their phase stamps (8 u64 per CTA), or nullptr.
+unsigned long long *g_gemv_trace = nullptr;
+
 int32_t gemv_launch(ErrorSlot &slot, const DeviceState &dev, GemvParams &p, int nt, const GemvPlan &plan, uint32_t ctas,
                     cudaStream_t stream) {
+  p.trace = g_gemv_trace;
   p.rm = plan.rm;
   p.kc = plan.kc;
   p.xs_steps = plan.xs_steps;
@@ -606,3 +629,8 @@ int32_t gemv_launch(ErrorSlot &slot, const DeviceState &dev, GemvParams &p, int 
 }
 
 }  // namespace b200q
+
+// Measurement only (not part of the public ABI): directs the phase stamps of later NVFP4 decode
+// launches on this thread's device to `buffer` (8 u64 per CTA of the largest launch), or stops
+// stamping with nullptr.
+extern "C" void b200q_debug_gemv_trace(void *buffer) { b200q::g_gemv_trace = static_cast<unsigned long long *>(buffer); }

@@ -34,6 +34,7 @@ struct GemvParams {
   uint32_t rm;        // 32-row groups per CTA: 1, 2, 4 or 8
   uint32_t kc;        // cluster size: K slices across CTAs
   uint32_t xs_steps;  // steps of activation fragments shared memory holds at a time
+  unsigned long long *trace;  // measurement only: 8 %globaltimer stamps per CTA, or nullptr
 };
 
 struct GemvPlan {
