@@ -241,6 +241,168 @@ def build_trellis_workload(layers: int, rank: int, world: int, tokens: int, devi
     return weights, inputs, outputs, total * layers
 
 
+def build_moe_workload(tokens: int, device, rank=0, world=1, hidden=2048, inter=768, experts=512, top_k=10, k2=5):
+    """configs[4]: 512 experts of (hidden 2048, intermediate 768) at 2.5 bits per weight, every record
+    distinct (random words: every bit pattern is a valid encoding), Zipf(1.1) expert popularity over a
+    seeded permutation, 10 distinct experts per token drawn in proportion to popularity, routing
+    weights = BF16(softmax of 10 normal logits). The shared expert is the FP8 row-scale one."""
+    import numpy as np
+    import torch
+
+    from ignis_b200 import moe
+
+    local_experts = experts // world
+    if world == 1:
+        moe.set_geometry(hidden, inter, experts, top_k)
+    else:
+        moe.set_geometry(hidden, inter, local_experts, 1)
+    moe.prepare()
+    gen = torch.Generator(device=device).manual_seed(20261129 + rank)
+    gu_bytes, dn_bytes = moe.record_bytes(moe.PROJ_GATE_UP, k2), moe.record_bytes(moe.PROJ_DOWN, k2)
+    buffer = torch.empty(local_experts * (gu_bytes + dn_bytes), dtype=torch.uint8, device=device)
+    offsets, k2s, assign = [], [], []
+
+    def fill(at: int, in_: int, out: int, amp_in: float, amp_out: float) -> None:
+        words = in_ * out * k2 // 16
+        buffer[at: at + words] = torch.randint(0, 256, (words,), dtype=torch.uint8, device=device, generator=gen)
+        for base, n, amp in ((at + words, in_, amp_in), (at + words + 2 * in_, out, amp_out)):
+            v = (torch.rand(n, device=device, generator=gen) * 1.5 + 0.5) * amp
+            v = v * (torch.randint(0, 2, (n,), device=device, generator=gen) * 2 - 1)
+            buffer[base: base + 2 * n] = v.to(torch.float16).view(torch.uint8)
+
+    at = 0
+    for e in range(local_experts):
+        fill(at, hidden, 2 * inter, 0.05, 0.03)
+        offsets.append(at); k2s.append(k2); at += gu_bytes
+        fill(at, inter, hidden, 0.25, 0.06)
+        offsets.append(at); k2s.append(k2); at += dn_bytes
+        assign.append((2 * e, 2 * e + 1))
+    table = moe.SlotTable.from_device_records(buffer, offsets, k2s, assign)
+
+    cpu = torch.Generator().manual_seed(20261129)
+    perm = torch.randperm(experts, generator=cpu)
+    popularity = torch.empty(experts)
+    popularity[perm] = 1.0 / torch.arange(1, experts + 1, dtype=torch.float32) ** 1.1
+    ids = torch.multinomial(popularity.expand(tokens, experts), top_k, replacement=False, generator=cpu).to(torch.int32)
+    weights = torch.softmax(torch.randn(tokens, top_k, generator=cpu), dim=1).to(torch.bfloat16).float()
+    x = (torch.randn(tokens, hidden, generator=cpu) * 0.5).to(torch.bfloat16)
+    shared = [torch.from_numpy(moe.fp8_row_scale_payload(torch.randn(r, c, generator=cpu) * 0.02)).to(device)
+              for r, c in ((inter, hidden), (inter, hidden), (hidden, inter))]
+    w_gate = (torch.randn(hidden, generator=cpu) * 0.02).to(torch.bfloat16).to(device)
+    hit = int(torch.unique(ids).numel())
+    flops = tokens * top_k * (2.0 * hidden * 2 * inter + 2.0 * inter * hidden) + tokens * (2.0 * hidden * 2 * inter + 2.0 * inter * hidden)
+    if world == 1:
+        ws = moe.Workspace(min(8, tokens), tokens, device)
+    else:   # a rank may be sent every row of the job
+        ws = moe.Workspace(8, tokens * top_k, device)
+        lo, hi = rank * tokens // world, (rank + 1) * tokens // world
+        ids, weights, x = ids[lo:hi], weights[lo:hi], x[lo:hi]
+    host = {"x": x.pin_memory(), "ids": ids.pin_memory(), "weights": weights.pin_memory()}
+    return {"table": table, "ids": ids.to(device), "weights": weights.to(device), "x": x.to(device), "shared": shared,
+            "w_gate": w_gate, "ws": ws, "flops": flops, "weight_bytes": hit * (gu_bytes + dn_bytes), "hit": hit,
+            "host": host, "experts": experts}
+
+
+def run_moe_workload(args) -> None:
+    """`--workload moe` (configs[4]): routed experts + shared expert + combine, TFLOP/s. One GPU: the
+    step is one CUDA graph. N GPUs: expert-parallel, tokens split over the ranks, one all-to-all
+    each way per step (NCCL), timed on the device, max over ranks."""
+    import torch
+    import torch.distributed as dist
+
+    from ignis_b200 import moe, moe_ep
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device")
+    torch.cuda.set_device(local_rank)
+    device = torch.device("cuda", local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=device)
+    tokens = args.tokens if args.tokens > 8 else 4096
+    m = build_moe_workload(tokens, device, rank, world)
+    out_host = torch.empty((m["x"].shape[0], 2048), dtype=torch.bfloat16).pin_memory()
+    stream = torch.cuda.Stream()
+
+    def one_step():
+        if world == 1:
+            moe.experts_prefill(m["x"], m["ids"], m["weights"], m["table"], m["ws"])
+            acc = None
+        else:
+            acc = moe_ep.routed_experts(m["x"], m["ids"], m["weights"], m["experts"],
+                                        lambda rows, local, w: moe.experts_rows(rows, local, w, m["table"], m["ws"]))
+        shared, _ = moe.shared_expert(m["shared"][0], m["shared"][1], m["shared"][2], m["x"])
+        return moe.combine(m["ws"], shared, m["x"], m["w_gate"], acc=acc)
+
+    def barrier() -> None:
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    with torch.cuda.stream(stream):
+        out = one_step()
+        stream.synchronize()
+        step = one_step
+        graphed = bool(args.graph) and world == 1   # the exchange sizes its buffers on the host
+        if graphed:
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph, stream=stream):
+                out = one_step()
+            step = graph.replay
+        for _ in range(args.warmup):
+            step()
+        barrier()
+        start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        with ClockSampler(local_rank) as clocks:
+            start.record(stream)
+            for _ in range(args.steps):
+                step()
+            stop.record(stream)
+            barrier()
+        device_ms = start.elapsed_time(stop)
+        # end to end: the step's tokens and routing from pinned host memory in, its output back
+        e2e_start, e2e_stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e2e_start.record(stream)
+        for _ in range(args.steps):
+            for key in ("x", "ids", "weights"):
+                m[key].copy_(m["host"][key], non_blocking=True)
+            got = step()
+            out_host.copy_(out if graphed else got, non_blocking=True)
+        e2e_stop.record(stream)
+        barrier()
+        e2e_ms = e2e_start.elapsed_time(e2e_stop)
+    status = m["ws"].status()
+    times = torch.tensor([device_ms, e2e_ms, float(status)], dtype=torch.float64, device=device)
+    if world > 1:
+        dist.all_reduce(times, op=dist.ReduceOp.MAX)
+        dist.destroy_process_group()
+    device_ms, e2e_ms, status = times.tolist()
+    if rank != 0:
+        return
+    ms = device_ms / args.steps
+    value = m["flops"] / 1e12 / (ms * 1e-3)
+    peak = 1403.2 * world
+    h2d = sum(t.numel() * t.element_size() for t in m["host"].values())
+    print(json.dumps({
+        "metric": "moe_expert_gemm_tflops", "value": value, "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+        "dtype": "f16xf16->f32", "data": "synthetic",
+        "config": {"workload": f"configs[4]: MoE routed experts + shared expert + combine, {tokens} tokens x top-10 of 512 experts, "
+                               f"hidden 2048, intermediate 768, 2.5 bpw trellis records, Zipf(1.1) routing; {m['hit']} experts hit, "
+                               f"{m['weight_bytes'] / 1e6:.0f} MB of expert records",
+                   "cuda_graph": graphed, "l2": "inputs larger than L2",
+                   "parallelism": "one GPU" if world == 1 else f"expert-parallel over {world} ranks, tokens split, NCCL all-to-all each way"},
+        "e2e": {"value": m["flops"] / 1e12 / (e2e_ms / args.steps * 1e-3), "unit": "TFLOP/s", "h2d_bytes_per_step": h2d,
+                "d2h_bytes_per_step": out_host.numel() * 2},
+        "gpu_launches": 8 * args.steps, "clocks": clocks.summary(),
+        "roofline": {"bound": "tensor", "achieved": value, "peak": peak, "unit": "TFLOP/s", "frac": value / peak,
+                     "peak_source": "measured sustained BF16 cuBLAS rate per GPU (the experts multiply in FP16 with FP32 accumulation)",
+                     "kernel": "moe_experts_kernel", "traffic": None, "device_status": int(status),
+                     "record_gbs": m["weight_bytes"] / (ms * 1e-3) / 1e9}}))
+
+
 def run_side_workload(args) -> None:
     """The other measured configs, one JSON line each, same timing rules as the headline:
     `--workload prefill` (configs[2], W4A4 tensor-core GEMM, TFLOP/s) and `--workload trellis`
@@ -297,17 +459,20 @@ def run_side_workload(args) -> None:
             workload = f"configs[3]: trellis 3 bpw decode, M={args.tokens}, 27B-style layer x {args.layers} layers of distinct weights"
         one_step()
         stream.synchronize()
-        graph = torch.cuda.CUDAGraph()
-        with torch.cuda.graph(graph, stream=stream):
-            one_step()
+        step = one_step
+        if args.graph:
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph, stream=stream):
+                one_step()
+            step = graph.replay
         for _ in range(args.warmup):
-            graph.replay()
+            step()
         torch.cuda.synchronize()
         start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         with ClockSampler(0) as clocks:
             start.record(stream)
             for _ in range(args.steps):
-                graph.replay()
+                step()
             stop.record(stream)
             torch.cuda.synchronize()
         ms = start.elapsed_time(stop) / args.steps
@@ -326,7 +491,7 @@ def run_side_workload(args) -> None:
     print(json.dumps({"metric": metric, "value": value, "unit": unit, "n_gpus": 1, "steps": args.steps, "warmup": args.warmup,
                       "ms_per_step": ms, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
                       "dtype": "e2m1xe2m1->f32" if args.workload == "prefill" else "f16xf16->f32", "data": "synthetic",
-                      "config": {"workload": workload, "cuda_graph": True, "l2": "inputs larger than L2"},
+                      "config": {"workload": workload, "cuda_graph": bool(args.graph), "l2": "inputs larger than L2"},
                       "gpu_launches": launches * args.steps, "clocks": clocks.summary(), "roofline": roof}))
 
 
@@ -465,11 +630,13 @@ def main() -> None:
     ap.add_argument("--group", type=int, default=1, help="1: q|k|v and gate|up share one launch each; 0: seven launches per layer")
     ap.add_argument("--graph", type=int, default=1, help="replay the step as one CUDA graph")
     ap.add_argument("--no-cpu-baseline", action="store_true")
-    ap.add_argument("--workload", default="decode", choices=["decode", "prefill", "trellis"],
-                    help="decode: configs[1] (the headline); prefill: configs[2]; trellis: configs[3]")
+    ap.add_argument("--workload", default="decode", choices=["decode", "prefill", "trellis", "moe"],
+                    help="decode: configs[1] (the headline); prefill: configs[2]; trellis: configs[3]; moe: configs[4]")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference_arm(args)
+    elif args.workload == "moe":
+        run_moe_workload(args)
     elif args.workload != "decode":
         run_side_workload(args)
     else:

@@ -99,6 +99,22 @@ class SlotTable:
                     table[e * 2 + proj] = (base + offsets[idx], records[idx][1], 0)
         self.slots = torch.from_numpy(table.view(np.uint8)).to(device)
 
+    @classmethod
+    def from_device_records(cls, buffer: torch.Tensor, offsets: list[int], k2s: list[int],
+                            assign: list[tuple[int, int]]) -> "SlotTable":
+        """A table over records already resident in `buffer` (uint8, record i at `offsets[i]`,
+        4096-byte aligned), for layers too large to stage through host memory."""
+        self = cls.__new__(cls)
+        self.buffer = buffer
+        base = buffer.data_ptr()
+        table = np.zeros(len(assign) * 2, dtype=[("record", np.uint64), ("k2", np.uint32), ("reserved", np.uint32)])
+        for e, pair in enumerate(assign):
+            for proj, idx in enumerate(pair):
+                if idx is not None and idx >= 0:
+                    table[e * 2 + proj] = (base + offsets[idx], k2s[idx], 0)
+        self.slots = torch.from_numpy(table.view(np.uint8)).to(buffer.device)
+        return self
+
 
 class Workspace:
     """The workspace and the routed accumulator of one MoE block, initialised."""
@@ -158,6 +174,19 @@ def experts_decode(x, ids, weights, table: SlotTable, ws: Workspace) -> torch.Te
     return _experts(_lib.load().ignis_moe_experts_decode, x, ids, weights, table, ws)
 
 
+def experts_rows(rows: torch.Tensor, local_ids: torch.Tensor, row_weights: torch.Tensor, table: SlotTable,
+                 ws: Workspace) -> torch.Tensor:
+    """The owner's side of the expert-parallel exchange (``ignis_b200.moe_ep``): every received row
+    is a one-choice token over this rank's own slot table. Needs a geometry with ``top_k == 1``
+    and ``experts`` = the rank's share. Returns the rows' weighted outputs, int64 fixed point."""
+    if _geometry.top_k != 1:
+        raise MoeError("experts_rows needs a one-choice geometry (set_geometry(hidden, inter, local_experts, 1))")
+    count = rows.shape[0]
+    ws.acc[:count].zero_()
+    experts_prefill(rows.contiguous(), local_ids.contiguous(), row_weights.contiguous(), table, ws)
+    return ws.acc[:count]
+
+
 def fp8_row_scale_payload(w: torch.Tensor) -> np.ndarray:
     """A [rows, cols] float weight as an FP8 row-scale payload: E4M3FN codes, zero padding to 256
     bytes, BF16 scales (kernel/include/ignis_fp8_linear.h:4-10)."""
@@ -183,9 +212,13 @@ def shared_expert(gate: torch.Tensor, up: torch.Tensor, down: torch.Tensor, x: t
     return shared, h
 
 
-def combine(ws: Workspace, shared: torch.Tensor, x: torch.Tensor, w_gate: torch.Tensor) -> torch.Tensor:
+def combine(ws: Workspace | None, shared: torch.Tensor, x: torch.Tensor, w_gate: torch.Tensor,
+            acc: torch.Tensor | None = None) -> torch.Tensor:
+    """``out = BF16(acc 2^-32 + sigmoid(x . w_gate) shared)``; clears the accumulator it read
+    (`acc` when given, else the workspace's)."""
     tokens = x.shape[0]
     out = torch.empty((tokens, _geometry.hidden), dtype=torch.bfloat16, device=x.device)
-    _check(_lib.load().ignis_moe_combine(ws.acc.data_ptr(), shared.data_ptr(), x.data_ptr(), w_gate.data_ptr(), tokens,
+    acc = ws.acc if acc is None else acc
+    _check(_lib.load().ignis_moe_combine(acc.data_ptr(), shared.data_ptr(), x.data_ptr(), w_gate.data_ptr(), tokens,
                                           out.data_ptr(), _stream()))
     return out

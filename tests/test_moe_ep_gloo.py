@@ -1,0 +1,108 @@
+"""The expert-parallel exchange with two CPU ranks over gloo: every rank holds half the tokens and
+owns half the experts, a stand-in expert (exact integer arithmetic, so sums are order-free) runs
+where the device kernels would, and the combined fixed-point accumulator equals the one a single
+rank computes for the same assignments, bit for bit. Skewed routing (one expert in every token,
+one rank receiving almost nothing) and an empty rank are included. No GPU."""
+from __future__ import annotations
+
+import os
+import socket
+import sys
+
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+EXPERTS, TOP_K, HIDDEN = 8, 3, 16
+
+
+def _free_port() -> int:
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+def _expert(rows: torch.Tensor, expert: torch.Tensor, weight: torch.Tensor) -> torch.Tensor:
+    """Stand-in: out = round(2^32 w) * (expert + 1) * row, all integers."""
+    w_fixed = torch.round(weight.double() * 4294967296.0).to(torch.int64)
+    return w_fixed * (expert.to(torch.int64) + 1) * rows.to(torch.int64)
+
+
+def _case(case: int, world: int):
+    gen = torch.Generator().manual_seed(100 + case)
+    tokens_per_rank = [5, 7] if case == 0 else ([6, 0] if case == 1 else [4, 4])
+    xs, ids, ws = [], [], []
+    for t in tokens_per_rank[:world]:
+        xs.append(torch.randint(-8, 9, (t, HIDDEN), generator=gen).float())
+        if case == 2:   # skew: expert 1 in every token, everything on rank 0's half
+            pick = torch.stack([torch.tensor([1, 0, 3])[torch.randperm(3, generator=gen)] for _ in range(t)]) if t else torch.zeros((0, 3), dtype=torch.int64)
+        else:
+            pick = torch.stack([torch.randperm(EXPERTS, generator=gen)[:TOP_K] for _ in range(t)]) if t else torch.zeros((0, TOP_K), dtype=torch.int64)
+        ids.append(pick.to(torch.int32))
+        ws.append(torch.rand(t, TOP_K, generator=gen).to(torch.bfloat16).float())
+    return xs, ids, ws
+
+
+def _worker(rank: int, world: int, port: int, failures) -> None:
+    sys.path.insert(0, ROOT)
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        from ignis_b200 import moe_ep
+
+        begin, end = moe_ep.expert_range(EXPERTS, rank, world)
+        assert (begin, end) == (rank * EXPERTS // world, (rank + 1) * EXPERTS // world)
+        for case in range(3):
+            xs, ids, ws = _case(case, world)
+            seen = []
+
+            def run_local(rows, local, wrow):
+                assert local.dtype == torch.int32 and local.shape == (rows.shape[0], 1)
+                assert int(local.min()) >= 0 and int(local.max()) < end - begin
+                seen.append(rows.shape[0])
+                return _expert(rows, local + begin, wrow)
+
+            acc = moe_ep.routed_experts(xs[rank], ids[rank], ws[rank], EXPERTS, run_local)
+            want = torch.zeros((xs[rank].shape[0], HIDDEN), dtype=torch.int64)
+            for t in range(xs[rank].shape[0]):
+                for c in range(TOP_K):
+                    want[t] += _expert(xs[rank][t:t + 1], ids[rank][t, c].reshape(1, 1), ws[rank][t, c].reshape(1, 1))[0]
+            assert torch.equal(acc, want), f"case {case}: combined accumulator differs from the single-rank sum"
+            # every assignment of every rank landed on exactly one owner
+            total = torch.tensor([sum(seen)], dtype=torch.int64)
+            dist.all_reduce(total)
+            assert int(total) == sum(i.numel() for i in ids), f"case {case}: rows lost or duplicated in dispatch"
+            if case == 2 and rank == 1:
+                assert sum(seen) == 0   # all experts of the skewed case live on rank 0
+        bad = torch.full((1, TOP_K), EXPERTS, dtype=torch.int32)
+        try:
+            moe_ep.dispatch(torch.zeros(1, HIDDEN), bad, torch.zeros(1, TOP_K), EXPERTS)
+            failures.append(f"rank {rank}: an out-of-range expert id was accepted")
+        except ValueError:
+            pass
+    except Exception as exc:  # an assert in a child is otherwise silent
+        failures.append(f"rank {rank}: {exc!r}")
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("world", [2])
+def test_exchange_matches_single_rank_accumulation(world):
+    manager = mp.Manager()
+    failures = manager.list()
+    mp.spawn(_worker, args=(world, _free_port(), failures), nprocs=world, join=True)
+    assert not list(failures), list(failures)
+
+
+def test_expert_range_rejects_ragged_splits():
+    sys.path.insert(0, ROOT)
+    from ignis_b200 import moe_ep
+
+    assert moe_ep.expert_range(512, 3, 8) == (192, 256)
+    with pytest.raises(ValueError):
+        moe_ep.expert_range(512, 0, 3)
+    with pytest.raises(ValueError):
+        moe_ep.expert_range(512, 8, 8)
