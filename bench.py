@@ -614,9 +614,10 @@ def run_cuda_arm(args) -> None:
     print(json.dumps(line))
 
 
-# dram__bytes_read.sum + dram__bytes_write.sum per launch of the dominant kernel from the ncu
-# capture summarised under profiles/; None until a capture exists.
-TRAFFIC_PER_LAUNCH = None
+# dram__bytes_read.sum + dram__bytes_write.sum per launch of the dominant kernel: the mean over the
+# four launches of one layer in the ncu capture summarised in profiles/nvfp4_gemv_decode_m8.md
+# (196.97 MB per layer; the algorithmic bytes of the same four launches are 193.3 MB).
+TRAFFIC_PER_LAUNCH = 49.24e6
 
 
 def main() -> None:

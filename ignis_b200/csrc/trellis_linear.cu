@@ -13,15 +13,16 @@
 // 1024 + sum) and half an HFMA2. The eight values of a lane are, without any shuffle, the A
 // fragment of the transposed tile (M = output column, K = input row), so tokens are the MMA's N.
 //
-// The linear (1..8 tokens per pass): one kernel. A CTA serves one block of 128 output columns and
-// a slice of the 128-input blocks; it first rotates its slice of the activations (x o suh, then
-// the 128-wide Hadamard in fp32 on a warp, a power-of-two scale per token and block, fp16) into
-// B fragments in shared memory, then each warp walks its blocks: 8 tiles per 16 inputs, decoded
-// and multiplied with fp32 accumulation, folded by the block's inverse scale every 128 inputs.
-// Warps meet in shared memory, the CTAs of a cluster (the split of the inputs) in distributed
-// shared memory, in a fixed order; the first CTA applies the output Hadamard, svh and the
-// epilogue. Weight words are prefetched one 16-input step ahead, the first before the grid waits
-// for its predecessor in the stream.
+// The linear (1..64 tokens per pass): one kernel. A CTA serves one block of 128 output columns and
+// a slice of the 128-input blocks; it rotates its slice of the activations (x o suh, then the
+// 128-wide Hadamard in fp32 on a warp, a power-of-two scale per token and block, fp16) into B
+// fragments in shared memory, a chunk at a time, then warp j walks tile column j down the slice:
+// one tile per 16 inputs, decoded once and multiplied with every token tile of 8, fp32
+// accumulation, folded by the block's inverse scale every 128 inputs. The CTAs of a cluster (the
+// split of the inputs) meet in distributed shared memory in a fixed order; each applies the
+// output Hadamard, svh and the epilogue to its share of the tokens. Weight words are requested
+// one 128-input block ahead, the first block before the grid waits for its predecessor in the
+// stream.
 #include "../../include/ignis_trellis_linear.h"
 
 #include "trellis_device.cuh"
@@ -33,7 +34,6 @@ using namespace trellis_dev;
 
 constexpr int kThreads = 256;
 constexpr int kWarps = 8;
-constexpr uint32_t kMaxSliceBlocks = 40;  // 128-input blocks of rotated activations a CTA holds (80 KB)
 
 // ---- reconstruct: one warp per tile ---------------------------------------------------------
 __global__ void __launch_bounds__(kThreads) trellis_reconstruct_kernel(const uint32_t *__restrict__ trellis, uint32_t k2,
@@ -79,155 +79,209 @@ struct TrellisParams {
   uint32_t in, out, tokens, ldy;
   uint32_t epilogue;    // 0 store, 1 add, 2 SwiGLU
   uint32_t kc;          // cluster size: slices of the input blocks
-  uint32_t slice_cap;   // 128-input blocks the shared-memory fragment buffer holds
+  uint32_t chunk;       // 128-input blocks of rotated activations shared memory holds at a time
 };
 
 constexpr uint32_t kEpiAdd = 1, kEpiSwiglu = 2;  // 0 stores
 
-__global__ void __launch_bounds__(kThreads, 2) trellis_linear_kernel(const __grid_constant__ TrellisParams p) {
+// The lane's words of the 8 steps of one 128-input block of one tile column.
+struct BlockWords {
+  uint32_t w[8][3];
+};
+
+// K2 = 0 decodes with the side's runtime k2 (a SwiGLU pair whose weights differ in width).
+template <int K2>
+__device__ __forceinline__ void decode_tile(uint32_t k2, uint32_t a, uint32_t b, uint32_t c, uint32_t off, uint32_t (&frag)[4]) {
+  if (K2 == 0) {
+    decode8_any(k2, a, b, c, off, frag);
+  } else {
+    decode8<(K2 == 0 ? 4 : K2)>(a, b, c, off, frag);
+  }
+}
+
+// Work split. A CTA serves one block of 128 output columns and a slice of the 128-input blocks
+// (the cluster splits the inputs); warp j owns tile column j of the block, all the way down the
+// slice, so the warps of a CTA never add into each other and the loop body is one tile: a few
+// hundred bytes of code that stay in the instruction cache. The words of the next 128-input block
+// are requested as the current block's are consumed (24 registers per weight in flight per lane).
+// NT token tiles of 8 share every decoded tile (up to 64 tokens a pass).
+template <int K2, int NT, int SIDES>
+__global__ void __launch_bounds__(kThreads, (SIDES == 1 && NT <= 2) ? 3 : ((NT * SIDES <= 8) ? 2 : 1))
+    trellis_linear_kernel(const __grid_constant__ TrellisParams p) {
   extern __shared__ __align__(16) uint8_t smem_raw[];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const uint32_t rank = cluster_rank(), kc = p.kc;
   const uint32_t col_block = blockIdx.x / kc;
-  const bool swiglu = p.epilogue == kEpiSwiglu;
-  const int sides = swiglu ? 2 : 1;
-  const int side = swiglu ? warp >> 2 : 0;           // which weight this warp multiplies
-  const int lanes_per_side = swiglu ? 4 : 8;          // warps sharing a side
-  const int wslot = swiglu ? (warp & 3) : warp;       // this warp's index inside its side
-  const TrellisSide &S = p.side[side];
 
-  // input blocks of this CTA
   const uint32_t nblk = p.in / 128u;
   const uint32_t b0 = static_cast<uint32_t>(static_cast<uint64_t>(nblk) * rank / kc);
   const uint32_t b1 = static_cast<uint32_t>(static_cast<uint64_t>(nblk) * (rank + 1) / kc);
-  const uint32_t slice = b1 - b0;
 
-  // shared memory: [fragments | reduction scratch (aliased)] [part] [inverse scales] [scales]
-  const size_t frag_bytes = static_cast<size_t>(sides) * p.slice_cap * 2048u;
-  const size_t red_bytes = static_cast<size_t>(kWarps - sides) * 8 * 32 * 16;
-  const size_t region = frag_bytes > red_bytes ? frag_bytes : red_bytes;
-  uint2 *xs = reinterpret_cast<uint2 *>(smem_raw);                  // [side][block][kt 8][lane 32] (b0, b1)
-  float4 *red = reinterpret_cast<float4 *>(smem_raw);               // after the main loop
-  float4 *part = reinterpret_cast<float4 *>(smem_raw + region);     // [side][tile 8][lane 32]
-  float *inv_s = reinterpret_cast<float *>(smem_raw + region + 2 * 8 * 32 * 16);  // [side][block][token 8]
-  float *scale_s = inv_s + static_cast<size_t>(sides) * p.slice_cap * 8;
+  // shared memory: [fragments (side, block, step, token tile, lane)] [part] [inverse scales] [scales]
+  const size_t frag_bytes = static_cast<size_t>(SIDES) * p.chunk * NT * 2048u;
+  uint2 *xs = reinterpret_cast<uint2 *>(smem_raw);
+  float4 *part = reinterpret_cast<float4 *>(smem_raw + frag_bytes);                       // [side][tile column 8][NT][lane 32]
+  float *inv_s = reinterpret_cast<float *>(smem_raw + frag_bytes + static_cast<size_t>(SIDES) * 8 * NT * 32 * 16);
+  float *scale_s = inv_s + static_cast<size_t>(SIDES) * p.chunk * NT * 8;                  // [side][block][token]
 
-  const LaneWindow win = lane_window(S.k2, lane);
-  const uint32_t tile_words = 4u * S.k2;
-  const uint32_t *col_base = S.trellis + static_cast<uint64_t>(col_block) * 8u * tile_words;
-  const uint64_t tk_stride = static_cast<uint64_t>(S.tile_stride) * tile_words;
-  const uint32_t blk_first = b0 + static_cast<uint32_t>(wslot);  // this warp's first block
+  // the lane's word pointers of this warp's tile column, at the slice's first step
+  LaneWindow win[SIDES];
+  const uint32_t *q[SIDES][3];
+  int64_t step_words[SIDES];
+#pragma unroll
+  for (int sd = 0; sd < SIDES; ++sd) {
+    const TrellisSide &S = p.side[sd];
+    win[sd] = lane_window(K2 != 0 ? static_cast<uint32_t>(K2) : S.k2, lane);
+    const uint32_t tile_words = 4u * S.k2;
+    step_words[sd] = static_cast<int64_t>(S.tile_stride) * tile_words;
+    const uint32_t *base = S.trellis + (static_cast<uint64_t>(col_block) * 8u + static_cast<uint32_t>(warp)) * tile_words +
+                           static_cast<uint64_t>(b0) * 8u * static_cast<uint64_t>(step_words[sd]);
+    q[sd][0] = base + win[sd].w0;
+    q[sd][1] = base + win[sd].w1;
+    q[sd][2] = base + win[sd].w2;
+  }
+  BlockWords bw[SIDES];
+  if (b0 < b1) {  // the weights never depend on the previous kernel: request the first block now
+#pragma unroll
+    for (int sd = 0; sd < SIDES; ++sd)
+#pragma unroll
+      for (int kt = 0; kt < 8; ++kt)
+#pragma unroll
+        for (int c = 0; c < 3; ++c) bw[sd].w[kt][c] = __ldg(q[sd][c] + kt * step_words[sd]);
+  }
 
   griddep_launch_dependents();
   griddep_wait();
 
-  // ---- rotate the slice of the activations into B fragments (each weight has its own suh) ----
-  {
-    const uint32_t items = slice * 8u * static_cast<uint32_t>(sides);  // (side, block, token slot), dealt to the warps
-    for (uint32_t item = static_cast<uint32_t>(warp); item < items; item += kWarps) {
-      const uint32_t tok = item & 7u, bl = (item >> 3) % slice, sd = (item >> 3) / slice;
-      float v[4] = {0.f, 0.f, 0.f, 0.f};
-      if (tok < p.tokens) {
-        const size_t k0 = static_cast<size_t>(b0 + bl) * 128u + 4u * lane;
-        const uint2 xb = ldg64_coherent(p.x + static_cast<size_t>(tok) * p.in + k0);
-        const uint2 sb = *reinterpret_cast<const uint2 *>(p.side[sd].suh + k0);
-        const __half2 s01 = *reinterpret_cast<const __half2 *>(&sb.x), s23 = *reinterpret_cast<const __half2 *>(&sb.y);
-        v[0] = bf16_bits_to_f32(xb.x & 0xFFFFu) * __low2float(s01);
-        v[1] = __uint_as_float(xb.x & 0xFFFF0000u) * __high2float(s01);
-        v[2] = bf16_bits_to_f32(xb.y & 0xFFFFu) * __low2float(s23);
-        v[3] = __uint_as_float(xb.y & 0xFFFF0000u) * __high2float(s23);
-      }
-      hadamard128(v, lane);
-      float m = fmaxf(fmaxf(fabsf(v[0]), fabsf(v[1])), fmaxf(fabsf(v[2]), fabsf(v[3])));
+  float tot[SIDES][NT][4];
 #pragma unroll
-      for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xFFFFFFFFu, m, o));
-      int shift = 0;
-      if (m > 0.0f && m <= 3.0e38f) {
-        int e;
-        (void)frexpf(m, &e);
-        shift = max(-126, min(126, 14 - e));
-      }
-      const float scale = ldexpf(1.0f, shift);
-      const __half2 h01 = __floats2half2_rn(v[0] * scale, v[1] * scale);
-      const __half2 h23 = __floats2half2_rn(v[2] * scale, v[3] * scale);
-      // element e = 4 lane + i of the block: step kt = e / 16, inside it k16 = e % 16; the reader
-      // lane (g = token, t) keeps k16 in {2t, 2t+1} in .x and {2t+8, 2t+9} in .y
-      const int kt = lane >> 2, k16 = (lane & 3) * 4;  // k16 in {0, 4, 8, 12}
-      const int t_first = (k16 & 7) >> 1;              // reader t of elements k16, k16 + 1
-      const int reg = k16 >> 3;                        // .x or .y
-      const size_t blk_slot = static_cast<size_t>(sd) * p.slice_cap + bl;
-      uint32_t *dst = reinterpret_cast<uint32_t *>(xs + (blk_slot * 8 + kt) * 32 + tok * 4);
-      dst[(t_first) * 2 + reg] = *reinterpret_cast<const uint32_t *>(&h01);
-      dst[(t_first + 1) * 2 + reg] = *reinterpret_cast<const uint32_t *>(&h23);
-      if (lane == 0) {
-        inv_s[blk_slot * 8 + tok] = tok < p.tokens ? ldexpf(1.0f, -shift) : 0.0f;
-        scale_s[blk_slot * 8 + tok] = scale;
-      }
-    }
-  }
-  __syncthreads();
+  for (int sd = 0; sd < SIDES; ++sd)
+#pragma unroll
+    for (int tt = 0; tt < NT; ++tt)
+#pragma unroll
+      for (int e = 0; e < 4; ++e) tot[sd][tt][e] = 0.0f;
+  float carry[SIDES][NT][2];  // the previous block's inverse scales of this lane's two tokens per tile
+#pragma unroll
+  for (int sd = 0; sd < SIDES; ++sd)
+#pragma unroll
+    for (int tt = 0; tt < NT; ++tt) carry[sd][tt][0] = carry[sd][tt][1] = 0.0f;
+  const int t2 = (lane & 3) * 2;
 
-  // ---- main loop: this warp's blocks, 8 steps of 16 inputs each ----
-  float tot[8][4];
+  for (uint32_t cb = b0; cb < b1; cb += p.chunk) {
+    const uint32_t ce = min(cb + p.chunk, b1), nb = ce - cb;
+    if (cb != b0) __syncthreads();  // the previous chunk's fragments are no longer read
+    // ---- rotate the chunk of the activations into B fragments (each weight has its own suh) ----
+    {
+      const uint32_t items = nb * 8u * NT * SIDES;  // (side, block, token), dealt to the warps
+      for (uint32_t item = static_cast<uint32_t>(warp); item < items; item += kWarps) {
+        const uint32_t tok = item % (8u * NT), rest = item / (8u * NT), bl = rest % nb, sd = rest / nb;
+        float v[4] = {0.f, 0.f, 0.f, 0.f};
+        if (tok < p.tokens) {
+          const size_t k0 = static_cast<size_t>(cb + bl) * 128u + 4u * lane;
+          const uint2 xb = ldg64_coherent(p.x + static_cast<size_t>(tok) * p.in + k0);
+          const uint2 sb = *reinterpret_cast<const uint2 *>(p.side[sd].suh + k0);
+          const __half2 s01 = *reinterpret_cast<const __half2 *>(&sb.x), s23 = *reinterpret_cast<const __half2 *>(&sb.y);
+          v[0] = bf16_bits_to_f32(xb.x & 0xFFFFu) * __low2float(s01);
+          v[1] = __uint_as_float(xb.x & 0xFFFF0000u) * __high2float(s01);
+          v[2] = bf16_bits_to_f32(xb.y & 0xFFFFu) * __low2float(s23);
+          v[3] = __uint_as_float(xb.y & 0xFFFF0000u) * __high2float(s23);
+        }
+        hadamard128(v, lane);
+        float m = fmaxf(fmaxf(fabsf(v[0]), fabsf(v[1])), fmaxf(fabsf(v[2]), fabsf(v[3])));
 #pragma unroll
-  for (int j = 0; j < 8; ++j)
-#pragma unroll
-    for (int e = 0; e < 4; ++e) tot[j][e] = 0.0f;
-  {
-    const size_t side_slot = static_cast<size_t>(side) * p.slice_cap;
-    const uint2 *xs_side = xs + side_slot * 8 * 32;
-    const float *inv_side = inv_s + side_slot * 8, *scale_side = scale_s + side_slot * 8;
-    switch (S.k2) {
-      case 4: walk_blocks<4>(col_base, tk_stride, win, blk_first, b0, b1, lanes_per_side, xs_side, inv_side, scale_side, lane, tot); break;
-      case 5: walk_blocks<5>(col_base, tk_stride, win, blk_first, b0, b1, lanes_per_side, xs_side, inv_side, scale_side, lane, tot); break;
-      case 6: walk_blocks<6>(col_base, tk_stride, win, blk_first, b0, b1, lanes_per_side, xs_side, inv_side, scale_side, lane, tot); break;
-      case 8: walk_blocks<8>(col_base, tk_stride, win, blk_first, b0, b1, lanes_per_side, xs_side, inv_side, scale_side, lane, tot); break;
-      case 10: walk_blocks<10>(col_base, tk_stride, win, blk_first, b0, b1, lanes_per_side, xs_side, inv_side, scale_side, lane, tot); break;
-      default: walk_blocks<12>(col_base, tk_stride, win, blk_first, b0, b1, lanes_per_side, xs_side, inv_side, scale_side, lane, tot); break;
-    }
-  }
-
-  // ---- reduce the warps of each side (fixed order), then the cluster ----
-  __syncthreads();  // the fragments are dead: the reduction scratch aliases them
-  if (wslot > 0) {
-    const int slot = side * (lanes_per_side - 1) + (wslot - 1);
-#pragma unroll
-    for (int j = 0; j < 8; ++j) red[(slot * 8 + j) * 32 + lane] = make_float4(tot[j][0], tot[j][1], tot[j][2], tot[j][3]);
-  }
-  __syncthreads();
-  if (wslot == 0) {
-    for (int o = 1; o < lanes_per_side; ++o) {
-      const int slot = side * (lanes_per_side - 1) + (o - 1);
-#pragma unroll
-      for (int j = 0; j < 8; ++j) {
-        const float4 v = red[(slot * 8 + j) * 32 + lane];
-        tot[j][0] += v.x;
-        tot[j][1] += v.y;
-        tot[j][2] += v.z;
-        tot[j][3] += v.w;
+        for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xFFFFFFFFu, m, o));
+        int shift = 0;
+        if (m > 0.0f && m <= 3.0e38f) {
+          int e;
+          (void)frexpf(m, &e);
+          shift = max(-126, min(126, 14 - e));
+        }
+        const float scale = ldexpf(1.0f, shift);
+        const __half2 h01 = __floats2half2_rn(v[0] * scale, v[1] * scale);
+        const __half2 h23 = __floats2half2_rn(v[2] * scale, v[3] * scale);
+        // element e = 4 lane + i of the block: step kt = e / 16, inside it k16 = e % 16; the reader
+        // lane (g = token slot, t) keeps k16 in {2t, 2t+1} in .x and {2t+8, 2t+9} in .y
+        const int kt = lane >> 2, k16 = (lane & 3) * 4;
+        const int t_first = (k16 & 7) >> 1, reg = k16 >> 3;
+        const uint32_t tt = tok >> 3, slot = tok & 7u;
+        const size_t blk_slot = static_cast<size_t>(sd) * p.chunk + bl;
+        uint32_t *dst = reinterpret_cast<uint32_t *>(xs + ((blk_slot * 8 + kt) * NT + tt) * 32 + slot * 4);
+        dst[t_first * 2 + reg] = *reinterpret_cast<const uint32_t *>(&h01);
+        dst[(t_first + 1) * 2 + reg] = *reinterpret_cast<const uint32_t *>(&h23);
+        if (lane == 0) {
+          inv_s[blk_slot * 8 * NT + tok] = tok < p.tokens ? ldexpf(1.0f, -shift) : 0.0f;
+          scale_s[blk_slot * 8 * NT + tok] = scale;
+        }
       }
     }
+    __syncthreads();
+
+    // ---- this warp's tile column down the chunk ----
+    for (uint32_t bl = 0; bl < nb; ++bl) {
+      const bool more = cb + bl + 1 < b1;  // uniform: another block follows in this CTA's slice
 #pragma unroll
-    for (int j = 0; j < 8; ++j) part[(side * 8 + j) * 32 + lane] = make_float4(tot[j][0], tot[j][1], tot[j][2], tot[j][3]);
+      for (int sd = 0; sd < SIDES; ++sd) {
+        const size_t blk_slot = static_cast<size_t>(sd) * p.chunk + bl;
+        // into this block's units: accumulators were in the previous block's
+#pragma unroll
+        for (int tt = 0; tt < NT; ++tt) {
+          const float2 sc = *reinterpret_cast<const float2 *>(scale_s + blk_slot * 8 * NT + tt * 8 + t2);
+          const float f0 = carry[sd][tt][0] * sc.x, f1 = carry[sd][tt][1] * sc.y;
+          tot[sd][tt][0] *= f0;
+          tot[sd][tt][1] *= f1;
+          tot[sd][tt][2] *= f0;
+          tot[sd][tt][3] *= f1;
+          const float2 iv = *reinterpret_cast<const float2 *>(inv_s + blk_slot * 8 * NT + tt * 8 + t2);
+          carry[sd][tt][0] = iv.x;
+          carry[sd][tt][1] = iv.y;
+        }
+        if (more) q[sd][0] += 8 * step_words[sd], q[sd][1] += 8 * step_words[sd], q[sd][2] += 8 * step_words[sd];
+      }
+#pragma unroll
+      for (int kt = 0; kt < 8; ++kt) {
+#pragma unroll
+        for (int sd = 0; sd < SIDES; ++sd) {
+          uint32_t frag[4];
+          decode_tile<K2>(p.side[sd].k2, bw[sd].w[kt][0], bw[sd].w[kt][1], bw[sd].w[kt][2], win[sd].off, frag);
+          if (more) {  // the same step of the next block, into the registers just consumed
+#pragma unroll
+            for (int c = 0; c < 3; ++c) bw[sd].w[kt][c] = __ldg(q[sd][c] + kt * step_words[sd]);
+          }
+          const uint2 *xb = xs + ((static_cast<size_t>(sd) * p.chunk + bl) * 8 + kt) * NT * 32 + lane;
+#pragma unroll
+          for (int tt = 0; tt < NT; ++tt) {
+            const uint2 b = xb[tt * 32];
+            mma_f16_f32(tot[sd][tt], frag[0], frag[2], frag[1], frag[3], b.x, b.y);
+          }
+        }
+      }
+    }
   }
+  // back to the activations' own units, and out to the cluster
+#pragma unroll
+  for (int sd = 0; sd < SIDES; ++sd)
+#pragma unroll
+    for (int tt = 0; tt < NT; ++tt) {
+      tot[sd][tt][0] *= carry[sd][tt][0];
+      tot[sd][tt][1] *= carry[sd][tt][1];
+      tot[sd][tt][2] *= carry[sd][tt][0];
+      tot[sd][tt][3] *= carry[sd][tt][1];
+      part[((sd * 8 + warp) * NT + tt) * 32 + lane] = make_float4(tot[sd][tt][0], tot[sd][tt][1], tot[sd][tt][2], tot[sd][tt][3]);
+    }
   cluster_barrier();
 
-  // ---- the first CTA of the cluster finishes: warp = token, lane = 4 output columns ----
-  if (rank == 0 && static_cast<uint32_t>(warp) < p.tokens) {
-    const int tok = warp;
-    const int tq = tok >> 1, te = tok & 1;
-    float v[2][4];
+  // ---- finish: tokens dealt over the cluster's CTAs and their warps; lane = 4 output columns ----
+  for (uint32_t tok = rank + kc * static_cast<uint32_t>(warp); tok < p.tokens; tok += kc * kWarps) {
+    const uint32_t tt = tok >> 3, slot = tok & 7u;
+    const int tq = static_cast<int>(slot >> 1), te = static_cast<int>(slot & 1u);
+    float v[SIDES][4];
 #pragma unroll
-    for (int sd = 0; sd < 2; ++sd) {
-#pragma unroll
-      for (int i = 0; i < 4; ++i) v[sd][i] = 0.0f;
-    }
-    for (int sd = 0; sd < sides; ++sd) {
+    for (int sd = 0; sd < SIDES; ++sd) {
 #pragma unroll
       for (int i = 0; i < 4; ++i) {
         const int c = 4 * lane + i;  // column inside the block
         const int j = c >> 4, cc = c & 15;
-        const float *src = reinterpret_cast<const float *>(&part[(sd * 8 + j) * 32 + (cc & 7) * 4 + tq]) + te + 2 * (cc >> 3);
+        const float *src = reinterpret_cast<const float *>(&part[((sd * 8 + j) * NT + tt) * 32 + (cc & 7) * 4 + tq]) + te + 2 * (cc >> 3);
         float sum = 0.0f;
         for (uint32_t r = 0; r < kc; ++r) sum += ld_cluster_f32(src, r);
         v[sd][i] = sum;
@@ -243,7 +297,7 @@ __global__ void __launch_bounds__(kThreads, 2) trellis_linear_kernel(const __gri
     uint16_t *dst = p.y + static_cast<size_t>(tok) * p.ldy + static_cast<size_t>(col_block) * 128u + 4u * lane;
     float r[4];
 #pragma unroll
-    for (int i = 0; i < 4; ++i) r[i] = swiglu ? v[0][i] / (1.0f + __expf(-v[0][i])) * v[1][i] : v[0][i];
+    for (int i = 0; i < 4; ++i) r[i] = SIDES == 2 ? v[0][i] / (1.0f + __expf(-v[0][i])) * v[SIDES - 1][i] : v[0][i];
     if (p.epilogue == kEpiAdd) {
       const uint2 old = *reinterpret_cast<const uint2 *>(dst);
       r[0] += bf16_bits_to_f32(old.x & 0xFFFFu);
@@ -257,14 +311,21 @@ __global__ void __launch_bounds__(kThreads, 2) trellis_linear_kernel(const __gri
     packed.y = *reinterpret_cast<const uint32_t *>(&o23);
     *reinterpret_cast<uint2 *>(dst) = packed;
   }
-  cluster_barrier();  // peers keep their partial sums alive until the first CTA has read them
+  cluster_barrier();  // peers keep their partial sums alive until every CTA has read them
 }
 
-size_t linear_smem_bytes(uint32_t slice_cap, int sides) {
-  const size_t frag_bytes = static_cast<size_t>(sides) * slice_cap * 2048u;
-  const size_t red_bytes = static_cast<size_t>(kWarps - sides) * 8 * 32 * 16;
-  return (frag_bytes > red_bytes ? frag_bytes : red_bytes) + 2 * 8 * 32 * 16 +
-         static_cast<size_t>(sides) * slice_cap * 8 * 4 * 2;
+constexpr size_t kLinearMaxSmem = 200 * 1024;
+
+size_t linear_smem_bytes(uint32_t chunk, int nt, int sides) {
+  return static_cast<size_t>(sides) * chunk * nt * 2048u + static_cast<size_t>(sides) * 8 * nt * 32 * 16 +
+         static_cast<size_t>(sides) * chunk * nt * 8 * 4 * 2;
+}
+
+// Blocks of rotated activations that fit the kernel's shared memory.
+uint32_t chunk_cap(int nt, int sides) {
+  const size_t fixed = static_cast<size_t>(sides) * 8 * nt * 32 * 16;
+  const size_t per_block = static_cast<size_t>(sides) * nt * (2048u + 64u);
+  return static_cast<uint32_t>((kLinearMaxSmem - fixed) / per_block);
 }
 
 bool aligned(const void *p, uintptr_t a) { return (reinterpret_cast<uintptr_t>(p) & (a - 1)) == 0; }
@@ -305,31 +366,95 @@ TrellisSide make_side(const ignis_trellis_weight *w) {
   return s;
 }
 
-// Cluster size for (in, out): enough slices that every slice fits shared memory, then the size
-// that fills the device's CTA slots best with the fewest idle warps.
-uint32_t plan_kc(const DeviceState &dev, uint32_t in, uint32_t out, int sides) {
+// CTAs of the linear kernel an SM holds at once, by (token tiles x weights).
+int ctas_per_sm(int nt, int sides) { return (sides == 1 && nt <= 2) ? 3 : (nt * sides <= 8 ? 2 : 1); }
+
+// Cluster size for (in, out): the one that costs least in waves of CTAs, each costing its warps'
+// walk down the slice (one tile per 16 inputs), the rotation of the slice and a fixed part.
+uint32_t plan_kc(const DeviceState &dev, uint32_t in, uint32_t out, int nt, int sides) {
   const uint32_t nblk = in / 128u, col_blocks = out / 128u;
   const uint32_t sms = dev.sm_cap > 0 ? static_cast<uint32_t>(dev.sm_cap) : static_cast<uint32_t>(dev.sm_count);
-  const double slots = 2.0 * sms;
-  const uint32_t warps_per_side = sides == 2 ? 4u : 8u;
-  uint32_t best = 0;
+  const double slots = static_cast<double>(ctas_per_sm(nt, sides)) * sms;
+  uint32_t best = 1;
   double best_cost = 1e30;
   for (uint32_t kc = 1; kc <= 8; ++kc) {
     if (kc > nblk) break;
     const uint32_t slice = (nblk + kc - 1) / kc;
-    if (slice * static_cast<uint32_t>(sides) > kMaxSliceBlocks) continue;
     const double ctas = static_cast<double>(col_blocks) * kc;
     const double waves = ceil(ctas / slots);
-    const double per_warp = ceil(static_cast<double>(slice) / warps_per_side);
-    // a block of 128 inputs costs 1 per warp; rotating the slice costs about 0.19 per block; 1.5
-    // stands for the reductions and the launch ramp
-    const double cost = waves * (per_warp + 0.19 * slice / 8.0 * 8.0 / warps_per_side + 1.5) + 0.01 * kc;
+    // in units of one decoded tile: 8 tiles per block and side, the rotation about 1.2 tiles per
+    // (block, token, side) shared by 8 warps, 25 for the reductions, the epilogue and the ramp
+    const double walk = 8.0 * slice * sides * (1.0 + 0.12 * (nt - 1));
+    const double rotate = 1.2 * slice * 8.0 * nt * sides / 8.0;
+    const double cost = waves * (walk + rotate + 25.0) + 0.05 * kc;
     if (cost < best_cost) {
       best_cost = cost;
       best = kc;
     }
   }
   return best;
+}
+
+template <int K2, int NT, int SIDES>
+cudaError_t launch_linear(const cudaLaunchConfig_t &config, const TrellisParams &p) {
+  return cudaLaunchKernelEx(&config, trellis_linear_kernel<K2, NT, SIDES>, p);
+}
+
+template <int K2, int NT>
+cudaError_t launch_sides(int sides, const cudaLaunchConfig_t &config, const TrellisParams &p) {
+  return sides == 2 ? launch_linear<K2, NT, 2>(config, p) : launch_linear<K2, NT, 1>(config, p);
+}
+
+template <int K2>
+cudaError_t launch_nt(int nt, int sides, const cudaLaunchConfig_t &config, const TrellisParams &p) {
+  switch (nt) {
+    case 1: return launch_sides<K2, 1>(sides, config, p);
+    case 2: return launch_sides<K2, 2>(sides, config, p);
+    case 4: return launch_sides<K2, 4>(sides, config, p);
+    default: return launch_sides<K2, 8>(sides, config, p);
+  }
+}
+
+cudaError_t launch_k2(uint32_t k2, int nt, int sides, const cudaLaunchConfig_t &config, const TrellisParams &p) {
+  switch (k2) {
+    case 0: return launch_nt<0>(nt, sides, config, p);
+    case 4: return launch_nt<4>(nt, sides, config, p);
+    case 5: return launch_nt<5>(nt, sides, config, p);
+    case 6: return launch_nt<6>(nt, sides, config, p);
+    case 8: return launch_nt<8>(nt, sides, config, p);
+    case 10: return launch_nt<10>(nt, sides, config, p);
+    default: return launch_nt<12>(nt, sides, config, p);
+  }
+}
+
+template <int K2, int NT, int SIDES>
+cudaError_t set_linear_attr() {
+  return cudaFuncSetAttribute(trellis_linear_kernel<K2, NT, SIDES>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                              static_cast<int>(kLinearMaxSmem));
+}
+
+template <int K2>
+cudaError_t set_linear_attrs() {
+  cudaError_t err = set_linear_attr<K2, 1, 1>();
+  if (err == cudaSuccess) err = set_linear_attr<K2, 1, 2>();
+  if (err == cudaSuccess) err = set_linear_attr<K2, 2, 1>();
+  if (err == cudaSuccess) err = set_linear_attr<K2, 2, 2>();
+  if (err == cudaSuccess) err = set_linear_attr<K2, 4, 1>();
+  if (err == cudaSuccess) err = set_linear_attr<K2, 4, 2>();
+  if (err == cudaSuccess) err = set_linear_attr<K2, 8, 1>();
+  if (err == cudaSuccess) err = set_linear_attr<K2, 8, 2>();
+  return err;
+}
+
+cudaError_t set_all_linear_attrs() {
+  cudaError_t err = set_linear_attrs<0>();
+  if (err == cudaSuccess) err = set_linear_attrs<4>();
+  if (err == cudaSuccess) err = set_linear_attrs<5>();
+  if (err == cudaSuccess) err = set_linear_attrs<6>();
+  if (err == cudaSuccess) err = set_linear_attrs<8>();
+  if (err == cudaSuccess) err = set_linear_attrs<10>();
+  if (err == cudaSuccess) err = set_linear_attrs<12>();
+  return err;
 }
 
 int32_t run_linear(ErrorSlot &slot, const ignis_trellis_weight *a, const ignis_trellis_weight *b, const void *x,
@@ -348,8 +473,6 @@ int32_t run_linear(ErrorSlot &slot, const ignis_trellis_weight *a, const ignis_t
   const DeviceState *dev = prepared(slot, what);
   if (dev == nullptr) return -1;
   const int sides = swiglu ? 2 : 1;
-  const uint32_t kc = plan_kc(*dev, a->in, a->out, sides);
-  if (kc == 0) return fail(slot, "%s: in = %u is too long for one call (at most %u)", what, a->in, 8u * kMaxSliceBlocks * 128u / static_cast<uint32_t>(sides));
   TrellisParams p = {};
   p.side[0] = make_side(a);
   p.side[1] = swiglu ? make_side(b) : p.side[0];
@@ -357,17 +480,23 @@ int32_t run_linear(ErrorSlot &slot, const ignis_trellis_weight *a, const ignis_t
   p.out = a->out;
   p.ldy = ldy;
   p.epilogue = epilogue;
-  p.kc = kc;
-  p.slice_cap = (a->in / 128u + kc - 1) / kc;
-  const size_t smem = linear_smem_bytes(p.slice_cap, sides);
-  for (uint32_t t0 = 0; t0 < tokens; t0 += 8) {
-    p.tokens = tokens - t0 < 8u ? tokens - t0 : 8u;
+  const uint32_t k2 = (swiglu && a->k2 != b->k2) ? 0u : a->k2;  // 0: each side decodes with its own width
+  // passes of up to 64 tokens (IGNIS_TRELLIS_DECODE_MAX_TOKENS): every decoded tile serves the
+  // pass's token tiles of 8
+  for (uint32_t t0 = 0; t0 < tokens; t0 += IGNIS_TRELLIS_DECODE_MAX_TOKENS) {
+    p.tokens = tokens - t0 < IGNIS_TRELLIS_DECODE_MAX_TOKENS ? tokens - t0 : IGNIS_TRELLIS_DECODE_MAX_TOKENS;
+    const int nt = p.tokens <= 8 ? 1 : (p.tokens <= 16 ? 2 : (p.tokens <= 32 ? 4 : 8));
+    const uint32_t kc = plan_kc(*dev, a->in, a->out, nt, sides);
+    const uint32_t slice = (a->in / 128u + kc - 1) / kc;
+    const uint32_t cap = chunk_cap(nt, sides);
+    p.kc = kc;
+    p.chunk = slice < cap ? slice : cap;
     p.x = static_cast<const uint16_t *>(x) + static_cast<size_t>(t0) * a->in;
     p.y = static_cast<uint16_t *>(y) + static_cast<size_t>(t0) * ldy;
     cudaLaunchConfig_t config = {};
     config.gridDim = dim3((a->out / 128u) * kc, 1, 1);
     config.blockDim = dim3(kThreads, 1, 1);
-    config.dynamicSmemBytes = smem;
+    config.dynamicSmemBytes = linear_smem_bytes(p.chunk, nt, sides);
     config.stream = static_cast<cudaStream_t>(stream);
     cudaLaunchAttribute attr[2];
     attr[0].id = cudaLaunchAttributeClusterDimension;
@@ -378,7 +507,7 @@ int32_t run_linear(ErrorSlot &slot, const ignis_trellis_weight *a, const ignis_t
     attr[1].val.programmaticStreamSerializationAllowed = 1;
     config.attrs = attr;
     config.numAttrs = dev->pdl ? 2 : 1;
-    const cudaError_t err = cudaLaunchKernelEx(&config, trellis_linear_kernel, p);
+    const cudaError_t err = launch_k2(k2, nt, sides, config, p);
     if (err != cudaSuccess) return fail(slot, "%s: launch failed: %s", what, cudaGetErrorString(err));
   }
   return 0;
@@ -415,8 +544,7 @@ extern "C" {
 int32_t ignis_trellis_prepare(void) {
   ErrorSlot &slot = trellis_error();
   if (prepare_device(slot) != 0) return -1;
-  const cudaError_t err = cudaFuncSetAttribute(trellis_linear_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                               static_cast<int>(linear_smem_bytes(kMaxSliceBlocks, 1)));
+  const cudaError_t err = set_all_linear_attrs();
   if (err != cudaSuccess) return fail(slot, "ignis_trellis_prepare: %s", cudaGetErrorString(err));
   return 0;
 }
@@ -431,7 +559,6 @@ uint64_t ignis_trellis_workspace_bytes(uint32_t in, uint32_t out, uint32_t weigh
   if (dev == nullptr || !dev->prepared) return 0;
   if (in == 0 || (in % 128u) != 0 || out == 0 || (out % 128u) != 0 || out > IGNIS_TRELLIS_MAX_OUT) return 0;
   if (weights < 1 || weights > 2 || tokens == 0) return 0;
-  if (plan_kc(*dev, in, out, static_cast<int>(weights)) == 0) return 0;
   return 256;  // partial sums meet in distributed shared memory: one aligned line, never read
 }
 
