@@ -2,13 +2,15 @@
 //
 // Routed experts (the reference's ignis_moe_experts_prefill / _decode, kernel/src/moe_prefill.cu:
 // 41-492 and moe_decode.cu:325-399): the (token, rank) assignments are grouped by expert on the
-// device (count, scan, scatter), cut into work items of at most 8 rows of one expert, and two
-// grouped launches follow - gate/up with the SwiGLU epilogue into h (fp32 [rows][inter]), then
-// down with the routing weight applied and the result added to `acc` in 64-bit fixed point
-// (2^-32), so the sum does not depend on arrival order. Each item's CTA cluster runs the dense
-// trellis linear's machinery (trellis_device.cuh): rotation of the rows into fp16 fragments,
-// tiles decoded in registers straight into MMA fragments, fp32 accumulation, shared-memory and
-// distributed-shared-memory reductions, output Hadamard and svh.
+// device (count, scan, scatter) and cut into work items of at most 64 rows of one expert (8 from
+// the decode entry) made of row tiles of 8. Every row is rotated once into MMA B fragments in the
+// workspace (x o suh, Hadamard, power-of-two scale per row and 128 inputs, fp16); a grouped launch
+// multiplies each item with its expert's gate|up record, one CTA per 128 output columns, warp j
+// walking tile column j: every tile is decoded once in registers and used for all the item's row
+// tiles. silu(g) u is rotated the same way and the down launch adds the weighted result to `acc`
+// in 64-bit fixed point (2^-32), so the sum does not depend on arrival order. No CTA waits for
+// another; a row's arithmetic does not depend on the item it is in, so the decode and prefill
+// entries give the same bits.
 //
 // Nothing here traps or spins: a bad expert id, an absent record or an out-of-range contribution
 // is skipped and recorded in the workspace's status word.
@@ -32,31 +34,49 @@ struct Geometry {
 };
 Geometry g_geo;
 
+// A work item: up to `item_rows` sorted rows of one expert (64 from the prefill entry, 8 from the
+// decode entry), i.e. up to 8 row tiles of 8.
 struct Item {
+  uint32_t expert, first, count, tile_first;
+};
+// A row tile: 8 consecutive sorted rows of one expert (the MMA's N), the unit the activations are
+// rotated in.
+struct Tile {
   uint32_t expert, first, count, pad;
 };
 
 // Workspace regions for `tokens_max` tokens.
 struct Layout {
-  uint64_t status, counts, cursor, offsets, n_items, sorted, items, h, total;
-  uint32_t rows_max, items_max;
+  uint64_t status, counts, cursor, offsets, n_items, sorted, items, tiles, frag_in, scale_in, gu, frag_h, scale_h, total;
+  uint32_t rows_max, items_max, tiles_max;
 };
 
 uint64_t align256(uint64_t v) { return (v + 255u) & ~static_cast<uint64_t>(255u); }
 
+uint32_t items_bound(const Geometry &g, uint32_t rows, uint32_t item_rows) {
+  return rows / item_rows + (g.experts < rows ? g.experts : rows);
+}
+
 Layout layout_for(const Geometry &g, uint32_t tokens_max) {
   Layout l = {};
   l.rows_max = tokens_max * g.top_k;
-  l.items_max = (l.rows_max + 7u) / 8u + (g.experts < l.rows_max ? g.experts : l.rows_max);
+  l.items_max = items_bound(g, l.rows_max, 8u);  // the bound for 8-row items covers 64-row items too
+  l.tiles_max = items_bound(g, l.rows_max, 8u);
+  const uint64_t nblk_h = g.hidden / 128u, nblk_i = g.inter / 128u;
   uint64_t at = 0;
   l.status = at; at += 256;
   l.counts = at; at = align256(at + 4ull * g.experts);
   l.cursor = at; at = align256(at + 4ull * g.experts);
   l.offsets = at; at = align256(at + 4ull * (g.experts + 1));
-  l.n_items = at; at += 256;
+  l.n_items = at; at += 256;  // [0] items, [1] tiles
   l.sorted = at; at = align256(at + 4ull * l.rows_max);
   l.items = at; at = align256(at + 16ull * l.items_max);
-  l.h = at; at = align256(at + 4ull * l.rows_max * g.inter);
+  l.tiles = at; at = align256(at + 16ull * l.tiles_max);
+  l.frag_in = at; at = align256(at + 2048ull * l.tiles_max * nblk_h);   // rotated x, fragment order
+  l.scale_in = at; at = align256(at + 64ull * l.tiles_max * nblk_h);    // (inverse scale, scale) x 8 rows
+  l.gu = at; at = align256(at + 8ull * l.rows_max * g.inter);           // fp32 [rows][2 inter]
+  l.frag_h = at; at = align256(at + 2048ull * l.tiles_max * nblk_i);    // rotated silu(g) u
+  l.scale_h = at; at = align256(at + 64ull * l.tiles_max * nblk_i);
   l.total = at;
   return l;
 }
@@ -76,42 +96,48 @@ __global__ void __launch_bounds__(256) moe_count_kernel(const int32_t *ids, uint
   }
 }
 
-// One CTA: exclusive scans of the per-expert row counts and item counts, then the item list.
-__global__ void __launch_bounds__(1024) moe_scan_kernel(const uint32_t *counts, uint32_t experts, uint32_t *offsets,
-                                                        uint32_t *n_items, Item *items) {
+// One CTA: exclusive scans of the per-expert row, item and tile counts, then the item and tile lists.
+__global__ void __launch_bounds__(1024) moe_scan_kernel(const uint32_t *counts, uint32_t experts, uint32_t item_rows,
+                                                        uint32_t *offsets, uint32_t *n_items, Item *items, Tile *tiles) {
   griddep_launch_dependents();
   griddep_wait();
-  __shared__ uint32_t row_sum[1024], item_sum[1024];
+  __shared__ uint32_t row_sum[1024], item_sum[1024], tile_sum[1024];
   const uint32_t per = (experts + 1023u) / 1024u;  // experts per thread, consecutive
   const uint32_t e0 = threadIdx.x * per;
-  uint32_t rows = 0, its = 0;
+  uint32_t rows = 0, its = 0, tls = 0;
   for (uint32_t e = e0; e < e0 + per && e < experts; ++e) {
     rows += counts[e];
-    its += (counts[e] + 7u) / 8u;
+    its += (counts[e] + item_rows - 1u) / item_rows;
+    tls += (counts[e] + 7u) / 8u;
   }
   row_sum[threadIdx.x] = rows;
   item_sum[threadIdx.x] = its;
+  tile_sum[threadIdx.x] = tls;
   __syncthreads();
   for (uint32_t d = 1; d < 1024; d <<= 1) {  // Hillis-Steele inclusive scan
     const uint32_t r = threadIdx.x >= d ? row_sum[threadIdx.x - d] : 0u;
     const uint32_t i = threadIdx.x >= d ? item_sum[threadIdx.x - d] : 0u;
+    const uint32_t t = threadIdx.x >= d ? tile_sum[threadIdx.x - d] : 0u;
     __syncthreads();
     row_sum[threadIdx.x] += r;
     item_sum[threadIdx.x] += i;
+    tile_sum[threadIdx.x] += t;
     __syncthreads();
   }
-  uint32_t row_at = row_sum[threadIdx.x] - rows, item_at = item_sum[threadIdx.x] - its;
+  uint32_t row_at = row_sum[threadIdx.x] - rows, item_at = item_sum[threadIdx.x] - its, tile_at = tile_sum[threadIdx.x] - tls;
   for (uint32_t e = e0; e < e0 + per && e < experts; ++e) {
     offsets[e] = row_at;
     const uint32_t c = counts[e];
-    for (uint32_t j = 0; j < c; j += 8) {
-      items[item_at++] = Item{e, row_at + j, c - j < 8u ? c - j : 8u, 0u};
+    for (uint32_t j = 0; j < c; j += item_rows) {
+      items[item_at++] = Item{e, row_at + j, c - j < item_rows ? c - j : item_rows, tile_at + j / 8u};
     }
+    for (uint32_t j = 0; j < c; j += 8) tiles[tile_at++] = Tile{e, row_at + j, c - j < 8u ? c - j : 8u, 0u};
     row_at += c;
   }
   if (threadIdx.x == 1023) {
     offsets[experts] = row_sum[1023];
-    *n_items = item_sum[1023];
+    n_items[0] = item_sum[1023];
+    n_items[1] = tile_sum[1023];
   }
 }
 
@@ -128,211 +154,291 @@ __global__ void __launch_bounds__(256) moe_scatter_kernel(const int32_t *ids, ui
   }
 }
 
-// ---- the grouped expert kernel ---------------------------------------------------------------
+// ---- the expert kernels ----------------------------------------------------------------------
 struct ExpertParams {
   const ignis_moe_slot *slots;
   const Item *items;
-  const uint32_t *n_items;
+  const Tile *tiles;
+  const uint32_t *n_items;  // [0] items, [1] tiles
   const uint32_t *sorted;   // row -> assignment index (token * top_k + rank)
   const uint16_t *x;        // BF16 [tokens][hidden]
   const float *weights;     // routing weights [tokens][top_k]
-  float *h;                 // fp32 [rows][inter]
+  uint2 *frag_in;           // rotated x: [tile][hidden / 128][step 8][lane 32]
+  float2 *scale_in;         // (inverse scale, scale): [tile][hidden / 128][row 8]
+  float *gu;                // fp32 [rows][2 inter]: gate | up products
+  uint2 *frag_h;            // rotated silu(g) u: [tile][inter / 128][step 8][lane 32]
+  float2 *scale_h;
   long long *acc;           // int64 [tokens][hidden]
   uint32_t *status;
   uint32_t hidden, inter, top_k, experts;
-  uint32_t kc;              // cluster size
-  uint32_t slice_cap;       // 128-input blocks of fragments a CTA holds
 };
 
-// PHASE 0: gate/up with SwiGLU into h. PHASE 1: down, weighted, into acc.
+// Rotates the rows of one tile into B fragments, once per row: PHASE 0 x o suh of the gate/up
+// record, PHASE 1 silu(g) u o suh of the down record; then the 128-wide Hadamard in fp32, a
+// power-of-two scale per (row, block) (largest value in [2^13, 2^14)) and fp16. One CTA per tile,
+// warp r = row r; a block's fragment (2 KB) is put together in shared memory and written out whole.
 template <int PHASE>
-__global__ void __launch_bounds__(kThreads, 2) moe_experts_kernel(const __grid_constant__ ExpertParams p) {
-  extern __shared__ __align__(16) uint8_t smem_raw[];
+__global__ void __launch_bounds__(kThreads) moe_rotate_kernel(const __grid_constant__ ExpertParams p) {
+  __shared__ __align__(16) uint2 frag[2][256];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const uint32_t rank = cluster_rank(), kc = p.kc;
+  griddep_launch_dependents();
+  griddep_wait();
+  const uint32_t tile_index = blockIdx.x;
+  if (tile_index >= p.n_items[1]) return;
+  const Tile tile = p.tiles[tile_index];
+  const ignis_moe_slot slot = p.slots[tile.expert * 2u + PHASE];
+  if (slot.record == nullptr || !(slot.k2 == 4 || slot.k2 == 5 || slot.k2 == 6 || slot.k2 == 8)) return;  // flagged by the walk
+  const uint32_t in = PHASE == 0 ? p.hidden : p.inter;
+  const uint32_t out_plane = PHASE == 0 ? 2u * p.inter : p.hidden;
+  const uint64_t trellis_bytes = static_cast<uint64_t>(in) * out_plane * slot.k2 / 16u;
+  const uint16_t *suh = reinterpret_cast<const uint16_t *>(static_cast<const uint8_t *>(slot.record) + trellis_bytes);
+  const uint32_t nblk = in / 128u;
+  const bool live = static_cast<uint32_t>(warp) < tile.count;
+  const uint32_t row = tile.first + static_cast<uint32_t>(warp);
+  uint32_t token = 0;
+  if (live && PHASE == 0) token = p.sorted[row] / p.top_k;
+  uint2 *dst_frag = (PHASE == 0 ? p.frag_in : p.frag_h) + static_cast<size_t>(tile_index) * nblk * 256u;
+  float2 *dst_scale = (PHASE == 0 ? p.scale_in : p.scale_h) + static_cast<size_t>(tile_index) * nblk * 8u;
+  for (uint32_t bl = 0; bl < nblk; ++bl) {
+    float v[4] = {0.f, 0.f, 0.f, 0.f};
+    if (live) {
+      const size_t k0 = static_cast<size_t>(bl) * 128u + 4u * lane;
+      const uint2 sb = *reinterpret_cast<const uint2 *>(suh + k0);
+      const __half2 s01 = *reinterpret_cast<const __half2 *>(&sb.x), s23 = *reinterpret_cast<const __half2 *>(&sb.y);
+      if (PHASE == 0) {
+        const uint2 xb = ldg64_coherent(p.x + static_cast<size_t>(token) * p.hidden + k0);
+        v[0] = bf16_bits_to_f32(xb.x & 0xFFFFu) * __low2float(s01);
+        v[1] = __uint_as_float(xb.x & 0xFFFF0000u) * __high2float(s01);
+        v[2] = bf16_bits_to_f32(xb.y & 0xFFFFu) * __low2float(s23);
+        v[3] = __uint_as_float(xb.y & 0xFFFF0000u) * __high2float(s23);
+      } else {
+        const float *g = p.gu + static_cast<size_t>(row) * 2u * p.inter + k0;
+        const uint4 gb = ldg128_coherent(g), ub = ldg128_coherent(g + p.inter);
+        const float gv[4] = {__uint_as_float(gb.x), __uint_as_float(gb.y), __uint_as_float(gb.z), __uint_as_float(gb.w)};
+        const float uv[4] = {__uint_as_float(ub.x), __uint_as_float(ub.y), __uint_as_float(ub.z), __uint_as_float(ub.w)};
+        const float sv[4] = {__low2float(s01), __high2float(s01), __low2float(s23), __high2float(s23)};
+#pragma unroll
+        for (int i = 0; i < 4; ++i) v[i] = gv[i] / (1.0f + __expf(-gv[i])) * uv[i] * sv[i];
+      }
+    }
+    hadamard128(v, lane);
+    float m = fmaxf(fmaxf(fabsf(v[0]), fabsf(v[1])), fmaxf(fabsf(v[2]), fabsf(v[3])));
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xFFFFFFFFu, m, o));
+    int shift = 0;
+    if (m > 0.0f && m <= 3.0e38f) {
+      int e;
+      (void)frexpf(m, &e);
+      shift = max(-126, min(126, 14 - e));
+    }
+    const float scale = ldexpf(1.0f, shift);
+    const __half2 h01 = __floats2half2_rn(v[0] * scale, v[1] * scale);
+    const __half2 h23 = __floats2half2_rn(v[2] * scale, v[3] * scale);
+    // element e = 4 lane + i of the block: step kt = e / 16, inside it k16 = e % 16; the reader
+    // lane (g = row, t) keeps k16 in {2t, 2t+1} in .x and {2t+8, 2t+9} in .y
+    const int kt = lane >> 2, k16 = (lane & 3) * 4;
+    const int t_first = (k16 & 7) >> 1, reg = k16 >> 3;
+    uint32_t *dst = reinterpret_cast<uint32_t *>(&frag[bl & 1][kt * 32 + warp * 4]);
+    dst[t_first * 2 + reg] = *reinterpret_cast<const uint32_t *>(&h01);
+    dst[(t_first + 1) * 2 + reg] = *reinterpret_cast<const uint32_t *>(&h23);
+    if (lane == 0) dst_scale[bl * 8u + warp] = make_float2(live ? ldexpf(1.0f, -shift) : 0.0f, scale);
+    __syncthreads();  // the block's fragment is whole; the other buffer is free for the next block
+    dst_frag[static_cast<size_t>(bl) * 256u + threadIdx.x] = frag[bl & 1][threadIdx.x];
+  }
+}
+
+// The lane's words of the 8 steps of one 128-input block of one tile column.
+struct BlockWords {
+  uint32_t w[8][3];
+};
+
+__device__ __forceinline__ void cp_async16(void *smem_dst, const void *src) {
+  const uint32_t dst = static_cast<uint32_t>(__cvta_generic_to_shared(smem_dst));
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+__device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wait_group 0;" ::: "memory"); }
+
+// The item's fragments and scales of one 128-input block, copied asynchronously into the CTA's
+// staging buffers: 2 KB per live row tile and 64 bytes of (inverse scale, scale) pairs.
+template <int NT>
+__device__ __forceinline__ void stage_block(uint2 *frag_buf, float2 *scale_buf, const uint2 *frag, const float2 *scales,
+                                            uint32_t nblk, uint32_t bl, uint32_t ntiles) {
+  for (uint32_t c = threadIdx.x; c < ntiles * 128u; c += kThreads) {
+    const uint32_t tt = c >> 7, off = c & 127u;  // 16-byte chunk `off` of tile tt's fragment
+    cp_async16(frag_buf + tt * 256u + off * 2u, frag + (static_cast<size_t>(tt) * nblk + bl) * 256u + off * 2u);
+  }
+  if (threadIdx.x < ntiles * 4u) {
+    const uint32_t tt = threadIdx.x >> 2, off = threadIdx.x & 3u;
+    cp_async16(scale_buf + tt * 8u + off * 2u, scales + (static_cast<size_t>(tt) * nblk + bl) * 8u + off * 2u);
+  }
+  cp_async_commit();
+}
+
+// Warp j of the CTA walks tile column j of the item's column block down all the inputs: one tile
+// per 16 inputs, decoded once and multiplied with every live row tile of the item (up to NT tiles
+// of 8 rows). The words of the next 128-input block are requested as the current block's are
+// consumed; the rows' fragments and scales of the next block are copied to shared memory while
+// the current block is multiplied (one CTA barrier per block). Sums are in the units of the
+// current block's per-row scale and carried exactly into the next block's.
+template <int K2, int NT>
+__device__ __forceinline__ void walk_tile_column(const uint32_t *tile_base, int64_t step_words, uint32_t nblk, const uint2 *frag,
+                                                 const float2 *scales, uint32_t ntiles, int lane, uint2 (*frag_buf)[NT * 256],
+                                                 float2 (*scale_buf)[NT * 8], float (&tot)[NT][4]) {
+  const LaneWindow win = lane_window(K2, lane);
+  const uint32_t *q0 = tile_base + win.w0, *q1 = tile_base + win.w1, *q2 = tile_base + win.w2;
+  BlockWords bw;
+#pragma unroll
+  for (int kt = 0; kt < 8; ++kt) {
+    bw.w[kt][0] = __ldg(q0 + kt * step_words);
+    bw.w[kt][1] = __ldg(q1 + kt * step_words);
+    bw.w[kt][2] = __ldg(q2 + kt * step_words);
+  }
+  stage_block<NT>(frag_buf[0], scale_buf[0], frag, scales, nblk, 0, ntiles);
+  const int t2 = (lane & 3) * 2;
+  for (uint32_t bl = 0; bl < nblk; ++bl) {
+    const bool more = bl + 1 < nblk;
+    cp_async_wait_all();
+    __syncthreads();  // this block's copies are visible; nobody still reads the buffers refilled next
+    if (more) stage_block<NT>(frag_buf[(bl + 1) & 1], scale_buf[(bl + 1) % 3], frag, scales, nblk, bl + 1, ntiles);
+    const uint2 *fb = frag_buf[bl & 1] + lane;
+    const float2 *cur = scale_buf[bl % 3] + t2, *prev = scale_buf[(bl + 2) % 3] + t2;
+    // into this block's units: the sums so far are in the previous block's (inverse scale of the
+    // previous block times scale of this one, an exact power of two; nothing to carry at block 0)
+#pragma unroll
+    for (int tt = 0; tt < NT; ++tt) {
+      float f0 = 0.0f, f1 = 0.0f;
+      if (bl > 0 && static_cast<uint32_t>(tt) < ntiles) {
+        const float4 c = *reinterpret_cast<const float4 *>(cur + tt * 8), pv = *reinterpret_cast<const float4 *>(prev + tt * 8);
+        f0 = pv.x * c.y;
+        f1 = pv.z * c.w;
+      }
+      tot[tt][0] *= f0;
+      tot[tt][1] *= f1;
+      tot[tt][2] *= f0;
+      tot[tt][3] *= f1;
+    }
+    if (more) q0 += 8 * step_words, q1 += 8 * step_words, q2 += 8 * step_words;
+#pragma unroll
+    for (int kt = 0; kt < 8; ++kt) {
+      uint32_t a[4];
+      decode8<K2>(bw.w[kt][0], bw.w[kt][1], bw.w[kt][2], win.off, a);
+      if (more) {
+        bw.w[kt][0] = __ldg(q0 + kt * step_words);
+        bw.w[kt][1] = __ldg(q1 + kt * step_words);
+        bw.w[kt][2] = __ldg(q2 + kt * step_words);
+      }
+#pragma unroll
+      for (int tt = 0; tt < NT; ++tt) {
+        if (static_cast<uint32_t>(tt) < ntiles) {  // uniform over the CTA
+          const uint2 b = fb[tt * 256 + kt * 32];
+          mma_f16_f32(tot[tt], a[0], a[2], a[1], a[3], b.x, b.y);
+        }
+      }
+    }
+  }
+  // back to the rows' own units
+  const float2 *last = scale_buf[(nblk - 1u) % 3] + t2;
+#pragma unroll
+  for (int tt = 0; tt < NT; ++tt) {
+    float i0 = 0.0f, i1 = 0.0f;
+    if (static_cast<uint32_t>(tt) < ntiles) {
+      const float4 c = *reinterpret_cast<const float4 *>(last + tt * 8);
+      i0 = c.x;
+      i1 = c.z;
+    }
+    tot[tt][0] *= i0;
+    tot[tt][1] *= i1;
+    tot[tt][2] *= i0;
+    tot[tt][3] *= i1;
+  }
+}
+
+// PHASE 0: gate | up products of an item into gu. PHASE 1: down, weighted, into acc.
+// One CTA per (item, block of 128 output columns); no CTA waits for another.
+template <int PHASE, int NT>
+__global__ void __launch_bounds__(kThreads, NT <= 2 ? 3 : 2) moe_experts_kernel(const __grid_constant__ ExpertParams p) {
+  // staging for two blocks of fragments, aliased after the walk by the partial sums
+  // [tile column 8][row tile NT][lane 32]; three blocks of scales
+  __shared__ __align__(16) uint2 frag_buf[2][NT * 256];
+  __shared__ __align__(16) float2 scale_buf[3][NT * 8];
+  float4 *part = reinterpret_cast<float4 *>(&frag_buf[0][0]);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const uint32_t in = PHASE == 0 ? p.hidden : p.inter;
   const uint32_t out_plane = PHASE == 0 ? 2u * p.inter : p.hidden;   // columns of the stored plane
-  const uint32_t col_blocks = (PHASE == 0 ? p.inter : p.hidden) / 128u;
-  const uint32_t item_index = blockIdx.x / (col_blocks * kc);
-  const uint32_t col_block = (blockIdx.x / kc) % col_blocks;
+  const uint32_t col_blocks = out_plane / 128u;
+  const uint32_t item_index = blockIdx.x / col_blocks;
+  const uint32_t col_block = blockIdx.x % col_blocks;
 
   griddep_launch_dependents();
-  griddep_wait();  // the item list comes from the grouping kernels
+  griddep_wait();  // the item list and the fragments come from the kernels before
 
-  if (item_index >= *p.n_items) return;  // every CTA of a cluster shares the item: a uniform exit
+  if (item_index >= p.n_items[0]) return;
   const Item item = p.items[item_index];
   const ignis_moe_slot slot = p.slots[item.expert * 2u + PHASE];
   const uint32_t k2 = slot.k2;
   if (slot.record == nullptr || !(k2 == 4 || k2 == 5 || k2 == 6 || k2 == 8)) {
-    if (threadIdx.x == 0 && rank == 0 && col_block == 0) atomicOr(p.status, kStatusAbsentRecord);
-    return;  // uniform over the cluster as well
+    if (threadIdx.x == 0 && col_block == 0) atomicOr(p.status, kStatusAbsentRecord);
+    return;
   }
   const uint32_t *trellis = static_cast<const uint32_t *>(slot.record);
   const uint64_t trellis_bytes = static_cast<uint64_t>(in) * out_plane * k2 / 16u;
-  const uint16_t *suh = reinterpret_cast<const uint16_t *>(static_cast<const uint8_t *>(slot.record) + trellis_bytes);
-  const uint16_t *svh = suh + in;
-
-  constexpr int sides = PHASE == 0 ? 2 : 1;             // gate and up column blocks share one rotation
-  const int side = PHASE == 0 ? warp >> 2 : 0;
-  const int warps_per_side = PHASE == 0 ? 4 : 8;
-  const int wslot = PHASE == 0 ? (warp & 3) : warp;
-  const uint32_t side_col_block = col_block + (side == 1 ? p.inter / 128u : 0u);
-
+  const uint16_t *svh = reinterpret_cast<const uint16_t *>(static_cast<const uint8_t *>(slot.record) + trellis_bytes) + in;
   const uint32_t nblk = in / 128u;
-  const uint32_t b0 = static_cast<uint32_t>(static_cast<uint64_t>(nblk) * rank / kc);
-  const uint32_t b1 = static_cast<uint32_t>(static_cast<uint64_t>(nblk) * (rank + 1) / kc);
-  const uint32_t slice = b1 - b0;
+  const uint32_t ntiles = (item.count + 7u) / 8u;
+  const uint2 *frag = (PHASE == 0 ? p.frag_in : p.frag_h) + static_cast<size_t>(item.tile_first) * nblk * 256u;
+  const float2 *scales = (PHASE == 0 ? p.scale_in : p.scale_h) + static_cast<size_t>(item.tile_first) * nblk * 8u;
 
-  const size_t frag_bytes = static_cast<size_t>(p.slice_cap) * 2048u;
-  const size_t red_bytes = static_cast<size_t>(kWarps - sides) * 8 * 32 * 16;
-  const size_t region = frag_bytes > red_bytes ? frag_bytes : red_bytes;
-  uint2 *xs = reinterpret_cast<uint2 *>(smem_raw);
-  float4 *red = reinterpret_cast<float4 *>(smem_raw);
-  float4 *part = reinterpret_cast<float4 *>(smem_raw + region);
-  float *inv_s = reinterpret_cast<float *>(smem_raw + region + 2 * 8 * 32 * 16);
-  float *scale_s = inv_s + static_cast<size_t>(p.slice_cap) * 8;
-  __shared__ uint32_t row_assign[8];
-  if (threadIdx.x < 8) row_assign[threadIdx.x] = threadIdx.x < item.count ? p.sorted[item.first + threadIdx.x] : 0u;
-  __syncthreads();
-
-  // ---- rotate the item's rows into B fragments ----
+  float tot[NT][4];
+#pragma unroll
+  for (int tt = 0; tt < NT; ++tt)
+#pragma unroll
+    for (int e = 0; e < 4; ++e) tot[tt][e] = 0.0f;
   {
-    const uint32_t units = slice * 8u;
-    for (uint32_t u = static_cast<uint32_t>(warp); u < units; u += kWarps) {
-      const uint32_t r = u & 7u, bl = u >> 3;
-      float v[4] = {0.f, 0.f, 0.f, 0.f};
-      if (r < item.count) {
-        const size_t k0 = static_cast<size_t>(b0 + bl) * 128u + 4u * lane;
-        const uint2 sb = *reinterpret_cast<const uint2 *>(suh + k0);
-        const __half2 s01 = *reinterpret_cast<const __half2 *>(&sb.x), s23 = *reinterpret_cast<const __half2 *>(&sb.y);
-        if (PHASE == 0) {
-          const uint32_t token = row_assign[r] / p.top_k;
-          const uint2 xb = ldg64_coherent(p.x + static_cast<size_t>(token) * p.hidden + k0);
-          v[0] = bf16_bits_to_f32(xb.x & 0xFFFFu) * __low2float(s01);
-          v[1] = __uint_as_float(xb.x & 0xFFFF0000u) * __high2float(s01);
-          v[2] = bf16_bits_to_f32(xb.y & 0xFFFFu) * __low2float(s23);
-          v[3] = __uint_as_float(xb.y & 0xFFFF0000u) * __high2float(s23);
-        } else {
-          const uint4 hb = ldg128_coherent(p.h + static_cast<size_t>(item.first + r) * p.inter + k0);
-          v[0] = __uint_as_float(hb.x) * __low2float(s01);
-          v[1] = __uint_as_float(hb.y) * __high2float(s01);
-          v[2] = __uint_as_float(hb.z) * __low2float(s23);
-          v[3] = __uint_as_float(hb.w) * __high2float(s23);
-        }
-      }
-      hadamard128(v, lane);
-      float m = fmaxf(fmaxf(fabsf(v[0]), fabsf(v[1])), fmaxf(fabsf(v[2]), fabsf(v[3])));
-#pragma unroll
-      for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xFFFFFFFFu, m, o));
-      int shift = 0;
-      if (m > 0.0f && m <= 3.0e38f) {
-        int e;
-        (void)frexpf(m, &e);
-        shift = max(-126, min(126, 14 - e));
-      }
-      const float scale = ldexpf(1.0f, shift);
-      const __half2 h01 = __floats2half2_rn(v[0] * scale, v[1] * scale);
-      const __half2 h23 = __floats2half2_rn(v[2] * scale, v[3] * scale);
-      const int kt = lane >> 2, k16 = (lane & 3) * 4;
-      const int t_first = (k16 & 7) >> 1, reg = k16 >> 3;
-      uint32_t *dst = reinterpret_cast<uint32_t *>(xs + (static_cast<size_t>(bl) * 8 + kt) * 32 + r * 4);
-      dst[t_first * 2 + reg] = *reinterpret_cast<const uint32_t *>(&h01);
-      dst[(t_first + 1) * 2 + reg] = *reinterpret_cast<const uint32_t *>(&h23);
-      if (lane == 0) {
-        inv_s[bl * 8 + r] = r < item.count ? ldexpf(1.0f, -shift) : 0.0f;
-        scale_s[bl * 8 + r] = scale;
-      }
-    }
-  }
-  __syncthreads();
-
-  // ---- main loop ----
-  float tot[8][4];
-#pragma unroll
-  for (int j = 0; j < 8; ++j)
-#pragma unroll
-    for (int e = 0; e < 4; ++e) tot[j][e] = 0.0f;
-  {
-    const LaneWindow win = lane_window(k2, lane);
     const uint32_t tile_words = 4u * k2;
-    const uint32_t *col_base = trellis + static_cast<uint64_t>(side_col_block) * 8u * tile_words;
-    const uint64_t tk_stride = static_cast<uint64_t>(out_plane / 16u) * tile_words;
-    const uint32_t blk_first = b0 + static_cast<uint32_t>(wslot);
+    const uint32_t *tile_base = trellis + (static_cast<uint64_t>(col_block) * 8u + static_cast<uint32_t>(warp)) * tile_words;
+    const int64_t step_words = static_cast<int64_t>(out_plane / 16u) * tile_words;
     switch (k2) {
-      case 4: walk_blocks<4>(col_base, tk_stride, win, blk_first, b0, b1, warps_per_side, xs, inv_s, scale_s, lane, tot); break;
-      case 5: walk_blocks<5>(col_base, tk_stride, win, blk_first, b0, b1, warps_per_side, xs, inv_s, scale_s, lane, tot); break;
-      case 6: walk_blocks<6>(col_base, tk_stride, win, blk_first, b0, b1, warps_per_side, xs, inv_s, scale_s, lane, tot); break;
-      default: walk_blocks<8>(col_base, tk_stride, win, blk_first, b0, b1, warps_per_side, xs, inv_s, scale_s, lane, tot); break;
+      case 4: walk_tile_column<4, NT>(tile_base, step_words, nblk, frag, scales, ntiles, lane, frag_buf, scale_buf, tot); break;
+      case 5: walk_tile_column<5, NT>(tile_base, step_words, nblk, frag, scales, ntiles, lane, frag_buf, scale_buf, tot); break;
+      case 6: walk_tile_column<6, NT>(tile_base, step_words, nblk, frag, scales, ntiles, lane, frag_buf, scale_buf, tot); break;
+      default: walk_tile_column<8, NT>(tile_base, step_words, nblk, frag, scales, ntiles, lane, frag_buf, scale_buf, tot); break;
     }
   }
-
-  // ---- reduce the warps of each side, then the cluster ----
+  __syncthreads();  // every warp is done with the staging buffers: the partial sums take their place
+#pragma unroll
+  for (int tt = 0; tt < NT; ++tt) part[(warp * NT + tt) * 32 + lane] = make_float4(tot[tt][0], tot[tt][1], tot[tt][2], tot[tt][3]);
   __syncthreads();
-  if (wslot > 0) {
-    const int rslot = side * (warps_per_side - 1) + (wslot - 1);
-#pragma unroll
-    for (int j = 0; j < 8; ++j) red[(rslot * 8 + j) * 32 + lane] = make_float4(tot[j][0], tot[j][1], tot[j][2], tot[j][3]);
-  }
-  __syncthreads();
-  if (wslot == 0) {
-    for (int o = 1; o < warps_per_side; ++o) {
-      const int rslot = side * (warps_per_side - 1) + (o - 1);
-#pragma unroll
-      for (int j = 0; j < 8; ++j) {
-        const float4 v = red[(rslot * 8 + j) * 32 + lane];
-        tot[j][0] += v.x;
-        tot[j][1] += v.y;
-        tot[j][2] += v.z;
-        tot[j][3] += v.w;
-      }
-    }
-#pragma unroll
-    for (int j = 0; j < 8; ++j) part[(side * 8 + j) * 32 + lane] = make_float4(tot[j][0], tot[j][1], tot[j][2], tot[j][3]);
-  }
-  cluster_barrier();
 
-  // ---- the first CTA finishes: warp = row of the item, lane = 4 output columns ----
-  if (rank == 0 && static_cast<uint32_t>(warp) < item.count) {
-    const int r = warp, tq = r >> 1, te = r & 1;
-    float v[2][4];
+  // ---- finish: rows dealt to the warps; lane = 4 output columns of the block ----
+  for (uint32_t r = static_cast<uint32_t>(warp); r < item.count; r += kWarps) {
+    const uint32_t tt = r >> 3, rs = r & 7u;
+    const int tq = static_cast<int>(rs >> 1), te = static_cast<int>(rs & 1u);
+    float v[4];
 #pragma unroll
-    for (int sd = 0; sd < 2; ++sd)
-#pragma unroll
-      for (int i = 0; i < 4; ++i) v[sd][i] = 0.0f;
-#pragma unroll
-    for (int sd = 0; sd < sides; ++sd) {
-#pragma unroll
-      for (int i = 0; i < 4; ++i) {
-        const int c = 4 * lane + i, j = c >> 4, cc = c & 15;
-        const float *src = reinterpret_cast<const float *>(&part[(sd * 8 + j) * 32 + (cc & 7) * 4 + tq]) + te + 2 * (cc >> 3);
-        float sum = 0.0f;
-        for (uint32_t q = 0; q < kc; ++q) sum += ld_cluster_f32(src, q);
-        v[sd][i] = sum;
-      }
-      hadamard128(v[sd], lane);
-      const uint32_t plane_col = (col_block + (sd == 1 ? p.inter / 128u : 0u)) * 128u + 4u * lane;
-      const uint2 sv = *reinterpret_cast<const uint2 *>(svh + plane_col);
-      const __half2 s01 = *reinterpret_cast<const __half2 *>(&sv.x), s23 = *reinterpret_cast<const __half2 *>(&sv.y);
-      v[sd][0] *= __low2float(s01);
-      v[sd][1] *= __high2float(s01);
-      v[sd][2] *= __low2float(s23);
-      v[sd][3] *= __high2float(s23);
+    for (int i = 0; i < 4; ++i) {
+      const int c = 4 * lane + i, j = c >> 4, cc = c & 15;
+      v[i] = *(reinterpret_cast<const float *>(&part[(j * NT + tt) * 32 + (cc & 7) * 4 + tq]) + te + 2 * (cc >> 3));
     }
+    hadamard128(v, lane);
+    const uint2 sv = *reinterpret_cast<const uint2 *>(svh + static_cast<size_t>(col_block) * 128u + 4u * lane);
+    const __half2 s01 = *reinterpret_cast<const __half2 *>(&sv.x), s23 = *reinterpret_cast<const __half2 *>(&sv.y);
+    v[0] *= __low2float(s01);
+    v[1] *= __high2float(s01);
+    v[2] *= __low2float(s23);
+    v[3] *= __high2float(s23);
+    const uint32_t row = item.first + r;
     if (PHASE == 0) {
-      float4 o;
-      o.x = v[0][0] / (1.0f + __expf(-v[0][0])) * v[1][0];
-      o.y = v[0][1] / (1.0f + __expf(-v[0][1])) * v[1][1];
-      o.z = v[0][2] / (1.0f + __expf(-v[0][2])) * v[1][2];
-      o.w = v[0][3] / (1.0f + __expf(-v[0][3])) * v[1][3];
-      *reinterpret_cast<float4 *>(p.h + static_cast<size_t>(item.first + r) * p.inter + col_block * 128u + 4u * lane) = o;
+      *reinterpret_cast<float4 *>(p.gu + static_cast<size_t>(row) * 2u * p.inter + col_block * 128u + 4u * lane) =
+          make_float4(v[0], v[1], v[2], v[3]);
     } else {
-      const uint32_t a = row_assign[r];
+      const uint32_t a = p.sorted[row];
       const uint32_t token = a / p.top_k;
       const float wr = p.weights[a];
       long long *dst = p.acc + static_cast<size_t>(token) * p.hidden + col_block * 128u + 4u * lane;
 #pragma unroll
       for (int i = 0; i < 4; ++i) {
-        const float c = wr * v[0][i];
+        const float c = wr * v[i];
         if (!(fabsf(c) < 2147483648.0f)) {  // also catches NaN
           atomicOr(p.status, kStatusRange);
         } else {
@@ -342,13 +448,6 @@ __global__ void __launch_bounds__(kThreads, 2) moe_experts_kernel(const __grid_c
       }
     }
   }
-  cluster_barrier();
-}
-
-size_t experts_smem_bytes(uint32_t slice_cap, int sides) {
-  const size_t frag_bytes = static_cast<size_t>(slice_cap) * 2048u;
-  const size_t red_bytes = static_cast<size_t>(kWarps - sides) * 8 * 32 * 16;
-  return (frag_bytes > red_bytes ? frag_bytes : red_bytes) + 2 * 8 * 32 * 16 + static_cast<size_t>(slice_cap) * 8 * 4 * 2;
 }
 
 // ---- router ----------------------------------------------------------------------------------
@@ -494,6 +593,93 @@ __global__ void __launch_bounds__(256) moe_fp8_rows_kernel(const uint8_t *w0, co
   }
 }
 
+// Two E4M3 codes (the low 16 bits of `pair`) as BF16 x 2, exactly: every E4M3 value has a BF16.
+__device__ __forceinline__ uint32_t e4m3x2_to_bf16x2(uint32_t pair) {
+  const uint32_t h = e4m3x2_to_half2(pair);
+  const float2 f = __half22float2(*reinterpret_cast<const __half2 *>(&h));
+  const __nv_bfloat162 b = __floats2bfloat162_rn(f.x, f.y);
+  return *reinterpret_cast<const uint32_t *>(&b);
+}
+
+// The same products for many tokens, on the tensor cores: a warp owns 16 weight rows (of both
+// weights in MODE 0) and 64 tokens, a CTA 128 rows. Weights are widened E4M3 -> BF16 (exact) into A
+// fragments, the activations are the B fragments as they lie in memory: inside a chunk of 64
+// columns the MMA's k slots are dealt so that a lane needs 16 contiguous codes of its two rows
+// and 16 contiguous activations of its token. FP32 accumulation, the row scale applied at the end.
+template <int MODE>
+__global__ void __launch_bounds__(256) moe_fp8_gemm_kernel(const uint8_t *w0, const uint8_t *w1, uint32_t rows, uint32_t cols,
+                                                           const uint16_t *x, uint32_t tokens, void *y) {
+  griddep_launch_dependents();
+  griddep_wait();
+  constexpr int S = MODE == 0 ? 2 : 1;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
+  const uint32_t row0 = (blockIdx.x * 8u + static_cast<uint32_t>(warp)) * 16u;
+  const uint32_t tok0 = blockIdx.y * 64u;
+  if (row0 >= rows) return;
+  const uint8_t *weights[2] = {w0, w1};
+  float acc[S][8][4];
+#pragma unroll
+  for (int s = 0; s < S; ++s)
+#pragma unroll
+    for (int nt = 0; nt < 8; ++nt)
+#pragma unroll
+      for (int e = 0; e < 4; ++e) acc[s][nt][e] = 0.0f;
+  for (uint32_t kb = 0; kb < cols; kb += 64) {
+    uint32_t a[S][4][4];  // [weight][MMA j][a0..a3]
+#pragma unroll
+    for (int s = 0; s < S; ++s) {
+#pragma unroll
+      for (int half = 0; half < 2; ++half) {
+        const uint4 cw = *reinterpret_cast<const uint4 *>(weights[s] + static_cast<uint64_t>(row0 + g + 8 * half) * cols + kb + 16 * t);
+        const uint32_t w[4] = {cw.x, cw.y, cw.z, cw.w};
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          a[s][j][half] = e4m3x2_to_bf16x2(w[j] & 0xFFFFu);      // k slots 2t, 2t + 1
+          a[s][j][2 + half] = e4m3x2_to_bf16x2(w[j] >> 16);       // k slots 2t + 8, 2t + 9
+        }
+      }
+    }
+#pragma unroll
+    for (int nt = 0; nt < 8; ++nt) {
+      const uint32_t token = tok0 + nt * 8 + g;
+      uint4 x0 = make_uint4(0u, 0u, 0u, 0u), x1 = x0;
+      if (token < tokens) {
+        const uint4 *src = reinterpret_cast<const uint4 *>(x + static_cast<uint64_t>(token) * cols + kb + 16 * t);
+        x0 = ldg128_coherent(src);
+        x1 = ldg128_coherent(src + 1);
+      }
+      const uint32_t b[8] = {x0.x, x0.y, x0.z, x0.w, x1.x, x1.y, x1.z, x1.w};
+#pragma unroll
+      for (int j = 0; j < 4; ++j)
+#pragma unroll
+        for (int s = 0; s < S; ++s) mma_bf16_f32(acc[s][nt], a[s][j][0], a[s][j][1], a[s][j][2], a[s][j][3], b[2 * j], b[2 * j + 1]);
+    }
+  }
+  const uint64_t scale_off = (static_cast<uint64_t>(rows) * cols + 255u) & ~static_cast<uint64_t>(255u);
+  float sc[S][2];
+#pragma unroll
+  for (int s = 0; s < S; ++s)
+#pragma unroll
+    for (int half = 0; half < 2; ++half)
+      sc[s][half] = bf16_bits_to_f32(reinterpret_cast<const uint16_t *>(weights[s] + scale_off)[row0 + g + 8 * half]);
+#pragma unroll
+  for (int nt = 0; nt < 8; ++nt) {
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      const uint32_t token = tok0 + nt * 8 + 2 * t + (e & 1);
+      const int half = e >> 1;
+      if (token >= tokens) continue;
+      const uint64_t at = static_cast<uint64_t>(token) * rows + row0 + g + 8 * half;
+      if (MODE == 0) {
+        const float gv = acc[0][nt][e] * sc[0][half], uv = acc[S - 1][nt][e] * sc[S - 1][half];
+        static_cast<__nv_bfloat16 *>(y)[at] = __float2bfloat16_rn(gv / (1.0f + __expf(-gv)) * uv);
+      } else {
+        static_cast<float *>(y)[at] = acc[0][nt][e] * sc[0][half];
+      }
+    }
+  }
+}
+
 // One CTA per token: out = BF16(acc * 2^-32 + sigmoid(x . w_gate) * shared), acc zeroed behind it.
 __global__ void __launch_bounds__(256) moe_combine_kernel(long long *acc, const float *shared, const uint16_t *x,
                                                           const uint16_t *w_gate, uint32_t hidden, uint16_t *out) {
@@ -534,7 +720,8 @@ const DeviceState *prepared(ErrorSlot &slot, const char *what) {
 }
 
 int32_t run_experts(const void *x, uint32_t tokens, const int32_t *ids, const float *weights, const ignis_moe_slot *slots,
-                    const ignis_moe_workspace *workspace, int64_t *acc, void *stream_v, uint32_t limit, const char *what) {
+                    const ignis_moe_workspace *workspace, int64_t *acc, void *stream_v, uint32_t limit, uint32_t item_rows,
+                    const char *what) {
   ErrorSlot &slot = moe_error();
   if (x == nullptr || ids == nullptr || weights == nullptr || slots == nullptr || workspace == nullptr || acc == nullptr ||
       workspace->base == nullptr) {
@@ -562,51 +749,47 @@ int32_t run_experts(const void *x, uint32_t tokens, const int32_t *ids, const fl
   const bool pdl = dev->pdl != 0;
   const uint32_t grid_rows = (rows + 255u) / 256u < 1184u ? (rows + 255u) / 256u : 1184u;
   err = launch(moe_count_kernel, dim3(grid_rows), dim3(256), 0, stream, false, ids, rows, g.experts, counts, status);
-  if (err == cudaSuccess) err = launch(moe_scan_kernel, dim3(1), dim3(1024), 0, stream, pdl, static_cast<const uint32_t *>(counts), g.experts, offsets, n_items, items);
+  if (err == cudaSuccess) err = launch(moe_scan_kernel, dim3(1), dim3(1024), 0, stream, pdl, static_cast<const uint32_t *>(counts), g.experts, item_rows, offsets, n_items, items, reinterpret_cast<Tile *>(base + l.tiles));
   if (err == cudaSuccess) err = launch(moe_scatter_kernel, dim3(grid_rows), dim3(256), 0, stream, pdl, ids, rows, g.experts, static_cast<const uint32_t *>(offsets), cursor, sorted);
   if (err != cudaSuccess) return fail(slot, "%s: grouping launch failed: %s", what, cudaGetErrorString(err));
 
   ExpertParams p = {};
   p.slots = slots;
   p.items = items;
+  p.tiles = reinterpret_cast<const Tile *>(base + l.tiles);
   p.n_items = n_items;
   p.sorted = sorted;
   p.x = static_cast<const uint16_t *>(x);
   p.weights = weights;
-  p.h = reinterpret_cast<float *>(base + l.h);
+  p.frag_in = reinterpret_cast<uint2 *>(base + l.frag_in);
+  p.scale_in = reinterpret_cast<float2 *>(base + l.scale_in);
+  p.gu = reinterpret_cast<float *>(base + l.gu);
+  p.frag_h = reinterpret_cast<uint2 *>(base + l.frag_h);
+  p.scale_h = reinterpret_cast<float2 *>(base + l.scale_h);
   p.acc = reinterpret_cast<long long *>(acc);
   p.status = status;
   p.hidden = g.hidden;
   p.inter = g.inter;
   p.top_k = g.top_k;
   p.experts = g.experts;
-  const uint32_t items_max = (rows + 7u) / 8u + (g.experts < rows ? g.experts : rows);
+  // Grids are sized for the worst case the host can know (the grouping happened on the device);
+  // CTAs beyond the item or tile count return at once.
+  const uint32_t items_max = items_bound(g, rows, item_rows);
+  const uint32_t tiles_max = items_bound(g, rows, 8u);
+  const bool wide = item_rows > 8u;
   for (int phase = 0; phase < 2; ++phase) {
-    const uint32_t in = phase == 0 ? g.hidden : g.inter;
-    const uint32_t col_blocks = (phase == 0 ? g.inter : g.hidden) / 128u;
-    const uint32_t warps = phase == 0 ? 4u : 8u;
-    const uint32_t nblk = in / 128u;
-    uint32_t kc = (nblk + 2u * warps - 1u) / (2u * warps);  // about two blocks per warp
-    if (kc < 1u) kc = 1u;
-    if (kc > 8u) kc = 8u;
-    p.kc = kc;
-    p.slice_cap = (nblk + kc - 1u) / kc;
-    const size_t smem = experts_smem_bytes(p.slice_cap, phase == 0 ? 2 : 1);
-    cudaLaunchConfig_t config = {};
-    config.gridDim = dim3(items_max * col_blocks * kc, 1, 1);
-    config.blockDim = dim3(kThreads, 1, 1);
-    config.dynamicSmemBytes = smem;
-    config.stream = stream;
-    cudaLaunchAttribute attr[2];
-    attr[0].id = cudaLaunchAttributeClusterDimension;
-    attr[0].val.clusterDim.x = kc;
-    attr[0].val.clusterDim.y = 1;
-    attr[0].val.clusterDim.z = 1;
-    attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-    attr[1].val.programmaticStreamSerializationAllowed = 1;
-    config.attrs = attr;
-    config.numAttrs = pdl ? 2 : 1;
-    err = phase == 0 ? cudaLaunchKernelEx(&config, moe_experts_kernel<0>, p) : cudaLaunchKernelEx(&config, moe_experts_kernel<1>, p);
+    const uint32_t col_blocks = (phase == 0 ? 2u * g.inter : g.hidden) / 128u;
+    err = phase == 0 ? launch(moe_rotate_kernel<0>, dim3(tiles_max), dim3(kThreads), 0, stream, pdl, p)
+                     : launch(moe_rotate_kernel<1>, dim3(tiles_max), dim3(kThreads), 0, stream, pdl, p);
+    if (err != cudaSuccess) return fail(slot, "%s: rotation launch failed: %s", what, cudaGetErrorString(err));
+    const dim3 grid(items_max * col_blocks);
+    if (phase == 0) {
+      err = wide ? launch(moe_experts_kernel<0, 8>, grid, dim3(kThreads), 0, stream, pdl, p)
+                 : launch(moe_experts_kernel<0, 1>, grid, dim3(kThreads), 0, stream, pdl, p);
+    } else {
+      err = wide ? launch(moe_experts_kernel<1, 8>, grid, dim3(kThreads), 0, stream, pdl, p)
+                 : launch(moe_experts_kernel<1, 1>, grid, dim3(kThreads), 0, stream, pdl, p);
+    }
     if (err != cudaSuccess) return fail(slot, "%s: expert launch failed: %s", what, cudaGetErrorString(err));
   }
   return 0;
@@ -654,9 +837,7 @@ int32_t ignis_moe_trellis_reconstruct(const void *trellis, uint32_t k2, uint32_t
 int32_t ignis_moe_prepare(void) {
   ErrorSlot &slot = moe_error();
   if (prepare_device(slot) != 0) return -1;
-  cudaError_t err = cudaFuncSetAttribute(moe_experts_kernel<0>, cudaFuncAttributeMaxDynamicSharedMemorySize, 100 * 1024);
-  if (err == cudaSuccess) err = cudaFuncSetAttribute(moe_experts_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, 100 * 1024);
-  if (err == cudaSuccess) err = cudaFuncSetAttribute(moe_router_logits_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024);
+  cudaError_t err = cudaFuncSetAttribute(moe_router_logits_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024);
   if (err != cudaSuccess) return fail(slot, "ignis_moe_prepare: %s", cudaGetErrorString(err));
   return 0;
 }
@@ -726,14 +907,14 @@ int32_t ignis_moe_experts_decode(const void *x, uint32_t tokens, const int32_t *
                                  const struct ignis_moe_slot *slots, const struct ignis_moe_workspace *workspace,
                                  int64_t *acc, void *stream) {
   const uint32_t limit = workspace != nullptr ? workspace->decode_tokens : 0u;
-  return run_experts(x, tokens, ids, weights, slots, workspace, acc, stream, limit, "ignis_moe_experts_decode");
+  return run_experts(x, tokens, ids, weights, slots, workspace, acc, stream, limit, 8u, "ignis_moe_experts_decode");
 }
 
 int32_t ignis_moe_experts_prefill(const void *x, uint32_t tokens, const int32_t *ids, const float *weights,
                                   const struct ignis_moe_slot *slots, const struct ignis_moe_workspace *workspace,
                                   int64_t *acc, void *stream) {
   const uint32_t limit = workspace != nullptr ? workspace->prefill_tokens : 0u;
-  return run_experts(x, tokens, ids, weights, slots, workspace, acc, stream, limit, "ignis_moe_experts_prefill");
+  return run_experts(x, tokens, ids, weights, slots, workspace, acc, stream, limit, tokens > 8u ? 64u : 8u, "ignis_moe_experts_prefill");
 }
 
 int32_t ignis_moe_decode_cluster_size(void) { return 0; }
@@ -751,13 +932,26 @@ int32_t ignis_moe_shared_expert(const void *gate, const void *up, const void *do
   const DeviceState *dev = prepared(slot, "ignis_moe_shared_expert");
   if (dev == nullptr) return -1;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
-  cudaError_t err = launch(moe_fp8_rows_kernel<0>, dim3((g_geo.inter + 7u) / 8u), dim3(256), 0, s, dev->pdl != 0,
-                           static_cast<const uint8_t *>(gate), static_cast<const uint8_t *>(up), g_geo.inter, g_geo.hidden,
-                           static_cast<const uint16_t *>(x), tokens, h);
-  if (err == cudaSuccess) {
-    err = launch(moe_fp8_rows_kernel<1>, dim3((g_geo.hidden + 7u) / 8u), dim3(256), 0, s, dev->pdl != 0,
-                 static_cast<const uint8_t *>(down), static_cast<const uint8_t *>(down), g_geo.hidden, g_geo.inter,
-                 static_cast<const uint16_t *>(h), tokens, static_cast<void *>(shared));
+  cudaError_t err;
+  if (tokens > 8u) {  // many tokens: the tensor-core form, 64 tokens a CTA
+    const uint32_t token_blocks = (tokens + 63u) / 64u;
+    err = launch(moe_fp8_gemm_kernel<0>, dim3((g_geo.inter + 127u) / 128u, token_blocks), dim3(256), 0, s, dev->pdl != 0,
+                 static_cast<const uint8_t *>(gate), static_cast<const uint8_t *>(up), g_geo.inter, g_geo.hidden,
+                 static_cast<const uint16_t *>(x), tokens, h);
+    if (err == cudaSuccess) {
+      err = launch(moe_fp8_gemm_kernel<1>, dim3((g_geo.hidden + 127u) / 128u, token_blocks), dim3(256), 0, s, dev->pdl != 0,
+                   static_cast<const uint8_t *>(down), static_cast<const uint8_t *>(down), g_geo.hidden, g_geo.inter,
+                   static_cast<const uint16_t *>(h), tokens, static_cast<void *>(shared));
+    }
+  } else {
+    err = launch(moe_fp8_rows_kernel<0>, dim3((g_geo.inter + 7u) / 8u), dim3(256), 0, s, dev->pdl != 0,
+                 static_cast<const uint8_t *>(gate), static_cast<const uint8_t *>(up), g_geo.inter, g_geo.hidden,
+                 static_cast<const uint16_t *>(x), tokens, h);
+    if (err == cudaSuccess) {
+      err = launch(moe_fp8_rows_kernel<1>, dim3((g_geo.hidden + 7u) / 8u), dim3(256), 0, s, dev->pdl != 0,
+                   static_cast<const uint8_t *>(down), static_cast<const uint8_t *>(down), g_geo.hidden, g_geo.inter,
+                   static_cast<const uint16_t *>(h), tokens, static_cast<void *>(shared));
+    }
   }
   if (err != cudaSuccess) return fail(slot, "ignis_moe_shared_expert: launch failed: %s", cudaGetErrorString(err));
   return 0;

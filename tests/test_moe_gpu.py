@@ -81,7 +81,8 @@ def check_tokens(acc: torch.Tensor, ref: np.ndarray):
         assert l2 <= 2e-3 and linf <= 1e-2, (t, l2, linf)
 
 
-@pytest.mark.parametrize("hidden,inter,experts,top_k,tokens", [(256, 128, 8, 2, 5), (512, 256, 16, 4, 19), (1024, 128, 32, 3, 40)])
+@pytest.mark.parametrize("hidden,inter,experts,top_k,tokens", [(256, 128, 8, 2, 5), (512, 256, 16, 4, 19), (1024, 128, 32, 3, 40),
+                                                                (256, 128, 4, 2, 150), (384, 256, 3, 1, 77)])
 def test_experts_small_geometries(mo, oracle, hidden, inter, experts, top_k, tokens):
     mo.set_geometry(hidden, inter, experts, top_k)
     rng = np.random.default_rng(hidden + tokens)
@@ -156,10 +157,11 @@ def test_router_matches_a_torch_model(mo):
     del order
 
 
-def test_shared_expert_and_combine(mo):
+@pytest.mark.parametrize("tokens", [5, 11, 130])   # up to 8: one warp per row; above: the tensor-core form, ragged token tiles
+def test_shared_expert_and_combine(mo, tokens):
     mo.set_geometry(256, 128, 8, 2)
     gen = torch.Generator().manual_seed(4)
-    x = torch.randn(11, 256, generator=gen).to(torch.bfloat16)
+    x = torch.randn(tokens, 256, generator=gen).to(torch.bfloat16)
     wg, wu = torch.randn(128, 256, generator=gen) * 0.05, torch.randn(128, 256, generator=gen) * 0.05
     wd = torch.randn(256, 128, generator=gen) * 0.05
     pg, pu, pd = (torch.from_numpy(mo.fp8_row_scale_payload(w)).cuda() for w in (wg, wu, wd))
@@ -179,15 +181,15 @@ def test_shared_expert_and_combine(mo):
     s_ref = h.cpu().double() @ deq(pd, 256, 128).T
     assert torch.allclose(shared.cpu().double(), s_ref, rtol=1e-4, atol=1e-5)
     # combine: out = BF16(acc * 2^-32 + sigmoid(x . w_gate) * shared), acc zeroed behind it
-    ws = mo.Workspace(8, 11)
-    routed = torch.randn(11, 256, generator=gen).double()
-    ws.acc[:11] = torch.round(routed * 2.0 ** 32).to(torch.int64).cuda()
+    ws = mo.Workspace(8, tokens)
+    routed = torch.randn(tokens, 256, generator=gen).double()
+    ws.acc[:tokens] = torch.round(routed * 2.0 ** 32).to(torch.int64).cuda()
     w_gate = (torch.randn(256, generator=gen) * 0.1).to(torch.bfloat16)
     out = mo.combine(ws, shared, x.cuda(), w_gate.cuda())
     gate = torch.sigmoid(x.double() @ w_gate.double())
     want = routed + gate.unsqueeze(1) * shared.cpu().double()
     assert torch.allclose(out.cpu().double(), want, rtol=2 ** -7, atol=1e-3)
-    assert int(ws.acc[:11].abs().sum().item()) == 0
+    assert int(ws.acc[:tokens].abs().sum().item()) == 0
 
 
 def test_plan_record_bytes_and_reconstruct(mo, oracle, golden):
