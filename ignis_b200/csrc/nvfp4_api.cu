@@ -96,7 +96,7 @@ int32_t linear_group_impl(const b200q_nvfp4_weight *const *w, uint32_t count, co
   // Wide calls under B200Q_NVFP4_ALLOW_A4 quantize the activations and take the tensor-core route
   // (the reference's AllowA4 resolution, nvfp4_dispatch.cpp:31-39, with one threshold); everything
   // else takes the decode route, which re-reads the weights once per 32 tokens.
-  if (policy == B200Q_NVFP4_ALLOW_A4 && tokens > B200Q_NVFP4_DECODE_MAX_TOKENS && count == 1 && !swiglu &&
+  if (policy == B200Q_NVFP4_ALLOW_A4 && tokens > B200Q_NVFP4_DECODE_MAX_TOKENS && count == 1 &&
       (epilogue & kEpilogueAdd) == 0u && w4a4_shape_ok(w[0]->n, w[0]->k)) {
     const b200q_nvfp4_weight *w0 = w[0];
     if (!std::isfinite(w0->input_scale_divisor) || !(w0->input_scale_divisor > 0.0f)) {

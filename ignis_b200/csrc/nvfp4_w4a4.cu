@@ -154,6 +154,19 @@ __device__ __forceinline__ void mma_commit(uint32_t bar) {
   asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
 }
 
+// 32 consecutive accumulator columns of this thread's lane (32x32b: one column per register).
+__device__ __forceinline__ void tmem_ld32(uint32_t addr, uint32_t (&r)[32]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
+        "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
+        "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(addr)
+      : "memory");
+}
+
 struct W4A4Params {
   const uint8_t *sfa;   // activation scales, tile order
   const uint8_t *sfb;   // weight scales, tile order
@@ -161,7 +174,7 @@ struct W4A4Params {
   uint32_t *status;
   uint32_t tokens, n, k, ldy;
   float alpha;
-  uint32_t epilogue;
+  uint32_t epilogue;  // STORE / OUT_F32, or the fused SwiGLU (the tile's columns 0..127 are gate rows, 128..255 the up rows)
 };
 
 __global__ void __launch_bounds__(192, 1) w4a4_gemm_kernel(const __grid_constant__ CUtensorMap map_a,
@@ -177,7 +190,13 @@ __global__ void __launch_bounds__(192, 1) w4a4_gemm_kernel(const __grid_constant
   const uint32_t m_tile = blockIdx.x, n_tile = blockIdx.y;
   const uint32_t k_iters = p.k / 256u;
   const uint32_t k_atoms = p.k / 64u;
-  const bool second_half = (n_tile * 2u + 1u) * 128u < p.n;  // the tile's rows 128..255 exist
+  // The tile's 256 weight rows are two boxes of 128: rows [row_a, +128) and [row_b, +128). A plain
+  // product takes consecutive boxes; the fused SwiGLU pairs 128 gate rows with their up rows, which
+  // lie n / 2 further down the fused parent.
+  const bool swiglu = (p.epilogue & kEpilogueSwiglu) != 0u;
+  const uint32_t row_a = swiglu ? n_tile * 128u : n_tile * kBN;
+  const uint32_t row_b = swiglu ? p.n / 2u + n_tile * 128u : n_tile * kBN + 128u;
+  const bool second_half = row_b < p.n;  // the tile's second box exists
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < kStages; ++s) {
@@ -210,14 +229,18 @@ __global__ void __launch_bounds__(192, 1) w4a4_gemm_kernel(const __grid_constant
       }
       const uint32_t full = bars + 8 * s;
       const uint32_t stage = base + s * kStageBytes;
-      mbar_expect_tx(full, kABytes + kBBytes + kSfaBytes + (second_half ? kSfbBytes : kSfbBytes / 2));
+      mbar_expect_tx(full, kABytes + kSfaBytes + (second_half ? kBBytes + kSfbBytes : (kBBytes + kSfbBytes) / 2));
       tma_load_2d(stage, &map_a, full, static_cast<int32_t>(it * kBKBytes), static_cast<int32_t>(m_tile * kBM));
-      tma_load_2d(stage + kABytes, &map_b, full, static_cast<int32_t>(it * kBKBytes), static_cast<int32_t>(n_tile * kBN));
-      bulk_load(stage + kABytes + kBBytes, p.sfa + (static_cast<uint64_t>(m_tile) * k_atoms + it * 4u) * 512u, kSfaBytes, full);
-      const uint8_t *sfb0 = p.sfb + (static_cast<uint64_t>(n_tile * 2u) * k_atoms + it * 4u) * 512u;
-      bulk_load(stage + kABytes + kBBytes + kSfaBytes, sfb0, kSfbBytes / 2, full);
+      tma_load_2d(stage + kABytes, &map_b, full, static_cast<int32_t>(it * kBKBytes), static_cast<int32_t>(row_a));
       if (second_half) {
-        bulk_load(stage + kABytes + kBBytes + kSfaBytes + kSfbBytes / 2, sfb0 + static_cast<uint64_t>(k_atoms) * 512u, kSfbBytes / 2, full);
+        tma_load_2d(stage + kABytes + kBBytes / 2, &map_b, full, static_cast<int32_t>(it * kBKBytes), static_cast<int32_t>(row_b));
+      }
+      bulk_load(stage + kABytes + kBBytes, p.sfa + (static_cast<uint64_t>(m_tile) * k_atoms + it * 4u) * 512u, kSfaBytes, full);
+      bulk_load(stage + kABytes + kBBytes + kSfaBytes, p.sfb + (static_cast<uint64_t>(row_a / 128u) * k_atoms + it * 4u) * 512u,
+                kSfbBytes / 2, full);
+      if (second_half) {
+        bulk_load(stage + kABytes + kBBytes + kSfaBytes + kSfbBytes / 2,
+                  p.sfb + (static_cast<uint64_t>(row_b / 128u) * k_atoms + it * 4u) * 512u, kSfbBytes / 2, full);
       }
     }
   } else if (warp == 5 && lane == 0) {
@@ -260,18 +283,41 @@ __global__ void __launch_bounds__(192, 1) w4a4_gemm_kernel(const __grid_constant
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
       const uint32_t token = m_tile * kBM + warp * 32 + lane;
       const uint32_t lane_base = tmem + (static_cast<uint32_t>(warp * 32) << 16);
+      if (swiglu) {
+        // h = BF16(silu(BF16(g alpha)) * BF16(u alpha)): gate in accumulator columns 0..127, up in 128..255
+#pragma unroll 1
+        for (uint32_t c = 0; c < 128u; c += 32) {
+          uint32_t g[32], u[32];
+          tmem_ld32(lane_base + c, g);
+          tmem_ld32(lane_base + 128u + c, u);
+          asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+          const uint32_t col0 = n_tile * 128u + c;
+          if (token < p.tokens && col0 < p.n / 2u) {
+            uint4 *dst = reinterpret_cast<uint4 *>(static_cast<__nv_bfloat16 *>(p.y) + static_cast<size_t>(token) * p.ldy + col0);
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              uint32_t o[4];
+#pragma unroll
+              for (int e = 0; e < 4; ++e) {
+                float h2[2];
+#pragma unroll
+                for (int i = 0; i < 2; ++i) {
+                  const float gv = __bfloat162float(__float2bfloat16_rn(__uint_as_float(g[8 * j + 2 * e + i]) * p.alpha));
+                  const float uv = __bfloat162float(__float2bfloat16_rn(__uint_as_float(u[8 * j + 2 * e + i]) * p.alpha));
+                  h2[i] = gv / (1.0f + __expf(-gv)) * uv;
+                }
+                const __nv_bfloat162 h = __floats2bfloat162_rn(h2[0], h2[1]);
+                o[e] = *reinterpret_cast<const uint32_t *>(&h);
+              }
+              dst[j] = make_uint4(o[0], o[1], o[2], o[3]);
+            }
+          }
+        }
+      } else {
 #pragma unroll 1
       for (uint32_t c = 0; c < kBN; c += 32) {
         uint32_t r[32];
-        asm volatile(
-            "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
-            "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
-            : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
-              "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
-              "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
-              "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
-            : "r"(lane_base + c)
-            : "memory");
+        tmem_ld32(lane_base + c, r);
         asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
         const uint32_t row0 = n_tile * kBN + c;
         if (token < p.tokens && row0 < p.n) {  // n is a multiple of 128, so a 32-row chunk is whole
@@ -297,6 +343,7 @@ __global__ void __launch_bounds__(192, 1) w4a4_gemm_kernel(const __grid_constant
             }
           }
         }
+      }
       }
     } else if (lane == 0) {
       atomicOr(p.status, kStatusEpilogueTimeout);
@@ -375,7 +422,7 @@ int32_t w4a4_launch(ErrorSlot &slot, const DeviceState &dev, const uint8_t *w_co
     if (err != cudaSuccess) return fail(slot, "nvfp4 activation quantizer launch: %s", cudaGetErrorString(err));
   }
   CUtensorMap map_a, map_b;
-  if (!make_code_map(&map_a, a_codes, pad, k / 2u, kBM) || !make_code_map(&map_b, w_codes, n, k / 2u, kBN)) {
+  if (!make_code_map(&map_a, a_codes, pad, k / 2u, kBM) || !make_code_map(&map_b, w_codes, n, k / 2u, 128u)) {
     return fail(slot, "nvfp4 prefill: tensor map encoding failed");
   }
   W4A4Params p = {};
@@ -389,7 +436,8 @@ int32_t w4a4_launch(ErrorSlot &slot, const DeviceState &dev, const uint8_t *w_co
   p.ldy = ldy;
   p.alpha = 1.0f / (d_in * d_w);
   p.epilogue = epilogue;
-  const dim3 grid(pad / kBM, (n + kBN - 1) / kBN, 1);
+  const bool swiglu = (epilogue & kEpilogueSwiglu) != 0u;
+  const dim3 grid(pad / kBM, swiglu ? n / 256u : (n + kBN - 1) / kBN, 1);
   const cudaError_t err = launch(w4a4_gemm_kernel, grid, dim3(192), kSmemBytes, stream, dev.pdl != 0, map_a, map_b, p);
   if (err != cudaSuccess) return fail(slot, "nvfp4 prefill launch: %s", cudaGetErrorString(err));
   return 0;

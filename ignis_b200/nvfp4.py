@@ -214,14 +214,17 @@ def linear_group(x: torch.Tensor, weights: list[Weight], outs: list[torch.Tensor
     return ys
 
 
-def linear_swiglu(x: torch.Tensor, gate_up: Weight, out: torch.Tensor | None = None, policy: int = A16_ONLY) -> torch.Tensor:
-    """``h[t, c] = silu(g) * u`` over the fused gate_up parent: ninfer::ops::linear_swiglu."""
+def linear_swiglu(x: torch.Tensor, gate_up: Weight, out: torch.Tensor | None = None, policy: int = A16_ONLY,
+                  workspace: Workspace | None = None) -> torch.Tensor:
+    """``h[t, c] = silu(g) * u`` over the fused gate_up parent: ninfer::ops::linear_swiglu. Under
+    ``ALLOW_A4`` wide calls take the tensor-core route with the SwiGLU in its epilogue
+    (prefill_swiglu::gate_up_swiglu, kernel/src/prefill_swiglu.h:73-107) and need `workspace`."""
     _check_x(x, gate_up.k)
     tokens = x.shape[0]
     h = _out(tokens, gate_up.n // 2, STORE, out, x.device)
     ws = gate_up.c_struct()
-    _check(_lib.load().b200q_nvfp4_linear_swiglu(C.byref(ws), x.data_ptr(), tokens, h.data_ptr(), h.stride(0), policy, None,
-                                                  _stream()))
+    _check(_lib.load().b200q_nvfp4_linear_swiglu(C.byref(ws), x.data_ptr(), tokens, h.data_ptr(), h.stride(0), policy,
+                                                  C.byref(workspace.c) if workspace is not None else None, _stream()))
     return h
 
 

@@ -319,6 +319,34 @@ def w4a4_reference(oracle, codes, scales, n, k, d_w, d_in, x_bf16: torch.Tensor)
     return oracle.nvfp4_w4a4_gemm(codes, scales, n, k, d_w, a_codes, a_scales, d_in)
 
 
+def test_w4a4_fused_swiglu(nv, oracle):
+    """The wide SwiGLU call under ALLOW_A4: gate rows [0, n/2) and up rows [n/2, n) of the fused
+    parent meet in one tensor-core tile; h = BF16(silu(BF16(g)) * BF16(u)) as the reference's
+    prefill epilogue rounds (kernel/src/prefill_swiglu.h:73-107). n/2 = 384 makes the last tile
+    pair ragged in neither half; 100 tokens leave a ragged token tile."""
+    tokens, n, k = 100, 768, 512
+    rng = np.random.default_rng(99)
+    codes, scales, d_w = make_weight(rng, n, k)
+    d_in = 448.0
+    w = nv.Weight.from_planes(codes, scales, d_w, d_in)
+    x = torch.randn(tokens, k, generator=torch.Generator().manual_seed(99)).to(torch.bfloat16)
+    ref = w4a4_reference(oracle, codes, scales, n, k, d_w, d_in, x)          # [tokens, n] in fp64
+    g = torch.from_numpy(ref[:, : n // 2]).to(torch.bfloat16).double()
+    u = torch.from_numpy(ref[:, n // 2:]).to(torch.bfloat16).double()
+    want = (g / (1 + torch.exp(-g)) * u).numpy()
+    ws = nv.Workspace(nv.workspace_bytes(n, k, nv.ALLOW_A4, tokens))
+    h = nv.linear_swiglu(x.cuda(), w, policy=nv.ALLOW_A4, workspace=ws)
+    assert ws.status() == 0 and h.shape == (tokens, n // 2)
+    got = h.double().cpu().numpy()
+    # a BF16 rounding of g or u on the other side of a tie moves h by up to 2^-8 of its factors
+    scale = np.abs(want).max()
+    assert np.all(np.abs(got - want) <= 2.0 ** -6 * np.abs(want) + 2e-3 * scale)
+    assert np.linalg.norm(got - want) <= 2.0 ** -7 * np.linalg.norm(want)
+    # the decode route computes the same function from unquantized activations: inside the A4 allowance
+    h16 = nv.linear_swiglu(x.cuda(), w).double().cpu().numpy()
+    assert np.linalg.norm(got - h16) <= 0.2 * np.linalg.norm(h16)
+
+
 @pytest.mark.parametrize("tokens,n,k", [(128, 256, 256), (200, 256, 512), (33, 128, 1024), (300, 384, 768), (256, 512, 2048)])
 def test_w4a4_tensor_core_route(nv, oracle, tokens, n, k):
     rng = np.random.default_rng(tokens + n + k)
