@@ -31,18 +31,25 @@ namespace b200q {
 namespace {
 
 constexpr int kBM = 128;          // tokens per tile (MMA M)
-constexpr int kBN = 256;          // weight rows per tile (MMA N)
 constexpr int kBKBytes = 128;     // bytes of codes per row per stage: 256 values along K
-constexpr int kStages = 4;
 constexpr uint32_t kABytes = kBM * kBKBytes;        // 16 KB
-constexpr uint32_t kBBytes = kBN * kBKBytes;        // 32 KB
 constexpr uint32_t kSfaBytes = 4 * 512;             // 4 K-atoms of one 128-row tile
-constexpr uint32_t kSfbBytes = 2 * 4 * 512;         // two 128-row tiles
-constexpr uint32_t kStageBytes = kABytes + kBBytes + kSfaBytes + kSfbBytes;  // 54 KB
-constexpr uint32_t kSmemBytes = kStages * kStageBytes + 256 + 1024;          // + barriers + alignment slack
-constexpr uint32_t kTmemCols = 512;
-constexpr uint32_t kSfColsPerStage = 48;  // 16 for the activations, 32 for the weights
 constexpr uint32_t kSpinLimit = 1u << 22;
+
+// Two tile shapes. 128 x 256 (one CTA per SM, 4 stages, all 512 tensor-memory columns) is the
+// fused-SwiGLU form: 128 gate rows and their 128 up rows side by side. 128 x 128 (3 stages, 256
+// columns) lets two CTAs share an SM, so one's pipeline fill and accumulator drain hide under the
+// other's MMAs: the plain product.
+template <int BN>
+struct Tile {
+  static constexpr int kStages = BN == 256 ? 4 : 3;
+  static constexpr uint32_t kBBytes = BN * kBKBytes;
+  static constexpr uint32_t kSfbBytes = (BN / 128) * 4 * 512;
+  static constexpr uint32_t kStageBytes = kABytes + kBBytes + kSfaBytes + kSfbBytes;
+  static constexpr uint32_t kSmemBytes = kStages * kStageBytes + 256 + 1024;  // + barriers + alignment slack
+  static constexpr uint32_t kTmemCols = BN == 256 ? 512 : 256;
+  static constexpr uint32_t kSfColsPerStage = 16 + (BN / 128) * 16;  // activations, then weights
+};
 
 constexpr uint32_t kStatusProducerTimeout = 1u, kStatusMmaTimeout = 2u, kStatusEpilogueTimeout = 4u;
 
@@ -177,9 +184,13 @@ struct W4A4Params {
   uint32_t epilogue;  // STORE / OUT_F32, or the fused SwiGLU (the tile's columns 0..127 are gate rows, 128..255 the up rows)
 };
 
-__global__ void __launch_bounds__(192, 1) w4a4_gemm_kernel(const __grid_constant__ CUtensorMap map_a,
+template <int kBN>
+__global__ void __launch_bounds__(192, kBN == 256 ? 1 : 2) w4a4_gemm_kernel(const __grid_constant__ CUtensorMap map_a,
                                                           const __grid_constant__ CUtensorMap map_b,
                                                           const __grid_constant__ W4A4Params p) {
+  constexpr int kStages = Tile<kBN>::kStages;
+  constexpr uint32_t kBBytes = Tile<kBN>::kBBytes, kSfbBytes = Tile<kBN>::kSfbBytes, kStageBytes = Tile<kBN>::kStageBytes;
+  constexpr uint32_t kTmemCols = Tile<kBN>::kTmemCols, kSfColsPerStage = Tile<kBN>::kSfColsPerStage;
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw = smem_u32(smem_raw);
   const uint32_t base = (raw + 1023u) & ~1023u;  // the 128-byte swizzle wants 1024-byte aligned tiles
@@ -193,10 +204,10 @@ __global__ void __launch_bounds__(192, 1) w4a4_gemm_kernel(const __grid_constant
   // The tile's 256 weight rows are two boxes of 128: rows [row_a, +128) and [row_b, +128). A plain
   // product takes consecutive boxes; the fused SwiGLU pairs 128 gate rows with their up rows, which
   // lie n / 2 further down the fused parent.
-  const bool swiglu = (p.epilogue & kEpilogueSwiglu) != 0u;
+  const bool swiglu = kBN == 256 && (p.epilogue & kEpilogueSwiglu) != 0u;
   const uint32_t row_a = swiglu ? n_tile * 128u : n_tile * kBN;
   const uint32_t row_b = swiglu ? p.n / 2u + n_tile * 128u : n_tile * kBN + 128u;
-  const bool second_half = row_b < p.n;  // the tile's second box exists
+  const bool second_half = kBN == 256 && row_b < p.n;  // the tile has a second box and it exists
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < kStages; ++s) {
@@ -229,18 +240,18 @@ __global__ void __launch_bounds__(192, 1) w4a4_gemm_kernel(const __grid_constant
       }
       const uint32_t full = bars + 8 * s;
       const uint32_t stage = base + s * kStageBytes;
-      mbar_expect_tx(full, kABytes + kSfaBytes + (second_half ? kBBytes + kSfbBytes : (kBBytes + kSfbBytes) / 2));
+      mbar_expect_tx(full, kABytes + kSfaBytes + (second_half ? 2u : 1u) * (128u * kBKBytes + 2048u));  // one or two boxes with their scales
       tma_load_2d(stage, &map_a, full, static_cast<int32_t>(it * kBKBytes), static_cast<int32_t>(m_tile * kBM));
       tma_load_2d(stage + kABytes, &map_b, full, static_cast<int32_t>(it * kBKBytes), static_cast<int32_t>(row_a));
       if (second_half) {
-        tma_load_2d(stage + kABytes + kBBytes / 2, &map_b, full, static_cast<int32_t>(it * kBKBytes), static_cast<int32_t>(row_b));
+        tma_load_2d(stage + kABytes + 128u * kBKBytes, &map_b, full, static_cast<int32_t>(it * kBKBytes), static_cast<int32_t>(row_b));
       }
       bulk_load(stage + kABytes + kBBytes, p.sfa + (static_cast<uint64_t>(m_tile) * k_atoms + it * 4u) * 512u, kSfaBytes, full);
       bulk_load(stage + kABytes + kBBytes + kSfaBytes, p.sfb + (static_cast<uint64_t>(row_a / 128u) * k_atoms + it * 4u) * 512u,
-                kSfbBytes / 2, full);
+                2048u, full);
       if (second_half) {
-        bulk_load(stage + kABytes + kBBytes + kSfaBytes + kSfbBytes / 2,
-                  p.sfb + (static_cast<uint64_t>(row_b / 128u) * k_atoms + it * 4u) * 512u, kSfbBytes / 2, full);
+        bulk_load(stage + kABytes + kBBytes + kSfaBytes + 2048u,
+                  p.sfb + (static_cast<uint64_t>(row_b / 128u) * k_atoms + it * 4u) * 512u, 2048u, full);
       }
     }
   } else if (warp == 5 && lane == 0) {
@@ -258,20 +269,21 @@ __global__ void __launch_bounds__(192, 1) w4a4_gemm_kernel(const __grid_constant
       }
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
       const uint32_t stage = base + s * kStageBytes;
-      const uint32_t sf_cols = tmem + 256u + s * kSfColsPerStage;
+      const uint32_t sf_cols = tmem + kBN + s * kSfColsPerStage;
       const uint32_t sfa_smem = stage + kABytes + kBBytes, sfb_smem = sfa_smem + kSfaBytes;
 #pragma unroll
       for (uint32_t kb = 0; kb < 4; ++kb) {
         tmem_cp_sf(sf_cols + kb * 4u, smem_desc(sfa_smem + kb * 512u, 128u, 0u));
-        tmem_cp_sf(sf_cols + 16u + kb * 8u, smem_desc(sfb_smem + kb * 512u, 128u, 0u));
-        tmem_cp_sf(sf_cols + 16u + kb * 8u + 4u, smem_desc(sfb_smem + kSfbBytes / 2 + kb * 512u, 128u, 0u));
+        constexpr uint32_t kSfbCols = (kBN / 128) * 4;  // columns of weight scales per 64 values along K
+        tmem_cp_sf(sf_cols + 16u + kb * kSfbCols, smem_desc(sfb_smem + kb * 512u, 128u, 0u));
+        if (kBN == 256) tmem_cp_sf(sf_cols + 16u + kb * kSfbCols + 4u, smem_desc(sfb_smem + 2048u + kb * 512u, 128u, 0u));
       }
       const uint64_t a_desc = smem_desc(stage, 1024u, 2u);
       const uint64_t b_desc = smem_desc(stage + kABytes, 1024u, 2u);
 #pragma unroll
       for (uint32_t kb = 0; kb < 4; ++kb) {
         // 64 values along K are 32 bytes: two 16-byte units further inside the swizzled row
-        mma_mxf4nvf4(tmem, a_desc + 2u * kb, b_desc + 2u * kb, idesc, sf_cols + kb * 4u, sf_cols + 16u + kb * 8u,
+        mma_mxf4nvf4(tmem, a_desc + 2u * kb, b_desc + 2u * kb, idesc, sf_cols + kb * 4u, sf_cols + 16u + kb * ((kBN / 128) * 4u),
                      (it | kb) != 0u ? 1u : 0u);
       }
       mma_commit(bars + 8 * (kStages + s));  // the stage's shared memory is free once these MMAs retire
@@ -356,6 +368,225 @@ __global__ void __launch_bounds__(192, 1) w4a4_gemm_kernel(const __grid_constant
   }
 }
 
+// ---- the persistent form ------------------------------------------------------------------------
+// One CTA per SM walks 128 x 256 tiles (tile = blockIdx.x, + gridDim.x, ...; the token tile index
+// runs fastest, so the CTAs at work share weight rows in the L2). The producer keeps the 4-stage ring
+// full across tile boundaries, so a tile's first MMAs find their operands waiting; the epilogue
+// warps pull the whole accumulator into registers (as packed BF16: 128 registers a thread - the
+// CTA has the SM's register file to itself), hand tensor memory back to the MMA thread and only
+// then store, under the next tile's MMAs. What a tile costs beyond its MMAs is the pull alone.
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+
+__global__ void __launch_bounds__(192, 1) w4a4_gemm_persistent_kernel(const __grid_constant__ CUtensorMap map_a,
+                                                                     const __grid_constant__ CUtensorMap map_b,
+                                                                     const __grid_constant__ W4A4Params p) {
+  constexpr int kBN = 256;
+  constexpr int kStages = Tile<256>::kStages;
+  constexpr uint32_t kBBytes = Tile<256>::kBBytes, kStageBytes = Tile<256>::kStageBytes;
+  constexpr uint32_t kTmemCols = Tile<256>::kTmemCols, kSfColsPerStage = Tile<256>::kSfColsPerStage;
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t raw = smem_u32(smem_raw);
+  const uint32_t base = (raw + 1023u) & ~1023u;
+  uint8_t *base_ptr = smem_raw + (base - raw);
+  // barriers: full[4], empty[4], accumulator full, accumulator empty; then the tensor-memory slot
+  const uint32_t bars = base + kStages * kStageBytes;
+  const uint32_t bar_acc_full = bars + 8 * 2 * kStages, bar_acc_empty = bar_acc_full + 8;
+  uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(base_ptr + kStages * kStageBytes + 128);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const uint32_t k_iters = p.k / 256u, k_atoms = p.k / 64u;
+  const bool swiglu = (p.epilogue & kEpilogueSwiglu) != 0u;
+  const uint32_t m_tiles = (p.tokens + kBM - 1) / kBM;
+  const uint32_t n_tiles = swiglu ? p.n / 256u : (p.n + 255u) / 256u;
+  const uint32_t tiles = m_tiles * n_tiles;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < kStages; ++s) {
+      mbar_init(bars + 8 * s, 1);
+      mbar_init(bars + 8 * (kStages + s), 1);
+    }
+    mbar_init(bar_acc_full, 1);
+    mbar_init(bar_acc_empty, 4);  // one arrival per epilogue warp
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 5) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(kTmemCols) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+  const uint32_t tmem = *tmem_slot;
+
+  griddep_launch_dependents();
+  griddep_wait();  // the quantized activations come from the previous kernel in the stream
+
+  if (warp == 4 && lane == 0) {
+    // ---- producer ----
+    uint32_t git = 0;  // stage uses since the kernel began
+    bool ok = true;
+    for (uint32_t tile = blockIdx.x; tile < tiles && ok; tile += gridDim.x) {
+      const uint32_t m_tile = tile % m_tiles, n_tile = tile / m_tiles;
+      const uint32_t row_a = swiglu ? n_tile * 128u : n_tile * kBN;
+      const uint32_t row_b = swiglu ? p.n / 2u + n_tile * 128u : n_tile * kBN + 128u;
+      const bool second_half = row_b < p.n;
+      for (uint32_t it = 0; it < k_iters; ++it, ++git) {
+        const uint32_t s = git % kStages;
+        if (!mbar_wait(bars + 8 * (kStages + s), ((git / kStages) & 1u) ^ 1u)) {
+          atomicOr(p.status, kStatusProducerTimeout);
+          ok = false;
+          break;
+        }
+        const uint32_t full = bars + 8 * s;
+        const uint32_t stage = base + s * kStageBytes;
+        mbar_expect_tx(full, kABytes + kSfaBytes + (second_half ? 2u : 1u) * (128u * kBKBytes + 2048u));
+        tma_load_2d(stage, &map_a, full, static_cast<int32_t>(it * kBKBytes), static_cast<int32_t>(m_tile * kBM));
+        tma_load_2d(stage + kABytes, &map_b, full, static_cast<int32_t>(it * kBKBytes), static_cast<int32_t>(row_a));
+        if (second_half) {
+          tma_load_2d(stage + kABytes + 128u * kBKBytes, &map_b, full, static_cast<int32_t>(it * kBKBytes), static_cast<int32_t>(row_b));
+        }
+        bulk_load(stage + kABytes + kBBytes, p.sfa + (static_cast<uint64_t>(m_tile) * k_atoms + it * 4u) * 512u, kSfaBytes, full);
+        bulk_load(stage + kABytes + kBBytes + kSfaBytes, p.sfb + (static_cast<uint64_t>(row_a / 128u) * k_atoms + it * 4u) * 512u, 2048u, full);
+        if (second_half) {
+          bulk_load(stage + kABytes + kBBytes + kSfaBytes + 2048u, p.sfb + (static_cast<uint64_t>(row_b / 128u) * k_atoms + it * 4u) * 512u,
+                    2048u, full);
+        }
+      }
+    }
+  } else if (warp == 5 && lane == 0) {
+    // ---- MMA issuer ----
+    const uint32_t idesc = (1u << 7) | (1u << 10) | ((kBN >> 3) << 17) | ((kBM >> 4) << 24);
+    uint32_t git = 0, tile_i = 0;
+    bool ok = true;
+    for (uint32_t tile = blockIdx.x; tile < tiles && ok; tile += gridDim.x, ++tile_i) {
+      // the epilogue warps have pulled the previous tile out of tensor memory
+      if (!mbar_wait(bar_acc_empty, (tile_i & 1u) ^ 1u)) {
+        atomicOr(p.status, kStatusMmaTimeout);
+        break;
+      }
+      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+      for (uint32_t it = 0; it < k_iters; ++it, ++git) {
+        const uint32_t s = git % kStages;
+        if (!mbar_wait(bars + 8 * s, (git / kStages) & 1u)) {
+          atomicOr(p.status, kStatusMmaTimeout);
+          ok = false;
+          break;
+        }
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        const uint32_t stage = base + s * kStageBytes;
+        const uint32_t sf_cols = tmem + kBN + s * kSfColsPerStage;
+        const uint32_t sfa_smem = stage + kABytes + kBBytes, sfb_smem = sfa_smem + kSfaBytes;
+#pragma unroll
+        for (uint32_t kb = 0; kb < 4; ++kb) {
+          tmem_cp_sf(sf_cols + kb * 4u, smem_desc(sfa_smem + kb * 512u, 128u, 0u));
+          tmem_cp_sf(sf_cols + 16u + kb * 8u, smem_desc(sfb_smem + kb * 512u, 128u, 0u));
+          tmem_cp_sf(sf_cols + 16u + kb * 8u + 4u, smem_desc(sfb_smem + 2048u + kb * 512u, 128u, 0u));
+        }
+        const uint64_t a_desc = smem_desc(stage, 1024u, 2u);
+        const uint64_t b_desc = smem_desc(stage + kABytes, 1024u, 2u);
+#pragma unroll
+        for (uint32_t kb = 0; kb < 4; ++kb) {
+          mma_mxf4nvf4(tmem, a_desc + 2u * kb, b_desc + 2u * kb, idesc, sf_cols + kb * 4u, sf_cols + 16u + kb * 8u,
+                       (it | kb) != 0u ? 1u : 0u);
+        }
+        mma_commit(bars + 8 * (kStages + s));
+      }
+      if (ok) mma_commit(bar_acc_full);
+    }
+  } else if (warp < 4) {
+    // ---- epilogue: warp q owns accumulator lanes (tokens) 32 q .. 32 q + 31 ----
+    const uint32_t lane_base = tmem + (static_cast<uint32_t>(warp * 32) << 16);
+    uint32_t tile_i = 0;
+    for (uint32_t tile = blockIdx.x; tile < tiles; tile += gridDim.x, ++tile_i) {
+      const uint32_t m_tile = tile % m_tiles, n_tile = tile / m_tiles;
+      if (!mbar_wait(bar_acc_full, tile_i & 1u)) {
+        if (lane == 0) atomicOr(p.status, kStatusEpilogueTimeout);
+        break;
+      }
+      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+      const uint32_t token = m_tile * kBM + warp * 32 + lane;
+      if (p.epilogue & kEpilogueF32) {
+        // float32 rows do not fit the register file: store chunk by chunk, then release
+#pragma unroll 1
+        for (uint32_t c = 0; c < kBN; c += 32) {
+          uint32_t r[32];
+          tmem_ld32(lane_base + c, r);
+          asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+          const uint32_t row0 = n_tile * kBN + c;
+          if (token < p.tokens && row0 < p.n) {
+            float4 *dst = reinterpret_cast<float4 *>(static_cast<float *>(p.y) + static_cast<size_t>(token) * p.ldy + row0);
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+              dst[j] = make_float4(__uint_as_float(r[4 * j]) * p.alpha, __uint_as_float(r[4 * j + 1]) * p.alpha,
+                                   __uint_as_float(r[4 * j + 2]) * p.alpha, __uint_as_float(r[4 * j + 3]) * p.alpha);
+            }
+          }
+        }
+        asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+        __syncwarp();
+        if (lane == 0) mbar_arrive(bar_acc_empty);
+        continue;
+      }
+      uint32_t out[128];  // the thread's output row as packed BF16 (128 columns of h in the SwiGLU form)
+      if (swiglu) {
+#pragma unroll
+        for (uint32_t c = 0; c < 128u; c += 32) {
+          uint32_t g[32], u[32];
+          tmem_ld32(lane_base + c, g);
+          tmem_ld32(lane_base + 128u + c, u);
+          asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+          for (int j = 0; j < 16; ++j) {
+            float h2[2];
+#pragma unroll
+            for (int i = 0; i < 2; ++i) {
+              const float gv = __bfloat162float(__float2bfloat16_rn(__uint_as_float(g[2 * j + i]) * p.alpha));
+              const float uv = __bfloat162float(__float2bfloat16_rn(__uint_as_float(u[2 * j + i]) * p.alpha));
+              h2[i] = gv / (1.0f + __expf(-gv)) * uv;
+            }
+            const __nv_bfloat162 h = __floats2bfloat162_rn(h2[0], h2[1]);
+            out[c / 2 + j] = *reinterpret_cast<const uint32_t *>(&h);
+          }
+        }
+      } else {
+#pragma unroll
+        for (uint32_t c = 0; c < kBN; c += 32) {
+          uint32_t r[32];
+          tmem_ld32(lane_base + c, r);
+          asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+          for (int j = 0; j < 16; ++j) {
+            const __nv_bfloat162 h = __floats2bfloat162_rn(__uint_as_float(r[2 * j]) * p.alpha, __uint_as_float(r[2 * j + 1]) * p.alpha);
+            out[c / 2 + j] = *reinterpret_cast<const uint32_t *>(&h);
+          }
+        }
+      }
+      // tensor memory is free for the next tile's MMAs; the stores run under them
+      asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+      __syncwarp();
+      if (lane == 0) mbar_arrive(bar_acc_empty);
+      if (token < p.tokens) {
+        const uint32_t width = swiglu ? 128u : kBN;
+        const uint32_t col0 = n_tile * width;
+        const uint32_t limit = swiglu ? p.n / 2u : p.n;
+        __nv_bfloat16 *row = static_cast<__nv_bfloat16 *>(p.y) + static_cast<size_t>(token) * p.ldy + col0;
+#pragma unroll
+        for (uint32_t c = 0; c < kBN; c += 8) {
+          if (c < width && col0 + c < limit) {  // n is a multiple of 128: an 8-column piece is whole
+            *reinterpret_cast<uint4 *>(row + c) = make_uint4(out[c / 2], out[c / 2 + 1], out[c / 2 + 2], out[c / 2 + 3]);
+          }
+        }
+      }
+    }
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  if (warp == 5) {
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(kTmemCols) : "memory");
+  }
+}
+
 // ---- host side --------------------------------------------------------------------------------
 using EncodeTiledFn = CUresult (*)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
                                    const cuuint64_t *, const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave,
@@ -400,8 +631,16 @@ uint64_t w4a4_workspace_bytes(uint32_t k, uint32_t tokens) {
 bool w4a4_shape_ok(uint32_t n, uint32_t k) { return (k % 256u) == 0 && (n % 128u) == 0; }
 
 int32_t w4a4_prepare(ErrorSlot &slot) {
-  const cudaError_t err = cudaFuncSetAttribute(w4a4_gemm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                               static_cast<int>(kSmemBytes));
+  cudaError_t err = cudaFuncSetAttribute(w4a4_gemm_kernel<256>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         static_cast<int>(Tile<256>::kSmemBytes));
+  if (err == cudaSuccess) {
+    err = cudaFuncSetAttribute(w4a4_gemm_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                               static_cast<int>(Tile<128>::kSmemBytes));
+  }
+  if (err == cudaSuccess) {
+    err = cudaFuncSetAttribute(w4a4_gemm_persistent_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                               static_cast<int>(Tile<256>::kSmemBytes));
+  }
   if (err != cudaSuccess) return fail(slot, "nvfp4 prefill kernel attributes: %s", cudaGetErrorString(err));
   if (encode_tiled_fn() == nullptr) return fail(slot, "cuTensorMapEncodeTiled is not available from this driver");
   return 0;
@@ -437,8 +676,20 @@ int32_t w4a4_launch(ErrorSlot &slot, const DeviceState &dev, const uint8_t *w_co
   p.alpha = 1.0f / (d_in * d_w);
   p.epilogue = epilogue;
   const bool swiglu = (epilogue & kEpilogueSwiglu) != 0u;
-  const dim3 grid(pad / kBM, swiglu ? n / 256u : (n + kBN - 1) / kBN, 1);
-  const cudaError_t err = launch(w4a4_gemm_kernel, grid, dim3(192), kSmemBytes, stream, dev.pdl != 0, map_a, map_b, p);
+  // the fused SwiGLU needs the wide tile (gate and up boxes side by side); the plain product takes
+  // the narrow one, two CTAs per SM
+  if (dev.w4a4_persistent != 0) {
+    const uint32_t tiles = (pad / kBM) * (swiglu ? n / 256u : (n + 255u) / 256u);
+    const uint32_t ctas = tiles < static_cast<uint32_t>(dev.sm_count) ? tiles : static_cast<uint32_t>(dev.sm_count);
+    const cudaError_t perr = launch(w4a4_gemm_persistent_kernel, dim3(ctas), dim3(192), Tile<256>::kSmemBytes, stream, dev.pdl != 0,
+                                    map_a, map_b, p);
+    if (perr != cudaSuccess) return fail(slot, "nvfp4 prefill launch: %s", cudaGetErrorString(perr));
+    return 0;
+  }
+  const bool wide = swiglu || dev.w4a4_bn == 256;
+  const dim3 grid(pad / kBM, swiglu ? n / 256u : (wide ? (n + 255u) / 256u : n / 128u), 1);
+  const cudaError_t err = wide ? launch(w4a4_gemm_kernel<256>, grid, dim3(192), Tile<256>::kSmemBytes, stream, dev.pdl != 0, map_a, map_b, p)
+                               : launch(w4a4_gemm_kernel<128>, grid, dim3(192), Tile<128>::kSmemBytes, stream, dev.pdl != 0, map_a, map_b, p);
   if (err != cudaSuccess) return fail(slot, "nvfp4 prefill launch: %s", cudaGetErrorString(err));
   return 0;
 }
