@@ -443,8 +443,29 @@ def run_side_workload(args) -> None:
                     nvfp4.linear(x, w, out=y, policy=nvfp4.ALLOW_A4, workspace=ws)
 
             launches = 2 * len(items)
+            if args.mlp:
+                # the layers' MLP through one entry: gate|up with the SwiGLU + re-quantizing epilogue, then down
+                gen.manual_seed(20261130)
+                n_gu, k_gu = 2 * 17408, 5120
+                codes = torch.randint(0, 256, (n_gu, k_gu // 2), dtype=torch.uint8, device=device, generator=gen)
+                natural = (torch.randn((n_gu, k_gu // 16), device=device, generator=gen).abs() + 0.1).to(torch.float8_e4m3fn).view(torch.uint8)
+                stored = natural.reshape(n_gu // 128, 4, 32, k_gu // 64, 4).permute(0, 3, 2, 1, 4).contiguous().reshape(-1)
+                gate_up = nvfp4.Weight(codes, stored, n_gu, k_gu, 448.0, 448.0)
+                down_w, _, y_down = items[1]
+                x_in = items[0][1]
+                mlp_ws = nvfp4.Workspace(nvfp4.mlp_workspace_bytes(n_gu, k_gu, nvfp4.ALLOW_A4, tokens), device)
+                flops = 2.0 * tokens * (n_gu * k_gu + down_w.n * down_w.k)
+
+                def one_step() -> None:
+                    nvfp4.mlp(x_in, gate_up, down_w, mlp_ws, out=y_down, policy=nvfp4.ALLOW_A4)
+
+                ws = mlp_ws
+                launches = 3
             metric, unit, work = "nvfp4_prefill_gemm_tflops", "TFLOP/s", flops / 1e12
             workload = f"configs[2]: NVFP4 W4A4 prefill GEMM, M={tokens}, up 5120->17408 and down 17408->5120, fused-layout activation quantizer + tcgen05 block-scaled MMA"
+            if args.mlp:
+                workload = (f"configs[2] as the layer's MLP, M={tokens}: gate|up 5120->34816 with SwiGLU and the down product's "
+                            "quantizer in its epilogue, then down 17408->5120; one activation quantizer launch")
         else:
             weights, inputs, outputs, nbytes = build_trellis_workload(args.layers, 0, 1, args.tokens, device)
             by = {name: (in_, out) for name, in_, out in TRELLIS_LAYER}
@@ -630,6 +651,7 @@ def main() -> None:
     ap.add_argument("--tokens", type=int, default=8)
     ap.add_argument("--group", type=int, default=1, help="1: q|k|v and gate|up share one launch each; 0: seven launches per layer")
     ap.add_argument("--graph", type=int, default=1, help="replay the step as one CUDA graph")
+    ap.add_argument("--mlp", type=int, default=0, help="with --workload prefill: 1 runs the fused MLP entry instead of two plain products")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--workload", default="decode", choices=["decode", "prefill", "trellis", "moe"],
                     help="decode: configs[1] (the headline); prefill: configs[2]; trellis: configs[3]; moe: configs[4]")

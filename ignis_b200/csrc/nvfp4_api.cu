@@ -97,7 +97,7 @@ int32_t linear_group_impl(const b200q_nvfp4_weight *const *w, uint32_t count, co
   // (the reference's AllowA4 resolution, nvfp4_dispatch.cpp:31-39, with one threshold); everything
   // else takes the decode route, which re-reads the weights once per 32 tokens.
   if (policy == B200Q_NVFP4_ALLOW_A4 && tokens > B200Q_NVFP4_DECODE_MAX_TOKENS && count == 1 &&
-      (epilogue & kEpilogueAdd) == 0u && w4a4_shape_ok(w[0]->n, w[0]->k)) {
+      !(swiglu && (epilogue & kEpilogueAdd)) && w4a4_shape_ok(w[0]->n, w[0]->k)) {
     const b200q_nvfp4_weight *w0 = w[0];
     if (!std::isfinite(w0->input_scale_divisor) || !(w0->input_scale_divisor > 0.0f)) {
       return fail(slot, "%s: input_scale_divisor must be finite and positive for the A4 route", what);
@@ -181,6 +181,63 @@ int32_t b200q_nvfp4_linear_group(const b200q_nvfp4_weight *const *w, uint32_t co
     return fail(nvfp4_error(), "b200q_nvfp4_linear_group: unknown epilogue 0x%x", epilogue);
   }
   return linear_group_impl(w, count, x, tokens, y, ldy, epilogue, policy, workspace, stream, "b200q_nvfp4_linear_group");
+}
+
+uint64_t b200q_nvfp4_mlp_workspace_bytes(uint32_t gate_up_n, uint32_t k, uint32_t policy, uint32_t tokens) {
+  if (gate_up_n == 0 || (gate_up_n % 256u) != 0 || k == 0 || (k % 64u) != 0 || tokens == 0) return 0;
+  if (policy != B200Q_NVFP4_A16_ONLY && policy != B200Q_NVFP4_ALLOW_A4) return 0;
+  const uint32_t inter = gate_up_n / 2u;
+  if (policy == B200Q_NVFP4_ALLOW_A4 && tokens > B200Q_NVFP4_DECODE_MAX_TOKENS && (k % 256u) == 0 && (inter % 256u) == 0) {
+    return w4a4_mlp_workspace_bytes(k, inter, tokens);
+  }
+  return 256u + static_cast<uint64_t>(tokens) * inter * 2u;  // the status line, then h as BF16
+}
+
+int32_t b200q_nvfp4_mlp(const b200q_nvfp4_weight *gate_up, const b200q_nvfp4_weight *down, const void *x, uint32_t tokens, void *y,
+                        uint32_t ldy, uint32_t epilogue, uint32_t policy, const b200q_nvfp4_workspace *workspace, void *stream) {
+  const char *what = "b200q_nvfp4_mlp";
+  ErrorSlot &slot = nvfp4_error();
+  if ((epilogue & ~(B200Q_NVFP4_ADD | B200Q_NVFP4_OUT_F32)) != 0u) return fail(slot, "%s: unknown epilogue 0x%x", what, epilogue);
+  if (policy != B200Q_NVFP4_A16_ONLY && policy != B200Q_NVFP4_ALLOW_A4) return fail(slot, "%s: unknown policy %u", what, policy);
+  if (check_weight(slot, gate_up, what) != 0 || check_weight(slot, down, what) != 0) return -1;
+  if ((gate_up->n % 256u) != 0) return fail(slot, "%s: a fused gate_up parent needs n a multiple of 256", what);
+  const uint32_t inter = gate_up->n / 2u;
+  if (down->k != inter) return fail(slot, "%s: down.k = %u is not gate_up.n / 2 = %u", what, down->k, inter);
+  if (tokens == 0) return fail(slot, "%s: tokens must be positive", what);
+  if (x == nullptr || !aligned(x, 16)) return fail(slot, "%s: x is NULL or not 16-byte aligned", what);
+  if (y == nullptr || !aligned(y, 16) || (ldy % 8u) != 0 || ldy < down->n) {
+    return fail(slot, "%s: y must be 16-byte aligned with ldy a multiple of 8 and at least down.n", what);
+  }
+  const uint64_t need = b200q_nvfp4_mlp_workspace_bytes(gate_up->n, gate_up->k, policy, tokens);
+  if (workspace == nullptr || workspace->base == nullptr || workspace->bytes < need || !aligned(workspace->base, 256)) {
+    return fail(slot, "%s: needs a 256-byte aligned workspace of %llu bytes", what, static_cast<unsigned long long>(need));
+  }
+  const DeviceState *dev = prepared_state(slot, what);
+  if (dev == nullptr) return -1;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  uint8_t *base = static_cast<uint8_t *>(workspace->base);
+  if (policy == B200Q_NVFP4_ALLOW_A4 && tokens > B200Q_NVFP4_DECODE_MAX_TOKENS && (gate_up->k % 256u) == 0 && (inter % 256u) == 0) {
+    for (const b200q_nvfp4_weight *w : {gate_up, down}) {
+      if (!std::isfinite(w->input_scale_divisor) || !(w->input_scale_divisor > 0.0f)) {
+        return fail(slot, "%s: input_scale_divisor must be finite and positive for the A4 route", what);
+      }
+    }
+    return w4a4_mlp_launch(slot, *dev, static_cast<const uint8_t *>(gate_up->codes), static_cast<const uint8_t *>(gate_up->scales),
+                           gate_up->n, gate_up->k, gate_up->weight_scale_divisor, gate_up->input_scale_divisor,
+                           static_cast<const uint8_t *>(down->codes), static_cast<const uint8_t *>(down->scales), down->n,
+                           down->weight_scale_divisor, down->input_scale_divisor, static_cast<const uint16_t *>(x), tokens, y, ldy,
+                           epilogue, base, s);
+  }
+  // narrow calls: the decode route twice, h (BF16) in the workspace behind the status line
+  void *h = base + 256;
+  const b200q_nvfp4_weight *w0[1] = {gate_up};
+  void *y0[1] = {h};
+  const uint32_t ld0[1] = {inter};
+  if (decode_route(slot, *dev, w0, 1, x, tokens, y0, ld0, kEpilogueSwiglu, s) != 0) return -1;
+  const b200q_nvfp4_weight *w1[1] = {down};
+  void *y1[1] = {y};
+  const uint32_t ld1[1] = {ldy};
+  return decode_route(slot, *dev, w1, 1, h, tokens, y1, ld1, epilogue, s);
 }
 
 int32_t b200q_nvfp4_linear_swiglu(const b200q_nvfp4_weight *gate_up, const void *x, uint32_t tokens, void *h, uint32_t ldh,

@@ -12,6 +12,7 @@ constexpr uint32_t kMaxGroup = 8;  // B200Q_NVFP4_MAX_GROUP
 constexpr uint32_t kEpilogueAdd = 1u;
 constexpr uint32_t kEpilogueF32 = 0x100u;
 constexpr uint32_t kEpilogueSwiglu = 0x200u;
+constexpr uint32_t kEpilogueQuant = 0x400u;  // with SwiGLU on the tensor-core route: h leaves as the next product's NVFP4 operand
 
 struct GemvWeight {
   const uint8_t *codes;
@@ -61,6 +62,13 @@ uint64_t w4a4_workspace_bytes(uint32_t k, uint32_t tokens);
 int32_t w4a4_launch(ErrorSlot &slot, const DeviceState &dev, const uint8_t *w_codes, const uint8_t *w_scales, uint32_t n,
                     uint32_t k, float d_w, float d_in, const uint16_t *x, uint32_t tokens, void *y, uint32_t ldy,
                     uint32_t epilogue, uint8_t *workspace, cudaStream_t stream);
+// The layers' MLP on the tensor-core route: x is quantized, the gate|up product's epilogue writes
+// silu(g) u already quantized under `down`'s input divisor, the down product reads it.
+uint64_t w4a4_mlp_workspace_bytes(uint32_t k, uint32_t inter, uint32_t tokens);
+int32_t w4a4_mlp_launch(ErrorSlot &slot, const DeviceState &dev, const uint8_t *gu_codes, const uint8_t *gu_scales, uint32_t gu_n,
+                        uint32_t k, float gu_dw, float gu_din, const uint8_t *dn_codes, const uint8_t *dn_scales, uint32_t dn_n,
+                        float dn_dw, float dn_din, const uint16_t *x, uint32_t tokens, void *y, uint32_t ldy, uint32_t epilogue,
+                        uint8_t *workspace, cudaStream_t stream);
 
 }  // namespace b200q
 

@@ -181,7 +181,10 @@ struct W4A4Params {
   uint32_t *status;
   uint32_t tokens, n, k, ldy;
   float alpha;
-  uint32_t epilogue;  // STORE / OUT_F32, or the fused SwiGLU (the tile's columns 0..127 are gate rows, 128..255 the up rows)
+  uint32_t epilogue;  // STORE / ADD / OUT_F32, or the fused SwiGLU (the tile's columns 0..127 are gate rows, 128..255 the up rows)
+  uint8_t *q_codes;   // kEpilogueQuant: h as the next product's operand, codes [pad tokens][n / 4] ...
+  uint8_t *q_scales;  // ... and scales in 512-byte tiles
+  float q_din;        // the next weight's input divisor
 };
 
 template <int kBN>
@@ -506,8 +509,9 @@ __global__ void __launch_bounds__(192, 1) w4a4_gemm_persistent_kernel(const __gr
       }
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
       const uint32_t token = m_tile * kBM + warp * 32 + lane;
-      if (p.epilogue & kEpilogueF32) {
-        // float32 rows do not fit the register file: store chunk by chunk, then release
+      if (p.epilogue & (kEpilogueF32 | kEpilogueAdd)) {
+        // float32 rows do not fit the register file, and a residual has to be read before the one
+        // rounding: these forms store chunk by chunk, then release
 #pragma unroll 1
         for (uint32_t c = 0; c < kBN; c += 32) {
           uint32_t r[32];
@@ -515,11 +519,35 @@ __global__ void __launch_bounds__(192, 1) w4a4_gemm_persistent_kernel(const __gr
           asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
           const uint32_t row0 = n_tile * kBN + c;
           if (token < p.tokens && row0 < p.n) {
-            float4 *dst = reinterpret_cast<float4 *>(static_cast<float *>(p.y) + static_cast<size_t>(token) * p.ldy + row0);
+            const bool add = (p.epilogue & kEpilogueAdd) != 0u;
+            if (p.epilogue & kEpilogueF32) {
+              float4 *dst = reinterpret_cast<float4 *>(static_cast<float *>(p.y) + static_cast<size_t>(token) * p.ldy + row0);
 #pragma unroll
-            for (int j = 0; j < 8; ++j) {
-              dst[j] = make_float4(__uint_as_float(r[4 * j]) * p.alpha, __uint_as_float(r[4 * j + 1]) * p.alpha,
-                                   __uint_as_float(r[4 * j + 2]) * p.alpha, __uint_as_float(r[4 * j + 3]) * p.alpha);
+              for (int j = 0; j < 8; ++j) {
+                float4 o = make_float4(__uint_as_float(r[4 * j]) * p.alpha, __uint_as_float(r[4 * j + 1]) * p.alpha,
+                                       __uint_as_float(r[4 * j + 2]) * p.alpha, __uint_as_float(r[4 * j + 3]) * p.alpha);
+                if (add) {
+                  const float4 old = dst[j];
+                  o.x += old.x, o.y += old.y, o.z += old.z, o.w += old.w;
+                }
+                dst[j] = o;
+              }
+            } else {
+              uint4 *dst = reinterpret_cast<uint4 *>(static_cast<__nv_bfloat16 *>(p.y) + static_cast<size_t>(token) * p.ldy + row0);
+#pragma unroll
+              for (int j = 0; j < 4; ++j) {
+                const uint4 old = dst[j];
+                const uint32_t ow[4] = {old.x, old.y, old.z, old.w};
+                uint32_t o[4];
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                  const __nv_bfloat162 h = __floats2bfloat162_rn(
+                      __uint_as_float(r[8 * j + 2 * e]) * p.alpha + bf16_bits_to_f32(ow[e] & 0xFFFFu),
+                      __uint_as_float(r[8 * j + 2 * e + 1]) * p.alpha + __uint_as_float(ow[e] & 0xFFFF0000u));
+                  o[e] = *reinterpret_cast<const uint32_t *>(&h);
+                }
+                dst[j] = make_uint4(o[0], o[1], o[2], o[3]);
+              }
             }
           }
         }
@@ -528,44 +556,57 @@ __global__ void __launch_bounds__(192, 1) w4a4_gemm_persistent_kernel(const __gr
         if (lane == 0) mbar_arrive(bar_acc_empty);
         continue;
       }
-      uint32_t out[128];  // the thread's output row as packed BF16 (128 columns of h in the SwiGLU form)
-      if (swiglu) {
+      // The thread's row as packed BF16: 256 columns of the product, or (SwiGLU) BF16(g alpha) in
+      // [0, 64) and BF16(u alpha) in [64, 128) - the two roundings the reference's formula makes first.
+      uint32_t out[128];
 #pragma unroll
-        for (uint32_t c = 0; c < 128u; c += 32) {
-          uint32_t g[32], u[32];
-          tmem_ld32(lane_base + c, g);
-          tmem_ld32(lane_base + 128u + c, u);
-          asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+      for (uint32_t c = 0; c < kBN; c += 32) {
+        uint32_t r[32];
+        tmem_ld32(lane_base + c, r);
+        asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 #pragma unroll
-          for (int j = 0; j < 16; ++j) {
-            float h2[2];
-#pragma unroll
-            for (int i = 0; i < 2; ++i) {
-              const float gv = __bfloat162float(__float2bfloat16_rn(__uint_as_float(g[2 * j + i]) * p.alpha));
-              const float uv = __bfloat162float(__float2bfloat16_rn(__uint_as_float(u[2 * j + i]) * p.alpha));
-              h2[i] = gv / (1.0f + __expf(-gv)) * uv;
-            }
-            const __nv_bfloat162 h = __floats2bfloat162_rn(h2[0], h2[1]);
-            out[c / 2 + j] = *reinterpret_cast<const uint32_t *>(&h);
-          }
-        }
-      } else {
-#pragma unroll
-        for (uint32_t c = 0; c < kBN; c += 32) {
-          uint32_t r[32];
-          tmem_ld32(lane_base + c, r);
-          asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-#pragma unroll
-          for (int j = 0; j < 16; ++j) {
-            const __nv_bfloat162 h = __floats2bfloat162_rn(__uint_as_float(r[2 * j]) * p.alpha, __uint_as_float(r[2 * j + 1]) * p.alpha);
-            out[c / 2 + j] = *reinterpret_cast<const uint32_t *>(&h);
-          }
+        for (int j = 0; j < 16; ++j) {
+          const __nv_bfloat162 h = __floats2bfloat162_rn(__uint_as_float(r[2 * j]) * p.alpha, __uint_as_float(r[2 * j + 1]) * p.alpha);
+          out[c / 2 + j] = *reinterpret_cast<const uint32_t *>(&h);
         }
       }
-      // tensor memory is free for the next tile's MMAs; the stores run under them
+      // tensor memory is free for the next tile's MMAs; the rest runs under them
       asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
       __syncwarp();
       if (lane == 0) mbar_arrive(bar_acc_empty);
+      if (swiglu) {
+        // h = BF16(silu(BF16(g)) * BF16(u)), in place over the gate half
+#pragma unroll
+        for (int j = 0; j < 64; ++j) {
+          const float2 g = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162 *>(&out[j]));
+          const float2 u = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162 *>(&out[64 + j]));
+          const __nv_bfloat162 h = __floats2bfloat162_rn(g.x / (1.0f + __expf(-g.x)) * u.x, g.y / (1.0f + __expf(-g.y)) * u.y);
+          out[j] = *reinterpret_cast<const uint32_t *>(&h);
+        }
+      }
+      if (swiglu && (p.epilogue & kEpilogueQuant)) {
+        // h leaves as the down product's operand: 8 blocks of 16 along its K, quantized as the
+        // standalone quantizer would from the BF16 values (padding rows are zeros and stay zeros)
+        const uint32_t inter = p.n / 2u, g0 = n_tile * 8u;
+        uint32_t sc[2] = {0u, 0u};
+        uint4 *code_dst = reinterpret_cast<uint4 *>(p.q_codes + static_cast<uint64_t>(token) * (inter / 2u) + n_tile * 64u);
+#pragma unroll
+        for (int b = 0; b < 8; b += 2) {
+          uint2 c0, c1;
+          uint8_t s0, s1;
+          quantize_block16(make_uint4(out[8 * b], out[8 * b + 1], out[8 * b + 2], out[8 * b + 3]),
+                           make_uint4(out[8 * b + 4], out[8 * b + 5], out[8 * b + 6], out[8 * b + 7]), p.q_din, c0, s0);
+          quantize_block16(make_uint4(out[8 * b + 8], out[8 * b + 9], out[8 * b + 10], out[8 * b + 11]),
+                           make_uint4(out[8 * b + 12], out[8 * b + 13], out[8 * b + 14], out[8 * b + 15]), p.q_din, c1, s1);
+          code_dst[b / 2] = make_uint4(c0.x, c0.y, c1.x, c1.y);
+          sc[b >> 2] |= (static_cast<uint32_t>(s0) << (8 * (b & 3))) | (static_cast<uint32_t>(s1) << (8 * ((b + 1) & 3)));
+        }
+        const uint64_t atom = (static_cast<uint64_t>(token >> 7) * (inter / 64u) + (g0 >> 2)) * 512u + (token & 31u) * 16u +
+                              ((token & 127u) >> 5) * 4u;
+        *reinterpret_cast<uint32_t *>(p.q_scales + atom) = sc[0];
+        *reinterpret_cast<uint32_t *>(p.q_scales + atom + 512u) = sc[1];
+        continue;
+      }
       if (token < p.tokens) {
         const uint32_t width = swiglu ? 128u : kBN;
         const uint32_t col0 = n_tile * width;
@@ -646,14 +687,20 @@ int32_t w4a4_prepare(ErrorSlot &slot) {
   return 0;
 }
 
-int32_t w4a4_launch(ErrorSlot &slot, const DeviceState &dev, const uint8_t *w_codes, const uint8_t *w_scales, uint32_t n,
-                    uint32_t k, float d_w, float d_in, const uint16_t *x, uint32_t tokens, void *y, uint32_t ldy,
-                    uint32_t epilogue, uint8_t *workspace, cudaStream_t stream) {
+namespace {
+struct QuantTarget {
+  uint8_t *codes = nullptr;
+  uint8_t *scales = nullptr;
+  float d_in = 1.0f;
+};
+
+// One product over activations at `a_codes` / `a_scales`; `x` non-NULL quantizes them there first.
+int32_t w4a4_product(ErrorSlot &slot, const DeviceState &dev, const uint8_t *w_codes, const uint8_t *w_scales, uint32_t n,
+                     uint32_t k, float d_w, float d_in, const uint16_t *x, uint32_t tokens, void *y, uint32_t ldy,
+                     uint32_t epilogue, uint32_t *status, uint8_t *a_codes, uint8_t *a_scales, const QuantTarget &q,
+                     cudaStream_t stream) {
   const uint32_t pad = w4a4_tokens_pad(tokens);
-  uint32_t *status = reinterpret_cast<uint32_t *>(workspace);
-  uint8_t *a_codes = workspace + 256;
-  uint8_t *a_scales = a_codes + static_cast<uint64_t>(pad) * (k / 2u);
-  {
+  if (x != nullptr) {
     const uint64_t total = static_cast<uint64_t>(pad) * (k / 16u);
     const uint32_t grid = static_cast<uint32_t>(total / 256u < 148u * 16u ? (total + 255u) / 256u : 148u * 16u);
     const cudaError_t err = launch(quantize_swizzled_kernel, dim3(grid), dim3(256), 0, stream, dev.pdl != 0, x, tokens, pad,
@@ -675,10 +722,13 @@ int32_t w4a4_launch(ErrorSlot &slot, const DeviceState &dev, const uint8_t *w_co
   p.ldy = ldy;
   p.alpha = 1.0f / (d_in * d_w);
   p.epilogue = epilogue;
+  p.q_codes = q.codes;
+  p.q_scales = q.scales;
+  p.q_din = q.d_in;
   const bool swiglu = (epilogue & kEpilogueSwiglu) != 0u;
   // the fused SwiGLU needs the wide tile (gate and up boxes side by side); the plain product takes
   // the narrow one, two CTAs per SM
-  if (dev.w4a4_persistent != 0) {
+  if (dev.w4a4_persistent != 0 || (epilogue & (kEpilogueAdd | kEpilogueQuant)) != 0u) {  // those two epilogues exist only here
     const uint32_t tiles = (pad / kBM) * (swiglu ? n / 256u : (n + 255u) / 256u);
     const uint32_t ctas = tiles < static_cast<uint32_t>(dev.sm_count) ? tiles : static_cast<uint32_t>(dev.sm_count);
     const cudaError_t perr = launch(w4a4_gemm_persistent_kernel, dim3(ctas), dim3(192), Tile<256>::kSmemBytes, stream, dev.pdl != 0,
@@ -692,6 +742,44 @@ int32_t w4a4_launch(ErrorSlot &slot, const DeviceState &dev, const uint8_t *w_co
                                : launch(w4a4_gemm_kernel<128>, grid, dim3(192), Tile<128>::kSmemBytes, stream, dev.pdl != 0, map_a, map_b, p);
   if (err != cudaSuccess) return fail(slot, "nvfp4 prefill launch: %s", cudaGetErrorString(err));
   return 0;
+}
+}  // namespace
+
+int32_t w4a4_launch(ErrorSlot &slot, const DeviceState &dev, const uint8_t *w_codes, const uint8_t *w_scales, uint32_t n,
+                    uint32_t k, float d_w, float d_in, const uint16_t *x, uint32_t tokens, void *y, uint32_t ldy,
+                    uint32_t epilogue, uint8_t *workspace, cudaStream_t stream) {
+  const uint32_t pad = w4a4_tokens_pad(tokens);
+  uint8_t *a_codes = workspace + 256;
+  uint8_t *a_scales = a_codes + static_cast<uint64_t>(pad) * (k / 2u);
+  return w4a4_product(slot, dev, w_codes, w_scales, n, k, d_w, d_in, x, tokens, y, ldy, epilogue,
+                      reinterpret_cast<uint32_t *>(workspace), a_codes, a_scales, QuantTarget(), stream);
+}
+
+// Workspace of the MLP: the status line, x quantized (K = k), h quantized (K = inter).
+uint64_t w4a4_mlp_workspace_bytes(uint32_t k, uint32_t inter, uint32_t tokens) {
+  const uint64_t pad = w4a4_tokens_pad(tokens);
+  return 256u + pad * (k / 2u) + pad * (k / 16u) + pad * (inter / 2u) + pad * (inter / 16u);
+}
+
+int32_t w4a4_mlp_launch(ErrorSlot &slot, const DeviceState &dev, const uint8_t *gu_codes, const uint8_t *gu_scales, uint32_t gu_n,
+                        uint32_t k, float gu_dw, float gu_din, const uint8_t *dn_codes, const uint8_t *dn_scales, uint32_t dn_n,
+                        float dn_dw, float dn_din, const uint16_t *x, uint32_t tokens, void *y, uint32_t ldy, uint32_t epilogue,
+                        uint8_t *workspace, cudaStream_t stream) {
+  const uint64_t pad = w4a4_tokens_pad(tokens);
+  const uint32_t inter = gu_n / 2u;
+  uint32_t *status = reinterpret_cast<uint32_t *>(workspace);
+  uint8_t *x_codes = workspace + 256;
+  uint8_t *x_scales = x_codes + pad * (k / 2u);
+  QuantTarget h;
+  h.codes = x_scales + pad * (k / 16u);
+  h.scales = h.codes + pad * (inter / 2u);
+  h.d_in = dn_din;
+  if (w4a4_product(slot, dev, gu_codes, gu_scales, gu_n, k, gu_dw, gu_din, x, tokens, nullptr, 0, kEpilogueSwiglu | kEpilogueQuant,
+                   status, x_codes, x_scales, h, stream) != 0) {
+    return -1;
+  }
+  return w4a4_product(slot, dev, dn_codes, dn_scales, dn_n, inter, dn_dw, dn_din, nullptr, tokens, y, ldy, epilogue, status,
+                      h.codes, h.scales, QuantTarget(), stream);
 }
 
 }  // namespace b200q

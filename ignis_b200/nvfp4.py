@@ -228,6 +228,24 @@ def linear_swiglu(x: torch.Tensor, gate_up: Weight, out: torch.Tensor | None = N
     return h
 
 
+def mlp_workspace_bytes(gate_up_n: int, k: int, policy: int, tokens: int) -> int:
+    return int(_lib.load().b200q_nvfp4_mlp_workspace_bytes(gate_up_n, k, policy, tokens))
+
+
+def mlp(x: torch.Tensor, gate_up: Weight, down: Weight, workspace: Workspace, out: torch.Tensor | None = None,
+        policy: int = A16_ONLY, epilogue: int = STORE) -> torch.Tensor:
+    """``out (+)= down(silu(g) * u)``: ignis::prefill_swiglu::mlp (kernel/src/prefill_swiglu.h:100-107). Wide
+    calls under ``ALLOW_A4`` never write the intermediate matrix: the gate|up product's epilogue
+    quantizes it straight into the down product's operand."""
+    _check_x(x, gate_up.k)
+    tokens = x.shape[0]
+    y = _out(tokens, down.n, epilogue, out, x.device)
+    gu, dn = gate_up.c_struct(), down.c_struct()
+    _check(_lib.load().b200q_nvfp4_mlp(C.byref(gu), C.byref(dn), x.data_ptr(), tokens, y.data_ptr(), y.stride(0), epilogue, policy,
+                                        C.byref(workspace.c), _stream()))
+    return y
+
+
 def dequantize(w: Weight) -> torch.Tensor:
     """The logical weight as float32 ``[n, k]`` (the bit-exact dequant seam)."""
     out = torch.empty((w.n, w.k), dtype=torch.float32, device=w.codes.device)

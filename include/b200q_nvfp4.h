@@ -119,6 +119,23 @@ int32_t b200q_nvfp4_linear_swiglu(const b200q_nvfp4_weight *gate_up, const void 
                                   void *h, uint32_t ldh, uint32_t policy,
                                   const b200q_nvfp4_workspace *workspace, void *stream);
 
+/* The layers' MLP: y (+)= down(silu(g) * u), g | u = gate_up x. reference:
+ * ignis::prefill_swiglu::mlp (kernel/src/prefill_swiglu.h:100-107) and, below its widths, the
+ * linear_swiglu + linear_add pair it falls back to. `epilogue` is B200Q_NVFP4_STORE or
+ * B200Q_NVFP4_ADD (the residual form), optionally with B200Q_NVFP4_OUT_F32.
+ * Above 32 tokens under B200Q_NVFP4_ALLOW_A4 (k and n / 2 multiples of 256): x is quantized once,
+ * the gate|up product's epilogue writes BF16(silu(BF16(g)) * BF16(u)) already quantized under
+ * `down`'s input divisor - byte for byte what the down product's own quantizer would write from
+ * the BF16 matrix (gate_up_swiglu_nvfp4, prefill_swiglu.h:84-92), which is never written - and the
+ * down product reads it. Otherwise the decode route's fused SwiGLU writes h (BF16) into the
+ * workspace and the decode route's down product reads it.
+ * The workspace (256-byte aligned, b200q_nvfp4_mlp_workspace_bytes, its first 256 bytes cleared
+ * once by b200q_nvfp4_workspace_init) holds the operands in between. */
+uint64_t b200q_nvfp4_mlp_workspace_bytes(uint32_t gate_up_n, uint32_t k, uint32_t policy, uint32_t tokens);
+int32_t b200q_nvfp4_mlp(const b200q_nvfp4_weight *gate_up, const b200q_nvfp4_weight *down, const void *x,
+                        uint32_t tokens, void *y, uint32_t ldy, uint32_t epilogue, uint32_t policy,
+                        const b200q_nvfp4_workspace *workspace, void *stream);
+
 /* The logical weight as float32 [n][k], bit for bit the reference's host dequantizer
  * (kernel/vendor/tests/ops/quantized_weight.h:642-690). Not on the serving path: the seam the
  * decode is held to, as ignis_trellis_reconstruct is for the trellis. */

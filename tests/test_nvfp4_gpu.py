@@ -347,6 +347,39 @@ def test_w4a4_fused_swiglu(nv, oracle):
     assert np.linalg.norm(got - h16) <= 0.2 * np.linalg.norm(h16)
 
 
+@pytest.mark.parametrize("tokens", [5, 100])
+def test_mlp_matches_its_parts(nv, oracle, tokens):
+    """b200q_nvfp4_mlp against the same ops called one by one. Wide under ALLOW_A4: the gate|up
+    epilogue must write the bytes the down product's own quantizer writes from the BF16 h, so the
+    MLP's output equals linear(linear_swiglu(x)) bit for bit, and with ADD the residual form.
+    Narrow: the decode route twice."""
+    k, inter, n_out = 512, 512, 384
+    rng = np.random.default_rng(7 + tokens)
+    gc, gs, d_w = make_weight(rng, 2 * inter, k)
+    dc, ds, _ = make_weight(rng, n_out, inter)
+    gate_up = nv.Weight.from_planes(gc, gs, d_w, 448.0)
+    down = nv.Weight.from_planes(dc, ds, d_w, 96.0)
+    x = torch.randn(tokens, k, generator=torch.Generator().manual_seed(tokens)).to(torch.bfloat16).cuda()
+    policy = nv.ALLOW_A4
+    ws_a = nv.Workspace(max(nv.workspace_bytes(2 * inter, k, policy, tokens), nv.workspace_bytes(n_out, inter, policy, tokens)))
+    h = nv.linear_swiglu(x, gate_up, policy=policy, workspace=ws_a)
+    want = nv.linear(h, down, policy=policy, workspace=ws_a).clone()
+    ws = nv.Workspace(nv.mlp_workspace_bytes(2 * inter, k, policy, tokens))
+    got = nv.mlp(x, gate_up, down, ws, policy=policy)
+    assert ws.status() == 0
+    assert torch.equal(got, want)
+    residual = torch.randn(tokens, n_out, generator=torch.Generator().manual_seed(1)).to(torch.bfloat16).cuda()
+    want_add = nv.linear(h, down, out=residual.clone(), policy=policy, epilogue=nv.ADD, workspace=ws_a)
+    got_add = nv.mlp(x, gate_up, down, ws, out=residual.clone(), policy=policy, epilogue=nv.ADD)
+    assert torch.equal(got_add, want_add)
+    # the residual form rounds once: BF16(acc + residual), not BF16(BF16(acc) + residual)
+    y32 = nv.linear(h, down, policy=policy, epilogue=nv.OUT_F32, workspace=ws_a)
+    once = (y32 + residual.float()).to(torch.bfloat16)
+    assert torch.equal(got_add, once)
+    with pytest.raises(nv.Nvfp4Error):
+        nv.mlp(x, down, down, ws, policy=policy)   # a fused parent needs n a multiple of 256 (and down.k = n / 2)
+
+
 @pytest.mark.parametrize("tokens,n,k", [(128, 256, 256), (200, 256, 512), (33, 128, 1024), (300, 384, 768), (256, 512, 2048)])
 def test_w4a4_tensor_core_route(nv, oracle, tokens, n, k):
     rng = np.random.default_rng(tokens + n + k)
