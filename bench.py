@@ -173,7 +173,7 @@ def run_reference_arm(args) -> None:
     value = sum(values) / len(values)
     line = {"impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus, "steps": args.steps,
             "warmup": args.warmup, "ms_per_step": total / max(1, args.steps) * 1e3, "higher_is_better": True,
-            "scaling": "strong", "vs_baseline": None, "dtype": "f64", "data": "synthetic",
+            "scaling": args.scaling, "vs_baseline": None, "dtype": "f64", "data": "synthetic",
             "config": {"workload": "configs[1]: NVFP4 decode, 8 lanes, 27B-style dense layer (CPU: a bounded row sample per step)"},
             "cpu_baseline": {"value": value, "unit": UNIT, **desc},
             "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
@@ -321,7 +321,7 @@ def run_moe_workload(args) -> None:
     device = torch.device("cuda", local_rank)
     if world > 1:
         dist.init_process_group("nccl", device_id=device)
-    tokens = args.tokens if args.tokens > 8 else 4096
+    tokens = args.moe_tokens
     m = build_moe_workload(tokens, device, rank, world)
     out_host = torch.empty((m["x"].shape[0], 2048), dtype=torch.bfloat16).pin_memory()
     stream = torch.cuda.Stream()
@@ -533,7 +533,11 @@ def run_cuda_arm(args) -> None:
         dist.init_process_group("nccl", device_id=device)
     nvfp4.prepare()
     tokens = args.tokens
-    weights, host_inputs, inputs, outputs = build_workload(args.layers, rank, world, tokens, device)
+    # How the matrices shard over N ranks: always column-wise (output rows) with no exchange inside
+    # a product. "weak" (default): every rank holds a full configs[1] layer set - the shard of a
+    # layer N times as wide - so per-GPU work is fixed. "strong": configs[1] itself is cut in N.
+    split = world if args.scaling == "strong" else 1
+    weights, host_inputs, inputs, outputs = build_workload(args.layers, rank, split, tokens, device)
     by_name = {name: (n, k, src) for name, n, k, src in LAYER}
     calls = GROUPS if args.group else [[name] for name, *_ in LAYER]
 
@@ -603,7 +607,7 @@ def run_cuda_arm(args) -> None:
     if rank != 0:
         return
 
-    per_rank_bytes = layer_algorithmic_bytes(tokens, world) * args.layers
+    per_rank_bytes = layer_algorithmic_bytes(tokens, split) * args.layers
     job_bytes = per_rank_bytes * world
     ms_per_step = device_ms / args.steps
     value = job_bytes / (ms_per_step * 1e-3) / 1e9
@@ -612,10 +616,12 @@ def run_cuda_arm(args) -> None:
     per_gpu = value / world
     line = {
         "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
-        "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f16xf16->f32",
+        "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": args.scaling, "vs_baseline": None, "dtype": "f16xf16->f32",
         "data": "synthetic",
         "config": {"workload": "configs[1]: NVFP4 decode, 8 lanes (M=8), 27B-style dense layer (q,k,v,o,gate,up,down), hidden 5120",
-                   "layers": args.layers, "tokens": tokens, "policy": "A16", "sharding": f"column-wise over N, {world} rank(s)",
+                   "layers": args.layers, "tokens": tokens, "policy": "A16", "sharding": (f"column-wise over N, {world} rank(s); " +
+                                ("every rank holds configs[1]-sized shards of a layer N times as wide (per-GPU work fixed)"
+                                 if args.scaling == "weak" else "configs[1] itself cut in N (total work fixed)")),
                    "calls_per_layer": len(calls), "cuda_graph": bool(args.graph),
                    "l2": "inputs larger than L2: %.2f GB of distinct weights per rank per step" % (per_rank_bytes / 1e9),
                    "collective": "none (outputs stay sharded)"},
@@ -627,7 +633,7 @@ def run_cuda_arm(args) -> None:
         "roofline": {"bound": "hbm", "achieved": per_gpu, "peak": peak, "unit": "GB/s", "frac": per_gpu / peak,
                      "peak_source": f"{peak_kind} copy bandwidth", "frac_of_nominal_8000": per_gpu / 8000.0,
                      "kernel": "nvfp4_gemv_kernel<1>", "bytes_per_launch": per_rank_bytes / launches_per_step,
-                     "us_per_launch": ms_per_step * 1e3 / launches_per_step, "traffic": TRAFFIC_PER_LAUNCH},
+                     "us_per_launch": ms_per_step * 1e3 / launches_per_step, "traffic": TRAFFIC_PER_LAUNCH / split},
     }
     if world == 1 and not args.no_cpu_baseline:
         v, desc = cpu_sample()
@@ -651,6 +657,9 @@ def main() -> None:
     ap.add_argument("--tokens", type=int, default=8)
     ap.add_argument("--group", type=int, default=1, help="1: q|k|v and gate|up share one launch each; 0: seven launches per layer")
     ap.add_argument("--graph", type=int, default=1, help="replay the step as one CUDA graph")
+    ap.add_argument("--scaling", default="weak", choices=["weak", "strong"],
+                    help="decode workload under torchrun: weak = per-GPU work fixed (default), strong = configs[1] cut in N")
+    ap.add_argument("--moe-tokens", type=int, default=4096, help="tokens of the --workload moe step (configs[4]: 4096; up to 8 takes the decode entry's item size)")
     ap.add_argument("--mlp", type=int, default=0, help="with --workload prefill: 1 runs the fused MLP entry instead of two plain products")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--workload", default="decode", choices=["decode", "prefill", "trellis", "moe"],
