@@ -470,12 +470,19 @@ def run_side_workload(args) -> None:
             weights, inputs, outputs, nbytes = build_trellis_workload(args.layers, 0, 1, args.tokens, device)
             by = {name: (in_, out) for name, in_, out in TRELLIS_LAYER}
 
+            # q | k | v share one launch (narrow weights alone cannot fill the device); the wide ones run alone
+            groups = [["q", "k", "v"], ["o"], ["gate"], ["up"], ["down"]] if args.group else [[n] for n, *_ in TRELLIS_LAYER]
+
             def one_step() -> None:
                 for layer in weights:
-                    for name, w in layer.items():
-                        trellis.linear(w, inputs[by[name][0]], out=outputs[name])
+                    for names in groups:
+                        src = inputs[by[names[0]][0]]
+                        if len(names) == 1:
+                            trellis.linear(layer[names[0]], src, out=outputs[names[0]])
+                        else:
+                            trellis.linear_group([layer[n] for n in names], src, outs=[outputs[n] for n in names])
 
-            launches = 7 * args.layers
+            launches = len(groups) * args.layers
             metric, unit, work = "trellis_gemv_gbs", "GB/s", nbytes / 1e9
             workload = f"configs[3]: trellis 3 bpw decode, M={args.tokens}, 27B-style layer x {args.layers} layers of distinct weights"
         one_step()

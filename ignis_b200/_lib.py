@@ -65,6 +65,8 @@ TRELLIS_SYMBOLS = {
     "ignis_trellis_workspace_init": (C.c_int32, [C.POINTER(Workspace), C.c_void_p]),
     "ignis_trellis_linear": (C.c_int32, [C.POINTER(TrellisWeight), C.c_void_p, C.c_uint32, C.c_void_p, C.c_uint32,
                                          C.c_uint32, C.POINTER(Workspace), C.c_void_p]),
+    "b200q_trellis_linear_group": (C.c_int32, [C.POINTER(C.POINTER(TrellisWeight)), C.c_uint32, C.c_void_p, C.c_uint32,
+                                               C.POINTER(C.c_void_p), C.POINTER(C.c_uint32), C.c_uint32, C.c_void_p]),
     "ignis_trellis_linear_swiglu": (C.c_int32, [C.POINTER(TrellisWeight), C.POINTER(TrellisWeight), C.c_void_p,
                                                 C.c_uint32, C.c_void_p, C.c_uint32, C.POINTER(Workspace), C.c_void_p]),
     "ignis_trellis_reconstruct": (C.c_int32, [C.POINTER(TrellisWeight), C.c_void_p, C.c_void_p]),

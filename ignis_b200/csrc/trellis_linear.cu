@@ -72,11 +72,22 @@ struct TrellisSide {
   uint32_t tile_stride;
 };
 
+constexpr uint32_t kMaxGroup = 4;  // weights one grouped call takes
+
+// One weight of a call with its output and the first CTA that serves it.
+struct TrellisTarget {
+  TrellisSide side;
+  uint16_t *y;  // BF16 [tokens][ldy]
+  uint32_t ldy;
+  uint32_t cta_begin;
+};
+
 struct TrellisParams {
-  TrellisSide side[2];  // [1] is the up weight of a SwiGLU call
-  const uint16_t *x;    // BF16 [tokens][in]
-  uint16_t *y;          // BF16 [tokens][ldy]
-  uint32_t in, out, tokens, ldy;
+  TrellisTarget target[kMaxGroup];  // the weights of a grouped call share x (and `in`); a plain call has one
+  TrellisSide up;                   // the up weight of a SwiGLU call (target[0] is the gate)
+  const uint16_t *x;                // BF16 [tokens][in]
+  uint32_t count;
+  uint32_t in, tokens;
   uint32_t epilogue;    // 0 store, 1 add, 2 SwiGLU
   uint32_t kc;          // cluster size: slices of the input blocks
   uint32_t chunk;       // 128-input blocks of rotated activations shared memory holds at a time
@@ -105,13 +116,26 @@ __device__ __forceinline__ void decode_tile(uint32_t k2, uint32_t a, uint32_t b,
 // hundred bytes of code that stay in the instruction cache. The words of the next 128-input block
 // are requested as the current block's are consumed (24 registers per weight in flight per lane).
 // NT token tiles of 8 share every decoded tile (up to 64 tokens a pass).
-template <int K2, int NT, int SIDES>
+template <int K2, int NT, int SIDES, bool GROUP>
 __global__ void __launch_bounds__(kThreads, (SIDES == 1 && NT <= 2) ? 3 : ((NT * SIDES <= 8) ? 2 : 1))
     trellis_linear_kernel(const __grid_constant__ TrellisParams p) {
   extern __shared__ __align__(16) uint8_t smem_raw[];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const uint32_t rank = cluster_rank(), kc = p.kc;
-  const uint32_t col_block = blockIdx.x / kc;
+  // The target this CTA serves. A plain call (GROUP false) reads target[0] straight from the launch
+  // constants, which keeps the walk's address arithmetic on the uniform datapath; a grouped call
+  // selects a copy, and pays about 5 % more instructions per tile for it.
+  TrellisTarget picked = {};
+  if (GROUP) {
+    picked = p.target[0];
+    if (p.count > 3u && blockIdx.x >= p.target[3].cta_begin) picked = p.target[3];
+    else if (p.count > 2u && blockIdx.x >= p.target[2].cta_begin) picked = p.target[2];
+    else if (blockIdx.x >= p.target[1].cta_begin) picked = p.target[1];
+  }
+  const TrellisSide &side0 = GROUP ? picked.side : p.target[0].side;
+  uint16_t *const y_out = GROUP ? picked.y : p.target[0].y;
+  const uint32_t ldy = GROUP ? picked.ldy : p.target[0].ldy;
+  const uint32_t col_block = (blockIdx.x - (GROUP ? picked.cta_begin : 0u)) / kc;
 
   const uint32_t nblk = p.in / 128u;
   const uint32_t b0 = static_cast<uint32_t>(static_cast<uint64_t>(nblk) * rank / kc);
@@ -130,7 +154,7 @@ __global__ void __launch_bounds__(kThreads, (SIDES == 1 && NT <= 2) ? 3 : ((NT *
   int64_t step_words[SIDES];
 #pragma unroll
   for (int sd = 0; sd < SIDES; ++sd) {
-    const TrellisSide &S = p.side[sd];
+    const TrellisSide &S = sd == 0 ? side0 : p.up;
     win[sd] = lane_window(K2 != 0 ? static_cast<uint32_t>(K2) : S.k2, lane);
     const uint32_t tile_words = 4u * S.k2;
     step_words[sd] = static_cast<int64_t>(S.tile_stride) * tile_words;
@@ -179,7 +203,7 @@ __global__ void __launch_bounds__(kThreads, (SIDES == 1 && NT <= 2) ? 3 : ((NT *
         if (tok < p.tokens) {
           const size_t k0 = static_cast<size_t>(cb + bl) * 128u + 4u * lane;
           const uint2 xb = ldg64_coherent(p.x + static_cast<size_t>(tok) * p.in + k0);
-          const uint2 sb = *reinterpret_cast<const uint2 *>(p.side[sd].suh + k0);
+          const uint2 sb = *reinterpret_cast<const uint2 *>((sd == 0 ? side0.suh : p.up.suh) + k0);
           const __half2 s01 = *reinterpret_cast<const __half2 *>(&sb.x), s23 = *reinterpret_cast<const __half2 *>(&sb.y);
           v[0] = bf16_bits_to_f32(xb.x & 0xFFFFu) * __low2float(s01);
           v[1] = __uint_as_float(xb.x & 0xFFFF0000u) * __high2float(s01);
@@ -242,7 +266,7 @@ __global__ void __launch_bounds__(kThreads, (SIDES == 1 && NT <= 2) ? 3 : ((NT *
 #pragma unroll
         for (int sd = 0; sd < SIDES; ++sd) {
           uint32_t frag[4];
-          decode_tile<K2>(p.side[sd].k2, bw[sd].w[kt][0], bw[sd].w[kt][1], bw[sd].w[kt][2], win[sd].off, frag);
+          decode_tile<K2>(sd == 0 ? side0.k2 : p.up.k2, bw[sd].w[kt][0], bw[sd].w[kt][1], bw[sd].w[kt][2], win[sd].off, frag);
           if (more) {  // the same step of the next block, into the registers just consumed
 #pragma unroll
             for (int c = 0; c < 3; ++c) bw[sd].w[kt][c] = __ldg(q[sd][c] + kt * step_words[sd]);
@@ -287,14 +311,14 @@ __global__ void __launch_bounds__(kThreads, (SIDES == 1 && NT <= 2) ? 3 : ((NT *
         v[sd][i] = sum;
       }
       hadamard128(v[sd], lane);
-      const uint2 sv = *reinterpret_cast<const uint2 *>(p.side[sd].svh + static_cast<size_t>(col_block) * 128u + 4u * lane);
+      const uint2 sv = *reinterpret_cast<const uint2 *>((sd == 0 ? side0.svh : p.up.svh) + static_cast<size_t>(col_block) * 128u + 4u * lane);
       const __half2 s01 = *reinterpret_cast<const __half2 *>(&sv.x), s23 = *reinterpret_cast<const __half2 *>(&sv.y);
       v[sd][0] *= __low2float(s01);
       v[sd][1] *= __high2float(s01);
       v[sd][2] *= __low2float(s23);
       v[sd][3] *= __high2float(s23);
     }
-    uint16_t *dst = p.y + static_cast<size_t>(tok) * p.ldy + static_cast<size_t>(col_block) * 128u + 4u * lane;
+    uint16_t *dst = y_out + static_cast<size_t>(tok) * ldy + static_cast<size_t>(col_block) * 128u + 4u * lane;
     float r[4];
 #pragma unroll
     for (int i = 0; i < 4; ++i) r[i] = SIDES == 2 ? v[0][i] / (1.0f + __expf(-v[0][i])) * v[SIDES - 1][i] : v[0][i];
@@ -397,7 +421,8 @@ uint32_t plan_kc(const DeviceState &dev, uint32_t in, uint32_t out, int nt, int 
 
 template <int K2, int NT, int SIDES>
 cudaError_t launch_linear(const cudaLaunchConfig_t &config, const TrellisParams &p) {
-  return cudaLaunchKernelEx(&config, trellis_linear_kernel<K2, NT, SIDES>, p);
+  if (SIDES == 1 && p.count > 1u) return cudaLaunchKernelEx(&config, trellis_linear_kernel<K2, NT, 1, true>, p);
+  return cudaLaunchKernelEx(&config, trellis_linear_kernel<K2, NT, SIDES, false>, p);
 }
 
 template <int K2, int NT>
@@ -429,8 +454,13 @@ cudaError_t launch_k2(uint32_t k2, int nt, int sides, const cudaLaunchConfig_t &
 
 template <int K2, int NT, int SIDES>
 cudaError_t set_linear_attr() {
-  return cudaFuncSetAttribute(trellis_linear_kernel<K2, NT, SIDES>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                              static_cast<int>(kLinearMaxSmem));
+  cudaError_t err = cudaFuncSetAttribute(trellis_linear_kernel<K2, NT, SIDES, false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         static_cast<int>(kLinearMaxSmem));
+  if (err == cudaSuccess && SIDES == 1) {
+    err = cudaFuncSetAttribute(trellis_linear_kernel<K2, NT, 1, true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                               static_cast<int>(kLinearMaxSmem));
+  }
+  return err;
 }
 
 template <int K2>
@@ -457,44 +487,63 @@ cudaError_t set_all_linear_attrs() {
   return err;
 }
 
-int32_t run_linear(ErrorSlot &slot, const ignis_trellis_weight *a, const ignis_trellis_weight *b, const void *x,
-                   uint32_t tokens, void *y, uint32_t ldy, uint32_t epilogue, void *stream, const char *what) {
-  if (check_weight(slot, a, what) != 0) return -1;
+// `count` weights over one x (count > 1: a grouped call, no SwiGLU), or the gate/up pair of a
+// SwiGLU call (`up` non-NULL, count 1).
+int32_t run_linear(ErrorSlot &slot, const ignis_trellis_weight *const *w, uint32_t count, const ignis_trellis_weight *up,
+                   const void *x, uint32_t tokens, void *const *y, const uint32_t *ldy, uint32_t epilogue, void *stream,
+                   const char *what) {
+  if (w == nullptr || y == nullptr || ldy == nullptr) return fail(slot, "%s: NULL argument array", what);
+  if (count == 0 || count > kMaxGroup) return fail(slot, "%s: count = %u is outside 1..%u", what, count, kMaxGroup);
   const bool swiglu = epilogue == kEpiSwiglu;
+  if (epilogue > kEpiSwiglu) return fail(slot, "%s: unknown epilogue %u", what, epilogue);
+  for (uint32_t i = 0; i < count; ++i) {
+    if (check_weight(slot, w[i], what) != 0) return -1;
+    if (w[i]->in != w[0]->in) return fail(slot, "%s: the weights of a group must share `in`", what);
+    if (y[i] == nullptr || !aligned(y[i], 8)) return fail(slot, "%s: y is NULL or not 8-byte aligned", what);
+    if ((ldy[i] % 4u) != 0 || ldy[i] < w[i]->out) return fail(slot, "%s: ldy = %u must be a multiple of 4 and at least out", what, ldy[i]);
+  }
   if (swiglu) {
-    if (check_weight(slot, b, what) != 0) return -1;
-    if (a->in != b->in || a->out != b->out) return fail(slot, "%s: gate and up must share (in, out)", what);
+    if (check_weight(slot, up, what) != 0) return -1;
+    if (w[0]->in != up->in || w[0]->out != up->out) return fail(slot, "%s: gate and up must share (in, out)", what);
   }
   if (tokens == 0) return fail(slot, "%s: tokens must be positive", what);
   if (x == nullptr || !aligned(x, 16)) return fail(slot, "%s: x is NULL or not 16-byte aligned", what);
-  if (y == nullptr || !aligned(y, 8)) return fail(slot, "%s: y is NULL or not 8-byte aligned", what);
-  if ((ldy % 4u) != 0 || ldy < a->out) return fail(slot, "%s: ldy = %u must be a multiple of 4 and at least out", what, ldy);
-  if (epilogue > kEpiSwiglu) return fail(slot, "%s: unknown epilogue %u", what, epilogue);
   const DeviceState *dev = prepared(slot, what);
   if (dev == nullptr) return -1;
   const int sides = swiglu ? 2 : 1;
+  const uint32_t in = w[0]->in;
+  uint32_t out_total = 0, k2 = w[0]->k2;
+  for (uint32_t i = 0; i < count; ++i) {
+    out_total += w[i]->out;
+    if (w[i]->k2 != k2) k2 = 0u;  // 0: every weight decodes with its own width
+  }
+  if (swiglu && up->k2 != k2) k2 = 0u;
   TrellisParams p = {};
-  p.side[0] = make_side(a);
-  p.side[1] = swiglu ? make_side(b) : p.side[0];
-  p.in = a->in;
-  p.out = a->out;
-  p.ldy = ldy;
+  p.count = count;
+  p.in = in;
   p.epilogue = epilogue;
-  const uint32_t k2 = (swiglu && a->k2 != b->k2) ? 0u : a->k2;  // 0: each side decodes with its own width
+  if (swiglu) p.up = make_side(up);
   // passes of up to 64 tokens (IGNIS_TRELLIS_DECODE_MAX_TOKENS): every decoded tile serves the
   // pass's token tiles of 8
   for (uint32_t t0 = 0; t0 < tokens; t0 += IGNIS_TRELLIS_DECODE_MAX_TOKENS) {
     p.tokens = tokens - t0 < IGNIS_TRELLIS_DECODE_MAX_TOKENS ? tokens - t0 : IGNIS_TRELLIS_DECODE_MAX_TOKENS;
     const int nt = p.tokens <= 8 ? 1 : (p.tokens <= 16 ? 2 : (p.tokens <= 32 ? 4 : 8));
-    const uint32_t kc = plan_kc(*dev, a->in, a->out, nt, sides);
-    const uint32_t slice = (a->in / 128u + kc - 1) / kc;
+    const uint32_t kc = plan_kc(*dev, in, out_total, nt, sides);
+    const uint32_t slice = (in / 128u + kc - 1) / kc;
     const uint32_t cap = chunk_cap(nt, sides);
     p.kc = kc;
     p.chunk = slice < cap ? slice : cap;
-    p.x = static_cast<const uint16_t *>(x) + static_cast<size_t>(t0) * a->in;
-    p.y = static_cast<uint16_t *>(y) + static_cast<size_t>(t0) * ldy;
+    p.x = static_cast<const uint16_t *>(x) + static_cast<size_t>(t0) * in;
+    uint32_t ctas = 0;
+    for (uint32_t i = 0; i < count; ++i) {
+      p.target[i].side = make_side(w[i]);
+      p.target[i].y = static_cast<uint16_t *>(y[i]) + static_cast<size_t>(t0) * ldy[i];
+      p.target[i].ldy = ldy[i];
+      p.target[i].cta_begin = ctas;
+      ctas += (w[i]->out / 128u) * kc;
+    }
     cudaLaunchConfig_t config = {};
-    config.gridDim = dim3((a->out / 128u) * kc, 1, 1);
+    config.gridDim = dim3(ctas, 1, 1);
     config.blockDim = dim3(kThreads, 1, 1);
     config.dynamicSmemBytes = linear_smem_bytes(p.chunk, nt, sides);
     config.stream = static_cast<cudaStream_t>(stream);
@@ -578,14 +627,28 @@ int32_t ignis_trellis_linear(const ignis_trellis_weight *w, const void *x, uint3
   if (epilogue != IGNIS_TRELLIS_STORE && epilogue != IGNIS_TRELLIS_ADD) {
     return fail(trellis_error(), "ignis_trellis_linear: unknown epilogue %u", epilogue);
   }
-  return run_linear(trellis_error(), w, nullptr, x, tokens, y, ldy, epilogue, stream, "ignis_trellis_linear");
+  const ignis_trellis_weight *ws[1] = {w};
+  void *ys[1] = {y};
+  const uint32_t lds[1] = {ldy};
+  return run_linear(trellis_error(), ws, 1, nullptr, x, tokens, ys, lds, epilogue, stream, "ignis_trellis_linear");
+}
+
+int32_t b200q_trellis_linear_group(const ignis_trellis_weight *const *w, uint32_t count, const void *x, uint32_t tokens,
+                                   void *const *y, const uint32_t *ldy, uint32_t epilogue, void *stream) {
+  if (epilogue != IGNIS_TRELLIS_STORE && epilogue != IGNIS_TRELLIS_ADD) {
+    return fail(trellis_error(), "b200q_trellis_linear_group: unknown epilogue %u", epilogue);
+  }
+  return run_linear(trellis_error(), w, count, nullptr, x, tokens, y, ldy, epilogue, stream, "b200q_trellis_linear_group");
 }
 
 int32_t ignis_trellis_linear_swiglu(const ignis_trellis_weight *gate, const ignis_trellis_weight *up, const void *x,
                                     uint32_t tokens, void *h, uint32_t ldh, const ignis_trellis_workspace *workspace,
                                     void *stream) {
   (void)workspace;
-  return run_linear(trellis_error(), gate, up, x, tokens, h, ldh, kEpiSwiglu, stream, "ignis_trellis_linear_swiglu");
+  const ignis_trellis_weight *ws[1] = {gate};
+  void *ys[1] = {h};
+  const uint32_t lds[1] = {ldh};
+  return run_linear(trellis_error(), ws, 1, up, x, tokens, ys, lds, kEpiSwiglu, stream, "ignis_trellis_linear_swiglu");
 }
 
 int32_t ignis_trellis_reconstruct(const ignis_trellis_weight *w, void *w_f16, void *stream) {

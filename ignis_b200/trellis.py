@@ -130,6 +130,27 @@ def linear(w: Weight, x: torch.Tensor, out: torch.Tensor | None = None, epilogue
     return out
 
 
+def linear_group(weights: list[Weight], x: torch.Tensor, outs: list[torch.Tensor] | None = None,
+                 epilogue: int = STORE) -> list[torch.Tensor]:
+    """Up to four weights of the same `in` over one x in one launch (``b200q_trellis_linear_group``;
+    not in the reference's ABI): the bits of separate ``linear`` calls."""
+    if not weights:
+        raise TrellisError("linear_group needs at least one weight")
+    _check_x(x, weights[0].in_)
+    tokens = x.shape[0]
+    if outs is None:
+        if epilogue == ADD:
+            raise TrellisError("the ADD epilogue accumulates into `outs`, which must be given")
+        outs = [torch.empty((tokens, w.out), dtype=torch.bfloat16, device=x.device) for w in weights]
+    structs = [w.c_struct() for w in weights]
+    count = len(weights)
+    wp = (C.POINTER(_lib.TrellisWeight) * count)(*[C.pointer(s) for s in structs])
+    yp = (C.c_void_p * count)(*[y.data_ptr() for y in outs])
+    ld = (C.c_uint32 * count)(*[y.stride(0) for y in outs])
+    _check(_lib.load().b200q_trellis_linear_group(wp, count, x.data_ptr(), tokens, yp, ld, epilogue, _stream()))
+    return outs
+
+
 def linear_swiglu(gate: Weight, up: Weight, x: torch.Tensor, out: torch.Tensor | None = None,
                   workspace: WorkspaceBuffer | None = None) -> torch.Tensor:
     """``h = silu(x G) * (x U)`` (``ignis_trellis_linear_swiglu``)."""

@@ -89,6 +89,14 @@ int32_t ignis_trellis_linear_swiglu(const ignis_trellis_weight *gate, const igni
                                     const void *x, uint32_t tokens, void *h, uint32_t ldh,
                                     const ignis_trellis_workspace *workspace, void *stream);
 
+/* Not in the reference's ABI: up to 4 weights of the same `in` applied to the same x in one launch,
+ * weight i writing y[i][t][..ldy[i]] (q | k | v and the like: a narrow weight alone cannot fill
+ * the device, and every launch has a fixed cost). Same arithmetic and bits as `count` separate
+ * ignis_trellis_linear calls; STORE or ADD. Needs no workspace. */
+int32_t b200q_trellis_linear_group(const ignis_trellis_weight *const *w, uint32_t count, const void *x,
+                                   uint32_t tokens, void *const *y, const uint32_t *ldy, uint32_t epilogue,
+                                   void *stream);
+
 /* `inner` decoded to fp16 [in][out] row-major, bit for bit exllamav3's `reconstruct`.
  * reference: ignis_trellis_linear.h:145 */
 int32_t ignis_trellis_reconstruct(const ignis_trellis_weight *w, void *w_f16, void *stream);

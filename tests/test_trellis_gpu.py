@@ -200,6 +200,35 @@ def test_epilogues_views_and_swiglu(tr, oracle):
     assert np.abs(got - want).max() <= 2.0 ** -6 * np.abs(want).max()
 
 
+@pytest.mark.parametrize("tokens", [3, 8, 21])
+def test_group_gives_the_bits_of_separate_calls(tr, oracle, tokens):
+    """q | k | v style: three weights of one `in`, different widths and bit widths, in one launch
+    (b200q_trellis_linear_group) against three ignis_trellis_linear calls; then ADD into strided
+    outputs. Same arithmetic, so the same bits."""
+    in_ = 384
+    rng = np.random.default_rng(40 + tokens)
+    ws = []
+    for i, (out, k2) in enumerate([(512, 6), (128, 4), (256, 8)]):
+        words = oracle.hash_trellis_words(900 + i, in_, out, k2)
+        ws.append(tr.Weight.from_numpy(words, make_scales(rng, in_, 0.05), make_scales(rng, out, 0.03), k2, in_, out))
+    x = torch.randn(tokens, in_, generator=torch.Generator().manual_seed(tokens)).to(torch.bfloat16).cuda()
+    separate = [tr.linear(w, x) for w in ws]
+    together = tr.linear_group(ws, x)
+    for a, b in zip(separate, together):
+        assert torch.equal(a, b)
+    same_k2 = tr.linear_group([ws[0], ws[0]], x)
+    assert torch.equal(same_k2[0], separate[0]) and torch.equal(same_k2[1], separate[0])
+    bases = [torch.randn(tokens, w.out + 64, generator=torch.Generator().manual_seed(i)).to(torch.bfloat16).cuda() for i, w in enumerate(ws)]
+    want = [tr.linear(w, x, out=b.clone()[:, : w.out], epilogue=tr.ADD) for w, b in zip(ws, bases)]
+    outs = [b.clone() for b in bases]
+    tr.linear_group(ws, x, outs=[o[:, : w.out] for o, w in zip(outs, ws)], epilogue=tr.ADD)
+    for o, w, b, wt in zip(outs, ws, bases, want):
+        assert torch.equal(o[:, : w.out], wt) and torch.equal(o[:, w.out:], b[:, w.out:])
+    with pytest.raises(tr.TrellisError):
+        other = tr.Weight.from_numpy(oracle.hash_trellis_words(7, 256, 128, 6), make_scales(rng, 256, 0.05), make_scales(rng, 128, 0.03), 6, 256, 128)
+        tr.linear_group([ws[0], other], x)   # different `in`
+
+
 def test_full_size_gate_projection(tr, oracle):
     """configs[3]: 5120 -> 17408 at 3 bits per weight, 8 tokens."""
     in_, out, k2 = 5120, 17408, 6
