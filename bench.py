@@ -548,22 +548,43 @@ def run_cuda_arm(args) -> None:
     by_name = {name: (n, k, src) for name, n, k, src in LAYER}
     calls = GROUPS if args.group else [[name] for name, *_ in LAYER]
 
+    gather = args.gather == 1 and world > 1
+    fused = args.gather == 2 and world > 1
+    if gather:
+        from ignis_b200 import shard
+
+        full = {name: torch.empty(tokens, outputs[name].shape[1] * world, dtype=torch.bfloat16, device=device) for name in outputs}
+    if fused:
+        from ignis_b200 import shard
+
+        peer = shard.PeerOutputs({name: (tokens, outputs[name].shape[1] * world) for name in outputs})
+
     def one_step() -> None:
         for layer in weights:
             for names in calls:
                 src = inputs[by_name[names[0]][2]]
-                if len(names) == 1:
+                if fused:
+                    # every rank's epilogue stores its columns into all ranks' full-width buffers; the
+                    # device barrier behind it is all that is left of the all-gather
+                    ws = [layer[nm] for nm in names]
+                    nvfp4.linear_group_scatter(src, ws, [peer.pointers(nm) for nm in names], [w.n * world for w in ws],
+                                               [w.n * rank for w in ws])
+                    peer.barrier()
+                elif len(names) == 1:
                     nvfp4.linear(src, layer[names[0]], out=outputs[names[0]])
                 else:
                     nvfp4.linear_group(src, [layer[nm] for nm in names], outs=[outputs[nm] for nm in names])
+                if gather:   # rejoin the column shards where a consumer would need the full width
+                    for nm in names:
+                        shard.gather_columns(outputs[nm], out=full[nm])
 
-    launches_per_step = len(calls) * args.layers
+    launches_per_step = len(calls) * args.layers * (2 if fused else 1)   # the fused form adds a barrier launch per call
     stream = torch.cuda.Stream()
     graph = None
     with torch.cuda.stream(stream):
         one_step()  # untimed: first-launch costs
         stream.synchronize()
-        if args.graph:
+        if args.graph and not gather:   # the collectives run outside a graph
             graph = torch.cuda.CUDAGraph()
             with torch.cuda.graph(graph, stream=stream):
                 one_step()
@@ -629,9 +650,12 @@ def run_cuda_arm(args) -> None:
                    "layers": args.layers, "tokens": tokens, "policy": "A16", "sharding": (f"column-wise over N, {world} rank(s); " +
                                 ("every rank holds configs[1]-sized shards of a layer N times as wide (per-GPU work fixed)"
                                  if args.scaling == "weak" else "configs[1] itself cut in N (total work fixed)")),
-                   "calls_per_layer": len(calls), "cuda_graph": bool(args.graph),
+                   "calls_per_layer": len(calls), "cuda_graph": bool(args.graph) and not gather,
                    "l2": "inputs larger than L2: %.2f GB of distinct weights per rank per step" % (per_rank_bytes / 1e9),
-                   "collective": "none (outputs stay sharded)"},
+                   "collective": ("NCCL all-gather of every output (%d per layer)" % len(LAYER)) if gather else
+                                 ("fused: epilogues store into every rank's buffer over NVLink, one device barrier per call" if fused
+                                  else "none (outputs stay sharded)"),
+                   **({"barrier_timeouts": peer.missing()} if fused else {})},
         "e2e": {"value": e2e_value, "unit": UNIT,
                 "h2d_bytes_per_step": sum(t.numel() * 2 for t in host_inputs.values()),
                 "d2h_bytes_per_step": outputs["down"].numel() * 2},
@@ -666,6 +690,7 @@ def main() -> None:
     ap.add_argument("--graph", type=int, default=1, help="replay the step as one CUDA graph")
     ap.add_argument("--scaling", default="weak", choices=["weak", "strong"],
                     help="decode workload under torchrun: weak = per-GPU work fixed (default), strong = configs[1] cut in N")
+    ap.add_argument("--gather", type=int, default=0, help="decode workload under torchrun: 1 all-gathers every output after its product (NCCL); 2 the fused form (peer stores + device barrier)")
     ap.add_argument("--moe-tokens", type=int, default=4096, help="tokens of the --workload moe step (configs[4]: 4096; up to 8 takes the decode entry's item size)")
     ap.add_argument("--mlp", type=int, default=0, help="with --workload prefill: 1 runs the fused MLP entry instead of two plain products")
     ap.add_argument("--no-cpu-baseline", action="store_true")

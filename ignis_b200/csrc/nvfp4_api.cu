@@ -34,9 +34,10 @@ const DeviceState *prepared_state(ErrorSlot &slot, const char *what) {
 }
 
 // The decode route over `count` weights that share x, in passes of at most 32 tokens.
+// `y` holds `peers` pointers per weight (weight i's at y[i * peers ..]); a plain product has one.
 int32_t decode_route(ErrorSlot &slot, const DeviceState &dev, const b200q_nvfp4_weight *const *w, uint32_t count,
                      const void *x, uint32_t tokens, void *const *y, const uint32_t *ldy, uint32_t epilogue,
-                     cudaStream_t stream) {
+                     cudaStream_t stream, uint32_t peers = 1) {
   const uint32_t k = w[0]->k;
   const bool swiglu = (epilogue & kEpilogueSwiglu) != 0u;
   const size_t out_elem = (epilogue & kEpilogueF32) ? 4u : 2u;
@@ -59,7 +60,10 @@ int32_t decode_route(ErrorSlot &slot, const DeviceState &dev, const b200q_nvfp4_
       GemvWeight &g = p.w[i];
       g.codes = static_cast<const uint8_t *>(w[i]->codes);
       g.scales = static_cast<const uint8_t *>(w[i]->scales);
-      g.y = static_cast<uint8_t *>(y[i]) + static_cast<size_t>(t0) * ldy[i] * out_elem;
+      for (uint32_t pp = 0; pp < peers; ++pp) {
+        g.y[pp] = static_cast<uint8_t *>(y[i * peers + pp]) + static_cast<size_t>(t0) * ldy[i] * out_elem;
+      }
+      g.peers = peers;
       g.n = w[i]->n;
       g.ldy = ldy[i];
       g.inv_dw = 1.0f / w[i]->weight_scale_divisor;
@@ -181,6 +185,33 @@ int32_t b200q_nvfp4_linear_group(const b200q_nvfp4_weight *const *w, uint32_t co
     return fail(nvfp4_error(), "b200q_nvfp4_linear_group: unknown epilogue 0x%x", epilogue);
   }
   return linear_group_impl(w, count, x, tokens, y, ldy, epilogue, policy, workspace, stream, "b200q_nvfp4_linear_group");
+}
+
+int32_t b200q_nvfp4_linear_group_scatter(const b200q_nvfp4_weight *const *w, uint32_t count, const void *x, uint32_t tokens,
+                                         void *const *y_peers, uint32_t peers, const uint32_t *ldy, const uint32_t *col_offset,
+                                         uint32_t epilogue, void *stream) {
+  const char *what = "b200q_nvfp4_linear_group_scatter";
+  ErrorSlot &slot = nvfp4_error();
+  if (w == nullptr || y_peers == nullptr || ldy == nullptr || col_offset == nullptr) return fail(slot, "%s: NULL argument array", what);
+  if (count == 0 || count > B200Q_NVFP4_MAX_GROUP) return fail(slot, "%s: count = %u is outside 1..%d", what, count, B200Q_NVFP4_MAX_GROUP);
+  if (peers == 0 || peers > kMaxPeers) return fail(slot, "%s: peers = %u is outside 1..%u", what, peers, kMaxPeers);
+  if (tokens == 0) return fail(slot, "%s: tokens must be positive", what);
+  if ((epilogue & ~static_cast<uint32_t>(B200Q_NVFP4_OUT_F32)) != 0u) return fail(slot, "%s: only STORE (optionally OUT_F32) is served", what);
+  if (x == nullptr || !aligned(x, 16)) return fail(slot, "%s: x is NULL or not 16-byte aligned", what);
+  const size_t out_elem = (epilogue & kEpilogueF32) ? 4u : 2u;
+  void *targets[B200Q_NVFP4_MAX_GROUP * kMaxPeers];
+  for (uint32_t i = 0; i < count; ++i) {
+    if (check_weight(slot, w[i], what) != 0) return -1;
+    if (w[i]->k != w[0]->k) return fail(slot, "%s: the weights of a group must share k", what);
+    if (ldy[i] < col_offset[i] + w[i]->n) return fail(slot, "%s: ldy[%u] = %u is narrower than col_offset + n", what, i, ldy[i]);
+    for (uint32_t pp = 0; pp < peers; ++pp) {
+      if (y_peers[i * peers + pp] == nullptr) return fail(slot, "%s: output %u of rank %u is NULL", what, i, pp);
+      targets[i * peers + pp] = static_cast<uint8_t *>(y_peers[i * peers + pp]) + static_cast<size_t>(col_offset[i]) * out_elem;
+    }
+  }
+  const DeviceState *dev = prepared_state(slot, what);
+  if (dev == nullptr) return -1;
+  return decode_route(slot, *dev, w, count, x, tokens, targets, ldy, epilogue, static_cast<cudaStream_t>(stream), peers);
 }
 
 uint64_t b200q_nvfp4_mlp_workspace_bytes(uint32_t gate_up_n, uint32_t k, uint32_t policy, uint32_t tokens) {

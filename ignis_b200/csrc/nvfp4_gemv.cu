@@ -463,13 +463,16 @@ __global__ void __launch_bounds__(kThreads, NT <= 2 ? 2 : 1) nvfp4_gemv_kernel(c
       const uint32_t row = out_row + (e >> 1) * 32u;
       if (tok >= p.tokens) continue;
       const size_t at = static_cast<size_t>(tok) * W.ldy + row;
-      if (p.epilogue & kEpilogueF32) {
-        float *y = static_cast<float *>(W.y);
-        y[at] = (p.epilogue & kEpilogueAdd) ? y[at] + v[e] : v[e];
-      } else {
-        __nv_bfloat16 *y = static_cast<__nv_bfloat16 *>(W.y);
-        const float r = (p.epilogue & kEpilogueAdd) ? v[e] + __bfloat162float(y[at]) : v[e];
-        y[at] = __float2bfloat16_rn(r);
+      // one buffer, or the same value into every rank's buffer (peer stores over NVLink)
+      for (uint32_t pp = 0; pp < W.peers; ++pp) {
+        if (p.epilogue & kEpilogueF32) {
+          float *y = static_cast<float *>(W.y[pp]);
+          y[at] = (p.epilogue & kEpilogueAdd) ? y[at] + v[e] : v[e];
+        } else {
+          __nv_bfloat16 *y = static_cast<__nv_bfloat16 *>(W.y[pp]);
+          const float r = (p.epilogue & kEpilogueAdd) ? v[e] + __bfloat162float(y[at]) : v[e];
+          y[at] = __float2bfloat16_rn(r);
+        }
       }
     }
   }

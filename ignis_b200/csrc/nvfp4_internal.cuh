@@ -14,10 +14,13 @@ constexpr uint32_t kEpilogueF32 = 0x100u;
 constexpr uint32_t kEpilogueSwiglu = 0x200u;
 constexpr uint32_t kEpilogueQuant = 0x400u;  // with SwiGLU on the tensor-core route: h leaves as the next product's NVFP4 operand
 
+constexpr uint32_t kMaxPeers = 8;  // ranks of one node a scattered product writes to
+
 struct GemvWeight {
   const uint8_t *codes;
   const uint8_t *scales;
-  void *y;               // [tokens][ldy], BF16 or float32
+  void *y[kMaxPeers];    // [tokens][ldy], BF16 or float32: this rank's buffer, or every rank's (peer mappings)
+  uint32_t peers;        // how many of them are written (1 for a plain product)
   uint32_t n;
   uint32_t ldy;
   float inv_dw;          // 1 / weight_scale_divisor

@@ -214,6 +214,26 @@ def linear_group(x: torch.Tensor, weights: list[Weight], outs: list[torch.Tensor
     return ys
 
 
+def linear_group_scatter(x: torch.Tensor, weights: list[Weight], peer_ptrs: list[list[int]], ldy: list[int],
+                         col_offset: list[int], epilogue: int = STORE) -> None:
+    """``b200q_nvfp4_linear_group_scatter``: the grouped decode product whose epilogue stores
+    weight i's columns at ``col_offset[i]`` of every buffer in ``peer_ptrs[i]`` (device addresses,
+    one per rank of the node, the other ranks' mapped into this process)."""
+    _check_x(x, weights[0].k)
+    count, peers = len(weights), len(peer_ptrs[0])
+    structs = [w.c_struct() for w in weights]
+    wp = (C.POINTER(_lib.Nvfp4Weight) * count)(*[C.pointer(s) for s in structs])
+    yp = (C.c_void_p * (count * peers))(*[ptr for row in peer_ptrs for ptr in row])
+    ld = (C.c_uint32 * count)(*ldy)
+    co = (C.c_uint32 * count)(*col_offset)
+    _check(_lib.load().b200q_nvfp4_linear_group_scatter(wp, count, x.data_ptr(), x.shape[0], yp, peers, ld, co, epilogue, _stream()))
+
+
+def peer_barrier(flags_peers: torch.Tensor, peers: int, rank: int, epoch: int, status: torch.Tensor) -> None:
+    """``b200q_peer_barrier``: `flags_peers` is a device int64 tensor of the ranks' flag-array addresses."""
+    _check(_lib.load().b200q_peer_barrier(flags_peers.data_ptr(), peers, rank, epoch, status.data_ptr(), _stream()))
+
+
 def linear_swiglu(x: torch.Tensor, gate_up: Weight, out: torch.Tensor | None = None, policy: int = A16_ONLY,
                   workspace: Workspace | None = None) -> torch.Tensor:
     """``h[t, c] = silu(g) * u`` over the fused gate_up parent: ninfer::ops::linear_swiglu. Under

@@ -38,3 +38,48 @@ def gather_columns(y_shard: torch.Tensor, group=None, out: torch.Tensor | None =
         out.copy_(full)
         return out
     return full.contiguous()
+
+
+class PeerOutputs:
+    """Full-width output buffers of a column-sharded layer, one set per rank, every rank's mapped
+    into every process of the node (``torch.distributed._symmetric_memory``), plus the flag arrays of
+    the device barrier. With them a sharded product stores its columns straight into all ranks'
+    buffers (``nvfp4.linear_group_scatter``) and the all-gather shrinks to ``barrier()``."""
+
+    def __init__(self, shapes: dict[str, tuple[int, int]], dtype=torch.bfloat16, group=None) -> None:
+        import torch.distributed._symmetric_memory as symm_mem
+
+        group = group if group is not None else dist.group.WORLD
+        self.rank, self.world = dist.get_rank(group), dist.get_world_size(group)
+        if self.world > 8:
+            raise ValueError("at most 8 ranks (one node)")
+        elem = torch.empty((), dtype=dtype).element_size()
+        self.offsets, at = {}, 512   # [0, 256): the flag array; [256, 512): spare
+        for name, (tokens, width) in shapes.items():
+            self.offsets[name] = at
+            at += (tokens * width * elem + 255) // 256 * 256
+        device = torch.device("cuda", torch.cuda.current_device())
+        self.arena = symm_mem.empty(at, dtype=torch.uint8, device=device)
+        self.arena.zero_()
+        handle = symm_mem.rendezvous(self.arena, group)
+        self.base = [int(p) for p in handle.buffer_ptrs]
+        self._handle = handle
+        self.views = {name: self.arena[off: off + shapes[name][0] * shapes[name][1] * elem].view(dtype).view(shapes[name])
+                      for name, off in self.offsets.items()}
+        self.flags = torch.tensor(self.base, dtype=torch.int64, device=device)   # every rank's flag array is at its base
+        self.status = torch.zeros(2, dtype=torch.int32, device=device)   # [0] ranks that missed a barrier, [1] barriers so far
+        torch.cuda.synchronize()
+        dist.barrier(group)   # every arena is zeroed before anyone publishes a flag
+
+    def pointers(self, name: str) -> list[int]:
+        """The buffer `name` on every rank, as device addresses valid in this process."""
+        return [b + self.offsets[name] for b in self.base]
+
+    def barrier(self) -> None:
+        from . import nvfp4
+
+        nvfp4.peer_barrier(self.flags, self.world, self.rank, 0, self.status)   # numbered on the device: graph-safe
+
+    def missing(self) -> int:
+        """Bit p set: rank p did not reach some barrier within the device-side limit."""
+        return int(self.status[0].item())

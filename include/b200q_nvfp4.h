@@ -119,6 +119,30 @@ int32_t b200q_nvfp4_linear_swiglu(const b200q_nvfp4_weight *gate_up, const void 
                                   void *h, uint32_t ldh, uint32_t policy,
                                   const b200q_nvfp4_workspace *workspace, void *stream);
 
+/* Column-sharded layers on the GPUs of one node. Not in the (single-GPU) reference.
+ *
+ * b200q_nvfp4_linear_group_scatter is b200q_nvfp4_linear_group on the decode route whose epilogue
+ * stores every value into `peers` buffers instead of one: weight i's output [tokens][n_i] lands at
+ * column col_offset[i] of y_peers[i * peers + p] (row stride ldy[i]) for every p < peers. One of
+ * the pointers is this rank's own full-width buffer, the others are the same buffer of the other
+ * ranks, mapped into this process (CUDA IPC or symmetric memory): the product IS the all-gather's
+ * data movement, as plain stores over NVLink. STORE, BF16 or B200Q_NVFP4_OUT_F32.
+ *
+ * b200q_peer_barrier is the rest of the all-gather: barrier number `epoch` (1, 2, ...) between the
+ * ranks, on the device, in stream order behind the product. flags_peers is a DEVICE array of
+ * `peers` pointers, entry p the flag array (`peers` uint32, zero at start) of rank p, mapped like
+ * the buffers. This rank publishes `epoch` in slot `rank` of every array and waits until every
+ * slot of its own array has reached it; the wait is bounded (about two seconds), and a wait that
+ * runs out sets bit p of status[0] for each rank p that did not arrive. `status` is two uint32 of
+ * this rank's device memory, zero at start; with epoch = 0 the kernel numbers the barrier itself
+ * from status[1] (for launches captured in a CUDA graph; every rank must then pass 0 every time). */
+int32_t b200q_nvfp4_linear_group_scatter(const b200q_nvfp4_weight *const *w, uint32_t count, const void *x,
+                                         uint32_t tokens, void *const *y_peers, uint32_t peers,
+                                         const uint32_t *ldy, const uint32_t *col_offset, uint32_t epilogue,
+                                         void *stream);
+int32_t b200q_peer_barrier(uint32_t *const *flags_peers, uint32_t peers, uint32_t rank, uint32_t epoch,
+                           uint32_t *status, void *stream);
+
 /* The layers' MLP: y (+)= down(silu(g) * u), g | u = gate_up x. reference:
  * ignis::prefill_swiglu::mlp (kernel/src/prefill_swiglu.h:100-107) and, below its widths, the
  * linear_swiglu + linear_add pair it falls back to. `epilogue` is B200Q_NVFP4_STORE or
