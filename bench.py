@@ -149,10 +149,14 @@ def cpu_sample(seconds_target: float = 12.0):
     probe_rows = 256
     t = run(probe_rows)
     rows = int(min(6144, max(256, seconds_target / max(t, 1e-6) * probe_rows))) // 128 * 128
-    elapsed = run(rows)
-    nbytes = weight_bytes(rows, k) + tokens * k * 2 + tokens * rows * 2
+    # whole q-sized pieces (fresh random rows each) until about `seconds_target` of CPU work is done
+    elapsed, pieces = 0.0, 0
+    while pieces == 0 or (elapsed < seconds_target and pieces < 64):
+        elapsed += run(rows)
+        pieces += 1
+    nbytes = pieces * (weight_bytes(rows, k) + tokens * k * 2 + tokens * rows * 2)
     desc = {"kind": kind, "cores": threads,
-            "sample": f"{rows} rows of q (K=5120) at 8 tokens: host dequantize ({kind}, 1 thread) + fp64 product "
+            "sample": f"{pieces} x {rows} rows of q (K=5120) at 8 tokens: host dequantize ({kind}, 1 thread) + fp64 product "
                       f"({threads} threads), {elapsed:.2f} s"}
     return nbytes / elapsed / 1e9, desc
 
