@@ -85,26 +85,40 @@ __device__ __forceinline__ void quantize_block16(const uint4 lo, const uint4 hi,
   codes = make_uint2(packed[0], packed[1]);
 }
 
-// One thread per (token row of the padded range, 16-value group). Rows at and beyond `tokens`
-// get zero codes and zero scales.
+// One thread per (token row of the padded range, 64 values): four blocks of 16, i.e. 128 bytes in,
+// 32 bytes of codes and the four scale bytes that lie side by side in a scale tile out. Rows at
+// and beyond `tokens` get zero codes and zero scales.
 __global__ void __launch_bounds__(256) quantize_swizzled_kernel(const uint16_t *x, uint32_t tokens, uint32_t tokens_pad,
                                                                 uint32_t k, float d_in, uint8_t *codes, uint8_t *scales) {
   griddep_launch_dependents();
   griddep_wait();
-  const uint32_t groups = k / 16u;
-  const uint64_t total = static_cast<uint64_t>(tokens_pad) * groups;
-  for (uint64_t bi = blockIdx.x * static_cast<uint64_t>(blockDim.x) + threadIdx.x; bi < total;
-       bi += static_cast<uint64_t>(gridDim.x) * blockDim.x) {
-    const uint32_t t = static_cast<uint32_t>(bi / groups), g = static_cast<uint32_t>(bi % groups);
-    uint2 c = make_uint2(0u, 0u);
-    uint8_t s = 0;
+  const uint32_t quads = k / 64u;
+  const uint64_t total = static_cast<uint64_t>(tokens_pad) * quads;
+  for (uint64_t qi = blockIdx.x * static_cast<uint64_t>(blockDim.x) + threadIdx.x; qi < total;
+       qi += static_cast<uint64_t>(gridDim.x) * blockDim.x) {
+    const uint32_t t = static_cast<uint32_t>(qi / quads), q = static_cast<uint32_t>(qi % quads);
+    uint2 c[4];
+    uint32_t sw = 0;
     if (t < tokens) {
-      const uint16_t *src = x + static_cast<uint64_t>(t) * k + g * 16u;
-      quantize_block16(ldg128_coherent(src), ldg128_coherent(src + 8), d_in, c, s);
+      const uint16_t *src = x + static_cast<uint64_t>(t) * k + q * 64u;
+      uint4 v[8];
+#pragma unroll
+      for (int j = 0; j < 8; ++j) v[j] = ldg128_coherent(src + 8 * j);
+#pragma unroll
+      for (int b = 0; b < 4; ++b) {
+        uint8_t s;
+        quantize_block16(v[2 * b], v[2 * b + 1], d_in, c[b], s);
+        sw |= static_cast<uint32_t>(s) << (8 * b);
+      }
+    } else {
+#pragma unroll
+      for (int b = 0; b < 4; ++b) c[b] = make_uint2(0u, 0u);
     }
-    *reinterpret_cast<uint2 *>(codes + bi * 8u) = c;
-    const uint64_t so = (static_cast<uint64_t>(t >> 7) * (k / 64u) + (g >> 2)) * 512u + (t & 31u) * 16u + ((t & 127u) >> 5) * 4u + (g & 3u);
-    scales[so] = s;
+    uint4 *dst = reinterpret_cast<uint4 *>(codes + qi * 32u);
+    dst[0] = make_uint4(c[0].x, c[0].y, c[1].x, c[1].y);
+    dst[1] = make_uint4(c[2].x, c[2].y, c[3].x, c[3].y);
+    const uint64_t so = (static_cast<uint64_t>(t >> 7) * quads + q) * 512u + (t & 31u) * 16u + ((t & 127u) >> 5) * 4u;
+    *reinterpret_cast<uint32_t *>(scales + so) = sw;
   }
 }
 
@@ -701,7 +715,7 @@ int32_t w4a4_product(ErrorSlot &slot, const DeviceState &dev, const uint8_t *w_c
                      cudaStream_t stream) {
   const uint32_t pad = w4a4_tokens_pad(tokens);
   if (x != nullptr) {
-    const uint64_t total = static_cast<uint64_t>(pad) * (k / 16u);
+    const uint64_t total = static_cast<uint64_t>(pad) * (k / 64u);
     const uint32_t grid = static_cast<uint32_t>(total / 256u < 148u * 16u ? (total + 255u) / 256u : 148u * 16u);
     const cudaError_t err = launch(quantize_swizzled_kernel, dim3(grid), dim3(256), 0, stream, dev.pdl != 0, x, tokens, pad,
                                    k, d_in, a_codes, a_scales);
