@@ -15,7 +15,8 @@ import subprocess
 import sys
 
 HERE = os.path.dirname(os.path.abspath(__file__))
-REFERENCE = os.environ.get("B200Q_REFERENCE_ROOT", "/root/reference")
+# the reference checkout: B200Q_REFERENCE_ROOT, else a directory `reference` beside this repository
+REFERENCE = os.environ.get("B200Q_REFERENCE_ROOT", os.path.join(os.path.dirname(os.path.dirname(HERE)), "reference"))
 CUDA_HOME = os.environ.get("CUDA_HOME", "/usr/local/cuda")
 
 ORACLE_SO = os.path.join(HERE, "liboracle.so")

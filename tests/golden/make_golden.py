@@ -33,7 +33,8 @@ import numpy as np
 
 HERE = os.path.dirname(os.path.abspath(__file__))
 ROOT = os.path.dirname(os.path.dirname(HERE))
-REFERENCE = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+# the reference checkout: first argument, else a directory `reference` beside this repository
+REFERENCE = sys.argv[1] if len(sys.argv) > 1 else os.path.join(os.path.dirname(ROOT), "reference")
 
 DTYPES = {0: np.uint8, 1: np.int16, 2: np.uint16, 3: np.int32, 4: np.float16, 5: np.uint16, 6: np.float32,
           7: np.float64, 8: np.uint32, 9: np.uint64}
