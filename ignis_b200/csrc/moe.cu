@@ -154,6 +154,74 @@ __global__ void __launch_bounds__(256) moe_scatter_kernel(const int32_t *ids, ui
   }
 }
 
+// Count, scan and scatter in one CTA for calls of a few rows (the decode widths): the three launches
+// above cost more than their work there. Counts and cursors live in shared memory.
+constexpr uint32_t kSmallRows = 4096, kSmallExperts = 4096;
+
+__global__ void __launch_bounds__(1024) moe_group_small_kernel(const int32_t *ids, uint32_t rows, uint32_t experts, uint32_t item_rows,
+                                                               uint32_t *offsets, uint32_t *n_items, Item *items, Tile *tiles,
+                                                               uint32_t *sorted, uint32_t *status) {
+  griddep_launch_dependents();
+  griddep_wait();
+  __shared__ uint32_t counts[kSmallExperts], start[kSmallExperts];
+  __shared__ uint32_t row_sum[1024], item_sum[1024], tile_sum[1024];
+  for (uint32_t e = threadIdx.x; e < experts; e += 1024) counts[e] = 0u;
+  __syncthreads();
+  for (uint32_t a = threadIdx.x; a < rows; a += 1024) {
+    const int32_t e = ids[a];
+    if (e < 0 || static_cast<uint32_t>(e) >= experts) {
+      atomicOr(status, kStatusBadExpert);
+    } else {
+      atomicAdd(&counts[e], 1u);
+    }
+  }
+  __syncthreads();
+  const uint32_t per = (experts + 1023u) / 1024u;
+  const uint32_t e0 = threadIdx.x * per;
+  uint32_t nrows = 0, its = 0, tls = 0;
+  for (uint32_t e = e0; e < e0 + per && e < experts; ++e) {
+    nrows += counts[e];
+    its += (counts[e] + item_rows - 1u) / item_rows;
+    tls += (counts[e] + 7u) / 8u;
+  }
+  row_sum[threadIdx.x] = nrows;
+  item_sum[threadIdx.x] = its;
+  tile_sum[threadIdx.x] = tls;
+  __syncthreads();
+  for (uint32_t d = 1; d < 1024; d <<= 1) {
+    const uint32_t r = threadIdx.x >= d ? row_sum[threadIdx.x - d] : 0u;
+    const uint32_t i = threadIdx.x >= d ? item_sum[threadIdx.x - d] : 0u;
+    const uint32_t t = threadIdx.x >= d ? tile_sum[threadIdx.x - d] : 0u;
+    __syncthreads();
+    row_sum[threadIdx.x] += r;
+    item_sum[threadIdx.x] += i;
+    tile_sum[threadIdx.x] += t;
+    __syncthreads();
+  }
+  uint32_t row_at = row_sum[threadIdx.x] - nrows, item_at = item_sum[threadIdx.x] - its, tile_at = tile_sum[threadIdx.x] - tls;
+  for (uint32_t e = e0; e < e0 + per && e < experts; ++e) {
+    offsets[e] = row_at;
+    start[e] = row_at;
+    const uint32_t c = counts[e];
+    for (uint32_t j = 0; j < c; j += item_rows) {
+      items[item_at++] = Item{e, row_at + j, c - j < item_rows ? c - j : item_rows, tile_at + j / 8u};
+    }
+    for (uint32_t j = 0; j < c; j += 8) tiles[tile_at++] = Tile{e, row_at + j, c - j < 8u ? c - j : 8u, 0u};
+    row_at += c;
+  }
+  if (threadIdx.x == 1023) {
+    offsets[experts] = row_sum[1023];
+    n_items[0] = item_sum[1023];
+    n_items[1] = tile_sum[1023];
+  }
+  __syncthreads();
+  for (uint32_t a = threadIdx.x; a < rows; a += 1024) {
+    const int32_t e = ids[a];
+    if (e < 0 || static_cast<uint32_t>(e) >= experts) continue;
+    sorted[atomicAdd(&start[e], 1u)] = a;  // rows of one expert are independent: their order changes no output bit
+  }
+}
+
 // ---- the expert kernels ----------------------------------------------------------------------
 struct ExpertParams {
   const ignis_moe_slot *slots;
@@ -744,14 +812,21 @@ int32_t run_experts(const void *x, uint32_t tokens, const int32_t *ids, const fl
   uint32_t *sorted = reinterpret_cast<uint32_t *>(base + l.sorted);
   Item *items = reinterpret_cast<Item *>(base + l.items);
   uint32_t *status = reinterpret_cast<uint32_t *>(base + l.status);
-  cudaError_t err = cudaMemsetAsync(counts, 0, l.offsets - l.counts, stream);  // counts and cursor
-  if (err != cudaSuccess) return fail(slot, "%s: %s", what, cudaGetErrorString(err));
   const bool pdl = dev->pdl != 0;
+  cudaError_t err = cudaSuccess;
+  if (rows <= kSmallRows && g.experts <= kSmallExperts) {
+    err = launch(moe_group_small_kernel, dim3(1), dim3(1024), 0, stream, false, ids, rows, g.experts, item_rows, offsets, n_items, items,
+                 reinterpret_cast<Tile *>(base + l.tiles), sorted, status);
+    if (err != cudaSuccess) return fail(slot, "%s: grouping launch failed: %s", what, cudaGetErrorString(err));
+  } else {
+  err = cudaMemsetAsync(counts, 0, l.offsets - l.counts, stream);  // counts and cursor
+  if (err != cudaSuccess) return fail(slot, "%s: %s", what, cudaGetErrorString(err));
   const uint32_t grid_rows = (rows + 255u) / 256u < 1184u ? (rows + 255u) / 256u : 1184u;
   err = launch(moe_count_kernel, dim3(grid_rows), dim3(256), 0, stream, false, ids, rows, g.experts, counts, status);
   if (err == cudaSuccess) err = launch(moe_scan_kernel, dim3(1), dim3(1024), 0, stream, pdl, static_cast<const uint32_t *>(counts), g.experts, item_rows, offsets, n_items, items, reinterpret_cast<Tile *>(base + l.tiles));
   if (err == cudaSuccess) err = launch(moe_scatter_kernel, dim3(grid_rows), dim3(256), 0, stream, pdl, ids, rows, g.experts, static_cast<const uint32_t *>(offsets), cursor, sorted);
   if (err != cudaSuccess) return fail(slot, "%s: grouping launch failed: %s", what, cudaGetErrorString(err));
+  }
 
   ExpertParams p = {};
   p.slots = slots;
