@@ -187,6 +187,67 @@ int32_t b200q_nvfp4_linear_group(const b200q_nvfp4_weight *const *w, uint32_t co
   return linear_group_impl(w, count, x, tokens, y, ldy, epilogue, policy, workspace, stream, "b200q_nvfp4_linear_group");
 }
 
+int32_t b200q_nvfp4_linear_split(const b200q_nvfp4_weight *parent, uint32_t count, const uint32_t *row_begin, const uint32_t *rows,
+                                 const void *x, uint32_t tokens, void *const *y, const uint32_t *ldy, uint32_t epilogue,
+                                 uint32_t policy, const b200q_nvfp4_workspace *workspace, void *stream) {
+  const char *what = "b200q_nvfp4_linear_split";
+  ErrorSlot &slot = nvfp4_error();
+  if (row_begin == nullptr || rows == nullptr || y == nullptr || ldy == nullptr) return fail(slot, "%s: NULL argument array", what);
+  if (count == 0 || count > B200Q_NVFP4_MAX_GROUP) return fail(slot, "%s: count = %u is outside 1..%d", what, count, B200Q_NVFP4_MAX_GROUP);
+  if ((epilogue & ~static_cast<uint32_t>(B200Q_NVFP4_OUT_F32)) != 0u) return fail(slot, "%s: only STORE (optionally OUT_F32) is served", what);
+  if (check_weight(slot, parent, what) != 0) return -1;
+  // every range as a weight of its own: whole 128-row tiles are contiguous in both planes
+  b200q_nvfp4_weight part[B200Q_NVFP4_MAX_GROUP];
+  const b200q_nvfp4_weight *parts[B200Q_NVFP4_MAX_GROUP];
+  const uint64_t row_bytes = parent->k / 2u, tile_bytes = static_cast<uint64_t>(parent->k / 64u) * 512u;
+  for (uint32_t i = 0; i < count; ++i) {
+    if (rows[i] == 0 || (rows[i] % 128u) != 0 || (row_begin[i] % 128u) != 0 ||
+        static_cast<uint64_t>(row_begin[i]) + rows[i] > parent->n) {
+      return fail(slot, "%s: range %u = [%u, +%u) is not whole 128-row tiles inside the parent's %u rows", what, i, row_begin[i],
+                  rows[i], parent->n);
+    }
+    part[i] = *parent;
+    part[i].codes = static_cast<const uint8_t *>(parent->codes) + row_begin[i] * row_bytes;
+    part[i].scales = static_cast<const uint8_t *>(parent->scales) + (row_begin[i] / 128u) * tile_bytes;
+    part[i].n = rows[i];
+    parts[i] = &part[i];
+  }
+  const bool wide = policy == B200Q_NVFP4_ALLOW_A4 && tokens > B200Q_NVFP4_DECODE_MAX_TOKENS && w4a4_shape_ok(parent->n, parent->k);
+  if (!wide || count == 1) {
+    return linear_group_impl(parts, count, x, tokens, y, ldy, epilogue, policy, workspace, stream, what);
+  }
+  // wide: one quantization of x, then a tensor-core product per range over the same operand
+  if (tokens == 0) return fail(slot, "%s: tokens must be positive", what);
+  if (x == nullptr || !aligned(x, 16)) return fail(slot, "%s: x is NULL or not 16-byte aligned", what);
+  if (!std::isfinite(parent->input_scale_divisor) || !(parent->input_scale_divisor > 0.0f)) {
+    return fail(slot, "%s: input_scale_divisor must be finite and positive for the A4 route", what);
+  }
+  const uint64_t need = w4a4_workspace_bytes(parent->k, tokens);
+  if (workspace == nullptr || workspace->base == nullptr || workspace->bytes < need || !aligned(workspace->base, 256)) {
+    return fail(slot, "%s: the A4 route needs a 256-byte aligned workspace of %llu bytes", what, static_cast<unsigned long long>(need));
+  }
+  const DeviceState *dev = prepared_state(slot, what);
+  if (dev == nullptr) return -1;
+  for (uint32_t i = 0; i < count; ++i) {
+    if (y[i] == nullptr || !aligned(y[i], 16) || (ldy[i] % 8u) != 0 || ldy[i] < rows[i]) {
+      return fail(slot, "%s: output %u must be 16-byte aligned with ldy a multiple of 8 and at least its rows", what, i);
+    }
+  }
+  uint8_t *base = static_cast<uint8_t *>(workspace->base);
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  for (uint32_t i = 0; i < count; ++i) {
+    const b200q_nvfp4_weight &w = part[i];
+    const int32_t rc = i == 0 ? w4a4_launch(slot, *dev, static_cast<const uint8_t *>(w.codes), static_cast<const uint8_t *>(w.scales), w.n, w.k,
+                                            w.weight_scale_divisor, w.input_scale_divisor, static_cast<const uint16_t *>(x), tokens,
+                                            y[i], ldy[i], epilogue, base, s)
+                              : w4a4_launch_prequantized(slot, *dev, static_cast<const uint8_t *>(w.codes),
+                                                         static_cast<const uint8_t *>(w.scales), w.n, w.k, w.weight_scale_divisor,
+                                                         w.input_scale_divisor, tokens, y[i], ldy[i], epilogue, base, s);
+    if (rc != 0) return -1;
+  }
+  return 0;
+}
+
 int32_t b200q_nvfp4_linear_group_scatter(const b200q_nvfp4_weight *const *w, uint32_t count, const void *x, uint32_t tokens,
                                          void *const *y_peers, uint32_t peers, const uint32_t *ldy, const uint32_t *col_offset,
                                          uint32_t epilogue, void *stream) {

@@ -65,6 +65,11 @@ uint64_t w4a4_workspace_bytes(uint32_t k, uint32_t tokens);
 int32_t w4a4_launch(ErrorSlot &slot, const DeviceState &dev, const uint8_t *w_codes, const uint8_t *w_scales, uint32_t n,
                     uint32_t k, float d_w, float d_in, const uint16_t *x, uint32_t tokens, void *y, uint32_t ldy,
                     uint32_t epilogue, uint8_t *workspace, cudaStream_t stream);
+// The same product over activations already quantized in `workspace` by an earlier w4a4_launch of
+// the same x, k and token count (split-output parents: one quantization, a product per range).
+int32_t w4a4_launch_prequantized(ErrorSlot &slot, const DeviceState &dev, const uint8_t *w_codes, const uint8_t *w_scales,
+                                 uint32_t n, uint32_t k, float d_w, float d_in, uint32_t tokens, void *y, uint32_t ldy,
+                                 uint32_t epilogue, uint8_t *workspace, cudaStream_t stream);
 // The layers' MLP on the tensor-core route: x is quantized, the gate|up product's epilogue writes
 // silu(g) u already quantized under `down`'s input divisor, the down product reads it.
 uint64_t w4a4_mlp_workspace_bytes(uint32_t k, uint32_t inter, uint32_t tokens);

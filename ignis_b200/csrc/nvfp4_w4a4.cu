@@ -769,6 +769,16 @@ int32_t w4a4_launch(ErrorSlot &slot, const DeviceState &dev, const uint8_t *w_co
                       reinterpret_cast<uint32_t *>(workspace), a_codes, a_scales, QuantTarget(), stream);
 }
 
+int32_t w4a4_launch_prequantized(ErrorSlot &slot, const DeviceState &dev, const uint8_t *w_codes, const uint8_t *w_scales,
+                                 uint32_t n, uint32_t k, float d_w, float d_in, uint32_t tokens, void *y, uint32_t ldy,
+                                 uint32_t epilogue, uint8_t *workspace, cudaStream_t stream) {
+  const uint32_t pad = w4a4_tokens_pad(tokens);
+  uint8_t *a_codes = workspace + 256;
+  uint8_t *a_scales = a_codes + static_cast<uint64_t>(pad) * (k / 2u);
+  return w4a4_product(slot, dev, w_codes, w_scales, n, k, d_w, d_in, nullptr, tokens, y, ldy, epilogue,
+                      reinterpret_cast<uint32_t *>(workspace), a_codes, a_scales, QuantTarget(), stream);
+}
+
 // Workspace of the MLP: the status line, x quantized (K = k), h quantized (K = inter).
 uint64_t w4a4_mlp_workspace_bytes(uint32_t k, uint32_t inter, uint32_t tokens) {
   const uint64_t pad = w4a4_tokens_pad(tokens);

@@ -214,6 +214,26 @@ def linear_group(x: torch.Tensor, weights: list[Weight], outs: list[torch.Tensor
     return ys
 
 
+def linear_split(x: torch.Tensor, parent: Weight, row_counts: list[int], outs: list[torch.Tensor] | None = None,
+                 policy: int = A16_ONLY, epilogue: int = STORE, workspace: Workspace | None = None) -> list[torch.Tensor]:
+    """A single-parent split-output projection (ninfer::ops::attn_input_proj / gdn_input_proj over an
+    NVFP4 parent): consecutive row ranges of `parent`, `row_counts[i]` rows each, every range into
+    its own contiguous output."""
+    _check_x(x, parent.k)
+    tokens = x.shape[0]
+    count = len(row_counts)
+    begins = [sum(row_counts[:i]) for i in range(count)]
+    ys = [_out(tokens, r, epilogue, None if outs is None else outs[i], x.device) for i, r in enumerate(row_counts)]
+    ws = parent.c_struct()
+    rb = (C.c_uint32 * count)(*begins)
+    rc = (C.c_uint32 * count)(*row_counts)
+    yp = (C.c_void_p * count)(*[y.data_ptr() for y in ys])
+    ld = (C.c_uint32 * count)(*[y.stride(0) for y in ys])
+    _check(_lib.load().b200q_nvfp4_linear_split(C.byref(ws), count, rb, rc, x.data_ptr(), tokens, yp, ld, epilogue, policy,
+                                                 C.byref(workspace.c) if workspace is not None else None, _stream()))
+    return ys
+
+
 def linear_group_scatter(x: torch.Tensor, weights: list[Weight], peer_ptrs: list[list[int]], ldy: list[int],
                          col_offset: list[int], epilogue: int = STORE) -> None:
     """``b200q_nvfp4_linear_group_scatter``: the grouped decode product whose epilogue stores

@@ -112,6 +112,20 @@ int32_t b200q_nvfp4_linear_group(const b200q_nvfp4_weight *const *w, uint32_t co
                                  uint32_t epilogue, uint32_t policy,
                                  const b200q_nvfp4_workspace *workspace, void *stream);
 
+/* One parent weight, `count` row ranges of it, each range its own output: the single-parent
+ * split-output projections of the reference - ninfer::ops::attn_input_proj over the NVFP4
+ * [14336, 5120] parent with row counts 6144 | 1024 | 6144 | 1024 (q | k | gate | v;
+ * ninfer/ops/attn_input_proj.h:75-91) and gdn_input_proj (qkv 10240 | z 6144). Range i is rows
+ * [row_begin[i], row_begin[i] + rows[i]) (multiples of 128: whole scale tiles, so every range is a
+ * contiguous byte range of both planes) and writes y[i][t][..ldy[i]]; no packed parent output is
+ * materialized. STORE only (BF16 or B200Q_NVFP4_OUT_F32). Narrow calls and A16: one decode launch over all ranges. Wide
+ * calls under B200Q_NVFP4_ALLOW_A4: x is quantized once into the workspace
+ * (b200q_nvfp4_workspace_bytes of the parent) and every range is one tensor-core product. */
+int32_t b200q_nvfp4_linear_split(const b200q_nvfp4_weight *parent, uint32_t count, const uint32_t *row_begin,
+                                 const uint32_t *rows, const void *x, uint32_t tokens, void *const *y,
+                                 const uint32_t *ldy, uint32_t epilogue, uint32_t policy,
+                                 const b200q_nvfp4_workspace *workspace, void *stream);
+
 /* h[t][c] = BF16(silu(g) * u), g and u the products with rows [0, n/2) and [n/2, n) of the fused
  * gate_up parent: ninfer::ops::linear_swiglu at decode widths
  * (linear_swiglu/nvfp4/nvfp4_linear_swiglu_decode.cu:57-69), one rounding from FP32. */

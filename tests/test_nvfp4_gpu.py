@@ -347,6 +347,29 @@ def test_w4a4_fused_swiglu(nv, oracle):
     assert np.linalg.norm(got - h16) <= 0.2 * np.linalg.norm(h16)
 
 
+@pytest.mark.parametrize("tokens", [6, 90])
+def test_split_outputs_equal_the_full_product(nv, oracle, tokens):
+    """attn_input_proj's shape in small: one parent, row ranges q | k | gate | v into four separate
+    outputs. Each must be the matching columns of the whole parent's product, bit for bit, on the
+    decode route (one launch) and on the tensor-core route (one quantization, four products)."""
+    k, counts = 512, [384, 128, 384, 128]
+    rng = np.random.default_rng(70 + tokens)
+    codes, scales, d_w = make_weight(rng, sum(counts), k)
+    parent = nv.Weight.from_planes(codes, scales, d_w, 448.0)
+    x = torch.randn(tokens, k, generator=torch.Generator().manual_seed(tokens)).to(torch.bfloat16).cuda()
+    for policy in (nv.A16_ONLY, nv.ALLOW_A4):
+        ws = nv.Workspace(nv.workspace_bytes(sum(counts), k, policy, tokens))
+        whole = nv.linear(x, parent, policy=policy, workspace=ws)
+        parts = nv.linear_split(x, parent, counts, policy=policy, workspace=ws)
+        assert ws.status() == 0
+        at = 0
+        for part, rows in zip(parts, counts):
+            assert part.shape == (tokens, rows) and torch.equal(part, whole[:, at: at + rows])
+            at += rows
+    with pytest.raises(nv.Nvfp4Error):
+        nv.linear_split(x, parent, [192, 832])   # ranges must be whole 128-row tiles
+
+
 @pytest.mark.parametrize("tokens", [5, 100])
 def test_mlp_matches_its_parts(nv, oracle, tokens):
     """b200q_nvfp4_mlp against the same ops called one by one. Wide under ALLOW_A4: the gate|up
