@@ -470,6 +470,27 @@ def run_side_workload(args) -> None:
             if args.mlp:
                 workload = (f"configs[2] as the layer's MLP, M={tokens}: gate|up 5120->34816 with SwiGLU and the down product's "
                             "quantizer in its epilogue, then down 17408->5120; one activation quantizer launch")
+        elif args.workload == "head":
+            # the output head: 5120 -> 248320 at 4 bits per weight, the largest product of a decode step
+            in_, out, k2 = 5120, 248320, 8
+            gen = torch.Generator(device=device).manual_seed(20261131)
+            heads = []
+            for _ in range(2):   # two copies: 2 x 636 MB streams past the L2
+                words = torch.randint(-32768, 32767, ((in_ // 16) * (out // 16) * 64,), dtype=torch.int16, device=device, generator=gen)
+                suh = ((torch.rand(in_, device=device, generator=gen) * 1.5 + 0.5) * 0.05).to(torch.float16)
+                svh = ((torch.rand(out, device=device, generator=gen) * 1.5 + 0.5) * 0.03).to(torch.float16)
+                heads.append(trellis.Weight(words, suh, svh, k2, in_, out))
+            xh = torch.randn(args.tokens, in_, device=device, generator=gen).to(torch.bfloat16)
+            yh = torch.empty(args.tokens, out, dtype=torch.bfloat16, device=device)
+            nbytes = 2 * (trellis.weight_bytes(in_, out, k2) + args.tokens * in_ * 2 + args.tokens * out * 2)
+
+            def one_step() -> None:
+                for w in heads:
+                    trellis.linear(w, xh, out=yh)
+
+            launches = 2
+            metric, unit, work = "trellis_gemv_gbs", "GB/s", nbytes / 1e9
+            workload = f"output head: trellis 4 bpw, 5120 -> 248320, M={args.tokens}, two distinct copies per step"
         else:
             weights, inputs, outputs, nbytes = build_trellis_workload(args.layers, 0, 1, args.tokens, device)
             by = {name: (in_, out) for name, in_, out in TRELLIS_LAYER}
@@ -519,7 +540,7 @@ def run_side_workload(args) -> None:
     else:
         roof = {"bound": "hbm", "achieved": value, "peak": peak_hbm, "unit": "GB/s", "frac": value / peak_hbm,
                 "peak_source": f"{peak_kind} copy bandwidth; the kernel is instruction-issue bound (about 5 integer operations per weight)",
-                "kernel": "trellis_linear_kernel", "traffic": None}
+                "kernel": "trellis_linear_kernel", "traffic": None}  # also the head workload
     print(json.dumps({"metric": metric, "value": value, "unit": unit, "n_gpus": 1, "steps": args.steps, "warmup": args.warmup,
                       "ms_per_step": ms, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
                       "dtype": "e2m1xe2m1->f32" if args.workload == "prefill" else "f16xf16->f32", "data": "synthetic",
@@ -698,7 +719,7 @@ def main() -> None:
     ap.add_argument("--moe-tokens", type=int, default=4096, help="tokens of the --workload moe step (configs[4]: 4096; up to 8 takes the decode entry's item size)")
     ap.add_argument("--mlp", type=int, default=0, help="with --workload prefill: 1 runs the fused MLP entry instead of two plain products")
     ap.add_argument("--no-cpu-baseline", action="store_true")
-    ap.add_argument("--workload", default="decode", choices=["decode", "prefill", "trellis", "moe"],
+    ap.add_argument("--workload", default="decode", choices=["decode", "prefill", "trellis", "moe", "head"],
                     help="decode: configs[1] (the headline); prefill: configs[2]; trellis: configs[3]; moe: configs[4]")
     args = ap.parse_args()
     if args.impl == "reference":

@@ -245,6 +245,28 @@ def test_full_size_gate_projection(tr, oracle):
     assert np.abs(got - ref).max() <= 4e-3 * np.abs(ref).max()
 
 
+def test_output_head_shape(tr, oracle):
+    """The output head, the largest product of a step: 5120 -> 248320 at 4 bits per weight
+    (docs/formats/flash-next-layout.md:148-175). At both ends and in the middle of the vocabulary
+    the full call is held to the fp64 oracle over 256-column views of the same plane (a view is
+    split over the inputs differently, so its own product may differ in the last bits)."""
+    in_, out, k2 = 5120, 248320, 8
+    gen = torch.Generator(device="cuda").manual_seed(77)
+    words = torch.randint(-32768, 32767, ((in_ // 16) * (out // 16) * 16 * k2 // 2,), dtype=torch.int16, device="cuda", generator=gen)
+    rng = np.random.default_rng(77)
+    suh, svh = make_scales(rng, in_, 0.05), make_scales(rng, out, 0.03)
+    w = tr.Weight(words, torch.from_numpy(suh.view(np.float16)).cuda(), torch.from_numpy(svh.view(np.float16)).cuda(), k2, in_, out)
+    x = torch.randn(4, in_, generator=torch.Generator().manual_seed(77)).to(torch.bfloat16)
+    full = tr.linear(w, x.cuda())
+    assert full.shape == (4, out)
+    x64 = x.double().numpy()
+    for c0 in (0, 124160, out - 256):
+        view = w.columns(c0, c0 + 256)
+        inner = f16_bits(tr.reconstruct(view))
+        ref = oracle.trellis_project(inner, suh, svh[c0: c0 + 256], x64)
+        check_linear(full[:, c0: c0 + 256], ref, tolerance(oracle, inner, suh, svh[c0: c0 + 256], x64))
+
+
 def test_workspace_and_rejects(tr):
     assert tr.workspace_bytes(5120, 17408, 1, 8) > 0
     assert tr.workspace_bytes(5120, 17408, 2, 64) > 0
