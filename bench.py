@@ -256,10 +256,7 @@ def build_moe_workload(tokens: int, device, rank=0, world=1, hidden=2048, inter=
     from ignis_b200 import moe
 
     local_experts = experts // world
-    if world == 1:
-        moe.set_geometry(hidden, inter, experts, top_k)
-    else:
-        moe.set_geometry(hidden, inter, local_experts, 1)
+    moe.set_geometry(hidden, inter, local_experts, top_k)
     moe.prepare()
     gen = torch.Generator(device=device).manual_seed(20261129 + rank)
     gu_bytes, dn_bytes = moe.record_bytes(moe.PROJ_GATE_UP, k2), moe.record_bytes(moe.PROJ_DOWN, k2)
@@ -297,8 +294,8 @@ def build_moe_workload(tokens: int, device, rank=0, world=1, hidden=2048, inter=
     flops = tokens * top_k * (2.0 * hidden * 2 * inter + 2.0 * inter * hidden) + tokens * (2.0 * hidden * 2 * inter + 2.0 * inter * hidden)
     if world == 1:
         ws = moe.Workspace(min(8, tokens), tokens, device)
-    else:   # a rank may be sent every row of the job
-        ws = moe.Workspace(8, tokens * top_k, device)
+    else:   # a rank may be sent every token of the job
+        ws = moe.Workspace(8, tokens, device)
         lo, hi = rank * tokens // world, (rank + 1) * tokens // world
         ids, weights, x = ids[lo:hi], weights[lo:hi], x[lo:hi]
     host = {"x": x.pin_memory(), "ids": ids.pin_memory(), "weights": weights.pin_memory()}
@@ -336,7 +333,7 @@ def run_moe_workload(args) -> None:
             acc = None
         else:
             acc = moe_ep.routed_experts(m["x"], m["ids"], m["weights"], m["experts"],
-                                        lambda rows, local, w: moe.experts_rows(rows, local, w, m["table"], m["ws"]))
+                                        lambda rows, local, w: moe.experts_tokens(rows, local, w, m["table"], m["ws"]))
         shared, _ = moe.shared_expert(m["shared"][0], m["shared"][1], m["shared"][2], m["x"])
         return moe.combine(m["ws"], shared, m["x"], m["w_gate"], acc=acc)
 

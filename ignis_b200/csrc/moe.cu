@@ -89,7 +89,7 @@ __global__ void __launch_bounds__(256) moe_count_kernel(const int32_t *ids, uint
   for (uint32_t a = blockIdx.x * blockDim.x + threadIdx.x; a < rows; a += gridDim.x * blockDim.x) {
     const int32_t e = ids[a];
     if (e < 0 || static_cast<uint32_t>(e) >= experts) {
-      atomicOr(status, kStatusBadExpert);
+      if (e != IGNIS_MOE_NO_EXPERT) atomicOr(status, kStatusBadExpert);  // -1 is "no expert for this choice": skipped, not an error
     } else {
       atomicAdd(&counts[e], 1u);
     }
@@ -170,7 +170,7 @@ __global__ void __launch_bounds__(1024) moe_group_small_kernel(const int32_t *id
   for (uint32_t a = threadIdx.x; a < rows; a += 1024) {
     const int32_t e = ids[a];
     if (e < 0 || static_cast<uint32_t>(e) >= experts) {
-      atomicOr(status, kStatusBadExpert);
+      if (e != IGNIS_MOE_NO_EXPERT) atomicOr(status, kStatusBadExpert);  // -1 is "no expert for this choice": skipped, not an error
     } else {
       atomicAdd(&counts[e], 1u);
     }

@@ -174,13 +174,12 @@ def experts_decode(x, ids, weights, table: SlotTable, ws: Workspace) -> torch.Te
     return _experts(_lib.load().ignis_moe_experts_decode, x, ids, weights, table, ws)
 
 
-def experts_rows(rows: torch.Tensor, local_ids: torch.Tensor, row_weights: torch.Tensor, table: SlotTable,
-                 ws: Workspace) -> torch.Tensor:
-    """The owner's side of the expert-parallel exchange (``ignis_b200.moe_ep``): every received row
-    is a one-choice token over this rank's own slot table. Needs a geometry with ``top_k == 1``
-    and ``experts`` = the rank's share. Returns the rows' weighted outputs, int64 fixed point."""
-    if _geometry.top_k != 1:
-        raise MoeError("experts_rows needs a one-choice geometry (set_geometry(hidden, inter, local_experts, 1))")
+def experts_tokens(rows: torch.Tensor, local_ids: torch.Tensor, row_weights: torch.Tensor, table: SlotTable,
+                   ws: Workspace) -> torch.Tensor:
+    """The owner's side of the expert-parallel exchange (``ignis_b200.moe_ep``): the tokens this rank
+    was sent, their ids local to its slot table or ``IGNIS_MOE_NO_EXPERT`` (-1) for choices owned
+    elsewhere. Needs a geometry whose ``experts`` is the rank's share. Returns, per token, the
+    weighted sum of its owned experts, int64 fixed point."""
     count = rows.shape[0]
     ws.acc[:count].zero_()
     experts_prefill(rows.contiguous(), local_ids.contiguous(), row_weights.contiguous(), table, ws)

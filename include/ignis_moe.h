@@ -52,6 +52,11 @@ extern "C" {
  * the workspace initialisation of a load; not thread-safe against running ops. */
 int32_t b200q_moe_set_geometry(uint32_t hidden, uint32_t inter, uint32_t experts, uint32_t top_k);
 
+/* Not in the reference: an expert id that means "this choice has no expert here". The expert ops
+ * skip it without setting a status bit (every other id outside the table is skipped and reported),
+ * so a rank of an expert-parallel group can run a token whose other choices live elsewhere. */
+#define IGNIS_MOE_NO_EXPERT (-1)
+
 /* One slot-table entry: ignis_moe.h:65-69 (16 bytes). A record is the trellis tensor, then suh
  * (fp16, `in`), then svh (fp16, `out`), each 16-byte aligned. The table of a layer is experts * 2
  * entries indexed expert * 2 + projection. */

@@ -1,7 +1,8 @@
 """The expert-parallel exchange with two CPU ranks over gloo: every rank holds half the tokens and
-owns half the experts, a stand-in expert (exact integer arithmetic, so sums are order-free) runs
-where the device kernels would, and the combined fixed-point accumulator equals the one a single
-rank computes for the same assignments, bit for bit. Skewed routing (one expert in every token,
+owns half the experts, tokens travel once per owner with the ids that owner does not hold marked
+-1, a stand-in expert (exact integer arithmetic, so sums are order-free) runs where the device
+kernels would, and the combined fixed-point accumulator equals the one a single rank computes for
+the same assignments, bit for bit. Skewed routing (one expert in every token,
 one rank receiving almost nothing) and an empty rank are included. No GPU."""
 from __future__ import annotations
 
@@ -25,9 +26,11 @@ def _free_port() -> int:
 
 
 def _expert(rows: torch.Tensor, expert: torch.Tensor, weight: torch.Tensor) -> torch.Tensor:
-    """Stand-in: out = round(2^32 w) * (expert + 1) * row, all integers."""
+    """Stand-in for a token's owned experts: sum over its choices of round(2^32 w) * (expert + 1) * row,
+    all integers; choices marked -1 (no expert on this rank) add nothing."""
     w_fixed = torch.round(weight.double() * 4294967296.0).to(torch.int64)
-    return w_fixed * (expert.to(torch.int64) + 1) * rows.to(torch.int64)
+    factor = torch.where(expert >= 0, w_fixed * (expert.to(torch.int64) + 1), torch.zeros_like(w_fixed)).sum(dim=1, keepdim=True)
+    return factor * rows.to(torch.int64)
 
 
 def _case(case: int, world: int):
@@ -60,16 +63,14 @@ def _worker(rank: int, world: int, port: int, failures) -> None:
             seen = []
 
             def run_local(rows, local, wrow):
-                assert local.dtype == torch.int32 and local.shape == (rows.shape[0], 1)
-                assert int(local.min()) >= 0 and int(local.max()) < end - begin
-                seen.append(rows.shape[0])
-                return _expert(rows, local + begin, wrow)
+                assert local.dtype == torch.int32 and local.shape == (rows.shape[0], TOP_K)
+                assert int(local.min()) >= -1 and int(local.max()) < end - begin
+                assert bool((local >= 0).any(dim=1).all())        # nobody is sent a token it owns nothing of
+                seen.append(int((local >= 0).sum()))
+                return _expert(rows, torch.where(local >= 0, local + begin, local), wrow)
 
             acc = moe_ep.routed_experts(xs[rank], ids[rank], ws[rank], EXPERTS, run_local)
-            want = torch.zeros((xs[rank].shape[0], HIDDEN), dtype=torch.int64)
-            for t in range(xs[rank].shape[0]):
-                for c in range(TOP_K):
-                    want[t] += _expert(xs[rank][t:t + 1], ids[rank][t, c].reshape(1, 1), ws[rank][t, c].reshape(1, 1))[0]
+            want = _expert(xs[rank], ids[rank], ws[rank])   # one rank owning every expert
             assert torch.equal(acc, want), f"case {case}: combined accumulator differs from the single-rank sum"
             # every assignment of every rank landed on exactly one owner
             total = torch.tensor([sum(seen)], dtype=torch.int64)

@@ -208,3 +208,20 @@ def test_plan_record_bytes_and_reconstruct(mo, oracle, golden):
     words = torch.from_numpy(g["trellis"].view(np.int16).reshape(-1)).cuda()
     recon = mo.trellis_reconstruct(words, 5, 256, 128)
     assert np.array_equal(recon.view(torch.int16).cpu().numpy().view(np.uint16), g["reconstruct"])
+
+
+def test_no_expert_id_is_skipped_silently(mo, oracle):
+    """IGNIS_MOE_NO_EXPERT (-1) marks a choice that has no expert on this rank (expert-parallel
+    groups): it adds nothing and sets no status bit, unlike any other id outside the table."""
+    mo.set_geometry(256, 128, 8, 2)
+    rng = np.random.default_rng(9)
+    rec = Records(mo, oracle, rng, 256, 128, 8)
+    x = torch.randn(4, 256, generator=torch.Generator().manual_seed(9)).to(torch.bfloat16)
+    ids = np.array([[0, -1], [-1, 5], [3, 4], [-1, -1]], np.int32)
+    w = np.full((4, 2), 0.5, np.float32)
+    ws = mo.Workspace(4, 4)
+    acc = mo.experts_prefill(x.cuda(), torch.from_numpy(ids).cuda(), torch.from_numpy(w).cuda(), rec.table, ws)
+    assert ws.status() == 0
+    ref = routed_reference(oracle, rec, x[:3], np.array([[0, 0], [5, 5], [3, 4]], np.int32), np.array([[.5, 0], [0, .5], [.5, .5]]), 256)
+    check_tokens(acc[:3], ref)
+    assert int(acc[3].abs().sum().item()) == 0
