@@ -327,14 +327,21 @@ def run_moe_workload(args) -> None:
     out_host = torch.empty((m["x"].shape[0], 2048), dtype=torch.bfloat16).pin_memory()
     stream = torch.cuda.Stream()
 
+    side = torch.cuda.Stream()   # the shared expert needs no exchange: it runs beside it
+
     def one_step():
         if world == 1:
             moe.experts_prefill(m["x"], m["ids"], m["weights"], m["table"], m["ws"])
-            acc = None
-        else:
-            acc = moe_ep.routed_experts(m["x"], m["ids"], m["weights"], m["experts"],
-                                        lambda rows, local, w: moe.experts_tokens(rows, local, w, m["table"], m["ws"]))
-        shared, _ = moe.shared_expert(m["shared"][0], m["shared"][1], m["shared"][2], m["x"])
+            shared, _ = moe.shared_expert(m["shared"][0], m["shared"][1], m["shared"][2], m["x"])
+            return moe.combine(m["ws"], shared, m["x"], m["w_gate"])
+        main = torch.cuda.current_stream()
+        side.wait_stream(main)
+        with torch.cuda.stream(side):
+            shared, _ = moe.shared_expert(m["shared"][0], m["shared"][1], m["shared"][2], m["x"])
+        acc = moe_ep.routed_experts(m["x"], m["ids"], m["weights"], m["experts"],
+                                    lambda rows, local, w: moe.experts_tokens(rows, local, w, m["table"], m["ws"]))
+        main.wait_stream(side)
+        shared.record_stream(main)
         return moe.combine(m["ws"], shared, m["x"], m["w_gate"], acc=acc)
 
     def barrier() -> None:
