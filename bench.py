@@ -448,9 +448,12 @@ def run_side_workload(args) -> None:
 
             def one_step() -> None:
                 for w, x, y in items:
-                    nvfp4.linear(x, w, out=y, policy=nvfp4.ALLOW_A4, workspace=ws)
+                    if args.a16:
+                        nvfp4.linear(x, w, out=y)   # A16: BF16 activations as they are, weights decoded into the MMA
+                    else:
+                        nvfp4.linear(x, w, out=y, policy=nvfp4.ALLOW_A4, workspace=ws)
 
-            launches = 2 * len(items)
+            launches = (1 if args.a16 else 2) * len(items)
             if args.mlp:
                 # the layers' MLP through one entry: gate|up with the SwiGLU + re-quantizing epilogue, then down
                 gen.manual_seed(20261130)
@@ -471,6 +474,9 @@ def run_side_workload(args) -> None:
                 launches = 3
             metric, unit, work = "nvfp4_prefill_gemm_tflops", "TFLOP/s", flops / 1e12
             workload = f"configs[2]: NVFP4 W4A4 prefill GEMM, M={tokens}, up 5120->17408 and down 17408->5120, fused-layout activation quantizer + tcgen05 block-scaled MMA"
+            if args.a16:
+                workload = (f"configs[2]'s shapes under the A16 policy, M={tokens}: weights decoded to BF16 in shared memory, "
+                            "tcgen05 kind::f16 MMA, no activation quantization")
             if args.mlp:
                 workload = (f"configs[2] as the layer's MLP, M={tokens}: gate|up 5120->34816 with SwiGLU and the down product's "
                             "quantizer in its epilogue, then down 17408->5120; one activation quantizer launch")
@@ -534,7 +540,12 @@ def run_side_workload(args) -> None:
             torch.cuda.synchronize()
         ms = start.elapsed_time(stop) / args.steps
     value = work / (ms * 1e-3)
-    if args.workload == "prefill":
+    if args.workload == "prefill" and args.a16:
+        peak = 1403.2
+        roof = {"bound": "tensor", "achieved": value, "peak": peak, "unit": "TFLOP/s", "frac": value / peak,
+                "peak_source": "measured sustained BF16 cuBLAS rate", "frac_of_nominal_2250": value / 2250.0,
+                "kernel": "nvfp4_a16_mma_kernel", "traffic": None, "device_status": nvfp4.device_status()}
+    elif args.workload == "prefill":
         status = ws.status()
         peak = 4.0 * 1403.2
         roof = {"bound": "tensor", "achieved": value, "peak": peak, "unit": "TFLOP/s", "frac": value / peak,
@@ -547,7 +558,7 @@ def run_side_workload(args) -> None:
                 "kernel": "trellis_linear_kernel", "traffic": None}  # also the head workload
     print(json.dumps({"metric": metric, "value": value, "unit": unit, "n_gpus": 1, "steps": args.steps, "warmup": args.warmup,
                       "ms_per_step": ms, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
-                      "dtype": "e2m1xe2m1->f32" if args.workload == "prefill" else "f16xf16->f32", "data": "synthetic",
+                      "dtype": ("bf16xbf16->f32" if args.a16 else "e2m1xe2m1->f32") if args.workload == "prefill" else "f16xf16->f32", "data": "synthetic",
                       "config": {"workload": workload, "cuda_graph": bool(args.graph), "l2": "inputs larger than L2"},
                       "gpu_launches": launches * args.steps, "clocks": clocks.summary(), "roofline": roof}))
 
@@ -721,6 +732,7 @@ def main() -> None:
                     help="decode workload under torchrun: weak = per-GPU work fixed (default), strong = configs[1] cut in N")
     ap.add_argument("--gather", type=int, default=0, help="decode workload under torchrun: 1 all-gathers every output after its product (NCCL); 2 the fused form (peer stores + device barrier)")
     ap.add_argument("--moe-tokens", type=int, default=4096, help="tokens of the --workload moe step (configs[4]: 4096; up to 8 takes the decode entry's item size)")
+    ap.add_argument("--a16", type=int, default=0, help="with --workload prefill: 1 runs the two products under the A16 policy")
     ap.add_argument("--mlp", type=int, default=0, help="with --workload prefill: 1 runs the fused MLP entry instead of two plain products")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--workload", default="decode", choices=["decode", "prefill", "trellis", "moe", "head"],

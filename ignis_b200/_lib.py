@@ -40,6 +40,7 @@ NVFP4_SYMBOLS = {
                                              C.POINTER(Workspace), C.c_void_p]),
     "b200q_nvfp4_linear_swiglu": (C.c_int32, [C.POINTER(Nvfp4Weight), C.c_void_p, C.c_uint32, C.c_void_p, C.c_uint32,
                                               C.c_uint32, C.POINTER(Workspace), C.c_void_p]),
+    "b200q_nvfp4_device_status": (C.c_int32, [C.c_void_p, C.POINTER(C.c_uint32)]),
     "b200q_nvfp4_linear_split": (C.c_int32, [C.POINTER(Nvfp4Weight), C.c_uint32, C.POINTER(C.c_uint32), C.POINTER(C.c_uint32), C.c_void_p,
                                              C.c_uint32, C.POINTER(C.c_void_p), C.POINTER(C.c_uint32), C.c_uint32, C.c_uint32,
                                              C.POINTER(Workspace), C.c_void_p]),

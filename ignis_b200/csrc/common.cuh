@@ -39,6 +39,7 @@ struct DeviceState {
   int gemv_kc = 0;       // B200Q_GEMV_KC: its cluster size (0: auto)
   int gemv_ctas_per_sm = 2;
   int gemv_slots[9] = {};  // CTAs of the NVFP4 decode kernel resident at once, by cluster size (0: unknown)
+  int a16_mma = 1;       // B200Q_A16_MMA: A16 calls of more than 8 tokens take the tensor-core kernel
   int w4a4_persistent = 1;  // B200Q_W4A4_PERSISTENT: one CTA per SM walking the tiles
   int w4a4_bn = 128;     // B200Q_W4A4_BN: weight rows per tile of the plain W4A4 product (128 or 256)
   int gemv_xu = 8;       // B200Q_GEMV_XU: words per row of 8 decoded by the hardware E2M1 conversion

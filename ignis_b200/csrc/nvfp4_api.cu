@@ -43,6 +43,29 @@ int32_t decode_route(ErrorSlot &slot, const DeviceState &dev, const b200q_nvfp4_
   const size_t out_elem = (epilogue & kEpilogueF32) ? 4u : 2u;
   uint32_t groups = 0;
   for (uint32_t i = 0; i < count; ++i) groups += w[i]->n / 32u;
+  if (dev.a16_mma != 0 && tokens > 16u && !swiglu && peers == 1u && a16mma_takes(k, x)) {
+    // beyond two token tiles the warp-level MMAs of the decode kernel are the limit: the weights
+    // are decoded once per tile of up to 256 tokens and multiplied on the tensor cores
+    {
+      const uint32_t t0 = 0, pass = tokens;
+      GemvWeight gw[kMaxGroup];
+      for (uint32_t i = 0; i < count; ++i) {
+        gw[i].codes = static_cast<const uint8_t *>(w[i]->codes);
+        gw[i].scales = static_cast<const uint8_t *>(w[i]->scales);
+        gw[i].y[0] = static_cast<uint8_t *>(y[i]) + static_cast<size_t>(t0) * ldy[i] * out_elem;
+        gw[i].peers = 1;
+        gw[i].n = w[i]->n;
+        gw[i].ldy = ldy[i];
+        gw[i].inv_dw = 1.0f / w[i]->weight_scale_divisor;
+        gw[i].block_begin = 0;
+      }
+      if (a16mma_launch(slot, dev, gw, count, static_cast<const uint16_t *>(x) + static_cast<size_t>(t0) * k, k, pass, epilogue,
+                        stream) != 0) {
+        return -1;
+      }
+    }
+    return 0;
+  }
   for (uint32_t t0 = 0; t0 < tokens; t0 += B200Q_NVFP4_DECODE_MAX_TOKENS) {
     const uint32_t pass = tokens - t0 < B200Q_NVFP4_DECODE_MAX_TOKENS ? tokens - t0 : B200Q_NVFP4_DECODE_MAX_TOKENS;
     const int nt = pass <= 8 ? 1 : (pass <= 16 ? 2 : 4);
@@ -130,6 +153,7 @@ int32_t b200q_nvfp4_prepare(void) {
   ErrorSlot &slot = nvfp4_error();
   if (prepare_device(slot) != 0) return -1;
   if (gemv_prepare(slot) != 0) return -1;
+  if (a16mma_prepare(slot) != 0) return -1;
   return w4a4_prepare(slot);
 }
 
@@ -185,6 +209,12 @@ int32_t b200q_nvfp4_linear_group(const b200q_nvfp4_weight *const *w, uint32_t co
     return fail(nvfp4_error(), "b200q_nvfp4_linear_group: unknown epilogue 0x%x", epilogue);
   }
   return linear_group_impl(w, count, x, tokens, y, ldy, epilogue, policy, workspace, stream, "b200q_nvfp4_linear_group");
+}
+
+int32_t b200q_nvfp4_device_status(void *stream, uint32_t *status) {
+  ErrorSlot &slot = nvfp4_error();
+  if (status == nullptr) return fail(slot, "b200q_nvfp4_device_status: status is NULL");
+  return a16mma_status(slot, static_cast<cudaStream_t>(stream), status);
 }
 
 int32_t b200q_nvfp4_linear_split(const b200q_nvfp4_weight *parent, uint32_t count, const uint32_t *row_begin, const uint32_t *rows,

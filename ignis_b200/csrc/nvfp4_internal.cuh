@@ -58,6 +58,13 @@ int32_t dequantize_launch(ErrorSlot &slot, const uint8_t *codes, const uint8_t *
 int32_t quantize_activations_launch(ErrorSlot &slot, const uint16_t *x, uint32_t tokens, uint32_t k, float d_in,
                                     uint8_t *codes, uint8_t *scales, cudaStream_t stream);
 
+// A16 products on the tensor cores (nvfp4_a16mma.cu): passes of up to 256 tokens.
+int32_t a16mma_prepare(ErrorSlot &slot);
+bool a16mma_takes(uint32_t k, const void *x);
+int32_t a16mma_launch(ErrorSlot &slot, const DeviceState &dev, const GemvWeight *weights, uint32_t count, const uint16_t *x,
+                      uint32_t k, uint32_t tokens, uint32_t epilogue, cudaStream_t stream);
+int32_t a16mma_status(ErrorSlot &slot, cudaStream_t stream, uint32_t *status);
+
 // The tensor-core prefill route (nvfp4_w4a4.cu).
 int32_t w4a4_prepare(ErrorSlot &slot);
 bool w4a4_shape_ok(uint32_t n, uint32_t k);

@@ -71,6 +71,7 @@ int32_t prepare_device(ErrorSlot &slot) {
   fresh.gemv_kc = env_int("B200Q_GEMV_KC", 0);
   fresh.gemv_ctas_per_sm = env_int("B200Q_GEMV_CTAS_PER_SM", 2);
   fresh.gemv_xu = env_int("B200Q_GEMV_XU", 8);
+  fresh.a16_mma = env_int("B200Q_A16_MMA", 1);
   fresh.w4a4_persistent = env_int("B200Q_W4A4_PERSISTENT", 1);
   fresh.w4a4_bn = env_int("B200Q_W4A4_BN", 128) == 256 ? 256 : 128;
   fresh.sm_cap = env_int("IGNIS_TRELLIS_SM_CAP", 0);

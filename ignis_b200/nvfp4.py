@@ -214,6 +214,13 @@ def linear_group(x: torch.Tensor, weights: list[Weight], outs: list[torch.Tensor
     return ys
 
 
+def device_status() -> int:
+    """``b200q_nvfp4_device_status``: non-zero after a bounded device-side wait ran out."""
+    word = C.c_uint32(0)
+    _check(_lib.load().b200q_nvfp4_device_status(_stream(), C.byref(word)))
+    return int(word.value)
+
+
 def linear_split(x: torch.Tensor, parent: Weight, row_counts: list[int], outs: list[torch.Tensor] | None = None,
                  policy: int = A16_ONLY, epilogue: int = STORE, workspace: Workspace | None = None) -> list[torch.Tensor]:
     """A single-parent split-output projection (ninfer::ops::attn_input_proj / gdn_input_proj over an

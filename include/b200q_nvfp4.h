@@ -210,6 +210,12 @@ int32_t b200q_nvfp4_quantize_activations(const void *x, uint32_t tokens, uint32_
 int32_t b200q_nvfp4_linear_noalloc(const b200q_nvfp4_weight *w, const void *x, uint32_t tokens, void *y,
                                    uint32_t ldy, uint32_t epilogue, void *stream);
 
+/* The status word of the kernels that take no workspace (A16 calls of more than 8 tokens run on the
+ * tensor cores with bounded device-side waits): copied to *status after `stream` has finished. 0
+ * unless a wait ran out, in which case that call's output is not valid. The word is per device and
+ * sticky. */
+int32_t b200q_nvfp4_device_status(void *stream, uint32_t *status);
+
 /* Thread-local message from the most recent failed call. Never NULL. */
 const char *b200q_nvfp4_last_error(void);
 

@@ -114,6 +114,32 @@ def test_linear_a16(nv, oracle, n, k, tokens):
     check_bf16(nv.linear(x.cuda(), w), ref)
 
 
+@pytest.mark.parametrize("tokens,n,k", [(17, 128, 64), (24, 256, 320), (40, 384, 1024), (100, 1024, 5120), (300, 256, 2048), (64, 5120, 6144)])
+def test_a16_tensor_core_route(nv, oracle, tokens, n, k):
+    """A16 calls of more than 8 tokens: weights decoded to fp16 in shared memory, BF16 activations as
+    they are, tcgen05 kind::f16 with FP32 accumulation. Token tiles 32 / 64 / 128 / 256, two passes at
+    300 tokens, K split over a cluster for the narrow weights; STORE, OUT_F32 and ADD."""
+    rng = np.random.default_rng(tokens + n + k)
+    codes, scales, d_w = make_weight(rng, n, k)
+    w = nv.Weight.from_planes(codes, scales, d_w)
+    x = torch.randn(tokens, k, generator=torch.Generator().manual_seed(k + tokens)).to(torch.bfloat16)
+    ref = ref_product(oracle, codes, scales, n, k, d_w, x)
+    y32 = nv.linear(x.cuda(), w, epilogue=nv.OUT_F32)
+    assert nv.device_status() == 0
+    check_f32(y32, ref)
+    check_bf16(nv.linear(x.cuda(), w), ref)
+    base = torch.randn(tokens, n, generator=torch.Generator().manual_seed(1)).to(torch.bfloat16)
+    y = nv.linear(x.cuda(), w, out=base.clone().cuda(), epilogue=nv.ADD)
+    once = (y32.cpu() + base.float()).to(torch.bfloat16)      # one rounding of acc + residual
+    assert torch.equal(y.cpu(), once)
+    # the same bits again, and a group shares the launch
+    assert torch.equal(nv.linear(x.cuda(), w, epilogue=nv.OUT_F32), y32)
+    pair = nv.linear_group(x.cuda(), [w, w], epilogue=nv.OUT_F32)   # may split K differently: same values, not same bits
+    assert torch.equal(pair[0], pair[1])
+    check_f32(pair[0], ref)
+    assert nv.device_status() == 0
+
+
 def test_config0_full_size(nv, oracle):
     """BASELINE configs[0]: M = 1, K = 5120, N = 17408, tensor scale 1/448."""
     n, k = 17408, 5120
