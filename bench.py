@@ -590,6 +590,9 @@ def run_cuda_arm(args) -> None:
 
     gather = args.gather == 1 and world > 1
     fused = args.gather == 2 and world > 1
+    # "a16" (the headline): BF16 activations as they are. "a4": the reference engine's default AllowA4
+    # policy, under which these calls quantize their activations from 4 / 5 / 8 tokens (W4A4).
+    policy = nvfp4.ALLOW_A4 if args.policy == "a4" and not fused else nvfp4.A16_ONLY
     if gather:
         from ignis_b200 import shard
 
@@ -611,9 +614,9 @@ def run_cuda_arm(args) -> None:
                                                [w.n * rank for w in ws])
                     peer.barrier()
                 elif len(names) == 1:
-                    nvfp4.linear(src, layer[names[0]], out=outputs[names[0]])
+                    nvfp4.linear(src, layer[names[0]], out=outputs[names[0]], policy=policy)
                 else:
-                    nvfp4.linear_group(src, [layer[nm] for nm in names], outs=[outputs[nm] for nm in names])
+                    nvfp4.linear_group(src, [layer[nm] for nm in names], outs=[outputs[nm] for nm in names], policy=policy)
                 if gather:   # rejoin the column shards where a consumer would need the full width
                     for nm in names:
                         shard.gather_columns(outputs[nm], out=full[nm])
@@ -687,7 +690,9 @@ def run_cuda_arm(args) -> None:
         "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": args.scaling, "vs_baseline": None, "dtype": "f16xf16->f32",
         "data": "synthetic",
         "config": {"workload": "configs[1]: NVFP4 decode, 8 lanes (M=8), 27B-style dense layer (q,k,v,o,gate,up,down), hidden 5120",
-                   "layers": args.layers, "tokens": tokens, "policy": "A16", "sharding": (f"column-wise over N, {world} rank(s); " +
+                   "layers": args.layers, "tokens": tokens,
+                   "policy": "AllowA4 (activations quantized to NVFP4 inside the product, W4A4 on tcgen05)" if policy == nvfp4.ALLOW_A4 else "A16",
+                   "device_status": nvfp4.device_status(), "sharding": (f"column-wise over N, {world} rank(s); " +
                                 ("every rank holds configs[1]-sized shards of a layer N times as wide (per-GPU work fixed)"
                                  if args.scaling == "weak" else "configs[1] itself cut in N (total work fixed)")),
                    "calls_per_layer": len(calls), "cuda_graph": bool(args.graph) and not gather,
@@ -732,6 +737,8 @@ def main() -> None:
                     help="decode workload under torchrun: weak = per-GPU work fixed (default), strong = configs[1] cut in N")
     ap.add_argument("--gather", type=int, default=0, help="decode workload under torchrun: 1 all-gathers every output after its product (NCCL); 2 the fused form (peer stores + device barrier)")
     ap.add_argument("--moe-tokens", type=int, default=4096, help="tokens of the --workload moe step (configs[4]: 4096; up to 8 takes the decode entry's item size)")
+    ap.add_argument("--policy", choices=["a16", "a4"], default="a16",
+                    help="decode workload: a16 (headline) or a4, the reference's AllowA4 policy (W4A4 from 4 / 5 / 8 tokens)")
     ap.add_argument("--a16", type=int, default=0, help="with --workload prefill: 1 runs the two products under the A16 policy")
     ap.add_argument("--mlp", type=int, default=0, help="with --workload prefill: 1 runs the fused MLP entry instead of two plain products")
     ap.add_argument("--no-cpu-baseline", action="store_true")

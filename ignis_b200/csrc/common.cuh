@@ -41,6 +41,11 @@ struct DeviceState {
   int gemv_slots[9] = {};  // CTAs of the NVFP4 decode kernel resident at once, by cluster size (0: unknown)
   int a16_mma = 1;       // B200Q_A16_MMA: A16 calls of more than 8 tokens take the tensor-core kernel
   int w4a4_persistent = 1;  // B200Q_W4A4_PERSISTENT: one CTA per SM walking the tiles
+  int a4_decode = 1;     // B200Q_A4_DECODE: AllowA4 calls of up to 32 tokens take the W4A4 decode kernel (0: the A16 route)
+  int a4_slots[9] = {};      // CTAs of the W4A4 decode kernel placed at one per SM, by cluster size (0: unknown)
+  int a4_decode_kc = 0;      // B200Q_A4_DECODE_KC: cluster size of that kernel (0: planned)
+  int a4_decode_groups = 0;  // B200Q_A4_DECODE_GROUPS: quantizer groups per CTA of that kernel (0: chosen by the token count)
+  int a4_decode_ctas = 2;  // B200Q_A4_DECODE_CTAS: CTAs of that kernel per SM (1: one CTA with a ring twice as deep)
   int w4a4_bn = 128;     // B200Q_W4A4_BN: weight rows per tile of the plain W4A4 product (128 or 256)
   int gemv_xu = 8;       // B200Q_GEMV_XU: words per row of 8 decoded by the hardware E2M1 conversion
   int sm_cap = 0;        // IGNIS_TRELLIS_SM_CAP

@@ -24,9 +24,7 @@
 //    (b200q_nvfp4_device_status) and the CTA falls through to the common exit, frees its tensor
 //    memory and returns.
 #include "nvfp4_internal.cuh"
-
-#include <cuda.h>
-#include <cudaTypedefs.h>
+#include "nvfp4_tc.cuh"
 
 #include <mutex>
 
@@ -35,79 +33,10 @@ namespace {
 
 constexpr int kBM = 128;             // weight rows per CTA
 constexpr uint32_t kABytes = kBM * 128;  // one stage of BF16 weights: 128 rows x 64 values
-constexpr uint32_t kSpin = 1u << 22;
 constexpr uint32_t kProducerTimeout = 0x10u, kMmaTimeout = 0x20u, kEpilogueTimeout = 0x40u, kDecodeTimeout = 0x80u;
 constexpr int kRing = 4;             // stages of codes a thread keeps in registers
 
 __device__ uint32_t g_a16_status = 0;
-
-__device__ __forceinline__ uint32_t smem_u32(const void *p) { return static_cast<uint32_t>(__cvta_generic_to_shared(p)); }
-__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
-  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
-}
-__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
-  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
-}
-__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
-  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
-}
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
-  for (uint32_t spin = 0; spin < kSpin; ++spin) {
-    uint32_t done;
-    asm volatile("{ .reg .pred p; mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2; selp.u32 %0, 1, 0, p; }"
-                 : "=r"(done)
-                 : "r"(bar), "r"(parity)
-                 : "memory");
-    if (done) return true;
-  }
-  return false;
-}
-__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap *map, uint32_t bar, int32_t x, int32_t y) {
-  asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
-               ::"r"(dst), "l"(map), "r"(bar), "r"(x), "r"(y)
-               : "memory");
-}
-// K-major operand tile with the 128-byte swizzle: rows of 128 bytes, groups of 8 rows 1024 bytes apart.
-__device__ __forceinline__ uint64_t smem_desc_sw128(uint32_t addr) {
-  return static_cast<uint64_t>((addr & 0x3FFFFu) >> 4) | (static_cast<uint64_t>(1024u >> 4) << 32) | (1ull << 46) | (2ull << 61);
-}
-__device__ __forceinline__ void mma_f16(uint32_t d, uint64_t a, uint64_t b, uint32_t idesc, uint32_t accumulate) {
-  asm volatile("{ .reg .pred p; setp.ne.u32 p, %4, 0;\n"
-               "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p; }"
-               ::"r"(d), "l"(a), "l"(b), "r"(idesc), "r"(accumulate)
-               : "memory");
-}
-__device__ __forceinline__ void mma_commit(uint32_t bar) {
-  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
-}
-__device__ __forceinline__ void tmem_ld32(uint32_t addr, uint32_t (&r)[32]) {
-  asm volatile(
-      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
-      "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
-      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
-        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
-        "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
-        "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
-      : "r"(addr)
-      : "memory");
-}
-__device__ __forceinline__ uint32_t cluster_ctarank() {
-  uint32_t r;
-  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
-  return r;
-}
-__device__ __forceinline__ void cluster_sync_all() {
-  asm volatile("barrier.cluster.arrive.release.aligned;\n"
-               "barrier.cluster.wait.acquire.aligned;" ::: "memory");
-}
-__device__ __forceinline__ float ld_cluster_f32(const float *local_smem, uint32_t rank) {
-  const uint32_t local = static_cast<uint32_t>(__cvta_generic_to_shared(local_smem));
-  uint32_t remote;
-  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(local), "r"(rank));
-  float v;
-  asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(remote) : "memory");
-  return v;
-}
 
 struct A16Weight {
   const uint8_t *codes;
@@ -375,23 +304,6 @@ __global__ void __launch_bounds__(192) nvfp4_a16_mma_kernel(const __grid_constan
 }
 
 // ---- host side --------------------------------------------------------------------------------
-using EncodeTiledFn = CUresult (*)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
-                                   const cuuint64_t *, const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave,
-                                   CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-
-EncodeTiledFn encode_tiled_fn() {
-  static EncodeTiledFn fn = [] {
-    void *sym = nullptr;
-    cudaDriverEntryPointQueryResult result;
-    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &result) != cudaSuccess ||
-        result != cudaDriverEntryPointSuccess) {
-      return static_cast<EncodeTiledFn>(nullptr);
-    }
-    return reinterpret_cast<EncodeTiledFn>(sym);
-  }();
-  return fn;
-}
-
 constexpr size_t kA16MaxSmem = 220 * 1024;
 
 size_t a16_smem_bytes(uint32_t bn, uint32_t stages) { return static_cast<size_t>(stages) * (kABytes + bn * 128u) + 8u * (2u * stages + 1u) + 16u + 1024u; }

@@ -99,6 +99,44 @@ int32_t decode_route(ErrorSlot &slot, const DeviceState &dev, const b200q_nvfp4_
   return 0;
 }
 
+// Tokens from which the reference's AllowA4 policy quantizes the activations, by problem
+// (nvfp4_dispatch.cpp:31-39): its fused GDN input always, attention inputs from 4 tokens, gate|up
+// from 5, the projections back to the residual stream from 8. Shapes are told apart by their
+// proportions, so that other model sizes of the same family resolve alike.
+uint32_t a4_min_tokens(uint32_t n_total, uint32_t k) {
+  if (n_total < k) return 8;
+  if (n_total >= 4u * k) return 5;
+  if (n_total == 16384u && k == 5120u) return 1;
+  return 4;
+}
+
+// Calls of up to 32 tokens. B200Q_NVFP4_ALLOW_A4 from the reference's per-problem thresholds: the
+// activations are quantized inside the W4A4 decode kernel (no workspace). Everything else: the A16
+// routes.
+int32_t narrow_route(ErrorSlot &slot, const DeviceState &dev, const b200q_nvfp4_weight *const *w, uint32_t count, const void *x,
+                     uint32_t tokens, void *const *y, const uint32_t *ldy, uint32_t epilogue, uint32_t policy,
+                     cudaStream_t stream) {
+  const bool swiglu = (epilogue & kEpilogueSwiglu) != 0u;
+  if (policy == B200Q_NVFP4_ALLOW_A4 && dev.a4_decode != 0 && !swiglu && tokens <= kA4DecodeMaxTokens) {
+    uint32_t n_total = 0;
+    bool takes = true;
+    for (uint32_t i = 0; i < count; ++i) {
+      n_total += w[i]->n;
+      takes = takes && w4a4_decode_takes(w[i]->n, w[i]->k, tokens) && std::isfinite(w[i]->input_scale_divisor) &&
+              w[i]->input_scale_divisor > 0.0f;
+    }
+    if (takes && tokens >= a4_min_tokens(n_total, w[0]->k)) {
+      A4Item items[kMaxGroup];
+      for (uint32_t i = 0; i < count; ++i) {
+        items[i] = A4Item{static_cast<const uint8_t *>(w[i]->codes), static_cast<const uint8_t *>(w[i]->scales), y[i], w[i]->n, ldy[i],
+                          w[i]->weight_scale_divisor, w[i]->input_scale_divisor};
+      }
+      return w4a4_decode_launch(slot, dev, items, count, static_cast<const uint16_t *>(x), w[0]->k, tokens, epilogue, stream);
+    }
+  }
+  return decode_route(slot, dev, w, count, x, tokens, y, ldy, epilogue, stream);
+}
+
 int32_t linear_group_impl(const b200q_nvfp4_weight *const *w, uint32_t count, const void *x, uint32_t tokens,
                           void *const *y, const uint32_t *ldy, uint32_t epilogue, uint32_t policy,
                           const b200q_nvfp4_workspace *workspace, void *stream, const char *what) {
@@ -120,9 +158,8 @@ int32_t linear_group_impl(const b200q_nvfp4_weight *const *w, uint32_t count, co
   }
   const DeviceState *dev = prepared_state(slot, what);
   if (dev == nullptr) return -1;
-  // Wide calls under B200Q_NVFP4_ALLOW_A4 quantize the activations and take the tensor-core route
-  // (the reference's AllowA4 resolution, nvfp4_dispatch.cpp:31-39, with one threshold); everything
-  // else takes the decode route, which re-reads the weights once per 32 tokens.
+  // Wide calls under B200Q_NVFP4_ALLOW_A4 quantize the activations into the workspace and take the
+  // prefill kernels; everything else takes the A16 routes.
   if (policy == B200Q_NVFP4_ALLOW_A4 && tokens > B200Q_NVFP4_DECODE_MAX_TOKENS && count == 1 &&
       !(swiglu && (epilogue & kEpilogueAdd)) && w4a4_shape_ok(w[0]->n, w[0]->k)) {
     const b200q_nvfp4_weight *w0 = w[0];
@@ -139,7 +176,7 @@ int32_t linear_group_impl(const b200q_nvfp4_weight *const *w, uint32_t count, co
                        w0->k, w0->weight_scale_divisor, w0->input_scale_divisor, static_cast<const uint16_t *>(x), tokens,
                        y[0], ldy[0], epilogue, static_cast<uint8_t *>(workspace->base), static_cast<cudaStream_t>(stream));
   }
-  return decode_route(slot, *dev, w, count, x, tokens, y, ldy, epilogue, static_cast<cudaStream_t>(stream));
+  return narrow_route(slot, *dev, w, count, x, tokens, y, ldy, epilogue, policy, static_cast<cudaStream_t>(stream));
 }
 
 }  // namespace
@@ -154,6 +191,7 @@ int32_t b200q_nvfp4_prepare(void) {
   if (prepare_device(slot) != 0) return -1;
   if (gemv_prepare(slot) != 0) return -1;
   if (a16mma_prepare(slot) != 0) return -1;
+  if (w4a4_decode_prepare(slot) != 0) return -1;
   return w4a4_prepare(slot);
 }
 
@@ -214,7 +252,11 @@ int32_t b200q_nvfp4_linear_group(const b200q_nvfp4_weight *const *w, uint32_t co
 int32_t b200q_nvfp4_device_status(void *stream, uint32_t *status) {
   ErrorSlot &slot = nvfp4_error();
   if (status == nullptr) return fail(slot, "b200q_nvfp4_device_status: status is NULL");
-  return a16mma_status(slot, static_cast<cudaStream_t>(stream), status);
+  uint32_t a16 = 0, a4 = 0;
+  if (a16mma_status(slot, static_cast<cudaStream_t>(stream), &a16) != 0) return -1;
+  if (w4a4_decode_status(slot, static_cast<cudaStream_t>(stream), &a4) != 0) return -1;
+  *status = a16 | a4;
+  return 0;
 }
 
 int32_t b200q_nvfp4_linear_split(const b200q_nvfp4_weight *parent, uint32_t count, const uint32_t *row_begin, const uint32_t *rows,
@@ -350,16 +392,16 @@ int32_t b200q_nvfp4_mlp(const b200q_nvfp4_weight *gate_up, const b200q_nvfp4_wei
                            down->weight_scale_divisor, down->input_scale_divisor, static_cast<const uint16_t *>(x), tokens, y, ldy,
                            epilogue, base, s);
   }
-  // narrow calls: the decode route twice, h (BF16) in the workspace behind the status line
+  // narrow calls: two products, h (BF16) in the workspace behind the status line
   void *h = base + 256;
   const b200q_nvfp4_weight *w0[1] = {gate_up};
   void *y0[1] = {h};
   const uint32_t ld0[1] = {inter};
-  if (decode_route(slot, *dev, w0, 1, x, tokens, y0, ld0, kEpilogueSwiglu, s) != 0) return -1;
+  if (narrow_route(slot, *dev, w0, 1, x, tokens, y0, ld0, kEpilogueSwiglu, policy, s) != 0) return -1;
   const b200q_nvfp4_weight *w1[1] = {down};
   void *y1[1] = {y};
   const uint32_t ld1[1] = {ldy};
-  return decode_route(slot, *dev, w1, 1, h, tokens, y1, ld1, epilogue, s);
+  return narrow_route(slot, *dev, w1, 1, h, tokens, y1, ld1, epilogue, policy, s);
 }
 
 int32_t b200q_nvfp4_linear_swiglu(const b200q_nvfp4_weight *gate_up, const void *x, uint32_t tokens, void *h, uint32_t ldh,

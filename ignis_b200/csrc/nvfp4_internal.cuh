@@ -65,6 +65,22 @@ int32_t a16mma_launch(ErrorSlot &slot, const DeviceState &dev, const GemvWeight 
                       uint32_t k, uint32_t tokens, uint32_t epilogue, cudaStream_t stream);
 int32_t a16mma_status(ErrorSlot &slot, cudaStream_t stream, uint32_t *status);
 
+// W4A4 at decode and verify widths (nvfp4_w4a4_decode.cu): activations quantized inside the kernel,
+// no workspace.
+constexpr uint32_t kA4DecodeMaxTokens = 32;
+struct A4Item {
+  const uint8_t *codes;
+  const uint8_t *scales;
+  void *y;
+  uint32_t n, ldy;
+  float d_w, d_in;
+};
+int32_t w4a4_decode_prepare(ErrorSlot &slot);
+bool w4a4_decode_takes(uint32_t n, uint32_t k, uint32_t tokens);
+int32_t w4a4_decode_launch(ErrorSlot &slot, const DeviceState &dev, const A4Item *items, uint32_t count, const uint16_t *x,
+                           uint32_t k, uint32_t tokens, uint32_t epilogue, cudaStream_t stream);
+int32_t w4a4_decode_status(ErrorSlot &slot, cudaStream_t stream, uint32_t *status);
+
 // The tensor-core prefill route (nvfp4_w4a4.cu).
 int32_t w4a4_prepare(ErrorSlot &slot);
 bool w4a4_shape_ok(uint32_t n, uint32_t k);

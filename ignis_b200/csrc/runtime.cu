@@ -73,6 +73,10 @@ int32_t prepare_device(ErrorSlot &slot) {
   fresh.gemv_xu = env_int("B200Q_GEMV_XU", 8);
   fresh.a16_mma = env_int("B200Q_A16_MMA", 1);
   fresh.w4a4_persistent = env_int("B200Q_W4A4_PERSISTENT", 1);
+  fresh.a4_decode = env_int("B200Q_A4_DECODE", 1);
+  fresh.a4_decode_kc = env_int("B200Q_A4_DECODE_KC", 0);
+  fresh.a4_decode_groups = env_int("B200Q_A4_DECODE_GROUPS", 0);
+  fresh.a4_decode_ctas = env_int("B200Q_A4_DECODE_CTAS", 2) == 1 ? 1 : 2;
   fresh.w4a4_bn = env_int("B200Q_W4A4_BN", 128) == 256 ? 256 : 128;
   fresh.sm_cap = env_int("IGNIS_TRELLIS_SM_CAP", 0);
   if (fresh.sm_cap < 0 || fresh.sm_cap > fresh.sm_count) fresh.sm_cap = 0;

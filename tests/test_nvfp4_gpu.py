@@ -101,6 +101,35 @@ def test_quantize_activations_is_bit_exact(nv, oracle):
         assert np.array_equal(codes.cpu().numpy(), want_c)
 
 
+def test_quantize_activations_code_boundaries(nv, oracle):
+    """Quotients on and beside every E2M1 rounding boundary (ties go to the even code), over many
+    binades and divisors with long significands, and dense random blocks: the device's shared-
+    reciprocal division must give the correctly rounded quotient the host's division gives."""
+    mids = torch.tensor([0.25, 0.75, 1.25, 1.75, 2.5, 3.5, 5.0])
+    rows = []
+    for e in range(-24, 25):
+        base = (mids * 2.0 ** e).to(torch.bfloat16)
+        bits = base.view(torch.int16)
+        near = torch.cat([base, (bits + 1).view(torch.bfloat16), (bits - 1).view(torch.bfloat16)])   # 21 values
+        for sign in (1.0, -1.0):
+            for amax in (6.0, 5.0, 3.5, 448.0):
+                block = torch.zeros(32, dtype=torch.bfloat16)
+                block[0] = amax * 2.0 ** e
+                block[16] = amax * 2.0 ** e
+                block[1:16] = sign * near[:15]
+                block[17:23] = sign * near[15:]
+                rows.append(block)
+    x = torch.stack(rows).reshape(-1, 64)
+    gen = torch.Generator().manual_seed(5)
+    dense = (torch.rand(256, 1024, generator=gen) * 2 - 1) * torch.exp2(torch.randint(-30, 30, (256, 1), generator=gen).float())
+    for xs in (x, dense.to(torch.bfloat16)):
+        for d_in in (1.0, 3.0, 448.0, 0.3, 3.7e-3, 1234.567, 2.0 ** -20):
+            codes, scales = nv.quantize_activations(xs.cuda(), d_in)
+            want_c, want_s = oracle.nvfp4_quantize_act(bf16_bits(xs), d_in)
+            assert np.array_equal(scales.cpu().numpy(), want_s)
+            assert np.array_equal(codes.cpu().numpy(), want_c)
+
+
 @pytest.mark.parametrize("n,k", [(128, 64), (128, 256), (256, 320), (384, 1024), (1024, 5120), (5120, 6144)])
 @pytest.mark.parametrize("tokens", [1, 3, 8, 13, 32])
 def test_linear_a16(nv, oracle, n, k, tokens):
@@ -427,6 +456,58 @@ def test_mlp_matches_its_parts(nv, oracle, tokens):
     assert torch.equal(got_add, once)
     with pytest.raises(nv.Nvfp4Error):
         nv.mlp(x, down, down, ws, policy=policy)   # a fused parent needs n a multiple of 256 (and down.k = n / 2)
+
+
+@pytest.mark.parametrize("tokens,n,k", [(4, 256, 256), (8, 128, 1024), (8, 1024, 5120), (13, 384, 768), (16, 512, 2048),
+                                        (17, 256, 512), (32, 640, 1280), (8, 5120, 6144), (5, 2048, 512)])
+def test_w4a4_decode_route(nv, oracle, tokens, n, k):
+    """ALLOW_A4 at decode and verify widths (the reference's default policy from 4 / 5 / 8 tokens):
+    activations quantized inside the kernel, no workspace; parity against the reference's W4A4
+    arithmetic on the host."""
+    rng = np.random.default_rng(3 * tokens + n + k)
+    codes, scales, d_w = make_weight(rng, n, k)
+    d_in = 448.0
+    w = nv.Weight.from_planes(codes, scales, d_w, d_in)
+    x = torch.randn(tokens, k, generator=torch.Generator().manual_seed(k + tokens)).to(torch.bfloat16)
+    ref = w4a4_reference(oracle, codes, scales, n, k, d_w, d_in, x)
+    y32 = nv.linear(x.cuda(), w, policy=nv.ALLOW_A4, epilogue=nv.OUT_F32)
+    assert nv.device_status() == 0
+    check_f32(y32, ref)
+    # not the A16 product: the route was taken
+    assert not torch.equal(y32, nv.linear(x.cuda(), w, policy=nv.A16_ONLY, epilogue=nv.OUT_F32))
+    y16 = nv.linear(x.cuda(), w, policy=nv.ALLOW_A4)
+    check_bf16(y16, ref)
+    exact = ref_product(oracle, codes, scales, n, k, d_w, x)
+    assert np.linalg.norm(y16.double().cpu().numpy() - exact) <= 0.16 * np.linalg.norm(exact)
+    # the residual form rounds once, and a strided output is respected
+    residual = torch.randn(tokens, n + 64, generator=torch.Generator().manual_seed(2)).to(torch.bfloat16).cuda()
+    got = nv.linear(x.cuda(), w, out=residual.clone()[:, :n], policy=nv.ALLOW_A4, epilogue=nv.ADD)
+    assert torch.equal(got, (y32 + residual[:, :n].float()).to(torch.bfloat16))
+    assert nv.device_status() == 0
+
+
+def test_w4a4_decode_thresholds_and_groups(nv, oracle):
+    """Below the reference's thresholds ALLOW_A4 is the A16 product bit for bit; a group (each weight
+    under its own input divisor) agrees with the host arithmetic weight by weight."""
+    k = 1024
+    rng = np.random.default_rng(11)
+    shapes = [(768, 448.0), (128, 96.0), (256, 448.0)]
+    planes = [make_weight(rng, n, k) for n, _ in shapes]
+    ws = [nv.Weight.from_planes(c, s, d_w, d_in) for (c, s, d_w), (_, d_in) in zip(planes, shapes)]
+    for tokens, same in ((3, True), (4, False)):   # n_total = 1152 >= k: quantized from 4 tokens
+        x = torch.randn(tokens, k, generator=torch.Generator().manual_seed(tokens)).to(torch.bfloat16)
+        a4 = nv.linear_group(x.cuda(), ws, policy=nv.ALLOW_A4)
+        a16 = nv.linear_group(x.cuda(), ws, policy=nv.A16_ONLY)
+        for (c, s, d_w), (n, d_in), got, plain in zip(planes, shapes, a4, a16):
+            assert torch.equal(got, plain) == same
+            if not same:
+                check_bf16(got, w4a4_reference(oracle, c, s, n, k, d_w, d_in, x))
+    # a projection back to the residual stream (n < k) keeps A16 up to 7 tokens
+    c, s, d_w = make_weight(rng, 256, k)
+    w = nv.Weight.from_planes(c, s, d_w, 448.0)
+    x = torch.randn(7, k, generator=torch.Generator().manual_seed(7)).to(torch.bfloat16).cuda()
+    assert torch.equal(nv.linear(x, w, policy=nv.ALLOW_A4), nv.linear(x, w, policy=nv.A16_ONLY))
+    assert nv.device_status() == 0
 
 
 @pytest.mark.parametrize("tokens,n,k", [(128, 256, 256), (200, 256, 512), (33, 128, 1024), (300, 384, 768), (256, 512, 2048)])
