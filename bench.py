@@ -381,6 +381,7 @@ def run_moe_workload(args) -> None:
         e2e_stop.record(stream)
         barrier()
         e2e_ms = e2e_start.elapsed_time(e2e_stop)
+
     status = m["ws"].status()
     times = torch.tensor([device_ms, e2e_ms, float(status)], dtype=torch.float64, device=device)
     if world > 1:
@@ -602,7 +603,7 @@ def run_cuda_arm(args) -> None:
 
         peer = shard.PeerOutputs({name: (tokens, outputs[name].shape[1] * world) for name in outputs})
 
-    def one_step() -> None:
+    def one_step(policy: int = policy) -> None:
         for layer in weights:
             for names in calls:
                 src = inputs[by_name[names[0]][2]]
@@ -669,6 +670,26 @@ def run_cuda_arm(args) -> None:
         barrier()
         e2e_ms = e2e_start.elapsed_time(e2e_stop)
 
+        # the same step under the reference engine's default policy, timed the same way, reported beside
+        # the headline (never instead of it)
+        a4_ms = None
+        if policy == nvfp4.A16_ONLY and world == 1 and args.graph and tokens >= 4:
+            one_step(nvfp4.ALLOW_A4)
+            stream.synchronize()
+            a4_graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(a4_graph, stream=stream):
+                one_step(nvfp4.ALLOW_A4)
+            for _ in range(args.warmup):
+                a4_graph.replay()
+            a4_start, a4_stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            torch.cuda.synchronize()
+            a4_start.record(stream)
+            for _ in range(args.steps):
+                a4_graph.replay()
+            a4_stop.record(stream)
+            torch.cuda.synchronize()
+            a4_ms = a4_start.elapsed_time(a4_stop) / args.steps
+
     times = torch.tensor([device_ms, e2e_ms], dtype=torch.float64, device=device)
     if world > 1:
         dist.all_reduce(times, op=dist.ReduceOp.MAX)
@@ -711,6 +732,12 @@ def run_cuda_arm(args) -> None:
                      "kernel": "nvfp4_gemv_kernel<1>", "bytes_per_launch": per_rank_bytes / launches_per_step,
                      "us_per_launch": ms_per_step * 1e3 / launches_per_step, "traffic": TRAFFIC_PER_LAUNCH / split},
     }
+    if a4_ms is not None:
+        a4_value = job_bytes / (a4_ms * 1e-3) / 1e9
+        line["allow_a4"] = {"policy": "the reference engine's default AllowA4: activations quantized to NVFP4 inside each product "
+                                      "(from 4 / 5 / 8 tokens by problem), W4A4 on tcgen05, weights from HBM to the tensor cores by TMA",
+                            "value": a4_value, "unit": UNIT, "ms_per_step": a4_ms, "frac": a4_value / peak,
+                            "kernel": "w4a4_decode_kernel", "us_per_launch": a4_ms * 1e3 / launches_per_step}
     if world == 1 and not args.no_cpu_baseline:
         v, desc = cpu_sample()
         line["cpu_baseline"] = {"value": v, "unit": UNIT, **desc}

@@ -116,13 +116,12 @@ uint32_t a4_min_tokens(uint32_t n_total, uint32_t k) {
 int32_t narrow_route(ErrorSlot &slot, const DeviceState &dev, const b200q_nvfp4_weight *const *w, uint32_t count, const void *x,
                      uint32_t tokens, void *const *y, const uint32_t *ldy, uint32_t epilogue, uint32_t policy,
                      cudaStream_t stream) {
-  const bool swiglu = (epilogue & kEpilogueSwiglu) != 0u;
-  if (policy == B200Q_NVFP4_ALLOW_A4 && dev.a4_decode != 0 && !swiglu && tokens <= kA4DecodeMaxTokens) {
+  if (policy == B200Q_NVFP4_ALLOW_A4 && dev.a4_decode != 0 && tokens <= kA4DecodeMaxTokens) {
     uint32_t n_total = 0;
     bool takes = true;
     for (uint32_t i = 0; i < count; ++i) {
       n_total += w[i]->n;
-      takes = takes && w4a4_decode_takes(w[i]->n, w[i]->k, tokens) && std::isfinite(w[i]->input_scale_divisor) &&
+      takes = takes && w4a4_decode_takes(w[i]->n, w[i]->k, tokens, epilogue) && std::isfinite(w[i]->input_scale_divisor) &&
               w[i]->input_scale_divisor > 0.0f;
     }
     if (takes && tokens >= a4_min_tokens(n_total, w[0]->k)) {

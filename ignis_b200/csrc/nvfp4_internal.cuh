@@ -76,7 +76,7 @@ struct A4Item {
   float d_w, d_in;
 };
 int32_t w4a4_decode_prepare(ErrorSlot &slot);
-bool w4a4_decode_takes(uint32_t n, uint32_t k, uint32_t tokens);
+bool w4a4_decode_takes(uint32_t n, uint32_t k, uint32_t tokens, uint32_t epilogue);
 int32_t w4a4_decode_launch(ErrorSlot &slot, const DeviceState &dev, const A4Item *items, uint32_t count, const uint16_t *x,
                            uint32_t k, uint32_t tokens, uint32_t epilogue, cudaStream_t stream);
 int32_t w4a4_decode_status(ErrorSlot &slot, cudaStream_t stream, uint32_t *status);

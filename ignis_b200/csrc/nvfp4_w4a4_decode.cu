@@ -17,6 +17,9 @@
 //    turn, so a group has several stage times for its stage.
 //  * The last warp owns tensor memory: per stage it copies both operands' scale tiles there (tcgen05.cp)
 //    and issues four tcgen05.mma kind::mxf4nvf4 block_scale scale_vec::4X (M 128, N, K 64).
+//  * The fused SwiGLU (a gate|up parent) pairs a tile's 128 gate rows with their up rows: per K
+//    stage two ring entries, each with its own weight tile, sharing the first one's token tile,
+//    into two accumulators; the epilogue writes BF16(silu(BF16(g alpha)) * BF16(u alpha)).
 //  * Narrow weights split K over the CTAs of a cluster, which meet in distributed shared memory and
 //    add their partial sums in rank order (bit-reproducible, no global scratch).
 //  * Every mbarrier wait is bounded; one that runs out sets a bit in the library's status word
@@ -31,7 +34,7 @@ namespace {
 constexpr uint32_t kABytes = 128 * 128;   // one stage of weight codes: 128 rows x 256 values
 constexpr uint32_t kSfBytes = 4 * 512;    // one stage of scales of a 128-row tile: four K-atoms
 constexpr uint32_t kProducerTimeout = 0x100u, kMmaTimeout = 0x200u, kEpilogueTimeout = 0x400u, kQuantTimeout = 0x800u;
-constexpr int kMaxQuantGroups = 4;
+constexpr int kMaxQuantGroups = 2;
 constexpr int kMaxItems = 4;              // 16-value items per quantizer thread and stage (32 tokens)
 
 __device__ uint32_t g_a4_status = 0;
@@ -58,8 +61,8 @@ struct A4Params {
   uint32_t stages;     // ring depth
   uint32_t groups;     // quantizer groups of 128 threads; then the producer warp and the MMA warp
   uint32_t kc;         // cluster size: K slices
-  uint32_t tmem_cols;  // accumulator (32) + 32 scale columns per stage, rounded up to a power of two
-  uint32_t epilogue;   // STORE / ADD / OUT_F32
+  uint32_t tmem_cols;  // accumulators (64) + 32 scale columns per ring entry, rounded up to a power of two
+  uint32_t epilogue;   // STORE / ADD / OUT_F32, or the fused SwiGLU
 };
 
 __device__ __forceinline__ void tma_load_2d_hint(uint32_t dst, const CUtensorMap *map, uint32_t bar, int32_t x, int32_t y,
@@ -86,7 +89,7 @@ struct RawItem {
   uint4 lo, hi;  // 16 BF16 activations
 };
 
-__global__ void __launch_bounds__(64 + 128 * kMaxQuantGroups) w4a4_decode_kernel(const __grid_constant__ A4Maps maps, const __grid_constant__ A4Params p) {
+__global__ void __launch_bounds__(64 + 128 * kMaxQuantGroups, 2) w4a4_decode_kernel(const __grid_constant__ A4Maps maps, const __grid_constant__ A4Params p) {
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw = smem_u32(smem_raw);
   const uint32_t base = (raw + 1023u) & ~1023u;
@@ -106,6 +109,8 @@ __global__ void __launch_bounds__(64 + 128 * kMaxQuantGroups) w4a4_decode_kernel
     if (i < p.count && blockIdx.x >= p.w[i].block_begin) wi = i;
   }
   const A4Weight &W = p.w[wi];
+  const bool swiglu = (p.epilogue & kEpilogueSwiglu) != 0u;
+  const uint32_t halves = swiglu ? 2u : 1u;   // ring entries per K stage: the gate tile, then the up tile
   const uint32_t m_tile = (blockIdx.x - W.block_begin) / kc;
   const uint32_t k_stages = p.k / 256u, k_atoms = p.k / 64u;
   const uint32_t s0 = static_cast<uint32_t>(static_cast<uint64_t>(k_stages) * rank / kc);
@@ -163,7 +168,8 @@ __global__ void __launch_bounds__(64 + 128 * kMaxQuantGroups) w4a4_decode_kernel
       }
     }
     bool ok = true;
-    for (uint32_t s = first, it = group; s < s1 && ok; s += p.groups, it += p.groups) {
+    for (uint32_t s = first; s < s1 && ok; s += p.groups) {
+      const uint32_t it = (s - s0) * halves;   // the stage's (first) ring entry
       uint2 codes[kMaxItems];
       uint8_t scale[kMaxItems];
 #pragma unroll
@@ -202,14 +208,25 @@ __global__ void __launch_bounds__(64 + 128 * kMaxQuantGroups) w4a4_decode_kernel
       // the tiles are read by the tensor core (async proxy): order these writes before it
       asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
       mbar_arrive(bars + 8 * slot);
+      if (swiglu) {   // the up entry reads this token tile: nothing to write, only its turn to take
+        const uint32_t it2 = it + 1u, slot2 = it2 % p.stages;
+        if (!mbar_wait(bars + 8 * (p.stages + slot2), ((it2 / p.stages) & 1u) ^ 1u)) {
+          if (lane == 0) atomicOr(&g_a4_status, kQuantTimeout);
+          ok = false;
+          break;
+        }
+        mbar_arrive(bars + 8 * slot2);
+      }
     }
   } else if (warp == producer_warp) {
     // ---- producer of the weight tiles: they never depend on the previous kernel ----
     griddep_launch_dependents();
     if (lane == 0) {
       const uint64_t policy = l2_evict_first_policy();
-      const uint8_t *scales = W.scales + static_cast<size_t>(m_tile) * k_atoms * 512u;
-      for (uint32_t s = s0, it = 0; s < s1; ++s, ++it) {
+      const uint32_t entries = (s1 - s0) * halves;
+      for (uint32_t it = 0; it < entries; ++it) {
+        const uint32_t s = s0 + it / halves;
+        const uint32_t row0 = m_tile * 128u + ((it % halves) != 0u ? W.n / 2u : 0u);   // the up rows lie n / 2 further down
         const uint32_t slot = it % p.stages;
         if (!mbar_wait(bars + 8 * (p.stages + slot), ((it / p.stages) & 1u) ^ 1u)) {
           atomicOr(&g_a4_status, kProducerTimeout);
@@ -218,8 +235,9 @@ __global__ void __launch_bounds__(64 + 128 * kMaxQuantGroups) w4a4_decode_kernel
         const uint32_t full = bars + 8 * slot;
         const uint32_t stage = base + slot * stage_bytes;
         mbar_expect_tx(full, kABytes + kSfBytes);
-        tma_load_2d_hint(stage, &maps.m[wi], full, static_cast<int32_t>(s * 128u), static_cast<int32_t>(m_tile * 128u), policy);
-        bulk_load_hint(stage + kABytes + b_bytes, scales + static_cast<size_t>(s) * kSfBytes, kSfBytes, full, policy);
+        tma_load_2d_hint(stage, &maps.m[wi], full, static_cast<int32_t>(s * 128u), static_cast<int32_t>(row0), policy);
+        bulk_load_hint(stage + kABytes + b_bytes, W.scales + (static_cast<size_t>(row0 / 128u) * k_atoms + s * 4u) * 512u, kSfBytes, full,
+                       policy);
       }
     }
   } else {
@@ -230,7 +248,9 @@ __global__ void __launch_bounds__(64 + 128 * kMaxQuantGroups) w4a4_decode_kernel
       // 17, UE4M3 scales (bit 23 clear), M >> 4 at bit 24
       const uint32_t idesc = (1u << 7) | (1u << 10) | ((p.bn >> 3) << 17) | ((128u >> 4) << 24);
       bool ok = true;
-      for (uint32_t s = s0, it = 0; s < s1; ++s, ++it) {
+      const uint32_t entries = (s1 - s0) * halves;
+      for (uint32_t it = 0; it < entries; ++it) {
+        const uint32_t half = it % halves;
         const uint32_t slot = it % p.stages;
         if (!mbar_wait(bars + 8 * slot, (it / p.stages) & 1u)) {
           atomicOr(&g_a4_status, kMmaTimeout);
@@ -238,22 +258,28 @@ __global__ void __launch_bounds__(64 + 128 * kMaxQuantGroups) w4a4_decode_kernel
           break;
         }
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-        const uint32_t stage = base + slot * stage_bytes;
-        const uint32_t sf_cols = tmem + 32u + slot * 32u;  // 16 columns of weight scales, 16 of token scales
+        // the token tile and its scales are those of the stage's first entry
+        const uint32_t b_slot = (it - half) % p.stages;
+        const uint32_t stage = base + slot * stage_bytes, b_stage = base + b_slot * stage_bytes;
+        const uint32_t sf_cols = tmem + 64u + slot * 32u;  // 16 columns of weight scales, 16 of token scales
+        const uint32_t sfb_cols = tmem + 64u + b_slot * 32u + 16u;
         const uint32_t sfa_smem = stage + kABytes + b_bytes, sfb_smem = sfa_smem + kSfBytes;
 #pragma unroll
         for (uint32_t kb = 0; kb < 4; ++kb) {
           tmem_cp_sf(sf_cols + kb * 4u, smem_desc(sfa_smem + kb * 512u, 128u, 0u));
-          tmem_cp_sf(sf_cols + 16u + kb * 4u, smem_desc(sfb_smem + kb * 512u, 128u, 0u));
+          if (half == 0u) tmem_cp_sf(sfb_cols + kb * 4u, smem_desc(sfb_smem + kb * 512u, 128u, 0u));
         }
         const uint64_t a_desc = smem_desc(stage, 1024u, 2u);
-        const uint64_t b_desc = smem_desc(stage + kABytes, 1024u, 2u);
+        const uint64_t b_desc = smem_desc(b_stage + kABytes, 1024u, 2u);
 #pragma unroll
         for (uint32_t kb = 0; kb < 4; ++kb) {   // 64 values along K are 32 bytes: two 16-byte units further
-          mma_mxf4nvf4(tmem, a_desc + 2u * kb, b_desc + 2u * kb, idesc, sf_cols + kb * 4u, sf_cols + 16u + kb * 4u,
-                       (it | kb) != 0u ? 1u : 0u);
+          mma_mxf4nvf4(tmem + half * p.bn, a_desc + 2u * kb, b_desc + 2u * kb, idesc, sf_cols + kb * 4u, sfb_cols + kb * 4u,
+                       (it >= halves || kb != 0u) ? 1u : 0u);
         }
-        mma_commit(bars + 8 * (p.stages + slot));
+        if (half + 1u == halves) {   // the stage's entries go back to their writers together
+          if (swiglu) mma_commit(bars + 8 * (p.stages + b_slot));
+          mma_commit(bars + 8 * (p.stages + slot));
+        }
       }
       if (ok) mma_commit(bars + 8 * 2 * p.stages);
     }
@@ -261,43 +287,59 @@ __global__ void __launch_bounds__(64 + 128 * kMaxQuantGroups) w4a4_decode_kernel
 
   // ---- epilogue: thread r of warps 0-3 owns accumulator lane r = weight row r of the tile ----
   const uint32_t out_elem_f32 = p.epilogue & kEpilogueF32;
-  const uint32_t row = m_tile * 128u + threadIdx.x;
-  float *part = reinterpret_cast<float *>(base_ptr);   // [token][128] partial sums, over the (then idle) stage ring
+  float *part = reinterpret_cast<float *>(base_ptr);   // [half][token][128] partial sums, over the (then idle) stage ring
   bool have = false;
-  uint32_t v[32];
+  uint32_t v[32], u[32];
   if (warp < 4) {
     have = mbar_wait(bars + 8 * 2 * p.stages, 0u);
     if (!have && lane == 0) atomicOr(&g_a4_status, kEpilogueTimeout);
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     if (have) {
       const uint32_t lane_base = tmem + (static_cast<uint32_t>(warp * 32) << 16);
-      if (p.bn == 16u) tmem_ld16(lane_base, v);
-      else tmem_ld32(lane_base, v);
+      if (p.bn == 16u) {
+        tmem_ld16(lane_base, v);
+        if (swiglu) tmem_ld16(lane_base + 16u, u);
+      } else {
+        tmem_ld32(lane_base, v);
+        if (swiglu) tmem_ld32(lane_base + 32u, u);
+      }
       asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
     }
   }
+  // one output: token tl, row r of the tile, from the accumulator sums (the up sum only with SwiGLU)
+  auto emit = [&](uint32_t tl, uint32_t r, float acc, float acc_up) {
+    const size_t at = static_cast<size_t>(tl) * W.ldy + m_tile * 128u + r;
+    const float val = __fmul_rn(acc, W.alpha);   // not contracted into the residual add: one value for every epilogue
+    if (swiglu) {
+      const float gv = __bfloat162float(__float2bfloat16_rn(val));
+      const float uv = __bfloat162float(__float2bfloat16_rn(__fmul_rn(acc_up, W.alpha)));
+      static_cast<__nv_bfloat16 *>(W.y)[at] = __float2bfloat16_rn(gv / (1.0f + __expf(-gv)) * uv);
+    } else if (out_elem_f32) {
+      float *y = static_cast<float *>(W.y);
+      y[at] = (p.epilogue & kEpilogueAdd) ? y[at] + val : val;
+    } else {
+      __nv_bfloat16 *y = static_cast<__nv_bfloat16 *>(W.y);
+      y[at] = __float2bfloat16_rn((p.epilogue & kEpilogueAdd) ? val + __bfloat162float(y[at]) : val);
+    }
+  };
   if (kc == 1u) {
     if (warp < 4 && have) {
 #pragma unroll
       for (int j = 0; j < 32; ++j) {
         if (static_cast<uint32_t>(j) >= p.tokens) break;
-        const size_t at = static_cast<size_t>(j) * W.ldy + row;
-        const float val = __fmul_rn(__uint_as_float(v[j]), W.alpha);
-        if (out_elem_f32) {
-          float *y = static_cast<float *>(W.y);
-          y[at] = (p.epilogue & kEpilogueAdd) ? y[at] + val : val;
-        } else {
-          __nv_bfloat16 *y = static_cast<__nv_bfloat16 *>(W.y);
-          y[at] = __float2bfloat16_rn((p.epilogue & kEpilogueAdd) ? val + __bfloat162float(y[at]) : val);
-        }
+        emit(static_cast<uint32_t>(j), threadIdx.x, __uint_as_float(v[j]), swiglu ? __uint_as_float(u[j]) : 0.0f);
       }
     }
   } else {
     __syncthreads();   // every role is done with the stage ring: the partial sums take its place
+    float *part_up = part + p.bn * 128u;
     if (warp < 4) {
 #pragma unroll
       for (int j = 0; j < 32; ++j) {
-        if (static_cast<uint32_t>(j) < p.bn) part[static_cast<size_t>(j) * 128u + threadIdx.x] = have ? __uint_as_float(v[j]) : 0.0f;
+        if (static_cast<uint32_t>(j) < p.bn) {
+          part[static_cast<size_t>(j) * 128u + threadIdx.x] = have ? __uint_as_float(v[j]) : 0.0f;
+          if (swiglu) part_up[static_cast<size_t>(j) * 128u + threadIdx.x] = have ? __uint_as_float(u[j]) : 0.0f;
+        }
       }
     }
     __syncwarp();
@@ -305,26 +347,22 @@ __global__ void __launch_bounds__(64 + 128 * kMaxQuantGroups) w4a4_decode_kernel
     if (warp < 4) {
       // tokens dealt over the cluster's CTAs in turn; a thread requests the kc partial sums of its
       // output together and adds them in rank order
-      const uint32_t outputs = p.tokens * 128u;
-      for (uint32_t o = rank * 128u + threadIdx.x; o < outputs; o += kc * 128u) {
-        const uint32_t tl = o >> 7, r = o & 127u;
-        float partial[8];
+      for (uint32_t tl = rank; tl < p.tokens; tl += kc) {
+        float pg[8], pu[8];
 #pragma unroll
-        for (uint32_t q = 0; q < 8u; ++q) partial[q] = q < kc ? ld_cluster_f32(part + static_cast<size_t>(tl) * 128u + r, q) : 0.0f;
-        float sum = partial[0];
+        for (uint32_t q = 0; q < 8u; ++q) {
+          pg[q] = q < kc ? ld_cluster_f32(part + static_cast<size_t>(tl) * 128u + threadIdx.x, q) : 0.0f;
+          pu[q] = q < kc && swiglu ? ld_cluster_f32(part_up + static_cast<size_t>(tl) * 128u + threadIdx.x, q) : 0.0f;
+        }
+        float sum = pg[0], sum_up = pu[0];
 #pragma unroll
         for (uint32_t q = 1; q < 8u; ++q) {
-          if (q < kc) sum += partial[q];
+          if (q < kc) {
+            sum += pg[q];
+            sum_up += pu[q];
+          }
         }
-        const size_t at = static_cast<size_t>(tl) * W.ldy + m_tile * 128u + r;
-        const float val = __fmul_rn(sum, W.alpha);
-        if (out_elem_f32) {
-          float *y = static_cast<float *>(W.y);
-          y[at] = (p.epilogue & kEpilogueAdd) ? y[at] + val : val;
-        } else {
-          __nv_bfloat16 *y = static_cast<__nv_bfloat16 *>(W.y);
-          y[at] = __float2bfloat16_rn((p.epilogue & kEpilogueAdd) ? val + __bfloat162float(y[at]) : val);
-        }
+        emit(tl, threadIdx.x, sum, sum_up);
       }
     }
     __syncwarp();
@@ -386,7 +424,8 @@ int32_t w4a4_decode_prepare(ErrorSlot &slot) {
   return 0;
 }
 
-bool w4a4_decode_takes(uint32_t n, uint32_t k, uint32_t tokens) {
+bool w4a4_decode_takes(uint32_t n, uint32_t k, uint32_t tokens, uint32_t epilogue) {
+  if ((epilogue & kEpilogueSwiglu) != 0u && ((n % 256u) != 0 || (epilogue & (kEpilogueAdd | kEpilogueF32)) != 0u)) return false;
   return tokens >= 1u && tokens <= kA4DecodeMaxTokens && (k % 256u) == 0 && (n % 128u) == 0;
 }
 
@@ -401,17 +440,19 @@ int32_t w4a4_decode_launch(ErrorSlot &slot, const DeviceState &dev, const A4Item
   p.bn = tokens <= 16u ? 16u : 32u;
   p.epilogue = epilogue;
   const uint32_t ctas_per_sm = dev.a4_decode_ctas == 1 ? 1u : 2u;
+  const bool swiglu = (epilogue & kEpilogueSwiglu) != 0u;
   const uint32_t k_stages = k / 256u;
-  const uint32_t stages = a4_ring_depth(ctas_per_sm, p.bn, k_stages);
+  uint32_t stages = a4_ring_depth(ctas_per_sm, p.bn, swiglu ? 2u * k_stages : k_stages);
+  if (swiglu) stages &= ~1u;   // a K stage takes two ring entries
   p.stages = stages;
   // quantizer groups: two, so that two CTAs still share an SM's registers
   p.groups = dev.a4_decode_groups > 0 ? static_cast<uint32_t>(dev.a4_decode_groups) : 2u;
   if (p.groups > static_cast<uint32_t>(kMaxQuantGroups)) p.groups = kMaxQuantGroups;
-  uint32_t cols = 32u + 32u * stages;
-  p.tmem_cols = cols <= 64u ? 64u : (cols <= 128u ? 128u : (cols <= 256u ? 256u : 512u));
+  const uint32_t cols = 64u + 32u * stages;
+  p.tmem_cols = cols <= 128u ? 128u : (cols <= 256u ? 256u : 512u);
   // cluster size: narrow weights split K so the launch fills the device
   uint32_t row_tiles = 0;
-  for (uint32_t i = 0; i < count; ++i) row_tiles += items[i].n / 128u;
+  for (uint32_t i = 0; i < count; ++i) row_tiles += (swiglu ? items[i].n / 2u : items[i].n) / 128u;
   // the largest split that still runs as one wave (clusters are placed inside one GPC: sizes 7 and 8
   // leave many slots empty)
   uint32_t kc = 1;
@@ -433,7 +474,7 @@ int32_t w4a4_decode_launch(ErrorSlot &slot, const DeviceState &dev, const A4Item
     g.alpha = 1.0f / (items[i].d_in * items[i].d_w);
     g.d_in = items[i].d_in;
     g.block_begin = ctas;
-    ctas += items[i].n / 128u * kc;
+    ctas += (swiglu ? items[i].n / 2u : items[i].n) / 128u * kc;
     const cuuint64_t dims[2] = {k / 2u, items[i].n};
     const cuuint64_t strides[1] = {k / 2u};
     const cuuint32_t box[2] = {128u, 128u};

@@ -374,13 +374,14 @@ def w4a4_reference(oracle, codes, scales, n, k, d_w, d_in, x_bf16: torch.Tensor)
     return oracle.nvfp4_w4a4_gemm(codes, scales, n, k, d_w, a_codes, a_scales, d_in)
 
 
-def test_w4a4_fused_swiglu(nv, oracle):
-    """The wide SwiGLU call under ALLOW_A4: gate rows [0, n/2) and up rows [n/2, n) of the fused
+@pytest.mark.parametrize("tokens,n,k", [(100, 768, 512), (8, 768, 512), (5, 2048, 256), (16, 512, 2048), (29, 1280, 1024)])
+def test_w4a4_fused_swiglu(nv, oracle, tokens, n, k):
+    """The SwiGLU call under ALLOW_A4, wide (prefill kernel) and at decode widths (decode kernel, K
+    split over a cluster or not): gate rows [0, n/2) and up rows [n/2, n) of the fused
     parent meet in one tensor-core tile; h = BF16(silu(BF16(g)) * BF16(u)) as the reference's
     prefill epilogue rounds (kernel/src/prefill_swiglu.h:73-107). n/2 = 384 makes the last tile
     pair ragged in neither half; 100 tokens leave a ragged token tile."""
-    tokens, n, k = 100, 768, 512
-    rng = np.random.default_rng(99)
+    rng = np.random.default_rng(99 + tokens)
     codes, scales, d_w = make_weight(rng, n, k)
     d_in = 448.0
     w = nv.Weight.from_planes(codes, scales, d_w, d_in)
@@ -391,7 +392,7 @@ def test_w4a4_fused_swiglu(nv, oracle):
     want = (g / (1 + torch.exp(-g)) * u).numpy()
     ws = nv.Workspace(nv.workspace_bytes(n, k, nv.ALLOW_A4, tokens))
     h = nv.linear_swiglu(x.cuda(), w, policy=nv.ALLOW_A4, workspace=ws)
-    assert ws.status() == 0 and h.shape == (tokens, n // 2)
+    assert ws.status() == 0 and nv.device_status() == 0 and h.shape == (tokens, n // 2)
     got = h.double().cpu().numpy()
     # a BF16 rounding of g or u on the other side of a tie moves h by up to 2^-8 of its factors
     scale = np.abs(want).max()
@@ -400,6 +401,7 @@ def test_w4a4_fused_swiglu(nv, oracle):
     # the decode route computes the same function from unquantized activations: inside the A4 allowance
     h16 = nv.linear_swiglu(x.cuda(), w).double().cpu().numpy()
     assert np.linalg.norm(got - h16) <= 0.2 * np.linalg.norm(h16)
+    assert not np.array_equal(got, h16)   # the quantized route was taken
 
 
 @pytest.mark.parametrize("tokens", [6, 90])
@@ -425,7 +427,7 @@ def test_split_outputs_equal_the_full_product(nv, oracle, tokens):
         nv.linear_split(x, parent, [192, 832])   # ranges must be whole 128-row tiles
 
 
-@pytest.mark.parametrize("tokens", [5, 100])
+@pytest.mark.parametrize("tokens", [5, 9, 100])
 def test_mlp_matches_its_parts(nv, oracle, tokens):
     """b200q_nvfp4_mlp against the same ops called one by one. Wide under ALLOW_A4: the gate|up
     epilogue must write the bytes the down product's own quantizer writes from the BF16 h, so the
