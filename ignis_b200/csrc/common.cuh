@@ -43,6 +43,8 @@ struct DeviceState {
   int w4a4_persistent = 1;  // B200Q_W4A4_PERSISTENT: one CTA per SM walking the tiles
   int a4_decode = 1;     // B200Q_A4_DECODE: AllowA4 calls of up to 32 tokens take the W4A4 decode kernel (0: the A16 route)
   int a4_slots[9] = {};      // CTAs of the W4A4 decode kernel placed at one per SM, by cluster size (0: unknown)
+  int trellis_kc_max = 8;    // B200Q_TRELLIS_KC_MAX: largest cluster the trellis linear plans (measurement knob)
+  int a4_decode_pair = -1;   // B200Q_A4_DECODE_PAIR: two row tiles per CTA of that kernel (-1: by the token count)
   int a4_decode_kc = 0;      // B200Q_A4_DECODE_KC: cluster size of that kernel (0: planned)
   int a4_decode_groups = 0;  // B200Q_A4_DECODE_GROUPS: quantizer groups per CTA of that kernel (0: chosen by the token count)
   int a4_decode_ctas = 2;  // B200Q_A4_DECODE_CTAS: CTAs of that kernel per SM (1: one CTA with a ring twice as deep)

@@ -59,6 +59,7 @@ struct A4Params {
   uint32_t k, tokens;
   uint32_t bn;         // token tile (MMA N): 16 or 32
   uint32_t stages;     // ring depth
+  uint32_t pair;       // plain products: 1 = a CTA owns two consecutive row tiles, which share the quantized token tile
   uint32_t groups;     // quantizer groups of 128 threads; then the producer warp and the MMA warp
   uint32_t kc;         // cluster size: K slices
   uint32_t tmem_cols;  // accumulators (64) + 32 scale columns per ring entry, rounded up to a power of two
@@ -110,13 +111,40 @@ __global__ void __launch_bounds__(64 + 128 * kMaxQuantGroups, 2) w4a4_decode_ker
   }
   const A4Weight &W = p.w[wi];
   const bool swiglu = (p.epilogue & kEpilogueSwiglu) != 0u;
-  const uint32_t halves = swiglu ? 2u : 1u;   // ring entries per K stage: the gate tile, then the up tile
+  const bool two = swiglu || p.pair != 0u;
+  const uint32_t halves = two ? 2u : 1u;   // ring entries per K stage: two weight tiles share a token tile
   const uint32_t m_tile = (blockIdx.x - W.block_begin) / kc;
+  // first weight rows of the CTA's tiles: gate rows and their up rows (n / 2 further down), or two
+  // consecutive tiles of a plain product, or one tile
+  const uint32_t row_a = swiglu ? m_tile * 128u : m_tile * 128u * halves;
+  const uint32_t row_b = swiglu ? W.n / 2u + m_tile * 128u : row_a + 128u;
   const uint32_t k_stages = p.k / 256u, k_atoms = p.k / 64u;
   const uint32_t s0 = static_cast<uint32_t>(static_cast<uint64_t>(k_stages) * rank / kc);
   const uint32_t s1 = static_cast<uint32_t>(static_cast<uint64_t>(k_stages) * (rank + 1) / kc);
 
-  if (threadIdx.x == 0) {
+  // One ring entry: a weight tile of K stage s0 + it / halves (entry 2 j is the first tile, 2 j + 1
+  // the second when the CTA has two) and its scale tiles.
+  const uint32_t entries = (s1 - s0) * halves;
+  auto produce = [&](uint32_t it, uint64_t policy) -> bool {
+    const uint32_t s = s0 + it / halves;
+    const uint32_t row0 = (it % halves) != 0u ? row_b : row_a;
+    const uint32_t slot = it % p.stages;
+    if (!mbar_wait(bars + 8 * (p.stages + slot), ((it / p.stages) & 1u) ^ 1u)) {
+      atomicOr(&g_a4_status, kProducerTimeout);
+      return false;
+    }
+    const uint32_t full = bars + 8 * slot;
+    const uint32_t stage = base + slot * stage_bytes;
+    mbar_expect_tx(full, kABytes + kSfBytes);
+    tma_load_2d_hint(stage, &maps.m[wi], full, static_cast<int32_t>(s * 128u), static_cast<int32_t>(row0), policy);
+    bulk_load_hint(stage + kABytes + b_bytes, W.scales + (static_cast<size_t>(row0 / 128u) * k_atoms + s * 4u) * 512u, kSfBytes, full,
+                   policy);
+    return true;
+  };
+  // (Requesting the first ring of weight tiles from here, before tensor memory is allocated, was
+  // measured slower: the early loads take bandwidth from the previous kernel's last CTAs, which
+  // this kernel's quantizers wait for.)
+  if (warp == producer_warp && lane == 0) {
     for (uint32_t s = 0; s < p.stages; ++s) {
       mbar_init(bars + 8 * s, 128 + 1);          // 128 quantizer threads and the producer's expect_tx arrival
       mbar_init(bars + 8 * (p.stages + s), 1);   // the MMA thread's commit
@@ -208,7 +236,7 @@ __global__ void __launch_bounds__(64 + 128 * kMaxQuantGroups, 2) w4a4_decode_ker
       // the tiles are read by the tensor core (async proxy): order these writes before it
       asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
       mbar_arrive(bars + 8 * slot);
-      if (swiglu) {   // the up entry reads this token tile: nothing to write, only its turn to take
+      if (two) {   // the second entry reads this token tile: nothing to write, only its turn to take
         const uint32_t it2 = it + 1u, slot2 = it2 % p.stages;
         if (!mbar_wait(bars + 8 * (p.stages + slot2), ((it2 / p.stages) & 1u) ^ 1u)) {
           if (lane == 0) atomicOr(&g_a4_status, kQuantTimeout);
@@ -223,21 +251,8 @@ __global__ void __launch_bounds__(64 + 128 * kMaxQuantGroups, 2) w4a4_decode_ker
     griddep_launch_dependents();
     if (lane == 0) {
       const uint64_t policy = l2_evict_first_policy();
-      const uint32_t entries = (s1 - s0) * halves;
       for (uint32_t it = 0; it < entries; ++it) {
-        const uint32_t s = s0 + it / halves;
-        const uint32_t row0 = m_tile * 128u + ((it % halves) != 0u ? W.n / 2u : 0u);   // the up rows lie n / 2 further down
-        const uint32_t slot = it % p.stages;
-        if (!mbar_wait(bars + 8 * (p.stages + slot), ((it / p.stages) & 1u) ^ 1u)) {
-          atomicOr(&g_a4_status, kProducerTimeout);
-          break;
-        }
-        const uint32_t full = bars + 8 * slot;
-        const uint32_t stage = base + slot * stage_bytes;
-        mbar_expect_tx(full, kABytes + kSfBytes);
-        tma_load_2d_hint(stage, &maps.m[wi], full, static_cast<int32_t>(s * 128u), static_cast<int32_t>(row0), policy);
-        bulk_load_hint(stage + kABytes + b_bytes, W.scales + (static_cast<size_t>(row0 / 128u) * k_atoms + s * 4u) * 512u, kSfBytes, full,
-                       policy);
+        if (!produce(it, policy)) break;
       }
     }
   } else {
@@ -248,7 +263,6 @@ __global__ void __launch_bounds__(64 + 128 * kMaxQuantGroups, 2) w4a4_decode_ker
       // 17, UE4M3 scales (bit 23 clear), M >> 4 at bit 24
       const uint32_t idesc = (1u << 7) | (1u << 10) | ((p.bn >> 3) << 17) | ((128u >> 4) << 24);
       bool ok = true;
-      const uint32_t entries = (s1 - s0) * halves;
       for (uint32_t it = 0; it < entries; ++it) {
         const uint32_t half = it % halves;
         const uint32_t slot = it % p.stages;
@@ -277,7 +291,7 @@ __global__ void __launch_bounds__(64 + 128 * kMaxQuantGroups, 2) w4a4_decode_ker
                        (it >= halves || kb != 0u) ? 1u : 0u);
         }
         if (half + 1u == halves) {   // the stage's entries go back to their writers together
-          if (swiglu) mma_commit(bars + 8 * (p.stages + b_slot));
+          if (two) mma_commit(bars + 8 * (p.stages + b_slot));
           mma_commit(bars + 8 * (p.stages + slot));
         }
       }
@@ -298,23 +312,18 @@ __global__ void __launch_bounds__(64 + 128 * kMaxQuantGroups, 2) w4a4_decode_ker
       const uint32_t lane_base = tmem + (static_cast<uint32_t>(warp * 32) << 16);
       if (p.bn == 16u) {
         tmem_ld16(lane_base, v);
-        if (swiglu) tmem_ld16(lane_base + 16u, u);
+        if (two) tmem_ld16(lane_base + 16u, u);
       } else {
         tmem_ld32(lane_base, v);
-        if (swiglu) tmem_ld32(lane_base + 32u, u);
+        if (two) tmem_ld32(lane_base + 32u, u);
       }
       asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
     }
   }
-  // one output: token tl, row r of the tile, from the accumulator sums (the up sum only with SwiGLU)
-  auto emit = [&](uint32_t tl, uint32_t r, float acc, float acc_up) {
-    const size_t at = static_cast<size_t>(tl) * W.ldy + m_tile * 128u + r;
+  // token tl, row r of the CTA's tile(s), from the accumulator sums (the second only with two tiles)
+  auto store = [&](size_t at, float acc) {
     const float val = __fmul_rn(acc, W.alpha);   // not contracted into the residual add: one value for every epilogue
-    if (swiglu) {
-      const float gv = __bfloat162float(__float2bfloat16_rn(val));
-      const float uv = __bfloat162float(__float2bfloat16_rn(__fmul_rn(acc_up, W.alpha)));
-      static_cast<__nv_bfloat16 *>(W.y)[at] = __float2bfloat16_rn(gv / (1.0f + __expf(-gv)) * uv);
-    } else if (out_elem_f32) {
+    if (out_elem_f32) {
       float *y = static_cast<float *>(W.y);
       y[at] = (p.epilogue & kEpilogueAdd) ? y[at] + val : val;
     } else {
@@ -322,12 +331,23 @@ __global__ void __launch_bounds__(64 + 128 * kMaxQuantGroups, 2) w4a4_decode_ker
       y[at] = __float2bfloat16_rn((p.epilogue & kEpilogueAdd) ? val + __bfloat162float(y[at]) : val);
     }
   };
+  auto emit = [&](uint32_t tl, uint32_t r, float acc, float acc_b) {
+    const size_t at = static_cast<size_t>(tl) * W.ldy + r;
+    if (swiglu) {
+      const float gv = __bfloat162float(__float2bfloat16_rn(__fmul_rn(acc, W.alpha)));
+      const float uv = __bfloat162float(__float2bfloat16_rn(__fmul_rn(acc_b, W.alpha)));
+      static_cast<__nv_bfloat16 *>(W.y)[at + row_a] = __float2bfloat16_rn(gv / (1.0f + __expf(-gv)) * uv);
+    } else {
+      store(at + row_a, acc);
+      if (two) store(at + row_b, acc_b);
+    }
+  };
   if (kc == 1u) {
     if (warp < 4 && have) {
 #pragma unroll
       for (int j = 0; j < 32; ++j) {
         if (static_cast<uint32_t>(j) >= p.tokens) break;
-        emit(static_cast<uint32_t>(j), threadIdx.x, __uint_as_float(v[j]), swiglu ? __uint_as_float(u[j]) : 0.0f);
+        emit(static_cast<uint32_t>(j), threadIdx.x, __uint_as_float(v[j]), two ? __uint_as_float(u[j]) : 0.0f);
       }
     }
   } else {
@@ -338,7 +358,7 @@ __global__ void __launch_bounds__(64 + 128 * kMaxQuantGroups, 2) w4a4_decode_ker
       for (int j = 0; j < 32; ++j) {
         if (static_cast<uint32_t>(j) < p.bn) {
           part[static_cast<size_t>(j) * 128u + threadIdx.x] = have ? __uint_as_float(v[j]) : 0.0f;
-          if (swiglu) part_up[static_cast<size_t>(j) * 128u + threadIdx.x] = have ? __uint_as_float(u[j]) : 0.0f;
+          if (two) part_up[static_cast<size_t>(j) * 128u + threadIdx.x] = have ? __uint_as_float(u[j]) : 0.0f;
         }
       }
     }
@@ -352,7 +372,7 @@ __global__ void __launch_bounds__(64 + 128 * kMaxQuantGroups, 2) w4a4_decode_ker
 #pragma unroll
         for (uint32_t q = 0; q < 8u; ++q) {
           pg[q] = q < kc ? ld_cluster_f32(part + static_cast<size_t>(tl) * 128u + threadIdx.x, q) : 0.0f;
-          pu[q] = q < kc && swiglu ? ld_cluster_f32(part_up + static_cast<size_t>(tl) * 128u + threadIdx.x, q) : 0.0f;
+          pu[q] = q < kc && two ? ld_cluster_f32(part_up + static_cast<size_t>(tl) * 128u + threadIdx.x, q) : 0.0f;
         }
         float sum = pg[0], sum_up = pu[0];
 #pragma unroll
@@ -442,25 +462,42 @@ int32_t w4a4_decode_launch(ErrorSlot &slot, const DeviceState &dev, const A4Item
   const uint32_t ctas_per_sm = dev.a4_decode_ctas == 1 ? 1u : 2u;
   const bool swiglu = (epilogue & kEpilogueSwiglu) != 0u;
   const uint32_t k_stages = k / 256u;
-  uint32_t stages = a4_ring_depth(ctas_per_sm, p.bn, swiglu ? 2u * k_stages : k_stages);
-  if (swiglu) stages &= ~1u;   // a K stage takes two ring entries
+  // cluster size for `tiles` CTA rows: the largest K split that still runs as one wave (clusters are
+  // placed inside one GPC: sizes 7 and 8 leave many slots empty)
+  auto plan_kc = [&](uint32_t tiles) {
+    uint32_t best = 1;
+    for (uint32_t c = 2; c <= 8u && k_stages / c >= 2u; ++c) {
+      const int known = dev.a4_slots[c];
+      const uint32_t resident = (known > 0 ? static_cast<uint32_t>(known) : static_cast<uint32_t>(dev.sm_count) * 3u / 4u) * ctas_per_sm;
+      if (tiles * c <= resident) best = c;
+    }
+    return best;
+  };
+  uint32_t row_tiles = 0;
+  bool even = true;
+  for (uint32_t i = 0; i < count; ++i) {
+    row_tiles += (swiglu ? items[i].n / 2u : items[i].n) / 128u;
+    even = even && (items[i].n % 256u) == 0;
+  }
+  uint32_t kc = plan_kc(row_tiles);
+  // Two row tiles per CTA halve the quantizers' work per weight byte, K being split twice as often to
+  // keep the CTA count. Worth it where the quantizers bound the kernel and K is hardly split yet:
+  // wide weights at more than 8 tokens.
+  const bool pair = !swiglu && even && k_stages >= 4u && (dev.a4_decode_pair >= 0 ? dev.a4_decode_pair != 0 : tokens > 8u && kc <= 2u);
+  if (pair) {
+    row_tiles /= 2u;
+    kc = plan_kc(row_tiles);
+  }
+  p.pair = pair ? 1u : 0u;
+  const bool two = swiglu || pair;
+  uint32_t stages = a4_ring_depth(ctas_per_sm, p.bn, two ? 2u * k_stages : k_stages);
+  if (two) stages &= ~1u;   // a K stage takes two ring entries
   p.stages = stages;
   // quantizer groups: two, so that two CTAs still share an SM's registers
   p.groups = dev.a4_decode_groups > 0 ? static_cast<uint32_t>(dev.a4_decode_groups) : 2u;
   if (p.groups > static_cast<uint32_t>(kMaxQuantGroups)) p.groups = kMaxQuantGroups;
   const uint32_t cols = 64u + 32u * stages;
   p.tmem_cols = cols <= 128u ? 128u : (cols <= 256u ? 256u : 512u);
-  // cluster size: narrow weights split K so the launch fills the device
-  uint32_t row_tiles = 0;
-  for (uint32_t i = 0; i < count; ++i) row_tiles += (swiglu ? items[i].n / 2u : items[i].n) / 128u;
-  // the largest split that still runs as one wave (clusters are placed inside one GPC: sizes 7 and 8
-  // leave many slots empty)
-  uint32_t kc = 1;
-  for (uint32_t c = 2; c <= 8u && k_stages / c >= 2u; ++c) {
-    const int known = dev.a4_slots[c];
-    const uint32_t resident = (known > 0 ? static_cast<uint32_t>(known) : static_cast<uint32_t>(dev.sm_count) * 3u / 4u) * ctas_per_sm;
-    if (row_tiles * c <= resident) kc = c;
-  }
   if (dev.a4_decode_kc > 0 && static_cast<uint32_t>(dev.a4_decode_kc) <= 8u && k_stages / dev.a4_decode_kc >= 1u) kc = dev.a4_decode_kc;
   p.kc = kc;
   EncodeTiledFn encode = encode_tiled_fn();
@@ -474,7 +511,7 @@ int32_t w4a4_decode_launch(ErrorSlot &slot, const DeviceState &dev, const A4Item
     g.alpha = 1.0f / (items[i].d_in * items[i].d_w);
     g.d_in = items[i].d_in;
     g.block_begin = ctas;
-    ctas += (swiglu ? items[i].n / 2u : items[i].n) / 128u * kc;
+    ctas += (two ? items[i].n / 2u : items[i].n) / 128u * kc;
     const cuuint64_t dims[2] = {k / 2u, items[i].n};
     const cuuint64_t strides[1] = {k / 2u};
     const cuuint32_t box[2] = {128u, 128u};

@@ -74,6 +74,8 @@ int32_t prepare_device(ErrorSlot &slot) {
   fresh.a16_mma = env_int("B200Q_A16_MMA", 1);
   fresh.w4a4_persistent = env_int("B200Q_W4A4_PERSISTENT", 1);
   fresh.a4_decode = env_int("B200Q_A4_DECODE", 1);
+  fresh.trellis_kc_max = env_int("B200Q_TRELLIS_KC_MAX", 8);
+  fresh.a4_decode_pair = env_int("B200Q_A4_DECODE_PAIR", -1);
   fresh.a4_decode_kc = env_int("B200Q_A4_DECODE_KC", 0);
   fresh.a4_decode_groups = env_int("B200Q_A4_DECODE_GROUPS", 0);
   fresh.a4_decode_ctas = env_int("B200Q_A4_DECODE_CTAS", 2) == 1 ? 1 : 2;

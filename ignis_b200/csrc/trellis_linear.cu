@@ -402,7 +402,7 @@ uint32_t plan_kc(const DeviceState &dev, uint32_t in, uint32_t out, int nt, int 
   uint32_t best = 1;
   double best_cost = 1e30;
   for (uint32_t kc = 1; kc <= 8; ++kc) {
-    if (kc > nblk) break;
+    if (kc > nblk || static_cast<int>(kc) > dev.trellis_kc_max) break;
     const uint32_t slice = (nblk + kc - 1) / kc;
     const double ctas = static_cast<double>(col_blocks) * kc;
     const double waves = ceil(ctas / slots);

@@ -461,7 +461,8 @@ def test_mlp_matches_its_parts(nv, oracle, tokens):
 
 
 @pytest.mark.parametrize("tokens,n,k", [(4, 256, 256), (8, 128, 1024), (8, 1024, 5120), (13, 384, 768), (16, 512, 2048),
-                                        (17, 256, 512), (32, 640, 1280), (8, 5120, 6144), (5, 2048, 512)])
+                                        (17, 256, 512), (32, 640, 1280), (8, 5120, 6144), (5, 2048, 512),
+                                        (24, 1024, 1024), (32, 512, 4096), (16, 38400, 1024)])   # the last three: two row tiles per CTA
 def test_w4a4_decode_route(nv, oracle, tokens, n, k):
     """ALLOW_A4 at decode and verify widths (the reference's default policy from 4 / 5 / 8 tokens):
     activations quantized inside the kernel, no workspace; parity against the reference's W4A4
