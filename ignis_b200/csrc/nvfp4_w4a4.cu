@@ -107,7 +107,7 @@ __global__ void __launch_bounds__(192, kBN == 256 ? 1 : 2) w4a4_gemm_kernel(cons
                                                           const __grid_constant__ CUtensorMap map_b,
                                                           const __grid_constant__ W4A4Params p) {
   constexpr int kStages = Tile<kBN>::kStages;
-  constexpr uint32_t kBBytes = Tile<kBN>::kBBytes, kSfbBytes = Tile<kBN>::kSfbBytes, kStageBytes = Tile<kBN>::kStageBytes;
+  constexpr uint32_t kBBytes = Tile<kBN>::kBBytes, kStageBytes = Tile<kBN>::kStageBytes;
   constexpr uint32_t kTmemCols = Tile<kBN>::kTmemCols, kSfColsPerStage = Tile<kBN>::kSfColsPerStage;
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw = smem_u32(smem_raw);
@@ -293,6 +293,128 @@ __global__ void __launch_bounds__(192, kBN == 256 ? 1 : 2) w4a4_gemm_kernel(cons
 // warps pull the whole accumulator into registers (as packed BF16: 128 registers a thread - the
 // CTA has the SM's register file to itself), hand tensor memory back to the MMA thread and only
 // then store, under the next tile's MMAs. What a tile costs beyond its MMAs is the pull alone.
+// ---- the persistent kernels' epilogue for one 128-token x 256-row tile ---------------------------
+// The calling warp q owns accumulator lanes (tokens) 32 q .. 32 q + 31 at `lane_base`. `release()`
+// hands tensor memory back to the MMA thread; it is called as soon as the accumulator has been
+// read, so that whatever follows runs under the next tile's MMAs.
+template <class Release>
+__device__ __forceinline__ void w4a4_epilogue_tile(const W4A4Params &p, uint32_t lane_base, int warp, int lane, uint32_t m_tile,
+                                                   uint32_t n_tile, bool swiglu, Release release) {
+  constexpr int kBN = 256;
+  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+  const uint32_t token = m_tile * kBM + warp * 32 + lane;
+  if (p.epilogue & (kEpilogueF32 | kEpilogueAdd)) {
+    // float32 rows do not fit the register file, and a residual has to be read before the one
+    // rounding: these forms store chunk by chunk, then release
+#pragma unroll 1
+    for (uint32_t c = 0; c < kBN; c += 32) {
+      uint32_t r[32];
+      tmem_ld32(lane_base + c, r);
+      asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+      const uint32_t row0 = n_tile * kBN + c;
+      if (token < p.tokens && row0 < p.n) {
+        const bool add = (p.epilogue & kEpilogueAdd) != 0u;
+        if (p.epilogue & kEpilogueF32) {
+          float4 *dst = reinterpret_cast<float4 *>(static_cast<float *>(p.y) + static_cast<size_t>(token) * p.ldy + row0);
+#pragma unroll
+          for (int j = 0; j < 8; ++j) {
+            float4 o = make_float4(__uint_as_float(r[4 * j]) * p.alpha, __uint_as_float(r[4 * j + 1]) * p.alpha,
+                                   __uint_as_float(r[4 * j + 2]) * p.alpha, __uint_as_float(r[4 * j + 3]) * p.alpha);
+            if (add) {
+              const float4 old = dst[j];
+              o.x += old.x, o.y += old.y, o.z += old.z, o.w += old.w;
+            }
+            dst[j] = o;
+          }
+        } else {
+          uint4 *dst = reinterpret_cast<uint4 *>(static_cast<__nv_bfloat16 *>(p.y) + static_cast<size_t>(token) * p.ldy + row0);
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            const uint4 old = dst[j];
+            const uint32_t ow[4] = {old.x, old.y, old.z, old.w};
+            uint32_t o[4];
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+              const __nv_bfloat162 h = __floats2bfloat162_rn(
+                  __uint_as_float(r[8 * j + 2 * e]) * p.alpha + bf16_bits_to_f32(ow[e] & 0xFFFFu),
+                  __uint_as_float(r[8 * j + 2 * e + 1]) * p.alpha + __uint_as_float(ow[e] & 0xFFFF0000u));
+              o[e] = *reinterpret_cast<const uint32_t *>(&h);
+            }
+            dst[j] = make_uint4(o[0], o[1], o[2], o[3]);
+          }
+        }
+      }
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncwarp();
+    release();
+    return;
+  }
+  // The thread's row as packed BF16: 256 columns of the product, or (SwiGLU) BF16(g alpha) in
+  // [0, 64) and BF16(u alpha) in [64, 128) - the two roundings the reference's formula makes first.
+  uint32_t out[128];
+#pragma unroll
+  for (uint32_t c = 0; c < kBN; c += 32) {
+    uint32_t r[32];
+    tmem_ld32(lane_base + c, r);
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+    for (int j = 0; j < 16; ++j) {
+      const __nv_bfloat162 h = __floats2bfloat162_rn(__uint_as_float(r[2 * j]) * p.alpha, __uint_as_float(r[2 * j + 1]) * p.alpha);
+      out[c / 2 + j] = *reinterpret_cast<const uint32_t *>(&h);
+    }
+  }
+  // tensor memory is free for the next tile's MMAs; the rest runs under them
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncwarp();
+  release();
+  if (swiglu) {
+    // h = BF16(silu(BF16(g)) * BF16(u)), in place over the gate half
+#pragma unroll
+    for (int j = 0; j < 64; ++j) {
+      const float2 g = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162 *>(&out[j]));
+      const float2 u = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162 *>(&out[64 + j]));
+      const __nv_bfloat162 h = __floats2bfloat162_rn(g.x / (1.0f + __expf(-g.x)) * u.x, g.y / (1.0f + __expf(-g.y)) * u.y);
+      out[j] = *reinterpret_cast<const uint32_t *>(&h);
+    }
+  }
+  if (swiglu && (p.epilogue & kEpilogueQuant)) {
+    // h leaves as the down product's operand: 8 blocks of 16 along its K, quantized as the
+    // standalone quantizer would from the BF16 values (padding rows are zeros and stay zeros)
+    const uint32_t inter = p.n / 2u, g0 = n_tile * 8u;
+    uint32_t sc[2] = {0u, 0u};
+    uint4 *code_dst = reinterpret_cast<uint4 *>(p.q_codes + static_cast<uint64_t>(token) * (inter / 2u) + n_tile * 64u);
+#pragma unroll
+    for (int b = 0; b < 8; b += 2) {
+      uint2 c0, c1;
+      uint8_t s0, s1;
+      quantize_block16(make_uint4(out[8 * b], out[8 * b + 1], out[8 * b + 2], out[8 * b + 3]),
+                       make_uint4(out[8 * b + 4], out[8 * b + 5], out[8 * b + 6], out[8 * b + 7]), p.q_din, c0, s0);
+      quantize_block16(make_uint4(out[8 * b + 8], out[8 * b + 9], out[8 * b + 10], out[8 * b + 11]),
+                       make_uint4(out[8 * b + 12], out[8 * b + 13], out[8 * b + 14], out[8 * b + 15]), p.q_din, c1, s1);
+      code_dst[b / 2] = make_uint4(c0.x, c0.y, c1.x, c1.y);
+      sc[b >> 2] |= (static_cast<uint32_t>(s0) << (8 * (b & 3))) | (static_cast<uint32_t>(s1) << (8 * ((b + 1) & 3)));
+    }
+    const uint64_t atom = (static_cast<uint64_t>(token >> 7) * (inter / 64u) + (g0 >> 2)) * 512u + (token & 31u) * 16u +
+                          ((token & 127u) >> 5) * 4u;
+    *reinterpret_cast<uint32_t *>(p.q_scales + atom) = sc[0];
+    *reinterpret_cast<uint32_t *>(p.q_scales + atom + 512u) = sc[1];
+    return;
+  }
+  if (token < p.tokens) {
+    const uint32_t width = swiglu ? 128u : kBN;
+    const uint32_t col0 = n_tile * width;
+    const uint32_t limit = swiglu ? p.n / 2u : p.n;
+    __nv_bfloat16 *row = static_cast<__nv_bfloat16 *>(p.y) + static_cast<size_t>(token) * p.ldy + col0;
+#pragma unroll
+    for (uint32_t c = 0; c < kBN; c += 8) {
+      if (c < width && col0 + c < limit) {  // n is a multiple of 128: an 8-column piece is whole
+        *reinterpret_cast<uint4 *>(row + c) = make_uint4(out[c / 2], out[c / 2 + 1], out[c / 2 + 2], out[c / 2 + 3]);
+      }
+    }
+  }
+}
+
 __global__ void __launch_bounds__(192, 1) w4a4_gemm_persistent_kernel(const __grid_constant__ CUtensorMap map_a,
                                                                      const __grid_constant__ CUtensorMap map_b,
                                                                      const __grid_constant__ W4A4Params p) {
@@ -370,6 +492,9 @@ __global__ void __launch_bounds__(192, 1) w4a4_gemm_persistent_kernel(const __gr
     }
   } else if (warp == 5 && lane == 0) {
     // ---- MMA issuer ----
+    // The scale copies run in the same in-order pipe as the MMAs and take about a quarter of its
+    // time (12 copies of 512 bytes a stage against 4 MMAs). Issuing a stage's copies one stage ahead
+    // of its MMAs was measured slower, not faster: the copies cost pipe time, not latency.
     const uint32_t idesc = (1u << 7) | (1u << 10) | ((kBN >> 3) << 17) | ((kBM >> 4) << 24);
     uint32_t git = 0, tile_i = 0;
     bool ok = true;
@@ -418,124 +543,206 @@ __global__ void __launch_bounds__(192, 1) w4a4_gemm_persistent_kernel(const __gr
         if (lane == 0) atomicOr(p.status, kStatusEpilogueTimeout);
         break;
       }
-      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-      const uint32_t token = m_tile * kBM + warp * 32 + lane;
-      if (p.epilogue & (kEpilogueF32 | kEpilogueAdd)) {
-        // float32 rows do not fit the register file, and a residual has to be read before the one
-        // rounding: these forms store chunk by chunk, then release
-#pragma unroll 1
-        for (uint32_t c = 0; c < kBN; c += 32) {
-          uint32_t r[32];
-          tmem_ld32(lane_base + c, r);
-          asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-          const uint32_t row0 = n_tile * kBN + c;
-          if (token < p.tokens && row0 < p.n) {
-            const bool add = (p.epilogue & kEpilogueAdd) != 0u;
-            if (p.epilogue & kEpilogueF32) {
-              float4 *dst = reinterpret_cast<float4 *>(static_cast<float *>(p.y) + static_cast<size_t>(token) * p.ldy + row0);
-#pragma unroll
-              for (int j = 0; j < 8; ++j) {
-                float4 o = make_float4(__uint_as_float(r[4 * j]) * p.alpha, __uint_as_float(r[4 * j + 1]) * p.alpha,
-                                       __uint_as_float(r[4 * j + 2]) * p.alpha, __uint_as_float(r[4 * j + 3]) * p.alpha);
-                if (add) {
-                  const float4 old = dst[j];
-                  o.x += old.x, o.y += old.y, o.z += old.z, o.w += old.w;
-                }
-                dst[j] = o;
-              }
-            } else {
-              uint4 *dst = reinterpret_cast<uint4 *>(static_cast<__nv_bfloat16 *>(p.y) + static_cast<size_t>(token) * p.ldy + row0);
-#pragma unroll
-              for (int j = 0; j < 4; ++j) {
-                const uint4 old = dst[j];
-                const uint32_t ow[4] = {old.x, old.y, old.z, old.w};
-                uint32_t o[4];
-#pragma unroll
-                for (int e = 0; e < 4; ++e) {
-                  const __nv_bfloat162 h = __floats2bfloat162_rn(
-                      __uint_as_float(r[8 * j + 2 * e]) * p.alpha + bf16_bits_to_f32(ow[e] & 0xFFFFu),
-                      __uint_as_float(r[8 * j + 2 * e + 1]) * p.alpha + __uint_as_float(ow[e] & 0xFFFF0000u));
-                  o[e] = *reinterpret_cast<const uint32_t *>(&h);
-                }
-                dst[j] = make_uint4(o[0], o[1], o[2], o[3]);
-              }
-            }
-          }
-        }
-        asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-        __syncwarp();
+      w4a4_epilogue_tile(p, lane_base, warp, lane, m_tile, n_tile, swiglu, [&] {
         if (lane == 0) mbar_arrive(bar_acc_empty);
-        continue;
-      }
-      // The thread's row as packed BF16: 256 columns of the product, or (SwiGLU) BF16(g alpha) in
-      // [0, 64) and BF16(u alpha) in [64, 128) - the two roundings the reference's formula makes first.
-      uint32_t out[128];
-#pragma unroll
-      for (uint32_t c = 0; c < kBN; c += 32) {
-        uint32_t r[32];
-        tmem_ld32(lane_base + c, r);
-        asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-#pragma unroll
-        for (int j = 0; j < 16; ++j) {
-          const __nv_bfloat162 h = __floats2bfloat162_rn(__uint_as_float(r[2 * j]) * p.alpha, __uint_as_float(r[2 * j + 1]) * p.alpha);
-          out[c / 2 + j] = *reinterpret_cast<const uint32_t *>(&h);
-        }
-      }
-      // tensor memory is free for the next tile's MMAs; the rest runs under them
-      asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-      __syncwarp();
-      if (lane == 0) mbar_arrive(bar_acc_empty);
-      if (swiglu) {
-        // h = BF16(silu(BF16(g)) * BF16(u)), in place over the gate half
-#pragma unroll
-        for (int j = 0; j < 64; ++j) {
-          const float2 g = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162 *>(&out[j]));
-          const float2 u = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162 *>(&out[64 + j]));
-          const __nv_bfloat162 h = __floats2bfloat162_rn(g.x / (1.0f + __expf(-g.x)) * u.x, g.y / (1.0f + __expf(-g.y)) * u.y);
-          out[j] = *reinterpret_cast<const uint32_t *>(&h);
-        }
-      }
-      if (swiglu && (p.epilogue & kEpilogueQuant)) {
-        // h leaves as the down product's operand: 8 blocks of 16 along its K, quantized as the
-        // standalone quantizer would from the BF16 values (padding rows are zeros and stay zeros)
-        const uint32_t inter = p.n / 2u, g0 = n_tile * 8u;
-        uint32_t sc[2] = {0u, 0u};
-        uint4 *code_dst = reinterpret_cast<uint4 *>(p.q_codes + static_cast<uint64_t>(token) * (inter / 2u) + n_tile * 64u);
-#pragma unroll
-        for (int b = 0; b < 8; b += 2) {
-          uint2 c0, c1;
-          uint8_t s0, s1;
-          quantize_block16(make_uint4(out[8 * b], out[8 * b + 1], out[8 * b + 2], out[8 * b + 3]),
-                           make_uint4(out[8 * b + 4], out[8 * b + 5], out[8 * b + 6], out[8 * b + 7]), p.q_din, c0, s0);
-          quantize_block16(make_uint4(out[8 * b + 8], out[8 * b + 9], out[8 * b + 10], out[8 * b + 11]),
-                           make_uint4(out[8 * b + 12], out[8 * b + 13], out[8 * b + 14], out[8 * b + 15]), p.q_din, c1, s1);
-          code_dst[b / 2] = make_uint4(c0.x, c0.y, c1.x, c1.y);
-          sc[b >> 2] |= (static_cast<uint32_t>(s0) << (8 * (b & 3))) | (static_cast<uint32_t>(s1) << (8 * ((b + 1) & 3)));
-        }
-        const uint64_t atom = (static_cast<uint64_t>(token >> 7) * (inter / 64u) + (g0 >> 2)) * 512u + (token & 31u) * 16u +
-                              ((token & 127u) >> 5) * 4u;
-        *reinterpret_cast<uint32_t *>(p.q_scales + atom) = sc[0];
-        *reinterpret_cast<uint32_t *>(p.q_scales + atom + 512u) = sc[1];
-        continue;
-      }
-      if (token < p.tokens) {
-        const uint32_t width = swiglu ? 128u : kBN;
-        const uint32_t col0 = n_tile * width;
-        const uint32_t limit = swiglu ? p.n / 2u : p.n;
-        __nv_bfloat16 *row = static_cast<__nv_bfloat16 *>(p.y) + static_cast<size_t>(token) * p.ldy + col0;
-#pragma unroll
-        for (uint32_t c = 0; c < kBN; c += 8) {
-          if (c < width && col0 + c < limit) {  // n is a multiple of 128: an 8-column piece is whole
-            *reinterpret_cast<uint4 *>(row + c) = make_uint4(out[c / 2], out[c / 2 + 1], out[c / 2 + 2], out[c / 2 + 3]);
-          }
-        }
-      }
+      });
     }
   }
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
   __syncthreads();
   if (warp == 5) {
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(kTmemCols) : "memory");
+  }
+}
+
+// ---- the persistent form on CTA pairs ------------------------------------------------------------
+// Two CTAs of a cluster share a 256-token x 256-row tile (tcgen05 cta_group::2): each CTA holds its
+// 128 tokens' codes and accumulator rows, and only half of the weight rows - the tensor cores read
+// the other half from the peer's shared memory - so a CTA brings 38 KB per K stage where the
+// single-CTA form brings 54 KB for the same FLOPs, and five stages fit where four did. Every load
+// of both CTAs reports to the barrier of the pair's first CTA, whose MMA thread issues for both;
+// its commits arrive at both CTAs' barriers (two plain commits, one per CTA). The scale tiles
+// travel as TMA tiles too (a bulk copy cannot report to the peer's barrier): the scale planes as
+// [tile][128] words.
+constexpr int kPairStages = 5;
+constexpr uint32_t kPairBBytes = 128 * kBKBytes;                                   // this CTA's half of the weight rows
+constexpr uint32_t kPairStageBytes = kABytes + kPairBBytes + kSfaBytes + 2 * 2048;  // + token scales + both halves' weight scales
+constexpr uint32_t kPairSmemBytes = kPairStages * kPairStageBytes + 256 + 1024;
+constexpr uint32_t kPairSfCols = 48;  // per stage: 16 columns of token scales, 32 of weight scales
+// The shared::cluster address of this CTA's `addr` in the cluster's CTA `rank`.
+__device__ __forceinline__ uint32_t in_cta(uint32_t addr, uint32_t rank) {
+  uint32_t remote;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(addr), "r"(rank));
+  return remote;
+}
+
+__device__ __forceinline__ void tma_load_2d_pair(uint32_t dst, const CUtensorMap *map, uint32_t bar, int32_t x, int32_t y) {
+  asm volatile("cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+               ::"r"(dst), "l"(map), "r"(bar), "r"(x), "r"(y)
+               : "memory");
+}
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t bar) {
+  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void tmem_cp_sf_pair(uint32_t taddr, uint64_t desc) {
+  asm volatile("tcgen05.cp.cta_group::2.32x128b.warpx4 [%0], %1;" ::"r"(taddr), "l"(desc) : "memory");
+}
+__device__ __forceinline__ void mma_mxf4nvf4_pair(uint32_t d, uint64_t a, uint64_t b, uint32_t idesc, uint32_t sfa, uint32_t sfb,
+                                                  uint32_t accumulate) {
+  asm volatile("{ .reg .pred p; setp.ne.u32 p, %6, 0;\n"
+               "tcgen05.mma.cta_group::2.kind::mxf4nvf4.block_scale.scale_vec::4X [%0], %1, %2, %3, [%4], [%5], p; }"
+               ::"r"(d), "l"(a), "l"(b), "r"(idesc), "r"(sfa), "r"(sfb), "r"(accumulate)
+               : "memory");
+}
+// Arrives at `bar` (a shared::cluster address: this CTA's or the peer's) once the pair's MMAs so far have retired.
+__device__ __forceinline__ void mma_commit_pair(uint32_t bar) {
+  asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+
+__global__ void __launch_bounds__(192, 1) w4a4_gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a,
+                                                               const __grid_constant__ CUtensorMap map_b,
+                                                               const __grid_constant__ CUtensorMap map_sfa,
+                                                               const __grid_constant__ CUtensorMap map_sfb,
+                                                               const __grid_constant__ W4A4Params p) {
+  constexpr int kBN = 256;
+  constexpr int kStages = kPairStages;
+  constexpr uint32_t kTmemCols = 512;
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t raw = smem_u32(smem_raw);
+  const uint32_t base = (raw + 1023u) & ~1023u;   // the same offset in both CTAs: they run the same kernel
+  uint8_t *base_ptr = smem_raw + (base - raw);
+  // barriers: full[5], empty[5], accumulator full, accumulator empty; then the tensor-memory slot
+  const uint32_t bars = base + kStages * kPairStageBytes;
+  const uint32_t bar_acc_full = bars + 8 * 2 * kStages, bar_acc_empty = bar_acc_full + 8;
+  uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(base_ptr + kStages * kPairStageBytes + 128);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const uint32_t rank = cluster_ctarank();        // 0: the pair's first CTA, which issues the MMAs
+  const uint32_t k_iters = p.k / 256u, k_atoms = p.k / 64u;
+  const bool swiglu = (p.epilogue & kEpilogueSwiglu) != 0u;
+  const uint32_t m_tiles = (p.tokens + kBM - 1) / kBM, m_pairs = (m_tiles + 1u) / 2u;
+  const uint32_t n_tiles = swiglu ? p.n / 256u : (p.n + 255u) / 256u;
+  const uint32_t tiles = m_pairs * n_tiles;
+  const uint32_t first = blockIdx.x / 2u, step = gridDim.x / 2u;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < kStages; ++s) {
+      mbar_init(bars + 8 * s, 1);               // the first CTA's: its producer's expect_tx arrival (the bytes of both CTAs)
+      mbar_init(bars + 8 * (kStages + s), 1);   // one commit
+    }
+    mbar_init(bar_acc_full, 1);
+    mbar_init(bar_acc_empty, 8);                // the first CTA's: one arrival per epilogue warp of the pair
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 5) {
+    asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(kTmemCols) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  cluster_sync_all();   // the peer's barriers exist before anything is sent to them
+  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+  const uint32_t tmem = *tmem_slot;
+
+  griddep_launch_dependents();
+  griddep_wait();  // the quantized activations come from the previous kernel in the stream
+
+  if (warp == 4 && lane == 0) {
+    // ---- producer (both CTAs): own tokens, own half of the weight rows, the scales of both halves ----
+    uint32_t git = 0;
+    bool ok = true;
+    for (uint32_t tile = first; tile < tiles && ok; tile += step) {
+      const uint32_t m_tile = 2u * (tile % m_pairs) + rank, n_tile = tile / m_pairs;
+      const uint32_t row_a = swiglu ? n_tile * 128u : n_tile * kBN;
+      const uint32_t row_b = swiglu ? p.n / 2u + n_tile * 128u : n_tile * kBN + 128u;
+      for (uint32_t it = 0; it < k_iters; ++it, ++git) {
+        const uint32_t s = git % kStages;
+        if (!mbar_wait(bars + 8 * (kStages + s), ((git / kStages) & 1u) ^ 1u)) {
+          atomicOr(p.status, kStatusProducerTimeout);
+          ok = false;
+          break;
+        }
+        const uint32_t full = in_cta(bars + 8 * s, 0u);   // the first CTA's barrier collects both CTAs' bytes
+        const uint32_t stage = base + s * kPairStageBytes;
+        if (rank == 0u) mbar_expect_tx(bars + 8 * s, 2u * kPairStageBytes);
+        tma_load_2d_pair(stage, &map_a, full, static_cast<int32_t>(it * kBKBytes), static_cast<int32_t>(m_tile * kBM));
+        tma_load_2d_pair(stage + kABytes, &map_b, full, static_cast<int32_t>(it * kBKBytes), static_cast<int32_t>(rank == 0u ? row_a : row_b));
+        tma_load_2d_pair(stage + kABytes + kPairBBytes, &map_sfa, full, 0, static_cast<int32_t>(m_tile * k_atoms + it * 4u));
+        tma_load_2d_pair(stage + kABytes + kPairBBytes + kSfaBytes, &map_sfb, full, 0,
+                         static_cast<int32_t>((row_a / 128u) * k_atoms + it * 4u));
+        tma_load_2d_pair(stage + kABytes + kPairBBytes + kSfaBytes + 2048u, &map_sfb, full, 0,
+                         static_cast<int32_t>((row_b / 128u) * k_atoms + it * 4u));
+      }
+    }
+  } else if (warp == 5 && lane == 0 && rank == 0u) {
+    // ---- MMA issuer of the pair: M 256 (128 per CTA), N 256, K 64 ----
+    const uint32_t idesc = (1u << 7) | (1u << 10) | ((kBN >> 3) << 17) | ((256u >> 4) << 24);
+    uint32_t git = 0, tile_i = 0;
+    bool ok = true;
+    for (uint32_t tile = first; tile < tiles && ok; tile += step, ++tile_i) {
+      if (!mbar_wait(bar_acc_empty, (tile_i & 1u) ^ 1u)) {   // both CTAs have pulled the previous tile out of tensor memory
+        atomicOr(p.status, kStatusMmaTimeout);
+        break;
+      }
+      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+      for (uint32_t it = 0; it < k_iters; ++it, ++git) {
+        const uint32_t s = git % kStages;
+        if (!mbar_wait(bars + 8 * s, (git / kStages) & 1u)) {
+          atomicOr(p.status, kStatusMmaTimeout);
+          ok = false;
+          break;
+        }
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        const uint32_t stage = base + s * kPairStageBytes;
+        const uint32_t sf_cols = tmem + kBN + s * kPairSfCols;
+        const uint32_t sfa_smem = stage + kABytes + kPairBBytes, sfb_smem = sfa_smem + kSfaBytes;
+#pragma unroll
+        for (uint32_t kb = 0; kb < 4; ++kb) {
+          tmem_cp_sf_pair(sf_cols + kb * 4u, smem_desc(sfa_smem + kb * 512u, 128u, 0u));
+          tmem_cp_sf_pair(sf_cols + 16u + kb * 8u, smem_desc(sfb_smem + kb * 512u, 128u, 0u));
+          tmem_cp_sf_pair(sf_cols + 16u + kb * 8u + 4u, smem_desc(sfb_smem + 2048u + kb * 512u, 128u, 0u));
+        }
+        const uint64_t a_desc = smem_desc(stage, 1024u, 2u);
+        const uint64_t b_desc = smem_desc(stage + kABytes, 1024u, 2u);
+#pragma unroll
+        for (uint32_t kb = 0; kb < 4; ++kb) {
+          mma_mxf4nvf4_pair(tmem, a_desc + 2u * kb, b_desc + 2u * kb, idesc, sf_cols + kb * 4u, sf_cols + 16u + kb * 8u,
+                            (it | kb) != 0u ? 1u : 0u);
+        }
+        mma_commit_pair(in_cta(bars + 8 * (kStages + s), 0u));   // this CTA's stage ...
+        mma_commit_pair(in_cta(bars + 8 * (kStages + s), 1u));   // ... and the peer's
+      }
+      if (ok) {
+        mma_commit_pair(in_cta(bar_acc_full, 0u));
+        mma_commit_pair(in_cta(bar_acc_full, 1u));
+      }
+    }
+  } else if (warp < 4) {
+    // ---- epilogue (both CTAs): warp q owns this CTA's accumulator lanes (tokens) 32 q .. 32 q + 31 ----
+    const uint32_t lane_base = tmem + (static_cast<uint32_t>(warp * 32) << 16);
+    const uint32_t acc_empty_first = in_cta(bar_acc_empty, 0u);
+    uint32_t tile_i = 0;
+    for (uint32_t tile = first; tile < tiles; tile += step, ++tile_i) {
+      const uint32_t m_tile = 2u * (tile % m_pairs) + rank, n_tile = tile / m_pairs;
+      if (!mbar_wait(bar_acc_full, tile_i & 1u)) {
+        if (lane == 0) atomicOr(p.status, kStatusEpilogueTimeout);
+        break;
+      }
+      if (m_tile >= m_tiles) {   // the odd pair's second CTA: nothing of this tile is its to store
+        asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+        __syncwarp();
+        if (lane == 0) mbar_arrive_cluster(acc_empty_first);
+        continue;
+      }
+      w4a4_epilogue_tile(p, lane_base, warp, lane, m_tile, n_tile, swiglu, [&] {
+        if (lane == 0) mbar_arrive_cluster(acc_empty_first);
+      });
+    }
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  cluster_sync_all();   // neither CTA leaves while the other may still reach its shared memory or barriers
+  if (warp == 5) {
+    asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(kTmemCols) : "memory");
   }
 }
 
@@ -550,6 +757,19 @@ bool make_code_map(CUtensorMap *map, const void *codes, uint64_t rows, uint64_t 
   const cuuint32_t elem[2] = {1, 1};
   return fn(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void *>(codes), dims, strides, box, elem,
             CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+// A scale plane of 512-byte tiles as a 2-D tensor [tiles][128 words] with boxes of four tiles (one K stage).
+bool make_scale_map(CUtensorMap *map, const void *scales, uint64_t tiles) {
+  EncodeTiledFn fn = encode_tiled_fn();
+  if (fn == nullptr) return false;
+  const cuuint64_t dims[2] = {128, tiles};
+  const cuuint64_t strides[1] = {512};
+  const cuuint32_t box[2] = {128, 4};
+  const cuuint32_t elem[2] = {1, 1};
+  return fn(map, CU_TENSOR_MAP_DATA_TYPE_UINT32, 2, const_cast<void *>(scales), dims, strides, box, elem,
+            CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
@@ -575,6 +795,9 @@ int32_t w4a4_prepare(ErrorSlot &slot) {
   if (err == cudaSuccess) {
     err = cudaFuncSetAttribute(w4a4_gemm_persistent_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                static_cast<int>(Tile<256>::kSmemBytes));
+  }
+  if (err == cudaSuccess) {
+    err = cudaFuncSetAttribute(w4a4_gemm_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(kPairSmemBytes));
   }
   if (err != cudaSuccess) return fail(slot, "nvfp4 prefill kernel attributes: %s", cudaGetErrorString(err));
   if (encode_tiled_fn() == nullptr) return fail(slot, "cuTensorMapEncodeTiled is not available from this driver");
@@ -622,6 +845,34 @@ int32_t w4a4_product(ErrorSlot &slot, const DeviceState &dev, const uint8_t *w_c
   const bool swiglu = (epilogue & kEpilogueSwiglu) != 0u;
   // the fused SwiGLU needs the wide tile (gate and up boxes side by side); the plain product takes
   // the narrow one, two CTAs per SM
+  if (dev.w4a4_pair != 0) {
+    // CTA pairs on 256-token x 256-row tiles
+    CUtensorMap map_sfa, map_sfb;
+    if (!make_scale_map(&map_sfa, a_scales, static_cast<uint64_t>(pad / kBM) * (k / 64u)) ||
+        !make_scale_map(&map_sfb, w_scales, static_cast<uint64_t>(n / 128u) * (k / 64u))) {
+      return fail(slot, "nvfp4 prefill: tensor map encoding failed");
+    }
+    const uint32_t m_pairs = (pad / kBM + 1u) / 2u;
+    const uint32_t tiles = m_pairs * (swiglu ? n / 256u : (n + 255u) / 256u);
+    const uint32_t pairs_max = static_cast<uint32_t>(dev.sm_count) / 2u;
+    cudaLaunchConfig_t config = {};
+    config.gridDim = dim3(2u * (tiles < pairs_max ? tiles : pairs_max), 1, 1);
+    config.blockDim = dim3(192, 1, 1);
+    config.dynamicSmemBytes = kPairSmemBytes;
+    config.stream = stream;
+    cudaLaunchAttribute attr[2];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 2;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[1].val.programmaticStreamSerializationAllowed = 1;
+    config.attrs = attr;
+    config.numAttrs = dev.pdl ? 2 : 1;
+    const cudaError_t perr = cudaLaunchKernelEx(&config, w4a4_gemm_pair_kernel, map_a, map_b, map_sfa, map_sfb, p);
+    if (perr != cudaSuccess) return fail(slot, "nvfp4 prefill launch: %s", cudaGetErrorString(perr));
+    return 0;
+  }
   if (dev.w4a4_persistent != 0 || (epilogue & (kEpilogueAdd | kEpilogueQuant)) != 0u) {  // those two epilogues exist only here
     const uint32_t tiles = (pad / kBM) * (swiglu ? n / 256u : (n + 255u) / 256u);
     const uint32_t ctas = tiles < static_cast<uint32_t>(dev.sm_count) ? tiles : static_cast<uint32_t>(dev.sm_count);
