@@ -415,7 +415,7 @@ __device__ __forceinline__ void w4a4_epilogue_tile(const W4A4Params &p, uint32_t
   }
 }
 
-__global__ void __launch_bounds__(192, 1) w4a4_gemm_persistent_kernel(const __grid_constant__ CUtensorMap map_a,
+__global__ void __launch_bounds__(256, 1) w4a4_gemm_persistent_kernel(const __grid_constant__ CUtensorMap map_a,
                                                                      const __grid_constant__ CUtensorMap map_b,
                                                                      const __grid_constant__ W4A4Params p) {
   constexpr int kBN = 256;
@@ -429,6 +429,7 @@ __global__ void __launch_bounds__(192, 1) w4a4_gemm_persistent_kernel(const __gr
   // barriers: full[4], empty[4], accumulator full, accumulator empty; then the tensor-memory slot
   const uint32_t bars = base + kStages * kStageBytes;
   const uint32_t bar_acc_full = bars + 8 * 2 * kStages, bar_acc_empty = bar_acc_full + 8;
+  const uint32_t bar_sf_ready = bar_acc_empty + 8;   // [4]: a stage's scales are in tensor memory
   uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(base_ptr + kStages * kStageBytes + 128);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const uint32_t k_iters = p.k / 256u, k_atoms = p.k / 64u;
@@ -444,6 +445,7 @@ __global__ void __launch_bounds__(192, 1) w4a4_gemm_persistent_kernel(const __gr
     }
     mbar_init(bar_acc_full, 1);
     mbar_init(bar_acc_empty, 4);  // one arrival per epilogue warp
+    for (int s = 0; s < kStages; ++s) mbar_init(bar_sf_ready + 8 * s, 2);  // the two scale copiers' commits
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   if (warp == 5) {
@@ -492,9 +494,9 @@ __global__ void __launch_bounds__(192, 1) w4a4_gemm_persistent_kernel(const __gr
     }
   } else if (warp == 5 && lane == 0) {
     // ---- MMA issuer ----
-    // The scale copies run in the same in-order pipe as the MMAs and take about a quarter of its
-    // time (12 copies of 512 bytes a stage against 4 MMAs). Issuing a stage's copies one stage ahead
-    // of its MMAs was measured slower, not faster: the copies cost pipe time, not latency.
+    // The scale copies of a stage (twelve of 512 bytes) cost this thread more issue time than its four
+    // MMAs when it issues both (880 cycles a stage, measured with clock64), so they come from the
+    // two copier warps below and this thread only waits for their commits.
     const uint32_t idesc = (1u << 7) | (1u << 10) | ((kBN >> 3) << 17) | ((kBM >> 4) << 24);
     uint32_t git = 0, tile_i = 0;
     bool ok = true;
@@ -507,7 +509,7 @@ __global__ void __launch_bounds__(192, 1) w4a4_gemm_persistent_kernel(const __gr
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
       for (uint32_t it = 0; it < k_iters; ++it, ++git) {
         const uint32_t s = git % kStages;
-        if (!mbar_wait(bars + 8 * s, (git / kStages) & 1u)) {
+        if (!mbar_wait(bar_sf_ready + 8 * s, (git / kStages) & 1u)) {   // operands landed and scales copied
           atomicOr(p.status, kStatusMmaTimeout);
           ok = false;
           break;
@@ -515,13 +517,6 @@ __global__ void __launch_bounds__(192, 1) w4a4_gemm_persistent_kernel(const __gr
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         const uint32_t stage = base + s * kStageBytes;
         const uint32_t sf_cols = tmem + kBN + s * kSfColsPerStage;
-        const uint32_t sfa_smem = stage + kABytes + kBBytes, sfb_smem = sfa_smem + kSfaBytes;
-#pragma unroll
-        for (uint32_t kb = 0; kb < 4; ++kb) {
-          tmem_cp_sf(sf_cols + kb * 4u, smem_desc(sfa_smem + kb * 512u, 128u, 0u));
-          tmem_cp_sf(sf_cols + 16u + kb * 8u, smem_desc(sfb_smem + kb * 512u, 128u, 0u));
-          tmem_cp_sf(sf_cols + 16u + kb * 8u + 4u, smem_desc(sfb_smem + 2048u + kb * 512u, 128u, 0u));
-        }
         const uint64_t a_desc = smem_desc(stage, 1024u, 2u);
         const uint64_t b_desc = smem_desc(stage + kABytes, 1024u, 2u);
 #pragma unroll
@@ -532,6 +527,30 @@ __global__ void __launch_bounds__(192, 1) w4a4_gemm_persistent_kernel(const __gr
         mma_commit(bars + 8 * (kStages + s));
       }
       if (ok) mma_commit(bar_acc_full);
+    }
+  } else if (warp >= 6 && lane == 0) {
+    // ---- scale copiers: a stage's scale tiles go to tensor memory from threads of their own,
+    //      warp 6 the first two K-atoms, warp 7 the other two ----
+    const uint32_t kb0 = static_cast<uint32_t>(warp - 6) * 2u;
+    const uint32_t my_tiles = tiles > blockIdx.x ? (tiles - blockIdx.x + gridDim.x - 1u) / gridDim.x : 0u;
+    const uint32_t total = my_tiles * k_iters;
+    for (uint32_t g = 0; g < total; ++g) {
+      const uint32_t s = g % kStages;
+      if (!mbar_wait(bars + 8 * s, (g / kStages) & 1u)) {
+        atomicOr(p.status, kStatusMmaTimeout);
+        break;
+      }
+      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+      const uint32_t stage = base + s * kStageBytes;
+      const uint32_t sf_cols = tmem + kBN + s * kSfColsPerStage;
+      const uint32_t sfa_smem = stage + kABytes + kBBytes, sfb_smem = sfa_smem + kSfaBytes;
+#pragma unroll
+      for (uint32_t kb = kb0; kb < kb0 + 2u; ++kb) {
+        tmem_cp_sf(sf_cols + kb * 4u, smem_desc(sfa_smem + kb * 512u, 128u, 0u));
+        tmem_cp_sf(sf_cols + 16u + kb * 8u, smem_desc(sfb_smem + kb * 512u, 128u, 0u));
+        tmem_cp_sf(sf_cols + 16u + kb * 8u + 4u, smem_desc(sfb_smem + 2048u + kb * 512u, 128u, 0u));
+      }
+      mma_commit(bar_sf_ready + 8 * s);
     }
   } else if (warp < 4) {
     // ---- epilogue: warp q owns accumulator lanes (tokens) 32 q .. 32 q + 31 ----
@@ -599,7 +618,7 @@ __device__ __forceinline__ void mma_commit_pair(uint32_t bar) {
   asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
 }
 
-__global__ void __launch_bounds__(192, 1) w4a4_gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a,
+__global__ void __launch_bounds__(256, 1) w4a4_gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a,
                                                                const __grid_constant__ CUtensorMap map_b,
                                                                const __grid_constant__ CUtensorMap map_sfa,
                                                                const __grid_constant__ CUtensorMap map_sfb,
@@ -614,6 +633,7 @@ __global__ void __launch_bounds__(192, 1) w4a4_gemm_pair_kernel(const __grid_con
   // barriers: full[5], empty[5], accumulator full, accumulator empty; then the tensor-memory slot
   const uint32_t bars = base + kStages * kPairStageBytes;
   const uint32_t bar_acc_full = bars + 8 * 2 * kStages, bar_acc_empty = bar_acc_full + 8;
+  const uint32_t bar_sf_ready = bar_acc_empty + 8;   // [5], the first CTA's: a stage's scales are in both CTAs' tensor memory
   uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(base_ptr + kStages * kPairStageBytes + 128);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const uint32_t rank = cluster_ctarank();        // 0: the pair's first CTA, which issues the MMAs
@@ -631,6 +651,7 @@ __global__ void __launch_bounds__(192, 1) w4a4_gemm_pair_kernel(const __grid_con
     }
     mbar_init(bar_acc_full, 1);
     mbar_init(bar_acc_empty, 8);                // the first CTA's: one arrival per epilogue warp of the pair
+    for (int s = 0; s < kStages; ++s) mbar_init(bar_sf_ready + 8 * s, 2);   // the two scale copiers' commits
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   if (warp == 5) {
@@ -686,7 +707,7 @@ __global__ void __launch_bounds__(192, 1) w4a4_gemm_pair_kernel(const __grid_con
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
       for (uint32_t it = 0; it < k_iters; ++it, ++git) {
         const uint32_t s = git % kStages;
-        if (!mbar_wait(bars + 8 * s, (git / kStages) & 1u)) {
+        if (!mbar_wait(bar_sf_ready + 8 * s, (git / kStages) & 1u)) {   // operands landed in both CTAs and scales copied
           atomicOr(p.status, kStatusMmaTimeout);
           ok = false;
           break;
@@ -694,13 +715,6 @@ __global__ void __launch_bounds__(192, 1) w4a4_gemm_pair_kernel(const __grid_con
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         const uint32_t stage = base + s * kPairStageBytes;
         const uint32_t sf_cols = tmem + kBN + s * kPairSfCols;
-        const uint32_t sfa_smem = stage + kABytes + kPairBBytes, sfb_smem = sfa_smem + kSfaBytes;
-#pragma unroll
-        for (uint32_t kb = 0; kb < 4; ++kb) {
-          tmem_cp_sf_pair(sf_cols + kb * 4u, smem_desc(sfa_smem + kb * 512u, 128u, 0u));
-          tmem_cp_sf_pair(sf_cols + 16u + kb * 8u, smem_desc(sfb_smem + kb * 512u, 128u, 0u));
-          tmem_cp_sf_pair(sf_cols + 16u + kb * 8u + 4u, smem_desc(sfb_smem + 2048u + kb * 512u, 128u, 0u));
-        }
         const uint64_t a_desc = smem_desc(stage, 1024u, 2u);
         const uint64_t b_desc = smem_desc(stage + kABytes, 1024u, 2u);
 #pragma unroll
@@ -715,6 +729,30 @@ __global__ void __launch_bounds__(192, 1) w4a4_gemm_pair_kernel(const __grid_con
         mma_commit_pair(in_cta(bar_acc_full, 0u));
         mma_commit_pair(in_cta(bar_acc_full, 1u));
       }
+    }
+  } else if (warp >= 6 && lane == 0 && rank == 0u) {
+    // ---- scale copiers of the pair (one copy instruction serves both CTAs): warp 6 the first two
+    //      K-atoms of a stage, warp 7 the other two ----
+    const uint32_t kb0 = static_cast<uint32_t>(warp - 6) * 2u;
+    const uint32_t my_tiles = tiles > first ? (tiles - first + step - 1u) / step : 0u;
+    const uint32_t total = my_tiles * k_iters;
+    for (uint32_t g = 0; g < total; ++g) {
+      const uint32_t s = g % kStages;
+      if (!mbar_wait(bars + 8 * s, (g / kStages) & 1u)) {
+        atomicOr(p.status, kStatusMmaTimeout);
+        break;
+      }
+      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+      const uint32_t stage = base + s * kPairStageBytes;
+      const uint32_t sf_cols = tmem + kBN + s * kPairSfCols;
+      const uint32_t sfa_smem = stage + kABytes + kPairBBytes, sfb_smem = sfa_smem + kSfaBytes;
+#pragma unroll
+      for (uint32_t kb = kb0; kb < kb0 + 2u; ++kb) {
+        tmem_cp_sf_pair(sf_cols + kb * 4u, smem_desc(sfa_smem + kb * 512u, 128u, 0u));
+        tmem_cp_sf_pair(sf_cols + 16u + kb * 8u, smem_desc(sfb_smem + kb * 512u, 128u, 0u));
+        tmem_cp_sf_pair(sf_cols + 16u + kb * 8u + 4u, smem_desc(sfb_smem + 2048u + kb * 512u, 128u, 0u));
+      }
+      mma_commit_pair(in_cta(bar_sf_ready + 8 * s, 0u));
     }
   } else if (warp < 4) {
     // ---- epilogue (both CTAs): warp q owns this CTA's accumulator lanes (tokens) 32 q .. 32 q + 31 ----
@@ -857,7 +895,7 @@ int32_t w4a4_product(ErrorSlot &slot, const DeviceState &dev, const uint8_t *w_c
     const uint32_t pairs_max = static_cast<uint32_t>(dev.sm_count) / 2u;
     cudaLaunchConfig_t config = {};
     config.gridDim = dim3(2u * (tiles < pairs_max ? tiles : pairs_max), 1, 1);
-    config.blockDim = dim3(192, 1, 1);
+    config.blockDim = dim3(256, 1, 1);
     config.dynamicSmemBytes = kPairSmemBytes;
     config.stream = stream;
     cudaLaunchAttribute attr[2];
@@ -876,7 +914,7 @@ int32_t w4a4_product(ErrorSlot &slot, const DeviceState &dev, const uint8_t *w_c
   if (dev.w4a4_persistent != 0 || (epilogue & (kEpilogueAdd | kEpilogueQuant)) != 0u) {  // those two epilogues exist only here
     const uint32_t tiles = (pad / kBM) * (swiglu ? n / 256u : (n + 255u) / 256u);
     const uint32_t ctas = tiles < static_cast<uint32_t>(dev.sm_count) ? tiles : static_cast<uint32_t>(dev.sm_count);
-    const cudaError_t perr = launch(w4a4_gemm_persistent_kernel, dim3(ctas), dim3(192), Tile<256>::kSmemBytes, stream, dev.pdl != 0,
+    const cudaError_t perr = launch(w4a4_gemm_persistent_kernel, dim3(ctas), dim3(256), Tile<256>::kSmemBytes, stream, dev.pdl != 0,
                                     map_a, map_b, p);
     if (perr != cudaSuccess) return fail(slot, "nvfp4 prefill launch: %s", cudaGetErrorString(perr));
     return 0;
