@@ -551,7 +551,7 @@ def run_side_workload(args) -> None:
         peak = 4.0 * 1403.2
         roof = {"bound": "tensor", "achieved": value, "peak": peak, "unit": "TFLOP/s", "frac": value / peak,
                 "peak_source": "4 x the measured sustained BF16 cuBLAS rate (FP4 dense is 4 x BF16 dense on this part)",
-                "frac_of_nominal_9000": value / 9000.0, "kernel": "w4a4_gemm_kernel", "traffic": None,
+                "frac_of_nominal_9000": value / 9000.0, "kernel": "w4a4_gemm_pair_kernel", "traffic": None,
                 "device_status": status}
     else:
         roof = {"bound": "hbm", "achieved": value, "peak": peak_hbm, "unit": "GB/s", "frac": value / peak_hbm,
