@@ -9,12 +9,18 @@
 //     scales, bit for bit the reference's rule (nvfp4_codec.cuh:81-110), the scales written in the
 //     same 512-byte (128 rows x 4 groups) tiles the weight plane uses - which is the scale-factor
 //     atom the block-scaled MMA reads, so neither operand's scales are ever reshuffled.
-//  2. `w4a4_gemm_kernel`: one CTA per 128-token x 256-row output tile. A producer thread streams
-//     K in stages of 256 (TMA 2-D tiles of codes with the 128-byte swizzle, plain bulk copies of
-//     the scale tiles) into a 4-deep mbarrier ring; one thread copies each stage's scale atoms to
-//     tensor memory (tcgen05.cp) and issues tcgen05.mma kind::mxf4nvf4 block_scale scale_vec::4X
-//     (M 128, N 256, K 64) with the fp32 accumulator in tensor memory; four warps read the
-//     accumulator back (tcgen05.ld), apply alpha and store BF16.
+//  2. The product, in three forms that share the stage layout and the epilogue:
+//     `w4a4_gemm_kernel` - one CTA per 128-token x 256-row (or 128-row) output tile: a producer
+//     thread streams K in stages of 256 (TMA 2-D tiles of codes with the 128-byte swizzle, bulk
+//     copies of the scale tiles) into an mbarrier ring; one thread copies each stage's scale atoms
+//     to tensor memory (tcgen05.cp) and issues tcgen05.mma kind::mxf4nvf4 block_scale
+//     scale_vec::4X (M 128, N 256, K 64) with the fp32 accumulator in tensor memory; four warps
+//     read the accumulator back (tcgen05.ld), apply alpha and store BF16.
+//     `w4a4_gemm_persistent_kernel` - one CTA per SM walking such tiles, the ring running across
+//     tile boundaries, the stores under the next tile's MMAs, the scale copies issued by two
+//     threads of their own.
+//     `w4a4_gemm_pair_kernel` (the default) - the persistent form on clusters of two CTAs sharing
+//     256 x 256 tiles (cta_group::2): fewer operand bytes per FLOP.
 //
 // Every wait on an mbarrier is bounded: after the limit the thread records a status bit in the
 // workspace, stops issuing and the CTA tears down (tensor memory freed) instead of hanging.
