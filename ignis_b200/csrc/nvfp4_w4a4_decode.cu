@@ -15,8 +15,9 @@
 //    call needs no workspace, no second launch and no pass over global memory. Every CTA repeats
 //    this for its K slice from the L2. The warps work in groups of four that take the stages in
 //    turn, so a group has several stage times for its stage.
-//  * The last warp owns tensor memory: per stage it copies both operands' scale tiles there (tcgen05.cp)
-//    and issues four tcgen05.mma kind::mxf4nvf4 block_scale scale_vec::4X (M 128, N, K 64).
+//  * The producer thread also copies a stage's scale tiles of both operands to tensor memory
+//    (tcgen05.cp) once everything of the stage is in place; the last warp owns tensor memory and
+//    issues four tcgen05.mma kind::mxf4nvf4 block_scale scale_vec::4X (M 128, N, K 64) per stage.
 //  * The fused SwiGLU (a gate|up parent) pairs a tile's 128 gate rows with their up rows: per K
 //    stage two ring entries, each with its own weight tile, sharing the first one's token tile,
 //    into two accumulators; the epilogue writes BF16(silu(BF16(g alpha)) * BF16(u alpha)).
@@ -98,8 +99,9 @@ __global__ void __launch_bounds__(64 + 128 * kMaxQuantGroups, 2) w4a4_decode_ker
   // a stage: weight codes | token codes | weight scale tiles | token scale tiles
   const uint32_t b_bytes = p.bn * 128u;
   const uint32_t stage_bytes = kABytes + b_bytes + 2u * kSfBytes;
-  const uint32_t bars = base + p.stages * stage_bytes;  // full[stages], empty[stages], accumulator full; then the TMEM slot
-  uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(base_ptr + p.stages * stage_bytes + 8u * (2u * p.stages + 1u) + 8u);
+  const uint32_t bars = base + p.stages * stage_bytes;  // full[stages], empty[stages], accumulator full, scales ready[stages]; then the TMEM slot
+  const uint32_t bar_sf_ready = bars + 8u * (2u * p.stages + 1u);
+  uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(base_ptr + p.stages * stage_bytes + 8u * (3u * p.stages + 1u) + 8u);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int producer_warp = 4 * static_cast<int>(p.groups), mma_warp = producer_warp + 1;
   const uint32_t rank = cluster_ctarank(), kc = p.kc;
@@ -125,21 +127,16 @@ __global__ void __launch_bounds__(64 + 128 * kMaxQuantGroups, 2) w4a4_decode_ker
   // One ring entry: a weight tile of K stage s0 + it / halves (entry 2 j is the first tile, 2 j + 1
   // the second when the CTA has two) and its scale tiles.
   const uint32_t entries = (s1 - s0) * halves;
-  auto produce = [&](uint32_t it, uint64_t policy) -> bool {
+  auto produce = [&](uint32_t it, uint64_t policy) {
     const uint32_t s = s0 + it / halves;
     const uint32_t row0 = (it % halves) != 0u ? row_b : row_a;
     const uint32_t slot = it % p.stages;
-    if (!mbar_wait(bars + 8 * (p.stages + slot), ((it / p.stages) & 1u) ^ 1u)) {
-      atomicOr(&g_a4_status, kProducerTimeout);
-      return false;
-    }
     const uint32_t full = bars + 8 * slot;
     const uint32_t stage = base + slot * stage_bytes;
     mbar_expect_tx(full, kABytes + kSfBytes);
     tma_load_2d_hint(stage, &maps.m[wi], full, static_cast<int32_t>(s * 128u), static_cast<int32_t>(row0), policy);
     bulk_load_hint(stage + kABytes + b_bytes, W.scales + (static_cast<size_t>(row0 / 128u) * k_atoms + s * 4u) * 512u, kSfBytes, full,
                    policy);
-    return true;
   };
   // (Requesting the first ring of weight tiles from here, before tensor memory is allocated, was
   // measured slower: the early loads take bandwidth from the previous kernel's last CTAs, which
@@ -150,6 +147,7 @@ __global__ void __launch_bounds__(64 + 128 * kMaxQuantGroups, 2) w4a4_decode_ker
       mbar_init(bars + 8 * (p.stages + s), 1);   // the MMA thread's commit
     }
     mbar_init(bars + 8 * 2 * p.stages, 1);
+    for (uint32_t s = 0; s < p.stages; ++s) mbar_init(bar_sf_ready + 8 * s, 1);   // the copies' commit
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   if (warp == mma_warp) {
@@ -250,9 +248,40 @@ __global__ void __launch_bounds__(64 + 128 * kMaxQuantGroups, 2) w4a4_decode_ker
     // ---- producer of the weight tiles: they never depend on the previous kernel ----
     griddep_launch_dependents();
     if (lane == 0) {
+      // Two jobs, whichever is ready: a free ring entry gets its loads requested; an entry whose
+      // operands are all in place (weights landed, tokens quantized) gets its scale tiles copied to
+      // tensor memory, so that the MMA thread issues MMAs only (issuing a copy costs its thread
+      // about as much as issuing an MMA, and there are twice as many).
       const uint64_t policy = l2_evict_first_policy();
-      for (uint32_t it = 0; it < entries; ++it) {
-        if (!produce(it, policy)) break;
+      uint32_t loaded = 0, copied = 0, idle = 0;
+      while (copied < entries) {
+        bool did = false;
+        if (loaded < entries && mbar_test(bars + 8 * (p.stages + loaded % p.stages), ((loaded / p.stages) & 1u) ^ 1u)) {
+          produce(loaded, policy);
+          ++loaded;
+          did = true;
+        }
+        if (copied < loaded && mbar_test(bars + 8 * (copied % p.stages), (copied / p.stages) & 1u)) {
+          asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+          const uint32_t half = copied % halves, slot = copied % p.stages;
+          const uint32_t stage = base + slot * stage_bytes;
+          const uint32_t sf_cols = tmem + 64u + slot * 32u;  // 16 columns of weight scales, 16 of token scales
+          const uint32_t sfa_smem = stage + kABytes + b_bytes, sfb_smem = sfa_smem + kSfBytes;
+#pragma unroll
+          for (uint32_t kb = 0; kb < 4; ++kb) {
+            tmem_cp_sf(sf_cols + kb * 4u, smem_desc(sfa_smem + kb * 512u, 128u, 0u));
+            if (half == 0u) tmem_cp_sf(sf_cols + 16u + kb * 4u, smem_desc(sfb_smem + kb * 512u, 128u, 0u));
+          }
+          mma_commit(bar_sf_ready + 8 * slot);
+          ++copied;
+          did = true;
+        }
+        if (did) {
+          idle = 0;
+        } else if (++idle > kSpinLimit) {
+          atomicOr(&g_a4_status, kProducerTimeout);
+          break;
+        }
       }
     }
   } else {
@@ -266,7 +295,7 @@ __global__ void __launch_bounds__(64 + 128 * kMaxQuantGroups, 2) w4a4_decode_ker
       for (uint32_t it = 0; it < entries; ++it) {
         const uint32_t half = it % halves;
         const uint32_t slot = it % p.stages;
-        if (!mbar_wait(bars + 8 * slot, (it / p.stages) & 1u)) {
+        if (!mbar_wait(bar_sf_ready + 8 * slot, (it / p.stages) & 1u)) {   // operands in place and scales copied
           atomicOr(&g_a4_status, kMmaTimeout);
           ok = false;
           break;
@@ -277,12 +306,6 @@ __global__ void __launch_bounds__(64 + 128 * kMaxQuantGroups, 2) w4a4_decode_ker
         const uint32_t stage = base + slot * stage_bytes, b_stage = base + b_slot * stage_bytes;
         const uint32_t sf_cols = tmem + 64u + slot * 32u;  // 16 columns of weight scales, 16 of token scales
         const uint32_t sfb_cols = tmem + 64u + b_slot * 32u + 16u;
-        const uint32_t sfa_smem = stage + kABytes + b_bytes, sfb_smem = sfa_smem + kSfBytes;
-#pragma unroll
-        for (uint32_t kb = 0; kb < 4; ++kb) {
-          tmem_cp_sf(sf_cols + kb * 4u, smem_desc(sfa_smem + kb * 512u, 128u, 0u));
-          if (half == 0u) tmem_cp_sf(sfb_cols + kb * 4u, smem_desc(sfb_smem + kb * 512u, 128u, 0u));
-        }
         const uint64_t a_desc = smem_desc(stage, 1024u, 2u);
         const uint64_t b_desc = smem_desc(b_stage + kABytes, 1024u, 2u);
 #pragma unroll
@@ -407,7 +430,7 @@ uint32_t a4_ring_depth(uint32_t ctas_per_sm, uint32_t bn, uint32_t k_stages) {
 }
 
 size_t a4_smem_bytes(uint32_t bn, uint32_t stages) {
-  return static_cast<size_t>(stages) * (kABytes + bn * 128u + 2u * kSfBytes) + 8u * (2u * stages + 1u) + 16u + 1024u;
+  return static_cast<size_t>(stages) * (kABytes + bn * 128u + 2u * kSfBytes) + 8u * (3u * stages + 1u) + 16u + 1024u;
 }
 
 }  // namespace
