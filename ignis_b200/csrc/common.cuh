@@ -48,6 +48,7 @@ struct DeviceState {
   int a4_decode_kc = 0;      // B200Q_A4_DECODE_KC: cluster size of that kernel (0: planned)
   int a4_decode_groups = 0;  // B200Q_A4_DECODE_GROUPS: quantizer groups per CTA of that kernel (0: chosen by the token count)
   int a4_decode_ctas = 2;  // B200Q_A4_DECODE_CTAS: CTAs of that kernel per SM (1: one CTA with a ring twice as deep)
+  int a16_mma_wide = 1;  // B200Q_A16_MMA_WIDE: beyond 256 tokens the A16 tensor-core kernel takes token tiles of 512 (two accumulators per decoded stage)
   int w4a4_pair = 1;     // B200Q_W4A4_PAIR: the prefill GEMM on CTA pairs (cta_group::2, 256 x 256 tiles); 0: one CTA per tile
   int w4a4_bn = 128;     // B200Q_W4A4_BN: weight rows per tile of the plain W4A4 product (128 or 256)
   int gemv_xu = 8;       // B200Q_GEMV_XU: words per row of 8 decoded by the hardware E2M1 conversion

@@ -51,7 +51,7 @@ struct A16Params {
   A16Weight w[kMaxGroup];
   uint32_t count;
   uint32_t k, tokens;   // all tokens of the call; token tile blockIdx.y covers [bn y, bn y + bn)
-  uint32_t bn;          // token tile: 32, 64, 128 or 256
+  uint32_t bn;          // token tile: 32, 64, 128, 256, or 512 as two MMA tiles of 256 with an accumulator each
   uint32_t stages;      // ring depth in shared memory
   uint32_t kc;          // cluster size: K slices
   uint32_t epilogue;    // STORE / ADD / OUT_F32
@@ -95,6 +95,7 @@ __global__ void __launch_bounds__(192) nvfp4_a16_mma_kernel(const __grid_constan
   const uint32_t s0 = static_cast<uint32_t>(static_cast<uint64_t>(k_stages) * rank / kc);
   const uint32_t s1 = static_cast<uint32_t>(static_cast<uint64_t>(k_stages) * (rank + 1) / kc);
   const uint32_t tmem_cols = p.bn < 32u ? 32u : p.bn;
+  const uint32_t mma_n = p.bn > 256u ? 256u : p.bn;   // tokens per MMA
   const uint32_t tok0 = by * p.bn;   // first token of this CTA's tile
 
   if (threadIdx.x == 0) {
@@ -196,6 +197,10 @@ __global__ void __launch_bounds__(192) nvfp4_a16_mma_kernel(const __grid_constan
         const uint32_t full = bars + 8 * slot;
         mbar_expect_tx(full, b_bytes);
         tma_load_2d(base + slot * stage_bytes + kABytes, &map_x, full, static_cast<int32_t>(s * 64u), static_cast<int32_t>(tok0));
+        if (p.bn > 256u) {   // the second MMA tile's tokens
+          tma_load_2d(base + slot * stage_bytes + kABytes + 256u * 128u, &map_x, full, static_cast<int32_t>(s * 64u),
+                      static_cast<int32_t>(tok0 + 256u));
+        }
       }
     }
   } else {
@@ -205,7 +210,7 @@ __global__ void __launch_bounds__(192) nvfp4_a16_mma_kernel(const __grid_constan
     if (lane == 0) {
       // instruction descriptor: FP32 accumulator (bit 4), A and B BF16 (format 1 at bits 7 and
       // 10), both K-major, N >> 3 at bit 17, M >> 4 at bit 24
-      const uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((p.bn >> 3) << 17) | ((static_cast<uint32_t>(kBM) >> 4) << 24);
+      const uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((mma_n >> 3) << 17) | ((static_cast<uint32_t>(kBM) >> 4) << 24);
       bool ok = true;
       for (uint32_t s = s0, it = 0; s < s1; ++s, ++it) {
         const uint32_t slot = it % p.stages;
@@ -220,6 +225,9 @@ __global__ void __launch_bounds__(192) nvfp4_a16_mma_kernel(const __grid_constan
 #pragma unroll
         for (uint32_t kb = 0; kb < 4; ++kb) {   // 16 values along K are 32 bytes: two 16-byte units further
           mma_f16(tmem, a_desc + 2u * kb, b_desc + 2u * kb, idesc, (it | kb) != 0u ? 1u : 0u);
+          if (p.bn > 256u) {   // the same decoded weights against the second 256 tokens, into their own accumulator
+            mma_f16(tmem + 256u, a_desc + 2u * kb, b_desc + (256u * 128u >> 4) + 2u * kb, idesc, (it | kb) != 0u ? 1u : 0u);
+          }
         }
         mma_commit(bars + 8 * (p.stages + slot));
       }
@@ -327,7 +335,7 @@ int32_t a16mma_launch(ErrorSlot &slot, const DeviceState &dev, const GemvWeight 
   p.count = count;
   p.k = k;
   p.tokens = tokens;
-  p.bn = tokens <= 32u ? 32u : (tokens <= 64u ? 64u : (tokens <= 128u ? 128u : 256u));
+  p.bn = tokens <= 32u ? 32u : (tokens <= 64u ? 64u : (tokens <= 128u ? 128u : (tokens <= 256u || dev.a16_mma_wide == 0 ? 256u : 512u)));
   p.epilogue = epilogue;
   // ring depth: as many stages as fit beside the other CTAs this token tile leaves room for
   const uint32_t stage_bytes = kABytes + p.bn * 128u;
@@ -365,7 +373,7 @@ int32_t a16mma_launch(ErrorSlot &slot, const DeviceState &dev, const GemvWeight 
   {
     const cuuint64_t dims[2] = {k, tokens};
     const cuuint64_t strides[1] = {static_cast<cuuint64_t>(k) * 2u};
-    const cuuint32_t box[2] = {64u, p.bn};
+    const cuuint32_t box[2] = {64u, p.bn > 256u ? 256u : p.bn};
     const cuuint32_t elem[2] = {1, 1};
     if (encode == nullptr ||
         encode(&map_x, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<uint16_t *>(x), dims, strides, box, elem,

@@ -79,6 +79,7 @@ int32_t prepare_device(ErrorSlot &slot) {
   fresh.a4_decode_kc = env_int("B200Q_A4_DECODE_KC", 0);
   fresh.a4_decode_groups = env_int("B200Q_A4_DECODE_GROUPS", 0);
   fresh.a4_decode_ctas = env_int("B200Q_A4_DECODE_CTAS", 2) == 1 ? 1 : 2;
+  fresh.a16_mma_wide = env_int("B200Q_A16_MMA_WIDE", 1);
   fresh.w4a4_pair = env_int("B200Q_W4A4_PAIR", 1);
   fresh.w4a4_bn = env_int("B200Q_W4A4_BN", 128) == 256 ? 256 : 128;
   fresh.sm_cap = env_int("IGNIS_TRELLIS_SM_CAP", 0);
