@@ -535,3 +535,43 @@ def test_w4a4_tensor_core_route(nv, oracle, tokens, n, k):
     # the route needs its workspace
     with pytest.raises(nv.Nvfp4Error):
         nv.linear(x.cuda(), w, policy=nv.ALLOW_A4)
+
+
+def test_w4a4_one_cta_forms_agree_with_the_pair_form(nv, oracle, tmp_path):
+    """The prefill GEMM forms kept behind environment switches (one CTA per tile, persistent or not)
+    run in a child process each - the switches are read once per process - on the same operands as
+    this process's CTA-pair form: K is walked in the same order, so the BF16 outputs agree bit for bit."""
+    import os
+    import subprocess
+    import sys
+
+    script = (
+        "import sys, numpy as np, torch\n"
+        "sys.path.insert(0, sys.argv[1])\n"
+        "from ignis_b200 import nvfp4 as nv\n"
+        "nv.prepare()\n"
+        "d = np.load(sys.argv[2])\n"
+        "w = nv.Weight.from_planes(d['codes'], d['scales'], 448.0, 448.0)\n"
+        "x = torch.from_numpy(d['x']).view(torch.bfloat16).cuda()\n"
+        "ws = nv.Workspace(nv.workspace_bytes(w.n, w.k, nv.ALLOW_A4, x.shape[0]))\n"
+        "y = nv.linear(x, w, policy=nv.ALLOW_A4, workspace=ws)\n"
+        "assert ws.status() == 0\n"
+        "np.save(sys.argv[3], y.view(torch.int16).cpu().numpy())\n"
+    )
+    tokens, n, k = 300, 640, 1024
+    rng = np.random.default_rng(5)
+    codes, scales, _ = make_weight(rng, n, k)
+    x = torch.randn(tokens, k, generator=torch.Generator().manual_seed(5)).to(torch.bfloat16)
+    np.savez(tmp_path / "in.npz", codes=codes, scales=scales, x=x.view(torch.int16).numpy())
+    w = nv.Weight.from_planes(codes, scales, 448.0, 448.0)
+    ws = nv.Workspace(nv.workspace_bytes(n, k, nv.ALLOW_A4, tokens))
+    here = nv.linear(x.cuda(), w, policy=nv.ALLOW_A4, workspace=ws).view(torch.int16).cpu().numpy()
+    check_bf16(torch.from_numpy(here).view(torch.bfloat16), w4a4_reference(oracle, codes, scales, n, k, 448.0, 448.0, x))
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    for switches in ({"B200Q_W4A4_PAIR": "0"}, {"B200Q_W4A4_PAIR": "0", "B200Q_W4A4_PERSISTENT": "0"},
+                     {"B200Q_W4A4_PAIR": "0", "B200Q_W4A4_PERSISTENT": "0", "B200Q_W4A4_BN": "256"}):
+        out = tmp_path / ("out_" + "_".join(switches.values()) + ".npy")
+        subprocess.run([sys.executable, "-c", script, root, str(tmp_path / "in.npz"), str(out)], check=True,
+                       env={**os.environ, **switches}, timeout=600)
+        assert np.array_equal(np.load(out), here)
+
