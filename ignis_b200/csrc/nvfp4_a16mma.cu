@@ -352,7 +352,7 @@ int32_t a16mma_launch(ErrorSlot &slot, const DeviceState &dev, const GemvWeight 
   const uint32_t k_stages = k / 64u;
   const uint32_t token_tiles = (tokens + p.bn - 1u) / p.bn;
   uint32_t kc = 1;
-  if (p.bn <= 64u) {  // the cluster reduction keeps bn x 128 floats in shared memory
+  if (p.bn * 512u <= stages * stage_bytes) {  // the cluster reduction keeps bn x 128 floats in shared memory, over the idle ring
     while (kc < 8u && row_tiles * token_tiles * (kc + 1u) <= slots && k_stages / (kc + 1u) >= 2u * stages) ++kc;
   }
   p.kc = kc;
