@@ -181,6 +181,32 @@ def test_config0_full_size(nv, oracle):
     check_bf16(nv.linear(x.cuda(), w), ref)
 
 
+def test_config2_full_size_sampled(nv, oracle):
+    """BASELINE configs[2] at its full size (M = 8192, up 5120 -> 17408, W4A4): the whole product on
+    the device, checked against the host arithmetic on sampled row tiles x tokens (first, last and
+    interior tiles of both dimensions), and through a size-independent property - a product over
+    the same weights with the tokens reversed is the reversed product, bit for bit."""
+    tokens, n, k = 8192, 17408, 5120
+    rng = np.random.default_rng(2)
+    codes, scales, d_w = make_weight(rng, n, k)
+    d_in = 448.0
+    w = nv.Weight.from_planes(codes, scales, d_w, d_in)
+    x = torch.randn(tokens, k, generator=torch.Generator().manual_seed(2)).to(torch.bfloat16)
+    ws = nv.Workspace(nv.workspace_bytes(n, k, nv.ALLOW_A4, tokens))
+    y = nv.linear(x.cuda(), w, policy=nv.ALLOW_A4, workspace=ws)
+    assert ws.status() == 0
+    natural = nv.unswizzle_scales(scales, n, k)
+    picks = torch.tensor([0, 1, 127, 128, 255, 256, 4095, 4096, 5000, 8063, 8064, 8191])
+    for tile in (0, 1, 67, 68, 135):
+        rows = slice(tile * 128, tile * 128 + 128)
+        sub_scales = nv.swizzle_scales(natural[rows])
+        ref = w4a4_reference(oracle, codes[rows], sub_scales, 128, k, d_w, d_in, x[picks])
+        check_bf16(y[picks.cuda()][:, rows], ref)
+    back = nv.linear(x.flip(0).contiguous().cuda(), w, policy=nv.ALLOW_A4, workspace=ws)
+    assert ws.status() == 0
+    assert torch.equal(back.flip(0), y)
+
+
 def test_reference_patterned_weight_and_criterion(nv, oracle):
     """The reference's own A16 arm: patterned weight, divisors 0.125 / 3.5, relative L2 and gross
     bounds {2^-8, 2^-8, 2 * 2^-8} (linear_test_common.cpp:29-48, :234-240)."""
