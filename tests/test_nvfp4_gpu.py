@@ -515,6 +515,33 @@ def test_w4a4_decode_route(nv, oracle, tokens, n, k):
     assert nv.device_status() == 0
 
 
+def test_config1_gate_up_full_size_under_allow_a4(nv, oracle):
+    """configs[1]'s widest product (gate|up, 34816 x 5120, 8 tokens) under ALLOW_A4 at full size: sampled
+    row tiles against the host arithmetic, and the token-order property (the same tokens in reverse
+    give the reversed outputs, bit for bit: every token is quantized and multiplied on its own)."""
+    tokens, n, k = 8, 34816, 5120
+    rng = np.random.default_rng(3)
+    codes, scales, d_w = make_weight(rng, n, k)
+    d_in = 448.0
+    w = nv.Weight.from_planes(codes, scales, d_w, d_in)
+    x = torch.randn(tokens, k, generator=torch.Generator().manual_seed(3)).to(torch.bfloat16)
+    y = nv.linear(x.cuda(), w, policy=nv.ALLOW_A4)
+    assert nv.device_status() == 0
+    natural = nv.unswizzle_scales(scales, n, k)
+    for tile in (0, 1, 135, 136, 271):
+        rows = slice(tile * 128, tile * 128 + 128)
+        ref = w4a4_reference(oracle, codes[rows], nv.swizzle_scales(natural[rows]), 128, k, d_w, d_in, x)
+        check_bf16(y[:, rows], ref)
+    back = nv.linear(x.flip(0).contiguous().cuda(), w, policy=nv.ALLOW_A4)
+    assert torch.equal(back.flip(0), y)
+    h = nv.linear_swiglu(x.cuda(), w, policy=nv.ALLOW_A4)   # the fused form over the same parent
+    g, u = y[:, : n // 2].double(), y[:, n // 2:].double()
+    want = (g / (1 + torch.exp(-g)) * u).cpu().numpy()
+    got = h.double().cpu().numpy()
+    assert np.all(np.abs(got - want) <= 2.0 ** -7 * np.abs(want) + 1e-3 * np.abs(want).max())
+    assert nv.device_status() == 0
+
+
 def test_w4a4_decode_thresholds_and_groups(nv, oracle):
     """Below the reference's thresholds ALLOW_A4 is the A16 product bit for bit; a group (each weight
     under its own input divisor) agrees with the host arithmetic weight by weight."""
