@@ -27,6 +27,12 @@ class Workspace(C.Structure):
     _fields_ = [("base", C.c_void_p), ("bytes", C.c_uint64)]
 
 
+class PeerSync(C.Structure):
+    """``b200q_peer_sync``: one rejoin point of a column-sharded layer."""
+
+    _fields_ = [("flags_peers", C.c_void_p), ("state", C.c_void_p), ("peers", C.c_uint32), ("rank", C.c_uint32)]
+
+
 # name -> (restype, argtypes); every symbol the headers declare appears here.
 NVFP4_SYMBOLS = {
     "b200q_nvfp4_prepare": (C.c_int32, []),
@@ -47,6 +53,9 @@ NVFP4_SYMBOLS = {
     "b200q_nvfp4_linear_group_scatter": (C.c_int32, [C.POINTER(C.POINTER(Nvfp4Weight)), C.c_uint32, C.c_void_p, C.c_uint32,
                                                      C.POINTER(C.c_void_p), C.c_uint32, C.POINTER(C.c_uint32), C.POINTER(C.c_uint32),
                                                      C.c_uint32, C.c_void_p]),
+    "b200q_nvfp4_linear_group_gather": (C.c_int32, [C.POINTER(C.POINTER(Nvfp4Weight)), C.c_uint32, C.c_void_p, C.c_uint32,
+                                                    C.POINTER(C.c_void_p), C.c_uint32, C.POINTER(C.c_uint32), C.POINTER(C.c_uint32),
+                                                    C.c_uint32, C.POINTER(PeerSync), C.POINTER(PeerSync), C.c_void_p]),
     "b200q_peer_barrier": (C.c_int32, [C.c_void_p, C.c_uint32, C.c_uint32, C.c_uint32, C.c_void_p, C.c_void_p]),
     "b200q_nvfp4_mlp_workspace_bytes": (C.c_uint64, [C.c_uint32, C.c_uint32, C.c_uint32, C.c_uint32]),
     "b200q_nvfp4_mlp": (C.c_int32, [C.POINTER(Nvfp4Weight), C.POINTER(Nvfp4Weight), C.c_void_p, C.c_uint32, C.c_void_p, C.c_uint32,
@@ -56,6 +65,12 @@ NVFP4_SYMBOLS = {
     "b200q_nvfp4_dequantize": (C.c_int32, [C.POINTER(Nvfp4Weight), C.c_void_p, C.c_void_p]),
     "b200q_nvfp4_quantize_activations": (C.c_int32, [C.c_void_p, C.c_uint32, C.c_uint32, C.c_float, C.c_void_p,
                                                      C.c_void_p, C.c_void_p]),
+    "b200q_nvfp4_quantize_operand": (C.c_int32, [C.c_void_p, C.c_uint32, C.c_uint32, C.c_uint32, C.c_uint32, C.c_float,
+                                                 C.POINTER(Workspace), C.c_void_p]),
+    "b200q_nvfp4_linear_prequantized": (C.c_int32, [C.POINTER(Nvfp4Weight), C.c_uint32, C.c_void_p, C.c_uint32, C.c_uint32,
+                                                    C.POINTER(Workspace), C.c_void_p]),
+    "b200q_nvfp4_mma_peak": (C.c_int32, [C.c_uint32, C.c_uint32, C.c_void_p, C.c_uint32, C.POINTER(C.c_double), C.c_void_p]),
+    "b200q_nvfp4_mma_peak_status": (C.c_int32, [C.c_void_p, C.POINTER(C.c_uint32)]),
     "b200q_nvfp4_last_error": (C.c_char_p, []),
 }
 

@@ -53,6 +53,7 @@ struct DeviceState {
   int w4a4_bn = 128;     // B200Q_W4A4_BN: weight rows per tile of the plain W4A4 product (128 or 256)
   int gemv_xu = 8;       // B200Q_GEMV_XU: words per row of 8 decoded by the hardware E2M1 conversion
   int sm_cap = 0;        // IGNIS_TRELLIS_SM_CAP
+  int peer_barrier_polls = 1 << 22;  // B200Q_PEER_BARRIER_POLLS: looks at a flag before b200q_peer_barrier gives up (400 ns apart)
 };
 // State of the current device, nullptr (and `slot` filled) when the device query fails.
 DeviceState *device_state(ErrorSlot &slot);
@@ -169,6 +170,39 @@ __device__ __forceinline__ void mma_bf16_f32(float (&d)[4], uint32_t a0, uint32_
 }
 
 __device__ __forceinline__ float bf16_bits_to_f32(uint32_t bits16) { return __uint_as_float(bits16 << 16); }
+
+// ---- flags between the GPUs of a node ------------------------------------------------------------
+__device__ __forceinline__ void st_release_sys(uint32_t *p, uint32_t v) {
+  asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t *p) {
+  uint32_t v;
+  asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ uint32_t ld_acquire_gpu(const uint32_t *p) {
+  uint32_t v;
+  asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+// Lane s < peers of one warp waits, with a bound, until slot s of this rank's own flag array has
+// reached `expected`; a wait that runs out records rank s in state[0] and returns.
+__device__ __forceinline__ void peer_wait_flags(uint32_t *const *flags_peers, uint32_t *state, uint32_t peers, uint32_t rank,
+                                                uint32_t polls, uint32_t expected, int lane) {
+  if (static_cast<uint32_t>(lane) < peers) {
+    const uint32_t *mine = flags_peers[rank] + lane;
+    bool seen = false;
+    for (uint32_t poll = 0; poll < polls; ++poll) {
+      if (static_cast<int32_t>(ld_acquire_sys(mine) - expected) >= 0) {
+        seen = true;
+        break;
+      }
+      __nanosleep(poll < 64u ? 40 : 400);
+    }
+    if (!seen) atomicOr(state, 1u << lane);
+  }
+  __syncwarp();
+}
 #endif  // __CUDACC__
 
 }  // namespace b200q

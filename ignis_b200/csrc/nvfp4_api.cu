@@ -35,15 +35,28 @@ const DeviceState *prepared_state(ErrorSlot &slot, const char *what) {
 
 // The decode route over `count` weights that share x, in passes of at most 32 tokens.
 // `y` holds `peers` pointers per weight (weight i's at y[i * peers ..]); a plain product has one.
+PeerSync make_sync(const DeviceState &dev, const b200q_peer_sync *s) {
+  PeerSync out = {};
+  if (s != nullptr) {
+    out.flags_peers = s->flags_peers;
+    out.state = s->state;
+    out.peers = s->peers;
+    out.rank = s->rank;
+    out.polls = static_cast<uint32_t>(dev.peer_barrier_polls);
+  }
+  return out;
+}
+
 int32_t decode_route(ErrorSlot &slot, const DeviceState &dev, const b200q_nvfp4_weight *const *w, uint32_t count,
                      const void *x, uint32_t tokens, void *const *y, const uint32_t *ldy, uint32_t epilogue,
-                     cudaStream_t stream, uint32_t peers = 1) {
+                     cudaStream_t stream, uint32_t peers = 1, const b200q_peer_sync *wait_for = nullptr,
+                     const b200q_peer_sync *signal = nullptr) {
   const uint32_t k = w[0]->k;
   const bool swiglu = (epilogue & kEpilogueSwiglu) != 0u;
   const size_t out_elem = (epilogue & kEpilogueF32) ? 4u : 2u;
   uint32_t groups = 0;
   for (uint32_t i = 0; i < count; ++i) groups += w[i]->n / 32u;
-  if (dev.a16_mma != 0 && tokens > 16u && !swiglu && peers == 1u && a16mma_takes(k, x)) {
+  if (dev.a16_mma != 0 && tokens > 16u && !swiglu && peers == 1u && wait_for == nullptr && signal == nullptr && a16mma_takes(k, x)) {
     // beyond two token tiles the warp-level MMAs of the decode kernel are the limit: the weights
     // are decoded once per tile of up to 256 tokens and multiplied on the tensor cores
     {
@@ -76,6 +89,9 @@ int32_t decode_route(ErrorSlot &slot, const DeviceState &dev, const b200q_nvfp4_
     p.ksteps = (k + 255u) / 256u;
     p.tokens = pass;
     p.epilogue = epilogue;
+    // a call of several passes waits before its first and publishes after its last
+    if (t0 == 0) p.wait = make_sync(dev, wait_for);
+    if (t0 + B200Q_NVFP4_DECODE_MAX_TOKENS >= tokens) p.signal = make_sync(dev, signal);
     const GemvPlan plan = gemv_plan(dev, groups, p.ksteps, nt, swiglu);
     const uint32_t rows_per_cta = static_cast<uint32_t>(swiglu ? plan.rm / 2 : plan.rm);
     uint32_t ctas = 0;
@@ -251,10 +267,11 @@ int32_t b200q_nvfp4_linear_group(const b200q_nvfp4_weight *const *w, uint32_t co
 int32_t b200q_nvfp4_device_status(void *stream, uint32_t *status) {
   ErrorSlot &slot = nvfp4_error();
   if (status == nullptr) return fail(slot, "b200q_nvfp4_device_status: status is NULL");
-  uint32_t a16 = 0, a4 = 0;
+  uint32_t a16 = 0, a4 = 0, noalloc = 0;
   if (a16mma_status(slot, static_cast<cudaStream_t>(stream), &a16) != 0) return -1;
   if (w4a4_decode_status(slot, static_cast<cudaStream_t>(stream), &a4) != 0) return -1;
-  *status = a16 | a4;
+  if (w4a4_noalloc_status(slot, static_cast<cudaStream_t>(stream), &noalloc) != 0) return -1;
+  *status = a16 | a4 | noalloc;
   return 0;
 }
 
@@ -319,10 +336,19 @@ int32_t b200q_nvfp4_linear_split(const b200q_nvfp4_weight *parent, uint32_t coun
   return 0;
 }
 
-int32_t b200q_nvfp4_linear_group_scatter(const b200q_nvfp4_weight *const *w, uint32_t count, const void *x, uint32_t tokens,
-                                         void *const *y_peers, uint32_t peers, const uint32_t *ldy, const uint32_t *col_offset,
-                                         uint32_t epilogue, void *stream) {
-  const char *what = "b200q_nvfp4_linear_group_scatter";
+namespace {
+int32_t check_sync(ErrorSlot &slot, const b200q_peer_sync *s, const char *what, const char *which) {
+  if (s == nullptr) return 0;
+  if (s->flags_peers == nullptr || s->state == nullptr) return fail(slot, "%s: %s has a NULL pointer", what, which);
+  if (s->peers == 0 || s->peers > kMaxPeers || s->rank >= s->peers) {
+    return fail(slot, "%s: %s has peers = %u, rank = %u out of range", what, which, s->peers, s->rank);
+  }
+  return 0;
+}
+
+int32_t scatter_impl(const b200q_nvfp4_weight *const *w, uint32_t count, const void *x, uint32_t tokens, void *const *y_peers,
+                     uint32_t peers, const uint32_t *ldy, const uint32_t *col_offset, uint32_t epilogue,
+                     const b200q_peer_sync *wait_for, const b200q_peer_sync *signal, void *stream, const char *what) {
   ErrorSlot &slot = nvfp4_error();
   if (w == nullptr || y_peers == nullptr || ldy == nullptr || col_offset == nullptr) return fail(slot, "%s: NULL argument array", what);
   if (count == 0 || count > B200Q_NVFP4_MAX_GROUP) return fail(slot, "%s: count = %u is outside 1..%d", what, count, B200Q_NVFP4_MAX_GROUP);
@@ -330,6 +356,7 @@ int32_t b200q_nvfp4_linear_group_scatter(const b200q_nvfp4_weight *const *w, uin
   if (tokens == 0) return fail(slot, "%s: tokens must be positive", what);
   if ((epilogue & ~static_cast<uint32_t>(B200Q_NVFP4_OUT_F32)) != 0u) return fail(slot, "%s: only STORE (optionally OUT_F32) is served", what);
   if (x == nullptr || !aligned(x, 16)) return fail(slot, "%s: x is NULL or not 16-byte aligned", what);
+  if (check_sync(slot, wait_for, what, "wait_for") != 0 || check_sync(slot, signal, what, "signal") != 0) return -1;
   const size_t out_elem = (epilogue & kEpilogueF32) ? 4u : 2u;
   void *targets[B200Q_NVFP4_MAX_GROUP * kMaxPeers];
   for (uint32_t i = 0; i < count; ++i) {
@@ -343,7 +370,23 @@ int32_t b200q_nvfp4_linear_group_scatter(const b200q_nvfp4_weight *const *w, uin
   }
   const DeviceState *dev = prepared_state(slot, what);
   if (dev == nullptr) return -1;
-  return decode_route(slot, *dev, w, count, x, tokens, targets, ldy, epilogue, static_cast<cudaStream_t>(stream), peers);
+  return decode_route(slot, *dev, w, count, x, tokens, targets, ldy, epilogue, static_cast<cudaStream_t>(stream), peers, wait_for, signal);
+}
+}  // namespace
+
+int32_t b200q_nvfp4_linear_group_scatter(const b200q_nvfp4_weight *const *w, uint32_t count, const void *x, uint32_t tokens,
+                                         void *const *y_peers, uint32_t peers, const uint32_t *ldy, const uint32_t *col_offset,
+                                         uint32_t epilogue, void *stream) {
+  return scatter_impl(w, count, x, tokens, y_peers, peers, ldy, col_offset, epilogue, nullptr, nullptr, stream,
+                      "b200q_nvfp4_linear_group_scatter");
+}
+
+int32_t b200q_nvfp4_linear_group_gather(const b200q_nvfp4_weight *const *w, uint32_t count, const void *x, uint32_t tokens,
+                                        void *const *y_peers, uint32_t peers, const uint32_t *ldy, const uint32_t *col_offset,
+                                        uint32_t epilogue, const b200q_peer_sync *wait_for, const b200q_peer_sync *signal,
+                                        void *stream) {
+  return scatter_impl(w, count, x, tokens, y_peers, peers, ldy, col_offset, epilogue, wait_for, signal, stream,
+                      "b200q_nvfp4_linear_group_gather");
 }
 
 uint64_t b200q_nvfp4_mlp_workspace_bytes(uint32_t gate_up_n, uint32_t k, uint32_t policy, uint32_t tokens) {
@@ -433,6 +476,54 @@ int32_t b200q_nvfp4_quantize_activations(const void *x, uint32_t tokens, uint32_
   return quantize_activations_launch(slot, static_cast<const uint16_t *>(x), tokens, k, input_scale_divisor,
                                      static_cast<uint8_t *>(codes), static_cast<uint8_t *>(scales),
                                      static_cast<cudaStream_t>(stream));
+}
+
+int32_t b200q_nvfp4_quantize_operand(const void *x_rows, uint32_t tokens_total, uint32_t token_begin, uint32_t token_count,
+                                     uint32_t k, float input_scale_divisor, const b200q_nvfp4_workspace *workspace, void *stream) {
+  const char *what = "b200q_nvfp4_quantize_operand";
+  ErrorSlot &slot = nvfp4_error();
+  if (x_rows == nullptr || !aligned(x_rows, 16)) return fail(slot, "%s: x_rows is NULL or not 16-byte aligned", what);
+  if (k == 0 || (k % 256u) != 0) return fail(slot, "%s: k = %u is not a positive multiple of 256", what, k);
+  if (token_count == 0 || (token_begin % 128u) != 0 || static_cast<uint64_t>(token_begin) + token_count > tokens_total) {
+    return fail(slot, "%s: tokens [%u, +%u) must start on a multiple of 128 inside the call's %u tokens", what, token_begin,
+                token_count, tokens_total);
+  }
+  if (token_begin + token_count < tokens_total && (token_count % 128u) != 0) {
+    return fail(slot, "%s: only the call's last range may end off a multiple of 128", what);
+  }
+  if (!std::isfinite(input_scale_divisor) || !(input_scale_divisor > 0.0f)) return fail(slot, "%s: input_scale_divisor must be finite and positive", what);
+  const uint64_t need = w4a4_workspace_bytes(k, tokens_total);
+  if (workspace == nullptr || workspace->base == nullptr || workspace->bytes < need || !aligned(workspace->base, 256)) {
+    return fail(slot, "%s: needs a 256-byte aligned workspace of %llu bytes", what, static_cast<unsigned long long>(need));
+  }
+  const DeviceState *dev = prepared_state(slot, what);
+  if (dev == nullptr) return -1;
+  return w4a4_quantize_range(slot, *dev, static_cast<const uint16_t *>(x_rows), tokens_total, token_begin, token_count, k,
+                             input_scale_divisor, static_cast<uint8_t *>(workspace->base), static_cast<cudaStream_t>(stream));
+}
+
+int32_t b200q_nvfp4_linear_prequantized(const b200q_nvfp4_weight *w, uint32_t tokens, void *y, uint32_t ldy, uint32_t epilogue,
+                                        const b200q_nvfp4_workspace *workspace, void *stream) {
+  const char *what = "b200q_nvfp4_linear_prequantized";
+  ErrorSlot &slot = nvfp4_error();
+  if (check_weight(slot, w, what) != 0) return -1;
+  if (!w4a4_shape_ok(w->n, w->k)) return fail(slot, "%s: k must be a multiple of 256", what);
+  if ((epilogue & ~(B200Q_NVFP4_ADD | B200Q_NVFP4_OUT_F32)) != 0u) return fail(slot, "%s: unknown epilogue 0x%x", what, epilogue);
+  if (tokens == 0) return fail(slot, "%s: tokens must be positive", what);
+  if (!std::isfinite(w->input_scale_divisor) || !(w->input_scale_divisor > 0.0f)) {
+    return fail(slot, "%s: input_scale_divisor must be finite and positive", what);
+  }
+  if (y == nullptr || !aligned(y, 16) || (ldy % 8u) != 0 || ldy < w->n) return fail(slot, "%s: y must be 16-byte aligned, ldy a multiple of 8 and at least n", what);
+  const uint64_t need = w4a4_workspace_bytes(w->k, tokens);
+  if (workspace == nullptr || workspace->base == nullptr || workspace->bytes < need || !aligned(workspace->base, 256)) {
+    return fail(slot, "%s: needs the 256-byte aligned workspace of %llu bytes the operand was quantized into", what,
+                static_cast<unsigned long long>(need));
+  }
+  const DeviceState *dev = prepared_state(slot, what);
+  if (dev == nullptr) return -1;
+  return w4a4_launch_prequantized(slot, *dev, static_cast<const uint8_t *>(w->codes), static_cast<const uint8_t *>(w->scales), w->n, w->k,
+                                  w->weight_scale_divisor, w->input_scale_divisor, tokens, y, ldy, epilogue,
+                                  static_cast<uint8_t *>(workspace->base), static_cast<cudaStream_t>(stream));
 }
 
 const char *b200q_nvfp4_last_error(void) { return nvfp4_error().text; }

@@ -154,15 +154,6 @@ __device__ __forceinline__ float4 ld_cluster_f4(const void *local_smem, uint32_t
   return v;
 }
 
-// Measurement hook: warp 0 lane 0 of a CTA stamps the nanosecond timer at phase boundaries.
-__device__ __forceinline__ void stamp(unsigned long long *trace, int slot) {
-  if (trace != nullptr && threadIdx.x == 0) {
-    unsigned long long t;
-    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
-    trace[static_cast<size_t>(blockIdx.x) * 8 + slot] = t;
-  }
-}
-
 __device__ __forceinline__ float silu_f32(float v) { return v / (1.0f + __expf(-v)); }
 
 // Eight BF16 values (one 16-byte chunk) times a power of two, as fp16, in the order the MMA
@@ -321,8 +312,6 @@ __global__ void __launch_bounds__(kThreads, NT <= 2 ? 2 : 1) nvfp4_gemv_kernel(c
   const int c0 = static_cast<int>(static_cast<uint64_t>(p.ksteps) * rank / kc);
   const int c1 = static_cast<int>(static_cast<uint64_t>(p.ksteps) * (rank + 1) / kc);
   const int ch = static_cast<int>(p.xs_steps);
-
-  stamp(p.trace, 0);
   Stage st0, st1;
   int s = c0 + kw;
   load_stage(st0, rows, s, c1, t, scale_tiles);
@@ -331,7 +320,13 @@ __global__ void __launch_bounds__(kThreads, NT <= 2 ? 2 : 1) nvfp4_gemv_kernel(c
   // The weights above never depend on the previous kernel; the activations may.
   griddep_launch_dependents();
   griddep_wait();
-  stamp(p.trace, 1);
+  if (p.wait.flags_peers != nullptr) {
+    // x was stored into this rank's buffer by every rank's product of the same point: this rank's
+    // own product (earlier in the stream, finished) counted the point in state[1]; wait until
+    // every rank's flag has reached that count
+    if (warp == 0) peer_wait_flags(p.wait.flags_peers, p.wait.state, p.wait.peers, p.wait.rank, p.wait.polls, ld_acquire_gpu(p.wait.state + 1), lane);
+    __syncthreads();
+  }
 
   // Accumulators live in the units of the current chunk's per-token scale; at a chunk boundary
   // they are carried into the next chunk's units by an exact power-of-two factor.
@@ -356,7 +351,6 @@ __global__ void __launch_bounds__(kThreads, NT <= 2 ? 2 : 1) nvfp4_gemv_kernel(c
     }
     prepare_activations<NT, XU>(p, cb, ce, xs, inv_s, scale_s, warp, lane);
     __syncthreads();
-    stamp(p.trace, 2);
     if (cb != c0) {
 #pragma unroll
       for (int tt = 0; tt < NT; ++tt) {
@@ -396,8 +390,6 @@ __global__ void __launch_bounds__(kThreads, NT <= 2 ? 2 : 1) nvfp4_gemv_kernel(c
       tot[a][tt][3] *= i1;
     }
   }
-
-  stamp(p.trace, 3);
   // ---- K reduction inside the CTA: columns kw = 1.. hand their sums to column 0, fixed order ----
   if (kw > 0) {
 #pragma unroll
@@ -429,9 +421,7 @@ __global__ void __launch_bounds__(kThreads, NT <= 2 ? 2 : 1) nvfp4_gemv_kernel(c
   }
 
   // ---- K reduction across the cluster, then the epilogue, the items dealt over ranks and warps ----
-  stamp(p.trace, 4);
   cluster_sync_all();
-  stamp(p.trace, 5);
   const int out_groups = swiglu ? rm / 2 : rm;
   const int items = out_groups * 2 * NT;
   const float coef = W.inv_dw * 128.0f;  // the operands carried 2^-7
@@ -476,9 +466,24 @@ __global__ void __launch_bounds__(kThreads, NT <= 2 ? 2 : 1) nvfp4_gemv_kernel(c
       }
     }
   }
-  stamp(p.trace, 6);
   cluster_sync_all();  // no CTA leaves while a peer may still read its partial sums
-  stamp(p.trace, 7);
+  if (p.signal.flags_peers != nullptr) {
+    // The all-gather's barrier, folded into the product: every CTA makes its stores (into every
+    // rank's buffer) visible system-wide and arrives at a counter; the launch's last CTA numbers the
+    // point and publishes that number in this rank's slot of every rank's flag array.
+    __threadfence_system();
+    __syncthreads();
+    if (warp == 0) {
+      uint32_t epoch = 0;
+      if (lane == 0 && atomicAdd(p.signal.state + 2, 1u) == gridDim.x - 1u) {
+        atomicExch(p.signal.state + 2, 0u);
+        epoch = atomicAdd(p.signal.state + 1, 1u) + 1u;
+        __threadfence_system();
+      }
+      epoch = __shfl_sync(0xFFFFFFFFu, epoch, 0);
+      if (epoch != 0u && static_cast<uint32_t>(lane) < p.signal.peers) st_release_sys(p.signal.flags_peers[lane] + p.signal.rank, epoch);
+    }
+  }
 }
 
 constexpr size_t kGemvMaxSmem = 160 * 1024;
@@ -607,12 +612,8 @@ GemvPlan gemv_plan(const DeviceState &dev, uint32_t groups, uint32_t ksteps, int
   return best;
 }
 
-// Measurement only: where the next launches write their phase stamps (8 u64 per CTA), or nullptr.
-unsigned long long *g_gemv_trace = nullptr;
-
 int32_t gemv_launch(ErrorSlot &slot, const DeviceState &dev, GemvParams &p, int nt, const GemvPlan &plan, uint32_t ctas,
                     cudaStream_t stream) {
-  p.trace = g_gemv_trace;
   p.rm = plan.rm;
   p.kc = plan.kc;
   p.xs_steps = plan.xs_steps;
@@ -632,8 +633,3 @@ int32_t gemv_launch(ErrorSlot &slot, const DeviceState &dev, GemvParams &p, int 
 }
 
 }  // namespace b200q
-
-// Measurement only (not part of the public ABI): directs the phase stamps of later NVFP4 decode
-// launches on this thread's device to `buffer` (8 u64 per CTA of the largest launch), or stops
-// stamping with nullptr.
-extern "C" void b200q_debug_gemv_trace(void *buffer) { b200q::g_gemv_trace = static_cast<unsigned long long *>(buffer); }

@@ -16,6 +16,17 @@ constexpr uint32_t kEpilogueQuant = 0x400u;  // with SwiGLU on the tensor-core r
 
 constexpr uint32_t kMaxPeers = 8;  // ranks of one node a scattered product writes to
 
+// One synchronization point between the ranks of a node (b200q_peer_sync): every rank owns an array
+// of `peers` flags (slot s written by rank s) that all ranks have mapped, and three words of its
+// own: state[0] ranks that missed a wait, state[1] the number of times this rank has published the
+// point, state[2] an arrival counter of the publishing launch's CTAs.
+struct PeerSync {
+  uint32_t *const *flags_peers;  // device array of `peers` pointers; nullptr: not used
+  uint32_t *state;
+  uint32_t peers, rank;
+  uint32_t polls;                // looks at a flag before a wait gives up
+};
+
 struct GemvWeight {
   const uint8_t *codes;
   const uint8_t *scales;
@@ -38,7 +49,8 @@ struct GemvParams {
   uint32_t rm;        // 32-row groups per CTA: 1, 2, 4 or 8
   uint32_t kc;        // cluster size: K slices across CTAs
   uint32_t xs_steps;  // steps of activation fragments shared memory holds at a time
-  unsigned long long *trace;  // measurement only: 8 %globaltimer stamps per CTA, or nullptr
+  PeerSync wait;      // before x is read: every rank has published the point that produced it
+  PeerSync signal;    // after the outputs are stored (into every rank's buffer): publish this point
 };
 
 struct GemvPlan {
@@ -93,6 +105,9 @@ int32_t w4a4_launch(ErrorSlot &slot, const DeviceState &dev, const uint8_t *w_co
 int32_t w4a4_launch_prequantized(ErrorSlot &slot, const DeviceState &dev, const uint8_t *w_codes, const uint8_t *w_scales,
                                  uint32_t n, uint32_t k, float d_w, float d_in, uint32_t tokens, void *y, uint32_t ldy,
                                  uint32_t epilogue, uint8_t *workspace, cudaStream_t stream);
+int32_t w4a4_quantize_range(ErrorSlot &slot, const DeviceState &dev, const uint16_t *x_rows, uint32_t tokens_total,
+                            uint32_t token_begin, uint32_t token_count, uint32_t k, float d_in, uint8_t *workspace,
+                            cudaStream_t stream);
 // The layers' MLP on the tensor-core route: x is quantized, the gate|up product's epilogue writes
 // silu(g) u already quantized under `down`'s input divisor, the down product reads it.
 uint64_t w4a4_mlp_workspace_bytes(uint32_t k, uint32_t inter, uint32_t tokens);
@@ -100,6 +115,10 @@ int32_t w4a4_mlp_launch(ErrorSlot &slot, const DeviceState &dev, const uint8_t *
                         uint32_t k, float gu_dw, float gu_din, const uint8_t *dn_codes, const uint8_t *dn_scales, uint32_t dn_n,
                         float dn_dw, float dn_din, const uint16_t *x, uint32_t tokens, void *y, uint32_t ldy, uint32_t epilogue,
                         uint8_t *workspace, cudaStream_t stream);
+
+// The status line of b200q_nvfp4_linear_noalloc's built-in scratch on the current device (0 before
+// that entry has run there), read after `stream` has finished.
+int32_t w4a4_noalloc_status(ErrorSlot &slot, cudaStream_t stream, uint32_t *status);
 
 }  // namespace b200q
 

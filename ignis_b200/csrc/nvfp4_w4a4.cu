@@ -954,6 +954,25 @@ int32_t w4a4_launch_prequantized(ErrorSlot &slot, const DeviceState &dev, const 
                       reinterpret_cast<uint32_t *>(workspace), a_codes, a_scales, QuantTarget(), stream);
 }
 
+// Quantizes tokens [token_begin, token_begin + token_count) of a call of `tokens_total` tokens into
+// their place of the operand in `workspace` (token_begin a multiple of 128: whole scale tiles);
+// `x_rows` points at the first of those tokens. Rows between the range's end and the next multiple
+// of 128 are written as zeros.
+int32_t w4a4_quantize_range(ErrorSlot &slot, const DeviceState &dev, const uint16_t *x_rows, uint32_t tokens_total,
+                            uint32_t token_begin, uint32_t token_count, uint32_t k, float d_in, uint8_t *workspace,
+                            cudaStream_t stream) {
+  const uint64_t pad_total = w4a4_tokens_pad(tokens_total);
+  const uint32_t pad = w4a4_tokens_pad(token_count);
+  uint8_t *codes = workspace + 256 + static_cast<uint64_t>(token_begin) * (k / 2u);
+  uint8_t *scales = workspace + 256 + pad_total * (k / 2u) + static_cast<uint64_t>(token_begin / 128u) * (k / 64u) * 512u;
+  const uint64_t total = static_cast<uint64_t>(pad) * (k / 64u);
+  const uint32_t grid = static_cast<uint32_t>(total / 256u < 148u * 16u ? (total + 255u) / 256u : 148u * 16u);
+  const cudaError_t err = launch(quantize_swizzled_kernel, dim3(grid), dim3(256), 0, stream, dev.pdl != 0, x_rows, token_count, pad, k,
+                                 d_in, codes, scales);
+  if (err != cudaSuccess) return fail(slot, "nvfp4 activation quantizer launch: %s", cudaGetErrorString(err));
+  return 0;
+}
+
 // Workspace of the MLP: the status line, x quantized (K = k), h quantized (K = inter).
 uint64_t w4a4_mlp_workspace_bytes(uint32_t k, uint32_t inter, uint32_t tokens) {
   const uint64_t pad = w4a4_tokens_pad(tokens);
@@ -1000,7 +1019,7 @@ constexpr int kMaxScratchDevices = 64;
 uint8_t *g_scratch_address[kMaxScratchDevices] = {};
 std::mutex g_scratch_mutex;
 
-int32_t static_scratch(ErrorSlot &slot, cudaStream_t stream, uint8_t **out) {
+int32_t static_scratch(ErrorSlot &slot, uint8_t **out) {
   int device = -1;
   cudaError_t err = cudaGetDevice(&device);
   if (err != cudaSuccess) return fail(slot, "b200q_nvfp4_linear_noalloc: no CUDA device: %s", cudaGetErrorString(err));
@@ -1012,9 +1031,9 @@ int32_t static_scratch(ErrorSlot &slot, cudaStream_t stream, uint8_t **out) {
     if (err != cudaSuccess || address == nullptr) {
       return fail(slot, "b200q_nvfp4_linear_noalloc: cudaGetSymbolAddress failed: %s", cudaGetErrorString(err));
     }
-    // the status line must start at zero; everything else is rewritten by every call
-    err = cudaMemsetAsync(address, 0, 256, stream);
-    if (err != cudaSuccess) return fail(slot, "b200q_nvfp4_linear_noalloc: clearing the status line failed: %s", cudaGetErrorString(err));
+    // The status line needs no clearing: a file-scope __device__ array is zero when the module is
+    // loaded, the kernels only ever OR bits into it, and everything behind it is rewritten by
+    // every call before it is read.
     g_scratch_address[device] = static_cast<uint8_t *>(address);
   }
   *out = g_scratch_address[device];
@@ -1024,6 +1043,26 @@ int32_t static_scratch(ErrorSlot &slot, cudaStream_t stream, uint8_t **out) {
 bool is_aligned(const void *p, uintptr_t a) { return (reinterpret_cast<uintptr_t>(p) & (a - 1)) == 0; }
 
 }  // namespace
+
+// The status line of the built-in scratch array on the current device, after `stream` has
+// finished: 0 when b200q_nvfp4_linear_noalloc has not run on this device yet.
+int32_t w4a4_noalloc_status(ErrorSlot &slot, cudaStream_t stream, uint32_t *status) {
+  *status = 0;
+  int device = -1;
+  cudaError_t err = cudaGetDevice(&device);
+  if (err != cudaSuccess) return fail(slot, "b200q_nvfp4_device_status: no CUDA device: %s", cudaGetErrorString(err));
+  const uint8_t *address = nullptr;
+  if (device >= 0 && device < kMaxScratchDevices) {
+    std::lock_guard<std::mutex> lock(g_scratch_mutex);
+    address = g_scratch_address[device];
+  }
+  if (address == nullptr) return 0;
+  err = cudaMemcpyAsync(status, address, sizeof(uint32_t), cudaMemcpyDeviceToHost, stream);
+  if (err == cudaSuccess) err = cudaStreamSynchronize(stream);
+  if (err != cudaSuccess) return fail(slot, "b200q_nvfp4_device_status: %s", cudaGetErrorString(err));
+  return 0;
+}
+
 }  // namespace b200q
 
 extern "C" int32_t b200q_nvfp4_linear_noalloc(const b200q_nvfp4_weight *w, const void *x, uint32_t tokens, void *y,
@@ -1054,7 +1093,7 @@ extern "C" int32_t b200q_nvfp4_linear_noalloc(const b200q_nvfp4_weight *w, const
   if (dev == nullptr) return -1;
   if (!dev->prepared) return fail(slot, "%s: the device was not prepared (call b200q_nvfp4_prepare at load)", what);
   uint8_t *scratch = nullptr;
-  if (static_scratch(slot, static_cast<cudaStream_t>(stream), &scratch) != 0) return -1;
+  if (static_scratch(slot, &scratch) != 0) return -1;
   return w4a4_launch(slot, *dev, static_cast<const uint8_t *>(w->codes), static_cast<const uint8_t *>(w->scales), w->n, w->k,
                      w->weight_scale_divisor, w->input_scale_divisor, static_cast<const uint16_t *>(x), tokens, y, ldy,
                      epilogue, scratch, static_cast<cudaStream_t>(stream));

@@ -18,10 +18,10 @@
 namespace b200q {
 namespace {
 
-constexpr uint32_t kBarrierPolls = 1u << 22;  // with the sleep below, about two seconds
-
+// `polls`: how often a thread looks at its flag before it gives up; with the sleep below the
+// default (2^22, B200Q_PEER_BARRIER_POLLS at prepare) is about two seconds.
 __global__ void __launch_bounds__(32) peer_barrier_kernel(uint32_t *const *flags_peers, uint32_t peers, uint32_t rank,
-                                                          uint32_t epoch, uint32_t *status) {
+                                                          uint32_t epoch, uint32_t *status, uint32_t polls) {
   griddep_launch_dependents();
   griddep_wait();  // the product before this kernel has finished and flushed its stores
   const uint32_t s = threadIdx.x;
@@ -32,14 +32,11 @@ __global__ void __launch_bounds__(32) peer_barrier_kernel(uint32_t *const *flags
   }
   if (s >= peers) return;
   __threadfence_system();
-  uint32_t *theirs = flags_peers[s] + rank;
-  asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(theirs), "r"(epoch) : "memory");
-  const uint32_t *mine = flags_peers[rank] + s;
+  st_release_sys(flags_peers[s] + rank, epoch);
   bool seen = false;
-  for (uint32_t poll = 0; poll < kBarrierPolls; ++poll) {
-    uint32_t v;
-    asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(mine) : "memory");
-    if (static_cast<int32_t>(v - epoch) >= 0) {
+  const uint32_t *mine = flags_peers[rank] + s;
+  for (uint32_t poll = 0; poll < polls; ++poll) {
+    if (static_cast<int32_t>(ld_acquire_sys(mine) - epoch) >= 0) {
       seen = true;
       break;
     }
@@ -62,7 +59,7 @@ extern "C" int32_t b200q_peer_barrier(uint32_t *const *flags_peers, uint32_t pee
   if (dev == nullptr) return -1;
   if (!dev->prepared) return fail(slot, "b200q_peer_barrier: the device was not prepared (call b200q_nvfp4_prepare at load)");
   const cudaError_t err = launch(peer_barrier_kernel, dim3(1), dim3(32), 0, static_cast<cudaStream_t>(stream), dev->pdl != 0,
-                                 flags_peers, peers, rank, epoch, status);
+                                 flags_peers, peers, rank, epoch, status, static_cast<uint32_t>(dev->peer_barrier_polls));
   if (err != cudaSuccess) return fail(slot, "b200q_peer_barrier: launch failed: %s", cudaGetErrorString(err));
   return 0;
 }

@@ -187,17 +187,25 @@ def experts_tokens(rows: torch.Tensor, local_ids: torch.Tensor, row_weights: tor
 
 
 def fp8_row_scale_payload(w: torch.Tensor) -> np.ndarray:
-    """A [rows, cols] float weight as an FP8 row-scale payload: E4M3FN codes, zero padding to 256
-    bytes, BF16 scales (kernel/include/ignis_fp8_linear.h:4-10)."""
+    """A [rows, cols] float weight as an `FP8_E4M3FN_ROW_BF16S` / `row-scale-v1` payload: E4M3FN
+    codes [rows][cols] row-major, zero padding to a multiple of 256 bytes, BF16 scales [rows]
+    (kernel/include/ignis_fp8_linear.h:4-10, docs/formats/flash-next-layout.md section 6.1). The
+    encoding rule is the reference converter's (tools/flash-next-converter/fp8.py:14-41): a row's
+    scale is amax / 448 rounded UP to the next BF16 (no code saturates), 1.0 for an all-zero row,
+    and the codes are the round-to-nearest-even E4M3FN of w / scale."""
     w = w.float()
-    amax = w.abs().amax(dim=1).clamp(min=1e-30)
-    scale = (amax / 448.0).to(torch.bfloat16)
-    codes = (w / scale.float().unsqueeze(1)).clamp(-448, 448).to(torch.float8_e4m3fn).view(torch.uint8).numpy()
     rows, cols = w.shape
+    amax = w.abs().amax(dim=1)
+    target = amax / 448.0
+    scale = target.to(torch.bfloat16)
+    bits = scale.view(torch.int16)
+    scale = torch.where(scale.float() < target, bits + 1, bits).view(torch.bfloat16)
+    scale = torch.where(amax > 0, scale, torch.ones_like(scale))
+    codes = (w / scale.float().unsqueeze(1)).clamp(-448, 448).to(torch.float8_e4m3fn).view(torch.uint8).numpy()
     pad = (rows * cols + 255) // 256 * 256
     out = np.zeros(pad + 2 * rows, np.uint8)
     out[: rows * cols] = codes.reshape(-1)
-    out[pad:] = scale.view(torch.int16).numpy().view(np.uint8)
+    out[pad:] = scale.contiguous().view(torch.int16).numpy().view(np.uint8)
     return out
 
 

@@ -104,13 +104,26 @@ def combine(row_acc: torch.Tensor, plan: Dispatch, group=None) -> torch.Tensor:
 
 
 def routed_experts(x: torch.Tensor, ids: torch.Tensor, weights: torch.Tensor, experts: int,
-                   run_local: Callable[[torch.Tensor, torch.Tensor, torch.Tensor], torch.Tensor], group=None) -> torch.Tensor:
+                   run_local: Callable[[torch.Tensor, torch.Tensor, torch.Tensor], torch.Tensor], group=None,
+                   phases: dict | None = None) -> torch.Tensor:
     """dispatch -> `run_local(rows, local_ids, row_weights)` -> combine. `run_local` returns, per
     received token, the weighted sum of its owned experts as int64 fixed point ``[r, hidden]`` (on a
-    GPU: the routed accumulator of ``ignis_moe_experts_prefill`` over the rank's own slot table)."""
+    GPU: the routed accumulator of ``ignis_moe_experts_prefill`` over the rank's own slot table).
+    `phases["events"]`, when given, is four CUDA events recorded on the current stream before the
+    dispatch, before and after the local experts, and after the combine (a measurement hook)."""
+    events = phases.get("events") if phases else None
+    if events:
+        events[0].record()
     rows, local, wrow, plan = dispatch(x, ids, weights, experts, group)
+    if events:
+        events[1].record()
     if rows.shape[0]:
         row_acc = run_local(rows, local, wrow)
     else:
         row_acc = torch.zeros((0, x.shape[1]), dtype=torch.int64, device=x.device)
-    return combine(row_acc, plan, group)
+    if events:
+        events[2].record()
+    acc = combine(row_acc, plan, group)
+    if events:
+        events[3].record()
+    return acc

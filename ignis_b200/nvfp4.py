@@ -256,6 +256,24 @@ def linear_group_scatter(x: torch.Tensor, weights: list[Weight], peer_ptrs: list
     _check(_lib.load().b200q_nvfp4_linear_group_scatter(wp, count, x.data_ptr(), x.shape[0], yp, peers, ld, co, epilogue, _stream()))
 
 
+def linear_group_gather(x: torch.Tensor, weights: list[Weight], peer_ptrs: list[list[int]], ldy: list[int],
+                        col_offset: list[int], wait_for=None, signal=None, epilogue: int = STORE) -> None:
+    """``b200q_nvfp4_linear_group_gather``: :func:`linear_group_scatter` with the all-gather's barrier
+    folded in. `wait_for` / `signal` are ``_lib.PeerSync`` structs (``shard.PeerOutputs.sync``) or
+    None: the call waits, before it reads `x`, until every rank has published the point that
+    produced `x`, and publishes its own point when its stores into all ranks' buffers are done."""
+    _check_x(x, weights[0].k)
+    count, peers = len(weights), len(peer_ptrs[0])
+    structs = [w.c_struct() for w in weights]
+    wp = (C.POINTER(_lib.Nvfp4Weight) * count)(*[C.pointer(s) for s in structs])
+    yp = (C.c_void_p * (count * peers))(*[ptr for row in peer_ptrs for ptr in row])
+    ld = (C.c_uint32 * count)(*ldy)
+    co = (C.c_uint32 * count)(*col_offset)
+    _check(_lib.load().b200q_nvfp4_linear_group_gather(wp, count, x.data_ptr(), x.shape[0], yp, peers, ld, co, epilogue,
+                                                        C.byref(wait_for) if wait_for is not None else None,
+                                                        C.byref(signal) if signal is not None else None, _stream()))
+
+
 def peer_barrier(flags_peers: torch.Tensor, peers: int, rank: int, epoch: int, status: torch.Tensor) -> None:
     """``b200q_peer_barrier``: `flags_peers` is a device int64 tensor of the ranks' flag-array addresses."""
     _check(_lib.load().b200q_peer_barrier(flags_peers.data_ptr(), peers, rank, epoch, status.data_ptr(), _stream()))
@@ -311,3 +329,49 @@ def quantize_activations(x: torch.Tensor, input_scale_divisor: float) -> tuple[t
     _check(_lib.load().b200q_nvfp4_quantize_activations(x.data_ptr(), tokens, k, float(input_scale_divisor),
                                                          codes.data_ptr(), scales.data_ptr(), _stream()))
     return codes, scales
+
+
+def quantize_operand(x_rows: torch.Tensor, tokens_total: int, token_begin: int, k: int, input_scale_divisor: float,
+                     workspace: Workspace) -> None:
+    """``b200q_nvfp4_quantize_operand``: the rows of `x_rows` (BF16 ``[count, k]``, tokens
+    ``token_begin ..`` of a call of `tokens_total`) into their place of the W4A4 operand in `workspace`."""
+    _check_x(x_rows, k)
+    _check(_lib.load().b200q_nvfp4_quantize_operand(x_rows.data_ptr(), tokens_total, token_begin, x_rows.shape[0], k,
+                                                     float(input_scale_divisor), C.byref(workspace.c), _stream()))
+
+
+def operand_ranges(k: int, tokens_total: int, token_begin: int, token_count: int) -> tuple[tuple[int, int], tuple[int, int]]:
+    """((offset, bytes) of the codes, (offset, bytes) of the scale tiles) of a 128-aligned token range
+    inside a W4A4 operand workspace: what a rank contributes to the all-gather of a token-sharded
+    quantization."""
+    pad_total = (tokens_total + 127) // 128 * 128
+    pad = (token_count + 127) // 128 * 128
+    codes = (256 + token_begin * (k // 2), pad * (k // 2))
+    scales = (256 + pad_total * (k // 2) + (token_begin // 128) * (k // 64) * 512, (pad // 128) * (k // 64) * 512)
+    return codes, scales
+
+
+def linear_prequantized(w: Weight, tokens: int, workspace: Workspace, out: torch.Tensor | None = None,
+                        epilogue: int = STORE) -> torch.Tensor:
+    """``b200q_nvfp4_linear_prequantized``: the tensor-core product over the operand in `workspace`."""
+    y = _out(tokens, w.n, epilogue, out, w.codes.device)
+    ws = w.c_struct()
+    _check(_lib.load().b200q_nvfp4_linear_prequantized(C.byref(ws), tokens, y.data_ptr(), y.stride(0), epilogue,
+                                                        C.byref(workspace.c), _stream()))
+    return y
+
+
+def mma_peak(iterations: int, pair: bool, sink: torch.Tensor | None = None) -> float:
+    """``b200q_nvfp4_mma_peak``: enqueues one launch of the block-scaled FP4 MMA loop over resident
+    operands on the current stream and returns the floating-point operations it performs; the
+    caller times it with CUDA events. `sink` is a float32 tensor of at least one element per SM."""
+    flops = C.c_double(0.0)
+    _check(_lib.load().b200q_nvfp4_mma_peak(int(iterations), 1 if pair else 0, sink.data_ptr() if sink is not None else None,
+                                             sink.numel() if sink is not None else 0, C.byref(flops), _stream()))
+    return float(flops.value)
+
+
+def mma_peak_status() -> int:
+    word = C.c_uint32(0)
+    _check(_lib.load().b200q_nvfp4_mma_peak_status(_stream(), C.byref(word)))
+    return int(word.value)

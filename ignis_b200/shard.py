@@ -42,38 +42,71 @@ def gather_columns(y_shard: torch.Tensor, group=None, out: torch.Tensor | None =
 
 class PeerOutputs:
     """Full-width output buffers of a column-sharded layer, one set per rank, every rank's mapped
-    into every process of the node (``torch.distributed._symmetric_memory``), plus the flag arrays of
-    the device barrier. With them a sharded product stores its columns straight into all ranks'
-    buffers (``nvfp4.linear_group_scatter``) and the all-gather shrinks to ``barrier()``."""
+    into every process of the node (``torch.distributed._symmetric_memory``), plus the flag arrays
+    that order writers and readers. With them a sharded product stores its columns straight into
+    all ranks' buffers and the all-gather shrinks to a flag: either a barrier launch behind the
+    product (``nvfp4.linear_group_scatter`` + :meth:`barrier`) or nothing at all
+    (``nvfp4.linear_group_gather`` with :meth:`sync`: the product's last CTA publishes the point,
+    the consumer's first instructions wait for it).
 
-    def __init__(self, shapes: dict[str, tuple[int, int]], dtype=torch.bfloat16, group=None) -> None:
+    `sets` buffers exist per name; callers alternate them (layer parity) so that a rank which runs
+    ahead never stores into a buffer another rank still reads (see the reuse rule in
+    ``include/b200q_nvfp4.h``). `points` names the rejoin points that get a flag array and a state
+    line of their own (default: one per buffer name)."""
+
+    MAX_POINTS = 28
+
+    def __init__(self, shapes: dict[str, tuple[int, int]], dtype=torch.bfloat16, group=None, sets: int = 1,
+                 points: list[str] | None = None) -> None:
         import torch.distributed._symmetric_memory as symm_mem
+
+        from . import _lib
 
         group = group if group is not None else dist.group.WORLD
         self.rank, self.world = dist.get_rank(group), dist.get_world_size(group)
         if self.world > 8:
             raise ValueError("at most 8 ranks (one node)")
+        self.points = list(points) if points is not None else list(shapes)
+        if len(self.points) > self.MAX_POINTS:
+            raise ValueError(f"at most {self.MAX_POINTS} rejoin points")
+        self.sets = sets
         elem = torch.empty((), dtype=dtype).element_size()
-        self.offsets, at = {}, 512   # [0, 256): the flag array; [256, 512): spare
+        # [0, 64): the flag array of barrier(); [64 (i + 1), 64 (i + 2)): the flag array of point i; buffers from 2048
+        self.offsets, at = {}, 2048
         for name, (tokens, width) in shapes.items():
-            self.offsets[name] = at
-            at += (tokens * width * elem + 255) // 256 * 256
+            for s in range(sets):
+                self.offsets[(name, s)] = at
+                at += (tokens * width * elem + 255) // 256 * 256
         device = torch.device("cuda", torch.cuda.current_device())
         self.arena = symm_mem.empty(at, dtype=torch.uint8, device=device)
         self.arena.zero_()
         handle = symm_mem.rendezvous(self.arena, group)
         self.base = [int(p) for p in handle.buffer_ptrs]
         self._handle = handle
-        self.views = {name: self.arena[off: off + shapes[name][0] * shapes[name][1] * elem].view(dtype).view(shapes[name])
-                      for name, off in self.offsets.items()}
-        self.flags = torch.tensor(self.base, dtype=torch.int64, device=device)   # every rank's flag array is at its base
+        self.views = {}
+        for (name, s), off in self.offsets.items():
+            view = self.arena[off: off + shapes[name][0] * shapes[name][1] * elem].view(dtype).view(shapes[name])
+            self.views[(name, s)] = view
+            if s == 0:
+                self.views[name] = view
+        self.flags = torch.tensor(self.base, dtype=torch.int64, device=device)   # barrier(): every rank's flag array is at its base
         self.status = torch.zeros(2, dtype=torch.int32, device=device)   # [0] ranks that missed a barrier, [1] barriers so far
+        # per point: the ranks' flag arrays (device array of pointers) and this rank's three state words
+        self.point_flags = torch.tensor([[b + 64 * (i + 1) for b in self.base] for i in range(len(self.points))],
+                                        dtype=torch.int64, device=device).reshape(max(1, len(self.points)), self.world)
+        self.point_state = torch.zeros((max(1, len(self.points)), 4), dtype=torch.int32, device=device)
+        self._syncs = {name: _lib.PeerSync(self.point_flags[i].data_ptr(), self.point_state[i].data_ptr(), self.world, self.rank)
+                       for i, name in enumerate(self.points)}
         torch.cuda.synchronize()
         dist.barrier(group)   # every arena is zeroed before anyone publishes a flag
 
-    def pointers(self, name: str) -> list[int]:
-        """The buffer `name` on every rank, as device addresses valid in this process."""
-        return [b + self.offsets[name] for b in self.base]
+    def pointers(self, name: str, which: int = 0) -> list[int]:
+        """Buffer `which` of `name` on every rank, as device addresses valid in this process."""
+        return [b + self.offsets[(name, which)] for b in self.base]
+
+    def sync(self, point: str):
+        """The ``b200q_peer_sync`` of a rejoin point, for ``nvfp4.linear_group_gather``."""
+        return self._syncs[point]
 
     def barrier(self) -> None:
         from . import nvfp4
@@ -81,5 +114,9 @@ class PeerOutputs:
         nvfp4.peer_barrier(self.flags, self.world, self.rank, 0, self.status)   # numbered on the device: graph-safe
 
     def missing(self) -> int:
-        """Bit p set: rank p did not reach some barrier within the device-side limit."""
-        return int(self.status[0].item())
+        """Bit p set: rank p did not reach some barrier, or was missing from some wait, within the
+        device-side limit."""
+        out = int(self.status[0].item())
+        for v in self.point_state[:, 0].tolist():
+            out |= int(v)
+        return out

@@ -146,8 +146,10 @@ int32_t b200q_nvfp4_linear_swiglu(const b200q_nvfp4_weight *gate_up, const void 
  * ranks, on the device, in stream order behind the product. flags_peers is a DEVICE array of
  * `peers` pointers, entry p the flag array (`peers` uint32, zero at start) of rank p, mapped like
  * the buffers. This rank publishes `epoch` in slot `rank` of every array and waits until every
- * slot of its own array has reached it; the wait is bounded (about two seconds), and a wait that
- * runs out sets bit p of status[0] for each rank p that did not arrive. `status` is two uint32 of
+ * slot of its own array has reached it; the wait is bounded (about two seconds; the number of
+ * looks at a flag, 400 ns apart, is read from B200Q_PEER_BARRIER_POLLS at prepare), and a wait that
+ * runs out sets bit p of status[0] for each rank p that did not arrive, after which the kernel
+ * returns and later barriers on the same arrays still work. `status` is two uint32 of
  * this rank's device memory, zero at start; with epoch = 0 the kernel numbers the barrier itself
  * from status[1] (for launches captured in a CUDA graph; every rank must then pass 0 every time). */
 int32_t b200q_nvfp4_linear_group_scatter(const b200q_nvfp4_weight *const *w, uint32_t count, const void *x,
@@ -156,6 +158,43 @@ int32_t b200q_nvfp4_linear_group_scatter(const b200q_nvfp4_weight *const *w, uin
                                          void *stream);
 int32_t b200q_peer_barrier(uint32_t *const *flags_peers, uint32_t peers, uint32_t rank, uint32_t epoch,
                            uint32_t *status, void *stream);
+
+/* The same all-gather with no barrier launch at all: the barrier's two halves ride in the product
+ * that writes a gathered buffer and in the product that reads it. Not in the reference.
+ *
+ * A b200q_peer_sync names one point of a layer where outputs are rejoined (after `o`, after
+ * gate|up, after `down`): flags_peers as for b200q_peer_barrier (a DEVICE array of `peers` pointers,
+ * entry p rank p's flag array of `peers` uint32, zero at start), and `state`, three uint32 of this
+ * rank's device memory, zero at start: [0] bit p set when rank p was missing from a wait that ran
+ * out, [1] how often this rank has published the point, [2] an arrival counter.
+ *   signal:   the call's last CTA - after every CTA's stores into all ranks' buffers are visible -
+ *             adds one to state[1] and stores that number into slot `rank` of every rank's flag
+ *             array (system-scope release).
+ *   wait_for: before the call reads x it waits until every slot of this rank's own flag array has
+ *             reached this rank's state[1]: every rank's shard of x has landed. The wait is bounded
+ *             like b200q_peer_barrier's; when it runs out the call goes on, state[0] says who was
+ *             missing and the output is not valid. The call that publishes a point on this rank
+ *             must precede, in stream order, the call that waits for it.
+ * Either may be NULL; with peers = 1 and both NULL this is b200q_nvfp4_linear_group. All ranks make
+ * the same sequence of calls. Counting happens on the device, so a captured sequence replays.
+ *
+ * Reuse rule for a gathered buffer: rank A's next product into a buffer may start while rank B
+ * still reads the buffer's previous contents unless something orders them. Give every point TWO
+ * buffers used alternately (layer parity): a rank cannot publish a point for the second time
+ * after a buffer's use before every rank has finished reading that use, because in between it
+ * waits for the other ranks to publish the NEXT point, which they do only after their readers of
+ * this one are done (stream order). The same rule makes b200q_nvfp4_linear_group_scatter +
+ * b200q_peer_barrier safe; with a single buffer per point put a second barrier behind the reader. */
+typedef struct b200q_peer_sync {
+  uint32_t *const *flags_peers;
+  uint32_t *state;
+  uint32_t peers;
+  uint32_t rank;
+} b200q_peer_sync;
+int32_t b200q_nvfp4_linear_group_gather(const b200q_nvfp4_weight *const *w, uint32_t count, const void *x,
+                                        uint32_t tokens, void *const *y_peers, uint32_t peers, const uint32_t *ldy,
+                                        const uint32_t *col_offset, uint32_t epilogue,
+                                        const b200q_peer_sync *wait_for, const b200q_peer_sync *signal, void *stream);
 
 /* The layers' MLP: y (+)= down(silu(g) * u), g | u = gate_up x. reference:
  * ignis::prefill_swiglu::mlp (kernel/src/prefill_swiglu.h:100-107) and, below its widths, the
@@ -186,6 +225,28 @@ int32_t b200q_nvfp4_quantize_activations(const void *x, uint32_t tokens, uint32_
                                          float input_scale_divisor, void *codes, void *scales,
                                          void *stream);
 
+/* The W4A4 route in its two halves, for callers that share the quantized operand: several products
+ * over one x, or token-sharded quantization across the GPUs of a node (each rank quantizes its
+ * tokens, the ranks all-gather the operand's bytes, every rank multiplies its row shard). Not in
+ * the reference, whose fused ops quantize inside one call (nvfp4_w4a4.cu:74-110).
+ *
+ * The operand of a call of `tokens_total` tokens at `k` lives in a workspace of
+ * b200q_nvfp4_workspace_bytes(n, k, B200Q_NVFP4_ALLOW_A4, tokens_total) bytes (any n): 256 bytes of
+ * status, the codes [ceil128(tokens_total)][k / 2], then the scales as 512-byte tiles of (128 tokens
+ * x 4 groups), token tile major. b200q_nvfp4_quantize_operand writes tokens [token_begin,
+ * token_begin + token_count) of it from `x_rows` (the first of those tokens; BF16 [token_count][k]):
+ * token_begin a multiple of 128, token_count a multiple of 128 unless the range is the call's last
+ * (whose padding rows are written as zeros). The bytes of a token range are therefore two
+ * contiguous pieces: codes at 256 + token_begin k / 2, scales at 256 + ceil128(tokens_total) k / 2
+ * + (token_begin / 128) (k / 64) 512. b200q_nvfp4_linear_prequantized is the product over a complete
+ * operand: the result of b200q_nvfp4_linear under B200Q_NVFP4_ALLOW_A4 on the tensor-core route, bit
+ * for bit, for any token count. */
+int32_t b200q_nvfp4_quantize_operand(const void *x_rows, uint32_t tokens_total, uint32_t token_begin,
+                                     uint32_t token_count, uint32_t k, float input_scale_divisor,
+                                     const b200q_nvfp4_workspace *workspace, void *stream);
+int32_t b200q_nvfp4_linear_prequantized(const b200q_nvfp4_weight *w, uint32_t tokens, void *y, uint32_t ldy,
+                                        uint32_t epilogue, const b200q_nvfp4_workspace *workspace, void *stream);
+
 /* The tensor-core W4A4 linear without any caller-supplied scratch. No counterpart in the
  * reference: its ops always take a workspace the load reserved.
  *
@@ -202,19 +263,36 @@ int32_t b200q_nvfp4_quantize_activations(const void *x, uint32_t tokens, uint32_
  * STORE only, k a multiple of 256, y 16-byte aligned, ldy a multiple of 8.
  * Limit: 256 + ceil128(tokens) * k * 9 / 16 bytes must fit the array (for example 2048 tokens at
  * k = 5120, 512 tokens at k = 17408); larger calls return -1 and say so.
- * The first call on a device looks the array's address up and clears its status line; make that
- * first call outside any stream capture. All calls on a device share the one array and it keeps
- * the previous call's contents (each call rewrites all it reads), so two calls whose kernels
- * overlap on the GPU - different streams, no ordering between them - race; order them. */
+ * The first call on a device looks the array's address up (cudaGetSymbolAddress, once per device,
+ * with that device current); make that first call outside any stream capture. The array's first
+ * 256 bytes are the status line of these calls: zero when the library is loaded, kernels only OR
+ * bits into it when a bounded device-side wait runs out (the output of that call is then not
+ * valid), and b200q_nvfp4_device_status reports it. All calls on a device share the one array and
+ * it keeps the previous call's contents (each call rewrites all it reads), so two calls whose
+ * kernels overlap on the GPU - different streams, no ordering between them - race; order them. */
 #define B200Q_NVFP4_NOALLOC_SCRATCH_BYTES (6u << 20)
 int32_t b200q_nvfp4_linear_noalloc(const b200q_nvfp4_weight *w, const void *x, uint32_t tokens, void *y,
                                    uint32_t ldy, uint32_t epilogue, void *stream);
 
-/* The status word of the kernels that take no workspace (A16 calls of more than 8 tokens run on the
- * tensor cores with bounded device-side waits): copied to *status after `stream` has finished. 0
- * unless a wait ran out, in which case that call's output is not valid. The word is per device and
- * sticky. */
+/* The status word of the kernels that take no workspace - A16 calls of more than 16 tokens and
+ * B200Q_NVFP4_ALLOW_A4 calls of up to 32 tokens run on the tensor cores with bounded device-side
+ * waits - OR-ed with the status line of b200q_nvfp4_linear_noalloc's built-in scratch (bits 0..2 as
+ * in b200q_nvfp4_workspace_status): copied to *status after `stream` has finished. 0 unless a wait
+ * ran out, in which case that call's output is not valid. The word is per device and sticky. */
 int32_t b200q_nvfp4_device_status(void *stream, uint32_t *status);
+
+/* Measurement, not serving: the tensor cores' block-scaled FP4 rate on this device, the denominator
+ * the W4A4 prefill GEMM is reported against. Stands where the reference measures its card's MMA
+ * peak with a loop over resident operands (kernel/tests/bench_mma_peak.cu:1-25). One launch: every
+ * SM (pair = 0: one CTA per SM, M 128 x N 256 x K 64; pair = 1: clusters of two CTAs, cta_group::2,
+ * M 256 x N 256 x K 64) issues `iterations` stages of four tcgen05.mma kind::mxf4nvf4 block_scale
+ * MMAs over operands that stay in shared and tensor memory; no global traffic. The caller times the
+ * launch on `stream`; *flops receives the floating-point operations it performs. `sink` (device,
+ * at least one float per CTA: pass the SM count) receives one accumulator word per CTA, or NULL.
+ * b200q_nvfp4_mma_peak_status reads the kernel's status word (non-zero: a bounded wait ran out). */
+int32_t b200q_nvfp4_mma_peak(uint32_t iterations, uint32_t pair, float *sink, uint32_t sink_count, double *flops,
+                             void *stream);
+int32_t b200q_nvfp4_mma_peak_status(void *stream, uint32_t *status);
 
 /* Thread-local message from the most recent failed call. Never NULL. */
 const char *b200q_nvfp4_last_error(void);

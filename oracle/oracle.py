@@ -162,6 +162,111 @@ class Oracle:
         return y
 
 
+# ---- numpy restatements (no C needed: array arithmetic) ------------------------------------------
+
+def hash_uniform_array(stream: int, n: int, amplitude: float) -> np.ndarray:
+    """float32 [n]: element i is ((lowbias32(i * 0x9E3779B9 + stream * 0x85EBCA6B) >> 8) * 2^-23 - 1)
+    * amplitude, every step in float32 (kernel/tests/moe_fixture.h:129-146)."""
+    i = np.arange(n, dtype=np.uint64)
+    x = (i * np.uint64(0x9E3779B9) + np.uint64(stream) * np.uint64(0x85EBCA6B)) & np.uint64(0xFFFFFFFF)
+    x ^= x >> np.uint64(16)
+    x = (x * np.uint64(0x7FEB352D)) & np.uint64(0xFFFFFFFF)
+    x ^= x >> np.uint64(15)
+    x = (x * np.uint64(0x846CA68B)) & np.uint64(0xFFFFFFFF)
+    x ^= x >> np.uint64(16)
+    u = (x >> np.uint64(8)).astype(np.float32) * np.float32(2.0 ** -23) - np.float32(1.0)
+    return u * np.float32(amplitude)
+
+
+def f32_to_bf16_bits(v: np.ndarray) -> np.ndarray:
+    """Round to nearest even, finite inputs (kernel/tests/moe_fixture.h: f32_to_bf16)."""
+    b = np.ascontiguousarray(v, np.float32).view(np.uint32).astype(np.uint64)
+    return ((b + np.uint64(0x7FFF) + ((b >> np.uint64(16)) & np.uint64(1))) >> np.uint64(16)).astype(np.uint16)
+
+
+def bf16_bits_to_f32(b: np.ndarray) -> np.ndarray:
+    return (np.ascontiguousarray(b, np.uint16).astype(np.uint32) << np.uint32(16)).view(np.float32)
+
+
+def moe_router(x_bf16_bits: np.ndarray, w_bf16_bits: np.ndarray, top_k: int):
+    """The router's contract (kernel/include/ignis_moe.h:83-95) in float64: logits = x . W^T, rounded
+    once to BF16; the top_k largest BF16 logits, ties to the lower id, in descending order; their
+    softmax rounded to BF16. Returns (logits float64 [t][e], logit BF16 bits, ids int32 [t][top_k],
+    weight BF16 bits [t][top_k])."""
+    x = bf16_bits_to_f32(x_bf16_bits).astype(np.float64)
+    w = bf16_bits_to_f32(w_bf16_bits).astype(np.float64)
+    logits = x @ w.T
+    rounded_bits = f32_to_bf16_bits(logits.astype(np.float32))
+    rounded = bf16_bits_to_f32(rounded_bits).astype(np.float64)
+    order = np.argsort(-rounded, axis=1, kind="stable")[:, :top_k]     # stable: equal values keep id order
+    top = np.take_along_axis(rounded, order, axis=1)
+    e = np.exp(top - top[:, :1])
+    weights = f32_to_bf16_bits((e / e.sum(axis=1, keepdims=True)).astype(np.float32))
+    return logits, rounded_bits, order.astype(np.int32), weights
+
+
+_F16_LUT = None
+
+
+def f16_bits_to_f64(bits: np.ndarray) -> np.ndarray:
+    global _F16_LUT
+    if _F16_LUT is None:
+        _F16_LUT = np.arange(65536, dtype=np.uint16).view(np.float16).astype(np.float64)
+    return _F16_LUT[np.ascontiguousarray(bits, np.uint16)]
+
+
+def hadamard128_rows(v: np.ndarray) -> np.ndarray:
+    """Every 128-block of every row times the Sylvester Hadamard / sqrt(128), natural order
+    (kernel/tests/moe_fixture.h:331-345), float64."""
+    rows, n = v.shape
+    a = v.reshape(rows, n // 128, 128).copy()
+    h = 1
+    while h < 128:
+        a = a.reshape(rows, n // 128, 128 // (2 * h), 2, h)
+        a = np.stack([a[:, :, :, 0] + a[:, :, :, 1], a[:, :, :, 0] - a[:, :, :, 1]], axis=3)
+        h *= 2
+    return a.reshape(rows, n) * (1.0 / np.sqrt(128.0))
+
+
+def trellis_project_rows(inner: np.ndarray, suh: np.ndarray, svh: np.ndarray, x: np.ndarray, chunk: int = 1024):
+    """The dense trellis product for many tokens at once, and the scale its tolerance is stated in:
+    y = had(had(x o suh) . inner) o svh in float64 (kernel/tests/moe_fixture.h:348-361, the formula of
+    orc_trellis_project as matrix products over column chunks), and s[t][j] = |svh_j| times the
+    root mean square over j's 128-block of sqrt(sum_k (x'_k inner_kj)^2)
+    (kernel/include/ignis_trellis_linear.h:32-44, kernel/tests/trellis_test_common.h:165-189).
+    inner [in][out] fp16 bits, suh / svh fp16 bits, x [t][in] float64. Returns (y, s)."""
+    in_, out = inner.shape
+    xs = hadamard128_rows(np.ascontiguousarray(x, np.float64) * f16_bits_to_f64(suh)[None, :])
+    xs2 = xs * xs
+    z = np.empty((x.shape[0], out))
+    sq = np.empty((x.shape[0], out))
+    for c0 in range(0, out, chunk):
+        w = f16_bits_to_f64(inner[:, c0: c0 + chunk])
+        z[:, c0: c0 + chunk] = xs @ w
+        sq[:, c0: c0 + chunk] = xs2 @ (w * w)
+    sv = f16_bits_to_f64(svh)
+    y = hadamard128_rows(z) * sv[None, :]
+    block_rms = np.sqrt(sq.reshape(x.shape[0], out // 128, 128).mean(axis=2))
+    return y, np.abs(sv)[None, :] * np.repeat(block_rms, 128, axis=1)
+
+
+def fp8_row_scale_decode(payload: np.ndarray, rows: int, cols: int) -> np.ndarray:
+    """float64 [rows][cols] = e4m3fn(code) * bf16(scale) of an `FP8_E4M3FN_ROW_BF16S` / `row-scale-v1`
+    payload: codes [rows][cols], zero padding to a multiple of 256 bytes, BF16 scales [rows]
+    (kernel/include/ignis_fp8_linear.h:4-10; docs/formats/flash-next-layout.md section 6.1)."""
+    payload = np.ascontiguousarray(payload, np.uint8)
+    n = rows * cols
+    off = (n + 255) // 256 * 256
+    codes = payload[:n].astype(np.int32)
+    sign = np.where(codes & 0x80, -1.0, 1.0)
+    exp = (codes >> 3) & 0xF
+    man = codes & 7
+    mag = np.where(exp == 0, man * 2.0 ** -9, (1.0 + man / 8.0) * np.exp2(exp.astype(np.float64) - 7.0))
+    mag = np.where((codes & 0x7F) == 0x7F, np.nan, mag)            # E4M3FN's NaN words
+    scale = bf16_bits_to_f32(payload[off: off + 2 * rows].view(np.uint16)).astype(np.float64)
+    return (sign * mag).reshape(rows, cols) * scale[:, None]
+
+
 class Reference:
     """The reference's own host oracle code (oracle/_ref/libref.so)."""
 

@@ -18,6 +18,14 @@ read the files this script writes. Sources of each file:
                          (test_encode.py:16-22), the worked 128 x 64 payload (test_encode.py:25-41),
                          and a seeded random 256 x 128 matrix with its payload and
                          `nvfp4_dequantize` values.
+  moe_router_ref.npz     kernel/tests/fixtures/flash_next/router_ref.bin: transformers' router for the
+                         checkpoint recorded on 192 counter-hash tokens at 512 experts x 2560 (BF16
+                         logits, top-10 ids, BF16 weights; the inputs are regenerated from the hash
+                         streams and amplitudes the record names: test_moe_router.cu:233-245).
+  fp8_row_scale.npz      the reference's FP8 row-scale encoder (tools/flash-next-converter/fp8.py,
+                         imported in place) on seeded weights: the weights (BF16 bits), the
+                         `row-scale-v1` payload bytes `encode` wrote and the BF16 weight `decode`
+                         gives back, plus the payload sizes its test names (test_fp8.py:8-16).
   nvfp4_patterned.npz    the reference's C++ patterned weight (quantized_weight.h:413-456) and its
                          `logical_weight_fp64` values at 256 x 128, produced by oracle/_ref/libref.so
                          (the reference's header compiled in place).
@@ -88,6 +96,34 @@ def checksum_tables() -> None:
     print("checksums:", {k: len(v) for k, v in table.items() if isinstance(v, dict)})
 
 
+def router_fixture() -> None:
+    fx = read_ignfx(os.path.join(REFERENCE, "kernel/tests/fixtures/flash_next/router_ref.bin"))
+    arrays = {k: (v.view(np.uint16) if v.dtype in (np.int16, np.float16) else v) for k, v in fx.items()}
+    np.savez_compressed(os.path.join(HERE, "moe_router_ref.npz"), **arrays)
+    print("router:", {k: (v.dtype.name, v.shape) for k, v in arrays.items()})
+
+
+def fp8_row_scale() -> None:
+    import torch
+
+    sys.path.insert(0, os.path.join(REFERENCE, "tools/flash-next-converter"))
+    import fp8  # the reference's encoder, imported in place
+
+    g = torch.Generator().manual_seed(20261125)
+    wide = (torch.randn(64, 256, generator=g) * torch.logspace(-3, 1, 64)[:, None]).to(torch.bfloat16)
+    wide[7] = 0.0                                    # an all-zero row: scale 1.0, zero codes
+    odd = (torch.randn(48, 100, generator=g) * 0.02).to(torch.bfloat16)   # 4800 code bytes: padded to 4864
+    out = {}
+    for name, w in (("wide", wide), ("odd", odd)):
+        payload = fp8.encode(w)
+        out[f"{name}_weight_bf16"] = w.view(torch.int16).numpy().view(np.uint16)
+        out[f"{name}_payload"] = np.frombuffer(payload, np.uint8)
+        out[f"{name}_decoded_bf16"] = fp8.decode(payload, tuple(w.shape)).view(torch.int16).numpy().view(np.uint16)
+    out["payload_bytes_256x512_48x2560_3x100"] = np.array([fp8.payload_bytes(sh) for sh in ((256, 512), (48, 2560), (3, 100))], np.int64)
+    np.savez_compressed(os.path.join(HERE, "fp8_row_scale.npz"), **out)
+    print("fp8 row scale:", {k: v.shape for k, v in out.items()})
+
+
 def nvfp4_encoder() -> None:
     import torch
 
@@ -135,5 +171,7 @@ def nvfp4_patterned() -> None:
 if __name__ == "__main__":
     trellis_fixtures()
     checksum_tables()
+    router_fixture()
+    fp8_row_scale()
     nvfp4_encoder()
     nvfp4_patterned()

@@ -130,3 +130,50 @@ def test_moe_experts_are_reproducible_and_capturable(oracle):
         assert ws.status() == 0
     finally:
         mo.set_geometry(2560, 640, 512, 10)
+
+
+def test_peer_barrier_gives_up_within_its_limit_and_reports_who_was_missing():
+    """Failure detection without a fault: one GPU plays rank 0 of two, both ranks' flag arrays in
+    its own memory, and nothing ever writes rank 1's flag. With the poll limit set to a few
+    thousand looks (B200Q_PEER_BARRIER_POLLS, read at prepare) the barrier kernel must return by
+    itself with bit 1 of status[0] set, the context stays usable, and a later barrier whose flag
+    is already there passes without touching the status."""
+    import os
+    import time
+
+    from ignis_b200 import nvfp4 as nv
+
+    old = os.environ.get("B200Q_PEER_BARRIER_POLLS")
+    os.environ["B200Q_PEER_BARRIER_POLLS"] = "2000"   # 2000 looks 400 ns apart: under a millisecond
+    try:
+        nv.prepare()
+        mine = torch.zeros(2, dtype=torch.int32, device="cuda")     # rank 0's flag array: slot s is written by rank s
+        theirs = torch.zeros(2, dtype=torch.int32, device="cuda")   # rank 1's
+        flags = torch.tensor([mine.data_ptr(), theirs.data_ptr()], dtype=torch.int64, device="cuda")
+        status = torch.zeros(2, dtype=torch.int32, device="cuda")
+        t0 = time.perf_counter()
+        nv.peer_barrier(flags, 2, 0, 1, status)
+        torch.cuda.synchronize()
+        assert time.perf_counter() - t0 < 1.0
+        assert status.tolist()[0] == 0b10           # rank 1 never arrived; rank 0 (itself) did
+        assert mine.tolist()[0] == 1 and theirs.tolist()[0] == 1   # its own flag went out to both arrays
+        # the epoch goes on after a miss: the next barrier finds rank 1's flag already published
+        status.zero_()
+        mine[1] = 2
+        nv.peer_barrier(flags, 2, 0, 2, status)
+        torch.cuda.synchronize()
+        assert status.tolist()[0] == 0
+        assert mine.tolist() == [2, 2]
+        # numbered on the device (epoch 0, as in a captured graph): barrier 1, 2, ... from status[1]
+        mine.zero_(); theirs.zero_(); status.zero_()
+        mine[1] = 5
+        for _ in range(3):
+            nv.peer_barrier(flags, 2, 0, 0, status)
+        torch.cuda.synchronize()
+        assert status.tolist() == [0, 3] and mine.tolist() == [3, 5]
+    finally:
+        if old is None:
+            del os.environ["B200Q_PEER_BARRIER_POLLS"]
+        else:
+            os.environ["B200Q_PEER_BARRIER_POLLS"] = old
+        nv.prepare()

@@ -123,6 +123,70 @@ def test_reference_geometry_decode_and_prefill_agree(mo, oracle):
     assert torch.equal(again[:tokens], acc[:tokens])   # one arithmetic whichever entry ran it
 
 
+def zipf_routing(tokens, experts, top_k, seed):
+    """configs[4]'s routing: Zipf(1.1) popularity over a seeded permutation of the expert ids, top_k
+    distinct experts per token drawn in proportion to it, weights = BF16(softmax of normal logits)."""
+    cpu = torch.Generator().manual_seed(seed)
+    perm = torch.randperm(experts, generator=cpu)
+    popularity = torch.empty(experts)
+    popularity[perm] = 1.0 / torch.arange(1, experts + 1, dtype=torch.float32) ** 1.1
+    ids = torch.multinomial(popularity.expand(tokens, experts), top_k, replacement=False, generator=cpu).to(torch.int32)
+    w = torch.softmax(torch.randn(tokens, top_k, generator=cpu), dim=1).to(torch.bfloat16).float()
+    return ids.numpy(), w.numpy()
+
+
+@pytest.mark.parametrize("k2s", [(5, 5, 5, 5), (4, 5, 6, 8)])   # configs[4]'s 2.5 bits per weight; the reference's mix of widths
+def test_config4_geometry_under_zipf_routing(mo, oracle, k2s):
+    """BASELINE configs[4]'s geometry - 512 experts of 2048 -> 768 -> 2048, top-10, Zipf(1.1) - at
+    1024 tokens through the prefill entry, the routed sum held to the fp64 reference on a sample of
+    tokens chosen for the shapes of work the skew produces (kernel/tests/test_moe_experts.cu:75-91):
+    the token of one singleton expert, 24 tokens of an expert that fills one 64-row item and part of
+    a second (rows are dealt to items in arrival order, so 24 of at most 128 rows land in both its
+    first and its last item), 16 tokens of the hottest expert (hundreds of rows), and a random rest. Bars: the reference's per-token relative L2 <= 2e-3, max <= 1e-2."""
+    from concurrent.futures import ThreadPoolExecutor
+
+    hidden, inter, experts, top_k, tokens = 2048, 768, 512, 10, 1024
+    mo.set_geometry(hidden, inter, experts, top_k)
+    rng = np.random.default_rng(44)
+    rec = Records(mo, oracle, rng, hidden, inter, experts, k2s=k2s)
+    x = (torch.randn(tokens, hidden, generator=torch.Generator().manual_seed(44)) * 0.5).to(torch.bfloat16)
+    ids, w = zipf_routing(tokens, experts, top_k, 20261129)
+    counts = np.bincount(ids.reshape(-1), minlength=experts)
+    hottest = int(counts.argmax())
+    assert counts[hottest] > 512                      # many 64-row items of one expert
+    singles = np.flatnonzero(counts == 1)
+    two_items = np.flatnonzero((counts > 64) & (counts <= 128))
+    assert singles.size > 0 and two_items.size > 0
+    sample = set(np.flatnonzero((ids == singles[0]).any(axis=1)).tolist())
+    sample |= set(rng.choice(np.flatnonzero((ids == two_items[0]).any(axis=1)), 24, replace=False).tolist())
+    sample |= set(np.flatnonzero((ids == hottest).any(axis=1))[:16].tolist())
+    sample |= set(rng.choice(tokens, 24, replace=False).tolist())
+    sample = sorted(sample)
+    ws = mo.Workspace(8, tokens)
+    acc = mo.experts_prefill(x.cuda(), torch.from_numpy(ids).cuda(), torch.from_numpy(w).cuda(), rec.table, ws)
+    assert ws.status() == 0
+    got = acc[torch.tensor(sample).cuda()].cpu().numpy().astype(np.float64) * 2.0 ** -32
+
+    def one(t):
+        x64 = x[t].double().numpy()
+        out = np.zeros(hidden)
+        for r in range(top_k):
+            out += float(w[t, r]) * rec.expert(oracle, int(ids[t, r]), x64)
+        return out
+
+    with ThreadPoolExecutor(8) as pool:              # the oracle is a C call: the GIL is released
+        ref = np.stack(list(pool.map(one, sample)))
+    for i, t in enumerate(sample):
+        l2 = np.linalg.norm(got[i] - ref[i]) / np.linalg.norm(ref[i])
+        linf = np.abs(got[i] - ref[i]).max() / np.abs(ref[i]).max()
+        assert l2 <= 2e-3 and linf <= 1e-2, (t, l2, linf)
+    # the decode entry's arithmetic on eight of the sampled tokens: the same bits
+    eight = torch.tensor(sample[:8])
+    ws8 = mo.Workspace(8, 8)
+    dec = mo.experts_decode(x[eight].cuda(), torch.from_numpy(ids)[eight].cuda(), torch.from_numpy(w)[eight].cuda(), rec.table, ws8)
+    assert torch.equal(dec[:8], acc[eight.cuda()])
+
+
 def test_absent_records_and_bad_ids_are_skipped_and_reported(mo, oracle):
     mo.set_geometry(256, 128, 8, 2)
     rng = np.random.default_rng(5)
@@ -155,6 +219,84 @@ def test_router_matches_a_torch_model(mo):
         sm = torch.softmax(vals[want], dim=0).to(torch.bfloat16).float()
         assert torch.equal(weights[t].cpu(), sm)
     del order
+
+
+def test_router_against_the_recorded_checkpoint_router(mo, golden):
+    """The reference's own router test at 512 experts x 2560, top-10, on its 192 recorded tokens
+    (kernel/tests/test_moe_router.cu:100-165; fixture kernel/tests/fixtures/flash_next/router_ref.bin
+    = transformers' router of the checkpoint). fp32 logits within 6e-6 sum|x w| of fp64; ids exactly
+    the (BF16 value descending, id ascending) top-10 of the kernel's own logits; weights within BF16's
+    half unit of an fp64 softmax; against the recording: BF16 logits equal for >= 99.9 %, every set
+    difference involves a differing logit, weights equal for >= 99 %."""
+    from oracle import oracle as orc
+
+    mo.set_geometry(2560, 640, 512, 10)
+    g = golden("moe_router_ref.npz")
+    tokens, hidden, experts, top_k, stream_x, stream_w = (int(v) for v in g["geometry"])
+    assert (hidden, experts, top_k) == (2560, 512, 10)
+    xb = orc.f32_to_bf16_bits(orc.hash_uniform_array(stream_x, tokens * hidden, float(g["amplitudes"][0]))).reshape(tokens, hidden)
+    wb = orc.f32_to_bf16_bits(orc.hash_uniform_array(stream_w, experts * hidden, float(g["amplitudes"][1]))).reshape(experts, hidden)
+    x = torch.from_numpy(xb.view(np.int16)).view(torch.bfloat16).cuda()
+    wr = torch.from_numpy(wb.view(np.int16)).view(torch.bfloat16).cuda()
+    ids, weights, logits = mo.router(x, wr)
+    ids, weights, logits = ids.cpu().numpy(), weights.cpu().numpy(), logits.cpu().numpy()
+    l64, _, _, _ = orc.moe_router(xb, wb, top_k)
+    sum_abs = np.abs(orc.bf16_bits_to_f32(xb).astype(np.float64)) @ np.abs(orc.bf16_bits_to_f32(wb).astype(np.float64)).T
+    assert np.all(np.abs(logits - l64) <= 6e-6 * sum_abs)
+    own_bits = orc.f32_to_bf16_bits(logits)
+    own = orc.bf16_bits_to_f32(own_bits).astype(np.float64)
+    order = np.argsort(-own, axis=1, kind="stable")[:, :top_k]
+    assert np.array_equal(ids, order.astype(np.int32))
+    top = np.take_along_axis(own, order, axis=1)
+    soft = np.exp(top - top[:, :1])
+    soft /= soft.sum(axis=1, keepdims=True)
+    assert np.all(np.abs(weights - soft) <= 2.0 ** -8 * soft + 1e-7)
+    assert np.array_equal(weights, orc.bf16_bits_to_f32(orc.f32_to_bf16_bits(weights)))   # stored as BF16 values
+    differs = own_bits != g["logits"]
+    assert differs.sum() * 1000 <= tokens * experts
+    equal = compared = 0
+    for t in range(tokens):
+        a, b = set(ids[t].tolist()), set(g["ids"][t].tolist())
+        if a != b:
+            assert any(differs[t, e] for e in a ^ b), t
+            continue
+        theirs = dict(zip(g["ids"][t].tolist(), g["weights"][t].tolist()))
+        for e, wv in zip(ids[t].tolist(), orc.f32_to_bf16_bits(weights[t]).tolist()):
+            compared += 1
+            equal += int(theirs[e] == wv)
+    assert equal * 100 >= compared * 99
+    # a token's outputs do not depend on how many tokens share the call
+    for first, count in ((5, 1), (5, 3)):
+        pi, pw, _ = mo.router(x[first: first + count].contiguous(), wr)
+        assert np.array_equal(pi.cpu().numpy(), ids[first: first + count]) and np.array_equal(pw.cpu().numpy(), weights[first: first + count])
+
+
+def test_shared_expert_on_payloads_the_reference_encoder_wrote(mo, golden):
+    """The FP8 row-scale shared expert on weights encoded by the reference's own converter
+    (tests/golden/fp8_row_scale.npz, tools/flash-next-converter/fp8.py): gate and up are the same
+    64 x 256 payload, down a 256 x 64 payload encoded here by the byte-identical writer
+    (tests/test_moe_host.py holds it to the recorded bytes). fp64 reference = code x BF16 scale."""
+    from oracle import oracle as orc
+
+    mo.set_geometry(256, 64 * 2, 8, 2)   # inter 128: two stacked copies of the 64-row payload's rows
+    g = golden("fp8_row_scale.npz")
+    w64 = torch.from_numpy(g["wide_weight_bf16"].view(np.int16)).view(torch.bfloat16).float()
+    gate_w = torch.cat([w64, w64.flip(0)])                     # [128, 256]
+    up_w = torch.cat([w64.flip(1), w64])
+    gen = torch.Generator().manual_seed(8)
+    down_w = torch.randn(256, 128, generator=gen) * 0.05
+    payloads = [mo.fp8_row_scale_payload(m) for m in (gate_w, up_w, down_w)]
+    assert np.array_equal(payloads[0][: 64 * 256], g["wide_payload"][: 64 * 256])   # the recorded code plane, row for row
+    dg, du = orc.fp8_row_scale_decode(payloads[0], 128, 256), orc.fp8_row_scale_decode(payloads[1], 128, 256)
+    dd = orc.fp8_row_scale_decode(payloads[2], 256, 128)
+    for tokens in (3, 40):
+        x = (torch.randn(tokens, 256, generator=gen) * 0.3).to(torch.bfloat16)
+        shared, h = mo.shared_expert(*(torch.from_numpy(p).cuda() for p in payloads), x.cuda())
+        gv, uv = x.double().numpy() @ dg.T, x.double().numpy() @ du.T
+        h_ref = gv / (1 + np.exp(-gv)) * uv
+        assert np.all(np.abs(h.double().cpu().numpy() - h_ref) <= 2.0 ** -7 * np.abs(h_ref) + 1e-4 * np.abs(h_ref).max())
+        s_ref = h.double().cpu().numpy() @ dd.T
+        assert np.all(np.abs(shared.double().cpu().numpy() - s_ref) <= 1e-4 * np.abs(s_ref).max() + 1e-6)
 
 
 @pytest.mark.parametrize("tokens", [5, 11, 130])   # up to 8: one warp per row; above: the tensor-core form, ragged token tiles

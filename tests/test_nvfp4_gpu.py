@@ -207,6 +207,63 @@ def test_config2_full_size_sampled(nv, oracle):
     assert torch.equal(back.flip(0), y)
 
 
+def test_config2_down_full_size_sampled(nv, oracle):
+    """BASELINE configs[2]'s second product at its full size (M = 8192, down 17408 -> 5120, W4A4):
+    sampled row tiles x tokens against the host arithmetic (first, last and interior tiles of both
+    dimensions; K = 17408 is 68 stages of the ring), and the token-reversal property."""
+    tokens, n, k = 8192, 5120, 17408
+    rng = np.random.default_rng(22)
+    codes, scales, d_w = make_weight(rng, n, k)
+    d_in = 448.0
+    w = nv.Weight.from_planes(codes, scales, d_w, d_in)
+    x = torch.randn(tokens, k, generator=torch.Generator().manual_seed(22)).to(torch.bfloat16)
+    ws = nv.Workspace(nv.workspace_bytes(n, k, nv.ALLOW_A4, tokens))
+    xd = x.cuda()
+    y = nv.linear(xd, w, policy=nv.ALLOW_A4, workspace=ws)
+    assert ws.status() == 0
+    natural = nv.unswizzle_scales(scales, n, k)
+    picks = torch.tensor([0, 1, 127, 128, 255, 256, 4095, 4096, 5000, 8063, 8064, 8191])
+    for tile in (0, 1, 19, 20, 39):
+        rows = slice(tile * 128, tile * 128 + 128)
+        ref = w4a4_reference(oracle, codes[rows], nv.swizzle_scales(natural[rows]), 128, k, d_w, d_in, x[picks])
+        check_bf16(y[picks.cuda()][:, rows], ref)
+    back = nv.linear(xd.flip(0).contiguous(), w, policy=nv.ALLOW_A4, workspace=ws)
+    assert ws.status() == 0
+    assert torch.equal(back.flip(0), y)
+
+
+@pytest.mark.parametrize("name,n,k", [("down", 5120, 17408), ("gate_up", 34816, 5120), ("qkv", 8192, 5120)])
+def test_config1_products_full_size_under_a16(nv, oracle, name, n, k):
+    """configs[1]'s widest and longest products at 8 tokens under the A16 policy (the headline
+    benchmark's kernel and launch plans at their real sizes): down 17408 -> 5120, the fused gate|up
+    parent 5120 -> 34816 and q|k|v as one parent, sampled row tiles against the fp64 product of the
+    exactly decoded weights, float32 and BF16 outputs; plus the token-order property."""
+    tokens = 8
+    rng = np.random.default_rng(n + k)
+    codes, scales, d_w = make_weight(rng, n, k)
+    w = nv.Weight.from_planes(codes, scales, d_w)
+    x = torch.randn(tokens, k, generator=torch.Generator().manual_seed(n)).to(torch.bfloat16)
+    y32 = nv.linear(x.cuda(), w, epilogue=nv.OUT_F32)
+    y16 = nv.linear(x.cuda(), w)
+    tiles = sorted({0, 1, n // 256, n // 256 + 1, n // 128 - 1})
+    for tile in tiles:
+        r0, r1 = tile * 128, tile * 128 + 128
+        ref = oracle.gemm_f64(oracle.nvfp4_dequant(codes, scales, n, k, d_w, r0, r1), x.float().numpy())
+        check_f32(y32[:, r0:r1], ref)
+        check_bf16(y16[:, r0:r1], ref)
+    assert torch.equal(nv.linear(x.flip(0).contiguous().cuda(), w).flip(0), y16)
+    if name == "gate_up":   # the grouped call the benchmark makes: two matrices, one launch, the same bits
+        gate, up = w.rows(0, n // 2), w.rows(n // 2, n)
+        pair = nv.linear_group(x.cuda(), [gate, up])
+        h = nv.linear_swiglu(x.cuda(), w)
+        g, u = y32[:, : n // 2].double(), y32[:, n // 2:].double()
+        want = (g / (1 + torch.exp(-g)) * u).cpu().numpy()
+        assert np.all(np.abs(h.double().cpu().numpy() - want) <= 2.0 ** -8 * np.abs(want) + 2e-3 * np.abs(want).max())
+        for part, r0 in zip(pair, (0, n // 2)):
+            ref = oracle.gemm_f64(oracle.nvfp4_dequant(codes, scales, n, k, d_w, r0, r0 + 128), x.float().numpy())
+            check_bf16(part[:, :128], ref)
+
+
 def test_reference_patterned_weight_and_criterion(nv, oracle):
     """The reference's own A16 arm: patterned weight, divisors 0.125 / 3.5, relative L2 and gross
     bounds {2^-8, 2^-8, 2 * 2^-8} (linear_test_common.cpp:29-48, :234-240)."""
@@ -628,3 +685,33 @@ def test_w4a4_one_cta_forms_agree_with_the_pair_form(nv, oracle, tmp_path):
                        env={**os.environ, **switches}, timeout=600)
         assert np.array_equal(np.load(out), here)
 
+
+
+def test_operand_quantized_in_token_ranges_equals_the_one_call_route(nv, oracle):
+    """The W4A4 route in its two halves: the operand quantized range by range (as the ranks of a
+    token-sharded prefill would, each into its own bytes of the workspace), then the product over it,
+    equals b200q_nvfp4_linear under ALLOW_A4 bit for bit; the byte ranges `operand_ranges` names are
+    exactly what a range's quantization writes."""
+    tokens, n, k = 300, 384, 1024
+    rng = np.random.default_rng(71)
+    codes, scales, d_w = make_weight(rng, n, k)
+    w = nv.Weight.from_planes(codes, scales, d_w, 448.0)
+    x = torch.randn(tokens, k, generator=torch.Generator().manual_seed(71)).to(torch.bfloat16).cuda()
+    ws_a = nv.Workspace(nv.workspace_bytes(n, k, nv.ALLOW_A4, tokens))
+    want = nv.linear(x, w, policy=nv.ALLOW_A4, workspace=ws_a)
+    check_bf16(want, w4a4_reference(oracle, codes, scales, n, k, d_w, 448.0, x.cpu()))
+    ws_b = nv.Workspace(nv.workspace_bytes(n, k, nv.ALLOW_A4, tokens))
+    ws_b.buffer[256:].fill_(0xEE)
+    for begin, end in ((128, 256), (0, 128), (256, 300)):      # any order: the ranges are disjoint
+        before = ws_b.buffer.clone()
+        nv.quantize_operand(x[begin:end].contiguous(), tokens, begin, k, 448.0, ws_b)
+        changed = torch.nonzero(before != ws_b.buffer).flatten()
+        (c0, cb), (s0, sb) = nv.operand_ranges(k, tokens, begin, end - begin)
+        inside = ((changed >= c0) & (changed < c0 + cb)) | ((changed >= s0) & (changed < s0 + sb))
+        assert bool(inside.all())
+    assert torch.equal(ws_a.buffer[256:], ws_b.buffer[256:])   # the operand, byte for byte
+    got = nv.linear_prequantized(w, tokens, ws_b)
+    assert ws_b.status() == 0
+    assert torch.equal(got, want)
+    with pytest.raises(nv.Nvfp4Error):
+        nv.quantize_operand(x[64:128].contiguous(), tokens, 64, k, 448.0, ws_b)   # a range must start on a multiple of 128

@@ -258,3 +258,30 @@ def test_trellis_tile_stride_views(oracle):
     view = np.ascontiguousarray(tiles.reshape(-1))[(128 // 16) * 8 * k2:]
     part = oracle.trellis_decode(np.concatenate([view, np.zeros(8 * k2 * 8, np.uint16)]), k2, in_, 128, tile_stride=out // 16)
     assert np.array_equal(part, whole[:, 128:256])
+
+
+def test_matrix_form_of_the_trellis_product_equals_the_token_form(oracle):
+    """oracle.trellis_project_rows (the fp64 product as matrix products over column chunks, used where
+    hundreds of tokens at the 27B's real shapes are checked) against orc_trellis_project, and its
+    tolerance scale against the definition, one output at a time."""
+    from oracle import oracle as orc
+
+    in_, out, k2 = 512, 384, 6
+    rng = np.random.default_rng(12)
+    words = oracle.hash_trellis_words(12, in_, out, k2)
+    inner = oracle.trellis_decode(words, k2, in_, out)
+    suh = (rng.uniform(0.5, 2.0, in_) * 0.05 * rng.choice([-1.0, 1.0], in_)).astype(np.float16).view(np.uint16)
+    svh = (rng.uniform(0.5, 2.0, out) * 0.03 * rng.choice([-1.0, 1.0], out)).astype(np.float16).view(np.uint16)
+    x = rng.standard_normal((5, in_))
+    y, s = orc.trellis_project_rows(inner, suh, svh, x, chunk=128)
+    want = oracle.trellis_project(inner, suh, svh, x)
+    assert np.abs(y - want).max() <= 1e-13 * np.abs(want).max()
+    lut = np.arange(65536, dtype=np.uint16).view(np.float16).astype(np.float64)
+    xs = x * lut[suh][None, :]
+    for t in range(5):
+        oracle.lib.orc_hadamard128(xs[t], in_)
+    w = lut[inner]
+    for t, j in ((0, 0), (2, 130), (4, 383)):
+        blk = j // 128 * 128
+        per_col = np.array([np.sqrt(np.sum((xs[t] * w[:, c]) ** 2)) for c in range(blk, blk + 128)])
+        assert abs(s[t, j] - abs(lut[svh[j]]) * np.sqrt(np.mean(per_col ** 2))) <= 1e-12 * s[t, j]

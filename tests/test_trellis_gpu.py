@@ -229,20 +229,100 @@ def test_group_gives_the_bits_of_separate_calls(tr, oracle, tokens):
         tr.linear_group([ws[0], other], x)   # different `in`
 
 
-def test_full_size_gate_projection(tr, oracle):
-    """configs[3]: 5120 -> 17408 at 3 bits per weight, 8 tokens."""
-    in_, out, k2 = 5120, 17408, 6
-    rng = np.random.default_rng(34)
-    words = oracle.hash_trellis_words(34301, in_, out, k2)
-    suh, svh = make_scales(rng, in_, 0.05), make_scales(rng, out, 0.03)
-    inner = oracle.trellis_decode(words, k2, in_, out)
-    x = torch.randn(8, in_, generator=torch.Generator().manual_seed(34)).to(torch.bfloat16)
+_REAL_SHAPES = {}
+
+
+def real_shape_weight(tr, oracle, in_, out, k2):
+    """A 27B-shaped weight over counter-hash words with hash scales, its decoded inner matrix and the
+    device copy, built once per module (the decode of 89 M weights on the host takes seconds)."""
+    key = (in_, out, k2)
+    if key not in _REAL_SHAPES:
+        rng = np.random.default_rng(in_ + out)
+        words = oracle.hash_trellis_words(34300 + in_ // 128 + out // 128, in_, out, k2)
+        suh, svh = make_scales(rng, in_, 0.05), make_scales(rng, out, 0.03)
+        _REAL_SHAPES[key] = (tr.Weight.from_numpy(words, suh, svh, k2, in_, out), oracle.trellis_decode(words, k2, in_, out), suh, svh)
+    return _REAL_SHAPES[key]
+
+
+def loud_activations(stream, tokens, in_):
+    """BF16 activations with a few loud channels, as a residual stream has: uniform in +-1.5, every
+    channel k with k % 97 == 13 times 24 (kernel/tests/test_trellis_linear.cu:80-89)."""
+    from oracle import oracle as orc
+
+    v = orc.hash_uniform_array(stream, tokens * in_, 1.5).reshape(tokens, in_)
+    v[:, np.arange(in_) % 97 == 13] *= np.float32(24.0)
+    return torch.from_numpy(v).to(torch.bfloat16)
+
+
+def checked_rows(tokens):
+    """The tokens a wide call is checked on: all up to 64, else 16 of every 128-token tile at an
+    offset that moves with the tile, the last tile's ragged rows included
+    (kernel/tests/test_trellis_linear.cu:92-105)."""
+    if tokens <= 64:
+        return list(range(tokens))
+    rows = set()
+    for t0 in range(0, tokens, 128):
+        span = min(128, tokens - t0)
+        rows |= {t0 + (i * 8 + (t0 // 128) * 3) % span for i in range(min(16, span))}
+    return sorted(rows)
+
+
+@pytest.mark.parametrize("in_,out", [(5120, 1024), (6144, 5120), (17408, 5120)])
+@pytest.mark.parametrize("tokens", [16, 64, 65, 130, 1024])
+def test_real_shapes_at_wide_token_counts(tr, oracle, in_, out, tokens):
+    """The reference's wide-token arms (kernel/tests/test_trellis_linear.cu:9-11): three of the 27B's
+    shapes at 3 bits per weight, 16 to 1024 tokens with loud channels, every checked token inside
+    |y - Y| <= 2^-8 |Y| + 2^-9 s of the fp64 product."""
+    from oracle import oracle as orc
+
+    w, inner, suh, svh = real_shape_weight(tr, oracle, in_, out, 6)
+    x = loud_activations(500 + tokens, tokens, in_)
+    y = tr.linear(w, x.cuda())
+    rows = checked_rows(tokens)
+    ref, s = orc.trellis_project_rows(inner, suh, svh, x[rows].double().numpy())
+    check_linear(y[torch.tensor(rows).cuda()], ref, s)
+
+
+@pytest.mark.parametrize("tokens", [64, 130, 300])
+def test_wide_token_epilogues(tr, oracle, tokens):
+    """Residual add and SwiGLU (gate and up of different widths) beyond one pass of 64 tokens
+    (kernel/tests/test_trellis_linear.cu 'epilogues' arm): STORE / ADD against the fp64 product inside
+    the reference's tolerance, SwiGLU within 2^-7 in relative L2 and 2^-6 of the largest output."""
+    from oracle import oracle as orc
+
+    in_, out = 1024, 768
+    rng = np.random.default_rng(tokens)
+    sides = []
+    for stream, k2 in ((61, 6), (62, 8)):
+        words = oracle.hash_trellis_words(stream, in_, out, k2)
+        suh, svh = make_scales(rng, in_, 0.05), make_scales(rng, out, 0.03)
+        sides.append((tr.Weight.from_numpy(words, suh, svh, k2, in_, out), oracle.trellis_decode(words, k2, in_, out), suh, svh))
+    x = loud_activations(700 + tokens, tokens, in_)
     x64 = x.double().numpy()
-    ref = oracle.trellis_project(inner, suh, svh, x64)
-    w = tr.Weight.from_numpy(words, suh, svh, k2, in_, out)
-    got = tr.linear(w, x.cuda()).float().cpu().numpy().astype(np.float64)
-    assert np.linalg.norm(got - ref) <= 2.0 ** -8 * np.linalg.norm(ref)
-    assert np.abs(got - ref).max() <= 4e-3 * np.abs(ref).max()
+    (gate, g_inner, g_suh, g_svh), (up, u_inner, u_suh, u_svh) = sides
+    g64, s = orc.trellis_project_rows(g_inner, g_suh, g_svh, x64)
+    u64, _ = orc.trellis_project_rows(u_inner, u_suh, u_svh, x64)
+    check_linear(tr.linear(gate, x.cuda()), g64, s)
+    base = torch.randn(tokens, out, generator=torch.Generator().manual_seed(tokens)).to(torch.bfloat16)
+    y = tr.linear(gate, x.cuda(), out=base.clone().cuda(), epilogue=tr.ADD)
+    check_linear(y, g64 + base.double().numpy(), s + 2.0 * np.abs(base.double().numpy()))
+    want = g64 / (1.0 + np.exp(-g64)) * u64
+    got = tr.linear_swiglu(gate, up, x.cuda()).float().cpu().numpy().astype(np.float64)
+    assert np.linalg.norm(got - want) <= 2.0 ** -7 * np.linalg.norm(want)
+    assert np.abs(got - want).max() <= 2.0 ** -6 * np.abs(want).max()
+
+
+def test_full_size_gate_projection(tr, oracle):
+    """configs[3]: 5120 -> 17408 at 3 bits per weight, 1 and 8 tokens, every output inside the
+    reference's tolerance."""
+    from oracle import oracle as orc
+
+    in_, out, k2 = 5120, 17408, 6
+    w, inner, suh, svh = real_shape_weight(tr, oracle, in_, out, k2)
+    for tokens in (1, 8):
+        x = torch.randn(tokens, in_, generator=torch.Generator().manual_seed(34 + tokens)).to(torch.bfloat16)
+        ref, s = orc.trellis_project_rows(inner, suh, svh, x.double().numpy())
+        check_linear(tr.linear(w, x.cuda()), ref, s)
 
 
 def test_output_head_shape(tr, oracle):
