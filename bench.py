@@ -560,6 +560,35 @@ def measure_trellis(stream, device, steps: int, warmup: int, peaks: dict, layers
                          "kernel": "trellis_linear_kernel", "traffic": None, "device_status": 0}}
 
 
+def measure_trellis_prefill(stream, device, steps: int, warmup: int, peaks: dict, layers: int = 4, tokens: int = 1024, graph: bool = True) -> dict:
+    """The dense trellis linear beyond 64 tokens (the tensor-core route): configs[3]'s seven shapes at
+    `tokens` tokens over `layers` distinct layers, TFLOP/s of 2 x tokens x in x out."""
+    from ignis_b200 import trellis
+
+    weights, inputs, outputs, _ = build_trellis_workload(layers, tokens, device)
+    by = {name: (in_, out) for name, in_, out in TRELLIS_LAYER}
+    ws = trellis.WorkspaceBuffer(max(trellis.workspace_bytes(in_, out, 1, tokens) for _, in_, out in TRELLIS_LAYER), device)
+    flops = layers * sum(2.0 * tokens * in_ * out for _, in_, out in TRELLIS_LAYER)
+
+    def one_step() -> None:
+        for layer in weights:
+            for name, (in_, _) in by.items():
+                trellis.linear(layer[name], inputs[in_], out=outputs[name], workspace=ws)
+
+    step = graphed(stream, one_step, graph)
+    sampler = ClockSampler(device.index or 0)
+    ms = time_region(stream, step, steps, warmup, sampler=sampler) / steps
+    value = flops / 1e12 / (ms * 1e-3)
+    return {"metric": "trellis_prefill_gemm_tflops", "value": value, "unit": "TFLOP/s", "ms_per_step": ms, "steps": steps, "warmup": warmup,
+            "dtype": "trellis 3 bpw -> f16 x f16 -> f32",
+            "config": {"workload": f"configs[3]'s shapes at M={tokens}: rotation + tcgen05 product per weight, {layers} layers of distinct weights",
+                       "cuda_graph": graph},
+            "gpu_launches": 2 * len(TRELLIS_LAYER) * layers * steps, "clocks": sampler.summary(),
+            "roofline": {"bound": "tensor", "achieved": value, "peak": peaks["bf16_tflops"], "unit": "TFLOP/s", "frac": value / peaks["bf16_tflops"],
+                         "peak_source": f"{peaks['kind']} BF16 cuBLAS burst rate (fp16 operands run at the same rate)",
+                         "kernel": "trellis_tc_dense_kernel", "traffic": None, "device_status": trellis.device_status()}}
+
+
 def measure_head(stream, device, steps: int, warmup: int, peaks: dict, tokens: int, graph: bool = True) -> dict:
     """The output head: 5120 -> 248320 at 4 bits per weight, the largest product of a decode step."""
     import torch
@@ -857,6 +886,9 @@ def run_cuda_arm(args) -> None:
             m1 = measure_trellis(stream, device, side_steps, side_warmup, peaks, tokens=1)
             extras["config3"]["m1"] = {k: m1[k] for k in ("value", "unit", "ms_per_step", "roofline", "gpu_launches")}
             torch.cuda.empty_cache()
+            pf = measure_trellis_prefill(stream, device, side_steps, side_warmup, peaks)
+            extras["config3"]["prefill_m1024"] = {k: pf[k] for k in ("metric", "value", "unit", "ms_per_step", "roofline", "config", "gpu_launches")}
+            torch.cuda.empty_cache()
             extras["config4"] = moe_line(measure_moe(stream, device, side_steps, side_warmup, peaks), side_steps, side_warmup, 1, peaks)
         elif world > 1 and args.extras:
             del weights, step
@@ -1001,6 +1033,9 @@ def run_side_workload(args) -> None:
         elif args.workload == "config0":
             weights, _, _, _ = build_workload(args.layers, 0, 1, 1, device)
             line = {**base, **measure_config0(stream, device, weights, args.steps, args.warmup, peaks, graph=graph)}
+        elif args.workload == "trellis" and args.tokens > 64:
+            line = {**base, **measure_trellis_prefill(stream, device, args.steps, args.warmup, peaks, layers=min(args.layers, 8), tokens=args.tokens,
+                                                      graph=graph)}
         elif args.workload == "head":
             line = {**base, **measure_head(stream, device, args.steps, args.warmup, peaks, args.tokens, graph=graph)}
         else:

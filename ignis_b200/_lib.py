@@ -93,6 +93,7 @@ TRELLIS_SYMBOLS = {
     "ignis_trellis_linear_swiglu": (C.c_int32, [C.POINTER(TrellisWeight), C.POINTER(TrellisWeight), C.c_void_p,
                                                 C.c_uint32, C.c_void_p, C.c_uint32, C.POINTER(Workspace), C.c_void_p]),
     "ignis_trellis_reconstruct": (C.c_int32, [C.POINTER(TrellisWeight), C.c_void_p, C.c_void_p]),
+    "b200q_trellis_device_status": (C.c_int32, [C.c_void_p, C.POINTER(C.c_uint32)]),
     "ignis_trellis_last_error": (C.c_char_p, []),
 }
 

@@ -468,17 +468,22 @@ __global__ void __launch_bounds__(kThreads, NT <= 2 ? 2 : 1) nvfp4_gemv_kernel(c
   }
   cluster_sync_all();  // no CTA leaves while a peer may still read its partial sums
   if (p.signal.flags_peers != nullptr) {
-    // The all-gather's barrier, folded into the product: every CTA makes its stores (into every
-    // rank's buffer) visible system-wide and arrives at a counter; the launch's last CTA numbers the
-    // point and publishes that number in this rank's slot of every rank's flag array.
-    __threadfence_system();
+    // The all-gather's barrier, folded into the product. The CTA's stores (into every rank's buffer)
+    // are ordered before its first thread by the CTA barrier; that one thread makes them visible
+    // system-wide (one fence per CTA: a system-scope fence waits for the peers' acknowledgements,
+    // and hundreds of threads issuing it queue behind each other) and arrives at a counter. The
+    // launch's last CTA numbers the point and publishes the number in this rank's slot of every
+    // rank's flag array.
     __syncthreads();
     if (warp == 0) {
       uint32_t epoch = 0;
-      if (lane == 0 && atomicAdd(p.signal.state + 2, 1u) == gridDim.x - 1u) {
-        atomicExch(p.signal.state + 2, 0u);
-        epoch = atomicAdd(p.signal.state + 1, 1u) + 1u;
+      if (lane == 0) {
         __threadfence_system();
+        if (atomicAdd(p.signal.state + 2, 1u) == gridDim.x - 1u) {
+          atomicExch(p.signal.state + 2, 0u);
+          epoch = atomicAdd(p.signal.state + 1, 1u) + 1u;
+          __threadfence_system();
+        }
       }
       epoch = __shfl_sync(0xFFFFFFFFu, epoch, 0);
       if (epoch != 0u && static_cast<uint32_t>(lane) < p.signal.peers) st_release_sys(p.signal.flags_peers[lane] + p.signal.rank, epoch);

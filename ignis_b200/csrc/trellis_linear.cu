@@ -26,6 +26,7 @@
 #include "../../include/ignis_trellis_linear.h"
 
 #include "trellis_device.cuh"
+#include "trellis_internal.cuh"
 
 namespace b200q {
 namespace {
@@ -491,7 +492,7 @@ cudaError_t set_all_linear_attrs() {
 // SwiGLU call (`up` non-NULL, count 1).
 int32_t run_linear(ErrorSlot &slot, const ignis_trellis_weight *const *w, uint32_t count, const ignis_trellis_weight *up,
                    const void *x, uint32_t tokens, void *const *y, const uint32_t *ldy, uint32_t epilogue, void *stream,
-                   const char *what) {
+                   const char *what, const ignis_trellis_workspace *workspace = nullptr) {
   if (w == nullptr || y == nullptr || ldy == nullptr) return fail(slot, "%s: NULL argument array", what);
   if (count == 0 || count > kMaxGroup) return fail(slot, "%s: count = %u is outside 1..%u", what, count, kMaxGroup);
   const bool swiglu = epilogue == kEpiSwiglu;
@@ -512,6 +513,11 @@ int32_t run_linear(ErrorSlot &slot, const ignis_trellis_weight *const *w, uint32
   if (dev == nullptr) return -1;
   const int sides = swiglu ? 2 : 1;
   const uint32_t in = w[0]->in;
+  // beyond one pass of 64 tokens, with a workspace for the rotated rows: the tensor-core route
+  if (count == 1 && trellis_tc_takes(*dev, in, tokens, static_cast<uint32_t>(sides), workspace)) {
+    return trellis_tc_linear(slot, *dev, w[0], swiglu ? up : nullptr, x, tokens, y[0], ldy[0], epilogue, workspace,
+                             static_cast<cudaStream_t>(stream), what);
+  }
   uint32_t out_total = 0, k2 = w[0]->k2;
   for (uint32_t i = 0; i < count; ++i) {
     out_total += w[i]->out;
@@ -595,7 +601,7 @@ int32_t ignis_trellis_prepare(void) {
   if (prepare_device(slot) != 0) return -1;
   const cudaError_t err = set_all_linear_attrs();
   if (err != cudaSuccess) return fail(slot, "ignis_trellis_prepare: %s", cudaGetErrorString(err));
-  return 0;
+  return trellis_tc_prepare(slot);
 }
 
 uint32_t ignis_trellis_sm_cap(void) {
@@ -608,7 +614,10 @@ uint64_t ignis_trellis_workspace_bytes(uint32_t in, uint32_t out, uint32_t weigh
   if (dev == nullptr || !dev->prepared) return 0;
   if (in == 0 || (in % 128u) != 0 || out == 0 || (out % 128u) != 0 || out > IGNIS_TRELLIS_MAX_OUT) return 0;
   if (weights < 1 || weights > 2 || tokens == 0) return 0;
-  return 256;  // partial sums meet in distributed shared memory: one aligned line, never read
+  // Up to 64 tokens partial sums meet in distributed shared memory: one aligned line, never read.
+  // Beyond, the tensor-core route keeps the rotated activations (fp16 rows and a scale per token) here.
+  if (tokens > IGNIS_TRELLIS_DECODE_MAX_TOKENS) return trellis_tc_workspace_bytes(in, weights, tokens);
+  return 256;
 }
 
 int32_t ignis_trellis_workspace_init(const ignis_trellis_workspace *workspace, void *stream) {
@@ -616,21 +625,21 @@ int32_t ignis_trellis_workspace_init(const ignis_trellis_workspace *workspace, v
   if (workspace == nullptr || workspace->base == nullptr) return fail(slot, "ignis_trellis_workspace_init: workspace is NULL");
   if (!aligned(workspace->base, 256)) return fail(slot, "ignis_trellis_workspace_init: base is not 256-byte aligned");
   if (prepared(slot, "ignis_trellis_workspace_init") == nullptr) return -1;
-  const cudaError_t err = cudaMemsetAsync(workspace->base, 0, workspace->bytes, static_cast<cudaStream_t>(stream));
+  // only the first line carries state; the rest is rewritten by every call that reads it
+  const cudaError_t err = cudaMemsetAsync(workspace->base, 0, workspace->bytes < 256u ? workspace->bytes : 256u, static_cast<cudaStream_t>(stream));
   if (err != cudaSuccess) return fail(slot, "ignis_trellis_workspace_init: %s", cudaGetErrorString(err));
   return 0;
 }
 
 int32_t ignis_trellis_linear(const ignis_trellis_weight *w, const void *x, uint32_t tokens, void *y, uint32_t ldy,
                              uint32_t epilogue, const ignis_trellis_workspace *workspace, void *stream) {
-  (void)workspace;
   if (epilogue != IGNIS_TRELLIS_STORE && epilogue != IGNIS_TRELLIS_ADD) {
     return fail(trellis_error(), "ignis_trellis_linear: unknown epilogue %u", epilogue);
   }
   const ignis_trellis_weight *ws[1] = {w};
   void *ys[1] = {y};
   const uint32_t lds[1] = {ldy};
-  return run_linear(trellis_error(), ws, 1, nullptr, x, tokens, ys, lds, epilogue, stream, "ignis_trellis_linear");
+  return run_linear(trellis_error(), ws, 1, nullptr, x, tokens, ys, lds, epilogue, stream, "ignis_trellis_linear", workspace);
 }
 
 int32_t b200q_trellis_linear_group(const ignis_trellis_weight *const *w, uint32_t count, const void *x, uint32_t tokens,
@@ -644,11 +653,10 @@ int32_t b200q_trellis_linear_group(const ignis_trellis_weight *const *w, uint32_
 int32_t ignis_trellis_linear_swiglu(const ignis_trellis_weight *gate, const ignis_trellis_weight *up, const void *x,
                                     uint32_t tokens, void *h, uint32_t ldh, const ignis_trellis_workspace *workspace,
                                     void *stream) {
-  (void)workspace;
   const ignis_trellis_weight *ws[1] = {gate};
   void *ys[1] = {h};
   const uint32_t lds[1] = {ldh};
-  return run_linear(trellis_error(), ws, 1, up, x, tokens, ys, lds, kEpiSwiglu, stream, "ignis_trellis_linear_swiglu");
+  return run_linear(trellis_error(), ws, 1, up, x, tokens, ys, lds, kEpiSwiglu, stream, "ignis_trellis_linear_swiglu", workspace);
 }
 
 int32_t ignis_trellis_reconstruct(const ignis_trellis_weight *w, void *w_f16, void *stream) {
@@ -656,6 +664,12 @@ int32_t ignis_trellis_reconstruct(const ignis_trellis_weight *w, void *w_f16, vo
   if (w == nullptr) return fail(slot, "ignis_trellis_reconstruct: weight is NULL");
   return trellis_reconstruct_raw(slot, "ignis_trellis_reconstruct", w->trellis, w->k2, w->in, w->out, w->tile_stride, w_f16,
                                  stream);
+}
+
+int32_t b200q_trellis_device_status(void *stream, uint32_t *status) {
+  ErrorSlot &slot = trellis_error();
+  if (status == nullptr) return fail(slot, "b200q_trellis_device_status: status is NULL");
+  return trellis_tc_status(slot, static_cast<cudaStream_t>(stream), status);
 }
 
 const char *ignis_trellis_last_error(void) { return trellis_error().text; }

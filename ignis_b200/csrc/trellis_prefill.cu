@@ -1,0 +1,229 @@
+// Dense trellis linear beyond 64 tokens: the prefill route on the tensor cores.
+//
+// Stands where the reference switches from its decode kernel to its prefill kernel
+// (kernel/src/trellis_linear.cu: rotate_kernel + prefill_kernel, trellis_linear_prefill.cu:162-279;
+// the route needs the workspace, as theirs does). Two launches: `trellis_rotate_rows_kernel` writes
+// the rotated activations as fp16 rows with one scale per token into the workspace, and
+// `trellis_tc_dense_kernel` multiplies them with the trellis plane on tcgen05 (trellis_tc.cuh).
+// SwiGLU runs the gate product first (BF16 into h, as the reference's prefill route stores the gate
+// between its passes: ignis_trellis_linear.h:43-44) and the up product with an epilogue that
+// multiplies by silu of what it finds there.
+#include "../../include/ignis_trellis_linear.h"
+
+#include "trellis_internal.cuh"
+#include "trellis_tc.cuh"
+
+namespace b200q {
+namespace {
+
+using namespace trellis_tc;
+
+__device__ uint32_t g_trellis_tc_status = 0;
+
+// ---- rotation: one CTA per token ------------------------------------------------------------------
+// x o suh, the 128-wide Hadamard per block (a warp per block, fp32), one power-of-two scale for the
+// whole token (largest magnitude in [2^13, 2^14)), fp16. The token's rotated values wait in shared
+// memory between the two passes (4 bytes per input).
+__global__ void __launch_bounds__(256) trellis_rotate_rows_kernel(const uint16_t *x, const uint16_t *suh, uint32_t in,
+                                                                  uint16_t *rows_f16, float *inv) {
+  extern __shared__ __align__(16) float rot[];
+  __shared__ float warp_max[8];
+  griddep_launch_dependents();
+  griddep_wait();
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const uint32_t token = blockIdx.x;
+  const uint32_t nblk = in / 128u;
+  float m = 0.0f;
+  for (uint32_t bl = static_cast<uint32_t>(warp); bl < nblk; bl += 8u) {
+    const size_t k0 = static_cast<size_t>(bl) * 128u + 4u * lane;
+    const uint2 xb = ldg64_coherent(x + static_cast<size_t>(token) * in + k0);
+    const uint2 sb = *reinterpret_cast<const uint2 *>(suh + k0);
+    const __half2 s01 = *reinterpret_cast<const __half2 *>(&sb.x), s23 = *reinterpret_cast<const __half2 *>(&sb.y);
+    float v[4];
+    v[0] = bf16_bits_to_f32(xb.x & 0xFFFFu) * __low2float(s01);
+    v[1] = __uint_as_float(xb.x & 0xFFFF0000u) * __high2float(s01);
+    v[2] = bf16_bits_to_f32(xb.y & 0xFFFFu) * __low2float(s23);
+    v[3] = __uint_as_float(xb.y & 0xFFFF0000u) * __high2float(s23);
+    hadamard128(v, lane);
+    *reinterpret_cast<float4 *>(rot + k0) = make_float4(v[0], v[1], v[2], v[3]);
+    m = fmaxf(m, fmaxf(fmaxf(fabsf(v[0]), fabsf(v[1])), fmaxf(fabsf(v[2]), fabsf(v[3]))));
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xFFFFFFFFu, m, o));
+  if (lane == 0) warp_max[warp] = m;
+  __syncthreads();
+  m = warp_max[0];
+#pragma unroll
+  for (int i = 1; i < 8; ++i) m = fmaxf(m, warp_max[i]);
+  int shift = 0;
+  if (m > 0.0f && m <= 3.0e38f) {
+    int e;
+    (void)frexpf(m, &e);  // m in [2^(e-1), 2^e)
+    shift = max(-126, min(126, 14 - e));
+  }
+  const float scale = ldexpf(1.0f, shift);
+  if (threadIdx.x == 0) inv[token] = ldexpf(1.0f, -shift);
+  uint16_t *dst = rows_f16 + static_cast<size_t>(token) * in;
+  for (uint32_t i = threadIdx.x * 4u; i < in; i += 1024u) {
+    const float4 v = *reinterpret_cast<const float4 *>(rot + i);
+    const __half2 h01 = __floats2half2_rn(v.x * scale, v.y * scale), h23 = __floats2half2_rn(v.z * scale, v.w * scale);
+    uint2 packed;
+    packed.x = *reinterpret_cast<const uint32_t *>(&h01);
+    packed.y = *reinterpret_cast<const uint32_t *>(&h23);
+    *reinterpret_cast<uint2 *>(dst + i) = packed;
+  }
+}
+
+// ---- the product -----------------------------------------------------------------------------------
+constexpr uint32_t kEpiStore = 0, kEpiAdd = 1, kEpiSiluMul = 2;   // kEpiSiluMul: y = BF16(silu(float(y)) * v)
+
+struct DenseParams {
+  const uint32_t *trellis;
+  const uint16_t *svh;
+  const float *inv;      // the tokens' inverse scales
+  uint16_t *y;           // BF16 [tokens][ldy]
+  uint32_t k2, tile_stride, in, out, tokens, ldy, epilogue;
+};
+
+__global__ void __launch_bounds__(kThreads, 1) trellis_tc_dense_kernel(const __grid_constant__ CUtensorMap map_a,
+                                                                      const __grid_constant__ DenseParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  const Core c = core_setup(smem_raw);
+  // Token tiles run fastest over the grid, so the CTAs at work at one time decode the same columns
+  // of the plane (read from HBM once, then from the L2).
+  const uint32_t row_tiles = (p.tokens + 255u) / 256u;
+  const uint32_t col_tile = blockIdx.x / row_tiles, row_tile = blockIdx.x % row_tiles;
+  Job job;
+  job.trellis = p.trellis;
+  job.k2 = p.k2;
+  job.tile_stride = p.tile_stride;
+  job.in = p.in;
+  job.blk0 = 2u * col_tile;
+  job.blk1 = 2u * col_tile + 1u;
+  job.nblk = job.blk1 < p.out / 128u ? 2u : 1u;
+  job.row0 = row_tile * 256u;
+  job.rows = p.tokens - job.row0 < 256u ? p.tokens - job.row0 : 256u;
+  const bool have = core_run(c, job, &map_a, &g_trellis_tc_status);
+  if (have) {
+    // (row tile, block) items dealt to the two groups of four warps; a warp's lanes are the rows
+    // 32 (warp % 4) .. + 31 of the row tile
+    const uint32_t tiles = job.rows > 128u ? 2u : 1u, items = tiles * job.nblk;
+    for (uint32_t item = static_cast<uint32_t>(c.warp) >> 2; item < items; item += 2u) {
+      const uint32_t tt = item / job.nblk, cb = item % job.nblk;
+      const uint32_t token = job.row0 + tt * 128u + (static_cast<uint32_t>(c.warp) & 3u) * 32u + static_cast<uint32_t>(c.lane);
+      float v[128];
+      load_block(c.tmem + (((static_cast<uint32_t>(c.warp) & 3u) * 32u) << 16) + tt * 256u + cb * 128u, v);
+      if (token < p.tokens) {
+        const float inv = p.inv[token];
+#pragma unroll
+        for (int i = 0; i < 128; ++i) v[i] *= inv;
+        hadamard128_regs(v);
+        const uint32_t col0 = (cb == 0u ? job.blk0 : job.blk1) * 128u;
+        const uint2 *sv = reinterpret_cast<const uint2 *>(p.svh + col0);
+        uint2 *dst = reinterpret_cast<uint2 *>(p.y + static_cast<size_t>(token) * p.ldy + col0);
+#pragma unroll
+        for (int q = 0; q < 32; ++q) {
+          const uint2 s = sv[q];
+          const __half2 s01 = *reinterpret_cast<const __half2 *>(&s.x), s23 = *reinterpret_cast<const __half2 *>(&s.y);
+          float r[4] = {v[4 * q] * __low2float(s01), v[4 * q + 1] * __high2float(s01), v[4 * q + 2] * __low2float(s23),
+                        v[4 * q + 3] * __high2float(s23)};
+          if (p.epilogue != kEpiStore) {
+            const uint2 old = dst[q];
+            const float o[4] = {bf16_bits_to_f32(old.x & 0xFFFFu), __uint_as_float(old.x & 0xFFFF0000u),
+                                bf16_bits_to_f32(old.y & 0xFFFFu), __uint_as_float(old.y & 0xFFFF0000u)};
+#pragma unroll
+            for (int e = 0; e < 4; ++e) r[e] = p.epilogue == kEpiAdd ? r[e] + o[e] : o[e] / (1.0f + __expf(-o[e])) * r[e];
+          }
+          const __nv_bfloat162 o01 = __floats2bfloat162_rn(r[0], r[1]), o23 = __floats2bfloat162_rn(r[2], r[3]);
+          uint2 packed;
+          packed.x = *reinterpret_cast<const uint32_t *>(&o01);
+          packed.y = *reinterpret_cast<const uint32_t *>(&o23);
+          dst[q] = packed;
+        }
+      }
+      __syncwarp();   // the accumulator loads of the next item are warp-wide
+    }
+  }
+  core_finish(c);
+}
+
+uint64_t align256(uint64_t v) { return (v + 255u) & ~static_cast<uint64_t>(255u); }
+
+constexpr size_t kRotateMaxSmem = 200 * 1024;   // 4 bytes per input: in <= 51200
+
+bool aligned_to(const void *p, uintptr_t a) { return (reinterpret_cast<uintptr_t>(p) & (a - 1)) == 0; }
+
+}  // namespace
+
+uint64_t trellis_tc_workspace_bytes(uint32_t in, uint32_t weights, uint32_t tokens) {
+  // a status line, then per weight the rotated rows (fp16) and the tokens' inverse scales
+  return 256u + static_cast<uint64_t>(weights) * (align256(static_cast<uint64_t>(tokens) * in * 2u) + align256(static_cast<uint64_t>(tokens) * 4u));
+}
+
+int32_t trellis_tc_prepare(ErrorSlot &slot) {
+  cudaError_t err = cudaFuncSetAttribute(trellis_tc_dense_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(kSmemBytes));
+  if (err == cudaSuccess) {
+    err = cudaFuncSetAttribute(trellis_rotate_rows_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(kRotateMaxSmem));
+  }
+  if (err != cudaSuccess) return fail(slot, "trellis prefill kernel attributes: %s", cudaGetErrorString(err));
+  if (encode_tiled_fn() == nullptr) return fail(slot, "cuTensorMapEncodeTiled is not available from this driver");
+  return 0;
+}
+
+bool trellis_tc_takes(const DeviceState &dev, uint32_t in, uint32_t tokens, uint32_t weights, const ignis_trellis_workspace *workspace) {
+  if (dev.trellis_tc == 0 || tokens <= IGNIS_TRELLIS_DECODE_MAX_TOKENS) return false;
+  if (static_cast<size_t>(in) * 4u > kRotateMaxSmem) return false;
+  if (workspace == nullptr || workspace->base == nullptr || !aligned_to(workspace->base, 256)) return false;
+  return workspace->bytes >= trellis_tc_workspace_bytes(in, weights, tokens);
+}
+
+namespace {
+int32_t one_product(ErrorSlot &slot, const DeviceState &dev, const ignis_trellis_weight *w, const uint16_t *x, uint32_t tokens, uint16_t *y,
+                    uint32_t ldy, uint32_t epilogue, uint8_t *region, cudaStream_t stream, const char *what) {
+  uint16_t *rows = reinterpret_cast<uint16_t *>(region);
+  float *inv = reinterpret_cast<float *>(region + align256(static_cast<uint64_t>(tokens) * w->in * 2u));
+  cudaError_t err = launch(trellis_rotate_rows_kernel, dim3(tokens), dim3(256), static_cast<size_t>(w->in) * 4u, stream, dev.pdl != 0, x,
+                           static_cast<const uint16_t *>(w->suh), w->in, rows, inv);
+  if (err != cudaSuccess) return fail(slot, "%s: rotation launch failed: %s", what, cudaGetErrorString(err));
+  CUtensorMap map_a;
+  if (!make_rows_map(&map_a, rows, tokens, w->in)) return fail(slot, "%s: tensor map encoding failed", what);
+  DenseParams p = {};
+  p.trellis = static_cast<const uint32_t *>(w->trellis);
+  p.svh = static_cast<const uint16_t *>(w->svh);
+  p.inv = inv;
+  p.y = y;
+  p.k2 = w->k2;
+  p.tile_stride = w->tile_stride ? w->tile_stride : w->out / 16u;
+  p.in = w->in;
+  p.out = w->out;
+  p.tokens = tokens;
+  p.ldy = ldy;
+  p.epilogue = epilogue;
+  const uint32_t col_tiles = (w->out + 255u) / 256u, row_tiles = (tokens + 255u) / 256u;
+  err = launch(trellis_tc_dense_kernel, dim3(col_tiles * row_tiles), dim3(kThreads), kSmemBytes, stream, dev.pdl != 0, map_a, p);
+  if (err != cudaSuccess) return fail(slot, "%s: launch failed: %s", what, cudaGetErrorString(err));
+  return 0;
+}
+}  // namespace
+
+int32_t trellis_tc_linear(ErrorSlot &slot, const DeviceState &dev, const ignis_trellis_weight *w, const ignis_trellis_weight *up,
+                          const void *x, uint32_t tokens, void *y, uint32_t ldy, uint32_t epilogue,
+                          const ignis_trellis_workspace *workspace, cudaStream_t stream, const char *what) {
+  uint8_t *base = static_cast<uint8_t *>(workspace->base) + 256;
+  const uint16_t *xs = static_cast<const uint16_t *>(x);
+  uint16_t *ys = static_cast<uint16_t *>(y);
+  if (up == nullptr) return one_product(slot, dev, w, xs, tokens, ys, ldy, epilogue == 1u ? kEpiAdd : kEpiStore, base, stream, what);
+  // SwiGLU: the gate product into h, then the up product times silu of what it finds there
+  if (one_product(slot, dev, w, xs, tokens, ys, ldy, kEpiStore, base, stream, what) != 0) return -1;
+  uint8_t *second = base + align256(static_cast<uint64_t>(tokens) * w->in * 2u) + align256(static_cast<uint64_t>(tokens) * 4u);
+  return one_product(slot, dev, up, xs, tokens, ys, ldy, kEpiSiluMul, second, stream, what);
+}
+
+int32_t trellis_tc_status(ErrorSlot &slot, cudaStream_t stream, uint32_t *status) {
+  cudaError_t err = cudaMemcpyFromSymbolAsync(status, g_trellis_tc_status, sizeof(uint32_t), 0, cudaMemcpyDeviceToHost, stream);
+  if (err == cudaSuccess) err = cudaStreamSynchronize(stream);
+  if (err != cudaSuccess) return fail(slot, "b200q_trellis_device_status: %s", cudaGetErrorString(err));
+  return 0;
+}
+
+}  // namespace b200q

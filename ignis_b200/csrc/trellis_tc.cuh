@@ -1,0 +1,301 @@
+// The trellis products on the 5th-generation tensor cores: the part shared by the dense prefill
+// route (trellis_prefill.cu) and the MoE expert GEMMs (moe_tc.cu).
+//
+// Stands where the reference runs its prefill kernels on warp-level MMAs - trellis tiles decoded
+// from shared memory into mma.sync fragments, fp16 accumulation folded every 32 inputs
+// (kernel/src/trellis_linear_prefill.cu:162-279, kernel/src/moe_prefill.cu:252-421). The design
+// here is not theirs:
+//
+//  * The activations are rotated once by a kernel of their own (x o suh, the 128-wide Hadamard in
+//    fp32) and stored as plain fp16 rows [row][in] with ONE power-of-two scale per row (largest
+//    magnitude in [2^13, 2^14)), so the whole sum over `in` accumulates in tensor memory and the
+//    inverse scale is applied once, in the epilogue. fp16 keeps 11 significant bits of every value
+//    down to 2^-28 of the row's largest; what lies below contributes less than that to any sum.
+//  * A CTA owns up to 256 rows (two MMA tiles of M = 128: the rows are the accumulator's lanes) and
+//    256 output columns (two 128-column Hadamard blocks: the MMA's N), and walks `in` in stages of
+//    64. Eight decoder warps turn the stage's 64 trellis tiles into fp16 in registers (the decode of
+//    trellis_device.cuh: funnel shifts, IMAD, DP4A, half an HFMA2 per weight) and store them into
+//    the stage's B tile in the K-major 128-byte-swizzle layout the tensor core reads: a lane's
+//    eight values are four 4-byte stores that hit 32 different banks across the warp. A producer
+//    thread brings the rows' fp16 activations by TMA (the same swizzle); one thread issues
+//    tcgen05.mma kind::f16 (M 128, N 256, K 16; fp16 x fp16, fp32 accumulation in tensor memory).
+//    Every decoded tile serves both row tiles: 512 accumulator columns, all of tensor memory.
+//  * The epilogue reads a row's 128 accumulator columns of one block into registers, applies the
+//    row's inverse scale, the output Hadamard (in registers: the 128 values of a row and block sit in
+//    one thread), svh and the caller's epilogue.
+//  * Every mbarrier wait is bounded; a wait that runs out sets a bit of a status word and the CTA
+//    falls through to the common exit and frees its tensor memory.
+#ifndef B200Q_TRELLIS_TC_CUH
+#define B200Q_TRELLIS_TC_CUH
+
+#include "nvfp4_tc.cuh"
+#include "trellis_device.cuh"
+
+namespace b200q {
+namespace trellis_tc {
+
+using namespace trellis_dev;
+
+constexpr int kThreads = 320;               // 8 decoder / epilogue warps, the producer warp, the MMA warp
+constexpr int kDecoderWarps = 8;
+constexpr uint32_t kStages = 3;
+constexpr uint32_t kABytes = 128 * 128;     // one row tile of a stage: 128 rows x 64 fp16
+constexpr uint32_t kBBytes = 256 * 128;     // one stage of decoded weights: 256 columns x 64 fp16
+constexpr uint32_t kStageBytes = 2 * kABytes + kBBytes;
+constexpr uint32_t kSmemBytes = kStages * kStageBytes + 256 + 1024;   // + barriers and the tensor-memory slot + alignment slack
+constexpr uint32_t kTmemCols = 512;
+constexpr uint32_t kStatusProducer = 1u, kStatusMma = 2u, kStatusEpilogue = 4u, kStatusDecoder = 8u;
+
+// What one CTA multiplies: rows [row0, row0 + rows) of the rotated activations (rows <= 256) with
+// two 128-column blocks of one trellis plane.
+struct Job {
+  const uint32_t *trellis;  // the plane: tile (tk, tn) at word (tk * tile_stride + tn) * 4 k2
+  uint32_t k2;
+  uint32_t tile_stride;     // tiles per stored row of the plane
+  uint32_t in;              // a multiple of 128
+  uint32_t blk0, blk1;      // the 128-column blocks behind accumulator columns 0..127 and 128..255
+  uint32_t nblk;            // 1: blk1 does not exist (the MMA's N is 128)
+  uint32_t row0, rows;      // row0 is also the TMA row coordinate
+};
+
+// The lane's words of the 8 tiles a decoder warp owns in one stage: 2 tile columns x 4 tile rows.
+struct StageWords {
+  uint32_t w[2][4][3];
+};
+
+// In-register Sylvester Hadamard of 128 values, natural order, times 1 / sqrt(128).
+__device__ __forceinline__ void hadamard128_regs(float (&v)[128]) {
+#pragma unroll
+  for (int h = 1; h < 128; h <<= 1) {
+#pragma unroll
+    for (int i = 0; i < 128; ++i) {
+      if ((i & h) == 0) {
+        const float a = v[i], b = v[i + h];
+        v[i] = a + b;
+        v[i + h] = a - b;
+      }
+    }
+  }
+#pragma unroll
+  for (int i = 0; i < 128; ++i) v[i] *= 0.08838834764831845f;
+}
+
+template <int K2>
+__device__ __forceinline__ void load_stage_words(StageWords &sw, const uint32_t *col0, const LaneWindow &win, uint64_t row_words,
+                                                 uint32_t ks) {
+  // tile rows 4 ks .. 4 ks + 3; the warp's second tile column is one tile (4 K2 words) further
+  const uint32_t *base = col0 + static_cast<uint64_t>(ks) * 4u * row_words;
+#pragma unroll
+  for (int r = 0; r < 4; ++r) {
+#pragma unroll
+    for (int j = 0; j < 2; ++j) {
+      const uint32_t *t = base + static_cast<uint64_t>(r) * row_words + j * 4 * K2;
+      sw.w[j][r][0] = __ldg(t + win.w0);
+      sw.w[j][r][1] = __ldg(t + win.w1);
+      sw.w[j][r][2] = __ldg(t + win.w2);
+    }
+  }
+}
+
+// The decoder warps' loop over the job's K stages. `b_tiles` is the shared-memory address of stage
+// 0's B tile; `bars`: full[kStages], empty[kStages].
+template <int K2>
+__device__ __forceinline__ bool decode_stages(const Job &job, uint32_t stages_base, uint32_t bars, int warp, int lane, uint32_t *status) {
+  const LaneWindow win = lane_window(K2, lane);
+  const uint32_t k_stages = job.in / 64u;
+  const uint32_t cb = static_cast<uint32_t>(warp) >> 2;                    // which of the job's two column blocks
+  const uint32_t blk = cb == 0u ? job.blk0 : job.blk1;
+  const uint32_t tn = blk * 8u + (static_cast<uint32_t>(warp) & 3u) * 2u;   // the warp's first tile column in the plane
+  const uint64_t row_words = static_cast<uint64_t>(job.tile_stride) * 4u * K2;
+  const uint32_t *col0 = job.trellis + static_cast<uint64_t>(tn) * 4u * K2;
+  const bool live = cb < job.nblk;
+  const uint32_t c0 = static_cast<uint32_t>(lane) >> 2, t = static_cast<uint32_t>(lane) & 3u;
+  // row n = 16 jj + c0 (+ 8) of the B tile, jj = 2 warp + j: 8-row group 4 warp + 2 j (+ 1)
+  const uint32_t lane_off = kABytes * 2u + (4u * static_cast<uint32_t>(warp)) * 1024u + c0 * 128u + 4u * t;
+  StageWords cur, nxt;
+  if (live) load_stage_words<K2>(cur, col0, win, row_words, 0);
+  griddep_launch_dependents();
+  griddep_wait();   // from here on the warp may also touch what an earlier kernel wrote
+  for (uint32_t it = 0; it < k_stages; ++it) {
+    const uint32_t slot = it % kStages;
+    if (live && it + 1u < k_stages) load_stage_words<K2>(nxt, col0, win, row_words, it + 1u);
+    if (!mbar_wait(bars + 8u * (kStages + slot), ((it / kStages) & 1u) ^ 1u)) {
+      if (lane == 0) atomicOr(status, kStatusDecoder);
+      return false;
+    }
+    if (live) {
+      const uint32_t tile = stages_base + slot * kStageBytes + lane_off;
+#pragma unroll
+      for (int j = 0; j < 2; ++j) {
+#pragma unroll
+        for (int r = 0; r < 4; ++r) {
+          uint32_t frag[4];
+          decode8<K2>(cur.w[j][r][0], cur.w[j][r][1], cur.w[j][r][2], win.off, frag);
+          const uint32_t at = tile + static_cast<uint32_t>(j) * 2048u;
+          const uint32_t lo = ((2u * r) ^ c0) << 4, hi = ((2u * r + 1u) ^ c0) << 4;
+          asm volatile("st.shared.b32 [%0], %1;" ::"r"(at + lo), "r"(frag[0]) : "memory");
+          asm volatile("st.shared.b32 [%0], %1;" ::"r"(at + hi), "r"(frag[1]) : "memory");
+          asm volatile("st.shared.b32 [%0], %1;" ::"r"(at + 1024u + lo), "r"(frag[2]) : "memory");
+          asm volatile("st.shared.b32 [%0], %1;" ::"r"(at + 1024u + hi), "r"(frag[3]) : "memory");
+        }
+      }
+      // the tile is read by the tensor core (async proxy): order these writes before it
+      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    }
+    mbar_arrive(bars + 8u * slot);
+    if (live) cur = nxt;
+  }
+  return true;
+}
+
+__device__ __forceinline__ bool decode_stages_any(const Job &job, uint32_t stages_base, uint32_t bars, int warp, int lane, uint32_t *status) {
+  switch (job.k2) {
+    case 4: return decode_stages<4>(job, stages_base, bars, warp, lane, status);
+    case 5: return decode_stages<5>(job, stages_base, bars, warp, lane, status);
+    case 6: return decode_stages<6>(job, stages_base, bars, warp, lane, status);
+    case 8: return decode_stages<8>(job, stages_base, bars, warp, lane, status);
+    case 10: return decode_stages<10>(job, stages_base, bars, warp, lane, status);
+    default: return decode_stages<12>(job, stages_base, bars, warp, lane, status);
+  }
+}
+
+// Shared-memory carve-up and the three roles up to the finished accumulator. On return with true,
+// the calling decoder warp may read the accumulators: tensor-memory columns [256 tt, 256 tt + 256)
+// hold row tile tt, lanes = rows, the job's block 0 in the first 128 columns of a tile. `tmem_out`
+// receives the base address. The caller ends with `finish()`.
+struct Core {
+  uint32_t base, bars, bar_acc, tmem;
+  uint32_t *tmem_slot;
+  int warp, lane;
+};
+
+__device__ __forceinline__ Core core_setup(uint8_t *smem_raw) {
+  Core c;
+  const uint32_t raw = smem_u32(smem_raw);
+  c.base = (raw + 1023u) & ~1023u;   // the 128-byte swizzle wants 1024-byte aligned tiles
+  c.bars = c.base + kStages * kStageBytes;       // full[kStages], empty[kStages], accumulator full
+  c.bar_acc = c.bars + 8u * 2u * kStages;
+  c.tmem_slot = reinterpret_cast<uint32_t *>(smem_raw + (c.base - raw) + kStages * kStageBytes + 128);
+  c.warp = threadIdx.x >> 5;
+  c.lane = threadIdx.x & 31;
+  if (threadIdx.x == 0) {
+    for (uint32_t s = 0; s < kStages; ++s) {
+      mbar_init(c.bars + 8u * s, kDecoderWarps * 32 + 1);   // every decoder thread and the producer's expect_tx arrival
+      mbar_init(c.bars + 8u * (kStages + s), 1);            // the MMA thread's commit
+    }
+    mbar_init(c.bar_acc, 1);
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (c.warp == kDecoderWarps + 1) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(c.tmem_slot)), "r"(kTmemCols) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+  c.tmem = *c.tmem_slot;
+  return c;
+}
+
+// Runs the CTA's role up to the finished accumulator. Returns true for a decoder warp whose
+// accumulator is complete (the epilogue may read tensor memory).
+__device__ __forceinline__ bool core_run(const Core &c, const Job &job, const CUtensorMap *map_a, uint32_t *status) {
+  const uint32_t k_stages = job.in / 64u;
+  const uint32_t row_tiles = job.rows > 128u ? 2u : 1u;
+  if (c.warp < kDecoderWarps) {
+    const bool ok = decode_stages_any(job, c.base, c.bars, c.warp, c.lane, status);
+    if (!ok) return false;
+    const bool have = mbar_wait(c.bar_acc, 0u);
+    if (!have && c.lane == 0) atomicOr(status, kStatusEpilogue);
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    return have;
+  }
+  if (c.warp == kDecoderWarps) {
+    // ---- producer of the activation tiles ----
+    griddep_launch_dependents();
+    griddep_wait();   // the rotated activations come from the kernel before
+    if (c.lane == 0) {
+      for (uint32_t it = 0; it < k_stages; ++it) {
+        const uint32_t slot = it % kStages;
+        if (!mbar_wait(c.bars + 8u * (kStages + slot), ((it / kStages) & 1u) ^ 1u)) {
+          atomicOr(status, kStatusProducer);
+          break;
+        }
+        const uint32_t full = c.bars + 8u * slot;
+        mbar_expect_tx(full, row_tiles * kABytes);
+        const uint32_t stage = c.base + slot * kStageBytes;
+        tma_load_2d(stage, map_a, full, static_cast<int32_t>(it * 64u), static_cast<int32_t>(job.row0));
+        if (row_tiles == 2u) tma_load_2d(stage + kABytes, map_a, full, static_cast<int32_t>(it * 64u), static_cast<int32_t>(job.row0 + 128u));
+      }
+    }
+    return false;
+  }
+  // ---- MMA issuer ----
+  griddep_launch_dependents();
+  griddep_wait();
+  if (c.lane == 0) {
+    // instruction descriptor: FP32 accumulator (bit 4), A and B FP16 (format 0), both K-major,
+    // N >> 3 at bit 17, M >> 4 at bit 24
+    const uint32_t mma_n = job.nblk * 128u;
+    const uint32_t idesc = (1u << 4) | ((mma_n >> 3) << 17) | ((128u >> 4) << 24);
+    bool ok = true;
+    for (uint32_t it = 0; it < k_stages; ++it) {
+      const uint32_t slot = it % kStages;
+      if (!mbar_wait(c.bars + 8u * slot, (it / kStages) & 1u)) {
+        atomicOr(status, kStatusMma);
+        ok = false;
+        break;
+      }
+      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+      const uint32_t stage = c.base + slot * kStageBytes;
+      const uint64_t a0 = smem_desc_sw128(stage), a1 = smem_desc_sw128(stage + kABytes), b = smem_desc_sw128(stage + 2u * kABytes);
+#pragma unroll
+      for (uint32_t kb = 0; kb < 4; ++kb) {   // 16 values along K are 32 bytes: two 16-byte units further
+        mma_f16(c.tmem, a0 + 2u * kb, b + 2u * kb, idesc, (it | kb) != 0u ? 1u : 0u);
+        if (row_tiles == 2u) mma_f16(c.tmem + 256u, a1 + 2u * kb, b + 2u * kb, idesc, (it | kb) != 0u ? 1u : 0u);
+      }
+      mma_commit(c.bars + 8u * (kStages + slot));
+    }
+    if (ok) mma_commit(c.bar_acc);
+  }
+  return false;
+}
+
+// 128 accumulator columns of the calling thread's lane (= row) into registers.
+__device__ __forceinline__ void load_block(uint32_t taddr, float (&v)[128]) {
+#pragma unroll
+  for (int q = 0; q < 4; ++q) {
+    uint32_t r[32];
+    tmem_ld32(taddr + 32u * q, r);
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+    for (int i = 0; i < 32; ++i) v[32 * q + i] = __uint_as_float(r[i]);
+  }
+}
+
+__device__ __forceinline__ void core_finish(const Core &c) {
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  if (c.warp == kDecoderWarps + 1) {
+    __syncwarp();
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(c.tmem), "r"(kTmemCols) : "memory");
+  }
+}
+
+// The rotated activations [rows][in] fp16 as a 2-D tensor with boxes of 128 rows x 64 values, 128-byte swizzle.
+inline bool make_rows_map(CUtensorMap *map, const void *rows_f16, uint64_t rows, uint64_t in) {
+  EncodeTiledFn fn = encode_tiled_fn();
+  if (fn == nullptr) return false;
+  const cuuint64_t dims[2] = {in, rows};
+  const cuuint64_t strides[1] = {in * 2u};
+  const cuuint32_t box[2] = {64u, 128u};
+  const cuuint32_t elem[2] = {1, 1};
+  return fn(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, const_cast<void *>(rows_f16), dims, strides, box, elem,
+            CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+}  // namespace trellis_tc
+}  // namespace b200q
+
+#endif

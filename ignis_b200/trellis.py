@@ -165,6 +165,14 @@ def linear_swiglu(gate: Weight, up: Weight, x: torch.Tensor, out: torch.Tensor |
     return out
 
 
+def device_status() -> int:
+    """``b200q_trellis_device_status``: non-zero after a bounded device-side wait of the tensor-core
+    route ran out."""
+    word = C.c_uint32(0)
+    _check(_lib.load().b200q_trellis_device_status(_stream(), C.byref(word)))
+    return int(word.value)
+
+
 def reconstruct(w: Weight) -> torch.Tensor:
     """The inner matrix as fp16 ``[in, out]``, bit for bit exllamav3's ``reconstruct``."""
     out = torch.empty((w.in_, w.out), dtype=torch.float16, device=w.trellis.device)

@@ -21,7 +21,13 @@
  * - fp16 operands with fp32 accumulation (the reference accumulates in fp16 and folds every 32
  *   inputs); a power-of-two scale per token and 128-input block keeps the rotated activations in
  *   fp16 range whatever the input;
- * - token counts above 8 are served by the same route in passes of 8 tokens.
+ * - up to 64 tokens a call shares every decoded tile among token tiles of 8; beyond 64 tokens, given
+ *   the workspace ignis_trellis_workspace_bytes asks for, a call takes the tensor-core route: the
+ *   activations rotated once into the workspace (fp16 rows, one power-of-two scale per token), the
+ *   trellis tiles decoded into shared memory and multiplied by tcgen05 with fp32 accumulation in
+ *   tensor memory; SwiGLU stores the gate in BF16 between its two products there, as the
+ *   reference's prefill route does (ignis_trellis_linear.h:43-44). Without that workspace a wide
+ *   call runs as passes of 64 tokens.
  *
  * Conventions (unchanged): activations device-resident token-major BF16 x [tokens][in], 16-byte
  * aligned; outputs BF16 [tokens][ldy], ldy a multiple of 4, y 8-byte aligned; `in` and `out`
@@ -100,6 +106,12 @@ int32_t b200q_trellis_linear_group(const ignis_trellis_weight *const *w, uint32_
 /* `inner` decoded to fp16 [in][out] row-major, bit for bit exllamav3's `reconstruct`.
  * reference: ignis_trellis_linear.h:145 */
 int32_t ignis_trellis_reconstruct(const ignis_trellis_weight *w, void *w_f16, void *stream);
+
+/* Not in the reference's ABI (its kernels trap or spin instead): the status word of the tensor-core
+ * route's bounded device-side waits, copied to *status after `stream` has finished. 0 unless a wait
+ * ran out (bit 0 producer, 1 MMA issuer, 2 epilogue, 3 decoder), in which case that call's output
+ * is not valid. Per device, sticky. */
+int32_t b200q_trellis_device_status(void *stream, uint32_t *status);
 
 /* Thread-local message of the most recent failed call. Never NULL.
  * reference: ignis_trellis_linear.h:148 */

@@ -79,9 +79,13 @@ def test_trellis_is_reproducible_and_capturable(oracle):
     x70 = torch.randn(70, in_, generator=torch.Generator().manual_seed(4)).to(torch.bfloat16).cuda()
     y, y70 = torch.empty(8, out, dtype=torch.bfloat16, device="cuda"), torch.empty(70, out, dtype=torch.bfloat16, device="cuda")
 
+    ws = tr.WorkspaceBuffer(tr.workspace_bytes(in_, out, 1, 70))
+    y70tc = torch.empty(70, out, dtype=torch.bfloat16, device="cuda")
+
     def step():
         tr.linear(w, x, out=y)
         tr.linear(w, x70, out=y70)   # two passes: 64 + 6 tokens
+        tr.linear(w, x70, out=y70tc, workspace=ws)   # the tensor-core route: a rotation launch and the product
 
     step()
     torch.cuda.synchronize()
@@ -91,7 +95,8 @@ def test_trellis_is_reproducible_and_capturable(oracle):
     assert torch.equal(a, y) and torch.equal(b, y70)
     # a token's result does not depend on how many tokens share its pass
     assert torch.equal(tr.linear(w, x70[:8].contiguous()), y70[:8])
-    _replay_equals_eager(step, lambda: [y, y70])
+    _replay_equals_eager(step, lambda: [y, y70, y70tc])
+    assert tr.device_status() == 0
 
 
 def test_moe_experts_are_reproducible_and_capturable(oracle):

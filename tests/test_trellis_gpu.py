@@ -277,10 +277,18 @@ def test_real_shapes_at_wide_token_counts(tr, oracle, in_, out, tokens):
 
     w, inner, suh, svh = real_shape_weight(tr, oracle, in_, out, 6)
     x = loud_activations(500 + tokens, tokens, in_)
-    y = tr.linear(w, x.cuda())
     rows = checked_rows(tokens)
     ref, s = orc.trellis_project_rows(inner, suh, svh, x[rows].double().numpy())
-    check_linear(y[torch.tensor(rows).cuda()], ref, s)
+    pick = torch.tensor(rows).cuda()
+    check_linear(tr.linear(w, x.cuda())[pick], ref, s)           # no workspace: passes of 64 tokens through the decode kernel
+    if tokens > 64:
+        # with the workspace the query asks for: rotated rows in the workspace, trellis tiles decoded into
+        # shared memory, tcgen05 with the accumulator in tensor memory
+        ws = tr.WorkspaceBuffer(tr.workspace_bytes(in_, out, 1, tokens))
+        y = tr.linear(w, x.cuda(), workspace=ws)
+        assert tr.device_status() == 0
+        check_linear(y[pick], ref, s)
+        assert torch.equal(y, tr.linear(w, x.cuda(), workspace=ws))   # the same bits again
 
 
 @pytest.mark.parametrize("tokens", [64, 130, 300])
@@ -302,14 +310,51 @@ def test_wide_token_epilogues(tr, oracle, tokens):
     (gate, g_inner, g_suh, g_svh), (up, u_inner, u_suh, u_svh) = sides
     g64, s = orc.trellis_project_rows(g_inner, g_suh, g_svh, x64)
     u64, _ = orc.trellis_project_rows(u_inner, u_suh, u_svh, x64)
-    check_linear(tr.linear(gate, x.cuda()), g64, s)
-    base = torch.randn(tokens, out, generator=torch.Generator().manual_seed(tokens)).to(torch.bfloat16)
-    y = tr.linear(gate, x.cuda(), out=base.clone().cuda(), epilogue=tr.ADD)
-    check_linear(y, g64 + base.double().numpy(), s + 2.0 * np.abs(base.double().numpy()))
+    base = torch.randn(tokens, out + 64, generator=torch.Generator().manual_seed(tokens)).to(torch.bfloat16)
+    b64 = base[:, :out].double().numpy()
     want = g64 / (1.0 + np.exp(-g64)) * u64
-    got = tr.linear_swiglu(gate, up, x.cuda()).float().cpu().numpy().astype(np.float64)
-    assert np.linalg.norm(got - want) <= 2.0 ** -7 * np.linalg.norm(want)
-    assert np.abs(got - want).max() <= 2.0 ** -6 * np.abs(want).max()
+    routes = [None] + ([tr.WorkspaceBuffer(tr.workspace_bytes(in_, out, 2, tokens))] if tokens > 64 else [])
+    for ws in routes:   # passes of the decode kernel, then (beyond 64 tokens) the tensor-core route
+        check_linear(tr.linear(gate, x.cuda(), workspace=ws), g64, s)
+        y = base.clone().cuda()
+        tr.linear(gate, x.cuda(), out=y[:, :out], epilogue=tr.ADD, workspace=ws)
+        check_linear(y[:, :out], g64 + b64, s + 2.0 * np.abs(b64))
+        assert torch.equal(y[:, out:].cpu(), base[:, out:])          # a wider buffer's other columns stay
+        got = tr.linear_swiglu(gate, up, x.cuda(), workspace=ws).float().cpu().numpy().astype(np.float64)
+        assert np.linalg.norm(got - want) <= 2.0 ** -7 * np.linalg.norm(want)
+        assert np.abs(got - want).max() <= 2.0 ** -6 * np.abs(want).max()
+        assert tr.device_status() == 0
+
+
+@pytest.mark.parametrize("k2", [4, 5, 8, 10, 12])
+def test_tensor_core_route_at_every_bit_width_and_on_column_views(tr, oracle, k2):
+    """The wide-token route at the other bit widths, on an odd number of 128-column blocks (the last
+    CTA multiplies one block), on a column view of a wider plane (tile_stride), with tokens of very
+    different scale (one scale per token) and a ragged last token tile."""
+    from oracle import oracle as orc
+
+    in_, out, tokens = 640, 896, 333
+    rng = np.random.default_rng(k2)
+    words = oracle.hash_trellis_words(4100 + k2, in_, out, k2)
+    suh, svh = make_scales(rng, in_, 0.05), make_scales(rng, out, 0.03)
+    inner = oracle.trellis_decode(words, k2, in_, out)
+    w = tr.Weight.from_numpy(words, suh, svh, k2, in_, out)
+    x = torch.randn(tokens, in_, generator=torch.Generator().manual_seed(k2))
+    x[:, 5] *= 1000.0
+    x[3] *= 1e-20
+    x[4] *= 1e15
+    x[5] = 0.0
+    x = x.to(torch.bfloat16)
+    ref, s = orc.trellis_project_rows(inner, suh, svh, x.double().numpy())
+    ws = tr.WorkspaceBuffer(tr.workspace_bytes(in_, out, 1, tokens))
+    y = tr.linear(w, x.cuda(), workspace=ws)
+    assert tr.device_status() == 0
+    got = y.float().cpu().numpy().astype(np.float64)
+    assert (np.abs(got - ref) <= 2.0 ** -8 * np.abs(ref) + 2.0 ** -9 * s).all()
+    assert np.all(got[5] == 0.0)
+    view = w.columns(128, 640)                     # four blocks of the seven, through the plane's tile stride
+    yv = tr.linear(view, x.cuda(), workspace=ws)
+    assert torch.equal(yv, y[:, 128:640])
 
 
 def test_full_size_gate_projection(tr, oracle):

@@ -77,9 +77,11 @@ def test_decode_widths_against_the_host_arithmetic(oracle, tokens):
     y16 = nv.linear_noalloc(x.cuda(), w, torch.empty(tokens, n, dtype=torch.bfloat16, device="cuda"))
     want = torch.from_numpy(ref).to(torch.bfloat16).float().numpy()
     assert np.all(np.abs(y16.float().cpu().numpy() - want) <= np.abs(want) * 2.0 ** -7 + 1e-5 * np.abs(ref).max())
-    # the decode-width kernel of the workspace-taking entry computes the same sums in another order
-    other = nv.linear(x.cuda(), w, policy=nv.ALLOW_A4, epilogue=nv.OUT_F32)
-    assert (other - y32).abs().max().item() <= 2e-3 * float(np.abs(ref).max())
+    if tokens >= 8:
+        # from 8 tokens (this shape's threshold under the reference's policy) the workspace-taking entry
+        # quantizes too, in its decode-width kernel: the same sums in another order
+        other = nv.linear(x.cuda(), w, policy=nv.ALLOW_A4, epilogue=nv.OUT_F32)
+        assert (other - y32).abs().max().item() <= 2e-3 * float(np.abs(ref).max())
     assert nv.device_status() == 0
 
 
