@@ -53,6 +53,7 @@ struct DeviceState {
   int w4a4_bn = 128;     // B200Q_W4A4_BN: weight rows per tile of the plain W4A4 product (128 or 256)
   int gemv_xu = 8;       // B200Q_GEMV_XU: words per row of 8 decoded by the hardware E2M1 conversion
   int sm_cap = 0;        // IGNIS_TRELLIS_SM_CAP
+  int moe_tc = 1;        // B200Q_MOE_TC: expert calls of more than 64 tokens take the tensor-core kernels
   int trellis_tc = 1;    // B200Q_TRELLIS_TC: dense trellis calls of more than 64 tokens with a workspace take the tensor-core route
   int peer_barrier_polls = 1 << 22;  // B200Q_PEER_BARRIER_POLLS: looks at a flag before b200q_peer_barrier gives up (400 ns apart)
 };

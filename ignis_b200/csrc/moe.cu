@@ -16,6 +16,7 @@
 // is skipped and recorded in the workspace's status word.
 #include "../../include/ignis_moe.h"
 
+#include "moe_internal.cuh"
 #include "trellis_device.cuh"
 
 #include <mutex>
@@ -27,23 +28,11 @@ using namespace trellis_dev;
 
 constexpr int kThreads = 256;
 constexpr int kWarps = 8;
-constexpr uint32_t kStatusBadExpert = 1u, kStatusAbsentRecord = 2u, kStatusRange = 4u;
 
 struct Geometry {
   uint32_t hidden = IGNIS_MOE_HIDDEN, inter = IGNIS_MOE_INTERMEDIATE, experts = IGNIS_MOE_EXPERTS, top_k = IGNIS_MOE_TOP_K;
 };
 Geometry g_geo;
-
-// A work item: up to `item_rows` sorted rows of one expert (64 from the prefill entry, 8 from the
-// decode entry), i.e. up to 8 row tiles of 8.
-struct Item {
-  uint32_t expert, first, count, tile_first;
-};
-// A row tile: 8 consecutive sorted rows of one expert (the MMA's N), the unit the activations are
-// rotated in.
-struct Tile {
-  uint32_t expert, first, count, pad;
-};
 
 // Workspace regions for `tokens_max` tokens.
 struct Layout {
@@ -223,24 +212,6 @@ __global__ void __launch_bounds__(1024) moe_group_small_kernel(const int32_t *id
 }
 
 // ---- the expert kernels ----------------------------------------------------------------------
-struct ExpertParams {
-  const ignis_moe_slot *slots;
-  const Item *items;
-  const Tile *tiles;
-  const uint32_t *n_items;  // [0] items, [1] tiles
-  const uint32_t *sorted;   // row -> assignment index (token * top_k + rank)
-  const uint16_t *x;        // BF16 [tokens][hidden]
-  const float *weights;     // routing weights [tokens][top_k]
-  uint2 *frag_in;           // rotated x: [tile][hidden / 128][step 8][lane 32]
-  float2 *scale_in;         // (inverse scale, scale): [tile][hidden / 128][row 8]
-  float *gu;                // fp32 [rows][2 inter]: gate | up products
-  uint2 *frag_h;            // rotated silu(g) u: [tile][inter / 128][step 8][lane 32]
-  float2 *scale_h;
-  long long *acc;           // int64 [tokens][hidden]
-  uint32_t *status;
-  uint32_t hidden, inter, top_k, experts;
-};
-
 // Rotates the rows of one tile into B fragments, once per row: PHASE 0 x o suh of the gate/up
 // record, PHASE 1 silu(g) u o suh of the down record; then the 128-wide Hadamard in fp32, a
 // power-of-two scale per (row, block) (largest value in [2^13, 2^14)) and fp16. One CTA per tile,
@@ -829,6 +800,7 @@ int32_t run_experts(const void *x, uint32_t tokens, const int32_t *ids, const fl
   }
 
   ExpertParams p = {};
+  p.ids = ids;
   p.slots = slots;
   p.items = items;
   p.tiles = reinterpret_cast<const Tile *>(base + l.tiles);
@@ -850,6 +822,9 @@ int32_t run_experts(const void *x, uint32_t tokens, const int32_t *ids, const fl
   // Grids are sized for the worst case the host can know (the grouping happened on the device);
   // CTAs beyond the item or tile count return at once.
   const uint32_t items_max = items_bound(g, rows, item_rows);
+  if (item_rows == kMoeTcItemRows) {   // the tensor-core route: items of up to 256 rows
+    return moe_tc_experts(slot, *dev, p, rows, items_max, offsets, stream, what);
+  }
   const uint32_t tiles_max = items_bound(g, rows, 8u);
   const bool wide = item_rows > 8u;
   for (int phase = 0; phase < 2; ++phase) {
@@ -914,7 +889,7 @@ int32_t ignis_moe_prepare(void) {
   if (prepare_device(slot) != 0) return -1;
   cudaError_t err = cudaFuncSetAttribute(moe_router_logits_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024);
   if (err != cudaSuccess) return fail(slot, "ignis_moe_prepare: %s", cudaGetErrorString(err));
-  return 0;
+  return moe_tc_prepare(slot);
 }
 
 uint64_t ignis_moe_workspace_bytes(uint32_t decode_tokens, uint32_t prefill_tokens) {
@@ -989,7 +964,12 @@ int32_t ignis_moe_experts_prefill(const void *x, uint32_t tokens, const int32_t 
                                   const struct ignis_moe_slot *slots, const struct ignis_moe_workspace *workspace,
                                   int64_t *acc, void *stream) {
   const uint32_t limit = workspace != nullptr ? workspace->prefill_tokens : 0u;
-  return run_experts(x, tokens, ids, weights, slots, workspace, acc, stream, limit, tokens > 8u ? 64u : 8u, "ignis_moe_experts_prefill");
+  // up to 8 tokens the decode entry's item size; up to 64 tokens items of 64 rows on the warp-level
+  // MMAs; beyond, items of 256 rows on the tensor cores (B200Q_MOE_TC = 0 keeps the warp-level kernels)
+  const DeviceState *dev = device_state(moe_error());
+  const bool tc = dev != nullptr && dev->prepared && dev->moe_tc != 0 && tokens > 64u;
+  return run_experts(x, tokens, ids, weights, slots, workspace, acc, stream, limit, tokens > 8u ? (tc ? kMoeTcItemRows : 64u) : 8u,
+                     "ignis_moe_experts_prefill");
 }
 
 int32_t ignis_moe_decode_cluster_size(void) { return 0; }
@@ -1057,9 +1037,11 @@ int32_t ignis_moe_stream_sync(void *stream) {
 int32_t ignis_moe_workspace_status(const struct ignis_moe_workspace *workspace, void *stream, uint32_t *status) {
   ErrorSlot &slot = moe_error();
   if (workspace == nullptr || workspace->base == nullptr || status == nullptr) return fail(slot, "ignis_moe_workspace_status: NULL argument");
-  cudaError_t err = cudaMemcpyAsync(status, workspace->base, sizeof(uint32_t), cudaMemcpyDeviceToHost, static_cast<cudaStream_t>(stream));
+  uint32_t words[2] = {0u, 0u};   // [0] the expert kernels' bits, [1] bounded waits of the tensor-core kernels that ran out
+  cudaError_t err = cudaMemcpyAsync(words, workspace->base, sizeof(words), cudaMemcpyDeviceToHost, static_cast<cudaStream_t>(stream));
   if (err == cudaSuccess) err = cudaStreamSynchronize(static_cast<cudaStream_t>(stream));
   if (err != cudaSuccess) return fail(slot, "ignis_moe_workspace_status: %s", cudaGetErrorString(err));
+  *status = words[0] | (words[1] != 0u ? kStatusTcWait : 0u);
   return 0;
 }
 

@@ -85,6 +85,7 @@ int32_t prepare_device(ErrorSlot &slot) {
   fresh.sm_cap = env_int("IGNIS_TRELLIS_SM_CAP", 0);
   if (fresh.sm_cap < 0 || fresh.sm_cap > fresh.sm_count) fresh.sm_cap = 0;
   fresh.trellis_tc = env_int("B200Q_TRELLIS_TC", 1);
+  fresh.moe_tc = env_int("B200Q_MOE_TC", 1);
   fresh.peer_barrier_polls = env_int("B200Q_PEER_BARRIER_POLLS", 1 << 22);
   if (fresh.peer_barrier_polls < 1) fresh.peer_barrier_polls = 1;
   for (int i = 0; i < 9; ++i) fresh.gemv_slots[i] = state->gemv_slots[i];

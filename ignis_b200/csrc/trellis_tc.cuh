@@ -58,10 +58,17 @@ struct Job {
   uint32_t row0, rows;      // row0 is also the TMA row coordinate
 };
 
-// The lane's words of the 8 tiles a decoder warp owns in one stage: 2 tile columns x 4 tile rows.
+// The raw words of the 8 tiles a decoder warp owns in one stage (2 tile columns x 4 tile rows), one
+// word per lane and tile (two for the widths whose tiles have more than 32 words): lane l holds
+// word l of the tile, and the three words a lane's window needs come from its neighbours by shuffle.
+// A 16 x 16 tile is 4 k2 words, so one coalesced load of up to 128 bytes fetches a whole tile.
+template <int K2>
 struct StageWords {
-  uint32_t w[2][4][3];
+  static constexpr int kPerTile = (4 * K2 + 31) / 32;
+  uint32_t w[2][4][kPerTile];
 };
+
+constexpr int kWordRing = 4;   // stages of raw words a decoder warp keeps in flight in registers
 
 // In-register Sylvester Hadamard of 128 values, natural order, times 1 / sqrt(128).
 __device__ __forceinline__ void hadamard128_regs(float (&v)[128]) {
@@ -81,24 +88,33 @@ __device__ __forceinline__ void hadamard128_regs(float (&v)[128]) {
 }
 
 template <int K2>
-__device__ __forceinline__ void load_stage_words(StageWords &sw, const uint32_t *col0, const LaneWindow &win, uint64_t row_words,
-                                                 uint32_t ks) {
+__device__ __forceinline__ void load_stage_words(StageWords<K2> &sw, const uint32_t *col0, int lane, uint64_t row_words, uint32_t ks) {
   // tile rows 4 ks .. 4 ks + 3; the warp's second tile column is one tile (4 K2 words) further
-  const uint32_t *base = col0 + static_cast<uint64_t>(ks) * 4u * row_words;
+  const uint32_t *base = col0 + static_cast<uint64_t>(ks) * 4u * row_words + lane;
 #pragma unroll
   for (int r = 0; r < 4; ++r) {
 #pragma unroll
     for (int j = 0; j < 2; ++j) {
       const uint32_t *t = base + static_cast<uint64_t>(r) * row_words + j * 4 * K2;
-      sw.w[j][r][0] = __ldg(t + win.w0);
-      sw.w[j][r][1] = __ldg(t + win.w1);
-      sw.w[j][r][2] = __ldg(t + win.w2);
+#pragma unroll
+      for (int h = 0; h < StageWords<K2>::kPerTile; ++h) {
+        sw.w[j][r][h] = (32 * h + lane < 4 * K2) ? __ldg(t + 32 * h) : 0u;
+      }
     }
   }
 }
 
-// The decoder warps' loop over the job's K stages. `b_tiles` is the shared-memory address of stage
-// 0's B tile; `bars`: full[kStages], empty[kStages].
+// Word `index` of a tile whose words lie one per lane (and, beyond 32, in the second register).
+template <int K2>
+__device__ __forceinline__ uint32_t tile_word(const uint32_t (&w)[(4 * K2 + 31) / 32], uint32_t index) {
+  if ((4 * K2 + 31) / 32 == 1) return __shfl_sync(0xFFFFFFFFu, w[0], static_cast<int>(index));
+  const uint32_t lo = __shfl_sync(0xFFFFFFFFu, w[0], static_cast<int>(index & 31u));
+  const uint32_t hi = __shfl_sync(0xFFFFFFFFu, w[(4 * K2 + 31) / 32 - 1], static_cast<int>(index & 31u));
+  return index < 32u ? lo : hi;
+}
+
+// The decoder warps' loop over the job's K stages. `stages_base` is the shared-memory address of
+// stage 0; `bars`: full[kStages], empty[kStages].
 template <int K2>
 __device__ __forceinline__ bool decode_stages(const Job &job, uint32_t stages_base, uint32_t bars, int warp, int lane, uint32_t *status) {
   const LaneWindow win = lane_window(K2, lane);
@@ -112,38 +128,50 @@ __device__ __forceinline__ bool decode_stages(const Job &job, uint32_t stages_ba
   const uint32_t c0 = static_cast<uint32_t>(lane) >> 2, t = static_cast<uint32_t>(lane) & 3u;
   // row n = 16 jj + c0 (+ 8) of the B tile, jj = 2 warp + j: 8-row group 4 warp + 2 j (+ 1)
   const uint32_t lane_off = kABytes * 2u + (4u * static_cast<uint32_t>(warp)) * 1024u + c0 * 128u + 4u * t;
-  StageWords cur, nxt;
-  if (live) load_stage_words<K2>(cur, col0, win, row_words, 0);
+  // The words of the next kWordRing stages are in flight in registers: a load issued when its
+  // stage's slot of the ring was last decoded has several stage times to arrive (one stage ahead is
+  // not enough: a stage is shorter than the latency of HBM).
+  StageWords<K2> ring[kWordRing];
+#pragma unroll
+  for (int d = 0; d < kWordRing; ++d) {   // the weights never depend on the previous kernel
+    if (live && static_cast<uint32_t>(d) < k_stages) load_stage_words<K2>(ring[d], col0, lane, row_words, static_cast<uint32_t>(d));
+  }
   griddep_launch_dependents();
   griddep_wait();   // from here on the warp may also touch what an earlier kernel wrote
-  for (uint32_t it = 0; it < k_stages; ++it) {
-    const uint32_t slot = it % kStages;
-    if (live && it + 1u < k_stages) load_stage_words<K2>(nxt, col0, win, row_words, it + 1u);
-    if (!mbar_wait(bars + 8u * (kStages + slot), ((it / kStages) & 1u) ^ 1u)) {
-      if (lane == 0) atomicOr(status, kStatusDecoder);
-      return false;
-    }
-    if (live) {
-      const uint32_t tile = stages_base + slot * kStageBytes + lane_off;
+  for (uint32_t it0 = 0; it0 < k_stages; it0 += kWordRing) {
 #pragma unroll
-      for (int j = 0; j < 2; ++j) {
-#pragma unroll
-        for (int r = 0; r < 4; ++r) {
-          uint32_t frag[4];
-          decode8<K2>(cur.w[j][r][0], cur.w[j][r][1], cur.w[j][r][2], win.off, frag);
-          const uint32_t at = tile + static_cast<uint32_t>(j) * 2048u;
-          const uint32_t lo = ((2u * r) ^ c0) << 4, hi = ((2u * r + 1u) ^ c0) << 4;
-          asm volatile("st.shared.b32 [%0], %1;" ::"r"(at + lo), "r"(frag[0]) : "memory");
-          asm volatile("st.shared.b32 [%0], %1;" ::"r"(at + hi), "r"(frag[1]) : "memory");
-          asm volatile("st.shared.b32 [%0], %1;" ::"r"(at + 1024u + lo), "r"(frag[2]) : "memory");
-          asm volatile("st.shared.b32 [%0], %1;" ::"r"(at + 1024u + hi), "r"(frag[3]) : "memory");
-        }
+    for (int d = 0; d < kWordRing; ++d) {
+      const uint32_t it = it0 + static_cast<uint32_t>(d);
+      if (it >= k_stages) break;
+      const uint32_t slot = it % kStages;
+      if (!mbar_wait(bars + 8u * (kStages + slot), ((it / kStages) & 1u) ^ 1u)) {
+        if (lane == 0) atomicOr(status, kStatusDecoder);
+        return false;
       }
-      // the tile is read by the tensor core (async proxy): order these writes before it
-      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+      if (live) {
+        const uint32_t tile = stages_base + slot * kStageBytes + lane_off;
+#pragma unroll
+        for (int j = 0; j < 2; ++j) {
+#pragma unroll
+          for (int r = 0; r < 4; ++r) {
+            const uint32_t w0 = tile_word<K2>(ring[d].w[j][r], win.w0), w1 = tile_word<K2>(ring[d].w[j][r], win.w1),
+                           w2 = tile_word<K2>(ring[d].w[j][r], win.w2);
+            uint32_t frag[4];
+            decode8<K2>(w0, w1, w2, win.off, frag);
+            const uint32_t at = tile + static_cast<uint32_t>(j) * 2048u;
+            const uint32_t lo = ((2u * r) ^ c0) << 4, hi = ((2u * r + 1u) ^ c0) << 4;
+            asm volatile("st.shared.b32 [%0], %1;" ::"r"(at + lo), "r"(frag[0]) : "memory");
+            asm volatile("st.shared.b32 [%0], %1;" ::"r"(at + hi), "r"(frag[1]) : "memory");
+            asm volatile("st.shared.b32 [%0], %1;" ::"r"(at + 1024u + lo), "r"(frag[2]) : "memory");
+            asm volatile("st.shared.b32 [%0], %1;" ::"r"(at + 1024u + hi), "r"(frag[3]) : "memory");
+          }
+        }
+        // the tile is read by the tensor core (async proxy): order these writes before it
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+      }
+      mbar_arrive(bars + 8u * slot);
+      if (live && it + kWordRing < k_stages) load_stage_words<K2>(ring[d], col0, lane, row_words, it + kWordRing);
     }
-    mbar_arrive(bars + 8u * slot);
-    if (live) cur = nxt;
   }
   return true;
 }

@@ -148,7 +148,9 @@ int32_t ignis_moe_stream_sync(void *stream);
 /* No counterpart in the reference (its kernels trap instead): copies the workspace's status word
  * to `*status` and blocks until `stream` is idle. Bit 0: an expert id outside the table; bit 1: a
  * selected record absent or of a k2 the experts do not take; bit 2: a contribution not finite or
- * beyond the accumulator's range. Each was skipped, never read as weights. */
+ * beyond the accumulator's range. Each was skipped, never read as weights. Bit 3: a bounded
+ * device-side wait of the tensor-core expert kernels (calls of more than 64 tokens) ran out; that
+ * call's sums are not valid. */
 int32_t ignis_moe_workspace_status(const struct ignis_moe_workspace *workspace, void *stream, uint32_t *status);
 
 /* Thread-local message of the most recent failed call. Never NULL. reference: ignis_moe.h:216 */

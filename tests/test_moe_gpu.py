@@ -180,11 +180,18 @@ def test_config4_geometry_under_zipf_routing(mo, oracle, k2s):
         l2 = np.linalg.norm(got[i] - ref[i]) / np.linalg.norm(ref[i])
         linf = np.abs(got[i] - ref[i]).max() / np.abs(ref[i]).max()
         assert l2 <= 2e-3 and linf <= 1e-2, (t, l2, linf)
-    # the decode entry's arithmetic on eight of the sampled tokens: the same bits
+    # the decode entry on eight of the sampled tokens: other kernels (warp-level MMAs, a scale per
+    # 128 inputs), the same fp64 reference and bars
     eight = torch.tensor(sample[:8])
     ws8 = mo.Workspace(8, 8)
     dec = mo.experts_decode(x[eight].cuda(), torch.from_numpy(ids)[eight].cuda(), torch.from_numpy(w)[eight].cuda(), rec.table, ws8)
-    assert torch.equal(dec[:8], acc[eight.cuda()])
+    assert ws8.status() == 0
+    check_tokens(dec[:8], ref[:8])
+    # 40 tokens take the warp-level prefill kernels (items of 64 rows): the decode entry's bits
+    few = torch.tensor(sample[:40])
+    ws40 = mo.Workspace(8, 40)
+    pre = mo.experts_prefill(x[few].cuda(), torch.from_numpy(ids)[few].cuda(), torch.from_numpy(w)[few].cuda(), rec.table, ws40)
+    assert torch.equal(pre[:8], dec[:8])
 
 
 def test_absent_records_and_bad_ids_are_skipped_and_reported(mo, oracle):
