@@ -139,53 +139,45 @@ __global__ void __launch_bounds__(kThreads, 1) moe_tc_gemm_kernel(const __grid_c
   const bool have = core_run(c, job, &map_a, p.status + 1);   // word 1 of the status line: waits of this kernel that ran out
   if (have) {
     const uint32_t tiles = job.rows > 128u ? 2u : 1u, items = tiles * job.nblk;
-    for (uint32_t it = static_cast<uint32_t>(c.warp) >> 2; it < items; it += 2u) {
+    const uint32_t group = static_cast<uint32_t>(c.warp) >> 2, quad = static_cast<uint32_t>(c.warp) & 3u;
+    float *stash = reinterpret_cast<float *>(smem_raw + (c.base - smem_u32(smem_raw))) + group * 8192u + quad * 32u + static_cast<uint32_t>(c.lane);
+    for (uint32_t it = group; it < items; it += kDecoderWarps / 4) {
       const uint32_t tt = it / job.nblk, cb = it % job.nblk;
-      const uint32_t local = tt * 128u + (static_cast<uint32_t>(c.warp) & 3u) * 32u + static_cast<uint32_t>(c.lane);
-      float v[128];
-      load_block(c.tmem + (((static_cast<uint32_t>(c.warp) & 3u) * 32u) << 16) + tt * 256u + cb * 128u, v);
-      if (local < item.count) {
-        const uint32_t row = item.first + local;
-        const float inv = inv_rows[row];
+      const uint32_t local = tt * 128u + quad * 32u + static_cast<uint32_t>(c.lane);
+      const bool valid = local < item.count;
+      const uint32_t row = item.first + (valid ? local : 0u);
+      const uint32_t col0 = (cb == 0u ? job.blk0 : job.blk1) * 128u;
+      const uint2 *sv = reinterpret_cast<const uint2 *>(svh + col0);
+      const uint32_t taddr = c.tmem + ((quad * 32u) << 16) + tt * 256u + cb * 128u;
+      if (PHASE == 0) {
+        float4 *dst = reinterpret_cast<float4 *>(p.gu + static_cast<size_t>(row) * 2u * p.inter + col0);
+        block_epilogue(taddr, valid ? inv_rows[row] : 0.0f, valid, stash, [&](int q, const float (&r)[4]) {
+          const uint2 s = sv[q];
+          const __half2 s01 = *reinterpret_cast<const __half2 *>(&s.x), s23 = *reinterpret_cast<const __half2 *>(&s.y);
+          dst[q] = make_float4(r[0] * __low2float(s01), r[1] * __high2float(s01), r[2] * __low2float(s23), r[3] * __high2float(s23));
+        });
+      } else {
+        const uint32_t a = p.sorted[row];
+        const uint32_t token = a / p.top_k;
+        const float wr = p.weights[a];
+        long long *dst = p.acc + static_cast<size_t>(token) * p.hidden + col0;
+        bool range = false;
+        block_epilogue(taddr, valid ? inv_rows[row] : 0.0f, valid, stash, [&](int q, const float (&r)[4]) {
+          const uint2 s = sv[q];
+          const __half2 s01 = *reinterpret_cast<const __half2 *>(&s.x), s23 = *reinterpret_cast<const __half2 *>(&s.y);
+          const float y[4] = {r[0] * __low2float(s01), r[1] * __high2float(s01), r[2] * __low2float(s23), r[3] * __high2float(s23)};
 #pragma unroll
-        for (int i = 0; i < 128; ++i) v[i] *= inv;
-        hadamard128_regs(v);
-        const uint32_t col0 = (cb == 0u ? job.blk0 : job.blk1) * 128u;
-        const uint2 *sv = reinterpret_cast<const uint2 *>(svh + col0);
-        if (PHASE == 0) {
-          float4 *dst = reinterpret_cast<float4 *>(p.gu + static_cast<size_t>(row) * 2u * p.inter + col0);
-#pragma unroll
-          for (int q = 0; q < 32; ++q) {
-            const uint2 s = sv[q];
-            const __half2 s01 = *reinterpret_cast<const __half2 *>(&s.x), s23 = *reinterpret_cast<const __half2 *>(&s.y);
-            dst[q] = make_float4(v[4 * q] * __low2float(s01), v[4 * q + 1] * __high2float(s01), v[4 * q + 2] * __low2float(s23),
-                                 v[4 * q + 3] * __high2float(s23));
-          }
-        } else {
-          const uint32_t a = p.sorted[row];
-          const uint32_t token = a / p.top_k;
-          const float wr = p.weights[a];
-          long long *dst = p.acc + static_cast<size_t>(token) * p.hidden + col0;
-          bool range = false;
-#pragma unroll
-          for (int q = 0; q < 32; ++q) {
-            const uint2 s = sv[q];
-            const __half2 s01 = *reinterpret_cast<const __half2 *>(&s.x), s23 = *reinterpret_cast<const __half2 *>(&s.y);
-            const float r[4] = {v[4 * q] * __low2float(s01), v[4 * q + 1] * __high2float(s01), v[4 * q + 2] * __low2float(s23),
-                                v[4 * q + 3] * __high2float(s23)};
-#pragma unroll
-            for (int e = 0; e < 4; ++e) {
-              const float cval = wr * r[e];
-              if (!(fabsf(cval) < 2147483648.0f)) {   // also catches NaN
-                range = true;
-              } else {
-                atomicAdd(reinterpret_cast<unsigned long long *>(dst + 4 * q + e),
-                          static_cast<unsigned long long>(__double2ll_rn(static_cast<double>(cval) * 4294967296.0)));
-              }
+          for (int e = 0; e < 4; ++e) {
+            const float cval = wr * y[e];
+            if (!(fabsf(cval) < 2147483648.0f)) {   // also catches NaN
+              range = true;
+            } else {
+              atomicAdd(reinterpret_cast<unsigned long long *>(dst + 4 * q + e),
+                        static_cast<unsigned long long>(__double2ll_rn(static_cast<double>(cval) * 4294967296.0)));
             }
           }
-          if (range) atomicOr(p.status, kStatusRange);
-        }
+        });
+        if (range) atomicOr(p.status, kStatusRange);
       }
       __syncwarp();   // the accumulator loads of the next item are warp-wide
     }

@@ -105,42 +105,36 @@ __global__ void __launch_bounds__(kThreads, 1) trellis_tc_dense_kernel(const __g
   job.rows = p.tokens - job.row0 < 256u ? p.tokens - job.row0 : 256u;
   const bool have = core_run(c, job, &map_a, &g_trellis_tc_status);
   if (have) {
-    // (row tile, block) items dealt to the two groups of four warps; a warp's lanes are the rows
-    // 32 (warp % 4) .. + 31 of the row tile
+    // the four (row tile, block) items go to the four groups of four warps; a warp's lanes are the
+    // rows 32 (warp % 4) .. + 31 of the row tile
     const uint32_t tiles = job.rows > 128u ? 2u : 1u, items = tiles * job.nblk;
-    for (uint32_t item = static_cast<uint32_t>(c.warp) >> 2; item < items; item += 2u) {
+    const uint32_t group = static_cast<uint32_t>(c.warp) >> 2, quad = static_cast<uint32_t>(c.warp) & 3u;
+    float *stash = reinterpret_cast<float *>(smem_raw + (c.base - smem_u32(smem_raw))) + group * 8192u + quad * 32u + static_cast<uint32_t>(c.lane);
+    for (uint32_t item = group; item < items; item += kDecoderWarps / 4) {
       const uint32_t tt = item / job.nblk, cb = item % job.nblk;
-      const uint32_t token = job.row0 + tt * 128u + (static_cast<uint32_t>(c.warp) & 3u) * 32u + static_cast<uint32_t>(c.lane);
-      float v[128];
-      load_block(c.tmem + (((static_cast<uint32_t>(c.warp) & 3u) * 32u) << 16) + tt * 256u + cb * 128u, v);
-      if (token < p.tokens) {
-        const float inv = p.inv[token];
+      const uint32_t token = job.row0 + tt * 128u + quad * 32u + static_cast<uint32_t>(c.lane);
+      const bool valid = token < p.tokens;
+      const uint32_t col0 = (cb == 0u ? job.blk0 : job.blk1) * 128u;
+      const uint2 *sv = reinterpret_cast<const uint2 *>(p.svh + col0);
+      uint2 *dst = reinterpret_cast<uint2 *>(p.y + static_cast<size_t>(valid ? token : 0u) * p.ldy + col0);
+      block_epilogue(c.tmem + ((quad * 32u) << 16) + tt * 256u + cb * 128u, valid ? p.inv[token] : 0.0f, valid, stash,
+                     [&](int q, const float (&r4)[4]) {
+                       const uint2 sw = sv[q];
+                       const __half2 s01 = *reinterpret_cast<const __half2 *>(&sw.x), s23 = *reinterpret_cast<const __half2 *>(&sw.y);
+                       float r[4] = {r4[0] * __low2float(s01), r4[1] * __high2float(s01), r4[2] * __low2float(s23), r4[3] * __high2float(s23)};
+                       if (p.epilogue != kEpiStore) {
+                         const uint2 old = dst[q];
+                         const float o[4] = {bf16_bits_to_f32(old.x & 0xFFFFu), __uint_as_float(old.x & 0xFFFF0000u),
+                                             bf16_bits_to_f32(old.y & 0xFFFFu), __uint_as_float(old.y & 0xFFFF0000u)};
 #pragma unroll
-        for (int i = 0; i < 128; ++i) v[i] *= inv;
-        hadamard128_regs(v);
-        const uint32_t col0 = (cb == 0u ? job.blk0 : job.blk1) * 128u;
-        const uint2 *sv = reinterpret_cast<const uint2 *>(p.svh + col0);
-        uint2 *dst = reinterpret_cast<uint2 *>(p.y + static_cast<size_t>(token) * p.ldy + col0);
-#pragma unroll
-        for (int q = 0; q < 32; ++q) {
-          const uint2 s = sv[q];
-          const __half2 s01 = *reinterpret_cast<const __half2 *>(&s.x), s23 = *reinterpret_cast<const __half2 *>(&s.y);
-          float r[4] = {v[4 * q] * __low2float(s01), v[4 * q + 1] * __high2float(s01), v[4 * q + 2] * __low2float(s23),
-                        v[4 * q + 3] * __high2float(s23)};
-          if (p.epilogue != kEpiStore) {
-            const uint2 old = dst[q];
-            const float o[4] = {bf16_bits_to_f32(old.x & 0xFFFFu), __uint_as_float(old.x & 0xFFFF0000u),
-                                bf16_bits_to_f32(old.y & 0xFFFFu), __uint_as_float(old.y & 0xFFFF0000u)};
-#pragma unroll
-            for (int e = 0; e < 4; ++e) r[e] = p.epilogue == kEpiAdd ? r[e] + o[e] : o[e] / (1.0f + __expf(-o[e])) * r[e];
-          }
-          const __nv_bfloat162 o01 = __floats2bfloat162_rn(r[0], r[1]), o23 = __floats2bfloat162_rn(r[2], r[3]);
-          uint2 packed;
-          packed.x = *reinterpret_cast<const uint32_t *>(&o01);
-          packed.y = *reinterpret_cast<const uint32_t *>(&o23);
-          dst[q] = packed;
-        }
-      }
+                         for (int e = 0; e < 4; ++e) r[e] = p.epilogue == kEpiAdd ? r[e] + o[e] : o[e] / (1.0f + __expf(-o[e])) * r[e];
+                       }
+                       const __nv_bfloat162 o01 = __floats2bfloat162_rn(r[0], r[1]), o23 = __floats2bfloat162_rn(r[2], r[3]);
+                       uint2 packed;
+                       packed.x = *reinterpret_cast<const uint32_t *>(&o01);
+                       packed.y = *reinterpret_cast<const uint32_t *>(&o23);
+                       dst[q] = packed;
+                     });
       __syncwarp();   // the accumulator loads of the next item are warp-wide
     }
   }

@@ -13,16 +13,19 @@
 //    down to 2^-28 of the row's largest; what lies below contributes less than that to any sum.
 //  * A CTA owns up to 256 rows (two MMA tiles of M = 128: the rows are the accumulator's lanes) and
 //    256 output columns (two 128-column Hadamard blocks: the MMA's N), and walks `in` in stages of
-//    64. Eight decoder warps turn the stage's 64 trellis tiles into fp16 in registers (the decode of
+//    64. Sixteen decoder warps (four per scheduler: the decode is a chain of dependent integer
+//    operations, and two warps per scheduler left it idle most cycles) turn the stage's 64
+//    trellis tiles into fp16 in registers (the decode of
 //    trellis_device.cuh: funnel shifts, IMAD, DP4A, half an HFMA2 per weight) and store them into
 //    the stage's B tile in the K-major 128-byte-swizzle layout the tensor core reads: a lane's
 //    eight values are four 4-byte stores that hit 32 different banks across the warp. A producer
 //    thread brings the rows' fp16 activations by TMA (the same swizzle); one thread issues
 //    tcgen05.mma kind::f16 (M 128, N 256, K 16; fp16 x fp16, fp32 accumulation in tensor memory).
 //    Every decoded tile serves both row tiles: 512 accumulator columns, all of tensor memory.
-//  * The epilogue reads a row's 128 accumulator columns of one block into registers, applies the
-//    row's inverse scale, the output Hadamard (in registers: the 128 values of a row and block sit in
-//    one thread), svh and the caller's epilogue.
+//  * The epilogue: a thread owns one row of one 128-column block. It reads the row's first 64
+//    accumulator columns, applies the row's inverse scale and six Hadamard stages in registers,
+//    parks the 64 values in the (by then idle) stage ring, does the same for the other 64 columns,
+//    and the seventh stage combines the two halves; then svh and the caller's epilogue.
 //  * Every mbarrier wait is bounded; a wait that runs out sets a bit of a status word and the CTA
 //    falls through to the common exit and frees its tensor memory.
 #ifndef B200Q_TRELLIS_TC_CUH
@@ -36,8 +39,8 @@ namespace trellis_tc {
 
 using namespace trellis_dev;
 
-constexpr int kThreads = 320;               // 8 decoder / epilogue warps, the producer warp, the MMA warp
-constexpr int kDecoderWarps = 8;
+constexpr int kDecoderWarps = 16;
+constexpr int kThreads = (kDecoderWarps + 2) * 32;   // the decoder / epilogue warps, the producer warp, the MMA warp
 constexpr uint32_t kStages = 3;
 constexpr uint32_t kABytes = 128 * 128;     // one row tile of a stage: 128 rows x 64 fp16
 constexpr uint32_t kBBytes = 256 * 128;     // one stage of decoded weights: 256 columns x 64 fp16
@@ -58,24 +61,25 @@ struct Job {
   uint32_t row0, rows;      // row0 is also the TMA row coordinate
 };
 
-// The raw words of the 8 tiles a decoder warp owns in one stage (2 tile columns x 4 tile rows), one
+// The raw words of the 4 tiles a decoder warp owns in one stage (1 tile column x 4 tile rows), one
 // word per lane and tile (two for the widths whose tiles have more than 32 words): lane l holds
 // word l of the tile, and the three words a lane's window needs come from its neighbours by shuffle.
 // A 16 x 16 tile is 4 k2 words, so one coalesced load of up to 128 bytes fetches a whole tile.
 template <int K2>
 struct StageWords {
   static constexpr int kPerTile = (4 * K2 + 31) / 32;
-  uint32_t w[2][4][kPerTile];
+  uint32_t w[4][kPerTile];
 };
 
 constexpr int kWordRing = 4;   // stages of raw words a decoder warp keeps in flight in registers
 
-// In-register Sylvester Hadamard of 128 values, natural order, times 1 / sqrt(128).
-__device__ __forceinline__ void hadamard128_regs(float (&v)[128]) {
+// Six stages of the in-register Sylvester Hadamard (natural order) on 64 values: one half of a
+// 128-wide transform, whose seventh stage pairs value i of one half with value i of the other.
+__device__ __forceinline__ void hadamard64_regs(float (&v)[64]) {
 #pragma unroll
-  for (int h = 1; h < 128; h <<= 1) {
+  for (int h = 1; h < 64; h <<= 1) {
 #pragma unroll
-    for (int i = 0; i < 128; ++i) {
+    for (int i = 0; i < 64; ++i) {
       if ((i & h) == 0) {
         const float a = v[i], b = v[i + h];
         v[i] = a + b;
@@ -83,23 +87,18 @@ __device__ __forceinline__ void hadamard128_regs(float (&v)[128]) {
       }
     }
   }
-#pragma unroll
-  for (int i = 0; i < 128; ++i) v[i] *= 0.08838834764831845f;
 }
 
 template <int K2>
 __device__ __forceinline__ void load_stage_words(StageWords<K2> &sw, const uint32_t *col0, int lane, uint64_t row_words, uint32_t ks) {
-  // tile rows 4 ks .. 4 ks + 3; the warp's second tile column is one tile (4 K2 words) further
+  // tile rows 4 ks .. 4 ks + 3 of the warp's tile column
   const uint32_t *base = col0 + static_cast<uint64_t>(ks) * 4u * row_words + lane;
 #pragma unroll
   for (int r = 0; r < 4; ++r) {
+    const uint32_t *t = base + static_cast<uint64_t>(r) * row_words;
 #pragma unroll
-    for (int j = 0; j < 2; ++j) {
-      const uint32_t *t = base + static_cast<uint64_t>(r) * row_words + j * 4 * K2;
-#pragma unroll
-      for (int h = 0; h < StageWords<K2>::kPerTile; ++h) {
-        sw.w[j][r][h] = (32 * h + lane < 4 * K2) ? __ldg(t + 32 * h) : 0u;
-      }
+    for (int h = 0; h < StageWords<K2>::kPerTile; ++h) {
+      sw.w[r][h] = (32 * h + lane < 4 * K2) ? __ldg(t + 32 * h) : 0u;
     }
   }
 }
@@ -119,15 +118,15 @@ template <int K2>
 __device__ __forceinline__ bool decode_stages(const Job &job, uint32_t stages_base, uint32_t bars, int warp, int lane, uint32_t *status) {
   const LaneWindow win = lane_window(K2, lane);
   const uint32_t k_stages = job.in / 64u;
-  const uint32_t cb = static_cast<uint32_t>(warp) >> 2;                    // which of the job's two column blocks
+  const uint32_t cb = static_cast<uint32_t>(warp) >> 3;                    // which of the job's two column blocks
   const uint32_t blk = cb == 0u ? job.blk0 : job.blk1;
-  const uint32_t tn = blk * 8u + (static_cast<uint32_t>(warp) & 3u) * 2u;   // the warp's first tile column in the plane
+  const uint32_t tn = blk * 8u + (static_cast<uint32_t>(warp) & 7u);        // the warp's tile column in the plane
   const uint64_t row_words = static_cast<uint64_t>(job.tile_stride) * 4u * K2;
   const uint32_t *col0 = job.trellis + static_cast<uint64_t>(tn) * 4u * K2;
   const bool live = cb < job.nblk;
   const uint32_t c0 = static_cast<uint32_t>(lane) >> 2, t = static_cast<uint32_t>(lane) & 3u;
-  // row n = 16 jj + c0 (+ 8) of the B tile, jj = 2 warp + j: 8-row group 4 warp + 2 j (+ 1)
-  const uint32_t lane_off = kABytes * 2u + (4u * static_cast<uint32_t>(warp)) * 1024u + c0 * 128u + 4u * t;
+  // row n = 16 warp + c0 (+ 8) of the B tile: 8-row group 2 warp (+ 1)
+  const uint32_t lane_off = kABytes * 2u + (2u * static_cast<uint32_t>(warp)) * 1024u + c0 * 128u + 4u * t;
   // The words of the next kWordRing stages are in flight in registers: a load issued when its
   // stage's slot of the ring was last decoded has several stage times to arrive (one stage ahead is
   // not enough: a stage is shorter than the latency of HBM).
@@ -151,20 +150,16 @@ __device__ __forceinline__ bool decode_stages(const Job &job, uint32_t stages_ba
       if (live) {
         const uint32_t tile = stages_base + slot * kStageBytes + lane_off;
 #pragma unroll
-        for (int j = 0; j < 2; ++j) {
-#pragma unroll
-          for (int r = 0; r < 4; ++r) {
-            const uint32_t w0 = tile_word<K2>(ring[d].w[j][r], win.w0), w1 = tile_word<K2>(ring[d].w[j][r], win.w1),
-                           w2 = tile_word<K2>(ring[d].w[j][r], win.w2);
-            uint32_t frag[4];
-            decode8<K2>(w0, w1, w2, win.off, frag);
-            const uint32_t at = tile + static_cast<uint32_t>(j) * 2048u;
-            const uint32_t lo = ((2u * r) ^ c0) << 4, hi = ((2u * r + 1u) ^ c0) << 4;
-            asm volatile("st.shared.b32 [%0], %1;" ::"r"(at + lo), "r"(frag[0]) : "memory");
-            asm volatile("st.shared.b32 [%0], %1;" ::"r"(at + hi), "r"(frag[1]) : "memory");
-            asm volatile("st.shared.b32 [%0], %1;" ::"r"(at + 1024u + lo), "r"(frag[2]) : "memory");
-            asm volatile("st.shared.b32 [%0], %1;" ::"r"(at + 1024u + hi), "r"(frag[3]) : "memory");
-          }
+        for (int r = 0; r < 4; ++r) {
+          const uint32_t w0 = tile_word<K2>(ring[d].w[r], win.w0), w1 = tile_word<K2>(ring[d].w[r], win.w1),
+                         w2 = tile_word<K2>(ring[d].w[r], win.w2);
+          uint32_t frag[4];
+          decode8<K2>(w0, w1, w2, win.off, frag);
+          const uint32_t lo = ((2u * r) ^ c0) << 4, hi = ((2u * r + 1u) ^ c0) << 4;
+          asm volatile("st.shared.b32 [%0], %1;" ::"r"(tile + lo), "r"(frag[0]) : "memory");
+          asm volatile("st.shared.b32 [%0], %1;" ::"r"(tile + hi), "r"(frag[1]) : "memory");
+          asm volatile("st.shared.b32 [%0], %1;" ::"r"(tile + 1024u + lo), "r"(frag[2]) : "memory");
+          asm volatile("st.shared.b32 [%0], %1;" ::"r"(tile + 1024u + hi), "r"(frag[3]) : "memory");
         }
         // the tile is read by the tensor core (async proxy): order these writes before it
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
@@ -189,8 +184,8 @@ __device__ __forceinline__ bool decode_stages_any(const Job &job, uint32_t stage
 
 // Shared-memory carve-up and the three roles up to the finished accumulator. On return with true,
 // the calling decoder warp may read the accumulators: tensor-memory columns [256 tt, 256 tt + 256)
-// hold row tile tt, lanes = rows, the job's block 0 in the first 128 columns of a tile. `tmem_out`
-// receives the base address. The caller ends with `finish()`.
+// hold row tile tt, lanes = rows, the job's block 0 in the first 128 columns of a tile. The caller
+// ends with core_finish().
 struct Core {
   uint32_t base, bars, bar_acc, tmem;
   uint32_t *tmem_slot;
@@ -289,15 +284,51 @@ __device__ __forceinline__ bool core_run(const Core &c, const Job &job, const CU
   return false;
 }
 
-// 128 accumulator columns of the calling thread's lane (= row) into registers.
-__device__ __forceinline__ void load_block(uint32_t taddr, float (&v)[128]) {
+// The epilogue of one (row tile, block) item for the calling warp: lanes = rows 32 (warp % 4) .. of
+// the row tile, `taddr` the tensor-memory address of the block's first column in those lanes. The
+// four warps of a group (warp / 4) share one item; `stash` is the group's 32 KB of the idle stage
+// ring ([value 64][thread 128] floats). `emit(q, r)` receives columns 4 q .. 4 q + 3 (q < 32) of the
+// row, already multiplied by `inv`, the Hadamard and 1 / sqrt(128); rows with `valid` false only
+// take part in the warp-wide accumulator loads.
+template <class Emit>
+__device__ __forceinline__ void block_epilogue(uint32_t taddr, float inv, bool valid, float *stash, Emit emit) {
+  float v[64];
 #pragma unroll
-  for (int q = 0; q < 4; ++q) {
-    uint32_t r[32];
-    tmem_ld32(taddr + 32u * q, r);
-    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+  for (int half = 0; half < 2; ++half) {
 #pragma unroll
-    for (int i = 0; i < 32; ++i) v[32 * q + i] = __uint_as_float(r[i]);
+    for (int q = 0; q < 2; ++q) {
+      uint32_t r[32];
+      tmem_ld32(taddr + 64u * half + 32u * q, r);
+      asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+      for (int i = 0; i < 32; ++i) v[32 * q + i] = __uint_as_float(r[i]) * inv;
+    }
+    if (valid) {
+      hadamard64_regs(v);
+      if (half == 0) {
+#pragma unroll
+        for (int i = 0; i < 64; ++i) stash[i * 128] = v[i];
+      }
+    }
+  }
+  if (!valid) return;
+  const float c = 0.08838834764831845f;   // 1 / sqrt(128)
+  // the seventh stage: columns i (sum) and 64 + i (difference); the differences wait in v
+#pragma unroll
+  for (int q = 0; q < 16; ++q) {
+    float r[4];
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      const float a = stash[(4 * q + e) * 128], b = v[4 * q + e];
+      r[e] = (a + b) * c;
+      v[4 * q + e] = (a - b) * c;
+    }
+    emit(q, r);
+  }
+#pragma unroll
+  for (int q = 0; q < 16; ++q) {
+    float r[4] = {v[4 * q], v[4 * q + 1], v[4 * q + 2], v[4 * q + 3]};
+    emit(16 + q, r);
   }
 }
 
