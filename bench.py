@@ -18,8 +18,8 @@ At N > 1 (launched under torch.distributed.run) configs[1] itself is cut in N: e
 sharded column-wise (output rows) over the ranks, total work fixed ("scaling": "strong"), and the
 outputs are rejoined where the next op needs the full width -- after `o`, after gate|up (down's
 K = 17408 input), after `down` -- by the products themselves: their epilogues store into every
-rank's buffer over NVLink and their last CTA publishes a flag the consumer's first instructions
-wait for (`--gather 3`, the default; 0 none, 1 NCCL all-gather, 2 a barrier launch per product;
+rank's buffer over NVLink and the barrier between the ranks rides in the first instructions of the
+consuming product (`--gather 3`, the default; 0 none, 1 NCCL all-gather, 2 a barrier launch per product;
 `--scaling weak` gives every rank a full layer set instead). The N > 1 line carries `config2`
 (the prefill GEMM N-sharded, both ways of sharing the quantized operand) and `config4` (MoE,
 expert-parallel with an NCCL all-to-all each way). Rank 0 prints one JSON line.
@@ -800,9 +800,8 @@ def run_cuda_arm(args) -> None:
         rejoined = ["o", "gate", "up", "down"]   # q | k | v feed attention heads that stay with their rank
         peer = shard.PeerOutputs({name: (tokens, outputs[name].shape[1] * world) for name in rejoined}, sets=2,
                                  points=["o", "gate_up", "down"])
-    # which rejoin point a call's input comes from, and which it publishes (the folded form)
-    waits_for = {"q": "down", "o": None, "gate": "o", "down": "gate_up"}
-    publishes = {"q": None, "o": "o", "gate": "gate_up", "down": "down"}
+    # the rejoin point a call's input comes from: its first instructions are that point's barrier
+    rejoin_of = {"q": "down", "o": None, "gate": "o", "down": "gate_up"}
 
     def one_step(policy: int = policy) -> None:
         for li, layer in enumerate(weights):
@@ -811,16 +810,14 @@ def run_cuda_arm(args) -> None:
                 src = inputs[by_name[names[0]][2]]
                 ws = [layer[nm] for nm in names]
                 if mode == 3:
-                    # the barrier rides in the products: the producer's last CTA publishes the point, the
-                    # consumer waits for it before it reads its activations
+                    # the barrier rides in the product that reads a gathered buffer (no barrier launch)
+                    point = rejoin_of[names[0]]
+                    sync = peer.sync(point) if point else None
                     if names[0] == "q":
-                        ptrs = [[outputs[nm].data_ptr()] for nm in names]
-                        nvfp4.linear_group_gather(src, ws, ptrs, [w.n for w in ws], [0] * len(ws), wait_for=peer.sync("down"))
+                        nvfp4.linear_group_gather(src, ws, [[outputs[nm].data_ptr()] for nm in names], [w.n for w in ws], [0] * len(ws), rejoin=sync)
                     else:
-                        wait = waits_for[names[0]]
                         nvfp4.linear_group_gather(src, ws, [peer.pointers(nm, which) for nm in names], [w.n * world for w in ws],
-                                                  [w.n * rank for w in ws], wait_for=peer.sync(wait) if wait else None,
-                                                  signal=peer.sync(publishes[names[0]]))
+                                                  [w.n * rank for w in ws], rejoin=sync)
                 elif mode == 2 and names[0] != "q":
                     # every rank's epilogue stores its columns into all ranks' full-width buffers; a
                     # barrier launch behind it is all that is left of the all-gather
@@ -921,8 +918,8 @@ def run_cuda_arm(args) -> None:
     collective = {0: "none (outputs stay sharded)",
                   1: "NCCL all-gather of every rejoined output (o, gate, up, down)",
                   2: "fused: epilogues store into every rank's buffer over NVLink, one device barrier launch per rejoined call",
-                  3: "fused, no barrier launch: epilogues store into every rank's buffer over NVLink (plain peer stores), the product's "
-                     "last CTA publishes a flag, the consuming product waits for it before reading its activations; rejoined after o, "
+                  3: "fused, no barrier launch: epilogues store into every rank's buffer over NVLink (plain peer stores); the barrier "
+                     "between the ranks rides in the first instructions of the product that reads the gathered buffer; rejoined after o, "
                      "gate|up and down, two buffers per point alternating by layer"}[mode]
     # dram bytes per launch of the dominant kernel, from the ncu capture of this exact configuration
     # (8 tokens, A16, grouped calls, one GPU): 196.97 MB per layer of four launches
@@ -1058,8 +1055,8 @@ def main() -> None:
     ap.add_argument("--scaling", default="strong", choices=["weak", "strong"],
                     help="decode workload under torchrun: strong = configs[1] cut in N (default), weak = per-GPU work fixed")
     ap.add_argument("--gather", type=int, default=3,
-                    help="decode workload under torchrun, how rejoined outputs reach every rank: 3 peer stores + a flag folded into "
-                         "producer and consumer (default), 2 peer stores + a barrier launch, 1 NCCL all-gather, 0 outputs stay sharded")
+                    help="decode workload under torchrun, how rejoined outputs reach every rank: 3 peer stores + the barrier folded into "
+                         "the consuming product (default), 2 peer stores + a barrier launch, 1 NCCL all-gather, 0 outputs stay sharded")
     ap.add_argument("--moe-tokens", type=int, default=4096, help="tokens of the --workload moe step (configs[4]: 4096; up to 8 takes the decode entry's item size)")
     ap.add_argument("--policy", choices=["a16", "a4"], default="a16",
                     help="decode workload: a16 (headline) or a4, the reference's AllowA4 policy (W4A4 from 4 / 5 / 8 tokens)")

@@ -55,7 +55,7 @@ NVFP4_SYMBOLS = {
                                                      C.c_uint32, C.c_void_p]),
     "b200q_nvfp4_linear_group_gather": (C.c_int32, [C.POINTER(C.POINTER(Nvfp4Weight)), C.c_uint32, C.c_void_p, C.c_uint32,
                                                     C.POINTER(C.c_void_p), C.c_uint32, C.POINTER(C.c_uint32), C.POINTER(C.c_uint32),
-                                                    C.c_uint32, C.POINTER(PeerSync), C.POINTER(PeerSync), C.c_void_p]),
+                                                    C.c_uint32, C.POINTER(PeerSync), C.c_void_p]),
     "b200q_peer_barrier": (C.c_int32, [C.c_void_p, C.c_uint32, C.c_uint32, C.c_uint32, C.c_void_p, C.c_void_p]),
     "b200q_nvfp4_mlp_workspace_bytes": (C.c_uint64, [C.c_uint32, C.c_uint32, C.c_uint32, C.c_uint32]),
     "b200q_nvfp4_mlp": (C.c_int32, [C.POINTER(Nvfp4Weight), C.POINTER(Nvfp4Weight), C.c_void_p, C.c_uint32, C.c_void_p, C.c_uint32,

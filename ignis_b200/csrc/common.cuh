@@ -199,7 +199,7 @@ __device__ __forceinline__ void peer_wait_flags(uint32_t *const *flags_peers, ui
         seen = true;
         break;
       }
-      __nanosleep(poll < 64u ? 40 : 400);
+      __nanosleep(poll < 4096u ? 250 : 1000);
     }
     if (!seen) atomicOr(state, 1u << lane);
   }

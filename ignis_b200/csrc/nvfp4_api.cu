@@ -49,14 +49,13 @@ PeerSync make_sync(const DeviceState &dev, const b200q_peer_sync *s) {
 
 int32_t decode_route(ErrorSlot &slot, const DeviceState &dev, const b200q_nvfp4_weight *const *w, uint32_t count,
                      const void *x, uint32_t tokens, void *const *y, const uint32_t *ldy, uint32_t epilogue,
-                     cudaStream_t stream, uint32_t peers = 1, const b200q_peer_sync *wait_for = nullptr,
-                     const b200q_peer_sync *signal = nullptr) {
+                     cudaStream_t stream, uint32_t peers = 1, const b200q_peer_sync *wait_for = nullptr) {
   const uint32_t k = w[0]->k;
   const bool swiglu = (epilogue & kEpilogueSwiglu) != 0u;
   const size_t out_elem = (epilogue & kEpilogueF32) ? 4u : 2u;
   uint32_t groups = 0;
   for (uint32_t i = 0; i < count; ++i) groups += w[i]->n / 32u;
-  if (dev.a16_mma != 0 && tokens > 16u && !swiglu && peers == 1u && wait_for == nullptr && signal == nullptr && a16mma_takes(k, x)) {
+  if (dev.a16_mma != 0 && tokens > 16u && !swiglu && peers == 1u && wait_for == nullptr && a16mma_takes(k, x)) {
     // beyond two token tiles the warp-level MMAs of the decode kernel are the limit: the weights
     // are decoded once per tile of up to 256 tokens and multiplied on the tensor cores
     {
@@ -89,9 +88,7 @@ int32_t decode_route(ErrorSlot &slot, const DeviceState &dev, const b200q_nvfp4_
     p.ksteps = (k + 255u) / 256u;
     p.tokens = pass;
     p.epilogue = epilogue;
-    // a call of several passes waits before its first and publishes after its last
-    if (t0 == 0) p.wait = make_sync(dev, wait_for);
-    if (t0 + B200Q_NVFP4_DECODE_MAX_TOKENS >= tokens) p.signal = make_sync(dev, signal);
+    if (t0 == 0) p.wait = make_sync(dev, wait_for);   // a call of several passes waits before its first
     const GemvPlan plan = gemv_plan(dev, groups, p.ksteps, nt, swiglu);
     const uint32_t rows_per_cta = static_cast<uint32_t>(swiglu ? plan.rm / 2 : plan.rm);
     uint32_t ctas = 0;
@@ -348,7 +345,7 @@ int32_t check_sync(ErrorSlot &slot, const b200q_peer_sync *s, const char *what, 
 
 int32_t scatter_impl(const b200q_nvfp4_weight *const *w, uint32_t count, const void *x, uint32_t tokens, void *const *y_peers,
                      uint32_t peers, const uint32_t *ldy, const uint32_t *col_offset, uint32_t epilogue,
-                     const b200q_peer_sync *wait_for, const b200q_peer_sync *signal, void *stream, const char *what) {
+                     const b200q_peer_sync *wait_for, void *stream, const char *what) {
   ErrorSlot &slot = nvfp4_error();
   if (w == nullptr || y_peers == nullptr || ldy == nullptr || col_offset == nullptr) return fail(slot, "%s: NULL argument array", what);
   if (count == 0 || count > B200Q_NVFP4_MAX_GROUP) return fail(slot, "%s: count = %u is outside 1..%d", what, count, B200Q_NVFP4_MAX_GROUP);
@@ -356,7 +353,7 @@ int32_t scatter_impl(const b200q_nvfp4_weight *const *w, uint32_t count, const v
   if (tokens == 0) return fail(slot, "%s: tokens must be positive", what);
   if ((epilogue & ~static_cast<uint32_t>(B200Q_NVFP4_OUT_F32)) != 0u) return fail(slot, "%s: only STORE (optionally OUT_F32) is served", what);
   if (x == nullptr || !aligned(x, 16)) return fail(slot, "%s: x is NULL or not 16-byte aligned", what);
-  if (check_sync(slot, wait_for, what, "wait_for") != 0 || check_sync(slot, signal, what, "signal") != 0) return -1;
+  if (check_sync(slot, wait_for, what, "rejoin") != 0) return -1;
   const size_t out_elem = (epilogue & kEpilogueF32) ? 4u : 2u;
   void *targets[B200Q_NVFP4_MAX_GROUP * kMaxPeers];
   for (uint32_t i = 0; i < count; ++i) {
@@ -370,23 +367,20 @@ int32_t scatter_impl(const b200q_nvfp4_weight *const *w, uint32_t count, const v
   }
   const DeviceState *dev = prepared_state(slot, what);
   if (dev == nullptr) return -1;
-  return decode_route(slot, *dev, w, count, x, tokens, targets, ldy, epilogue, static_cast<cudaStream_t>(stream), peers, wait_for, signal);
+  return decode_route(slot, *dev, w, count, x, tokens, targets, ldy, epilogue, static_cast<cudaStream_t>(stream), peers, wait_for);
 }
 }  // namespace
 
 int32_t b200q_nvfp4_linear_group_scatter(const b200q_nvfp4_weight *const *w, uint32_t count, const void *x, uint32_t tokens,
                                          void *const *y_peers, uint32_t peers, const uint32_t *ldy, const uint32_t *col_offset,
                                          uint32_t epilogue, void *stream) {
-  return scatter_impl(w, count, x, tokens, y_peers, peers, ldy, col_offset, epilogue, nullptr, nullptr, stream,
-                      "b200q_nvfp4_linear_group_scatter");
+  return scatter_impl(w, count, x, tokens, y_peers, peers, ldy, col_offset, epilogue, nullptr, stream, "b200q_nvfp4_linear_group_scatter");
 }
 
 int32_t b200q_nvfp4_linear_group_gather(const b200q_nvfp4_weight *const *w, uint32_t count, const void *x, uint32_t tokens,
                                         void *const *y_peers, uint32_t peers, const uint32_t *ldy, const uint32_t *col_offset,
-                                        uint32_t epilogue, const b200q_peer_sync *wait_for, const b200q_peer_sync *signal,
-                                        void *stream) {
-  return scatter_impl(w, count, x, tokens, y_peers, peers, ldy, col_offset, epilogue, wait_for, signal, stream,
-                      "b200q_nvfp4_linear_group_gather");
+                                        uint32_t epilogue, const b200q_peer_sync *rejoin, void *stream) {
+  return scatter_impl(w, count, x, tokens, y_peers, peers, ldy, col_offset, epilogue, rejoin, stream, "b200q_nvfp4_linear_group_gather");
 }
 
 uint64_t b200q_nvfp4_mlp_workspace_bytes(uint32_t gate_up_n, uint32_t k, uint32_t policy, uint32_t tokens) {

@@ -321,10 +321,24 @@ __global__ void __launch_bounds__(kThreads, NT <= 2 ? 2 : 1) nvfp4_gemv_kernel(c
   griddep_launch_dependents();
   griddep_wait();
   if (p.wait.flags_peers != nullptr) {
-    // x was stored into this rank's buffer by every rank's product of the same point: this rank's
-    // own product (earlier in the stream, finished) counted the point in state[1]; wait until
-    // every rank's flag has reached that count
-    if (warp == 0) peer_wait_flags(p.wait.flags_peers, p.wait.state, p.wait.peers, p.wait.rank, p.wait.polls, ld_acquire_gpu(p.wait.state + 1), lane);
+    // x lies in a buffer every rank's previous product stored its columns into. The barrier between
+    // the ranks rides here, in the consumer's first instructions, instead of in a launch of its own:
+    // this rank's product has finished and its stores (peer stores included) are complete - that is
+    // what griddep_wait / stream order gives - so the grid's first CTA publishes barrier number
+    // state[1] + 1 in this rank's slot of every rank's flag array, and every CTA waits until all
+    // slots of its own rank's array have reached it. The last CTA through counts the barrier.
+    if (warp == 0) {
+      const uint32_t epoch = ld_acquire_gpu(p.wait.state + 1) + 1u;
+      if (blockIdx.x == 0 && static_cast<uint32_t>(lane) < p.wait.peers) {
+        __threadfence_system();
+        st_release_sys(p.wait.flags_peers[lane] + p.wait.rank, epoch);
+      }
+      peer_wait_flags(p.wait.flags_peers, p.wait.state, p.wait.peers, p.wait.rank, p.wait.polls, epoch, lane);
+      if (lane == 0 && atomicAdd(p.wait.state + 2, 1u) == gridDim.x - 1u) {   // every CTA has read state[1]
+        atomicExch(p.wait.state + 2, 0u);
+        atomicAdd(p.wait.state + 1, 1u);
+      }
+    }
     __syncthreads();
   }
 
@@ -467,28 +481,6 @@ __global__ void __launch_bounds__(kThreads, NT <= 2 ? 2 : 1) nvfp4_gemv_kernel(c
     }
   }
   cluster_sync_all();  // no CTA leaves while a peer may still read its partial sums
-  if (p.signal.flags_peers != nullptr) {
-    // The all-gather's barrier, folded into the product. The CTA's stores (into every rank's buffer)
-    // are ordered before its first thread by the CTA barrier; that one thread makes them visible
-    // system-wide (one fence per CTA: a system-scope fence waits for the peers' acknowledgements,
-    // and hundreds of threads issuing it queue behind each other) and arrives at a counter. The
-    // launch's last CTA numbers the point and publishes the number in this rank's slot of every
-    // rank's flag array.
-    __syncthreads();
-    if (warp == 0) {
-      uint32_t epoch = 0;
-      if (lane == 0) {
-        __threadfence_system();
-        if (atomicAdd(p.signal.state + 2, 1u) == gridDim.x - 1u) {
-          atomicExch(p.signal.state + 2, 0u);
-          epoch = atomicAdd(p.signal.state + 1, 1u) + 1u;
-          __threadfence_system();
-        }
-      }
-      epoch = __shfl_sync(0xFFFFFFFFu, epoch, 0);
-      if (epoch != 0u && static_cast<uint32_t>(lane) < p.signal.peers) st_release_sys(p.signal.flags_peers[lane] + p.signal.rank, epoch);
-    }
-  }
 }
 
 constexpr size_t kGemvMaxSmem = 160 * 1024;

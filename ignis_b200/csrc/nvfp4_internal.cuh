@@ -18,8 +18,8 @@ constexpr uint32_t kMaxPeers = 8;  // ranks of one node a scattered product writ
 
 // One synchronization point between the ranks of a node (b200q_peer_sync): every rank owns an array
 // of `peers` flags (slot s written by rank s) that all ranks have mapped, and three words of its
-// own: state[0] ranks that missed a wait, state[1] the number of times this rank has published the
-// point, state[2] an arrival counter of the publishing launch's CTAs.
+// own: state[0] ranks that missed a wait, state[1] the barriers completed at this point, state[2] an
+// arrival counter of the waiting launch's CTAs.
 struct PeerSync {
   uint32_t *const *flags_peers;  // device array of `peers` pointers; nullptr: not used
   uint32_t *state;
@@ -49,8 +49,7 @@ struct GemvParams {
   uint32_t rm;        // 32-row groups per CTA: 1, 2, 4 or 8
   uint32_t kc;        // cluster size: K slices across CTAs
   uint32_t xs_steps;  // steps of activation fragments shared memory holds at a time
-  PeerSync wait;      // before x is read: every rank has published the point that produced it
-  PeerSync signal;    // after the outputs are stored (into every rank's buffer): publish this point
+  PeerSync wait;      // before x is read: a barrier between the ranks (every rank's shard of x has landed)
 };
 
 struct GemvPlan {

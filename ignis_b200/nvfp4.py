@@ -257,11 +257,10 @@ def linear_group_scatter(x: torch.Tensor, weights: list[Weight], peer_ptrs: list
 
 
 def linear_group_gather(x: torch.Tensor, weights: list[Weight], peer_ptrs: list[list[int]], ldy: list[int],
-                        col_offset: list[int], wait_for=None, signal=None, epilogue: int = STORE) -> None:
-    """``b200q_nvfp4_linear_group_gather``: :func:`linear_group_scatter` with the all-gather's barrier
-    folded in. `wait_for` / `signal` are ``_lib.PeerSync`` structs (``shard.PeerOutputs.sync``) or
-    None: the call waits, before it reads `x`, until every rank has published the point that
-    produced `x`, and publishes its own point when its stores into all ranks' buffers are done."""
+                        col_offset: list[int], rejoin=None, epilogue: int = STORE) -> None:
+    """``b200q_nvfp4_linear_group_gather``: :func:`linear_group_scatter` whose first instructions are
+    the barrier between the ranks. `rejoin` is a ``_lib.PeerSync`` (``shard.PeerOutputs.sync``) naming
+    the point whose gathered buffer `x` is, or None for an input that needs no barrier."""
     _check_x(x, weights[0].k)
     count, peers = len(weights), len(peer_ptrs[0])
     structs = [w.c_struct() for w in weights]
@@ -270,8 +269,7 @@ def linear_group_gather(x: torch.Tensor, weights: list[Weight], peer_ptrs: list[
     ld = (C.c_uint32 * count)(*ldy)
     co = (C.c_uint32 * count)(*col_offset)
     _check(_lib.load().b200q_nvfp4_linear_group_gather(wp, count, x.data_ptr(), x.shape[0], yp, peers, ld, co, epilogue,
-                                                        C.byref(wait_for) if wait_for is not None else None,
-                                                        C.byref(signal) if signal is not None else None, _stream()))
+                                                        C.byref(rejoin) if rejoin is not None else None, _stream()))
 
 
 def peer_barrier(flags_peers: torch.Tensor, peers: int, rank: int, epoch: int, status: torch.Tensor) -> None:

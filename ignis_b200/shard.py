@@ -46,8 +46,8 @@ class PeerOutputs:
     that order writers and readers. With them a sharded product stores its columns straight into
     all ranks' buffers and the all-gather shrinks to a flag: either a barrier launch behind the
     product (``nvfp4.linear_group_scatter`` + :meth:`barrier`) or nothing at all
-    (``nvfp4.linear_group_gather`` with :meth:`sync`: the product's last CTA publishes the point,
-    the consumer's first instructions wait for it).
+    (``nvfp4.linear_group_gather`` with :meth:`sync`: the barrier rides in the first instructions of
+    the product that reads the gathered buffer).
 
     `sets` buffers exist per name; callers alternate them (layer parity) so that a rank which runs
     ahead never stores into a buffer another rank still reads (see the reuse rule in

@@ -159,31 +159,31 @@ int32_t b200q_nvfp4_linear_group_scatter(const b200q_nvfp4_weight *const *w, uin
 int32_t b200q_peer_barrier(uint32_t *const *flags_peers, uint32_t peers, uint32_t rank, uint32_t epoch,
                            uint32_t *status, void *stream);
 
-/* The same all-gather with no barrier launch at all: the barrier's two halves ride in the product
- * that writes a gathered buffer and in the product that reads it. Not in the reference.
+/* The same all-gather with no barrier launch at all: the barrier rides in the first instructions of
+ * the product that READS the gathered buffer. Not in the reference.
+ *
+ * b200q_nvfp4_linear_group_gather is b200q_nvfp4_linear_group_scatter with one more argument. With
+ * `rejoin` non-NULL the call's x is a buffer that every rank's previous call in its stream stored
+ * its columns into (a scatter or gather product, or any kernel): before the call reads x, its first
+ * CTA publishes the next barrier number of the point in slot `rank` of every rank's flag array
+ * (system-scope release; this rank's own stores into the buffers are complete, being an earlier
+ * kernel of the same stream) and every CTA waits until all slots of this rank's own array have
+ * reached that number. The wait is bounded like b200q_peer_barrier's; when it runs out the call goes
+ * on, state[0] says who was missing and the output is not valid.
  *
  * A b200q_peer_sync names one point of a layer where outputs are rejoined (after `o`, after
  * gate|up, after `down`): flags_peers as for b200q_peer_barrier (a DEVICE array of `peers` pointers,
  * entry p rank p's flag array of `peers` uint32, zero at start), and `state`, three uint32 of this
  * rank's device memory, zero at start: [0] bit p set when rank p was missing from a wait that ran
- * out, [1] how often this rank has published the point, [2] an arrival counter.
- *   signal:   the call's last CTA - after every CTA's stores into all ranks' buffers are visible -
- *             adds one to state[1] and stores that number into slot `rank` of every rank's flag
- *             array (system-scope release).
- *   wait_for: before the call reads x it waits until every slot of this rank's own flag array has
- *             reached this rank's state[1]: every rank's shard of x has landed. The wait is bounded
- *             like b200q_peer_barrier's; when it runs out the call goes on, state[0] says who was
- *             missing and the output is not valid. The call that publishes a point on this rank
- *             must precede, in stream order, the call that waits for it.
- * Either may be NULL; with peers = 1 and both NULL this is b200q_nvfp4_linear_group. All ranks make
- * the same sequence of calls. Counting happens on the device, so a captured sequence replays.
+ * out, [1] barriers completed at this point, [2] an arrival counter. All ranks make the same
+ * sequence of calls. Counting happens on the device, so a captured sequence replays. With peers = 1
+ * and `rejoin` NULL this is b200q_nvfp4_linear_group.
  *
  * Reuse rule for a gathered buffer: rank A's next product into a buffer may start while rank B
  * still reads the buffer's previous contents unless something orders them. Give every point TWO
- * buffers used alternately (layer parity): a rank cannot publish a point for the second time
- * after a buffer's use before every rank has finished reading that use, because in between it
- * waits for the other ranks to publish the NEXT point, which they do only after their readers of
- * this one are done (stream order). The same rule makes b200q_nvfp4_linear_group_scatter +
+ * buffers used alternately (layer parity): before a rank stores into a buffer for the second time
+ * after a use, it has passed the point's NEXT barrier, which every other rank joins only after its
+ * reader of that use is done (stream order). The same rule makes b200q_nvfp4_linear_group_scatter +
  * b200q_peer_barrier safe; with a single buffer per point put a second barrier behind the reader. */
 typedef struct b200q_peer_sync {
   uint32_t *const *flags_peers;
@@ -194,7 +194,7 @@ typedef struct b200q_peer_sync {
 int32_t b200q_nvfp4_linear_group_gather(const b200q_nvfp4_weight *const *w, uint32_t count, const void *x,
                                         uint32_t tokens, void *const *y_peers, uint32_t peers, const uint32_t *ldy,
                                         const uint32_t *col_offset, uint32_t epilogue,
-                                        const b200q_peer_sync *wait_for, const b200q_peer_sync *signal, void *stream);
+                                        const b200q_peer_sync *rejoin, void *stream);
 
 /* The layers' MLP: y (+)= down(silu(g) * u), g | u = gate_up x. reference:
  * ignis::prefill_swiglu::mlp (kernel/src/prefill_swiglu.h:100-107) and, below its widths, the

@@ -62,9 +62,9 @@ def _worker(rank: int, world: int, port: int, failures) -> None:
 
 def _chain_worker(rank: int, world: int, port: int, failures) -> None:
     """A chain of sharded products with no host synchronisation between them: layer i's product
-    stores its columns into every rank's buffer i % 2 of point "y" and publishes the point from
-    its last CTA; layer i's consumer (a second sharded product over that buffer, which waits for the
-    point in its first instructions) follows at once, and layer i + 1 re-uses the other buffer. The
+    stores its columns into every rank's buffer i % 2 of point "y"; layer i's consumer (a second
+    sharded product over that buffer, whose first instructions are the barrier between the ranks)
+    follows at once, and layer i + 1 re-uses the other buffer. The
     activations of every layer differ, so a rank that read a buffer too early, or had it overwritten
     too early, gets other bits than the unsharded chain computed on one GPU."""
     sys.path.insert(0, ROOT)
@@ -97,8 +97,8 @@ def _chain_worker(rank: int, world: int, port: int, failures) -> None:
         def chain():
             for i, x in enumerate(xs):
                 which = i % 2
-                nvfp4.linear_group_gather(x, [m1], [peer.pointers("y", which)], [n], [rank * m1.n], signal=peer.sync("y"))
-                nvfp4.linear_group_gather(peer.views[("y", which)], [m2], [[outs[i].data_ptr()]], [m2.n], [0], wait_for=peer.sync("y"))
+                nvfp4.linear_group_gather(x, [m1], [peer.pointers("y", which)], [n], [rank * m1.n])
+                nvfp4.linear_group_gather(peer.views[("y", which)], [m2], [[outs[i].data_ptr()]], [m2.n], [0], rejoin=peer.sync("y"))
 
         chain()                                      # eager, no synchronisation inside
         torch.cuda.synchronize()
@@ -134,10 +134,11 @@ def test_gather_folded_into_producer_and_consumer_over_alternating_buffers():
     assert not list(failures), list(failures)
 
 
-def test_wait_for_a_point_nobody_published_gives_up_and_reports():
-    """One GPU plays rank 0 of two: its own product publishes the point, rank 1 never does, and the
-    consumer's bounded wait runs out (B200Q_PEER_BARRIER_POLLS = 2000), records rank 1 in state[0]
-    and lets the call finish; with the missing flag written by hand the same call waits for nothing."""
+def test_barrier_in_the_consumer_gives_up_and_reports_when_a_rank_is_missing():
+    """One GPU plays rank 0 of two: the consumer's first CTA publishes this rank's flag in both
+    ranks' arrays, rank 1 never does, and the bounded wait runs out (B200Q_PEER_BARRIER_POLLS = 2000),
+    records rank 1 in state[0] and lets the call finish; with the missing flag written by hand the
+    next call passes, and the barrier number has moved on by one each time."""
     sys.path.insert(0, ROOT)
     from ignis_b200 import _lib, nvfp4
 
@@ -158,19 +159,19 @@ def test_wait_for_a_point_nobody_published_gives_up_and_reports():
         sync = _lib.PeerSync(flags.data_ptr(), state.data_ptr(), 2, 0)
         y = torch.empty(4, 256, dtype=torch.bfloat16, device="cuda")
         z = torch.empty(4, 256, dtype=torch.bfloat16, device="cuda")
-        nvfp4.linear_group_gather(x, [w], [[y.data_ptr(), z.data_ptr()]], [256], [0], signal=sync)   # "both ranks'" buffers are local
+        nvfp4.linear_group_gather(x, [w], [[y.data_ptr(), z.data_ptr()]], [256], [0])   # "both ranks'" buffers are local; no barrier
         torch.cuda.synchronize()
-        assert torch.equal(y, want) and torch.equal(z, want)
-        assert state.tolist()[:3] == [0, 1, 0] and mine.tolist() == [1, 0] and theirs.tolist() == [1, 0]
+        assert torch.equal(y, want) and torch.equal(z, want) and state.tolist()[:3] == [0, 0, 0]
         out = torch.empty(4, 256, dtype=torch.bfloat16, device="cuda")
-        nvfp4.linear_group_gather(x, [w], [[out.data_ptr()]], [256], [0], wait_for=sync)
+        nvfp4.linear_group_gather(x, [w], [[out.data_ptr()]], [256], [0], rejoin=sync)
         torch.cuda.synchronize()
-        assert state.tolist()[0] == 0b10             # rank 1 never published; the call still returned
+        assert state.tolist()[:3] == [0b10, 1, 0]     # rank 1 never published; the call still returned and counted the barrier
+        assert mine.tolist() == [1, 0] and theirs.tolist() == [1, 0]
         state[0] = 0
-        mine[1] = 1                                   # rank 1's flag, by hand
-        nvfp4.linear_group_gather(x, [w], [[out.data_ptr()]], [256], [0], wait_for=sync)
+        mine[1] = 2                                   # rank 1's flag for the next barrier, by hand
+        nvfp4.linear_group_gather(x, [w], [[out.data_ptr()]], [256], [0], rejoin=sync)
         torch.cuda.synchronize()
-        assert state.tolist()[0] == 0 and torch.equal(out, want)
+        assert state.tolist()[:3] == [0, 2, 0] and mine.tolist() == [2, 2] and torch.equal(out, want)
     finally:
         if old is None:
             del os.environ["B200Q_PEER_BARRIER_POLLS"]
