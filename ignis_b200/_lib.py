@@ -117,6 +117,12 @@ class MoePlan(C.Structure):
                 ("total", C.c_uint64)]
 
 
+class MoeGeometry(C.Structure):
+    """``b200q_moe_geometry``: hidden, inter, experts, top_k."""
+
+    _fields_ = [("hidden", C.c_uint32), ("inter", C.c_uint32), ("experts", C.c_uint32), ("top_k", C.c_uint32)]
+
+
 _experts_args = [C.c_void_p, C.c_uint32, C.c_void_p, C.c_void_p, C.c_void_p, C.POINTER(MoeWorkspace), C.c_void_p, C.c_void_p]
 MOE_SYMBOLS = {
     "b200q_moe_set_geometry": (C.c_int32, [C.c_uint32] * 4),
@@ -138,6 +144,19 @@ MOE_SYMBOLS = {
     "ignis_moe_workspace_status": (C.c_int32, [C.POINTER(MoeWorkspace), C.c_void_p, C.POINTER(C.c_uint32)]),
     "ignis_moe_last_error": (C.c_char_p, []),
 }
+_G = C.POINTER(MoeGeometry)
+MOE_SYMBOLS.update({
+    "b200q_moe_record_bytes": (C.c_int32, [_G] + MOE_SYMBOLS["ignis_moe_record_bytes"][1]),
+    "b200q_moe_workspace_bytes": (C.c_uint64, [_G] + MOE_SYMBOLS["ignis_moe_workspace_bytes"][1]),
+    "b200q_moe_workspace_init": (C.c_int32, [_G] + MOE_SYMBOLS["ignis_moe_workspace_init"][1]),
+    "b200q_moe_plan_bytes": (C.c_int32, [_G] + MOE_SYMBOLS["ignis_moe_plan_bytes"][1]),
+    "b200q_moe_router_logits": (C.c_int32, [_G] + MOE_SYMBOLS["ignis_moe_router_logits"][1]),
+    "b200q_moe_router": (C.c_int32, [_G] + MOE_SYMBOLS["ignis_moe_router"][1]),
+    "b200q_moe_experts_decode": (C.c_int32, [_G] + _experts_args),
+    "b200q_moe_experts_prefill": (C.c_int32, [_G] + _experts_args),
+    "b200q_moe_shared_expert": (C.c_int32, [_G] + MOE_SYMBOLS["ignis_moe_shared_expert"][1]),
+    "b200q_moe_combine": (C.c_int32, [_G] + MOE_SYMBOLS["ignis_moe_combine"][1]),
+})
 
 ALL_SYMBOLS = {**NVFP4_SYMBOLS, **TRELLIS_SYMBOLS, **MOE_SYMBOLS}
 

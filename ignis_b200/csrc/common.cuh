@@ -40,7 +40,6 @@ struct DeviceState {
   int gemv_ctas_per_sm = 2;
   int gemv_slots[9] = {};  // CTAs of the NVFP4 decode kernel resident at once, by cluster size (0: unknown)
   int a16_mma = 1;       // B200Q_A16_MMA: A16 calls of more than 8 tokens take the tensor-core kernel
-  int w4a4_persistent = 1;  // B200Q_W4A4_PERSISTENT: one CTA per SM walking the tiles
   int a4_decode = 1;     // B200Q_A4_DECODE: AllowA4 calls of up to 32 tokens take the W4A4 decode kernel (0: the A16 route)
   int a4_slots[9] = {};      // CTAs of the W4A4 decode kernel placed at one per SM, by cluster size (0: unknown)
   int trellis_kc_max = 8;    // B200Q_TRELLIS_KC_MAX: largest cluster the trellis linear plans (measurement knob)
@@ -49,8 +48,7 @@ struct DeviceState {
   int a4_decode_groups = 0;  // B200Q_A4_DECODE_GROUPS: quantizer groups per CTA of that kernel (0: chosen by the token count)
   int a4_decode_ctas = 2;  // B200Q_A4_DECODE_CTAS: CTAs of that kernel per SM (1: one CTA with a ring twice as deep)
   int a16_mma_wide = 1;  // B200Q_A16_MMA_WIDE: beyond 256 tokens the A16 tensor-core kernel takes token tiles of 512 (two accumulators per decoded stage)
-  int w4a4_pair = 1;     // B200Q_W4A4_PAIR: the prefill GEMM on CTA pairs (cta_group::2, 256 x 256 tiles); 0: one CTA per tile
-  int w4a4_bn = 128;     // B200Q_W4A4_BN: weight rows per tile of the plain W4A4 product (128 or 256)
+  int w4a4_pair = 1;     // B200Q_W4A4_PAIR: the prefill GEMM on CTA pairs (cta_group::2, 256 x 256 tiles); 0: one CTA per 128 x 256 tile
   int gemv_xu = 8;       // B200Q_GEMV_XU: words per row of 8 decoded by the hardware E2M1 conversion
   int sm_cap = 0;        // IGNIS_TRELLIS_SM_CAP
   int moe_tc = 1;        // B200Q_MOE_TC: expert calls of more than 64 tokens take the tensor-core kernels

@@ -29,10 +29,22 @@ using namespace trellis_dev;
 constexpr int kThreads = 256;
 constexpr int kWarps = 8;
 
-struct Geometry {
-  uint32_t hidden = IGNIS_MOE_HIDDEN, inter = IGNIS_MOE_INTERMEDIATE, experts = IGNIS_MOE_EXPERTS, top_k = IGNIS_MOE_TOP_K;
-};
-Geometry g_geo;
+using Geometry = b200q_moe_geometry;
+// The geometry the reference's own entry points (no geometry argument) work at: the reference
+// compiles it in; here it starts at the reference's and b200q_moe_set_geometry replaces it.
+Geometry g_default = {IGNIS_MOE_HIDDEN, IGNIS_MOE_INTERMEDIATE, IGNIS_MOE_EXPERTS, IGNIS_MOE_TOP_K};
+
+int32_t check_geometry(ErrorSlot &slot, const Geometry *g, const char *what) {
+  if (g == nullptr) return fail(slot, "%s: geometry is NULL", what);
+  if (g->hidden == 0 || (g->hidden % 128u) != 0 || g->inter == 0 || (g->inter % 128u) != 0) {
+    return fail(slot, "%s: hidden and inter must be positive multiples of 128", what);
+  }
+  if (g->experts == 0 || g->experts > 4096u || g->top_k == 0 || g->top_k > 32u || g->top_k > g->experts) {
+    return fail(slot, "%s: experts must lie in 1..4096 and top_k in 1..min(32, experts)", what);
+  }
+  if (g->hidden / 128u > 8u * 40u || g->inter / 128u > 8u * 40u) return fail(slot, "%s: dimension too long", what);
+  return 0;
+}
 
 // Workspace regions for `tokens_max` tokens.
 struct Layout {
@@ -758,7 +770,7 @@ const DeviceState *prepared(ErrorSlot &slot, const char *what) {
   return dev;
 }
 
-int32_t run_experts(const void *x, uint32_t tokens, const int32_t *ids, const float *weights, const ignis_moe_slot *slots,
+int32_t run_experts(const Geometry &g, const void *x, uint32_t tokens, const int32_t *ids, const float *weights, const ignis_moe_slot *slots,
                     const ignis_moe_workspace *workspace, int64_t *acc, void *stream_v, uint32_t limit, uint32_t item_rows,
                     const char *what) {
   ErrorSlot &slot = moe_error();
@@ -770,7 +782,6 @@ int32_t run_experts(const void *x, uint32_t tokens, const int32_t *ids, const fl
   if (!aligned(x, 16) || !aligned(workspace->base, 256)) return fail(slot, "%s: x must be 16-byte and the workspace 256-byte aligned", what);
   const DeviceState *dev = prepared(slot, what);
   if (dev == nullptr) return -1;
-  const Geometry g = g_geo;
   const uint32_t tokens_max = workspace->decode_tokens > workspace->prefill_tokens ? workspace->decode_tokens : workspace->prefill_tokens;
   const Layout l = layout_for(g, tokens_max);
   uint8_t *base = static_cast<uint8_t *>(workspace->base);
@@ -853,23 +864,16 @@ using namespace b200q;
 extern "C" {
 
 int32_t b200q_moe_set_geometry(uint32_t hidden, uint32_t inter, uint32_t experts, uint32_t top_k) {
-  ErrorSlot &slot = moe_error();
-  if (hidden == 0 || (hidden % 128u) != 0 || inter == 0 || (inter % 128u) != 0) {
-    return fail(slot, "b200q_moe_set_geometry: hidden and inter must be positive multiples of 128");
-  }
-  if (experts == 0 || experts > 4096u || top_k == 0 || top_k > 32u || top_k > experts) {
-    return fail(slot, "b200q_moe_set_geometry: experts must lie in 1..4096 and top_k in 1..min(32, experts)");
-  }
-  if (hidden / 128u > 8u * 40u || inter / 128u > 8u * 40u) return fail(slot, "b200q_moe_set_geometry: dimension too long");
-  g_geo.hidden = hidden;
-  g_geo.inter = inter;
-  g_geo.experts = experts;
-  g_geo.top_k = top_k;
+  const Geometry g = {hidden, inter, experts, top_k};
+  if (check_geometry(moe_error(), &g, "b200q_moe_set_geometry") != 0) return -1;
+  g_default = g;
   return 0;
 }
 
-int32_t ignis_moe_record_bytes(uint32_t projection, uint32_t k2, uint64_t *bytes) {
+int32_t b200q_moe_record_bytes(const b200q_moe_geometry *geometry, uint32_t projection, uint32_t k2, uint64_t *bytes) {
   ErrorSlot &slot = moe_error();
+  if (check_geometry(slot, geometry, "ignis_moe_record_bytes") != 0) return -1;
+  const Geometry &g_geo = *geometry;
   if (bytes == nullptr) return fail(slot, "ignis_moe_record_bytes: bytes is NULL");
   if (projection > IGNIS_MOE_PROJ_DOWN) return fail(slot, "ignis_moe_record_bytes: unknown projection %u", projection);
   if (!(k2 == 4 || k2 == 5 || k2 == 6 || k2 == 8)) return fail(slot, "ignis_moe_record_bytes: k2 = %u is not one of 4, 5, 6, 8", k2);
@@ -892,14 +896,18 @@ int32_t ignis_moe_prepare(void) {
   return moe_tc_prepare(slot);
 }
 
-uint64_t ignis_moe_workspace_bytes(uint32_t decode_tokens, uint32_t prefill_tokens) {
+uint64_t b200q_moe_workspace_bytes(const b200q_moe_geometry *geometry, uint32_t decode_tokens, uint32_t prefill_tokens) {
+  if (check_geometry(moe_error(), geometry, "ignis_moe_workspace_bytes") != 0) return 0;
+  const Geometry &g_geo = *geometry;
   const uint32_t tokens_max = decode_tokens > prefill_tokens ? decode_tokens : prefill_tokens;
   if (tokens_max == 0 || decode_tokens > IGNIS_MOE_DECODE_MAX_TOKENS) return 0;
   return layout_for(g_geo, tokens_max).total;
 }
 
-int32_t ignis_moe_workspace_init(const struct ignis_moe_workspace *workspace, int64_t *acc, void *stream) {
+int32_t b200q_moe_workspace_init(const b200q_moe_geometry *geometry, const struct ignis_moe_workspace *workspace, int64_t *acc, void *stream) {
   ErrorSlot &slot = moe_error();
+  if (check_geometry(slot, geometry, "ignis_moe_workspace_init") != 0) return -1;
+  const Geometry &g_geo = *geometry;
   if (workspace == nullptr || workspace->base == nullptr || acc == nullptr) return fail(slot, "ignis_moe_workspace_init: NULL argument");
   if (!aligned(workspace->base, 256)) return fail(slot, "ignis_moe_workspace_init: base is not 256-byte aligned");
   if (ignis_moe_prepare() != 0) return -1;
@@ -912,10 +920,12 @@ int32_t ignis_moe_workspace_init(const struct ignis_moe_workspace *workspace, in
   return 0;
 }
 
-int32_t ignis_moe_plan_bytes(uint32_t decode_tokens, uint32_t prefill_tokens, struct ignis_moe_plan *plan) {
+int32_t b200q_moe_plan_bytes(const b200q_moe_geometry *geometry, uint32_t decode_tokens, uint32_t prefill_tokens, struct ignis_moe_plan *plan) {
   ErrorSlot &slot = moe_error();
   if (plan == nullptr) return fail(slot, "ignis_moe_plan_bytes: plan is NULL");
-  const uint64_t ws = ignis_moe_workspace_bytes(decode_tokens, prefill_tokens);
+  if (check_geometry(slot, geometry, "ignis_moe_plan_bytes") != 0) return -1;
+  const Geometry &g_geo = *geometry;
+  const uint64_t ws = b200q_moe_workspace_bytes(geometry, decode_tokens, prefill_tokens);
   if (ws == 0) return fail(slot, "ignis_moe_plan_bytes: no tokens, or more than %d decode tokens", IGNIS_MOE_DECODE_MAX_TOKENS);
   const uint64_t mx = decode_tokens > prefill_tokens ? decode_tokens : prefill_tokens;
   plan->workspace = ws;
@@ -926,8 +936,11 @@ int32_t ignis_moe_plan_bytes(uint32_t decode_tokens, uint32_t prefill_tokens, st
   return 0;
 }
 
-int32_t ignis_moe_router_logits(const void *x, uint32_t tokens, const void *w_router, float *logits, void *stream) {
+int32_t b200q_moe_router_logits(const b200q_moe_geometry *geometry, const void *x, uint32_t tokens, const void *w_router, float *logits,
+                                void *stream) {
   ErrorSlot &slot = moe_error();
+  if (check_geometry(slot, geometry, "ignis_moe_router_logits") != 0) return -1;
+  const Geometry &g_geo = *geometry;
   if (x == nullptr || w_router == nullptr || logits == nullptr) return fail(slot, "ignis_moe_router_logits: NULL argument");
   if (tokens == 0) return fail(slot, "ignis_moe_router_logits: tokens must be positive");
   if (!aligned(x, 16) || !aligned(w_router, 16)) return fail(slot, "ignis_moe_router_logits: x and w_router must be 16-byte aligned");
@@ -940,11 +953,12 @@ int32_t ignis_moe_router_logits(const void *x, uint32_t tokens, const void *w_ro
   return 0;
 }
 
-int32_t ignis_moe_router(const void *x, uint32_t tokens, const void *w_router, int32_t *ids, float *weights, float *logits,
-                         void *stream) {
+int32_t b200q_moe_router(const b200q_moe_geometry *geometry, const void *x, uint32_t tokens, const void *w_router, int32_t *ids,
+                         float *weights, float *logits, void *stream) {
   ErrorSlot &slot = moe_error();
   if (ids == nullptr || weights == nullptr) return fail(slot, "ignis_moe_router: NULL argument");
-  if (ignis_moe_router_logits(x, tokens, w_router, logits, stream) != 0) return -1;
+  if (b200q_moe_router_logits(geometry, x, tokens, w_router, logits, stream) != 0) return -1;
+  const Geometry &g_geo = *geometry;
   const DeviceState *dev = prepared(slot, "ignis_moe_router");
   if (dev == nullptr) return -1;
   const cudaError_t err = launch(moe_router_select_kernel, dim3((tokens + 7u) / 8u), dim3(256), 0, static_cast<cudaStream_t>(stream),
@@ -953,30 +967,34 @@ int32_t ignis_moe_router(const void *x, uint32_t tokens, const void *w_router, i
   return 0;
 }
 
-int32_t ignis_moe_experts_decode(const void *x, uint32_t tokens, const int32_t *ids, const float *weights,
-                                 const struct ignis_moe_slot *slots, const struct ignis_moe_workspace *workspace,
-                                 int64_t *acc, void *stream) {
+int32_t b200q_moe_experts_decode(const b200q_moe_geometry *geometry, const void *x, uint32_t tokens, const int32_t *ids,
+                                 const float *weights, const struct ignis_moe_slot *slots,
+                                 const struct ignis_moe_workspace *workspace, int64_t *acc, void *stream) {
+  if (check_geometry(moe_error(), geometry, "ignis_moe_experts_decode") != 0) return -1;
   const uint32_t limit = workspace != nullptr ? workspace->decode_tokens : 0u;
-  return run_experts(x, tokens, ids, weights, slots, workspace, acc, stream, limit, 8u, "ignis_moe_experts_decode");
+  return run_experts(*geometry, x, tokens, ids, weights, slots, workspace, acc, stream, limit, 8u, "ignis_moe_experts_decode");
 }
 
-int32_t ignis_moe_experts_prefill(const void *x, uint32_t tokens, const int32_t *ids, const float *weights,
-                                  const struct ignis_moe_slot *slots, const struct ignis_moe_workspace *workspace,
-                                  int64_t *acc, void *stream) {
+int32_t b200q_moe_experts_prefill(const b200q_moe_geometry *geometry, const void *x, uint32_t tokens, const int32_t *ids,
+                                  const float *weights, const struct ignis_moe_slot *slots,
+                                  const struct ignis_moe_workspace *workspace, int64_t *acc, void *stream) {
+  if (check_geometry(moe_error(), geometry, "ignis_moe_experts_prefill") != 0) return -1;
   const uint32_t limit = workspace != nullptr ? workspace->prefill_tokens : 0u;
   // up to 8 tokens the decode entry's item size; up to 64 tokens items of 64 rows on the warp-level
   // MMAs; beyond, items of 256 rows on the tensor cores (B200Q_MOE_TC = 0 keeps the warp-level kernels)
   const DeviceState *dev = device_state(moe_error());
   const bool tc = dev != nullptr && dev->prepared && dev->moe_tc != 0 && tokens > 64u;
-  return run_experts(x, tokens, ids, weights, slots, workspace, acc, stream, limit, tokens > 8u ? (tc ? kMoeTcItemRows : 64u) : 8u,
+  return run_experts(*geometry, x, tokens, ids, weights, slots, workspace, acc, stream, limit, tokens > 8u ? (tc ? kMoeTcItemRows : 64u) : 8u,
                      "ignis_moe_experts_prefill");
 }
 
 int32_t ignis_moe_decode_cluster_size(void) { return 0; }
 
-int32_t ignis_moe_shared_expert(const void *gate, const void *up, const void *down, const void *x, uint32_t tokens, void *h,
-                                float *shared, void *stream) {
+int32_t b200q_moe_shared_expert(const b200q_moe_geometry *geometry, const void *gate, const void *up, const void *down, const void *x,
+                                uint32_t tokens, void *h, float *shared, void *stream) {
   ErrorSlot &slot = moe_error();
+  if (check_geometry(slot, geometry, "ignis_moe_shared_expert") != 0) return -1;
+  const Geometry &g_geo = *geometry;
   if (gate == nullptr || up == nullptr || down == nullptr || x == nullptr || h == nullptr || shared == nullptr) {
     return fail(slot, "ignis_moe_shared_expert: NULL argument");
   }
@@ -1012,9 +1030,11 @@ int32_t ignis_moe_shared_expert(const void *gate, const void *up, const void *do
   return 0;
 }
 
-int32_t ignis_moe_combine(int64_t *acc, const float *shared, const void *x, const void *w_gate, uint32_t tokens, void *out,
-                          void *stream) {
+int32_t b200q_moe_combine(const b200q_moe_geometry *geometry, int64_t *acc, const float *shared, const void *x, const void *w_gate,
+                          uint32_t tokens, void *out, void *stream) {
   ErrorSlot &slot = moe_error();
+  if (check_geometry(slot, geometry, "ignis_moe_combine") != 0) return -1;
+  const Geometry &g_geo = *geometry;
   if (acc == nullptr || shared == nullptr || x == nullptr || w_gate == nullptr || out == nullptr) {
     return fail(slot, "ignis_moe_combine: NULL argument");
   }
@@ -1026,6 +1046,45 @@ int32_t ignis_moe_combine(int64_t *acc, const float *shared, const void *x, cons
                                  static_cast<const uint16_t *>(w_gate), g_geo.hidden, static_cast<uint16_t *>(out));
   if (err != cudaSuccess) return fail(slot, "ignis_moe_combine: launch failed: %s", cudaGetErrorString(err));
   return 0;
+}
+
+// ---- the reference's own entry points: the same calls at the default geometry -----------------------
+int32_t ignis_moe_record_bytes(uint32_t projection, uint32_t k2, uint64_t *bytes) {
+  return b200q_moe_record_bytes(&g_default, projection, k2, bytes);
+}
+uint64_t ignis_moe_workspace_bytes(uint32_t decode_tokens, uint32_t prefill_tokens) {
+  return b200q_moe_workspace_bytes(&g_default, decode_tokens, prefill_tokens);
+}
+int32_t ignis_moe_workspace_init(const struct ignis_moe_workspace *workspace, int64_t *acc, void *stream) {
+  return b200q_moe_workspace_init(&g_default, workspace, acc, stream);
+}
+int32_t ignis_moe_plan_bytes(uint32_t decode_tokens, uint32_t prefill_tokens, struct ignis_moe_plan *plan) {
+  return b200q_moe_plan_bytes(&g_default, decode_tokens, prefill_tokens, plan);
+}
+int32_t ignis_moe_router_logits(const void *x, uint32_t tokens, const void *w_router, float *logits, void *stream) {
+  return b200q_moe_router_logits(&g_default, x, tokens, w_router, logits, stream);
+}
+int32_t ignis_moe_router(const void *x, uint32_t tokens, const void *w_router, int32_t *ids, float *weights, float *logits,
+                         void *stream) {
+  return b200q_moe_router(&g_default, x, tokens, w_router, ids, weights, logits, stream);
+}
+int32_t ignis_moe_experts_decode(const void *x, uint32_t tokens, const int32_t *ids, const float *weights,
+                                 const struct ignis_moe_slot *slots, const struct ignis_moe_workspace *workspace,
+                                 int64_t *acc, void *stream) {
+  return b200q_moe_experts_decode(&g_default, x, tokens, ids, weights, slots, workspace, acc, stream);
+}
+int32_t ignis_moe_experts_prefill(const void *x, uint32_t tokens, const int32_t *ids, const float *weights,
+                                  const struct ignis_moe_slot *slots, const struct ignis_moe_workspace *workspace,
+                                  int64_t *acc, void *stream) {
+  return b200q_moe_experts_prefill(&g_default, x, tokens, ids, weights, slots, workspace, acc, stream);
+}
+int32_t ignis_moe_shared_expert(const void *gate, const void *up, const void *down, const void *x, uint32_t tokens, void *h,
+                                float *shared, void *stream) {
+  return b200q_moe_shared_expert(&g_default, gate, up, down, x, tokens, h, shared, stream);
+}
+int32_t ignis_moe_combine(int64_t *acc, const float *shared, const void *x, const void *w_gate, uint32_t tokens, void *out,
+                          void *stream) {
+  return b200q_moe_combine(&g_default, acc, shared, x, w_gate, tokens, out, stream);
 }
 
 int32_t ignis_moe_stream_sync(void *stream) {

@@ -10,6 +10,12 @@ namespace {
 
 bool aligned(const void *p, uintptr_t a) { return (reinterpret_cast<uintptr_t>(p) & (a - 1)) == 0; }
 
+// A16_ONLY or ALLOW_A4 in the low byte, optionally one B200Q_NVFP4_PROBLEM_* class above it.
+bool policy_ok(uint32_t policy) {
+  return (policy & ~(0xFFu | B200Q_NVFP4_PROBLEM_MASK)) == 0u && (policy & 0xFFu) <= B200Q_NVFP4_ALLOW_A4 &&
+         (policy & B200Q_NVFP4_PROBLEM_MASK) <= B200Q_NVFP4_PROBLEM_RESIDUAL;
+}
+
 int32_t check_weight(ErrorSlot &slot, const b200q_nvfp4_weight *w, const char *what) {
   if (w == nullptr) return fail(slot, "%s: weight is NULL", what);
   if (w->codes == nullptr || w->scales == nullptr) return fail(slot, "%s: weight planes are NULL", what);
@@ -114,9 +120,19 @@ int32_t decode_route(ErrorSlot &slot, const DeviceState &dev, const b200q_nvfp4_
 
 // Tokens from which the reference's AllowA4 policy quantizes the activations, by problem
 // (nvfp4_dispatch.cpp:31-39): its fused GDN input always, attention inputs from 4 tokens, gate|up
-// from 5, the projections back to the residual stream from 8. Shapes are told apart by their
-// proportions, so that other model sizes of the same family resolve alike.
-uint32_t a4_min_tokens(uint32_t n_total, uint32_t k) {
+// from 5, the projections back to the residual stream from 8. The reference resolves this by the
+// problem the weight was registered as; a caller says which problem a call is with the
+// B200Q_NVFP4_PROBLEM_* bits of `policy`. Without them the problem is told from the shape's
+// proportions (so other model sizes of the same family resolve alike), and one literal shape for
+// the GDN input whose proportions equal an attention input's.
+uint32_t a4_min_tokens(uint32_t policy, uint32_t n_total, uint32_t k) {
+  switch (policy & B200Q_NVFP4_PROBLEM_MASK) {
+    case B200Q_NVFP4_PROBLEM_GDN_INPUT: return 1;
+    case B200Q_NVFP4_PROBLEM_ATTN_INPUT: return 4;
+    case B200Q_NVFP4_PROBLEM_GATE_UP: return 5;
+    case B200Q_NVFP4_PROBLEM_RESIDUAL: return 8;
+    default: break;
+  }
   if (n_total < k) return 8;
   if (n_total >= 4u * k) return 5;
   if (n_total == 16384u && k == 5120u) return 1;
@@ -129,7 +145,7 @@ uint32_t a4_min_tokens(uint32_t n_total, uint32_t k) {
 int32_t narrow_route(ErrorSlot &slot, const DeviceState &dev, const b200q_nvfp4_weight *const *w, uint32_t count, const void *x,
                      uint32_t tokens, void *const *y, const uint32_t *ldy, uint32_t epilogue, uint32_t policy,
                      cudaStream_t stream) {
-  if (policy == B200Q_NVFP4_ALLOW_A4 && dev.a4_decode != 0 && tokens <= kA4DecodeMaxTokens) {
+  if ((policy & 0xFFu) == B200Q_NVFP4_ALLOW_A4 && dev.a4_decode != 0 && tokens <= kA4DecodeMaxTokens) {
     uint32_t n_total = 0;
     bool takes = true;
     for (uint32_t i = 0; i < count; ++i) {
@@ -137,7 +153,7 @@ int32_t narrow_route(ErrorSlot &slot, const DeviceState &dev, const b200q_nvfp4_
       takes = takes && w4a4_decode_takes(w[i]->n, w[i]->k, tokens, epilogue) && std::isfinite(w[i]->input_scale_divisor) &&
               w[i]->input_scale_divisor > 0.0f;
     }
-    if (takes && tokens >= a4_min_tokens(n_total, w[0]->k)) {
+    if (takes && tokens >= a4_min_tokens(policy, n_total, w[0]->k)) {
       A4Item items[kMaxGroup];
       for (uint32_t i = 0; i < count; ++i) {
         items[i] = A4Item{static_cast<const uint8_t *>(w[i]->codes), static_cast<const uint8_t *>(w[i]->scales), y[i], w[i]->n, ldy[i],
@@ -156,7 +172,7 @@ int32_t linear_group_impl(const b200q_nvfp4_weight *const *w, uint32_t count, co
   if (w == nullptr || y == nullptr || ldy == nullptr) return fail(slot, "%s: NULL argument array", what);
   if (count == 0 || count > B200Q_NVFP4_MAX_GROUP) return fail(slot, "%s: count = %u is outside 1..%d", what, count, B200Q_NVFP4_MAX_GROUP);
   if (tokens == 0) return fail(slot, "%s: tokens must be positive", what);
-  if (policy != B200Q_NVFP4_A16_ONLY && policy != B200Q_NVFP4_ALLOW_A4) return fail(slot, "%s: unknown policy %u", what, policy);
+  if (!policy_ok(policy)) return fail(slot, "%s: unknown policy 0x%x", what, policy);
   if ((epilogue & ~(kEpilogueAdd | kEpilogueF32 | kEpilogueSwiglu)) != 0u) return fail(slot, "%s: unknown epilogue 0x%x", what, epilogue);
   if (x == nullptr || !aligned(x, 16)) return fail(slot, "%s: x is NULL or not 16-byte aligned", what);
   const bool swiglu = (epilogue & kEpilogueSwiglu) != 0u;
@@ -172,7 +188,7 @@ int32_t linear_group_impl(const b200q_nvfp4_weight *const *w, uint32_t count, co
   if (dev == nullptr) return -1;
   // Wide calls under B200Q_NVFP4_ALLOW_A4 quantize the activations into the workspace and take the
   // prefill kernels; everything else takes the A16 routes.
-  if (policy == B200Q_NVFP4_ALLOW_A4 && tokens > B200Q_NVFP4_DECODE_MAX_TOKENS && count == 1 &&
+  if ((policy & 0xFFu) == B200Q_NVFP4_ALLOW_A4 && tokens > B200Q_NVFP4_DECODE_MAX_TOKENS && count == 1 &&
       !(swiglu && (epilogue & kEpilogueAdd)) && w4a4_shape_ok(w[0]->n, w[0]->k)) {
     const b200q_nvfp4_weight *w0 = w[0];
     if (!std::isfinite(w0->input_scale_divisor) || !(w0->input_scale_divisor > 0.0f)) {
@@ -209,11 +225,11 @@ int32_t b200q_nvfp4_prepare(void) {
 
 uint64_t b200q_nvfp4_workspace_bytes(uint32_t n, uint32_t k, uint32_t policy, uint32_t tokens) {
   if (n == 0 || (n % 128u) != 0 || k == 0 || (k % 64u) != 0 || tokens == 0) return 0;
-  if (policy != B200Q_NVFP4_A16_ONLY && policy != B200Q_NVFP4_ALLOW_A4) return 0;
+  if (!policy_ok(policy)) return 0;
   // The decode route keeps its partial sums in distributed shared memory and needs no global
   // scratch (one aligned line, so a workspace pointer is never NULL); the A4 route keeps the
   // quantized activations there.
-  if (policy == B200Q_NVFP4_ALLOW_A4 && tokens > B200Q_NVFP4_DECODE_MAX_TOKENS && w4a4_shape_ok(n, k)) {
+  if ((policy & 0xFFu) == B200Q_NVFP4_ALLOW_A4 && tokens > B200Q_NVFP4_DECODE_MAX_TOKENS && w4a4_shape_ok(n, k)) {
     return w4a4_workspace_bytes(k, tokens);
   }
   return 256;
@@ -297,7 +313,7 @@ int32_t b200q_nvfp4_linear_split(const b200q_nvfp4_weight *parent, uint32_t coun
     part[i].n = rows[i];
     parts[i] = &part[i];
   }
-  const bool wide = policy == B200Q_NVFP4_ALLOW_A4 && tokens > B200Q_NVFP4_DECODE_MAX_TOKENS && w4a4_shape_ok(parent->n, parent->k);
+  const bool wide = (policy & 0xFFu) == B200Q_NVFP4_ALLOW_A4 && tokens > B200Q_NVFP4_DECODE_MAX_TOKENS && w4a4_shape_ok(parent->n, parent->k);
   if (!wide || count == 1) {
     return linear_group_impl(parts, count, x, tokens, y, ldy, epilogue, policy, workspace, stream, what);
   }
@@ -385,9 +401,9 @@ int32_t b200q_nvfp4_linear_group_gather(const b200q_nvfp4_weight *const *w, uint
 
 uint64_t b200q_nvfp4_mlp_workspace_bytes(uint32_t gate_up_n, uint32_t k, uint32_t policy, uint32_t tokens) {
   if (gate_up_n == 0 || (gate_up_n % 256u) != 0 || k == 0 || (k % 64u) != 0 || tokens == 0) return 0;
-  if (policy != B200Q_NVFP4_A16_ONLY && policy != B200Q_NVFP4_ALLOW_A4) return 0;
+  if (!policy_ok(policy)) return 0;
   const uint32_t inter = gate_up_n / 2u;
-  if (policy == B200Q_NVFP4_ALLOW_A4 && tokens > B200Q_NVFP4_DECODE_MAX_TOKENS && (k % 256u) == 0 && (inter % 256u) == 0) {
+  if ((policy & 0xFFu) == B200Q_NVFP4_ALLOW_A4 && tokens > B200Q_NVFP4_DECODE_MAX_TOKENS && (k % 256u) == 0 && (inter % 256u) == 0) {
     return w4a4_mlp_workspace_bytes(k, inter, tokens);
   }
   return 256u + static_cast<uint64_t>(tokens) * inter * 2u;  // the status line, then h as BF16
@@ -398,7 +414,7 @@ int32_t b200q_nvfp4_mlp(const b200q_nvfp4_weight *gate_up, const b200q_nvfp4_wei
   const char *what = "b200q_nvfp4_mlp";
   ErrorSlot &slot = nvfp4_error();
   if ((epilogue & ~(B200Q_NVFP4_ADD | B200Q_NVFP4_OUT_F32)) != 0u) return fail(slot, "%s: unknown epilogue 0x%x", what, epilogue);
-  if (policy != B200Q_NVFP4_A16_ONLY && policy != B200Q_NVFP4_ALLOW_A4) return fail(slot, "%s: unknown policy %u", what, policy);
+  if (!policy_ok(policy)) return fail(slot, "%s: unknown policy 0x%x", what, policy);
   if (check_weight(slot, gate_up, what) != 0 || check_weight(slot, down, what) != 0) return -1;
   if ((gate_up->n % 256u) != 0) return fail(slot, "%s: a fused gate_up parent needs n a multiple of 256", what);
   const uint32_t inter = gate_up->n / 2u;
@@ -416,7 +432,7 @@ int32_t b200q_nvfp4_mlp(const b200q_nvfp4_weight *gate_up, const b200q_nvfp4_wei
   if (dev == nullptr) return -1;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   uint8_t *base = static_cast<uint8_t *>(workspace->base);
-  if (policy == B200Q_NVFP4_ALLOW_A4 && tokens > B200Q_NVFP4_DECODE_MAX_TOKENS && (gate_up->k % 256u) == 0 && (inter % 256u) == 0) {
+  if ((policy & 0xFFu) == B200Q_NVFP4_ALLOW_A4 && tokens > B200Q_NVFP4_DECODE_MAX_TOKENS && (gate_up->k % 256u) == 0 && (inter % 256u) == 0) {
     for (const b200q_nvfp4_weight *w : {gate_up, down}) {
       if (!std::isfinite(w->input_scale_divisor) || !(w->input_scale_divisor > 0.0f)) {
         return fail(slot, "%s: input_scale_divisor must be finite and positive for the A4 route", what);

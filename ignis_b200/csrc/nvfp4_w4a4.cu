@@ -9,18 +9,16 @@
 //     scales, bit for bit the reference's rule (nvfp4_codec.cuh:81-110), the scales written in the
 //     same 512-byte (128 rows x 4 groups) tiles the weight plane uses - which is the scale-factor
 //     atom the block-scaled MMA reads, so neither operand's scales are ever reshuffled.
-//  2. The product, in three forms that share the stage layout and the epilogue:
-//     `w4a4_gemm_kernel` - one CTA per 128-token x 256-row (or 128-row) output tile: a producer
+//  2. The product, in two forms that share the stage layout and the epilogue:
+//     `w4a4_gemm_persistent_kernel` - one CTA per SM walking 128-token x 256-row tiles: a producer
 //     thread streams K in stages of 256 (TMA 2-D tiles of codes with the 128-byte swizzle, bulk
-//     copies of the scale tiles) into an mbarrier ring; one thread copies each stage's scale atoms
-//     to tensor memory (tcgen05.cp) and issues tcgen05.mma kind::mxf4nvf4 block_scale
-//     scale_vec::4X (M 128, N 256, K 64) with the fp32 accumulator in tensor memory; four warps
-//     read the accumulator back (tcgen05.ld), apply alpha and store BF16.
-//     `w4a4_gemm_persistent_kernel` - one CTA per SM walking such tiles, the ring running across
-//     tile boundaries, the stores under the next tile's MMAs, the scale copies issued by two
-//     threads of their own.
-//     `w4a4_gemm_pair_kernel` (the default) - the persistent form on clusters of two CTAs sharing
-//     256 x 256 tiles (cta_group::2): fewer operand bytes per FLOP.
+//     copies of the scale tiles) into an mbarrier ring that keeps running across tile boundaries;
+//     two threads copy each stage's scale atoms to tensor memory (tcgen05.cp); one thread issues
+//     tcgen05.mma kind::mxf4nvf4 block_scale scale_vec::4X (M 128, N 256, K 64) with the fp32
+//     accumulator in tensor memory; four warps pull the accumulator (tcgen05.ld), hand tensor
+//     memory back and store under the next tile's MMAs. Kept behind B200Q_W4A4_PAIR = 0.
+//     `w4a4_gemm_pair_kernel` (the default) - the same on clusters of two CTAs sharing 256 x 256
+//     tiles (cta_group::2): fewer operand bytes per FLOP.
 //
 // Every wait on an mbarrier is bounded: after the limit the thread records a status bit in the
 // workspace, stops issuing and the CTA tears down (tensor memory freed) instead of hanging.
@@ -107,190 +105,6 @@ struct W4A4Params {
   uint8_t *q_scales;  // ... and scales in 512-byte tiles
   float q_din;        // the next weight's input divisor
 };
-
-template <int kBN>
-__global__ void __launch_bounds__(192, kBN == 256 ? 1 : 2) w4a4_gemm_kernel(const __grid_constant__ CUtensorMap map_a,
-                                                          const __grid_constant__ CUtensorMap map_b,
-                                                          const __grid_constant__ W4A4Params p) {
-  constexpr int kStages = Tile<kBN>::kStages;
-  constexpr uint32_t kBBytes = Tile<kBN>::kBBytes, kStageBytes = Tile<kBN>::kStageBytes;
-  constexpr uint32_t kTmemCols = Tile<kBN>::kTmemCols, kSfColsPerStage = Tile<kBN>::kSfColsPerStage;
-  extern __shared__ uint8_t smem_raw[];
-  const uint32_t raw = smem_u32(smem_raw);
-  const uint32_t base = (raw + 1023u) & ~1023u;  // the 128-byte swizzle wants 1024-byte aligned tiles
-  uint8_t *base_ptr = smem_raw + (base - raw);
-  const uint32_t bars = base + kStages * kStageBytes;  // full[4], empty[4], tmem_full, then the tmem slot
-  uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(base_ptr + kStages * kStageBytes + 128);
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const uint32_t m_tile = blockIdx.x, n_tile = blockIdx.y;
-  const uint32_t k_iters = p.k / 256u;
-  const uint32_t k_atoms = p.k / 64u;
-  // The tile's 256 weight rows are two boxes of 128: rows [row_a, +128) and [row_b, +128). A plain
-  // product takes consecutive boxes; the fused SwiGLU pairs 128 gate rows with their up rows, which
-  // lie n / 2 further down the fused parent.
-  const bool swiglu = kBN == 256 && (p.epilogue & kEpilogueSwiglu) != 0u;
-  const uint32_t row_a = swiglu ? n_tile * 128u : n_tile * kBN;
-  const uint32_t row_b = swiglu ? p.n / 2u + n_tile * 128u : n_tile * kBN + 128u;
-  const bool second_half = kBN == 256 && row_b < p.n;  // the tile has a second box and it exists
-
-  if (threadIdx.x == 0) {
-    for (int s = 0; s < kStages; ++s) {
-      mbar_init(bars + 8 * s, 1);
-      mbar_init(bars + 8 * (kStages + s), 1);
-    }
-    mbar_init(bars + 8 * 2 * kStages, 1);
-    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-  }
-  if (warp == 5) {
-    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(kTmemCols) : "memory");
-    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
-  }
-  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-  __syncthreads();
-  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-  const uint32_t tmem = *tmem_slot;
-
-  // the quantized activations come from the previous kernel in the stream
-  griddep_launch_dependents();
-  griddep_wait();
-
-  if (warp == 4 && lane == 0) {
-    // ---- producer ----
-    for (uint32_t it = 0; it < k_iters; ++it) {
-      const uint32_t s = it % kStages;
-      if (!mbar_wait(bars + 8 * (kStages + s), ((it / kStages) & 1u) ^ 1u)) {
-        atomicOr(p.status, kStatusProducerTimeout);
-        break;
-      }
-      const uint32_t full = bars + 8 * s;
-      const uint32_t stage = base + s * kStageBytes;
-      mbar_expect_tx(full, kABytes + kSfaBytes + (second_half ? 2u : 1u) * (128u * kBKBytes + 2048u));  // one or two boxes with their scales
-      tma_load_2d(stage, &map_a, full, static_cast<int32_t>(it * kBKBytes), static_cast<int32_t>(m_tile * kBM));
-      tma_load_2d(stage + kABytes, &map_b, full, static_cast<int32_t>(it * kBKBytes), static_cast<int32_t>(row_a));
-      if (second_half) {
-        tma_load_2d(stage + kABytes + 128u * kBKBytes, &map_b, full, static_cast<int32_t>(it * kBKBytes), static_cast<int32_t>(row_b));
-      }
-      bulk_load(stage + kABytes + kBBytes, p.sfa + (static_cast<uint64_t>(m_tile) * k_atoms + it * 4u) * 512u, kSfaBytes, full);
-      bulk_load(stage + kABytes + kBBytes + kSfaBytes, p.sfb + (static_cast<uint64_t>(row_a / 128u) * k_atoms + it * 4u) * 512u,
-                2048u, full);
-      if (second_half) {
-        bulk_load(stage + kABytes + kBBytes + kSfaBytes + 2048u,
-                  p.sfb + (static_cast<uint64_t>(row_b / 128u) * k_atoms + it * 4u) * 512u, 2048u, full);
-      }
-    }
-  } else if (warp == 5 && lane == 0) {
-    // ---- MMA issuer ----
-    // instruction descriptor: E2M1 x E2M1 (format 1 at bits 7 and 10), both K-major, N >> 3 at
-    // bit 17, UE4M3 scales (bit 23 clear), M >> 4 at bit 24, scale ids 0, K 64
-    const uint32_t idesc = (1u << 7) | (1u << 10) | ((kBN >> 3) << 17) | ((kBM >> 4) << 24);
-    bool ok = true;
-    for (uint32_t it = 0; it < k_iters && ok; ++it) {
-      const uint32_t s = it % kStages;
-      if (!mbar_wait(bars + 8 * s, (it / kStages) & 1u)) {
-        atomicOr(p.status, kStatusMmaTimeout);
-        ok = false;
-        break;
-      }
-      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-      const uint32_t stage = base + s * kStageBytes;
-      const uint32_t sf_cols = tmem + kBN + s * kSfColsPerStage;
-      const uint32_t sfa_smem = stage + kABytes + kBBytes, sfb_smem = sfa_smem + kSfaBytes;
-#pragma unroll
-      for (uint32_t kb = 0; kb < 4; ++kb) {
-        tmem_cp_sf(sf_cols + kb * 4u, smem_desc(sfa_smem + kb * 512u, 128u, 0u));
-        constexpr uint32_t kSfbCols = (kBN / 128) * 4;  // columns of weight scales per 64 values along K
-        tmem_cp_sf(sf_cols + 16u + kb * kSfbCols, smem_desc(sfb_smem + kb * 512u, 128u, 0u));
-        if (kBN == 256) tmem_cp_sf(sf_cols + 16u + kb * kSfbCols + 4u, smem_desc(sfb_smem + 2048u + kb * 512u, 128u, 0u));
-      }
-      const uint64_t a_desc = smem_desc(stage, 1024u, 2u);
-      const uint64_t b_desc = smem_desc(stage + kABytes, 1024u, 2u);
-#pragma unroll
-      for (uint32_t kb = 0; kb < 4; ++kb) {
-        // 64 values along K are 32 bytes: two 16-byte units further inside the swizzled row
-        mma_mxf4nvf4(tmem, a_desc + 2u * kb, b_desc + 2u * kb, idesc, sf_cols + kb * 4u, sf_cols + 16u + kb * ((kBN / 128) * 4u),
-                     (it | kb) != 0u ? 1u : 0u);
-      }
-      mma_commit(bars + 8 * (kStages + s));  // the stage's shared memory is free once these MMAs retire
-    }
-    if (ok) mma_commit(bars + 8 * 2 * kStages);  // accumulator complete
-  } else if (warp < 4) {
-    // ---- epilogue: warp q owns accumulator lanes (tokens) 32 q .. 32 q + 31 ----
-    if (mbar_wait(bars + 8 * 2 * kStages, 0u)) {
-      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-      const uint32_t token = m_tile * kBM + warp * 32 + lane;
-      const uint32_t lane_base = tmem + (static_cast<uint32_t>(warp * 32) << 16);
-      if (swiglu) {
-        // h = BF16(silu(BF16(g alpha)) * BF16(u alpha)): gate in accumulator columns 0..127, up in 128..255
-#pragma unroll 1
-        for (uint32_t c = 0; c < 128u; c += 32) {
-          uint32_t g[32], u[32];
-          tmem_ld32(lane_base + c, g);
-          tmem_ld32(lane_base + 128u + c, u);
-          asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-          const uint32_t col0 = n_tile * 128u + c;
-          if (token < p.tokens && col0 < p.n / 2u) {
-            uint4 *dst = reinterpret_cast<uint4 *>(static_cast<__nv_bfloat16 *>(p.y) + static_cast<size_t>(token) * p.ldy + col0);
-#pragma unroll
-            for (int j = 0; j < 4; ++j) {
-              uint32_t o[4];
-#pragma unroll
-              for (int e = 0; e < 4; ++e) {
-                float h2[2];
-#pragma unroll
-                for (int i = 0; i < 2; ++i) {
-                  const float gv = __bfloat162float(__float2bfloat16_rn(__uint_as_float(g[8 * j + 2 * e + i]) * p.alpha));
-                  const float uv = __bfloat162float(__float2bfloat16_rn(__uint_as_float(u[8 * j + 2 * e + i]) * p.alpha));
-                  h2[i] = gv / (1.0f + __expf(-gv)) * uv;
-                }
-                const __nv_bfloat162 h = __floats2bfloat162_rn(h2[0], h2[1]);
-                o[e] = *reinterpret_cast<const uint32_t *>(&h);
-              }
-              dst[j] = make_uint4(o[0], o[1], o[2], o[3]);
-            }
-          }
-        }
-      } else {
-#pragma unroll 1
-      for (uint32_t c = 0; c < kBN; c += 32) {
-        uint32_t r[32];
-        tmem_ld32(lane_base + c, r);
-        asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-        const uint32_t row0 = n_tile * kBN + c;
-        if (token < p.tokens && row0 < p.n) {  // n is a multiple of 128, so a 32-row chunk is whole
-          if (p.epilogue & kEpilogueF32) {
-            float4 *dst = reinterpret_cast<float4 *>(static_cast<float *>(p.y) + static_cast<size_t>(token) * p.ldy + row0);
-#pragma unroll
-            for (int j = 0; j < 8; ++j) {
-              dst[j] = make_float4(__uint_as_float(r[4 * j]) * p.alpha, __uint_as_float(r[4 * j + 1]) * p.alpha,
-                                   __uint_as_float(r[4 * j + 2]) * p.alpha, __uint_as_float(r[4 * j + 3]) * p.alpha);
-            }
-          } else {
-            uint4 *dst = reinterpret_cast<uint4 *>(static_cast<__nv_bfloat16 *>(p.y) + static_cast<size_t>(token) * p.ldy + row0);
-#pragma unroll
-            for (int j = 0; j < 4; ++j) {
-              uint32_t o[4];
-#pragma unroll
-              for (int e = 0; e < 4; ++e) {
-                const __nv_bfloat162 h = __floats2bfloat162_rn(__uint_as_float(r[8 * j + 2 * e]) * p.alpha,
-                                                               __uint_as_float(r[8 * j + 2 * e + 1]) * p.alpha);
-                o[e] = *reinterpret_cast<const uint32_t *>(&h);
-              }
-              dst[j] = make_uint4(o[0], o[1], o[2], o[3]);
-            }
-          }
-        }
-      }
-      }
-    } else if (lane == 0) {
-      atomicOr(p.status, kStatusEpilogueTimeout);
-    }
-  }
-  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-  __syncthreads();
-  if (warp == 5) {
-    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(kTmemCols) : "memory");
-  }
-}
 
 // ---- the persistent form ------------------------------------------------------------------------
 // One CTA per SM walks 128 x 256 tiles (tile = blockIdx.x, + gridDim.x, ...; the token tile index
@@ -830,16 +644,8 @@ uint64_t w4a4_workspace_bytes(uint32_t k, uint32_t tokens) {
 bool w4a4_shape_ok(uint32_t n, uint32_t k) { return (k % 256u) == 0 && (n % 128u) == 0; }
 
 int32_t w4a4_prepare(ErrorSlot &slot) {
-  cudaError_t err = cudaFuncSetAttribute(w4a4_gemm_kernel<256>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+  cudaError_t err = cudaFuncSetAttribute(w4a4_gemm_persistent_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                          static_cast<int>(Tile<256>::kSmemBytes));
-  if (err == cudaSuccess) {
-    err = cudaFuncSetAttribute(w4a4_gemm_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                               static_cast<int>(Tile<128>::kSmemBytes));
-  }
-  if (err == cudaSuccess) {
-    err = cudaFuncSetAttribute(w4a4_gemm_persistent_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                               static_cast<int>(Tile<256>::kSmemBytes));
-  }
   if (err == cudaSuccess) {
     err = cudaFuncSetAttribute(w4a4_gemm_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(kPairSmemBytes));
   }
@@ -917,19 +723,11 @@ int32_t w4a4_product(ErrorSlot &slot, const DeviceState &dev, const uint8_t *w_c
     if (perr != cudaSuccess) return fail(slot, "nvfp4 prefill launch: %s", cudaGetErrorString(perr));
     return 0;
   }
-  if (dev.w4a4_persistent != 0 || (epilogue & (kEpilogueAdd | kEpilogueQuant)) != 0u) {  // those two epilogues exist only here
-    const uint32_t tiles = (pad / kBM) * (swiglu ? n / 256u : (n + 255u) / 256u);
-    const uint32_t ctas = tiles < static_cast<uint32_t>(dev.sm_count) ? tiles : static_cast<uint32_t>(dev.sm_count);
-    const cudaError_t perr = launch(w4a4_gemm_persistent_kernel, dim3(ctas), dim3(256), Tile<256>::kSmemBytes, stream, dev.pdl != 0,
-                                    map_a, map_b, p);
-    if (perr != cudaSuccess) return fail(slot, "nvfp4 prefill launch: %s", cudaGetErrorString(perr));
-    return 0;
-  }
-  const bool wide = swiglu || dev.w4a4_bn == 256;
-  const dim3 grid(pad / kBM, swiglu ? n / 256u : (wide ? (n + 255u) / 256u : n / 128u), 1);
-  const cudaError_t err = wide ? launch(w4a4_gemm_kernel<256>, grid, dim3(192), Tile<256>::kSmemBytes, stream, dev.pdl != 0, map_a, map_b, p)
-                               : launch(w4a4_gemm_kernel<128>, grid, dim3(192), Tile<128>::kSmemBytes, stream, dev.pdl != 0, map_a, map_b, p);
-  if (err != cudaSuccess) return fail(slot, "nvfp4 prefill launch: %s", cudaGetErrorString(err));
+  // B200Q_W4A4_PAIR = 0: the persistent form on single CTAs, 128-token x 256-row tiles
+  const uint32_t tiles = (pad / kBM) * (swiglu ? n / 256u : (n + 255u) / 256u);
+  const uint32_t ctas = tiles < static_cast<uint32_t>(dev.sm_count) ? tiles : static_cast<uint32_t>(dev.sm_count);
+  const cudaError_t perr = launch(w4a4_gemm_persistent_kernel, dim3(ctas), dim3(256), Tile<256>::kSmemBytes, stream, dev.pdl != 0, map_a, map_b, p);
+  if (perr != cudaSuccess) return fail(slot, "nvfp4 prefill launch: %s", cudaGetErrorString(perr));
   return 0;
 }
 }  // namespace

@@ -72,7 +72,6 @@ int32_t prepare_device(ErrorSlot &slot) {
   fresh.gemv_ctas_per_sm = env_int("B200Q_GEMV_CTAS_PER_SM", 2);
   fresh.gemv_xu = env_int("B200Q_GEMV_XU", 8);
   fresh.a16_mma = env_int("B200Q_A16_MMA", 1);
-  fresh.w4a4_persistent = env_int("B200Q_W4A4_PERSISTENT", 1);
   fresh.a4_decode = env_int("B200Q_A4_DECODE", 1);
   fresh.trellis_kc_max = env_int("B200Q_TRELLIS_KC_MAX", 8);
   fresh.a4_decode_pair = env_int("B200Q_A4_DECODE_PAIR", -1);
@@ -81,7 +80,6 @@ int32_t prepare_device(ErrorSlot &slot) {
   fresh.a4_decode_ctas = env_int("B200Q_A4_DECODE_CTAS", 2) == 1 ? 1 : 2;
   fresh.a16_mma_wide = env_int("B200Q_A16_MMA_WIDE", 1);
   fresh.w4a4_pair = env_int("B200Q_W4A4_PAIR", 1);
-  fresh.w4a4_bn = env_int("B200Q_W4A4_BN", 128) == 256 ? 256 : 128;
   fresh.sm_cap = env_int("IGNIS_TRELLIS_SM_CAP", 0);
   if (fresh.sm_cap < 0 || fresh.sm_cap > fresh.sm_count) fresh.sm_cap = 0;
   fresh.trellis_tc = env_int("B200Q_TRELLIS_TC", 1);

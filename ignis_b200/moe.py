@@ -4,6 +4,12 @@ Names follow the reference's Rust binding of the same ABI (crates/core/src/moe.r
 ``record_bytes``, ``trellis_reconstruct``, ``router``, ``router_logits``, ``prepare``,
 ``workspace_bytes``, ``plan_bytes``, ``experts_decode``, ``experts_prefill``, ``shared_expert``,
 ``combine``; a failed call raises ``MoeError`` carrying ``ignis_moe_last_error()``.
+
+The reference compiles one geometry in (2560 / 640 / 512 / top-10). Every call here goes through
+the library's geometry-taking variants (``b200q_moe_*``) and passes its geometry explicitly: the
+`geometry` argument, else the module's default, which :func:`set_geometry` replaces. Nothing
+process-wide changes inside the library; a :class:`Workspace` remembers the geometry it was sized
+for.
 """
 from __future__ import annotations
 
@@ -33,45 +39,58 @@ def _stream() -> C.c_void_p:
     return C.c_void_p(torch.cuda.current_stream().cuda_stream)
 
 
-@dataclass
+@dataclass(frozen=True)
 class Geometry:
     hidden: int = 2560
     inter: int = 640
     experts: int = 512
     top_k: int = 10
 
+    def c_struct(self) -> _lib.MoeGeometry:
+        return _lib.MoeGeometry(self.hidden, self.inter, self.experts, self.top_k)
+
 
 _geometry = Geometry()
 
 
 def set_geometry(hidden: int, inter: int, experts: int, top_k: int) -> None:
-    """``b200q_moe_set_geometry``: the reference's compile-time geometry made a setting."""
+    """Replaces this module's default geometry (a Python-side default: the library is told the
+    geometry with every call)."""
     global _geometry
-    _check(_lib.load().b200q_moe_set_geometry(hidden, inter, experts, top_k))
-    _geometry = Geometry(hidden, inter, experts, top_k)
+    g = Geometry(hidden, inter, experts, top_k)
+    out = C.c_uint64(0)
+    gs = g.c_struct()
+    _check(_lib.load().b200q_moe_record_bytes(C.byref(gs), PROJ_GATE_UP, 4, C.byref(out)))   # validates the geometry
+    _geometry = g
 
 
 def geometry() -> Geometry:
     return _geometry
 
 
+def _geo(g: Geometry | None) -> _lib.MoeGeometry:
+    return (g or _geometry).c_struct()
+
+
 def prepare() -> None:
     _check(_lib.load().ignis_moe_prepare())
 
 
-def record_bytes(projection: int, k2: int) -> int:
+def record_bytes(projection: int, k2: int, geometry: Geometry | None = None) -> int:
     out = C.c_uint64(0)
-    _check(_lib.load().ignis_moe_record_bytes(projection, k2, C.byref(out)))
+    gs = _geo(geometry)
+    _check(_lib.load().b200q_moe_record_bytes(C.byref(gs), projection, k2, C.byref(out)))
     return int(out.value)
 
 
-def pack_record(words: np.ndarray, suh: np.ndarray, svh: np.ndarray, projection: int, k2: int) -> np.ndarray:
+def pack_record(words: np.ndarray, suh: np.ndarray, svh: np.ndarray, projection: int, k2: int,
+                geometry: Geometry | None = None) -> np.ndarray:
     """One expert-projection record as the artifact stores it: trellis words, suh, svh, zero
     padding to 4096 bytes (docs/formats/flash-next-layout.md section 3)."""
     body = np.concatenate([np.ascontiguousarray(words).view(np.uint8).reshape(-1),
                            np.ascontiguousarray(suh).view(np.uint8).reshape(-1),
                            np.ascontiguousarray(svh).view(np.uint8).reshape(-1)])
-    size = record_bytes(projection, k2)
+    size = record_bytes(projection, k2, geometry)
     if body.size > size:
         raise ValueError("record contents exceed the record size of this geometry")
     out = np.zeros(size, np.uint8)
@@ -117,16 +136,18 @@ class SlotTable:
 
 
 class Workspace:
-    """The workspace and the routed accumulator of one MoE block, initialised."""
+    """The workspace and the routed accumulator of one MoE block, initialised, for one geometry."""
 
-    def __init__(self, decode_tokens: int, prefill_tokens: int, device="cuda") -> None:
-        nbytes = int(_lib.load().ignis_moe_workspace_bytes(decode_tokens, prefill_tokens))
+    def __init__(self, decode_tokens: int, prefill_tokens: int, device="cuda", geometry: Geometry | None = None) -> None:
+        self.geometry = geometry or _geometry
+        gs = self.geometry.c_struct()
+        nbytes = int(_lib.load().b200q_moe_workspace_bytes(C.byref(gs), decode_tokens, prefill_tokens))
         if nbytes == 0:
             raise MoeError("ignis_moe_workspace_bytes refused the token counts")
         self.buffer = torch.empty(nbytes, dtype=torch.uint8, device=device)
         self.c = _lib.MoeWorkspace(self.buffer.data_ptr(), decode_tokens, prefill_tokens, 0)
-        self.acc = torch.empty((max(decode_tokens, prefill_tokens), _geometry.hidden), dtype=torch.int64, device=device)
-        _check(_lib.load().ignis_moe_workspace_init(C.byref(self.c), self.acc.data_ptr(), _stream()))
+        self.acc = torch.empty((max(decode_tokens, prefill_tokens), self.geometry.hidden), dtype=torch.int64, device=device)
+        _check(_lib.load().b200q_moe_workspace_init(C.byref(gs), C.byref(self.c), self.acc.data_ptr(), _stream()))
 
     def status(self) -> int:
         word = C.c_uint32(0)
@@ -134,9 +155,10 @@ class Workspace:
         return int(word.value)
 
 
-def plan_bytes(decode_tokens: int, prefill_tokens: int) -> dict:
+def plan_bytes(decode_tokens: int, prefill_tokens: int, geometry: Geometry | None = None) -> dict:
     plan = _lib.MoePlan()
-    _check(_lib.load().ignis_moe_plan_bytes(decode_tokens, prefill_tokens, C.byref(plan)))
+    gs = _geo(geometry)
+    _check(_lib.load().b200q_moe_plan_bytes(C.byref(gs), decode_tokens, prefill_tokens, C.byref(plan)))
     return {k: int(getattr(plan, k)) for k in ("workspace", "acc", "router", "shared", "total")}
 
 
@@ -146,32 +168,35 @@ def trellis_reconstruct(words: torch.Tensor, k2: int, in_: int, out: int) -> tor
     return w
 
 
-def router(x: torch.Tensor, w_router: torch.Tensor):
+def router(x: torch.Tensor, w_router: torch.Tensor, geometry: Geometry | None = None):
     """(ids int32 [tokens, top_k], weights fp32 [tokens, top_k], logits fp32 [tokens, experts])."""
-    g = _geometry
+    g = geometry or _geometry
     tokens = x.shape[0]
     ids = torch.empty((tokens, g.top_k), dtype=torch.int32, device=x.device)
     weights = torch.empty((tokens, g.top_k), dtype=torch.float32, device=x.device)
     logits = torch.empty((tokens, g.experts), dtype=torch.float32, device=x.device)
-    _check(_lib.load().ignis_moe_router(x.data_ptr(), tokens, w_router.data_ptr(), ids.data_ptr(), weights.data_ptr(),
+    gs = g.c_struct()
+    _check(_lib.load().b200q_moe_router(C.byref(gs), x.data_ptr(), tokens, w_router.data_ptr(), ids.data_ptr(), weights.data_ptr(),
                                          logits.data_ptr(), _stream()))
     return ids, weights, logits
 
 
 def _experts(fn, x, ids, weights, table: SlotTable, ws: Workspace) -> torch.Tensor:
     tokens = x.shape[0]
-    _check(fn(x.data_ptr(), tokens, ids.data_ptr(), weights.data_ptr(), table.slots.data_ptr(), C.byref(ws.c),
+    gs = ws.geometry.c_struct()
+    _check(fn(C.byref(gs), x.data_ptr(), tokens, ids.data_ptr(), weights.data_ptr(), table.slots.data_ptr(), C.byref(ws.c),
               ws.acc.data_ptr(), _stream()))
     return ws.acc
 
 
 def experts_prefill(x, ids, weights, table: SlotTable, ws: Workspace) -> torch.Tensor:
-    """Adds the routed experts of every token into ``ws.acc`` (int64, value = acc * 2^-32)."""
-    return _experts(_lib.load().ignis_moe_experts_prefill, x, ids, weights, table, ws)
+    """Adds the routed experts of every token into ``ws.acc`` (int64, value = acc * 2^-32), at the
+    workspace's geometry."""
+    return _experts(_lib.load().b200q_moe_experts_prefill, x, ids, weights, table, ws)
 
 
 def experts_decode(x, ids, weights, table: SlotTable, ws: Workspace) -> torch.Tensor:
-    return _experts(_lib.load().ignis_moe_experts_decode, x, ids, weights, table, ws)
+    return _experts(_lib.load().b200q_moe_experts_decode, x, ids, weights, table, ws)
 
 
 def experts_tokens(rows: torch.Tensor, local_ids: torch.Tensor, row_weights: torch.Tensor, table: SlotTable,
@@ -209,23 +234,26 @@ def fp8_row_scale_payload(w: torch.Tensor) -> np.ndarray:
     return out
 
 
-def shared_expert(gate: torch.Tensor, up: torch.Tensor, down: torch.Tensor, x: torch.Tensor):
-    g = _geometry
+def shared_expert(gate: torch.Tensor, up: torch.Tensor, down: torch.Tensor, x: torch.Tensor, geometry: Geometry | None = None):
+    g = geometry or _geometry
     tokens = x.shape[0]
     h = torch.empty((tokens, g.inter), dtype=torch.bfloat16, device=x.device)
     shared = torch.empty((tokens, g.hidden), dtype=torch.float32, device=x.device)
-    _check(_lib.load().ignis_moe_shared_expert(gate.data_ptr(), up.data_ptr(), down.data_ptr(), x.data_ptr(), tokens,
+    gs = g.c_struct()
+    _check(_lib.load().b200q_moe_shared_expert(C.byref(gs), gate.data_ptr(), up.data_ptr(), down.data_ptr(), x.data_ptr(), tokens,
                                                 h.data_ptr(), shared.data_ptr(), _stream()))
     return shared, h
 
 
 def combine(ws: Workspace | None, shared: torch.Tensor, x: torch.Tensor, w_gate: torch.Tensor,
-            acc: torch.Tensor | None = None) -> torch.Tensor:
+            acc: torch.Tensor | None = None, geometry: Geometry | None = None) -> torch.Tensor:
     """``out = BF16(acc 2^-32 + sigmoid(x . w_gate) shared)``; clears the accumulator it read
     (`acc` when given, else the workspace's)."""
+    g = geometry or (ws.geometry if ws is not None else _geometry)
     tokens = x.shape[0]
-    out = torch.empty((tokens, _geometry.hidden), dtype=torch.bfloat16, device=x.device)
+    out = torch.empty((tokens, g.hidden), dtype=torch.bfloat16, device=x.device)
     acc = ws.acc if acc is None else acc
-    _check(_lib.load().ignis_moe_combine(acc.data_ptr(), shared.data_ptr(), x.data_ptr(), w_gate.data_ptr(), tokens,
+    gs = g.c_struct()
+    _check(_lib.load().b200q_moe_combine(C.byref(gs), acc.data_ptr(), shared.data_ptr(), x.data_ptr(), w_gate.data_ptr(), tokens,
                                           out.data_ptr(), _stream()))
     return out

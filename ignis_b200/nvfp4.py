@@ -19,6 +19,8 @@ from . import _lib
 
 A16_ONLY = 0   # LinearPolicy::A16Only
 ALLOW_A4 = 1   # LinearPolicy::AllowA4
+# the problem a call is, OR-ed into the policy: the reference's per-problem AllowA4 thresholds (nvfp4_dispatch.cpp:31-39)
+PROBLEM_GDN_INPUT, PROBLEM_ATTN_INPUT, PROBLEM_GATE_UP, PROBLEM_RESIDUAL = 0x100, 0x200, 0x300, 0x400
 STORE = 0
 ADD = 1
 OUT_F32 = 0x100

@@ -58,6 +58,17 @@ typedef struct b200q_nvfp4_workspace {
  * quantize the activations to NVFP4 (nvfp4_codec.cuh:81-110) and multiply in FP4. */
 #define B200Q_NVFP4_A16_ONLY 0
 #define B200Q_NVFP4_ALLOW_A4 1
+/* Under ALLOW_A4 the reference quantizes the activations of a call from a token count that depends
+ * on the problem the weight was registered as (nvfp4_dispatch.cpp:31-39): its fused GDN input
+ * always, the attention inputs from 4 tokens, gate|up from 5, the projections back to the residual
+ * stream (attention out, GDN out, down) from 8. OR one of these into `policy` to say which problem a
+ * call is (a grouped q | k | v call and a fused q|k|gate|v parent are both ATTN_INPUT); without one
+ * the problem is told from the weights' proportions. */
+#define B200Q_NVFP4_PROBLEM_MASK 0x700u
+#define B200Q_NVFP4_PROBLEM_GDN_INPUT 0x100u
+#define B200Q_NVFP4_PROBLEM_ATTN_INPUT 0x200u
+#define B200Q_NVFP4_PROBLEM_GATE_UP 0x300u
+#define B200Q_NVFP4_PROBLEM_RESIDUAL 0x400u
 
 /* Epilogues. STORE and ADD write BF16; OR-ing B200Q_NVFP4_OUT_F32 makes `y` float32 (the FP32
  * accumulators before the final rounding, for numerical checks). Under B200Q_NVFP4_ALLOW_A4 a call

@@ -47,9 +47,21 @@ extern "C" {
 #define IGNIS_MOE_PROJ_GATE_UP 0 /* ignis_moe.h:51 */
 #define IGNIS_MOE_PROJ_DOWN 1    /* ignis_moe.h:52 */
 
-/* No counterpart in the reference: sets the geometry every op below uses from now on (hidden and
- * inter positive multiples of 128, experts 1..4096, top_k 1..32). Call it before the queries and
- * the workspace initialisation of a load; not thread-safe against running ops. */
+/* No counterpart in the reference, which compiles one geometry in (ignis_moe.h:42-47): the
+ * geometry as an argument. Every b200q_moe_* entry below is the ignis_moe_* entry of the same name
+ * with this struct in front - same arguments, same results - and carries no state between calls,
+ * so two models (or two threads) use different geometries side by side. hidden and inter are
+ * positive multiples of 128, experts 1..4096, top_k 1..min(32, experts). */
+typedef struct b200q_moe_geometry {
+  uint32_t hidden;
+  uint32_t inter;
+  uint32_t experts;
+  uint32_t top_k;
+} b200q_moe_geometry;
+
+/* The geometry the reference's own entry points (ignis_moe_*, no geometry argument) work at: the
+ * reference's at start. A convenience for callers bound to the verbatim ABI with another model;
+ * process-wide, so set it once at load before any query. New code passes the struct instead. */
 int32_t b200q_moe_set_geometry(uint32_t hidden, uint32_t inter, uint32_t experts, uint32_t top_k);
 
 /* Not in the reference: an expert id that means "this choice has no expert here". The expert ops
@@ -152,6 +164,28 @@ int32_t ignis_moe_stream_sync(void *stream);
  * device-side wait of the tensor-core expert kernels (calls of more than 64 tokens) ran out; that
  * call's sums are not valid. */
 int32_t ignis_moe_workspace_status(const struct ignis_moe_workspace *workspace, void *stream, uint32_t *status);
+
+/* The geometry-taking variants (see b200q_moe_geometry above). */
+int32_t b200q_moe_record_bytes(const b200q_moe_geometry *geometry, uint32_t projection, uint32_t k2, uint64_t *bytes);
+uint64_t b200q_moe_workspace_bytes(const b200q_moe_geometry *geometry, uint32_t decode_tokens, uint32_t prefill_tokens);
+int32_t b200q_moe_workspace_init(const b200q_moe_geometry *geometry, const struct ignis_moe_workspace *workspace, int64_t *acc,
+                                 void *stream);
+int32_t b200q_moe_plan_bytes(const b200q_moe_geometry *geometry, uint32_t decode_tokens, uint32_t prefill_tokens,
+                             struct ignis_moe_plan *plan);
+int32_t b200q_moe_router_logits(const b200q_moe_geometry *geometry, const void *x, uint32_t tokens, const void *w_router,
+                                float *logits, void *stream);
+int32_t b200q_moe_router(const b200q_moe_geometry *geometry, const void *x, uint32_t tokens, const void *w_router, int32_t *ids,
+                         float *weights, float *logits, void *stream);
+int32_t b200q_moe_experts_decode(const b200q_moe_geometry *geometry, const void *x, uint32_t tokens, const int32_t *ids,
+                                 const float *weights, const struct ignis_moe_slot *slots,
+                                 const struct ignis_moe_workspace *workspace, int64_t *acc, void *stream);
+int32_t b200q_moe_experts_prefill(const b200q_moe_geometry *geometry, const void *x, uint32_t tokens, const int32_t *ids,
+                                  const float *weights, const struct ignis_moe_slot *slots,
+                                  const struct ignis_moe_workspace *workspace, int64_t *acc, void *stream);
+int32_t b200q_moe_shared_expert(const b200q_moe_geometry *geometry, const void *gate, const void *up, const void *down,
+                                const void *x, uint32_t tokens, void *h, float *shared, void *stream);
+int32_t b200q_moe_combine(const b200q_moe_geometry *geometry, int64_t *acc, const float *shared, const void *x,
+                          const void *w_gate, uint32_t tokens, void *out, void *stream);
 
 /* Thread-local message of the most recent failed call. Never NULL. reference: ignis_moe.h:216 */
 const char *ignis_moe_last_error(void);

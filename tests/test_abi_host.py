@@ -109,3 +109,29 @@ def test_workspace_query():
     assert nvfp4.workspace_bytes(17408, 5120, nvfp4.A16_ONLY, 8) > 0
     assert nvfp4.workspace_bytes(100, 5120, nvfp4.A16_ONLY, 8) == 0
     assert nvfp4.workspace_bytes(128, 64, 7, 8) == 0
+
+
+def test_moe_geometry_is_an_argument_and_the_verbatim_entries_keep_a_default():
+    """The geometry-taking variants carry no state: two geometries answer side by side. The
+    reference's own entry points (no geometry argument) answer at the default geometry, the
+    reference's until b200q_moe_set_geometry replaces it."""
+    from ignis_b200 import _lib
+
+    lib = _lib.load()
+    out = C.c_uint64(0)
+    ref = _lib.MoeGeometry(2560, 640, 512, 10)
+    cfg4 = _lib.MoeGeometry(2048, 768, 512, 10)
+    assert lib.b200q_moe_record_bytes(C.byref(ref), 0, 5, C.byref(out)) == 0 and out.value == 1032192
+    assert lib.b200q_moe_record_bytes(C.byref(cfg4), 0, 5, C.byref(out)) == 0 and out.value == (2048 * 1536 * 5 // 16 + 2 * 2048 + 2 * 1536 + 4095) // 4096 * 4096
+    assert lib.b200q_moe_record_bytes(C.byref(ref), 1, 8, C.byref(out)) == 0 and out.value == 827392
+    assert lib.ignis_moe_record_bytes(0, 5, C.byref(out)) == 0 and out.value == 1032192      # the reference's geometry at start
+    bad = _lib.MoeGeometry(2000, 768, 512, 10)
+    assert lib.b200q_moe_record_bytes(C.byref(bad), 0, 5, C.byref(out)) == -1
+    assert b"multiples of 128" in lib.ignis_moe_last_error()
+    try:
+        assert lib.b200q_moe_set_geometry(2048, 768, 512, 10) == 0
+        assert lib.ignis_moe_record_bytes(1, 5, C.byref(out)) == 0 and out.value == (768 * 2048 * 5 // 16 + 2 * 768 + 2 * 2048 + 4095) // 4096 * 4096
+        assert lib.b200q_moe_record_bytes(C.byref(ref), 0, 5, C.byref(out)) == 0 and out.value == 1032192   # untouched by the default
+    finally:
+        assert lib.b200q_moe_set_geometry(2560, 640, 512, 10) == 0
+    assert C.sizeof(_lib.MoeGeometry) == 16

@@ -194,6 +194,32 @@ def test_config4_geometry_under_zipf_routing(mo, oracle, k2s):
     assert torch.equal(pre[:8], dec[:8])
 
 
+def test_two_geometries_side_by_side(mo, oracle):
+    """The geometry travels with every call (and with the workspace sized for it): two models'
+    blocks interleave in one process without touching each other, and give the bits they give alone."""
+    rng = np.random.default_rng(21)
+    small, wide = mo.Geometry(256, 128, 8, 2), mo.Geometry(384, 256, 4, 1)
+    sets = []
+    for g, tokens in ((small, 12), (wide, 9)):
+        mo.set_geometry(g.hidden, g.inter, g.experts, g.top_k)     # only while the host-side records are packed
+        rec = Records(mo, oracle, rng, g.hidden, g.inter, g.experts)
+        x = (torch.randn(tokens, g.hidden, generator=torch.Generator().manual_seed(tokens)) * 0.5).to(torch.bfloat16)
+        ids, w = make_routing(rng, tokens, g.experts, g.top_k)
+        sets.append((g, rec, x, ids, w, mo.Workspace(8, tokens, geometry=g)))
+    mo.set_geometry(2560, 640, 512, 10)                            # the module default is neither of them now
+    alone = []
+    for g, rec, x, ids, w, ws in sets:
+        alone.append(mo.experts_prefill(x.cuda(), torch.from_numpy(ids).cuda(), torch.from_numpy(w).cuda(), rec.table, ws).clone())
+        ws.acc.zero_()
+    for _ in range(2):                                             # interleaved: small, wide, small, wide
+        for g, rec, x, ids, w, ws in sets:
+            mo.experts_prefill(x.cuda(), torch.from_numpy(ids).cuda(), torch.from_numpy(w).cuda(), rec.table, ws)
+    for (g, rec, x, ids, w, ws), first in zip(sets, alone):
+        assert ws.status() == 0
+        assert torch.equal(ws.acc, 2 * first)
+        check_tokens(first[: x.shape[0]], routed_reference(oracle, rec, x, ids, w, g.hidden))
+
+
 def test_absent_records_and_bad_ids_are_skipped_and_reported(mo, oracle):
     mo.set_geometry(256, 128, 8, 2)
     rng = np.random.default_rng(5)

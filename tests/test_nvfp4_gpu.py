@@ -615,6 +615,21 @@ def test_w4a4_decode_thresholds_and_groups(nv, oracle):
             assert torch.equal(got, plain) == same
             if not same:
                 check_bf16(got, w4a4_reference(oracle, c, s, n, k, d_w, d_in, x))
+    # the problem named outright (the reference resolves by registered problem): the same group as a
+    # residual projection stays A16 at 4 tokens, as the GDN input it quantizes from the first token
+    x4 = torch.randn(4, k, generator=torch.Generator().manual_seed(4)).to(torch.bfloat16).cuda()
+    plain = nv.linear_group(x4, ws, policy=nv.A16_ONLY)
+    as_residual = nv.linear_group(x4, ws, policy=nv.ALLOW_A4 | nv.PROBLEM_RESIDUAL)
+    as_attention = nv.linear_group(x4, ws, policy=nv.ALLOW_A4 | nv.PROBLEM_ATTN_INPUT)
+    assert all(torch.equal(a, b) for a, b in zip(as_residual, plain))
+    assert all(torch.equal(a, b) for a, b in zip(as_attention, a4))          # what the proportions resolved to
+    x1 = x4[:1].contiguous()
+    gdn = nv.linear_group(x1, ws, policy=nv.ALLOW_A4 | nv.PROBLEM_GDN_INPUT)
+    for (c, s, d_w), (n, d_in), got in zip(planes, shapes, gdn):
+        check_bf16(got, w4a4_reference(oracle, c, s, n, k, d_w, d_in, x1.cpu()))
+    assert not torch.equal(gdn[0], nv.linear_group(x1, ws, policy=nv.A16_ONLY)[0])
+    with pytest.raises(nv.Nvfp4Error):
+        nv.linear_group(x4, ws, policy=nv.ALLOW_A4 | 0x500)                  # no such problem class
     # a projection back to the residual stream (n < k) keeps A16 up to 7 tokens
     c, s, d_w = make_weight(rng, 256, k)
     w = nv.Weight.from_planes(c, s, d_w, 448.0)
@@ -648,9 +663,9 @@ def test_w4a4_tensor_core_route(nv, oracle, tokens, n, k):
 
 
 def test_w4a4_one_cta_forms_agree_with_the_pair_form(nv, oracle, tmp_path):
-    """The prefill GEMM forms kept behind environment switches (one CTA per tile, persistent or not)
-    run in a child process each - the switches are read once per process - on the same operands as
-    this process's CTA-pair form: K is walked in the same order, so the BF16 outputs agree bit for bit."""
+    """The prefill GEMM form kept behind an environment switch (one CTA per tile, persistent) runs in
+    a child process - the switch is read once per process - on the same operands as this process's
+    CTA-pair form: K is walked in the same order, so the BF16 outputs agree bit for bit."""
     import os
     import subprocess
     import sys
@@ -678,8 +693,7 @@ def test_w4a4_one_cta_forms_agree_with_the_pair_form(nv, oracle, tmp_path):
     here = nv.linear(x.cuda(), w, policy=nv.ALLOW_A4, workspace=ws).view(torch.int16).cpu().numpy()
     check_bf16(torch.from_numpy(here).view(torch.bfloat16), w4a4_reference(oracle, codes, scales, n, k, 448.0, 448.0, x))
     root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
-    for switches in ({"B200Q_W4A4_PAIR": "0"}, {"B200Q_W4A4_PAIR": "0", "B200Q_W4A4_PERSISTENT": "0"},
-                     {"B200Q_W4A4_PAIR": "0", "B200Q_W4A4_PERSISTENT": "0", "B200Q_W4A4_BN": "256"}):
+    for switches in ({"B200Q_W4A4_PAIR": "0"},):
         out = tmp_path / ("out_" + "_".join(switches.values()) + ".npy")
         subprocess.run([sys.executable, "-c", script, root, str(tmp_path / "in.npz"), str(out)], check=True,
                        env={**os.environ, **switches}, timeout=600)
