@@ -623,10 +623,13 @@ def measure_head(stream, device, steps: int, warmup: int, peaks: dict, tokens: i
 
 
 def measure_moe(stream, device, steps: int, warmup: int, peaks: dict, tokens: int = 4096, rank: int = 0, world: int = 1,
-                graph: bool = True, barrier=None) -> dict:
+                graph: bool = True, barrier=None, exchange: str = "gathered") -> dict:
     """configs[4]: routed experts + shared expert + combine, TFLOP/s. One GPU: the step is one CUDA
-    graph. N GPUs: expert-parallel, tokens split over the ranks, one all-to-all each way per step
-    (NCCL), timed on the device (the caller takes the max over ranks)."""
+    graph. N GPUs: expert-parallel, tokens split over the ranks. `exchange` "gathered": all-gather
+    of the tokens, every rank runs its experts over all of them, one reduce-scatter of the integer
+    sums (fixed sizes, no host synchronisation, the step is one CUDA graph); "compact": the
+    counted all-to-all each way (sizes known on the host, eager). Timed on the device (the caller
+    takes the max over ranks)."""
     import torch
 
     from ignis_b200 import moe, moe_ep
@@ -645,14 +648,20 @@ def measure_moe(stream, device, steps: int, warmup: int, peaks: dict, tokens: in
         side.wait_stream(main)
         with torch.cuda.stream(side):
             shared, _ = moe.shared_expert(m["shared"][0], m["shared"][1], m["shared"][2], m["x"])
-        acc = moe_ep.routed_experts(m["x"], m["ids"], m["weights"], m["experts"],
-                                    lambda rows, local, w: moe.experts_tokens(rows, local, w, m["table"], m["ws"]),
-                                    phases=phases)
+        run = lambda rows, local, w: moe.experts_tokens(rows, local, w, m["table"], m["ws"])
+        if exchange == "gathered":
+            acc = moe_ep.routed_experts_gathered(m["x"], m["ids"], m["weights"], m["experts"], run, buffers=buffers, phases=phases)
+        else:
+            acc = moe_ep.routed_experts(m["x"], m["ids"], m["weights"], m["experts"], run, phases=phases)
         main.wait_stream(side)
         shared.record_stream(main)
         return moe.combine(m["ws"], shared, m["x"], m["w_gate"], acc=acc)
 
-    use_graph = graph and world == 1   # the exchange sizes its buffers on the host
+    buffers = None
+    if world > 1 and exchange == "gathered":
+        moe_ep.check_shard_table(m["experts"], m["hidden"], m["ids"].shape[1])
+        buffers = moe_ep.GatheredExchange(m["x"].shape[0], m["hidden"], m["ids"].shape[1], m["x"].dtype, device)
+    use_graph = graph and (world == 1 or exchange == "gathered")   # the counted exchange sizes its buffers on the host
     out = one_step()
     stream.synchronize()
     step = one_step
@@ -682,7 +691,8 @@ def measure_moe(stream, device, steps: int, warmup: int, peaks: dict, tokens: in
     status = m["ws"].status()
     h2d = sum(t.numel() * t.element_size() for t in m["host"].values())
     return {"device_ms": device_ms, "e2e_ms": e2e_ms, "status": status, "flops": m["flops"], "hit": m["hit"], "weight_bytes": m["weight_bytes"],
-            "h2d": h2d, "d2h": out_host.numel() * 2, "clocks": sampler.summary(), "graph": use_graph, "tokens": tokens, "split": split}
+            "h2d": h2d, "d2h": out_host.numel() * 2, "clocks": sampler.summary(), "graph": use_graph, "tokens": tokens, "split": split,
+            "exchange": exchange}
 
 
 def moe_line(r: dict, steps: int, warmup: int, world: int, peaks: dict) -> dict:
@@ -696,7 +706,10 @@ def moe_line(r: dict, steps: int, warmup: int, world: int, peaks: dict) -> dict:
                                    f"hidden 2048, intermediate 768, 2.5 bpw trellis records, Zipf(1.1) routing; {r['hit']} experts hit, "
                                    f"{r['weight_bytes'] / 1e6:.0f} MB of expert records",
                        "cuda_graph": r["graph"], "l2": "inputs larger than L2",
-                       "parallelism": "one GPU" if world == 1 else f"expert-parallel over {world} ranks, tokens split, NCCL all-to-all each way",
+                       "parallelism": "one GPU" if world == 1 else (
+                           f"expert-parallel over {world} ranks, tokens split; NCCL all-gather of tokens, reduce-scatter of the integer sums, no host synchronisation"
+                           if r.get("exchange") == "gathered" else
+                           f"expert-parallel over {world} ranks, tokens split, counted NCCL all-to-all each way"),
                        **({"rank0_step_split": r["split"]} if r["split"] else {})},
             "e2e": {"value": r["flops"] / 1e12 / (r["e2e_ms"] / steps * 1e-3), "unit": "TFLOP/s", "h2d_bytes_per_step": r["h2d"],
                     "d2h_bytes_per_step": r["d2h"]},
@@ -1009,7 +1022,7 @@ def run_side_workload(args) -> None:
     with torch.cuda.stream(stream):
         if args.workload == "moe":
             r = measure_moe(stream, device, args.steps, args.warmup, peaks, tokens=args.moe_tokens, rank=rank, world=world, graph=graph,
-                            barrier=barrier)
+                            barrier=barrier, exchange=args.exchange)
             t = torch.tensor([r["device_ms"], r["e2e_ms"], float(r["status"])], dtype=torch.float64, device=device)
             if world > 1:
                 dist.all_reduce(t, op=dist.ReduceOp.MAX)
@@ -1058,6 +1071,8 @@ def main() -> None:
                     help="decode workload under torchrun, how rejoined outputs reach every rank: 3 peer stores + the barrier folded into "
                          "the consuming product (default), 2 peer stores + a barrier launch, 1 NCCL all-gather, 0 outputs stay sharded")
     ap.add_argument("--moe-tokens", type=int, default=4096, help="tokens of the --workload moe step (configs[4]: 4096; up to 8 takes the decode entry's item size)")
+    ap.add_argument("--exchange", choices=["gathered", "compact"], default="gathered",
+                    help="with --workload moe on N > 1 GPUs: the fixed-size all-gather / reduce-scatter exchange, or the counted all-to-all")
     ap.add_argument("--policy", choices=["a16", "a4"], default="a16",
                     help="decode workload: a16 (headline) or a4, the reference's AllowA4 policy (W4A4 from 4 / 5 / 8 tokens)")
     ap.add_argument("--a16", type=int, default=0, help="with --workload prefill: 1 runs the two products under the A16 policy")

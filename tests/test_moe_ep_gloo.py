@@ -78,12 +78,38 @@ def _worker(rank: int, world: int, port: int, failures) -> None:
             assert int(total) == sum(i.numel() for i in ids), f"case {case}: rows lost or duplicated in dispatch"
             if case == 2 and rank == 1:
                 assert sum(seen) == 0   # all experts of the skewed case live on rank 0
-        bad = torch.full((1, TOP_K), EXPERTS, dtype=torch.int32)
+        # the fixed-size form: every rank sees every token, masks what it does not own, one reduce-scatter home
+        for case in (2,):                                 # equal token counts: the fixed-size form needs them
+            xs, ids, ws = _case(case, world)
+
+            def run_all(rows, local, wrow):
+                assert rows.shape[0] == world * xs[rank].shape[0]
+                assert int(local.min()) >= -1 and int(local.max()) < end - begin
+                return _expert(rows, torch.where(local >= 0, local + begin, local), wrow)
+
+            acc = moe_ep.routed_experts_gathered(xs[rank], ids[rank], ws[rank], EXPERTS, run_all)
+            assert torch.equal(acc, _expert(xs[rank], ids[rank], ws[rank])), "gathered form differs from the single-rank sum"
+        # shard tables: agreeing ranks pass; a rank that believes in another expert count is caught on every rank
+        moe_ep.check_shard_table(EXPERTS, HIDDEN, TOP_K)
         try:
-            moe_ep.dispatch(torch.zeros(1, HIDDEN), bad, torch.zeros(1, TOP_K), EXPERTS)
+            moe_ep.check_shard_table(EXPERTS if rank == 0 else 2 * EXPERTS, HIDDEN, TOP_K)
+            failures.append(f"rank {rank}: mismatched shard tables were accepted")
+        except ValueError as exc:
+            assert "disagree" in str(exc)
+        # an id outside the table on ONE rank: every rank raises after the same collective, none is left waiting
+        one = torch.full((1, TOP_K), EXPERTS if rank == world - 1 else 0, dtype=torch.int32)
+        try:
+            moe_ep.dispatch(torch.zeros(1, HIDDEN), one, torch.zeros(1, TOP_K), EXPERTS)
             failures.append(f"rank {rank}: an out-of-range expert id was accepted")
-        except ValueError:
-            pass
+        except ValueError as exc:
+            assert f"rank(s) {world - 1}" in str(exc)
+        # a choice marked NO_EXPERT is nobody's: the exchange skips it as the single-GPU entry points do
+        xs, ids, ws = _case(2, world)
+        holed = ids[rank].clone()
+        holed[0, 0] = moe_ep.NO_EXPERT
+        acc = moe_ep.routed_experts(xs[rank], holed, ws[rank], EXPERTS, lambda rows, local, wrow: _expert(
+            rows, torch.where(local >= 0, local + begin, local), wrow))
+        assert torch.equal(acc, _expert(xs[rank], holed, ws[rank]))
     except Exception as exc:  # an assert in a child is otherwise silent
         failures.append(f"rank {rank}: {exc!r}")
     finally:
@@ -107,3 +133,43 @@ def test_expert_range_rejects_ragged_splits():
         moe_ep.expert_range(512, 0, 3)
     with pytest.raises(ValueError):
         moe_ep.expert_range(512, 8, 8)
+
+
+def _drop_worker(rank: int, world: int, port: int, failures) -> None:
+    """Rank 1 leaves between steps (it never joins the second exchange). Rank 0 learns of it on the
+    host - the collective's timeout raises - instead of waiting for ever."""
+    import datetime
+
+    sys.path.insert(0, ROOT)
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world, timeout=datetime.timedelta(seconds=5))
+    try:
+        from ignis_b200 import moe_ep
+
+        xs, ids, ws = _case(2, world)
+        run_all = lambda rows, local, wrow: _expert(rows, torch.where(local >= 0, local + rank * (EXPERTS // world), local), wrow)
+        moe_ep.routed_experts_gathered(xs[rank], ids[rank], ws[rank], EXPERTS, run_all)   # step 1: both ranks
+        if rank == 1:
+            return                                                                       # the dropped rank: gone before step 2
+        try:
+            moe_ep.routed_experts_gathered(xs[rank], ids[rank], ws[rank], EXPERTS, run_all)
+            failures.append("rank 0: a step completed although its peer had left")
+        except Exception as exc:   # the backend's timeout / connection error, whatever its type
+            if "closed" not in str(exc).lower() and "timed out" not in str(exc).lower() and "timeout" not in str(exc).lower() \
+                    and "reset" not in str(exc).lower() and "peer" not in str(exc).lower():
+                failures.append(f"rank 0: unexpected error text {exc!r}")
+    except Exception as exc:
+        failures.append(f"rank {rank}: {exc!r}")
+    finally:
+        try:
+            dist.destroy_process_group()
+        except Exception:
+            pass
+
+
+def test_a_dropped_rank_is_detected_on_the_host():
+    manager = mp.Manager()
+    failures = manager.list()
+    mp.spawn(_drop_worker, args=(2, _free_port(), failures), nprocs=2, join=True)
+    assert not list(failures), list(failures)
