@@ -158,7 +158,58 @@ MOE_SYMBOLS.update({
     "b200q_moe_combine": (C.c_int32, [_G] + MOE_SYMBOLS["ignis_moe_combine"][1]),
 })
 
-ALL_SYMBOLS = {**NVFP4_SYMBOLS, **TRELLIS_SYMBOLS, **MOE_SYMBOLS}
+
+
+class ArtifactObject(C.Structure):
+    """``b200q_artifact_object`` (include/b200q_artifact.h)."""
+
+    _fields_ = [("name", C.c_char_p), ("kind", C.c_uint32), ("format", C.c_uint32), ("layout", C.c_uint32), ("rank", C.c_uint32),
+                ("shape", C.c_uint64 * 16), ("offset", C.c_uint64), ("bytes", C.c_uint64), ("file_offset", C.c_uint64),
+                ("data", C.c_void_p)]
+
+
+class BlockscaleGeometry(C.Structure):
+    """``b200q_blockscale_geometry``: nine u64."""
+
+    _fields_ = [(k, C.c_uint64) for k in ("rows", "columns", "groups_per_row", "k_tiles", "code_plane_bytes", "scale_plane_offset",
+                                          "scale_plane_bytes", "weight_divisor_offset", "encoded_bytes")]
+
+
+class TrellisGeometry(C.Structure):
+    """``b200q_trellis_geometry``: eight u64."""
+
+    _fields_ = [(k, C.c_uint64) for k in ("rows", "columns", "k2", "trellis_bytes", "suh_offset", "svh_offset", "data_bytes",
+                                          "encoded_bytes")]
+
+
+_U64P = C.POINTER(C.c_uint64)
+ARTIFACT_SYMBOLS = {
+    "b200q_artifact_format_by_name": (C.c_uint32, [C.c_char_p]),
+    "b200q_artifact_layout_by_name": (C.c_uint32, [C.c_char_p]),
+    "b200q_artifact_format_name": (C.c_char_p, [C.c_uint32]),
+    "b200q_artifact_layout_name": (C.c_char_p, [C.c_uint32]),
+    "b200q_artifact_trellis_k2": (C.c_uint32, [C.c_uint32]),
+    "b200q_artifact_alignment": (C.c_uint64, [C.c_uint32]),
+    "b200q_artifact_encoded_size": (C.c_int32, [C.c_uint32, C.c_uint32, _U64P, C.c_uint32, _U64P]),
+    "b200q_artifact_blockscale_geometry": (C.c_int32, [C.c_uint32, _U64P, C.c_uint32, C.POINTER(BlockscaleGeometry)]),
+    "b200q_artifact_trellis_geometry": (C.c_int32, [C.c_uint32, _U64P, C.c_uint32, C.POINTER(TrellisGeometry)]),
+    "b200q_artifact_open": (C.c_int32, [C.c_char_p, C.POINTER(C.c_void_p)]),
+    "b200q_artifact_close": (None, [C.c_void_p]),
+    "b200q_artifact_model_id": (C.c_char_p, [C.c_void_p]),
+    "b200q_artifact_weights_id": (C.c_char_p, [C.c_void_p]),
+    "b200q_artifact_object_count": (C.c_uint64, [C.c_void_p]),
+    "b200q_artifact_payload_offset": (C.c_uint64, [C.c_void_p]),
+    "b200q_artifact_file_bytes": (C.c_uint64, [C.c_void_p]),
+    "b200q_artifact_object_at": (C.c_int32, [C.c_void_p, C.c_uint64, C.POINTER(ArtifactObject)]),
+    "b200q_artifact_find": (C.c_int32, [C.c_void_p, C.c_char_p, C.POINTER(ArtifactObject)]),
+    "b200q_artifact_content_hash": (C.c_int32, [C.c_void_p, C.POINTER(C.c_uint8 * 32)]),
+    "b200q_artifact_divisor_name": (C.c_int32, [C.c_char_p, C.c_char_p, C.c_uint64]),
+    "b200q_artifact_nvfp4_weight": (C.c_int32, [C.c_void_p, C.c_char_p, C.c_char_p, C.c_void_p, C.POINTER(Nvfp4Weight)]),
+    "b200q_artifact_trellis_weight": (C.c_int32, [C.c_void_p, C.c_char_p, C.c_void_p, C.POINTER(TrellisWeight)]),
+    "b200q_artifact_last_error": (C.c_char_p, []),
+}
+
+ALL_SYMBOLS = {**NVFP4_SYMBOLS, **TRELLIS_SYMBOLS, **MOE_SYMBOLS, **ARTIFACT_SYMBOLS}
 
 
 def load() -> C.CDLL:

@@ -2,7 +2,7 @@
 
     python -m ignis_b200.build [--force] [--verbose]
 
-Every .cu under csrc/ is compiled with nvcc to an object (in parallel) and linked into one
+Every .cu and .cpp under csrc/ is compiled with nvcc to an object (in parallel) and linked into one
 shared library with the CUDA runtime linked statically, so the file loads beside any PyTorch
 build. nvcc cross-compiles without a GPU.
 """
@@ -27,7 +27,7 @@ FLAGS = [
 
 
 def _sources() -> list[str]:
-    return sorted(glob.glob(os.path.join(CSRC, "*.cu")))
+    return sorted(glob.glob(os.path.join(CSRC, "*.cu")) + glob.glob(os.path.join(CSRC, "*.cpp")))
 
 
 def _deps() -> list[str]:
@@ -44,7 +44,7 @@ def _stale(target: str, sources: list[str]) -> bool:
 
 
 def _compile(src: str, verbose: bool) -> str:
-    obj = os.path.join(OBJ, os.path.basename(src)[:-3] + ".o")
+    obj = os.path.join(OBJ, os.path.splitext(os.path.basename(src))[0] + ".o")
     if _stale(obj, [src] + _deps()):
         cmd = [NVCC, *FLAGS, "-c", src, "-o", obj] + (["-Xptxas", "-v"] if verbose else [])
         res = subprocess.run(cmd, capture_output=True, text=True)

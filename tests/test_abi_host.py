@@ -19,7 +19,7 @@ def _declared_symbols():
     for path in sorted(glob.glob(os.path.join(ROOT, "include", "*.h"))):
         text = open(path).read()
         text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
-        names += re.findall(r"^\s*(?:const\s+char\s*\*|u?int(?:32|64)_t)\s*\*?\s*(\w+)\s*\(", text, flags=re.M)
+        names += re.findall(r"^\s*(?:const\s+char\s*\*|u?int(?:32|64)_t|void)\s*\*?\s*(\w+)\s*\(", text, flags=re.M)
     return names
 
 
