@@ -992,12 +992,98 @@ def run_cuda_arm(args) -> None:
     print(json.dumps(line))
 
 
+def measure_timeline(stream, device, layers: int, tokens: int, policy_name: str) -> dict:
+    """Where a decode launch's time goes, from the phase stamps of the trace build of the library
+    (`python -m ignis_b200.build --trace`): the step is `layers` layers of configs[1] replayed as one
+    CUDA graph; per call of a layer, medians over the steady-state layers of
+      gap      predecessor's last CTA through its K reduction -> this grid's first CTA sees it complete
+      rewrite  -> activations rewritten as fragments (median CTA)
+      loop     -> K loop done (median CTA)
+      straggle -> K loop done in the last CTA
+      finish   -> last CTA through the cluster's meeting point (the epilogue's stores follow)
+    all in microseconds. The stamps cost a little: the step runs about 1 % slower than the shipped one."""
+    import ctypes as C
+
+    import numpy as np
+    import torch
+
+    from ignis_b200 import _lib, nvfp4
+
+    lib = _lib.load()
+    if not hasattr(lib, "b200q_debug_gemv_trace"):
+        raise SystemExit("the timeline needs the trace build: python -m ignis_b200.build --trace")
+    weights, _, inputs, outputs = build_workload(layers, 0, 1, tokens, device)
+    by_name = {name: (n, k, src) for name, n, k, src in LAYER}
+    policy = nvfp4.ALLOW_A4 if policy_name == "a4" else nvfp4.A16_ONLY
+    if policy != nvfp4.A16_ONLY:
+        raise SystemExit("the phase stamps sit in the A16 decode kernel")
+
+    def one_step() -> None:
+        for layer in weights:
+            for names in GROUPS:
+                src = inputs[by_name[names[0]][2]]
+                ws = [layer[nm] for nm in names]
+                if len(names) == 1:
+                    nvfp4.linear(src, ws[0], out=outputs[names[0]], policy=policy)
+                else:
+                    nvfp4.linear_group(src, ws, outs=[outputs[nm] for nm in names], policy=policy)
+
+    step = graphed(stream, one_step, True)
+    for _ in range(3):
+        step()
+    stream.synchronize()
+    stamps = np.zeros((128, 512, 8), np.uint64)
+    lib.b200q_debug_gemv_trace.restype = C.c_int32
+    lib.b200q_debug_gemv_trace.argtypes = [C.c_void_p, C.c_uint64]
+    assert lib.b200q_debug_gemv_trace(stamps.ctypes.data, stamps.nbytes) == 0      # drop the warm-up's stamps
+    ms = time_region(stream, step, 1, 0)
+    assert lib.b200q_debug_gemv_trace(stamps.ctypes.data, stamps.nbytes) == 0
+    launches = []
+    for slot in range(stamps.shape[0]):
+        grid = int(stamps[slot, 0, 7] >> np.uint64(32))
+        if grid:
+            t = stamps[slot, :min(grid, 512), :7].astype(np.int64)
+            launches.append((int(t[:, 0].min()), grid, t))
+    launches.sort(key=lambda e: e[0])
+    if len(launches) != layers * len(GROUPS):
+        raise SystemExit(f"expected {layers * len(GROUPS)} stamped launches, found {len(launches)}")
+    rows = {i: [] for i in range(len(GROUPS))}
+    prev_end = None
+    for idx, (_, grid, t) in enumerate(launches):
+        if prev_end is not None and idx >= 2 * len(GROUPS):     # the first two layers run behind a cold start
+            ready, looped = np.median(t[:, 3]), np.median(t[:, 4])
+            rows[idx % len(GROUPS)].append([(t[:, 2].min() - prev_end) / 1e3, (ready - t[:, 2].min()) / 1e3, (looped - ready) / 1e3,
+                                            (t[:, 4].max() - looped) / 1e3, (t[:, 6].max() - t[:, 4].max()) / 1e3,
+                                            (t[:, 6].max() - prev_end) / 1e3, float(np.mean(t[:, 0] < prev_end - 1000)), grid])
+        prev_end = t[:, 6].max()
+    calls = {}
+    for i, names in enumerate(GROUPS):
+        m = np.mean(np.array(rows[i]), axis=0)
+        nbytes = sum(weight_bytes(by_name[nm][0], by_name[nm][1]) for nm in names)
+        calls["|".join(names)] = {"ctas": int(m[7]), "weight_mb": nbytes / 1e6, "gap_us": m[0], "rewrite_us": m[1], "loop_us": m[2],
+                                  "straggle_us": m[3], "finish_us": m[4], "total_us": m[5], "ctas_resident_early": m[6],
+                                  "loop_gbs": nbytes / (m[2] * 1e-6) / 1e9, "call_gbs": nbytes / (m[5] * 1e-6) / 1e9}
+    layer_us = sum(c["total_us"] for c in calls.values())
+    return {"metric": "nvfp4_decode_layer_timeline_us", "value": layer_us, "unit": "us", "steps": 1, "warmup": 3, "ms_per_step": ms,
+            "higher_is_better": False, "dtype": DTYPE,
+            "config": {"workload": f"configs[1] decode chain, {layers} layers x {len(GROUPS)} calls, {tokens} tokens, one CUDA graph; "
+                                   "phase stamps of the trace build", "l2": "weights larger than L2"},
+            "calls": calls,
+            "share": {k: sum(c[k] for c in calls.values()) / layer_us for k in ("gap_us", "rewrite_us", "loop_us", "straggle_us", "finish_us")}}
+
+
 def run_side_workload(args) -> None:
     """`--workload X`: one of the other configs alone, one JSON line, same timing rules as the headline."""
     import torch
     import torch.distributed as dist
 
-    from ignis_b200 import nvfp4, trellis
+    from ignis_b200 import _lib, nvfp4, trellis
+
+    if args.workload == "timeline":     # the library with the phase stamps compiled in stands in for the shipped one
+        trace_lib = os.path.join(ROOT, "ignis_b200", "libignis_b200_trace.so")
+        if not os.path.exists(trace_lib):
+            raise SystemExit("the timeline needs the trace build: python -m ignis_b200.build --trace")
+        _lib.LIB_PATH = trace_lib
 
     if not torch.cuda.is_available():
         raise SystemExit("bench.py needs a CUDA device")
@@ -1040,6 +1126,8 @@ def run_side_workload(args) -> None:
             fp4 = measure_fp4_peak(stream, device, seconds=args.peak_seconds)
             line = {**base, "metric": "fp4_mma_peak_tflops", "value": fp4["burst_tflops"], "unit": "TFLOP/s", "steps": 0, "warmup": 0,
                     "ms_per_step": None, "dtype": "e2m1 x e2m1 (ue4m3 block scales) -> f32", "config": {"workload": fp4["how"]}, "fp4_peak": fp4}
+        elif args.workload == "timeline":
+            line = {**base, **measure_timeline(stream, device, min(args.layers, 24), args.tokens, args.policy)}
         elif args.workload == "config0":
             weights, _, _, _ = build_workload(args.layers, 0, 1, 1, device)
             line = {**base, **measure_config0(stream, device, weights, args.steps, args.warmup, peaks, graph=graph)}
@@ -1081,9 +1169,10 @@ def main() -> None:
     ap.add_argument("--peak-seconds", type=float, default=6.0, help="with --workload peak: seconds of back-to-back launches per issue form")
     ap.add_argument("--extras", type=int, default=1, help="0: the headline alone (no config0 / config2 / config3 / config4 objects)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
-    ap.add_argument("--workload", default="decode", choices=["decode", "config0", "prefill", "trellis", "moe", "head", "peak"],
+    ap.add_argument("--workload", default="decode", choices=["decode", "config0", "prefill", "trellis", "moe", "head", "peak", "timeline"],
                     help="decode: configs[1] (the headline, with the other configs as objects); config0 / prefill / trellis / moe: "
-                         "configs[0] / [2] / [3] / [4] alone; head: the output head; peak: the FP4 tensor-core loop")
+                         "configs[0] / [2] / [3] / [4] alone; head: the output head; peak: the FP4 tensor-core loop; timeline: where a decode "
+                         "launch's time goes (needs python -m ignis_b200.build --trace)")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference_arm(args)

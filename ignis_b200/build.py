@@ -1,10 +1,14 @@
 """Builds the CUDA library in-tree: ignis_b200/libignis_b200.so (sm_100a only).
 
-    python -m ignis_b200.build [--force] [--verbose]
+    python -m ignis_b200.build [--force] [--verbose] [--trace]
 
 Every .cu and .cpp under csrc/ is compiled with nvcc to an object (in parallel) and linked into one
 shared library with the CUDA runtime linked statically, so the file loads beside any PyTorch
 build. nvcc cross-compiles without a GPU.
+
+--trace builds a second library beside it, ignis_b200/libignis_b200_trace.so: the same objects except
+the NVFP4 decode kernel compiled with -DB200Q_GEMV_TRACE (phase time stamps per CTA, read by
+`bench.py --workload timeline`). The shipped library never carries the stamps.
 """
 from __future__ import annotations
 
@@ -18,6 +22,8 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 OBJ = os.path.join(HERE, "build")
 LIB = os.path.join(HERE, "libignis_b200.so")
+TRACE_LIB = os.path.join(HERE, "libignis_b200_trace.so")
+TRACE_SOURCES = ("nvfp4_gemv.cu",)   # the files B200Q_GEMV_TRACE changes
 NVCC = os.environ.get("NVCC", "/usr/local/cuda/bin/nvcc")
 
 FLAGS = [
@@ -43,10 +49,10 @@ def _stale(target: str, sources: list[str]) -> bool:
     return any(os.path.getmtime(s) > t for s in sources)
 
 
-def _compile(src: str, verbose: bool) -> str:
-    obj = os.path.join(OBJ, os.path.splitext(os.path.basename(src))[0] + ".o")
+def _compile(src: str, verbose: bool, trace: bool = False) -> str:
+    obj = os.path.join(OBJ, os.path.splitext(os.path.basename(src))[0] + (".trace.o" if trace else ".o"))
     if _stale(obj, [src] + _deps()):
-        cmd = [NVCC, *FLAGS, "-c", src, "-o", obj] + (["-Xptxas", "-v"] if verbose else [])
+        cmd = [NVCC, *FLAGS, "-c", src, "-o", obj] + (["-Xptxas", "-v"] if verbose else []) + (["-DB200Q_GEMV_TRACE"] if trace else [])
         res = subprocess.run(cmd, capture_output=True, text=True)
         if verbose or res.returncode != 0:
             sys.stderr.write(res.stdout + res.stderr)
@@ -70,5 +76,21 @@ def build(force: bool = False, verbose: bool = False) -> str:
     return LIB
 
 
+def build_trace(verbose: bool = False) -> str:
+    """The library with the decode kernel's phase stamps compiled in (see the module text)."""
+    build(verbose=verbose)
+    objs = []
+    for src in _sources():
+        traced = os.path.basename(src) in TRACE_SOURCES
+        objs.append(_compile(src, verbose, trace=True) if traced else os.path.join(OBJ, os.path.splitext(os.path.basename(src))[0] + ".o"))
+    if _stale(TRACE_LIB, objs):
+        subprocess.run([NVCC, "-shared", "-o", TRACE_LIB, *objs, "-gencode", "arch=compute_100a,code=sm_100a", "-cudart", "static",
+                        "-Xlinker", "--exclude-libs=ALL"], check=True)
+    return TRACE_LIB
+
+
 if __name__ == "__main__":
-    print(build(force="--force" in sys.argv, verbose="--verbose" in sys.argv))
+    if "--trace" in sys.argv:
+        print(build_trace(verbose="--verbose" in sys.argv))
+    else:
+        print(build(force="--force" in sys.argv, verbose="--verbose" in sys.argv))

@@ -32,6 +32,35 @@ namespace {
 constexpr int kThreads = 256;
 constexpr int kWarps = 8;
 
+// A build with -DB200Q_GEMV_TRACE (python -m ignis_b200.build --trace: a second library, never the
+// shipped one) stamps the global timer at the phase boundaries of every CTA, for the timeline of a
+// chain of calls: [0] entry, [1] first weight loads issued, [2] predecessor complete, [3]
+// activations rewritten, [4] K loop done, [5] partial sums written, [6] cluster met, [7] SM and
+// grid size. The host numbers the launches (modulo 128) in bits 16..22 of the epilogue word, which
+// the kernel otherwise reads through single-bit masks.
+#ifdef B200Q_GEMV_TRACE
+constexpr int kTraceLaunches = 128, kTraceCtas = 512, kTraceWords = 8;
+__device__ unsigned long long g_trace[kTraceLaunches][kTraceCtas][kTraceWords];
+__device__ __forceinline__ void trace_stamp(int launch, int word) {
+  if (launch < 0 || blockIdx.x >= kTraceCtas) return;
+  unsigned long long now;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(now));
+  g_trace[launch][blockIdx.x][word] = now;
+}
+#define GEMV_TRACE_BEGIN(word)                                                   \
+  const int trace_launch = threadIdx.x == 0 ? static_cast<int>(((word) >> 16) & 127u) : -1; \
+  if (trace_launch >= 0 && blockIdx.x < kTraceCtas) {                            \
+    unsigned int sm;                                                             \
+    asm volatile("mov.u32 %0, %%smid;" : "=r"(sm));                              \
+    g_trace[trace_launch][blockIdx.x][7] = sm | (static_cast<unsigned long long>(gridDim.x) << 32); \
+  }                                                                              \
+  trace_stamp(trace_launch, 0)
+#define GEMV_TRACE(word) trace_stamp(trace_launch, word)
+#else
+#define GEMV_TRACE_BEGIN(word) ((void)0)
+#define GEMV_TRACE(word) ((void)0)
+#endif
+
 struct Stage {
   uint32_t c[4][8];  // 32 bytes of codes for each of the lane's four rows
   uint4 sc;          // scales: .x .y .z .w = rows q = 0..3, byte j = group j of the lane's scale tile
@@ -184,40 +213,55 @@ __device__ __forceinline__ uint4 convert_chunk(const uint4 v, float scale, int i
                     *reinterpret_cast<uint32_t *>(&r[2]), *reinterpret_cast<uint32_t *>(&r[3]));
 }
 
-__device__ __forceinline__ float chunk_amax(const uint4 v) {
-  const uint32_t w[4] = {v.x, v.y, v.z, v.w};
-  float amax = 0.0f;
-#pragma unroll
-  for (int j = 0; j < 4; ++j) {
-    amax = fmaxf(amax, fabsf(bf16_bits_to_f32(w[j] & 0xFFFFu)));
-    amax = fmaxf(amax, fabsf(__uint_as_float(w[j] & 0xFFFF0000u)));
-  }
-  return amax;
+// The largest magnitude among eight BF16 values and a running pair of maxima, as bit patterns: the
+// magnitudes of finite BF16 numbers order like their bits read as unsigned integers, so the maximum
+// is two 16-bit integer maxima per word (infinities and NaNs come out on top and are caught by the
+// caller). `run` holds one maximum per half.
+__device__ __forceinline__ uint32_t chunk_amax_bits(const uint4 v, uint32_t run) {
+  run = __vmaxu2(run, v.x & 0x7FFF7FFFu);
+  run = __vmaxu2(run, v.y & 0x7FFF7FFFu);
+  run = __vmaxu2(run, v.z & 0x7FFF7FFFu);
+  run = __vmaxu2(run, v.w & 0x7FFF7FFFu);
+  return run;
 }
+
+// The power of two that brings a token's largest magnitude (BF16 bits, sign cleared) into
+// [2^13, 2^14): 14 minus the exponent frexp would report, held to what a float can carry; zero for
+// an all-zero slice and for one that holds an infinity or a NaN.
+__device__ __forceinline__ int amax_shift(uint32_t amax_bits) {
+  if (amax_bits == 0u || amax_bits >= 0x7F80u) return 0;
+  const int e8 = static_cast<int>(amax_bits >> 7);  // 0 for a subnormal maximum: far below every clamp
+  return e8 == 0 ? 126 : max(-126, min(126, 140 - e8));
+}
+__device__ __forceinline__ float pow2f(int e) { return __uint_as_float(static_cast<uint32_t>(e + 127) << 23); }  // e in [-126, 127]
 
 constexpr int kPrepRegs = 5;  // chunks a lane keeps in registers between the amax and the store
 
 // Rewrites steps [cb, ce) of the activations as scaled fp16 B fragments. Warp w prepares token
-// slots w, w + 8, ...; lane l owns the 16-byte chunk l of every step (t = l / 8 is the lane
-// quarter that will read it, i = l % 8 the word it multiplies). The slot's inverse scale goes to
+// slots w, w + 8, ...; a lane owns one 16-byte chunk of every step (t: the lane quarter that will
+// read it, i: the word it multiplies). The slot's inverse scale goes to
 // inv_s, its scale to scale_s.
 template <int NT, int XU>
 __device__ __forceinline__ void prepare_activations(const GemvParams &p, int cb, int ce, uint4 *xs, float *inv_s,
                                                     float *scale_s, int warp, int lane) {
   const int nsteps = ce - cb;
+  // Lane l takes chunk l of a step: t = l / 8 is the lane quarter that will read it, i = l % 8 the
+  // word it multiplies. (Dealing the chunks so that the fragment stores avoid their four-way bank
+  // conflict scatters each quarter-warp's global load over four lines, and measured slower.)
   const int t = lane >> 3, i = lane & 7;
+  const int chunk = lane;
   const int slot = ((warp ^ i) << 2) | t;  // fragment slot of lane (g = warp, t), swizzled by the word
 #pragma unroll
   for (int tt = 0; tt < NT; ++tt) {
     const uint32_t tok = static_cast<uint32_t>(tt * 8 + warp);
     const bool live = tok < p.tokens;
     const uint4 *src =
-        reinterpret_cast<const uint4 *>(p.x + static_cast<size_t>(tok) * p.k + static_cast<size_t>(cb) * 256u) + lane;
+        reinterpret_cast<const uint4 *>(p.x + static_cast<size_t>(tok) * p.k + static_cast<size_t>(cb) * 256u) + chunk;
     // steps whose chunk for this lane lies inside K
-    const int inside = (static_cast<int>(p.k / 8u) - cb * 32 - lane + 31) / 32;
+    const int inside = (static_cast<int>(p.k / 8u) - cb * 32 - chunk + 31) / 32;
     const int valid = live ? min(nsteps, max(inside, 0)) : 0;
     uint4 *dst = xs + tt * 32 + slot + static_cast<size_t>(i) * NT * 32;
-    float amax = 0.0f;
+    uint32_t amax = 0u;  // one running maximum per 16-bit half
     uint4 held[kPrepRegs];
     const bool hold = nsteps <= kPrepRegs;
     if (hold) {
@@ -227,21 +271,27 @@ __device__ __forceinline__ void prepare_activations(const GemvParams &p, int cb,
         if (m < valid) held[m] = ldg128_coherent(src + m * 32);
       }
 #pragma unroll
-      for (int m = 0; m < kPrepRegs; ++m) amax = fmaxf(amax, chunk_amax(held[m]));
+      for (int m = 0; m < kPrepRegs; ++m) amax = chunk_amax_bits(held[m], amax);
     } else {
-      for (int m = 0; m < valid; ++m) amax = fmaxf(amax, chunk_amax(ldg128_coherent(src + m * 32)));
+      // a longer slice does not fit in registers beside the two weight stages: two passes over it,
+      // four loads in flight at a time
+      for (int m0 = 0; m0 < valid; m0 += 4) {
+        uint4 v[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          v[j] = make_uint4(0u, 0u, 0u, 0u);
+          if (m0 + j < valid) v[j] = ldg128_coherent(src + (m0 + j) * 32);
+        }
+#pragma unroll
+        for (int j = 0; j < 4; ++j) amax = chunk_amax_bits(v[j], amax);
+      }
     }
 #pragma unroll
-    for (int o = 16; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xFFFFFFFFu, amax, o));
-    int shift = 0;
-    if (amax > 0.0f && amax <= 3.0e38f) {
-      int e;
-      (void)frexpf(amax, &e);  // amax in [2^(e-1), 2^e)
-      shift = max(-126, min(126, 14 - e));
-    }
-    const float scale = ldexpf(1.0f, shift);
+    for (int o = 16; o > 0; o >>= 1) amax = __vmaxu2(amax, __shfl_xor_sync(0xFFFFFFFFu, amax, o));
+    const int shift = amax_shift(max(amax & 0xFFFFu, amax >> 16));
+    const float scale = pow2f(shift);
     if (lane == 0) {
-      inv_s[tt * 8 + warp] = live ? ldexpf(1.0f, -shift) : 0.0f;
+      inv_s[tt * 8 + warp] = live ? pow2f(-shift) : 0.0f;
       scale_s[tt * 8 + warp] = scale;
     }
     if (hold) {
@@ -250,10 +300,17 @@ __device__ __forceinline__ void prepare_activations(const GemvParams &p, int cb,
         if (m < nsteps) dst[static_cast<size_t>(m) * 8 * NT * 32] = convert_chunk<XU>(held[m], scale, i);
       }
     } else {
-      for (int m = 0; m < nsteps; ++m) {
-        uint4 v = make_uint4(0u, 0u, 0u, 0u);
-        if (m < valid) v = ldg128_coherent(src + m * 32);
-        dst[static_cast<size_t>(m) * 8 * NT * 32] = convert_chunk<XU>(v, scale, i);
+      for (int m0 = 0; m0 < nsteps; m0 += 4) {
+        uint4 v[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          v[j] = make_uint4(0u, 0u, 0u, 0u);
+          if (m0 + j < valid) v[j] = ldg128_coherent(src + (m0 + j) * 32);
+        }
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          if (m0 + j < nsteps) dst[static_cast<size_t>(m0 + j) * 8 * NT * 32] = convert_chunk<XU>(v[j], scale, i);
+        }
       }
     }
   }
@@ -264,6 +321,7 @@ __global__ void __launch_bounds__(kThreads, NT <= 2 ? 2 : 1) nvfp4_gemv_kernel(c
   extern __shared__ __align__(16) uint8_t smem_raw[];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int g = lane >> 2, t = lane & 3;
+  GEMV_TRACE_BEGIN(p.epilogue);
   const int rm = static_cast<int>(p.rm), kw_count = kWarps / rm;
   const int rgl = warp % rm, kw = warp / rm;
   const uint32_t kc = p.kc;
@@ -318,8 +376,10 @@ __global__ void __launch_bounds__(kThreads, NT <= 2 ? 2 : 1) nvfp4_gemv_kernel(c
   load_stage(st1, rows, s + kw_count, c1, t, scale_tiles);
 
   // The weights above never depend on the previous kernel; the activations may.
+  GEMV_TRACE(1);
   griddep_launch_dependents();
   griddep_wait();
+  GEMV_TRACE(2);
   if (p.wait.flags_peers != nullptr) {
     // x lies in a buffer every rank's previous product stored its columns into. The barrier between
     // the ranks rides here, in the consumer's first instructions, instead of in a launch of its own:
@@ -365,6 +425,7 @@ __global__ void __launch_bounds__(kThreads, NT <= 2 ? 2 : 1) nvfp4_gemv_kernel(c
     }
     prepare_activations<NT, XU>(p, cb, ce, xs, inv_s, scale_s, warp, lane);
     __syncthreads();
+    if (cb == c0) GEMV_TRACE(3);
     if (cb != c0) {
 #pragma unroll
       for (int tt = 0; tt < NT; ++tt) {
@@ -392,6 +453,7 @@ __global__ void __launch_bounds__(kThreads, NT <= 2 ? 2 : 1) nvfp4_gemv_kernel(c
       }
     }
   }
+  GEMV_TRACE(4);
   // back to the activations' own units
 #pragma unroll
   for (int tt = 0; tt < NT; ++tt) {
@@ -435,7 +497,9 @@ __global__ void __launch_bounds__(kThreads, NT <= 2 ? 2 : 1) nvfp4_gemv_kernel(c
   }
 
   // ---- K reduction across the cluster, then the epilogue, the items dealt over ranks and warps ----
+  GEMV_TRACE(5);
   cluster_sync_all();
+  GEMV_TRACE(6);
   const int out_groups = swiglu ? rm / 2 : rm;
   const int items = out_groups * 2 * NT;
   const float coef = W.inv_dw * 128.0f;  // the operands carried 2^-7
@@ -533,6 +597,21 @@ cudaError_t launch_for_nt(int nt, const GemvParams &p, uint32_t ctas, size_t sme
 
 }  // namespace
 
+#ifdef B200Q_GEMV_TRACE
+}  // namespace b200q
+// Copies the stamps out ([128][512][8] u64) and clears them for the next window.
+extern "C" int32_t b200q_debug_gemv_trace(void *out, uint64_t bytes) {
+  if (out == nullptr || bytes != sizeof(b200q::g_trace)) return -1;
+  if (cudaDeviceSynchronize() != cudaSuccess) return -1;
+  if (cudaMemcpyFromSymbol(out, b200q::g_trace, bytes) != cudaSuccess) return -1;
+  void *stamps = nullptr;
+  if (cudaGetSymbolAddress(&stamps, b200q::g_trace) != cudaSuccess) return -1;
+  if (cudaMemset(stamps, 0, sizeof(b200q::g_trace)) != cudaSuccess) return -1;
+  return 0;
+}
+namespace b200q {
+#endif
+
 int32_t gemv_prepare(ErrorSlot &slot) {
   cudaError_t err = set_smem_attrs<0>();
   if (err == cudaSuccess) err = set_smem_attrs<2>();
@@ -614,6 +693,10 @@ int32_t gemv_launch(ErrorSlot &slot, const DeviceState &dev, GemvParams &p, int 
   p.rm = plan.rm;
   p.kc = plan.kc;
   p.xs_steps = plan.xs_steps;
+#ifdef B200Q_GEMV_TRACE
+  static uint32_t trace_counter = 0;
+  p.epilogue = (p.epilogue & 0xFFFFu) | ((trace_counter++ & 127u) << 16);
+#endif
   const size_t smem = gemv_smem_bytes(nt, plan.rm, plan.xs_steps);
   if (smem > kGemvMaxSmem) return fail(slot, "nvfp4 decode: %zu bytes of shared memory exceed the kernel's limit", smem);
   cudaError_t err;
