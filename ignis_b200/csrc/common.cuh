@@ -59,6 +59,13 @@ struct DeviceState {
 DeviceState *device_state(ErrorSlot &slot);
 // Prepares the current device once (thread-safe). 0 on success.
 int32_t prepare_device(ErrorSlot &slot);
+// Kernel attributes of one family each (defined beside the kernels), and all of them behind
+// prepare_device: what every *_prepare entry point runs, so that a process that prepared through one
+// family's entry can call the others' ops too.
+int32_t prepare_nvfp4_kernels(ErrorSlot &slot);
+int32_t prepare_trellis_kernels(ErrorSlot &slot);
+int32_t prepare_moe_kernels(ErrorSlot &slot);
+int32_t prepare_all(ErrorSlot &slot);
 
 // The trellis tile decoder as a launch (trellis_linear.cu), shared by the dense and MoE entry points.
 int32_t trellis_reconstruct_raw(ErrorSlot &slot, const char *what, const void *trellis, uint32_t k2, uint32_t in,

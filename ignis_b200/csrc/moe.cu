@@ -857,6 +857,12 @@ int32_t run_experts(const Geometry &g, const void *x, uint32_t tokens, const int
 }
 
 }  // namespace
+
+int32_t prepare_moe_kernels(ErrorSlot &slot) {
+  const cudaError_t err = cudaFuncSetAttribute(moe_router_logits_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024);
+  if (err != cudaSuccess) return fail(slot, "ignis_moe_prepare: %s", cudaGetErrorString(err));
+  return moe_tc_prepare(slot);
+}
 }  // namespace b200q
 
 using namespace b200q;
@@ -888,13 +894,7 @@ int32_t ignis_moe_trellis_reconstruct(const void *trellis, uint32_t k2, uint32_t
   return trellis_reconstruct_raw(moe_error(), "ignis_moe_trellis_reconstruct", trellis, k2, in, out, 0, w_f16, stream);
 }
 
-int32_t ignis_moe_prepare(void) {
-  ErrorSlot &slot = moe_error();
-  if (prepare_device(slot) != 0) return -1;
-  cudaError_t err = cudaFuncSetAttribute(moe_router_logits_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024);
-  if (err != cudaSuccess) return fail(slot, "ignis_moe_prepare: %s", cudaGetErrorString(err));
-  return moe_tc_prepare(slot);
-}
+int32_t ignis_moe_prepare(void) { return prepare_all(moe_error()); }
 
 uint64_t b200q_moe_workspace_bytes(const b200q_moe_geometry *geometry, uint32_t decode_tokens, uint32_t prefill_tokens) {
   if (check_geometry(moe_error(), geometry, "ignis_moe_workspace_bytes") != 0) return 0;

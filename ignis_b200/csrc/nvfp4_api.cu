@@ -212,16 +212,18 @@ int32_t linear_group_impl(const b200q_nvfp4_weight *const *w, uint32_t count, co
 
 using namespace b200q;
 
-extern "C" {
-
-int32_t b200q_nvfp4_prepare(void) {
-  ErrorSlot &slot = nvfp4_error();
-  if (prepare_device(slot) != 0) return -1;
+namespace b200q {
+int32_t prepare_nvfp4_kernels(ErrorSlot &slot) {
   if (gemv_prepare(slot) != 0) return -1;
   if (a16mma_prepare(slot) != 0) return -1;
   if (w4a4_decode_prepare(slot) != 0) return -1;
   return w4a4_prepare(slot);
 }
+}  // namespace b200q
+
+extern "C" {
+
+int32_t b200q_nvfp4_prepare(void) { return prepare_all(nvfp4_error()); }
 
 uint64_t b200q_nvfp4_workspace_bytes(uint32_t n, uint32_t k, uint32_t policy, uint32_t tokens) {
   if (n == 0 || (n % 128u) != 0 || k == 0 || (k % 64u) != 0 || tokens == 0) return 0;

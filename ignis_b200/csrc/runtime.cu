@@ -50,6 +50,13 @@ DeviceState *device_state(ErrorSlot &slot) {
   return &g_state[device];
 }
 
+int32_t prepare_all(ErrorSlot &slot) {
+  if (prepare_device(slot) != 0) return -1;
+  if (prepare_nvfp4_kernels(slot) != 0) return -1;
+  if (prepare_trellis_kernels(slot) != 0) return -1;
+  return prepare_moe_kernels(slot);
+}
+
 int32_t prepare_device(ErrorSlot &slot) {
   std::lock_guard<std::mutex> lock(g_mutex);
   DeviceState *state = device_state(slot);

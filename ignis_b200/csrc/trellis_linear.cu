@@ -592,17 +592,19 @@ int32_t trellis_reconstruct_raw(ErrorSlot &slot, const char *what, const void *t
 
 }  // namespace b200q
 
-using namespace b200q;
-
-extern "C" {
-
-int32_t ignis_trellis_prepare(void) {
-  ErrorSlot &slot = trellis_error();
-  if (prepare_device(slot) != 0) return -1;
+namespace b200q {
+int32_t prepare_trellis_kernels(ErrorSlot &slot) {
   const cudaError_t err = set_all_linear_attrs();
   if (err != cudaSuccess) return fail(slot, "ignis_trellis_prepare: %s", cudaGetErrorString(err));
   return trellis_tc_prepare(slot);
 }
+}  // namespace b200q
+
+using namespace b200q;
+
+extern "C" {
+
+int32_t ignis_trellis_prepare(void) { return prepare_all(trellis_error()); }
 
 uint32_t ignis_trellis_sm_cap(void) {
   const DeviceState *dev = device_state(trellis_error());

@@ -89,6 +89,8 @@ typedef struct b200q_nvfp4_workspace {
 
 /* Prepares the current device: kernel attributes, SM count, environment switches. Once per
  * device at load, outside any stream capture; the ops refuse to run on an unprepared device.
+ * Prepares the whole library (the trellis and MoE kernels too: ignis_trellis_prepare and
+ * ignis_moe_prepare do the same), so one call per device is enough whichever family's it is.
  * Stands where the reference configures its ops at ignis_model_load
  * (kernel/include/ignis_model.h:820). */
 int32_t b200q_nvfp4_prepare(void);
