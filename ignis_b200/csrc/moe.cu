@@ -861,7 +861,8 @@ int32_t run_experts(const Geometry &g, const void *x, uint32_t tokens, const int
 int32_t prepare_moe_kernels(ErrorSlot &slot) {
   const cudaError_t err = cudaFuncSetAttribute(moe_router_logits_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024);
   if (err != cudaSuccess) return fail(slot, "ignis_moe_prepare: %s", cudaGetErrorString(err));
-  return moe_tc_prepare(slot);
+  if (moe_tc_prepare(slot) != 0) return -1;
+  return moe_fp8_tc_prepare(slot);
 }
 }  // namespace b200q
 
@@ -1006,7 +1007,11 @@ int32_t b200q_moe_shared_expert(const b200q_moe_geometry *geometry, const void *
   if (dev == nullptr) return -1;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   cudaError_t err;
-  if (tokens > 8u) {  // many tokens: the tensor-core form, 64 tokens a CTA
+  if (moe_fp8_tc_takes(*dev, g_geo.hidden, g_geo.inter, tokens, x, h)) {  // wide calls: tcgen05
+    err = moe_fp8_tc_shared_expert(*dev, static_cast<const uint8_t *>(gate), static_cast<const uint8_t *>(up),
+                                   static_cast<const uint8_t *>(down), static_cast<const uint16_t *>(x), tokens, g_geo.hidden, g_geo.inter, h,
+                                   shared, s);
+  } else if (tokens > 8u) {  // some tokens: warp-level MMAs, 64 tokens a CTA
     const uint32_t token_blocks = (tokens + 63u) / 64u;
     err = launch(moe_fp8_gemm_kernel<0>, dim3((g_geo.inter + 127u) / 128u, token_blocks), dim3(256), 0, s, dev->pdl != 0,
                  static_cast<const uint8_t *>(gate), static_cast<const uint8_t *>(up), g_geo.inter, g_geo.hidden,
@@ -1097,10 +1102,12 @@ int32_t ignis_moe_workspace_status(const struct ignis_moe_workspace *workspace, 
   ErrorSlot &slot = moe_error();
   if (workspace == nullptr || workspace->base == nullptr || status == nullptr) return fail(slot, "ignis_moe_workspace_status: NULL argument");
   uint32_t words[2] = {0u, 0u};   // [0] the expert kernels' bits, [1] bounded waits of the tensor-core kernels that ran out
+  uint32_t shared_expert = 0u;    // the same for the shared expert's tensor-core kernels (no workspace of their own)
   cudaError_t err = cudaMemcpyAsync(words, workspace->base, sizeof(words), cudaMemcpyDeviceToHost, static_cast<cudaStream_t>(stream));
+  if (err == cudaSuccess) err = moe_fp8_tc_status(&shared_expert, static_cast<cudaStream_t>(stream));
   if (err == cudaSuccess) err = cudaStreamSynchronize(static_cast<cudaStream_t>(stream));
   if (err != cudaSuccess) return fail(slot, "ignis_moe_workspace_status: %s", cudaGetErrorString(err));
-  *status = words[0] | (words[1] != 0u ? kStatusTcWait : 0u);
+  *status = words[0] | ((words[1] | shared_expert) != 0u ? kStatusTcWait : 0u);
   return 0;
 }
 

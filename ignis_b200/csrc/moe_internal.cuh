@@ -51,6 +51,15 @@ constexpr uint32_t kMoeTcItemRows = 256;
 int32_t moe_tc_experts(ErrorSlot &slot, const DeviceState &dev, const ExpertParams &p, uint32_t rows, uint32_t items_max,
                        const uint32_t *offsets, cudaStream_t stream, const char *what);
 
+// The shared expert of a wide call on the tensor cores (moe_fp8_tc.cu): FP8 rows widened exactly to
+// BF16 in swizzled shared memory, BF16 activations by TMA, tcgen05 kind::f16. Takes calls of more
+// than 64 tokens whose widths are multiples of 128 and whose x and h are 16-byte aligned.
+int32_t moe_fp8_tc_prepare(ErrorSlot &slot);
+bool moe_fp8_tc_takes(const DeviceState &dev, uint32_t hidden, uint32_t inter, uint32_t tokens, const void *x, const void *h);
+cudaError_t moe_fp8_tc_shared_expert(const DeviceState &dev, const uint8_t *gate, const uint8_t *up, const uint8_t *down, const uint16_t *x,
+                                     uint32_t tokens, uint32_t hidden, uint32_t inter, void *h, float *shared, cudaStream_t stream);
+cudaError_t moe_fp8_tc_status(uint32_t *status, cudaStream_t stream);   // non-zero: one of its bounded waits ran out
+
 }  // namespace b200q
 
 #endif

@@ -145,7 +145,10 @@ int32_t ignis_moe_decode_cluster_size(void);
 /* The shared expert's SwiGLU on FP8 row-scale weights (E4M3FN codes [rows][cols], zero padding to
  * 256 bytes, BF16 scales [rows]: kernel/include/ignis_fp8_linear.h:4-10): gate and up
  * [inter][hidden], down [hidden][inter], into `shared` fp32 [tokens][hidden]; `h` is BF16
- * [tokens][inter] scratch. reference: ignis_moe.h:203-204 */
+ * [tokens][inter] scratch. reference: ignis_moe.h:203-204
+ * Up to 8 tokens a warp per row; up to 64 warp-level MMAs; beyond (widths multiples of 128, x and h
+ * 16-byte aligned) the codes are widened exactly to BF16 in shared memory and multiplied by
+ * tcgen05, whose bounded waits report through bit 3 of ignis_moe_workspace_status. */
 int32_t ignis_moe_shared_expert(const void *gate, const void *up, const void *down, const void *x,
                                 uint32_t tokens, void *h, float *shared, void *stream);
 

@@ -332,7 +332,53 @@ def test_shared_expert_on_payloads_the_reference_encoder_wrote(mo, golden):
         assert np.all(np.abs(shared.double().cpu().numpy() - s_ref) <= 1e-4 * np.abs(s_ref).max() + 1e-6)
 
 
-@pytest.mark.parametrize("tokens", [5, 11, 130])   # up to 8: one warp per row; above: the tensor-core form, ragged token tiles
+def test_shared_expert_wide_at_config4_widths(mo):
+    """700 tokens at hidden 2048 / intermediate 768 (three token tiles of 256, the last ragged): the
+    tcgen05 form of the shared expert against the fp64 product of the decoded payloads, and against
+    the warp-level form of the same call."""
+    mo.set_geometry(2048, 768, 512, 10)
+    gen = torch.Generator().manual_seed(14)
+    tokens = 700
+    x = (torch.randn(tokens, 2048, generator=gen) * 0.5).to(torch.bfloat16)
+    ws = [torch.randn(768, 2048, generator=gen) * 0.02, torch.randn(768, 2048, generator=gen) * 0.02, torch.randn(2048, 768, generator=gen) * 0.03]
+    payloads = [torch.from_numpy(mo.fp8_row_scale_payload(w)).cuda() for w in ws]
+
+    def deq(payload, rows, cols):
+        p = payload.cpu()
+        pad = (rows * cols + 255) // 256 * 256
+        codes = p[: rows * cols].view(torch.float8_e4m3fn).float().reshape(rows, cols)
+        return (codes * p[pad: pad + 2 * rows].view(torch.bfloat16).float().unsqueeze(1)).double()
+
+    shared, h = mo.shared_expert(*payloads, x.cuda())
+    g = x.double() @ deq(payloads[0], 768, 2048).T
+    u = x.double() @ deq(payloads[1], 768, 2048).T
+    h_ref = g / (1 + torch.exp(-g)) * u
+    assert torch.allclose(h.cpu().double(), h_ref, rtol=2 ** -7, atol=1e-4 * float(h_ref.abs().max()))
+    s_ref = h.cpu().double() @ deq(payloads[2], 2048, 768).T
+    assert torch.allclose(shared.cpu().double(), s_ref, rtol=1e-4, atol=1e-5 * float(s_ref.abs().max()) + 1e-6)
+    block = mo.Workspace(8, tokens)
+    assert block.status() == 0          # bit 3 would name a bounded wait of the tensor-core kernels that ran out
+    import subprocess, sys, os
+    # the same call with the tensor-core forms switched off, in a process of its own (the switch is read at prepare)
+    code = ("import torch, numpy as np, sys\n"
+            "from ignis_b200 import moe\n"
+            "moe.prepare(); moe.set_geometry(2048, 768, 512, 10)\n"
+            "d = torch.load(sys.argv[1])\n"
+            "shared, h = moe.shared_expert(*[p.cuda() for p in d['payloads']], d['x'].cuda())\n"
+            "torch.save({'shared': shared.cpu(), 'h': h.cpu()}, sys.argv[2])\n")
+    import tempfile
+    with tempfile.TemporaryDirectory() as tmp:
+        torch.save({"payloads": [p.cpu() for p in payloads], "x": x}, os.path.join(tmp, "in.pt"))
+        env = dict(os.environ, B200Q_MOE_TC="0", PYTHONPATH=os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+        subprocess.run([sys.executable, "-c", code, os.path.join(tmp, "in.pt"), os.path.join(tmp, "out.pt")], check=True, env=env, timeout=300)
+        other = torch.load(os.path.join(tmp, "out.pt"))
+    # both forms accumulate exact BF16 products in FP32, in different orders: h may differ by one BF16
+    # step where a sum lands on a rounding boundary, and the down product inherits those steps
+    assert torch.allclose(h.cpu().float(), other["h"].float(), rtol=2 ** -7, atol=1e-4 * float(h_ref.abs().max()))
+    assert torch.allclose(shared.cpu(), other["shared"], rtol=2 ** -7, atol=2e-3 * float(s_ref.abs().max()))
+
+
+@pytest.mark.parametrize("tokens", [5, 11, 130, 300])   # up to 8: one warp per row; to 64: warp-level MMAs; above: tcgen05, ragged token tiles
 def test_shared_expert_and_combine(mo, tokens):
     mo.set_geometry(256, 128, 8, 2)
     gen = torch.Generator().manual_seed(4)
