@@ -296,6 +296,24 @@ def test_wide_dynamic_range_activations(nv, oracle):
         scale = np.abs(ref[t]).max()
         assert np.abs(got[t] - ref[t]).max() <= REL_TOL * scale
     assert np.all(got[7] == 0.0)
+    # the ends of BF16: one value at 2^127 in a token of zeros, a token of subnormals only, a token
+    # that holds an infinity (its outputs are not finite; the other tokens do not notice)
+    edge = torch.zeros(4, k, dtype=torch.float32)
+    edge[0, 77] = 2.0 ** 127
+    edge[1, :] = 2.0 ** -130
+    edge[2] = torch.randn(k, generator=torch.Generator().manual_seed(13))
+    edge[2, 5] = float("inf")
+    edge[3] = torch.randn(k, generator=torch.Generator().manual_seed(14))
+    edge = edge.to(torch.bfloat16)
+    got = nv.linear(edge.cuda(), w, epilogue=nv.OUT_F32).double().cpu().numpy()
+    finite = edge.clone()
+    finite[2, 5] = 0.0
+    ref = ref_product(oracle, codes, scales, n, k, d_w, finite)
+    for t in (0, 1, 3):
+        assert np.all(np.isfinite(got[t]))
+        assert np.abs(got[t] - ref[t]).max() <= REL_TOL * np.abs(ref[t]).max()
+    assert not np.any(np.isfinite(got[2]))
+    assert nv.device_status() == 0
 
 
 def test_epilogues_and_strided_outputs(nv, oracle):
