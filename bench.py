@@ -998,7 +998,8 @@ def measure_timeline(stream, device, layers: int, tokens: int, policy_name: str)
     (`python -m ignis_b200.build --trace`): the step is `layers` layers of configs[1] replayed as one
     CUDA graph; per call of a layer, medians over the steady-state layers of
       gap      predecessor's last CTA through its K reduction -> this grid's first CTA sees it complete
-      rewrite  -> activations rewritten as fragments (median CTA)
+      rewrite  -> activations rewritten as fragments (median CTA; `rewrite_split_us`: per CTA, its first pass over
+               the slice, the conversion and stores, the wait for the CTA's other warps)
       loop     -> K loop done (median CTA)
       straggle -> K loop done in the last CTA
       finish   -> last CTA through the cluster's meeting point (the epilogue's stores follow)
@@ -1033,7 +1034,7 @@ def measure_timeline(stream, device, layers: int, tokens: int, policy_name: str)
     for _ in range(3):
         step()
     stream.synchronize()
-    stamps = np.zeros((128, 512, 8), np.uint64)
+    stamps = np.zeros((128, 512, 10), np.uint64)
     lib.b200q_debug_gemv_trace.restype = C.c_int32
     lib.b200q_debug_gemv_trace.argtypes = [C.c_void_p, C.c_uint64]
     assert lib.b200q_debug_gemv_trace(stamps.ctypes.data, stamps.nbytes) == 0      # drop the warm-up's stamps
@@ -1043,7 +1044,7 @@ def measure_timeline(stream, device, layers: int, tokens: int, policy_name: str)
     for slot in range(stamps.shape[0]):
         grid = int(stamps[slot, 0, 7] >> np.uint64(32))
         if grid:
-            t = stamps[slot, :min(grid, 512), :7].astype(np.int64)
+            t = stamps[slot, :min(grid, 512), :].astype(np.int64)
             launches.append((int(t[:, 0].min()), grid, t))
     launches.sort(key=lambda e: e[0])
     if len(launches) != layers * len(GROUPS):
@@ -1055,7 +1056,8 @@ def measure_timeline(stream, device, layers: int, tokens: int, policy_name: str)
             ready, looped = np.median(t[:, 3]), np.median(t[:, 4])
             rows[idx % len(GROUPS)].append([(t[:, 2].min() - prev_end) / 1e3, (ready - t[:, 2].min()) / 1e3, (looped - ready) / 1e3,
                                             (t[:, 4].max() - looped) / 1e3, (t[:, 6].max() - t[:, 4].max()) / 1e3,
-                                            (t[:, 6].max() - prev_end) / 1e3, float(np.mean(t[:, 0] < prev_end - 1000)), grid])
+                                            (t[:, 6].max() - prev_end) / 1e3, float(np.mean(t[:, 0] < prev_end - 1000)), grid,
+                                            np.median(t[:, 8] - t[:, 2]) / 1e3, np.median(t[:, 9] - t[:, 8]) / 1e3, np.median(t[:, 3] - t[:, 9]) / 1e3])
         prev_end = t[:, 6].max()
     calls = {}
     for i, names in enumerate(GROUPS):
@@ -1063,6 +1065,7 @@ def measure_timeline(stream, device, layers: int, tokens: int, policy_name: str)
         nbytes = sum(weight_bytes(by_name[nm][0], by_name[nm][1]) for nm in names)
         calls["|".join(names)] = {"ctas": int(m[7]), "weight_mb": nbytes / 1e6, "gap_us": m[0], "rewrite_us": m[1], "loop_us": m[2],
                                   "straggle_us": m[3], "finish_us": m[4], "total_us": m[5], "ctas_resident_early": m[6],
+                                  "rewrite_split_us": {"maximum_pass": m[8], "convert_and_store": m[9], "cta_barrier": m[10]},
                                   "loop_gbs": nbytes / (m[2] * 1e-6) / 1e9, "call_gbs": nbytes / (m[5] * 1e-6) / 1e9}
     layer_us = sum(c["total_us"] for c in calls.values())
     return {"metric": "nvfp4_decode_layer_timeline_us", "value": layer_us, "unit": "us", "steps": 1, "warmup": 3, "ms_per_step": ms,

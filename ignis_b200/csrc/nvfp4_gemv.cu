@@ -36,10 +36,11 @@ constexpr int kWarps = 8;
 // shipped one) stamps the global timer at the phase boundaries of every CTA, for the timeline of a
 // chain of calls: [0] entry, [1] first weight loads issued, [2] predecessor complete, [3]
 // activations rewritten, [4] K loop done, [5] partial sums written, [6] cluster met, [7] SM and
-// grid size. The host numbers the launches (modulo 128) in bits 16..22 of the epilogue word, which
+// grid size, [8] the first chunk's maximum known (first pass over the activations done), [9] its
+// fragments stored (before the CTA's barrier). The host numbers the launches (modulo 128) in bits 16..22 of the epilogue word, which
 // the kernel otherwise reads through single-bit masks.
 #ifdef B200Q_GEMV_TRACE
-constexpr int kTraceLaunches = 128, kTraceCtas = 512, kTraceWords = 8;
+constexpr int kTraceLaunches = 128, kTraceCtas = 512, kTraceWords = 10;
 __device__ unsigned long long g_trace[kTraceLaunches][kTraceCtas][kTraceWords];
 __device__ __forceinline__ void trace_stamp(int launch, int word) {
   if (launch < 0 || blockIdx.x >= kTraceCtas) return;
@@ -57,8 +58,8 @@ __device__ __forceinline__ void trace_stamp(int launch, int word) {
   trace_stamp(trace_launch, 0)
 #define GEMV_TRACE(word) trace_stamp(trace_launch, word)
 #else
-#define GEMV_TRACE_BEGIN(word) ((void)0)
-#define GEMV_TRACE(word) ((void)0)
+#define GEMV_TRACE_BEGIN(word) constexpr int trace_launch = -1
+#define GEMV_TRACE(word) ((void)trace_launch)
 #endif
 
 struct Stage {
@@ -111,7 +112,7 @@ __device__ __forceinline__ void e2m1x8_to_half2x4_alu(uint32_t w, uint32_t (&h)[
 }
 
 // One K step of a warp: 4 rows x 64 weights per lane against the prepared activations of the
-// step (`xs_step`: [8 words][NT tiles][32 slots] uint4, slot = lane ^ (word << 2)).
+// step (`xs_step`: [8 words][NT tiles][32 slots] uint4, slot = lane ^ (word << 2) ^ ((word >> 1) & 3)).
 //
 // The hardware E2M1 conversion runs on the quarter-rate special-function pipe, which alone would
 // cap the kernel below the HBM rate, so only the first XU of a row's 8 words take it; the others
@@ -155,7 +156,7 @@ __device__ __forceinline__ void compute_stage(const Stage &st, const uint4 *xs_s
     }
 #pragma unroll
     for (int tt = 0; tt < NT; ++tt) {
-      const uint4 v = xs_step[(i * NT + tt) * 32 + (lane ^ (i << 2))];
+      const uint4 v = xs_step[(i * NT + tt) * 32 + ((lane ^ (i << 2)) ^ ((i >> 1) & 3))];
       mma_f16_f32(acc[0][tt], h[0][0], h[1][0], h[0][1], h[1][1], v.x, v.y);
       mma_f16_f32(acc[1][tt], h[2][0], h[3][0], h[2][1], h[3][1], v.x, v.y);
       mma_f16_f32(acc[0][tt], h[0][2], h[1][2], h[0][3], h[1][3], v.z, v.w);
@@ -243,14 +244,18 @@ constexpr int kPrepRegs = 5;  // chunks a lane keeps in registers between the am
 // inv_s, its scale to scale_s.
 template <int NT, int XU>
 __device__ __forceinline__ void prepare_activations(const GemvParams &p, int cb, int ce, uint4 *xs, float *inv_s,
-                                                    float *scale_s, int warp, int lane) {
+                                                    float *scale_s, int warp, int lane, int trace_launch) {
   const int nsteps = ce - cb;
   // Lane l takes chunk l of a step: t = l / 8 is the lane quarter that will read it, i = l % 8 the
   // word it multiplies. (Dealing the chunks so that the fragment stores avoid their four-way bank
   // conflict scatters each quarter-warp's global load over four lines, and measured slower.)
   const int t = lane >> 3, i = lane & 7;
   const int chunk = lane;
-  const int slot = ((warp ^ i) << 2) | t;  // fragment slot of lane (g = warp, t), swizzled by the word
+  // Fragment slot of lane (g = warp, t), swizzled by the word i in both fields: the token by i (a
+  // warp's 32 reads of one word fall in 32 different slots) and the lane quarter by bits 1..2 of i
+  // (the eight lanes of one phase of this 16-byte store - one t, eight words - fall in the eight
+  // different bank groups instead of two).
+  const int slot = ((warp ^ i) << 2) | (t ^ ((i >> 1) & 3));
 #pragma unroll
   for (int tt = 0; tt < NT; ++tt) {
     const uint32_t tok = static_cast<uint32_t>(tt * 8 + warp);
@@ -288,6 +293,7 @@ __device__ __forceinline__ void prepare_activations(const GemvParams &p, int cb,
     }
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) amax = __vmaxu2(amax, __shfl_xor_sync(0xFFFFFFFFu, amax, o));
+    if (tt == 0) GEMV_TRACE(8);
     const int shift = amax_shift(max(amax & 0xFFFFu, amax >> 16));
     const float scale = pow2f(shift);
     if (lane == 0) {
@@ -423,7 +429,8 @@ __global__ void __launch_bounds__(kThreads, NT <= 2 ? 2 : 1) nvfp4_gemv_kernel(c
       }
       __syncthreads();  // the previous chunk's fragments and scales are no longer read
     }
-    prepare_activations<NT, XU>(p, cb, ce, xs, inv_s, scale_s, warp, lane);
+    prepare_activations<NT, XU>(p, cb, ce, xs, inv_s, scale_s, warp, lane, cb == c0 ? trace_launch : -1);
+    if (cb == c0) GEMV_TRACE(9);
     __syncthreads();
     if (cb == c0) GEMV_TRACE(3);
     if (cb != c0) {
