@@ -678,8 +678,10 @@ GemvPlan gemv_plan(const DeviceState &dev, uint32_t groups, uint32_t ksteps, int
         const double slice = ceil(static_cast<double>(ksteps) / kc);
         const double steps = ceil(slice / kwc);
         // fitted on B200 (microseconds per launch): a warp's step costs about 1.6, a step of the
-        // CTA's activation slice 0.3 per token tile, a wave of CTAs 3, the launch itself 2.4
-        const double cost = waves * (1.57 * steps + 0.3 * nt * slice + 3.0) + 2.4 + 0.01 * kc;
+        // CTA's activation slice 0.3 per token tile, a wave of CTAs 3, the launch itself 2.4, and every
+        // CTA of a cluster 0.35: clusters are placed inside one GPC, so the wider they are the more
+        // SMs stay empty and the later the last CTA starts (phase stamps of the four configs[1] calls)
+        const double cost = waves * (1.57 * steps + 0.3 * nt * slice + 3.0) + 2.4 + 0.35 * kc;
         if (cost < best_cost) {
           best_cost = cost;
           best.rm = rm;
