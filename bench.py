@@ -961,7 +961,7 @@ def run_cuda_arm(args) -> None:
                      "peak_source": f"{peaks['kind']} copy bandwidth", "frac_of_nominal_8000": per_gpu / 8000.0,
                      "kernel": "nvfp4_gemv_kernel<1>", "bytes_per_launch": per_rank_bytes / (len(calls) * args.layers),
                      "us_per_launch": ms_per_step * 1e3 / (len(calls) * args.layers),
-                     "traffic": 196.97e6 / 4 if profiled else None,
+                     "traffic": 196.08e6 / 4 if profiled else None,   # profiles/nvfp4_gemv_decode_m8.md: read + write of the four launches
                      "traffic_source": "ncu dram__bytes_read.sum + dram__bytes_write.sum, mean of one layer's four launches" if profiled else None},
     }
     if "allow_a4_ms" in extras:
