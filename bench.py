@@ -788,7 +788,7 @@ def run_cuda_arm(args) -> None:
     device = torch.device("cuda", local_rank)
     if world > 1:
         os.environ.setdefault("NCCL_NVLS_ENABLE", "0")   # plain peer stores beside NCCL: no multicast objects on the buffers
-        os.environ["NCCL_DEBUG"] = os.environ.get("B200Q_NCCL_DEBUG", "WARN")   # NCCL's version banner goes to stdout, where one JSON line belongs
+        os.environ.setdefault("NCCL_DEBUG_FILE", "/dev/stderr")   # NCCL's version banner and warnings: not on stdout, where one JSON line belongs
         dist.init_process_group("nccl", device_id=device)
     nvfp4.prepare()
     peaks = measured_peaks()
@@ -1099,7 +1099,7 @@ def run_side_workload(args) -> None:
     torch.cuda.set_device(device)
     if world > 1:
         os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
-        os.environ["NCCL_DEBUG"] = os.environ.get("B200Q_NCCL_DEBUG", "WARN")   # NCCL's version banner goes to stdout, where one JSON line belongs
+        os.environ.setdefault("NCCL_DEBUG_FILE", "/dev/stderr")   # NCCL's version banner and warnings: not on stdout, where one JSON line belongs
         dist.init_process_group("nccl", device_id=device)
     nvfp4.prepare()
     trellis.prepare()
