@@ -51,6 +51,26 @@ UNIT = "GB/s"
 DTYPE = "e2m1 (ue4m3 block scale) x bf16 -> f32"
 
 
+_RESULT_STREAM = None
+
+
+def claim_stdout() -> None:
+    """Under torchrun, libraries write to file descriptor 1 on their own (NCCL prints its version
+    there): keep a private copy of stdout for the result line and point descriptor 1 at stderr."""
+    global _RESULT_STREAM
+    if _RESULT_STREAM is None and int(os.environ.get("WORLD_SIZE", "1")) > 1:
+        sys.stdout.flush()
+        _RESULT_STREAM = os.fdopen(os.dup(1), "w")
+        os.dup2(2, 1)
+
+
+def emit(line: dict) -> None:
+    """The run's one JSON line, on the process's original stdout."""
+    out = _RESULT_STREAM or sys.stdout
+    out.write(json.dumps(line) + "\n")
+    out.flush()
+
+
 def weight_bytes(n: int, k: int) -> int:
     return n * k // 2 + n * k // 16 + 4
 
@@ -197,7 +217,7 @@ def run_reference_arm(args) -> None:
             "config": {"workload": "configs[1]: NVFP4 decode, 8 lanes, 27B-style dense layer (CPU: a bounded row sample per step)"},
             "cpu_baseline": {"value": value, "unit": UNIT, **desc},
             "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
-    print(json.dumps(line))
+    emit(line)
 
 
 # ---- synthetic weights ----------------------------------------------------------------------------
@@ -788,7 +808,6 @@ def run_cuda_arm(args) -> None:
     device = torch.device("cuda", local_rank)
     if world > 1:
         os.environ.setdefault("NCCL_NVLS_ENABLE", "0")   # plain peer stores beside NCCL: no multicast objects on the buffers
-        os.environ.setdefault("NCCL_DEBUG_FILE", "/dev/stderr")   # NCCL's version banner and warnings: not on stdout, where one JSON line belongs
         dist.init_process_group("nccl", device_id=device)
     nvfp4.prepare()
     peaks = measured_peaks()
@@ -991,7 +1010,7 @@ def run_cuda_arm(args) -> None:
     if world == 1 and not args.no_cpu_baseline:
         v, desc = cpu_sample()
         line["cpu_baseline"] = {"value": v, "unit": UNIT, **desc}
-    print(json.dumps(line))
+    emit(line)
 
 
 def measure_timeline(stream, device, layers: int, tokens: int, policy_name: str) -> dict:
@@ -1099,7 +1118,6 @@ def run_side_workload(args) -> None:
     torch.cuda.set_device(device)
     if world > 1:
         os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
-        os.environ.setdefault("NCCL_DEBUG_FILE", "/dev/stderr")   # NCCL's version banner and warnings: not on stdout, where one JSON line belongs
         dist.init_process_group("nccl", device_id=device)
     nvfp4.prepare()
     trellis.prepare()
@@ -1147,7 +1165,7 @@ def run_side_workload(args) -> None:
             line = {**base, **measure_trellis(stream, device, args.steps, args.warmup, peaks, layers=args.layers, tokens=args.tokens,
                                               group=bool(args.group), graph=graph)}
     if rank == 0:
-        print(json.dumps(line))
+        emit(line)
 
 
 def main() -> None:
@@ -1181,6 +1199,7 @@ def main() -> None:
                          "configs[0] / [2] / [3] / [4] alone; head: the output head; peak: the FP4 tensor-core loop; timeline: where a decode "
                          "launch's time goes (needs python -m ignis_b200.build --trace)")
     args = ap.parse_args()
+    claim_stdout()
     if args.impl == "reference":
         run_reference_arm(args)
     elif args.workload != "decode":
