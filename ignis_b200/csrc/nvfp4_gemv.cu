@@ -236,15 +236,17 @@ __device__ __forceinline__ int amax_shift(uint32_t amax_bits) {
 }
 __device__ __forceinline__ float pow2f(int e) { return __uint_as_float(static_cast<uint32_t>(e + 127) << 23); }  // e in [-126, 127]
 
+constexpr int kNoShiftYet = 1 << 20;  // a token whose chunks so far held nothing to scale
 constexpr int kPrepRegs = 5;  // chunks a lane keeps in registers between the amax and the store
 
 // Rewrites steps [cb, ce) of the activations as scaled fp16 B fragments. Warp w prepares token
 // slots w, w + 8, ...; a lane owns one 16-byte chunk of every step (t: the lane quarter that will
 // read it, i: the word it multiplies). The slot's inverse scale goes to
 // inv_s, its scale to scale_s.
-template <int NT, int XU>
+template <int NT, int XU, bool CHUNKED>
 __device__ __forceinline__ void prepare_activations(const GemvParams &p, int cb, int ce, uint4 *xs, float *inv_s,
-                                                    float *scale_s, int warp, int lane, int trace_launch) {
+                                                    float *scale_s, int *low_s, bool first, int warp, int lane,
+                                                    int trace_launch) {
   const int nsteps = ce - cb;
   // Lane l takes chunk l of a step: t = l / 8 is the lane quarter that will read it, i = l % 8 the
   // word it multiplies. (Dealing the chunks so that the fragment stores avoid their four-way bank
@@ -267,6 +269,7 @@ __device__ __forceinline__ void prepare_activations(const GemvParams &p, int cb,
     const int valid = live ? min(nsteps, max(inside, 0)) : 0;
     uint4 *dst = xs + tt * 32 + slot + static_cast<size_t>(i) * NT * 32;
     uint32_t amax = 0u;  // one running maximum per 16-bit half
+    int prov = 0;        // the provisional shift of a long slice
     uint4 held[kPrepRegs];
     const bool hold = nsteps <= kPrepRegs;
     if (hold) {
@@ -278,23 +281,58 @@ __device__ __forceinline__ void prepare_activations(const GemvParams &p, int cb,
 #pragma unroll
       for (int m = 0; m < kPrepRegs; ++m) amax = chunk_amax_bits(held[m], amax);
     } else {
-      // a longer slice does not fit in registers beside the two weight stages: two passes over it,
-      // four loads in flight at a time
-      for (int m0 = 0; m0 < valid; m0 += 4) {
+      // A longer slice does not fit in registers beside the two weight stages. It is converted in
+      // one pass at a provisional scale taken from its first four steps (their maximum brought into
+      // [2^9, 2^10), which leaves the rest of the slice room to be 32 times larger), the slice's own
+      // maximum being gathered on the way; only a slice whose maximum ends outside what fp16
+      // carries well at that scale is converted again below.
+      float pscale = 1.0f;
+      for (int m0 = 0; m0 < nsteps; m0 += 4) {
         uint4 v[4];
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
           v[j] = make_uint4(0u, 0u, 0u, 0u);
           if (m0 + j < valid) v[j] = ldg128_coherent(src + (m0 + j) * 32);
         }
+        uint32_t bm = 0u;
 #pragma unroll
-        for (int j = 0; j < 4; ++j) amax = chunk_amax_bits(v[j], amax);
+        for (int j = 0; j < 4; ++j) bm = chunk_amax_bits(v[j], bm);
+        amax = __vmaxu2(amax, bm);
+        if (m0 == 0) {
+#pragma unroll
+          for (int o = 16; o > 0; o >>= 1) bm = __vmaxu2(bm, __shfl_xor_sync(0xFFFFFFFFu, bm, o));
+          prov = max(-126, amax_shift(max(bm & 0xFFFFu, bm >> 16)) - 4);
+          pscale = pow2f(prov);
+        }
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          if (m0 + j < nsteps) dst[static_cast<size_t>(m0 + j) * 8 * NT * 32] = convert_chunk<XU>(v[j], pscale, i);
+        }
       }
     }
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) amax = __vmaxu2(amax, __shfl_xor_sync(0xFFFFFFFFu, amax, o));
     if (tt == 0) GEMV_TRACE(8);
-    const int shift = amax_shift(max(amax & 0xFFFFu, amax >> 16));
+    const uint32_t top = max(amax & 0xFFFFu, amax >> 16);
+    // The accumulators are carried from one chunk of a slice into the next chunk's units. A chunk
+    // far smaller than an earlier one of its token must not pull them up by its whole ratio (the
+    // sums gathered so far would leave the range of a float): its shift stays within 64 of the
+    // lowest shift the token has had, and what it then loses lies 2^-50 below the earlier sums.
+    int cap = 126, low = kNoShiftYet;
+    if (CHUNKED && !first) {
+      low = low_s[tt * 8 + warp];
+      if (low != kNoShiftYet) cap = min(126, low + 64);
+      __syncwarp();  // every lane has read the token's lowest shift before lane 0 replaces it
+    }
+    int shift = min(amax_shift(top), cap);
+    bool again = false;
+    if (!hold) {
+      // the maximum lies in [2^e, 2^(e + 1)) at the provisional scale
+      const int e = static_cast<int>(top >> 7) - 127 + prov;
+      if (prov <= cap && (top == 0u || (top < 0x7F80u && e >= 5 && e <= 14))) shift = prov;
+      else again = true;
+    }
+    if (CHUNKED && lane == 0) low_s[tt * 8 + warp] = (top == 0u || top >= 0x7F80u) ? low : min(low, shift);
     const float scale = pow2f(shift);
     if (lane == 0) {
       inv_s[tt * 8 + warp] = live ? pow2f(-shift) : 0.0f;
@@ -305,7 +343,7 @@ __device__ __forceinline__ void prepare_activations(const GemvParams &p, int cb,
       for (int m = 0; m < kPrepRegs; ++m) {
         if (m < nsteps) dst[static_cast<size_t>(m) * 8 * NT * 32] = convert_chunk<XU>(held[m], scale, i);
       }
-    } else {
+    } else if (again) {
       for (int m0 = 0; m0 < nsteps; m0 += 4) {
         uint4 v[4];
 #pragma unroll
@@ -322,7 +360,7 @@ __device__ __forceinline__ void prepare_activations(const GemvParams &p, int cb,
   }
 }
 
-template <int NT, int XU>
+template <int NT, int XU, bool CHUNKED>
 __global__ void __launch_bounds__(kThreads, NT <= 2 ? 2 : 1) nvfp4_gemv_kernel(const __grid_constant__ GemvParams p) {
   extern __shared__ __align__(16) uint8_t smem_raw[];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -339,6 +377,7 @@ __global__ void __launch_bounds__(kThreads, NT <= 2 ? 2 : 1) nvfp4_gemv_kernel(c
   float4 *part = red + static_cast<size_t>(kw_count - 1) * rm * 2 * NT * 32;
   float *inv_s = reinterpret_cast<float *>(part + static_cast<size_t>(rm) * 2 * NT * 32);
   float *scale_s = inv_s + 8 * NT;
+  int *low_s = reinterpret_cast<int *>(scale_s + 8 * NT);
 
   // which weight of the group this CTA serves
   uint32_t wi = 0;
@@ -421,7 +460,7 @@ __global__ void __launch_bounds__(kThreads, NT <= 2 ? 2 : 1) nvfp4_gemv_kernel(c
   for (int cb = c0; cb < c1; cb += ch) {
     const int ce = min(cb + ch, c1);
     float carry[NT][2];
-    if (cb != c0) {
+    if (CHUNKED && cb != c0) {
 #pragma unroll
       for (int tt = 0; tt < NT; ++tt) {
         carry[tt][0] = inv_s[tt * 8 + 2 * t];
@@ -429,11 +468,11 @@ __global__ void __launch_bounds__(kThreads, NT <= 2 ? 2 : 1) nvfp4_gemv_kernel(c
       }
       __syncthreads();  // the previous chunk's fragments and scales are no longer read
     }
-    prepare_activations<NT, XU>(p, cb, ce, xs, inv_s, scale_s, warp, lane, cb == c0 ? trace_launch : -1);
+    prepare_activations<NT, XU, CHUNKED>(p, cb, ce, xs, inv_s, scale_s, low_s, cb == c0, warp, lane, cb == c0 ? trace_launch : -1);
     if (cb == c0) GEMV_TRACE(9);
     __syncthreads();
     if (cb == c0) GEMV_TRACE(3);
-    if (cb != c0) {
+    if (CHUNKED && cb != c0) {
 #pragma unroll
       for (int tt = 0; tt < NT; ++tt) {
         const float f0 = carry[tt][0] * scale_s[tt * 8 + 2 * t], f1 = carry[tt][1] * scale_s[tt * 8 + 2 * t + 1];
@@ -559,10 +598,10 @@ constexpr size_t kGemvMaxSmem = 160 * 1024;
 size_t gemv_smem_bytes(int nt, int rm, int xs_steps) {
   const int kw_count = kWarps / rm;
   return static_cast<size_t>(xs_steps) * 4096u * nt + static_cast<size_t>(kw_count - 1) * rm * 2 * nt * 32 * 16 +
-         static_cast<size_t>(rm) * 2 * nt * 32 * 16 + static_cast<size_t>(16 * nt) * 4;
+         static_cast<size_t>(rm) * 2 * nt * 32 * 16 + static_cast<size_t>(24 * nt) * 4;
 }
 
-template <int NT, int XU>
+template <int NT, int XU, bool CHUNKED>
 cudaError_t launch_gemv(const GemvParams &p, uint32_t ctas, size_t smem, cudaStream_t stream, bool pdl) {
   cudaLaunchConfig_t config = {};
   config.gridDim = dim3(ctas, 1, 1);
@@ -578,13 +617,17 @@ cudaError_t launch_gemv(const GemvParams &p, uint32_t ctas, size_t smem, cudaStr
   attr[1].val.programmaticStreamSerializationAllowed = 1;
   config.attrs = attr;
   config.numAttrs = pdl ? 2 : 1;
-  return cudaLaunchKernelEx(&config, nvfp4_gemv_kernel<NT, XU>, p);
+  return cudaLaunchKernelEx(&config, nvfp4_gemv_kernel<NT, XU, CHUNKED>, p);
 }
 
 template <int NT, int XU>
 cudaError_t set_smem_attr() {
-  return cudaFuncSetAttribute(nvfp4_gemv_kernel<NT, XU>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                              static_cast<int>(kGemvMaxSmem));
+  cudaError_t err = cudaFuncSetAttribute(nvfp4_gemv_kernel<NT, XU, false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         static_cast<int>(kGemvMaxSmem));
+  if (err == cudaSuccess)
+    err = cudaFuncSetAttribute(nvfp4_gemv_kernel<NT, XU, true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                               static_cast<int>(kGemvMaxSmem));
+  return err;
 }
 
 template <int XU>
@@ -595,11 +638,17 @@ cudaError_t set_smem_attrs() {
   return err;
 }
 
-template <int XU>
+template <int XU, bool CHUNKED>
 cudaError_t launch_for_nt(int nt, const GemvParams &p, uint32_t ctas, size_t smem, cudaStream_t stream, bool pdl) {
-  if (nt == 1) return launch_gemv<1, XU>(p, ctas, smem, stream, pdl);
-  if (nt == 2) return launch_gemv<2, XU>(p, ctas, smem, stream, pdl);
-  return launch_gemv<4, XU>(p, ctas, smem, stream, pdl);
+  if (nt == 1) return launch_gemv<1, XU, CHUNKED>(p, ctas, smem, stream, pdl);
+  if (nt == 2) return launch_gemv<2, XU, CHUNKED>(p, ctas, smem, stream, pdl);
+  return launch_gemv<4, XU, CHUNKED>(p, ctas, smem, stream, pdl);
+}
+
+// `chunked`: some CTA's K slice is longer than the fragments the shared memory holds at a time.
+template <int XU>
+cudaError_t launch_for_slice(bool chunked, int nt, const GemvParams &p, uint32_t ctas, size_t smem, cudaStream_t stream, bool pdl) {
+  return chunked ? launch_for_nt<XU, true>(nt, p, ctas, smem, stream, pdl) : launch_for_nt<XU, false>(nt, p, ctas, smem, stream, pdl);
 }
 
 }  // namespace
@@ -643,7 +692,7 @@ int32_t gemv_prepare(ErrorSlot &slot) {
     config.attrs = attr;
     config.numAttrs = 1;
     int clusters = 0;
-    if (cudaOccupancyMaxActiveClusters(&clusters, nvfp4_gemv_kernel<1, 8>, &config) == cudaSuccess && clusters > 0) {
+    if (cudaOccupancyMaxActiveClusters(&clusters, nvfp4_gemv_kernel<1, 8, false>, &config) == cudaSuccess && clusters > 0) {
       dev->gemv_slots[kc] = clusters * kc;
     } else {
       dev->gemv_slots[kc] = 0;
@@ -707,15 +756,16 @@ int32_t gemv_launch(ErrorSlot &slot, const DeviceState &dev, GemvParams &p, int 
   p.epilogue = (p.epilogue & 0xFFFFu) | ((trace_counter++ & 127u) << 16);
 #endif
   const size_t smem = gemv_smem_bytes(nt, plan.rm, plan.xs_steps);
+  const bool chunked = (p.ksteps + plan.kc - 1u) / plan.kc > plan.xs_steps;
   if (smem > kGemvMaxSmem) return fail(slot, "nvfp4 decode: %zu bytes of shared memory exceed the kernel's limit", smem);
   cudaError_t err;
   const bool pdl = dev.pdl != 0;
   switch (dev.gemv_xu) {  // words per row of 8 that take the hardware E2M1 conversion
-    case 0: err = launch_for_nt<0>(nt, p, ctas, smem, stream, pdl); break;
-    case 2: err = launch_for_nt<2>(nt, p, ctas, smem, stream, pdl); break;
-    case 4: err = launch_for_nt<4>(nt, p, ctas, smem, stream, pdl); break;
-    case 8: err = launch_for_nt<8>(nt, p, ctas, smem, stream, pdl); break;
-    default: err = launch_for_nt<3>(nt, p, ctas, smem, stream, pdl); break;
+    case 0: err = launch_for_slice<0>(chunked, nt, p, ctas, smem, stream, pdl); break;
+    case 2: err = launch_for_slice<2>(chunked, nt, p, ctas, smem, stream, pdl); break;
+    case 4: err = launch_for_slice<4>(chunked, nt, p, ctas, smem, stream, pdl); break;
+    case 8: err = launch_for_slice<8>(chunked, nt, p, ctas, smem, stream, pdl); break;
+    default: err = launch_for_slice<3>(chunked, nt, p, ctas, smem, stream, pdl); break;
   }
   if (err != cudaSuccess) return fail(slot, "nvfp4 decode launch: %s", cudaGetErrorString(err));
   return 0;

@@ -264,6 +264,39 @@ def test_config1_products_full_size_under_a16(nv, oracle, name, n, k):
             check_bf16(part[:, :128], ref)
 
 
+@pytest.mark.parametrize("world", [4, 8])
+def test_config1_row_shards_of_four_and_eight_ranks(nv, oracle, world):
+    """The launches one rank of `world` makes for configs[1] at 8 tokens - the q | k | v shards as one
+    group, o, the gate | up shards as one group, down - at the first and
+    the last rank's rows: every output column against the fp64 product of the exactly decoded
+    rows it stands for."""
+    tokens = 8
+    rng = np.random.default_rng(80 + world)
+    shapes = {"q": (6144, 5120), "k": (1024, 5120), "v": (1024, 5120), "o": (5120, 6144),
+              "gate": (17408, 5120), "up": (17408, 5120), "down": (5120, 17408)}
+    planes = {name: make_weight(rng, n, k) for name, (n, k) in shapes.items()}
+    weights = {name: nv.Weight.from_planes(*planes[name]) for name in shapes}
+    xs = {k: torch.randn(tokens, k, generator=torch.Generator().manual_seed(k)).to(torch.bfloat16) for k in (5120, 6144, 17408)}
+
+    def want(name, rank, r0, r1):
+        n, k = shapes[name]
+        codes, scales, d_w = planes[name]
+        base = rank * (n // world)
+        return oracle.gemm_f64(oracle.nvfp4_dequant(codes, scales, n, k, d_w, base + r0, base + r1), xs[k].float().numpy())
+
+    for rank in (0, world - 1):
+        mine = {name: w.shard(rank, world) for name, w in weights.items()}
+        for group in (["q", "k", "v"], ["o"], ["gate", "up"], ["down"]):
+            x = xs[shapes[group[0]][1]].cuda()
+            outs = nv.linear_group(x, [mine[g] for g in group])
+            for name, y in zip(group, outs):
+                per = shapes[name][0] // world
+                assert y.shape == (tokens, per)
+                for r0 in sorted({0, per - 128}):
+                    check_bf16(y[:, r0:r0 + 128], want(name, rank, r0, r0 + 128))
+    assert nv.device_status() == 0
+
+
 def test_reference_patterned_weight_and_criterion(nv, oracle):
     """The reference's own A16 arm: patterned weight, divisors 0.125 / 3.5, relative L2 and gross
     bounds {2^-8, 2^-8, 2 * 2^-8} (linear_test_common.cpp:29-48, :234-240)."""
@@ -410,6 +443,41 @@ def test_long_k_takes_several_fragment_chunks(nv, oracle):
         os.environ.pop("B200Q_GEMV_RM", None)
         os.environ.pop("B200Q_GEMV_KC", None)
         nv.prepare()
+
+
+def test_long_slices_keep_or_redo_their_provisional_scale(nv, oracle):
+    """A slice longer than a lane keeps in registers is converted in one pass at a scale taken from
+    its first four steps, and converted again when its own maximum does not sit well at that scale.
+    One CTA per row block over K = 5120 (20 steps): tokens whose later steps are far larger than the
+    first four (convert again), far smaller, all zero at first, tiny throughout, holding one huge
+    value late, and plain ones (kept)."""
+    n, k = 256, 5120
+    rng = np.random.default_rng(23)
+    codes, scales, d_w = make_weight(rng, n, k)
+    w = nv.Weight.from_planes(codes, scales, d_w)
+    x = torch.randn(8, k, generator=torch.Generator().manual_seed(23))
+    x[1, 1024:] *= 1e6          # grows past the room the provisional scale leaves
+    x[2, 1024:] *= 1e-7         # the first steps dominate
+    x[3, :1024] = 0.0           # nothing to take a scale from in the first four steps
+    x[4] *= 1e-25               # small everywhere
+    x[5, 4000] = 1e36           # one huge value late in the slice
+    x[6, :1024] *= 1e-12        # first steps far below the rest
+    x[7] *= 40.0
+    x = x.to(torch.bfloat16)
+    ref = ref_product(oracle, codes, scales, n, k, d_w, x)
+    try:
+        for rm, kc in ((8, 1), (2, 1), (4, 2)):
+            os.environ["B200Q_GEMV_RM"], os.environ["B200Q_GEMV_KC"] = str(rm), str(kc)
+            nv.prepare()
+            got = nv.linear(x.cuda(), w, epilogue=nv.OUT_F32).double().cpu().numpy()
+            for t in range(8):
+                assert np.all(np.isfinite(got[t]))
+                assert np.abs(got[t] - ref[t]).max() <= REL_TOL * np.abs(ref[t]).max(), (rm, kc, t)
+    finally:
+        os.environ.pop("B200Q_GEMV_RM", None)
+        os.environ.pop("B200Q_GEMV_KC", None)
+        nv.prepare()
+    assert nv.device_status() == 0
 
 
 def test_dependent_chain_with_and_without_overlapped_launch(nv, oracle):
