@@ -48,7 +48,7 @@ int32_t check_geometry(ErrorSlot &slot, const Geometry *g, const char *what) {
 
 // Workspace regions for `tokens_max` tokens.
 struct Layout {
-  uint64_t status, counts, cursor, offsets, n_items, sorted, items, tiles, frag_in, scale_in, gu, frag_h, scale_h, total;
+  uint64_t status, counts, cursor, offsets, n_items, sorted, items, tiles, frag_in, scale_in, gu, frag_h, scale_h, down_rows, total;
   uint32_t rows_max, items_max, tiles_max;
 };
 
@@ -78,6 +78,7 @@ Layout layout_for(const Geometry &g, uint32_t tokens_max) {
   l.gu = at; at = align256(at + 8ull * l.rows_max * g.inter);           // fp32 [rows][2 inter]
   l.frag_h = at; at = align256(at + 2048ull * l.tiles_max * nblk_i);    // rotated silu(g) u
   l.scale_h = at; at = align256(at + 64ull * l.tiles_max * nblk_i);
+  l.down_rows = at; at = align256(at + (tokens_max > 8u ? 4ull * l.rows_max * g.hidden : 0ull));   // wide calls only (the tensor-core route)
   l.total = at;
   return l;
 }
@@ -824,6 +825,7 @@ int32_t run_experts(const Geometry &g, const void *x, uint32_t tokens, const int
   p.gu = reinterpret_cast<float *>(base + l.gu);
   p.frag_h = reinterpret_cast<uint2 *>(base + l.frag_h);
   p.scale_h = reinterpret_cast<float2 *>(base + l.scale_h);
+  p.down_rows = reinterpret_cast<float *>(base + l.down_rows);
   p.acc = reinterpret_cast<long long *>(acc);
   p.status = status;
   p.hidden = g.hidden;

@@ -36,6 +36,7 @@ struct ExpertParams {
   float *gu;                // fp32 [rows][2 inter]: gate | up products
   uint2 *frag_h;            // rotated silu(g) u: [tile][inter / 128][step 8][lane 32]
   float2 *scale_h;
+  float *down_rows;         // fp32 [tokens][top_k][hidden]: the weighted down products of the tensor-core route, before they are added
   long long *acc;           // int64 [tokens][hidden]
   uint32_t *status;
   uint32_t hidden, inter, top_k, experts;

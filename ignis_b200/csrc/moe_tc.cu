@@ -6,13 +6,15 @@
 // multiplied with its expert's record by the kernel core of trellis_tc.cuh: the rows rotated once
 // into plain fp16 rows with one scale per row, the record's trellis tiles decoded into swizzled
 // shared memory, tcgen05.mma kind::f16 with the accumulator in tensor memory, and the output
-// Hadamard in registers. Four launches behind the grouping:
+// Hadamard in registers. Five launches behind the grouping:
 //
 //   moe_tc_rotate_kernel<0>   x o suh (the row's expert's gate|up record), Hadamard, fp16 rows
 //   moe_tc_gemm_kernel<0>     rows x gate|up record -> gu fp32 [row][2 inter] (gate columns, then up)
 //   moe_tc_rotate_kernel<1>   silu(g) u o suh (the down record), Hadamard, fp16 rows
-//   moe_tc_gemm_kernel<1>     rows x down record, times the routing weight, added to the int64
-//                             fixed-point accumulator of the row's token (atomic, order-free)
+//   moe_tc_gemm_kernel<1>     rows x down record, times the routing weight -> fp32 [token][rank][hidden]
+//   moe_tc_fold_kernel        a token's products as 2^-32 fixed-point integers, summed, added to the
+//                             token's int64 accumulator row (84 M atomic additions into the
+//                             accumulator from the product's epilogue took two thirds of that launch)
 //
 // A row's arithmetic does not depend on the item it is in or on the rows beside it, so results are
 // reproducible bit for bit whatever the grouping order.
@@ -136,53 +138,114 @@ __global__ void __launch_bounds__(kThreads, 1) moe_tc_gemm_kernel(const __grid_c
   const uint64_t trellis_bytes = static_cast<uint64_t>(in) * out_plane * slot.k2 / 16u;
   const uint16_t *svh = reinterpret_cast<const uint16_t *>(static_cast<const uint8_t *>(slot.record) + trellis_bytes) + in;
   const float *inv_rows = reinterpret_cast<const float *>(PHASE == 0 ? p.scale_in : p.scale_h);
-  const bool have = core_run(c, job, &map_a, p.status + 1);   // word 1 of the status line: waits of this kernel that ran out
-  if (have) {
+  const bool decoded = core_roles(c, job, &map_a, p.status + 1);   // word 1 of the status line: waits of this kernel that ran out
+  if (c.warp < kDecoderWarps) {
+    // One row tile: (block, half of its columns) per warp group, all four groups at work. Two row
+    // tiles: (row tile, block) per group. What the epilogue needs from global memory is asked for
+    // here, before the wait for the accumulator: the loads travel while the last MMAs retire.
     const uint32_t tiles = job.rows > 128u ? 2u : 1u, items = tiles * job.nblk;
     const uint32_t group = static_cast<uint32_t>(c.warp) >> 2, quad = static_cast<uint32_t>(c.warp) & 3u;
-    float *stash = reinterpret_cast<float *>(smem_raw + (c.base - smem_u32(smem_raw))) + group * 8192u + quad * 32u + static_cast<uint32_t>(c.lane);
-    for (uint32_t it = group; it < items; it += kDecoderWarps / 4) {
-      const uint32_t tt = it / job.nblk, cb = it % job.nblk;
-      const uint32_t local = tt * 128u + quad * 32u + static_cast<uint32_t>(c.lane);
-      const bool valid = local < item.count;
-      const uint32_t row = item.first + (valid ? local : 0u);
-      const uint32_t col0 = (cb == 0u ? job.blk0 : job.blk1) * 128u;
-      const uint2 *sv = reinterpret_cast<const uint2 *>(svh + col0);
+    const uint32_t lane = static_cast<uint32_t>(c.lane);
+    const bool split = tiles == 1u;
+    const uint32_t tt = split ? 0u : group / job.nblk, cb = split ? (group & 1u) : group % job.nblk;
+    const bool live = split ? cb < job.nblk : group < items;
+    const uint32_t first = tt * 128u + quad * 32u;                         // the warp's first row of the item
+    const uint32_t rows = !live || item.count <= first ? 0u : (item.count - first < 32u ? item.count - first : 32u);
+    const bool valid = lane < rows;
+    const uint32_t row = item.first + first + (valid ? lane : 0u);
+    const uint32_t col0 = (cb == 0u ? job.blk0 : job.blk1) * 128u;
+    const float inv = valid ? inv_rows[row] : 0.0f;
+    // the lane's own row (PHASE 1): which assignment (token, rank) it is and its routing weight
+    const uint32_t my_a = PHASE == 1 && valid ? p.sorted[row] : 0u;
+    const float my_weight = PHASE == 1 && valid ? p.weights[my_a] : 0.0f;
+    float sv[2][2];   // svh of the four columns a lane writes: [pass][lo, hi] = columns 64 pass + lane, + 32
+#pragma unroll
+    for (int ps = 0; ps < 2; ++ps) {
+      sv[ps][0] = live ? __half2float(__ushort_as_half(__ldg(svh + col0 + 64u * ps + lane))) : 0.0f;
+      sv[ps][1] = live ? __half2float(__ushort_as_half(__ldg(svh + col0 + 64u * ps + 32u + lane))) : 0.0f;
+    }
+    if (core_accumulator(c, decoded, p.status + 1) && (split || live)) {
+      float *areas = reinterpret_cast<float *>(smem_raw + (c.base - smem_u32(smem_raw)));
+      float *mine = areas + group * 8192u;
+      const float *other = areas + (group ^ 2u) * 8192u;
       const uint32_t taddr = c.tmem + ((quad * 32u) << 16) + tt * 256u + cb * 128u;
       if (PHASE == 0) {
-        float4 *dst = reinterpret_cast<float4 *>(p.gu + static_cast<size_t>(row) * 2u * p.inter + col0);
-        block_epilogue(taddr, valid ? inv_rows[row] : 0.0f, valid, stash, [&](int q, const float (&r)[4]) {
-          const uint2 s = sv[q];
-          const __half2 s01 = *reinterpret_cast<const __half2 *>(&s.x), s23 = *reinterpret_cast<const __half2 *>(&s.y);
-          dst[q] = make_float4(r[0] * __low2float(s01), r[1] * __high2float(s01), r[2] * __low2float(s23), r[3] * __high2float(s23));
-        });
+        float *out = p.gu + static_cast<size_t>(item.first + first) * 2u * p.inter + col0 + lane;
+        auto emit = [&](uint32_t ps, uint32_t r, float lo, float hi) {
+          float *dst = out + static_cast<size_t>(r) * 2u * p.inter + 64u * ps;
+          dst[0] = lo * sv[ps][0];
+          dst[32] = hi * sv[ps][1];
+        };
+        if (split) half_epilogue(taddr, group >> 1, live, inv, valid, mine, other, quad, lane, rows, emit);
+        else block_epilogue(taddr, inv, valid, mine, quad, lane, rows, emit);
       } else {
-        const uint32_t a = p.sorted[row];
-        const uint32_t token = a / p.top_k;
-        const float wr = p.weights[a];
-        long long *dst = p.acc + static_cast<size_t>(token) * p.hidden + col0;
-        bool range = false;
-        block_epilogue(taddr, valid ? inv_rows[row] : 0.0f, valid, stash, [&](int q, const float (&r)[4]) {
-          const uint2 s = sv[q];
-          const __half2 s01 = *reinterpret_cast<const __half2 *>(&s.x), s23 = *reinterpret_cast<const __half2 *>(&s.y);
-          const float y[4] = {r[0] * __low2float(s01), r[1] * __high2float(s01), r[2] * __low2float(s23), r[3] * __high2float(s23)};
-#pragma unroll
-          for (int e = 0; e < 4; ++e) {
-            const float cval = wr * y[e];
-            if (!(fabsf(cval) < 2147483648.0f)) {   // also catches NaN
-              range = true;
-            } else {
-              atomicAdd(reinterpret_cast<unsigned long long *>(dst + 4 * q + e),
-                        static_cast<unsigned long long>(__double2ll_rn(static_cast<double>(cval) * 4294967296.0)));
-            }
-          }
-        });
-        if (range) atomicOr(p.status, kStatusRange);
+        auto emit = [&](uint32_t ps, uint32_t r, float lo, float hi) {   // the row's assignment and weight, handed round by shuffle
+          const uint32_t a = __shfl_sync(0xFFFFFFFFu, my_a, static_cast<int>(r));
+          const float wr = __shfl_sync(0xFFFFFFFFu, my_weight, static_cast<int>(r));
+          float *dst = p.down_rows + static_cast<size_t>(a) * p.hidden + col0 + 64u * ps + lane;
+          dst[0] = wr * (lo * sv[ps][0]);
+          dst[32] = wr * (hi * sv[ps][1]);
+        };
+        if (split) half_epilogue(taddr, group >> 1, live, inv, valid, mine, other, quad, lane, rows, emit);
+        else block_epilogue(taddr, inv, valid, mine, quad, lane, rows, emit);
       }
-      __syncwarp();   // the accumulator loads of the next item are warp-wide
     }
   }
   core_finish(c);
+}
+
+// One CTA per token: the token's weighted down products (one row per choice that had an expert with a
+// record) become 2^-32 fixed-point integers and are added to the token's accumulator row. Integer
+// sums do not depend on their order: the bits are those of adding every product on its own.
+__global__ void __launch_bounds__(256) moe_tc_fold_kernel(const __grid_constant__ ExpertParams p, uint32_t tokens) {
+  griddep_launch_dependents();
+  griddep_wait();
+  const uint32_t token = blockIdx.x;
+  if (token >= tokens) return;
+  __shared__ uint32_t present[64];
+  const uint32_t top_k = p.top_k < 64u ? p.top_k : 64u;
+  if (threadIdx.x < top_k) {
+    const int32_t e = p.ids[static_cast<size_t>(token) * p.top_k + threadIdx.x];
+    bool ok = e >= 0 && static_cast<uint32_t>(e) < p.experts;
+    if (ok) {
+      const ignis_moe_slot slot = p.slots[static_cast<uint32_t>(e) * 2u + 1u];
+      ok = slot.record != nullptr && (slot.k2 == 4 || slot.k2 == 5 || slot.k2 == 6 || slot.k2 == 8);
+    }
+    present[threadIdx.x] = ok ? 1u : 0u;
+  }
+  __syncthreads();
+  bool range = false;
+  // four columns per thread and trip (hidden is a multiple of 128), the choices' loads issued together
+  const float4 *rows4 = reinterpret_cast<const float4 *>(p.down_rows + static_cast<size_t>(token) * p.top_k * p.hidden);
+  const uint32_t quads = p.hidden / 4u;
+  for (uint32_t c4 = threadIdx.x; c4 < quads; c4 += 256u) {
+    long long sum[4] = {0, 0, 0, 0};
+    for (uint32_t k0 = 0; k0 < top_k; k0 += 8u) {
+      float4 v[8];
+#pragma unroll
+      for (uint32_t j = 0; j < 8u; ++j) {
+        v[j] = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (k0 + j < top_k && present[k0 + j] != 0u) v[j] = __ldcs(rows4 + static_cast<size_t>(k0 + j) * quads + c4);
+      }
+#pragma unroll
+      for (uint32_t j = 0; j < 8u; ++j) {
+        const float e[4] = {v[j].x, v[j].y, v[j].z, v[j].w};
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          if (!(fabsf(e[i]) < 2147483648.0f)) {   // also catches NaN
+            range = true;
+          } else {
+            // times 2^32 is exact in a float (the magnitude is below 2^31): the integer a double product would round to
+            sum[i] += __float2ll_rn(e[i] * 4294967296.0f);
+          }
+        }
+      }
+    }
+    long long *dst = p.acc + static_cast<size_t>(token) * p.hidden + 4u * c4;   // the caller's buffer: 8-byte alignment is all it promises
+#pragma unroll
+    for (int i = 0; i < 4; ++i) dst[i] += sum[i];
+  }
+  if (range) atomicOr(p.status, kStatusRange);
 }
 
 constexpr size_t kRotateSmemMax = 200 * 1024;
@@ -202,6 +265,7 @@ int32_t moe_tc_prepare(ErrorSlot &slot) {
 int32_t moe_tc_experts(ErrorSlot &slot, const DeviceState &dev, const ExpertParams &p, uint32_t rows, uint32_t items_max,
                        const uint32_t *offsets, cudaStream_t stream, const char *what) {
   const bool pdl = dev.pdl != 0;
+  const uint32_t tokens = rows / p.top_k;
   for (int phase = 0; phase < 2; ++phase) {
     const uint32_t in = phase == 0 ? p.hidden : p.inter;
     const uint32_t out_plane = phase == 0 ? 2u * p.inter : p.hidden;
@@ -219,6 +283,9 @@ int32_t moe_tc_experts(ErrorSlot &slot, const DeviceState &dev, const ExpertPara
                      : launch(moe_tc_gemm_kernel<1>, grid, dim3(kThreads), kSmemBytes, stream, pdl, map_a, p);
     if (err != cudaSuccess) return fail(slot, "%s: expert launch failed: %s", what, cudaGetErrorString(err));
   }
+  if (p.top_k > 64u) return fail(slot, "%s: more than 64 choices per token on the tensor-core route", what);
+  const cudaError_t err = launch(moe_tc_fold_kernel, dim3(tokens), dim3(256), 0, stream, pdl, p, tokens);
+  if (err != cudaSuccess) return fail(slot, "%s: fold launch failed: %s", what, cudaGetErrorString(err));
   return 0;
 }
 

@@ -105,36 +105,47 @@ __global__ void __launch_bounds__(kThreads, 1) trellis_tc_dense_kernel(const __g
   job.rows = p.tokens - job.row0 < 256u ? p.tokens - job.row0 : 256u;
   const bool have = core_run(c, job, &map_a, &g_trellis_tc_status);
   if (have) {
-    // the four (row tile, block) items go to the four groups of four warps; a warp's lanes are the
-    // rows 32 (warp % 4) .. + 31 of the row tile
+    // Two row tiles: the four (row tile, block) items go to the four groups of four warps. One: a
+    // group takes half a block's columns, so that all four are at work. A warp's lanes are the rows
+    // 32 (warp % 4) .. + 31 of the row tile.
     const uint32_t tiles = job.rows > 128u ? 2u : 1u, items = tiles * job.nblk;
     const uint32_t group = static_cast<uint32_t>(c.warp) >> 2, quad = static_cast<uint32_t>(c.warp) & 3u;
-    float *stash = reinterpret_cast<float *>(smem_raw + (c.base - smem_u32(smem_raw))) + group * 8192u + quad * 32u + static_cast<uint32_t>(c.lane);
-    for (uint32_t item = group; item < items; item += kDecoderWarps / 4) {
-      const uint32_t tt = item / job.nblk, cb = item % job.nblk;
-      const uint32_t token = job.row0 + tt * 128u + quad * 32u + static_cast<uint32_t>(c.lane);
-      const bool valid = token < p.tokens;
+    const uint32_t lane = static_cast<uint32_t>(c.lane);
+    float *areas = reinterpret_cast<float *>(smem_raw + (c.base - smem_u32(smem_raw)));
+    const bool split = tiles == 1u;
+    for (uint32_t item = split ? 0u : group; item < (split ? 1u : items); item += kDecoderWarps / 4) {
+      const uint32_t tt = split ? 0u : item / job.nblk, cb = split ? (group & 1u) : item % job.nblk;
+      const bool live = cb < job.nblk;
+      const uint32_t first = tt * 128u + quad * 32u;   // the warp's first row of the job
+      const uint32_t rows = !live || job.rows <= first ? 0u : (job.rows - first < 32u ? job.rows - first : 32u);
+      const bool valid = lane < rows;
+      const uint32_t token0 = job.row0 + first;
       const uint32_t col0 = (cb == 0u ? job.blk0 : job.blk1) * 128u;
-      const uint2 *sv = reinterpret_cast<const uint2 *>(p.svh + col0);
-      uint2 *dst = reinterpret_cast<uint2 *>(p.y + static_cast<size_t>(valid ? token : 0u) * p.ldy + col0);
-      block_epilogue(c.tmem + ((quad * 32u) << 16) + tt * 256u + cb * 128u, valid ? p.inv[token] : 0.0f, valid, stash,
-                     [&](int q, const float (&r4)[4]) {
-                       const uint2 sw = sv[q];
-                       const __half2 s01 = *reinterpret_cast<const __half2 *>(&sw.x), s23 = *reinterpret_cast<const __half2 *>(&sw.y);
-                       float r[4] = {r4[0] * __low2float(s01), r4[1] * __high2float(s01), r4[2] * __low2float(s23), r4[3] * __high2float(s23)};
-                       if (p.epilogue != kEpiStore) {
-                         const uint2 old = dst[q];
-                         const float o[4] = {bf16_bits_to_f32(old.x & 0xFFFFu), __uint_as_float(old.x & 0xFFFF0000u),
-                                             bf16_bits_to_f32(old.y & 0xFFFFu), __uint_as_float(old.y & 0xFFFF0000u)};
+      const float inv = valid ? p.inv[token0 + lane] : 0.0f;
+      float sv[2][2];   // svh of the four columns a lane writes: [pass][lo, hi] = columns 64 pass + lane, + 32
 #pragma unroll
-                         for (int e = 0; e < 4; ++e) r[e] = p.epilogue == kEpiAdd ? r[e] + o[e] : o[e] / (1.0f + __expf(-o[e])) * r[e];
-                       }
-                       const __nv_bfloat162 o01 = __floats2bfloat162_rn(r[0], r[1]), o23 = __floats2bfloat162_rn(r[2], r[3]);
-                       uint2 packed;
-                       packed.x = *reinterpret_cast<const uint32_t *>(&o01);
-                       packed.y = *reinterpret_cast<const uint32_t *>(&o23);
-                       dst[q] = packed;
-                     });
+      for (int ps = 0; ps < 2; ++ps) {
+        sv[ps][0] = live ? __half2float(__ushort_as_half(__ldg(p.svh + col0 + 64u * ps + lane))) : 0.0f;
+        sv[ps][1] = live ? __half2float(__ushort_as_half(__ldg(p.svh + col0 + 64u * ps + 32u + lane))) : 0.0f;
+      }
+      uint16_t *out = p.y + static_cast<size_t>(token0) * p.ldy + col0 + lane;
+      auto emit = [&](uint32_t ps, uint32_t r, float lo, float hi) {
+        uint16_t *dst = out + static_cast<size_t>(r) * p.ldy + 64u * ps;
+        float v[2] = {lo * sv[ps][0], hi * sv[ps][1]};
+        if (p.epilogue != kEpiStore) {
+#pragma unroll
+          for (int e = 0; e < 2; ++e) {
+            const float o = bf16_bits_to_f32(dst[32 * e]);
+            v[e] = p.epilogue == kEpiAdd ? v[e] + o : o / (1.0f + __expf(-o)) * v[e];
+          }
+        }
+#pragma unroll
+        for (int e = 0; e < 2; ++e) dst[32 * e] = __bfloat16_as_ushort(__float2bfloat16_rn(v[e]));
+      };
+      const uint32_t taddr = c.tmem + ((quad * 32u) << 16) + tt * 256u + cb * 128u;
+      float *mine = areas + group * 8192u;
+      if (split) half_epilogue(taddr, group >> 1, live, inv, valid, mine, areas + (group ^ 2u) * 8192u, quad, lane, rows, emit);
+      else block_epilogue(taddr, inv, valid, mine, quad, lane, rows, emit);
       __syncwarp();   // the accumulator loads of the next item are warp-wide
     }
   }

@@ -22,10 +22,12 @@
 //    thread brings the rows' fp16 activations by TMA (the same swizzle); one thread issues
 //    tcgen05.mma kind::f16 (M 128, N 256, K 16; fp16 x fp16, fp32 accumulation in tensor memory).
 //    Every decoded tile serves both row tiles: 512 accumulator columns, all of tensor memory.
-//  * The epilogue: a thread owns one row of one 128-column block. It reads the row's first 64
-//    accumulator columns, applies the row's inverse scale and six Hadamard stages in registers,
-//    parks the 64 values in the (by then idle) stage ring, does the same for the other 64 columns,
-//    and the seventh stage combines the two halves; then svh and the caller's epilogue.
+//  * The epilogue: a thread owns one row of one 128-column block (of half a block when the job has
+//    one row tile, so that all sixteen warps take part). It reads 64 accumulator columns, applies
+//    the row's inverse scale and six Hadamard stages in registers and parks the 64 values in the
+//    (by then idle) stage ring, where the seventh stage combines the two halves; the results are
+//    parked once more and written out row-wise - a warp per row, a lane per column - with svh and
+//    the caller's epilogue, so that a warp's stores (or atomics) are contiguous.
 //  * Every mbarrier wait is bounded; a wait that runs out sets a bit of a status word and the CTA
 //    falls through to the common exit and frees its tensor memory.
 #ifndef B200Q_TRELLIS_TC_CUH
@@ -220,19 +222,32 @@ __device__ __forceinline__ Core core_setup(uint8_t *smem_raw) {
   return c;
 }
 
-// Runs the CTA's role up to the finished accumulator. Returns true for a decoder warp whose
-// accumulator is complete (the epilogue may read tensor memory).
-__device__ __forceinline__ bool core_run(const Core &c, const Job &job, const CUtensorMap *map_a, uint32_t *status) {
+// The decoder warps' second step: waits for the accumulator. Returns true in the decoder warps when
+// all of them have the complete accumulator (the epilogue may read tensor memory and use barrier 1).
+// Every decoder warp calls it, with what core_roles returned to it.
+__device__ __forceinline__ bool core_accumulator(const Core &c, bool decoded, uint32_t *status) {
+  bool have = false;
+  if (decoded) {
+    have = mbar_wait(c.bar_acc, 0u);
+    if (!have && c.lane == 0) atomicOr(status, kStatusEpilogue);
+  }
+  // The epilogue's warps meet at barriers of their own: either every decoder warp has its
+  // accumulator or none goes on (a warp whose wait ran out must not leave the others waiting).
+  uint32_t all;
+  asm volatile("{ .reg .pred p, q; setp.ne.u32 p, %1, 0; bar.red.and.pred q, 1, %2, p; selp.u32 %0, 1, 0, q; }"
+               : "=r"(all) : "r"(static_cast<uint32_t>(have)), "n"(kDecoderWarps * 32) : "memory");
+  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+  return all != 0u;
+}
+
+// Runs the CTA's roles: the producer and the MMA thread to their end, the decoder warps through
+// their K stages. Returns true in a decoder warp that decoded all of them; such a warp has time for
+// loads of its own (what its epilogue will need) before it calls core_accumulator, while the last
+// MMAs retire.
+__device__ __forceinline__ bool core_roles(const Core &c, const Job &job, const CUtensorMap *map_a, uint32_t *status) {
   const uint32_t k_stages = job.in / 64u;
   const uint32_t row_tiles = job.rows > 128u ? 2u : 1u;
-  if (c.warp < kDecoderWarps) {
-    const bool ok = decode_stages_any(job, c.base, c.bars, c.warp, c.lane, status);
-    if (!ok) return false;
-    const bool have = mbar_wait(c.bar_acc, 0u);
-    if (!have && c.lane == 0) atomicOr(status, kStatusEpilogue);
-    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-    return have;
-  }
+  if (c.warp < kDecoderWarps) return decode_stages_any(job, c.base, c.bars, c.warp, c.lane, status);
   if (c.warp == kDecoderWarps) {
     // ---- producer of the activation tiles ----
     griddep_launch_dependents();
@@ -284,52 +299,122 @@ __device__ __forceinline__ bool core_run(const Core &c, const Job &job, const CU
   return false;
 }
 
-// The epilogue of one (row tile, block) item for the calling warp: lanes = rows 32 (warp % 4) .. of
-// the row tile, `taddr` the tensor-memory address of the block's first column in those lanes. The
-// four warps of a group (warp / 4) share one item; `stash` is the group's 32 KB of the idle stage
-// ring ([value 64][thread 128] floats). `emit(q, r)` receives columns 4 q .. 4 q + 3 (q < 32) of the
-// row, already multiplied by `inv`, the Hadamard and 1 / sqrt(128); rows with `valid` false only
-// take part in the warp-wide accumulator loads.
-template <class Emit>
-__device__ __forceinline__ void block_epilogue(uint32_t taddr, float inv, bool valid, float *stash, Emit emit) {
+// Both steps back to back.
+__device__ __forceinline__ bool core_run(const Core &c, const Job &job, const CUtensorMap *map_a, uint32_t *status) {
+  const bool decoded = core_roles(c, job, map_a, status);
+  return c.warp < kDecoderWarps ? core_accumulator(c, decoded, status) : false;
+}
+
+// ---- epilogue ------------------------------------------------------------------------------------
+// A warp group (warp / 4: four warps, 128 threads = the 128 rows of a row tile, a warp's lanes the
+// rows 32 (warp % 4) .. + 31) owns 32 KB of the idle stage ring as [value 64][row 128] floats. The
+// row's low five bits are XORed with the value index, so a warp's accesses are free of bank
+// conflicts both when its lanes are 32 rows of one value (a thread parking its row) and when they
+// are 32 values of one row (the warp writing a row out).
+__device__ __forceinline__ uint32_t stash_at(uint32_t i, uint32_t t) { return i * 128u + (t & 96u) + ((t ^ i) & 31u); }
+
+// Hands the calling warp's first `rows` rows of 64 parked values to `emit(r, lo, hi)`: lane l gets
+// values l and l + 32 of row r, so what the caller stores per row is contiguous across the warp.
+// (A thread storing its own row touches 32 different lines per instruction, and the memory pipe
+// takes them one per cycle: the row-wise form is what makes the epilogue short.)
+template <class RowEmit>
+__device__ __forceinline__ void emit_rows(const float *area, uint32_t quad, uint32_t lane, uint32_t rows, RowEmit emit) {
+  for (uint32_t r = 0; r < rows; ++r) {
+    const uint32_t t = quad * 32u + r;
+    emit(r, area[stash_at(lane, t)], area[stash_at(lane + 32u, t)]);
+  }
+}
+
+__device__ __forceinline__ void load_half_row(uint32_t taddr, float inv, float (&v)[64]) {
+#pragma unroll
+  for (int q = 0; q < 2; ++q) {
+    uint32_t r[32];
+    tmem_ld32(taddr + 32u * q, r);
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+    for (int i = 0; i < 32; ++i) v[32 * q + i] = __uint_as_float(r[i]) * inv;
+  }
+}
+
+// The epilogue of one (row tile, block) item for the calling warp: a thread owns one row (lane =
+// row 32 quad + lane of the row tile; `rows` of the warp's 32 exist, `valid` = lane < rows) and
+// `taddr` is the tensor-memory address of the block's first column in those lanes. The thread
+// applies `inv` and six Hadamard stages to each half of its 128 columns in registers, the seventh
+// stage combines the halves through `area`, and `emit(pass, r, lo, hi)` receives, a row at a
+// time, columns 64 pass + lane (lo) and 64 pass + 32 + lane (hi), 1 / sqrt(128) included.
+template <class RowEmit>
+__device__ __forceinline__ void block_epilogue(uint32_t taddr, float inv, bool valid, float *area, uint32_t quad, uint32_t lane,
+                                               uint32_t rows, RowEmit emit) {
+  const uint32_t t = quad * 32u + lane;
   float v[64];
 #pragma unroll
   for (int half = 0; half < 2; ++half) {
-#pragma unroll
-    for (int q = 0; q < 2; ++q) {
-      uint32_t r[32];
-      tmem_ld32(taddr + 64u * half + 32u * q, r);
-      asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-#pragma unroll
-      for (int i = 0; i < 32; ++i) v[32 * q + i] = __uint_as_float(r[i]) * inv;
-    }
+    load_half_row(taddr + 64u * half, inv, v);
     if (valid) {
       hadamard64_regs(v);
       if (half == 0) {
 #pragma unroll
-        for (int i = 0; i < 64; ++i) stash[i * 128] = v[i];
+        for (int i = 0; i < 64; ++i) area[stash_at(i, t)] = v[i];
       }
     }
   }
-  if (!valid) return;
   const float c = 0.08838834764831845f;   // 1 / sqrt(128)
-  // the seventh stage: columns i (sum) and 64 + i (difference); the differences wait in v
+  if (valid) {   // the seventh stage: columns i (sum, parked) and 64 + i (difference, kept)
 #pragma unroll
-  for (int q = 0; q < 16; ++q) {
-    float r[4];
-#pragma unroll
-    for (int e = 0; e < 4; ++e) {
-      const float a = stash[(4 * q + e) * 128], b = v[4 * q + e];
-      r[e] = (a + b) * c;
-      v[4 * q + e] = (a - b) * c;
+    for (int i = 0; i < 64; ++i) {
+      const float a = area[stash_at(i, t)], b = v[i];
+      area[stash_at(i, t)] = (a + b) * c;
+      v[i] = (a - b) * c;
     }
-    emit(q, r);
   }
+  __syncwarp();
+  emit_rows(area, quad, lane, rows, [&](uint32_t r, float lo, float hi) { emit(0u, r, lo, hi); });
+  __syncwarp();
+  if (valid) {
 #pragma unroll
-  for (int q = 0; q < 16; ++q) {
-    float r[4] = {v[4 * q], v[4 * q + 1], v[4 * q + 2], v[4 * q + 3]};
-    emit(16 + q, r);
+    for (int i = 0; i < 64; ++i) area[stash_at(i, t)] = v[i];
   }
+  __syncwarp();
+  emit_rows(area, quad, lane, rows, [&](uint32_t r, float lo, float hi) { emit(1u, r, lo, hi); });
+}
+
+// The same for a job of one row tile, where only two of the four warp groups would have a block:
+// groups g and g ^ 2 share block g & 1, a thread owning 64 columns of its row (half = g >> 1). Each
+// transforms its half and parks it in its group's area (`mine`); all decoder warps meet at barrier 1;
+// the seventh stage gives the first half's owner columns 0..63 (sums) and the other's columns
+// 64..127 (differences), parked again after a second meeting and written out row-wise:
+// `emit(half, r, lo, hi)` as above. Every decoder warp calls this exactly once (`live`: the group's
+// block exists - warp-uniform).
+template <class RowEmit>
+__device__ __forceinline__ void half_epilogue(uint32_t taddr_block, uint32_t half, bool live, float inv, bool valid, float *mine,
+                                              const float *other, uint32_t quad, uint32_t lane, uint32_t rows, RowEmit emit) {
+  const uint32_t t = quad * 32u + lane;
+  float v[64];
+  if (live) {
+    load_half_row(taddr_block + 64u * half, inv, v);
+    if (valid) {
+      hadamard64_regs(v);
+#pragma unroll
+      for (int i = 0; i < 64; ++i) mine[stash_at(i, t)] = v[i];
+    }
+  }
+  asm volatile("bar.sync 1, %0;" ::"n"(kDecoderWarps * 32) : "memory");
+  const float c = 0.08838834764831845f;   // 1 / sqrt(128)
+  if (live && valid) {
+#pragma unroll
+    for (int i = 0; i < 64; ++i) {
+      const float o = other[stash_at(i, t)];
+      v[i] = half == 0u ? (v[i] + o) * c : (o - v[i]) * c;
+    }
+  }
+  asm volatile("bar.sync 1, %0;" ::"n"(kDecoderWarps * 32) : "memory");
+  if (!live) return;
+  if (valid) {
+#pragma unroll
+    for (int i = 0; i < 64; ++i) mine[stash_at(i, t)] = v[i];
+  }
+  __syncwarp();
+  emit_rows(mine, quad, lane, rows, [&](uint32_t r, float lo, float hi) { emit(half, r, lo, hi); });
 }
 
 __device__ __forceinline__ void core_finish(const Core &c) {
