@@ -107,13 +107,14 @@ __global__ void __launch_bounds__(256) moe_tc_rotate_kernel(const __grid_constan
 
 // PHASE 0: gate | up products of an item into gu. PHASE 1: down, weighted, into acc.
 // One CTA per (item, 256 output columns); no CTA waits for another.
-template <int PHASE>
-__global__ void __launch_bounds__(kThreads, 1) moe_tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a,
+template <int PHASE, int DW>
+__global__ void __launch_bounds__(Shape<DW>::kThreads, DW == 16 ? 1 : 2) moe_tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a,
                                                                  const __grid_constant__ ExpertParams p) {
   extern __shared__ uint8_t smem_raw[];
   const uint32_t in = PHASE == 0 ? p.hidden : p.inter;
   const uint32_t out_plane = PHASE == 0 ? 2u * p.inter : p.hidden;
-  const uint32_t col_tiles = (out_plane + 255u) / 256u;
+  constexpr uint32_t kCols = Shape<DW>::kCols, kBlocks = Shape<DW>::kBlocks;
+  const uint32_t col_tiles = (out_plane + kCols - 1u) / kCols;
   const uint32_t item_index = blockIdx.x / col_tiles, col_tile = blockIdx.x % col_tiles;
   griddep_launch_dependents();
   griddep_wait();   // the item list and the rotated rows come from the kernels before
@@ -124,30 +125,31 @@ __global__ void __launch_bounds__(kThreads, 1) moe_tc_gemm_kernel(const __grid_c
     if (threadIdx.x == 0 && col_tile == 0) atomicOr(p.status, kStatusAbsentRecord);
     return;
   }
-  const Core c = core_setup(smem_raw);
+  const Core c = core_setup<DW>(smem_raw);
   Job job;
   job.trellis = static_cast<const uint32_t *>(slot.record);
   job.k2 = slot.k2;
   job.tile_stride = out_plane / 16u;
   job.in = in;
-  job.blk0 = 2u * col_tile;
-  job.blk1 = 2u * col_tile + 1u;
-  job.nblk = job.blk1 < out_plane / 128u ? 2u : 1u;
+  job.blk0 = kBlocks * col_tile;
+  job.blk1 = kBlocks * col_tile + 1u;
+  job.nblk = kBlocks == 2u && job.blk1 < out_plane / 128u ? 2u : 1u;
   job.row0 = item.first;
   job.rows = item.count;
   const uint64_t trellis_bytes = static_cast<uint64_t>(in) * out_plane * slot.k2 / 16u;
   const uint16_t *svh = reinterpret_cast<const uint16_t *>(static_cast<const uint8_t *>(slot.record) + trellis_bytes) + in;
   const float *inv_rows = reinterpret_cast<const float *>(PHASE == 0 ? p.scale_in : p.scale_h);
-  const bool decoded = core_roles(c, job, &map_a, p.status + 1);   // word 1 of the status line: waits of this kernel that ran out
-  if (c.warp < kDecoderWarps) {
-    // One row tile: (block, half of its columns) per warp group, all four groups at work. Two row
+  const bool decoded = core_roles<DW>(c, job, &map_a, p.status + 1);   // word 1 of the status line: waits of this kernel that ran out
+  if (c.warp < DW) {
+    // One row tile: (block, half of its columns) per warp group, all groups at work. Two row
     // tiles: (row tile, block) per group. What the epilogue needs from global memory is asked for
     // here, before the wait for the accumulator: the loads travel while the last MMAs retire.
     const uint32_t tiles = job.rows > 128u ? 2u : 1u, items = tiles * job.nblk;
     const uint32_t group = static_cast<uint32_t>(c.warp) >> 2, quad = static_cast<uint32_t>(c.warp) & 3u;
     const uint32_t lane = static_cast<uint32_t>(c.lane);
     const bool split = tiles == 1u;
-    const uint32_t tt = split ? 0u : group / job.nblk, cb = split ? (group & 1u) : group % job.nblk;
+    const uint32_t tt = split ? 0u : group / job.nblk, cb = split ? group % kBlocks : group % job.nblk;
+    const uint32_t half = group / kBlocks;   // split jobs: which 64 columns of the block
     const bool live = split ? cb < job.nblk : group < items;
     const uint32_t first = tt * 128u + quad * 32u;                         // the warp's first row of the item
     const uint32_t rows = !live || item.count <= first ? 0u : (item.count - first < 32u ? item.count - first : 32u);
@@ -164,11 +166,11 @@ __global__ void __launch_bounds__(kThreads, 1) moe_tc_gemm_kernel(const __grid_c
       sv[ps][0] = live ? __half2float(__ushort_as_half(__ldg(svh + col0 + 64u * ps + lane))) : 0.0f;
       sv[ps][1] = live ? __half2float(__ushort_as_half(__ldg(svh + col0 + 64u * ps + 32u + lane))) : 0.0f;
     }
-    if (core_accumulator(c, decoded, p.status + 1) && (split || live)) {
+    if (core_accumulator<DW>(c, decoded, p.status + 1) && (split || live)) {
       float *areas = reinterpret_cast<float *>(smem_raw + (c.base - smem_u32(smem_raw)));
       float *mine = areas + group * 8192u;
-      const float *other = areas + (group ^ 2u) * 8192u;
-      const uint32_t taddr = c.tmem + ((quad * 32u) << 16) + tt * 256u + cb * 128u;
+      const float *other = areas + (group ^ kBlocks) * 8192u;
+      const uint32_t taddr = c.tmem + ((quad * 32u) << 16) + tt * kCols + cb * 128u;
       if (PHASE == 0) {
         float *out = p.gu + static_cast<size_t>(item.first + first) * 2u * p.inter + col0 + lane;
         auto emit = [&](uint32_t ps, uint32_t r, float lo, float hi) {
@@ -176,7 +178,7 @@ __global__ void __launch_bounds__(kThreads, 1) moe_tc_gemm_kernel(const __grid_c
           dst[0] = lo * sv[ps][0];
           dst[32] = hi * sv[ps][1];
         };
-        if (split) half_epilogue(taddr, group >> 1, live, inv, valid, mine, other, quad, lane, rows, emit);
+        if (split) half_epilogue<DW>(taddr, half, live, inv, valid, mine, other, quad, lane, rows, emit);
         else block_epilogue(taddr, inv, valid, mine, quad, lane, rows, emit);
       } else {
         auto emit = [&](uint32_t ps, uint32_t r, float lo, float hi) {   // the row's assignment and weight, handed round by shuffle
@@ -186,12 +188,12 @@ __global__ void __launch_bounds__(kThreads, 1) moe_tc_gemm_kernel(const __grid_c
           dst[0] = wr * (lo * sv[ps][0]);
           dst[32] = wr * (hi * sv[ps][1]);
         };
-        if (split) half_epilogue(taddr, group >> 1, live, inv, valid, mine, other, quad, lane, rows, emit);
+        if (split) half_epilogue<DW>(taddr, half, live, inv, valid, mine, other, quad, lane, rows, emit);
         else block_epilogue(taddr, inv, valid, mine, quad, lane, rows, emit);
       }
     }
   }
-  core_finish(c);
+  core_finish<DW>(c);
 }
 
 // One CTA per token: the token's weighted down products (one row per choice that had an expert with a
@@ -250,11 +252,33 @@ __global__ void __launch_bounds__(256) moe_tc_fold_kernel(const __grid_constant_
 
 constexpr size_t kRotateSmemMax = 200 * 1024;
 
+
+// Which shape the expert products take: 8 decoder warps and two CTAs per SM unless B200Q_MOE_TC_WIDE
+// is set to 1 (read when the kernels are prepared).
+int g_moe_dw = 8;
+
+template <int DW>
+cudaError_t set_gemm_attrs() {
+  cudaError_t err = cudaFuncSetAttribute(moe_tc_gemm_kernel<0, DW>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(Shape<DW>::kSmemBytes));
+  if (err == cudaSuccess) err = cudaFuncSetAttribute(moe_tc_gemm_kernel<1, DW>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(Shape<DW>::kSmemBytes));
+  return err;
+}
+
+template <int DW>
+cudaError_t launch_gemm(int phase, uint32_t items_max, uint32_t out_plane, cudaStream_t stream, bool pdl, const CUtensorMap &map_a, const ExpertParams &p) {
+  const uint32_t col_tiles = (out_plane + Shape<DW>::kCols - 1u) / Shape<DW>::kCols;
+  const dim3 grid(items_max * col_tiles);
+  return phase == 0 ? launch(moe_tc_gemm_kernel<0, DW>, grid, dim3(Shape<DW>::kThreads), Shape<DW>::kSmemBytes, stream, pdl, map_a, p)
+                    : launch(moe_tc_gemm_kernel<1, DW>, grid, dim3(Shape<DW>::kThreads), Shape<DW>::kSmemBytes, stream, pdl, map_a, p);
+}
+
 }  // namespace
 
 int32_t moe_tc_prepare(ErrorSlot &slot) {
-  cudaError_t err = cudaFuncSetAttribute(moe_tc_gemm_kernel<0>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(kSmemBytes));
-  if (err == cudaSuccess) err = cudaFuncSetAttribute(moe_tc_gemm_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(kSmemBytes));
+  const char *wide = getenv("B200Q_MOE_TC_WIDE");
+  g_moe_dw = wide != nullptr && wide[0] == '1' ? 16 : 8;
+  cudaError_t err = set_gemm_attrs<16>();
+  if (err == cudaSuccess) err = set_gemm_attrs<8>();
   if (err == cudaSuccess) err = cudaFuncSetAttribute(moe_tc_rotate_kernel<0>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(kRotateSmemMax));
   if (err == cudaSuccess) err = cudaFuncSetAttribute(moe_tc_rotate_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(kRotateSmemMax));
   if (err != cudaSuccess) return fail(slot, "MoE tensor-core kernel attributes: %s", cudaGetErrorString(err));
@@ -277,10 +301,7 @@ int32_t moe_tc_experts(ErrorSlot &slot, const DeviceState &dev, const ExpertPara
     if (!make_rows_map(&map_a, phase == 0 ? static_cast<const void *>(p.frag_in) : static_cast<const void *>(p.frag_h), rows, in)) {
       return fail(slot, "%s: tensor map encoding failed", what);
     }
-    const uint32_t col_tiles = (out_plane + 255u) / 256u;
-    const dim3 grid(items_max * col_tiles);
-    err = phase == 0 ? launch(moe_tc_gemm_kernel<0>, grid, dim3(kThreads), kSmemBytes, stream, pdl, map_a, p)
-                     : launch(moe_tc_gemm_kernel<1>, grid, dim3(kThreads), kSmemBytes, stream, pdl, map_a, p);
+    err = g_moe_dw == 16 ? launch_gemm<16>(phase, items_max, out_plane, stream, pdl, map_a, p) : launch_gemm<8>(phase, items_max, out_plane, stream, pdl, map_a, p);
     if (err != cudaSuccess) return fail(slot, "%s: expert launch failed: %s", what, cudaGetErrorString(err));
   }
   if (p.top_k > 64u) return fail(slot, "%s: more than 64 choices per token on the tensor-core route", what);

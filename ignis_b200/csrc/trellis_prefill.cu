@@ -85,10 +85,13 @@ struct DenseParams {
   uint32_t k2, tile_stride, in, out, tokens, ldy, epilogue;
 };
 
-__global__ void __launch_bounds__(kThreads, 1) trellis_tc_dense_kernel(const __grid_constant__ CUtensorMap map_a,
+constexpr int kDenseDw = 16;   // the wide shape: a decoded tile serves 256 tokens
+using DenseShape = Shape<kDenseDw>;
+
+__global__ void __launch_bounds__(DenseShape::kThreads, 1) trellis_tc_dense_kernel(const __grid_constant__ CUtensorMap map_a,
                                                                       const __grid_constant__ DenseParams p) {
   extern __shared__ uint8_t smem_raw[];
-  const Core c = core_setup(smem_raw);
+  const Core c = core_setup<kDenseDw>(smem_raw);
   // Token tiles run fastest over the grid, so the CTAs at work at one time decode the same columns
   // of the plane (read from HBM once, then from the L2).
   const uint32_t row_tiles = (p.tokens + 255u) / 256u;
@@ -103,7 +106,7 @@ __global__ void __launch_bounds__(kThreads, 1) trellis_tc_dense_kernel(const __g
   job.nblk = job.blk1 < p.out / 128u ? 2u : 1u;
   job.row0 = row_tile * 256u;
   job.rows = p.tokens - job.row0 < 256u ? p.tokens - job.row0 : 256u;
-  const bool have = core_run(c, job, &map_a, &g_trellis_tc_status);
+  const bool have = core_run<kDenseDw>(c, job, &map_a, &g_trellis_tc_status);
   if (have) {
     // Two row tiles: the four (row tile, block) items go to the four groups of four warps. One: a
     // group takes half a block's columns, so that all four are at work. A warp's lanes are the rows
@@ -113,7 +116,7 @@ __global__ void __launch_bounds__(kThreads, 1) trellis_tc_dense_kernel(const __g
     const uint32_t lane = static_cast<uint32_t>(c.lane);
     float *areas = reinterpret_cast<float *>(smem_raw + (c.base - smem_u32(smem_raw)));
     const bool split = tiles == 1u;
-    for (uint32_t item = split ? 0u : group; item < (split ? 1u : items); item += kDecoderWarps / 4) {
+    for (uint32_t item = split ? 0u : group; item < (split ? 1u : items); item += kDenseDw / 4) {
       const uint32_t tt = split ? 0u : item / job.nblk, cb = split ? (group & 1u) : item % job.nblk;
       const bool live = cb < job.nblk;
       const uint32_t first = tt * 128u + quad * 32u;   // the warp's first row of the job
@@ -144,12 +147,12 @@ __global__ void __launch_bounds__(kThreads, 1) trellis_tc_dense_kernel(const __g
       };
       const uint32_t taddr = c.tmem + ((quad * 32u) << 16) + tt * 256u + cb * 128u;
       float *mine = areas + group * 8192u;
-      if (split) half_epilogue(taddr, group >> 1, live, inv, valid, mine, areas + (group ^ 2u) * 8192u, quad, lane, rows, emit);
+      if (split) half_epilogue<kDenseDw>(taddr, group >> 1, live, inv, valid, mine, areas + (group ^ 2u) * 8192u, quad, lane, rows, emit);
       else block_epilogue(taddr, inv, valid, mine, quad, lane, rows, emit);
       __syncwarp();   // the accumulator loads of the next item are warp-wide
     }
   }
-  core_finish(c);
+  core_finish<kDenseDw>(c);
 }
 
 uint64_t align256(uint64_t v) { return (v + 255u) & ~static_cast<uint64_t>(255u); }
@@ -166,7 +169,7 @@ uint64_t trellis_tc_workspace_bytes(uint32_t in, uint32_t weights, uint32_t toke
 }
 
 int32_t trellis_tc_prepare(ErrorSlot &slot) {
-  cudaError_t err = cudaFuncSetAttribute(trellis_tc_dense_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(kSmemBytes));
+  cudaError_t err = cudaFuncSetAttribute(trellis_tc_dense_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(DenseShape::kSmemBytes));
   if (err == cudaSuccess) {
     err = cudaFuncSetAttribute(trellis_rotate_rows_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(kRotateMaxSmem));
   }
@@ -205,7 +208,7 @@ int32_t one_product(ErrorSlot &slot, const DeviceState &dev, const ignis_trellis
   p.ldy = ldy;
   p.epilogue = epilogue;
   const uint32_t col_tiles = (w->out + 255u) / 256u, row_tiles = (tokens + 255u) / 256u;
-  err = launch(trellis_tc_dense_kernel, dim3(col_tiles * row_tiles), dim3(kThreads), kSmemBytes, stream, dev.pdl != 0, map_a, p);
+  err = launch(trellis_tc_dense_kernel, dim3(col_tiles * row_tiles), dim3(DenseShape::kThreads), DenseShape::kSmemBytes, stream, dev.pdl != 0, map_a, p);
   if (err != cudaSuccess) return fail(slot, "%s: launch failed: %s", what, cudaGetErrorString(err));
   return 0;
 }

@@ -41,14 +41,25 @@ namespace trellis_tc {
 
 using namespace trellis_dev;
 
-constexpr int kDecoderWarps = 16;
-constexpr int kThreads = (kDecoderWarps + 2) * 32;   // the decoder / epilogue warps, the producer warp, the MMA warp
-constexpr uint32_t kStages = 3;
 constexpr uint32_t kABytes = 128 * 128;     // one row tile of a stage: 128 rows x 64 fp16
-constexpr uint32_t kBBytes = 256 * 128;     // one stage of decoded weights: 256 columns x 64 fp16
-constexpr uint32_t kStageBytes = 2 * kABytes + kBBytes;
-constexpr uint32_t kSmemBytes = kStages * kStageBytes + 256 + 1024;   // + barriers and the tensor-memory slot + alignment slack
-constexpr uint32_t kTmemCols = 512;
+
+// Two shapes of the CTA. DW = 16 decoder warps: 256 output columns (two Hadamard blocks), three
+// stages, all 512 tensor-memory columns, one CTA per SM - every decoded tile serves up to 256 rows
+// once. DW = 8: 128 output columns (one block), two stages, 256 tensor-memory columns, so that TWO
+// CTAs share an SM (the same sixteen decoder warps in all) and one's setup, pipeline fill, drain and
+// epilogue run under the other's decoding: for jobs too short to amortise those (the MoE items).
+template <int DW>
+struct Shape {
+  static constexpr int kDecoderWarps = DW;
+  static constexpr int kThreads = (DW + 2) * 32;   // the decoder / epilogue warps, the producer warp, the MMA warp
+  static constexpr uint32_t kBlocks = DW / 8;       // 128-column blocks per CTA
+  static constexpr uint32_t kCols = DW * 16;        // output columns per CTA = accumulator columns per row tile
+  static constexpr uint32_t kStages = DW == 16 ? 3 : 2;
+  static constexpr uint32_t kBBytes = kCols * 128;  // one stage of decoded weights: kCols columns x 64 fp16
+  static constexpr uint32_t kStageBytes = 2 * kABytes + kBBytes;
+  static constexpr uint32_t kSmemBytes = kStages * kStageBytes + 256 + 1024;   // + barriers and the tensor-memory slot + alignment slack
+  static constexpr uint32_t kTmemCols = 2 * kCols;
+};
 constexpr uint32_t kStatusProducer = 1u, kStatusMma = 2u, kStatusEpilogue = 4u, kStatusDecoder = 8u;
 
 // What one CTA multiplies: rows [row0, row0 + rows) of the rotated activations (rows <= 256) with
@@ -116,8 +127,9 @@ __device__ __forceinline__ uint32_t tile_word(const uint32_t (&w)[(4 * K2 + 31) 
 
 // The decoder warps' loop over the job's K stages. `stages_base` is the shared-memory address of
 // stage 0; `bars`: full[kStages], empty[kStages].
-template <int K2>
+template <int K2, int DW>
 __device__ __forceinline__ bool decode_stages(const Job &job, uint32_t stages_base, uint32_t bars, int warp, int lane, uint32_t *status) {
+  constexpr uint32_t kStages = Shape<DW>::kStages, kStageBytes = Shape<DW>::kStageBytes;
   const LaneWindow win = lane_window(K2, lane);
   const uint32_t k_stages = job.in / 64u;
   const uint32_t cb = static_cast<uint32_t>(warp) >> 3;                    // which of the job's two column blocks
@@ -173,14 +185,15 @@ __device__ __forceinline__ bool decode_stages(const Job &job, uint32_t stages_ba
   return true;
 }
 
+template <int DW>
 __device__ __forceinline__ bool decode_stages_any(const Job &job, uint32_t stages_base, uint32_t bars, int warp, int lane, uint32_t *status) {
   switch (job.k2) {
-    case 4: return decode_stages<4>(job, stages_base, bars, warp, lane, status);
-    case 5: return decode_stages<5>(job, stages_base, bars, warp, lane, status);
-    case 6: return decode_stages<6>(job, stages_base, bars, warp, lane, status);
-    case 8: return decode_stages<8>(job, stages_base, bars, warp, lane, status);
-    case 10: return decode_stages<10>(job, stages_base, bars, warp, lane, status);
-    default: return decode_stages<12>(job, stages_base, bars, warp, lane, status);
+    case 4: return decode_stages<4, DW>(job, stages_base, bars, warp, lane, status);
+    case 5: return decode_stages<5, DW>(job, stages_base, bars, warp, lane, status);
+    case 6: return decode_stages<6, DW>(job, stages_base, bars, warp, lane, status);
+    case 8: return decode_stages<8, DW>(job, stages_base, bars, warp, lane, status);
+    case 10: return decode_stages<10, DW>(job, stages_base, bars, warp, lane, status);
+    default: return decode_stages<12, DW>(job, stages_base, bars, warp, lane, status);
   }
 }
 
@@ -194,7 +207,10 @@ struct Core {
   int warp, lane;
 };
 
+template <int DW>
 __device__ __forceinline__ Core core_setup(uint8_t *smem_raw) {
+  constexpr uint32_t kStages = Shape<DW>::kStages, kStageBytes = Shape<DW>::kStageBytes, kTmemCols = Shape<DW>::kTmemCols;
+  constexpr int kDecoderWarps = DW;
   Core c;
   const uint32_t raw = smem_u32(smem_raw);
   c.base = (raw + 1023u) & ~1023u;   // the 128-byte swizzle wants 1024-byte aligned tiles
@@ -225,7 +241,9 @@ __device__ __forceinline__ Core core_setup(uint8_t *smem_raw) {
 // The decoder warps' second step: waits for the accumulator. Returns true in the decoder warps when
 // all of them have the complete accumulator (the epilogue may read tensor memory and use barrier 1).
 // Every decoder warp calls it, with what core_roles returned to it.
+template <int DW>
 __device__ __forceinline__ bool core_accumulator(const Core &c, bool decoded, uint32_t *status) {
+  constexpr int kDecoderWarps = DW;
   bool have = false;
   if (decoded) {
     have = mbar_wait(c.bar_acc, 0u);
@@ -244,10 +262,13 @@ __device__ __forceinline__ bool core_accumulator(const Core &c, bool decoded, ui
 // their K stages. Returns true in a decoder warp that decoded all of them; such a warp has time for
 // loads of its own (what its epilogue will need) before it calls core_accumulator, while the last
 // MMAs retire.
+template <int DW>
 __device__ __forceinline__ bool core_roles(const Core &c, const Job &job, const CUtensorMap *map_a, uint32_t *status) {
+  constexpr uint32_t kStages = Shape<DW>::kStages, kStageBytes = Shape<DW>::kStageBytes;
+  constexpr int kDecoderWarps = DW;
   const uint32_t k_stages = job.in / 64u;
   const uint32_t row_tiles = job.rows > 128u ? 2u : 1u;
-  if (c.warp < kDecoderWarps) return decode_stages_any(job, c.base, c.bars, c.warp, c.lane, status);
+  if (c.warp < kDecoderWarps) return decode_stages_any<DW>(job, c.base, c.bars, c.warp, c.lane, status);
   if (c.warp == kDecoderWarps) {
     // ---- producer of the activation tiles ----
     griddep_launch_dependents();
@@ -290,7 +311,7 @@ __device__ __forceinline__ bool core_roles(const Core &c, const Job &job, const 
 #pragma unroll
       for (uint32_t kb = 0; kb < 4; ++kb) {   // 16 values along K are 32 bytes: two 16-byte units further
         mma_f16(c.tmem, a0 + 2u * kb, b + 2u * kb, idesc, (it | kb) != 0u ? 1u : 0u);
-        if (row_tiles == 2u) mma_f16(c.tmem + 256u, a1 + 2u * kb, b + 2u * kb, idesc, (it | kb) != 0u ? 1u : 0u);
+        if (row_tiles == 2u) mma_f16(c.tmem + Shape<DW>::kCols, a1 + 2u * kb, b + 2u * kb, idesc, (it | kb) != 0u ? 1u : 0u);
       }
       mma_commit(c.bars + 8u * (kStages + slot));
     }
@@ -300,9 +321,10 @@ __device__ __forceinline__ bool core_roles(const Core &c, const Job &job, const 
 }
 
 // Both steps back to back.
+template <int DW>
 __device__ __forceinline__ bool core_run(const Core &c, const Job &job, const CUtensorMap *map_a, uint32_t *status) {
-  const bool decoded = core_roles(c, job, map_a, status);
-  return c.warp < kDecoderWarps ? core_accumulator(c, decoded, status) : false;
+  const bool decoded = core_roles<DW>(c, job, map_a, status);
+  return c.warp < DW ? core_accumulator<DW>(c, decoded, status) : false;
 }
 
 // ---- epilogue ------------------------------------------------------------------------------------
@@ -385,7 +407,7 @@ __device__ __forceinline__ void block_epilogue(uint32_t taddr, float inv, bool v
 // 64..127 (differences), parked again after a second meeting and written out row-wise:
 // `emit(half, r, lo, hi)` as above. Every decoder warp calls this exactly once (`live`: the group's
 // block exists - warp-uniform).
-template <class RowEmit>
+template <int DW, class RowEmit>
 __device__ __forceinline__ void half_epilogue(uint32_t taddr_block, uint32_t half, bool live, float inv, bool valid, float *mine,
                                               const float *other, uint32_t quad, uint32_t lane, uint32_t rows, RowEmit emit) {
   const uint32_t t = quad * 32u + lane;
@@ -398,7 +420,7 @@ __device__ __forceinline__ void half_epilogue(uint32_t taddr_block, uint32_t hal
       for (int i = 0; i < 64; ++i) mine[stash_at(i, t)] = v[i];
     }
   }
-  asm volatile("bar.sync 1, %0;" ::"n"(kDecoderWarps * 32) : "memory");
+  asm volatile("bar.sync 1, %0;" ::"n"(DW * 32) : "memory");
   const float c = 0.08838834764831845f;   // 1 / sqrt(128)
   if (live && valid) {
 #pragma unroll
@@ -407,7 +429,7 @@ __device__ __forceinline__ void half_epilogue(uint32_t taddr_block, uint32_t hal
       v[i] = half == 0u ? (v[i] + o) * c : (o - v[i]) * c;
     }
   }
-  asm volatile("bar.sync 1, %0;" ::"n"(kDecoderWarps * 32) : "memory");
+  asm volatile("bar.sync 1, %0;" ::"n"(DW * 32) : "memory");
   if (!live) return;
   if (valid) {
 #pragma unroll
@@ -417,7 +439,10 @@ __device__ __forceinline__ void half_epilogue(uint32_t taddr_block, uint32_t hal
   emit_rows(mine, quad, lane, rows, [&](uint32_t r, float lo, float hi) { emit(half, r, lo, hi); });
 }
 
+template <int DW>
 __device__ __forceinline__ void core_finish(const Core &c) {
+  constexpr int kDecoderWarps = DW;
+  constexpr uint32_t kTmemCols = Shape<DW>::kTmemCols;
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
   __syncthreads();
   if (c.warp == kDecoderWarps + 1) {
