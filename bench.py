@@ -733,7 +733,7 @@ def moe_line(r: dict, steps: int, warmup: int, world: int, peaks: dict) -> dict:
                        **({"rank0_step_split": r["split"]} if r["split"] else {})},
             "e2e": {"value": r["flops"] / 1e12 / (r["e2e_ms"] / steps * 1e-3), "unit": "TFLOP/s", "h2d_bytes_per_step": r["h2d"],
                     "d2h_bytes_per_step": r["d2h"]},
-            "gpu_launches": 10 * steps, "clocks": r["clocks"],   # count, scan, scatter, 2 rotations, 2 expert products, 2 shared-expert products, combine
+            "gpu_launches": (11 if r["tokens"] > 8 else 10) * steps, "clocks": r["clocks"],   # count, scan, scatter, 2 rotations, 2 expert products, the fold (wide calls), 2 shared-expert products, combine
             "roofline": {"bound": "tensor", "achieved": value, "peak": peak, "unit": "TFLOP/s", "frac": value / peak,
                          "peak_source": f"{peaks['kind']} sustained BF16 cuBLAS rate per GPU (the experts multiply in FP16 with FP32 accumulation)",
                          "kernel": "moe_tc_gemm_kernel" if r["tokens"] > 64 else "moe_experts_kernel", "traffic": None,

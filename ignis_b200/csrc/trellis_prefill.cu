@@ -85,11 +85,12 @@ struct DenseParams {
   uint32_t k2, tile_stride, in, out, tokens, ldy, epilogue;
 };
 
-constexpr int kDenseDw = 16;   // the wide shape: a decoded tile serves 256 tokens
-using DenseShape = Shape<kDenseDw>;
-
-__global__ void __launch_bounds__(DenseShape::kThreads, 1) trellis_tc_dense_kernel(const __grid_constant__ CUtensorMap map_a,
-                                                                      const __grid_constant__ DenseParams p) {
+// DW: the core's shape - 16 (256 columns a CTA, one CTA per SM) or 8 (128 columns, two per SM).
+template <int DW>
+__global__ void __launch_bounds__(Shape<DW>::kThreads, DW == 16 ? 1 : 2) trellis_tc_dense_kernel(const __grid_constant__ CUtensorMap map_a,
+                                                                                              const __grid_constant__ DenseParams p) {
+  constexpr int kDenseDw = DW;
+  constexpr uint32_t kCols = Shape<DW>::kCols, kBlocks = Shape<DW>::kBlocks;
   extern __shared__ uint8_t smem_raw[];
   const Core c = core_setup<kDenseDw>(smem_raw);
   // Token tiles run fastest over the grid, so the CTAs at work at one time decode the same columns
@@ -101,36 +102,38 @@ __global__ void __launch_bounds__(DenseShape::kThreads, 1) trellis_tc_dense_kern
   job.k2 = p.k2;
   job.tile_stride = p.tile_stride;
   job.in = p.in;
-  job.blk0 = 2u * col_tile;
-  job.blk1 = 2u * col_tile + 1u;
-  job.nblk = job.blk1 < p.out / 128u ? 2u : 1u;
+  job.blk0 = kBlocks * col_tile;
+  job.blk1 = kBlocks * col_tile + 1u;
+  job.nblk = kBlocks == 2u && job.blk1 < p.out / 128u ? 2u : 1u;
   job.row0 = row_tile * 256u;
   job.rows = p.tokens - job.row0 < 256u ? p.tokens - job.row0 : 256u;
-  const bool have = core_run<kDenseDw>(c, job, &map_a, &g_trellis_tc_status);
-  if (have) {
-    // Two row tiles: the four (row tile, block) items go to the four groups of four warps. One: a
-    // group takes half a block's columns, so that all four are at work. A warp's lanes are the rows
-    // 32 (warp % 4) .. + 31 of the row tile.
+  const bool decoded = core_roles<kDenseDw>(c, job, &map_a, &g_trellis_tc_status);
+  if (c.warp < kDenseDw) {
+    // Two row tiles: the (row tile, block) items go to the groups of four warps. One: a group takes
+    // half a block's columns, so that all groups are at work. A warp's lanes are the rows
+    // 32 (warp % 4) .. + 31 of the row tile. What the epilogue needs from global memory is asked
+    // for before the wait for the accumulator, while the last MMAs retire.
     const uint32_t tiles = job.rows > 128u ? 2u : 1u, items = tiles * job.nblk;
     const uint32_t group = static_cast<uint32_t>(c.warp) >> 2, quad = static_cast<uint32_t>(c.warp) & 3u;
     const uint32_t lane = static_cast<uint32_t>(c.lane);
-    float *areas = reinterpret_cast<float *>(smem_raw + (c.base - smem_u32(smem_raw)));
     const bool split = tiles == 1u;
-    for (uint32_t item = split ? 0u : group; item < (split ? 1u : items); item += kDenseDw / 4) {
-      const uint32_t tt = split ? 0u : item / job.nblk, cb = split ? (group & 1u) : item % job.nblk;
-      const bool live = cb < job.nblk;
-      const uint32_t first = tt * 128u + quad * 32u;   // the warp's first row of the job
-      const uint32_t rows = !live || job.rows <= first ? 0u : (job.rows - first < 32u ? job.rows - first : 32u);
-      const bool valid = lane < rows;
-      const uint32_t token0 = job.row0 + first;
-      const uint32_t col0 = (cb == 0u ? job.blk0 : job.blk1) * 128u;
-      const float inv = valid ? p.inv[token0 + lane] : 0.0f;
-      float sv[2][2];   // svh of the four columns a lane writes: [pass][lo, hi] = columns 64 pass + lane, + 32
+    const uint32_t tt = split ? 0u : group / job.nblk, cb = split ? group % kBlocks : group % job.nblk;
+    const uint32_t half = group / kBlocks;   // split jobs: which 64 columns of the block
+    const bool live = split ? cb < job.nblk : group < items;
+    const uint32_t first = tt * 128u + quad * 32u;   // the warp's first row of the job
+    const uint32_t rows = !live || job.rows <= first ? 0u : (job.rows - first < 32u ? job.rows - first : 32u);
+    const bool valid = lane < rows;
+    const uint32_t token0 = job.row0 + first;
+    const uint32_t col0 = (cb == 0u ? job.blk0 : job.blk1) * 128u;
+    const float inv = valid ? p.inv[token0 + lane] : 0.0f;
+    float sv[2][2];   // svh of the four columns a lane writes: [pass][lo, hi] = columns 64 pass + lane, + 32
 #pragma unroll
-      for (int ps = 0; ps < 2; ++ps) {
-        sv[ps][0] = live ? __half2float(__ushort_as_half(__ldg(p.svh + col0 + 64u * ps + lane))) : 0.0f;
-        sv[ps][1] = live ? __half2float(__ushort_as_half(__ldg(p.svh + col0 + 64u * ps + 32u + lane))) : 0.0f;
-      }
+    for (int ps = 0; ps < 2; ++ps) {
+      sv[ps][0] = live ? __half2float(__ushort_as_half(__ldg(p.svh + col0 + 64u * ps + lane))) : 0.0f;
+      sv[ps][1] = live ? __half2float(__ushort_as_half(__ldg(p.svh + col0 + 64u * ps + 32u + lane))) : 0.0f;
+    }
+    if (core_accumulator<kDenseDw>(c, decoded, &g_trellis_tc_status) && (split || live)) {
+      float *areas = reinterpret_cast<float *>(smem_raw + (c.base - smem_u32(smem_raw)));
       uint16_t *out = p.y + static_cast<size_t>(token0) * p.ldy + col0 + lane;
       auto emit = [&](uint32_t ps, uint32_t r, float lo, float hi) {
         uint16_t *dst = out + static_cast<size_t>(r) * p.ldy + 64u * ps;
@@ -145,11 +148,10 @@ __global__ void __launch_bounds__(DenseShape::kThreads, 1) trellis_tc_dense_kern
 #pragma unroll
         for (int e = 0; e < 2; ++e) dst[32 * e] = __bfloat16_as_ushort(__float2bfloat16_rn(v[e]));
       };
-      const uint32_t taddr = c.tmem + ((quad * 32u) << 16) + tt * 256u + cb * 128u;
+      const uint32_t taddr = c.tmem + ((quad * 32u) << 16) + tt * kCols + cb * 128u;
       float *mine = areas + group * 8192u;
-      if (split) half_epilogue<kDenseDw>(taddr, group >> 1, live, inv, valid, mine, areas + (group ^ 2u) * 8192u, quad, lane, rows, emit);
+      if (split) half_epilogue<kDenseDw>(taddr, half, live, inv, valid, mine, areas + (group ^ kBlocks) * 8192u, quad, lane, rows, emit);
       else block_epilogue(taddr, inv, valid, mine, quad, lane, rows, emit);
-      __syncwarp();   // the accumulator loads of the next item are warp-wide
     }
   }
   core_finish<kDenseDw>(c);
@@ -168,8 +170,17 @@ uint64_t trellis_tc_workspace_bytes(uint32_t in, uint32_t weights, uint32_t toke
   return 256u + static_cast<uint64_t>(weights) * (align256(static_cast<uint64_t>(tokens) * in * 2u) + align256(static_cast<uint64_t>(tokens) * 4u));
 }
 
+// Which shape a dense product takes: the narrow one (8 decoder warps, two CTAs per SM), which
+// measured faster at 256, 1024 and 4096 tokens (a decoded tile serves 256 tokens in both, and the
+// narrow CTAs overlap each other's fill, drain and epilogue); B200Q_TRELLIS_TC_SHAPE = 16 selects
+// the wide one (read when the kernels are prepared).
+int g_dense_dw = 8;
+
 int32_t trellis_tc_prepare(ErrorSlot &slot) {
-  cudaError_t err = cudaFuncSetAttribute(trellis_tc_dense_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(DenseShape::kSmemBytes));
+  const char *shape = getenv("B200Q_TRELLIS_TC_SHAPE");
+  g_dense_dw = shape != nullptr && atoi(shape) == 16 ? 16 : 8;
+  cudaError_t err = cudaFuncSetAttribute(trellis_tc_dense_kernel<16>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(Shape<16>::kSmemBytes));
+  if (err == cudaSuccess) err = cudaFuncSetAttribute(trellis_tc_dense_kernel<8>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(Shape<8>::kSmemBytes));
   if (err == cudaSuccess) {
     err = cudaFuncSetAttribute(trellis_rotate_rows_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(kRotateMaxSmem));
   }
@@ -207,8 +218,11 @@ int32_t one_product(ErrorSlot &slot, const DeviceState &dev, const ignis_trellis
   p.tokens = tokens;
   p.ldy = ldy;
   p.epilogue = epilogue;
-  const uint32_t col_tiles = (w->out + 255u) / 256u, row_tiles = (tokens + 255u) / 256u;
-  err = launch(trellis_tc_dense_kernel, dim3(col_tiles * row_tiles), dim3(DenseShape::kThreads), DenseShape::kSmemBytes, stream, dev.pdl != 0, map_a, p);
+  const uint32_t row_tiles = (tokens + 255u) / 256u;
+  const uint32_t wide_ctas = (w->out + 255u) / 256u * row_tiles;
+  err = g_dense_dw == 16 ? launch(trellis_tc_dense_kernel<16>, dim3(wide_ctas), dim3(Shape<16>::kThreads), Shape<16>::kSmemBytes, stream, dev.pdl != 0, map_a, p)
+                 : launch(trellis_tc_dense_kernel<8>, dim3((w->out + 127u) / 128u * row_tiles), dim3(Shape<8>::kThreads), Shape<8>::kSmemBytes, stream,
+                          dev.pdl != 0, map_a, p);
   if (err != cudaSuccess) return fail(slot, "%s: launch failed: %s", what, cudaGetErrorString(err));
   return 0;
 }
