@@ -6,6 +6,8 @@ and max error <= 1e-2 of the token's largest output.
 """
 from __future__ import annotations
 
+import os
+
 import numpy as np
 import pytest
 import torch
@@ -166,6 +168,19 @@ def test_config4_geometry_under_zipf_routing(mo, oracle, k2s):
     acc = mo.experts_prefill(x.cuda(), torch.from_numpy(ids).cuda(), torch.from_numpy(w).cuda(), rec.table, ws)
     assert ws.status() == 0
     got = acc[torch.tensor(sample).cuda()].cpu().numpy().astype(np.float64) * 2.0 ** -32
+    # the expert products' other shape (sixteen decoder warps, 256 columns, one CTA per SM): a row's
+    # arithmetic does not depend on the shape, so the accumulators hold the same integers
+    kept = acc.clone()
+    os.environ["B200Q_MOE_TC_WIDE"] = "1"
+    try:
+        mo.prepare()
+        ws.acc.zero_()
+        wide = mo.experts_prefill(x.cuda(), torch.from_numpy(ids).cuda(), torch.from_numpy(w).cuda(), rec.table, ws)
+        assert ws.status() == 0
+        assert torch.equal(wide, kept)
+    finally:
+        os.environ.pop("B200Q_MOE_TC_WIDE", None)
+        mo.prepare()
 
     def one(t):
         x64 = x[t].double().numpy()

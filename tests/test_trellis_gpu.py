@@ -8,6 +8,8 @@ value), within 2e-3 of the largest output.
 """
 from __future__ import annotations
 
+import os
+
 import numpy as np
 import pytest
 import torch
@@ -355,6 +357,36 @@ def test_tensor_core_route_at_every_bit_width_and_on_column_views(tr, oracle, k2
     view = w.columns(128, 640)                     # four blocks of the seven, through the plane's tile stride
     yv = tr.linear(view, x.cuda(), workspace=ws)
     assert torch.equal(yv, y[:, 128:640])
+
+
+@pytest.mark.parametrize("tokens", [100, 333])   # one row tile (a warp group per half block) and ragged row-tile pairs
+def test_both_shapes_of_the_tensor_core_route_give_the_same_bits(tr, oracle, tokens):
+    """The wide-token route in its default shape (eight decoder warps, 128 columns a CTA, two CTAs per
+    SM) and in the other (sixteen, 256 columns, one per SM): every output element is the same sum in
+    the same order, so the outputs are equal bit for bit; the first is held to the oracle."""
+    from oracle import oracle as orc
+
+    in_, out, k2 = 768, 640, 6
+    rng = np.random.default_rng(tokens)
+    words = oracle.hash_trellis_words(5200 + tokens, in_, out, k2)
+    suh, svh = make_scales(rng, in_, 0.05), make_scales(rng, out, 0.03)
+    inner = oracle.trellis_decode(words, k2, in_, out)
+    w = tr.Weight.from_numpy(words, suh, svh, k2, in_, out)
+    x = torch.randn(tokens, in_, generator=torch.Generator().manual_seed(tokens)).to(torch.bfloat16)
+    ref, s = orc.trellis_project_rows(inner, suh, svh, x.double().numpy())
+    ws = tr.WorkspaceBuffer(tr.workspace_bytes(in_, out, 1, tokens))
+    y = tr.linear(w, x.cuda(), workspace=ws)
+    got = y.float().cpu().numpy().astype(np.float64)
+    assert (np.abs(got - ref) <= 2.0 ** -8 * np.abs(ref) + 2.0 ** -9 * s).all()
+    os.environ["B200Q_TRELLIS_TC_SHAPE"] = "16"
+    try:
+        tr.prepare()
+        y16 = tr.linear(w, x.cuda(), workspace=ws)
+        assert tr.device_status() == 0
+        assert torch.equal(y16, y)
+    finally:
+        os.environ.pop("B200Q_TRELLIS_TC_SHAPE", None)
+        tr.prepare()
 
 
 def test_full_size_gate_projection(tr, oracle):
