@@ -290,6 +290,7 @@ int32_t moe_tc_experts(ErrorSlot &slot, const DeviceState &dev, const ExpertPara
                        const uint32_t *offsets, cudaStream_t stream, const char *what) {
   const bool pdl = dev.pdl != 0;
   const uint32_t tokens = rows / p.top_k;
+  if (p.top_k > 64u) return fail(slot, "%s: more than 64 choices per token on the tensor-core route", what);
   for (int phase = 0; phase < 2; ++phase) {
     const uint32_t in = phase == 0 ? p.hidden : p.inter;
     const uint32_t out_plane = phase == 0 ? 2u * p.inter : p.hidden;
@@ -304,7 +305,6 @@ int32_t moe_tc_experts(ErrorSlot &slot, const DeviceState &dev, const ExpertPara
     err = g_moe_dw == 16 ? launch_gemm<16>(phase, items_max, out_plane, stream, pdl, map_a, p) : launch_gemm<8>(phase, items_max, out_plane, stream, pdl, map_a, p);
     if (err != cudaSuccess) return fail(slot, "%s: expert launch failed: %s", what, cudaGetErrorString(err));
   }
-  if (p.top_k > 64u) return fail(slot, "%s: more than 64 choices per token on the tensor-core route", what);
   const cudaError_t err = launch(moe_tc_fold_kernel, dim3(tokens), dim3(256), 0, stream, pdl, p, tokens);
   if (err != cudaSuccess) return fail(slot, "%s: fold launch failed: %s", what, cudaGetErrorString(err));
   return 0;
