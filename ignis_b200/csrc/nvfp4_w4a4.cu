@@ -56,40 +56,42 @@ struct Tile {
 constexpr uint32_t kStatusProducerTimeout = 1u, kStatusMmaTimeout = 2u, kStatusEpilogueTimeout = 4u;
 
 // ---- activation quantizer, scales in tile order -------------------------------------------------
-// One thread per (token row of the padded range, 64 values): four blocks of 16, i.e. 128 bytes in,
-// 32 bytes of codes and the four scale bytes that lie side by side in a scale tile out. Rows at
-// and beyond `tokens` get zero codes and zero scales.
-__global__ void __launch_bounds__(256) quantize_swizzled_kernel(const uint16_t *x, uint32_t tokens, uint32_t tokens_pad,
-                                                                uint32_t k, float d_in, uint8_t *codes, uint8_t *scales) {
+// One thread per (token row of the padded range, 32 values): two blocks of 16, i.e. 64 bytes in,
+// 16 bytes of codes and two of the four scale bytes that lie side by side in a scale tile out. The
+// kernel is bound by instruction issue as much as by memory (about 13 instructions per value), so a
+// thread is kept small: 48 registers, five CTAs an SM, their load and arithmetic phases interleaved
+// (four blocks a thread at 65 registers and three CTAs: 2.6 % slower on the configs[2] step).
+// Rows at and beyond `tokens` get zero codes and zero scales.
+__global__ void __launch_bounds__(256, 5) quantize_swizzled_kernel(const uint16_t *x, uint32_t tokens, uint32_t tokens_pad,
+                                                                   uint32_t k, float d_in, uint8_t *codes, uint8_t *scales) {
   griddep_launch_dependents();
   griddep_wait();
-  const uint32_t quads = k / 64u;
-  const uint64_t total = static_cast<uint64_t>(tokens_pad) * quads;
-  for (uint64_t qi = blockIdx.x * static_cast<uint64_t>(blockDim.x) + threadIdx.x; qi < total;
-       qi += static_cast<uint64_t>(gridDim.x) * blockDim.x) {
-    const uint32_t t = static_cast<uint32_t>(qi / quads), q = static_cast<uint32_t>(qi % quads);
-    uint2 c[4];
+  const uint32_t halves = k / 32u, quads = k / 64u;
+  const uint64_t total = static_cast<uint64_t>(tokens_pad) * halves;
+  for (uint64_t hi = blockIdx.x * static_cast<uint64_t>(blockDim.x) + threadIdx.x; hi < total;
+       hi += static_cast<uint64_t>(gridDim.x) * blockDim.x) {
+    const uint32_t t = static_cast<uint32_t>(hi / halves), h = static_cast<uint32_t>(hi % halves);
+    uint2 c[2];
     uint32_t sw = 0;
     if (t < tokens) {
-      const uint16_t *src = x + static_cast<uint64_t>(t) * k + q * 64u;
-      uint4 v[8];
+      const uint16_t *src = x + static_cast<uint64_t>(t) * k + h * 32u;
+      uint4 v[4];
 #pragma unroll
-      for (int j = 0; j < 8; ++j) v[j] = ldg128_coherent(src + 8 * j);
+      for (int j = 0; j < 4; ++j) v[j] = ldg128_coherent(src + 8 * j);
 #pragma unroll
-      for (int b = 0; b < 4; ++b) {
+      for (int b = 0; b < 2; ++b) {
         uint8_t s;
         quantize_block16(v[2 * b], v[2 * b + 1], d_in, c[b], s);
         sw |= static_cast<uint32_t>(s) << (8 * b);
       }
     } else {
 #pragma unroll
-      for (int b = 0; b < 4; ++b) c[b] = make_uint2(0u, 0u);
+      for (int b = 0; b < 2; ++b) c[b] = make_uint2(0u, 0u);
     }
-    uint4 *dst = reinterpret_cast<uint4 *>(codes + qi * 32u);
-    dst[0] = make_uint4(c[0].x, c[0].y, c[1].x, c[1].y);
-    dst[1] = make_uint4(c[2].x, c[2].y, c[3].x, c[3].y);
-    const uint64_t so = (static_cast<uint64_t>(t >> 7) * quads + q) * 512u + (t & 31u) * 16u + ((t & 127u) >> 5) * 4u;
-    *reinterpret_cast<uint32_t *>(scales + so) = sw;
+    *reinterpret_cast<uint4 *>(codes + hi * 16u) = make_uint4(c[0].x, c[0].y, c[1].x, c[1].y);
+    const uint32_t q = h >> 1;
+    const uint64_t so = (static_cast<uint64_t>(t >> 7) * quads + q) * 512u + (t & 31u) * 16u + ((t & 127u) >> 5) * 4u + (h & 1u) * 2u;
+    *reinterpret_cast<uint16_t *>(scales + so) = static_cast<uint16_t>(sw);
   }
 }
 
@@ -668,8 +670,8 @@ int32_t w4a4_product(ErrorSlot &slot, const DeviceState &dev, const uint8_t *w_c
                      cudaStream_t stream) {
   const uint32_t pad = w4a4_tokens_pad(tokens);
   if (x != nullptr) {
-    const uint64_t total = static_cast<uint64_t>(pad) * (k / 64u);
-    const uint32_t grid = static_cast<uint32_t>(total / 256u < 148u * 16u ? (total + 255u) / 256u : 148u * 16u);
+    const uint64_t total = static_cast<uint64_t>(pad) * (k / 32u);
+    const uint32_t grid = static_cast<uint32_t>(total / 256u < 148u * 24u ? (total + 255u) / 256u : 148u * 24u);
     const cudaError_t err = launch(quantize_swizzled_kernel, dim3(grid), dim3(256), 0, stream, dev.pdl != 0, x, tokens, pad,
                                    k, d_in, a_codes, a_scales);
     if (err != cudaSuccess) return fail(slot, "nvfp4 activation quantizer launch: %s", cudaGetErrorString(err));
@@ -763,8 +765,8 @@ int32_t w4a4_quantize_range(ErrorSlot &slot, const DeviceState &dev, const uint1
   const uint32_t pad = w4a4_tokens_pad(token_count);
   uint8_t *codes = workspace + 256 + static_cast<uint64_t>(token_begin) * (k / 2u);
   uint8_t *scales = workspace + 256 + pad_total * (k / 2u) + static_cast<uint64_t>(token_begin / 128u) * (k / 64u) * 512u;
-  const uint64_t total = static_cast<uint64_t>(pad) * (k / 64u);
-  const uint32_t grid = static_cast<uint32_t>(total / 256u < 148u * 16u ? (total + 255u) / 256u : 148u * 16u);
+  const uint64_t total = static_cast<uint64_t>(pad) * (k / 32u);
+  const uint32_t grid = static_cast<uint32_t>(total / 256u < 148u * 24u ? (total + 255u) / 256u : 148u * 24u);
   const cudaError_t err = launch(quantize_swizzled_kernel, dim3(grid), dim3(256), 0, stream, dev.pdl != 0, x_rows, token_count, pad, k,
                                  d_in, codes, scales);
   if (err != cudaSuccess) return fail(slot, "nvfp4 activation quantizer launch: %s", cudaGetErrorString(err));
