@@ -249,6 +249,31 @@ def test_absent_records_and_bad_ids_are_skipped_and_reported(mo, oracle):
     check_tokens(acc[:3], ref)
 
 
+@pytest.mark.parametrize("tokens", [6, 40, 150])   # one warp per row; warp-level MMAs; tcgen05 with the fold
+def test_contributions_beyond_the_fixed_point_range_are_skipped_and_reported(mo, oracle, tokens):
+    """A weighted contribution of 2^31 or more in magnitude does not fit the 2^-32 fixed-point
+    accumulator: it is left out and bit 2 of the status word says so (the reference's rule,
+    kernel/include/ignis_moe.h:26-27); every other contribution is added as usual, so the
+    accumulators equal those of a call in which the offending choices carry weight zero."""
+    hidden, inter, experts, top_k = 256, 128, 8, 2
+    mo.set_geometry(hidden, inter, experts, top_k)
+    rng = np.random.default_rng(tokens)
+    rec = Records(mo, oracle, rng, hidden, inter, experts)
+    x = (torch.randn(tokens, hidden, generator=torch.Generator().manual_seed(tokens)) * 0.5).to(torch.bfloat16)
+    ids, w = make_routing(rng, tokens, experts, top_k)
+    loud, quiet = w.copy(), w.copy()
+    for t in (0, tokens // 2, tokens - 1):
+        loud[t, 1] = 3.0e30      # every output of this choice leaves the range
+        quiet[t, 1] = 0.0
+    ws = mo.Workspace(min(8, tokens), tokens)
+    acc = mo.experts_prefill(x.cuda(), torch.from_numpy(ids).cuda(), torch.from_numpy(loud).cuda(), rec.table, ws).clone()
+    assert ws.status() == 4
+    ws2 = mo.Workspace(min(8, tokens), tokens)
+    want = mo.experts_prefill(x.cuda(), torch.from_numpy(ids).cuda(), torch.from_numpy(quiet).cuda(), rec.table, ws2)
+    assert ws2.status() == 0
+    assert torch.equal(acc[:tokens], want[:tokens])
+
+
 def test_router_matches_a_torch_model(mo):
     mo.set_geometry(256, 128, 64, 6)
     gen = torch.Generator().manual_seed(3)
