@@ -139,7 +139,7 @@ def zipf_routing(tokens, experts, top_k, seed):
 
 @pytest.mark.parametrize("k2s", [(5, 5, 5, 5), (4, 5, 6, 8)])   # configs[4]'s 2.5 bits per weight; the reference's mix of widths
 def test_config4_geometry_under_zipf_routing(mo, oracle, k2s):
-    """BASELINE configs[4]'s geometry - 512 experts of 2048 -> 768 -> 2048, top-10, Zipf(1.1) - at
+    """The benchmark's configs[4]'s geometry - 512 experts of 2048 -> 768 -> 2048, top-10, Zipf(1.1) - at
     1024 tokens through the prefill entry, the routed sum held to the fp64 reference on a sample of
     tokens chosen for the shapes of work the skew produces (kernel/tests/test_moe_experts.cu:75-91):
     the token of one singleton expert, 24 tokens of an expert that fills one 64-row item and part of

@@ -170,7 +170,7 @@ def test_a16_tensor_core_route(nv, oracle, tokens, n, k):
 
 
 def test_config0_full_size(nv, oracle):
-    """BASELINE configs[0]: M = 1, K = 5120, N = 17408, tensor scale 1/448."""
+    """The benchmark's configs[0]: M = 1, K = 5120, N = 17408, tensor scale 1/448."""
     n, k = 17408, 5120
     rng = np.random.default_rng(20261125)
     codes, scales, d_w = make_weight(rng, n, k)
@@ -182,7 +182,7 @@ def test_config0_full_size(nv, oracle):
 
 
 def test_config2_full_size_sampled(nv, oracle):
-    """BASELINE configs[2] at its full size (M = 8192, up 5120 -> 17408, W4A4): the whole product on
+    """The benchmark's configs[2] at its full size (M = 8192, up 5120 -> 17408, W4A4): the whole product on
     the device, checked against the host arithmetic on sampled row tiles x tokens (first, last and
     interior tiles of both dimensions), and through a size-independent property - a product over
     the same weights with the tokens reversed is the reversed product, bit for bit."""
@@ -208,7 +208,7 @@ def test_config2_full_size_sampled(nv, oracle):
 
 
 def test_config2_down_full_size_sampled(nv, oracle):
-    """BASELINE configs[2]'s second product at its full size (M = 8192, down 17408 -> 5120, W4A4):
+    """The benchmark's configs[2]'s second product at its full size (M = 8192, down 17408 -> 5120, W4A4):
     sampled row tiles x tokens against the host arithmetic (first, last and interior tiles of both
     dimensions; K = 17408 is 68 stages of the ring), and the token-reversal property."""
     tokens, n, k = 8192, 5120, 17408
