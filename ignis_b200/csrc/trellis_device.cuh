@@ -80,11 +80,13 @@ __device__ __forceinline__ void hadamard128(float (&v)[4], int lane) {
   v[3] = b - d;
 #pragma unroll
   for (int m = 1; m < 32; m <<= 1) {
-    const bool upper = (lane & m) != 0;
+    // the upper lane of a pair keeps (other - own), the lower (own + other): one fused multiply-add by
+    // -1 or +1 gives either, rounded once like the subtraction or the addition it stands for
+    const float sign = (lane & m) != 0 ? -1.0f : 1.0f;
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
       const float o = __shfl_xor_sync(0xFFFFFFFFu, v[i], m);
-      v[i] = upper ? o - v[i] : v[i] + o;
+      v[i] = __fmaf_rn(sign, v[i], o);
     }
   }
 #pragma unroll
