@@ -65,3 +65,26 @@ def test_fp8_row_scale_payload_is_byte_for_byte_the_reference_encoders(golden):
     assert sizes == g["payload_bytes_256x512_48x2560_3x100"].tolist() == [131584, 122976, 518]
     zero = moe.fp8_row_scale_payload(torch.zeros(2, 32))
     assert not zero[:64].any() and zero[256:260].view(np.uint16).tolist() == [0x3F80, 0x3F80]   # scale 1.0
+
+
+def test_workspace_holds_the_weighted_down_rows_of_wide_calls():
+    """The workspace query is host arithmetic (no GPU): beyond 8 prefill tokens it includes the fp32
+    rows [token][choice][hidden] the tensor-core route writes before they are folded into the
+    accumulator; decode-sized workspaces do not pay for them; the plan's workspace line is the
+    same number."""
+    import ctypes as C
+
+    from ignis_b200 import _lib, moe
+
+    lib = _lib.load()
+    geometry = moe.Geometry(2048, 768, 512, 10)
+    gs = geometry.c_struct()
+
+    def nbytes(decode, prefill):
+        return int(lib.b200q_moe_workspace_bytes(C.byref(gs), decode, prefill))
+
+    rows_region = 4 * 4096 * 10 * 2048
+    assert nbytes(8, 4096) >= rows_region + 8 * 4096 * 10 * 768      # + the gate|up products
+    assert nbytes(8, 8) < 64 << 20                                     # a decode block stays small
+    assert nbytes(8, 4096) > nbytes(8, 2048) > nbytes(8, 8)
+    assert moe.plan_bytes(8, 4096, geometry)["workspace"] == nbytes(8, 4096)
