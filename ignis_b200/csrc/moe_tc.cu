@@ -105,8 +105,8 @@ __global__ void __launch_bounds__(256) moe_tc_rotate_kernel(const __grid_constan
   }
 }
 
-// PHASE 0: gate | up products of an item into gu. PHASE 1: down, weighted, into acc.
-// One CTA per (item, 256 output columns); no CTA waits for another.
+// PHASE 0: gate | up products of an item into gu. PHASE 1: down, weighted, into the rows the fold
+// kernel adds up. One CTA per (item, 16 DW output columns); no CTA waits for another.
 template <int PHASE, int DW>
 __global__ void __launch_bounds__(Shape<DW>::kThreads, DW == 16 ? 1 : 2) moe_tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a,
                                                                  const __grid_constant__ ExpertParams p) {
