@@ -26,13 +26,18 @@ namespace {
 
 using namespace trellis_tc;
 
-// One CTA per sorted row: the row's `in` values times the expert's suh, the 128-wide Hadamard per
-// block (a warp per block), one power-of-two scale per row (largest magnitude in [2^13, 2^14)),
-// fp16. PHASE 0 reads the token's activations, PHASE 1 silu(g) u of the row's gate|up products.
+constexpr uint32_t kRotateThreads = 128;
+
+// One CTA of four warps per sorted row: the row's `in` values times the expert's suh, the 128-wide
+// Hadamard per block (a warp per block), one power-of-two scale per row (largest magnitude in
+// [2^13, 2^14)), fp16. PHASE 0 reads the token's activations, PHASE 1 silu(g) u of the row's gate|up
+// products. The kernel is bound by instruction issue, and what every warp repeats for its row (the
+// walk to the expert's record, the row maximum, the scale) weighs as much as the transforms: hence
+// four warps a row rather than eight, and the scale from the maximum's exponent bits.
 template <int PHASE>
-__global__ void __launch_bounds__(256) moe_tc_rotate_kernel(const __grid_constant__ ExpertParams p, const uint32_t *offsets) {
+__global__ void __launch_bounds__(kRotateThreads) moe_tc_rotate_kernel(const __grid_constant__ ExpertParams p, const uint32_t *offsets) {
   extern __shared__ __align__(16) float rot[];
-  __shared__ float warp_max[8];
+  __shared__ float warp_max[kRotateThreads / 32];
   griddep_launch_dependents();
   griddep_wait();
   const uint32_t row = blockIdx.x;
@@ -46,7 +51,7 @@ __global__ void __launch_bounds__(256) moe_tc_rotate_kernel(const __grid_constan
   float *inv = reinterpret_cast<float *>(PHASE == 0 ? p.scale_in : p.scale_h) + row;
   if (slot.record == nullptr || !(slot.k2 == 4 || slot.k2 == 5 || slot.k2 == 6 || slot.k2 == 8)) {
     // an absent record: the product kernel flags it and skips the item; leave finite rows behind
-    for (uint32_t i = threadIdx.x * 4u; i < in; i += 1024u) *reinterpret_cast<uint2 *>(dst + i) = make_uint2(0u, 0u);
+    for (uint32_t i = threadIdx.x * 4u; i < in; i += 4u * kRotateThreads) *reinterpret_cast<uint2 *>(dst + i) = make_uint2(0u, 0u);
     if (threadIdx.x == 0) *inv = 0.0f;
     return;
   }
@@ -56,7 +61,7 @@ __global__ void __launch_bounds__(256) moe_tc_rotate_kernel(const __grid_constan
   const uint32_t token = a / p.top_k;
   const uint32_t nblk = in / 128u;
   float m = 0.0f;
-  for (uint32_t bl = static_cast<uint32_t>(warp); bl < nblk; bl += 8u) {
+  for (uint32_t bl = static_cast<uint32_t>(warp); bl < nblk; bl += kRotateThreads / 32u) {
     const size_t k0 = static_cast<size_t>(bl) * 128u + 4u * lane;
     const uint2 sb = *reinterpret_cast<const uint2 *>(suh + k0);
     const __half2 s01 = *reinterpret_cast<const __half2 *>(&sb.x), s23 = *reinterpret_cast<const __half2 *>(&sb.y);
@@ -86,16 +91,13 @@ __global__ void __launch_bounds__(256) moe_tc_rotate_kernel(const __grid_constan
   __syncthreads();
   m = warp_max[0];
 #pragma unroll
-  for (int i = 1; i < 8; ++i) m = fmaxf(m, warp_max[i]);
+  for (uint32_t i = 1; i < kRotateThreads / 32u; ++i) m = fmaxf(m, warp_max[i]);
+  // m in [2^(e-1), 2^e) with e = (exponent field) - 126: the scale 2^(14 - e), held to what a float carries
   int shift = 0;
-  if (m > 0.0f && m <= 3.0e38f) {
-    int e;
-    (void)frexpf(m, &e);
-    shift = max(-126, min(126, 14 - e));
-  }
-  const float scale = ldexpf(1.0f, shift);
-  if (threadIdx.x == 0) *inv = ldexpf(1.0f, -shift);
-  for (uint32_t i = threadIdx.x * 4u; i < in; i += 1024u) {
+  if (m > 0.0f && m <= 3.0e38f) shift = max(-126, min(126, 140 - static_cast<int>(__float_as_uint(m) >> 23)));
+  const float scale = __uint_as_float(static_cast<uint32_t>(shift + 127) << 23);
+  if (threadIdx.x == 0) *inv = __uint_as_float(static_cast<uint32_t>(127 - shift) << 23);
+  for (uint32_t i = threadIdx.x * 4u; i < in; i += 4u * kRotateThreads) {
     const float4 v = *reinterpret_cast<const float4 *>(rot + i);
     const __half2 h01 = __floats2half2_rn(v.x * scale, v.y * scale), h23 = __floats2half2_rn(v.z * scale, v.w * scale);
     uint2 packed;
@@ -295,8 +297,8 @@ int32_t moe_tc_experts(ErrorSlot &slot, const DeviceState &dev, const ExpertPara
     const uint32_t in = phase == 0 ? p.hidden : p.inter;
     const uint32_t out_plane = phase == 0 ? 2u * p.inter : p.hidden;
     if (static_cast<size_t>(in) * 4u > kRotateSmemMax) return fail(slot, "%s: a dimension is too long for the tensor-core route", what);
-    cudaError_t err = phase == 0 ? launch(moe_tc_rotate_kernel<0>, dim3(rows), dim3(256), static_cast<size_t>(in) * 4u, stream, pdl, p, offsets)
-                                 : launch(moe_tc_rotate_kernel<1>, dim3(rows), dim3(256), static_cast<size_t>(in) * 4u, stream, pdl, p, offsets);
+    cudaError_t err = phase == 0 ? launch(moe_tc_rotate_kernel<0>, dim3(rows), dim3(kRotateThreads), static_cast<size_t>(in) * 4u, stream, pdl, p, offsets)
+                                 : launch(moe_tc_rotate_kernel<1>, dim3(rows), dim3(kRotateThreads), static_cast<size_t>(in) * 4u, stream, pdl, p, offsets);
     if (err != cudaSuccess) return fail(slot, "%s: rotation launch failed: %s", what, cudaGetErrorString(err));
     CUtensorMap map_a;
     if (!make_rows_map(&map_a, phase == 0 ? static_cast<const void *>(p.frag_in) : static_cast<const void *>(p.frag_h), rows, in)) {
