@@ -26,14 +26,15 @@ namespace {
 
 using namespace trellis_tc;
 
-constexpr uint32_t kRotateThreads = 128;
+constexpr uint32_t kRotateThreads = 64;
 
-// One CTA of four warps per sorted row: the row's `in` values times the expert's suh, the 128-wide
+// One CTA of two warps per sorted row: the row's `in` values times the expert's suh, the 128-wide
 // Hadamard per block (a warp per block), one power-of-two scale per row (largest magnitude in
 // [2^13, 2^14)), fp16. PHASE 0 reads the token's activations, PHASE 1 silu(g) u of the row's gate|up
 // products. The kernel is bound by instruction issue, and what every warp repeats for its row (the
 // walk to the expert's record, the row maximum, the scale) weighs as much as the transforms: hence
-// four warps a row rather than eight, and the scale from the maximum's exponent bits.
+// two warps a row (eight: 147 + 132 us for 40 960 rows of 2048 and 768 inputs; four: 106 + 91; two: a
+// further 1.4 % on the step), and the scale from the maximum's exponent bits.
 template <int PHASE>
 __global__ void __launch_bounds__(kRotateThreads) moe_tc_rotate_kernel(const __grid_constant__ ExpertParams p, const uint32_t *offsets) {
   extern __shared__ __align__(16) float rot[];
