@@ -55,14 +55,11 @@ __global__ void __launch_bounds__(256) trellis_rotate_rows_kernel(const uint16_t
   m = warp_max[0];
 #pragma unroll
   for (int i = 1; i < 8; ++i) m = fmaxf(m, warp_max[i]);
+  // m in [2^(e-1), 2^e) with e = (exponent field) - 126: the scale 2^(14 - e), held to what a float carries
   int shift = 0;
-  if (m > 0.0f && m <= 3.0e38f) {
-    int e;
-    (void)frexpf(m, &e);  // m in [2^(e-1), 2^e)
-    shift = max(-126, min(126, 14 - e));
-  }
-  const float scale = ldexpf(1.0f, shift);
-  if (threadIdx.x == 0) inv[token] = ldexpf(1.0f, -shift);
+  if (m > 0.0f && m <= 3.0e38f) shift = max(-126, min(126, 140 - static_cast<int>(__float_as_uint(m) >> 23)));
+  const float scale = __uint_as_float(static_cast<uint32_t>(shift + 127) << 23);
+  if (threadIdx.x == 0) inv[token] = __uint_as_float(static_cast<uint32_t>(127 - shift) << 23);
   uint16_t *dst = rows_f16 + static_cast<size_t>(token) * in;
   for (uint32_t i = threadIdx.x * 4u; i < in; i += 1024u) {
     const float4 v = *reinterpret_cast<const float4 *>(rot + i);
